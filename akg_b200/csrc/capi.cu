@@ -1,0 +1,374 @@
+// C ABI + runtime launcher.  Replaces the generated CUDA-driver launcher of the
+// reference (akg-mlir/python/akg_mlir/utils/code_template.py:16-211): instead of
+// creating a context, JIT-ing PTX and allocating per call, a compiled kernel
+// object keeps its plan and (for the host-pointer entry points) its device
+// staging buffers, and launches are asynchronous on the caller's stream.
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "../../include/akgb.h"
+#include "graph.hpp"
+#include "kernels.hpp"
+#include "plan.hpp"
+
+using namespace akgb;
+
+namespace {
+thread_local std::string g_err;
+akgb_status fail(akgb_status st, const std::string& msg) {
+  g_err = msg;
+  return st;
+}
+akgb_status cuda_fail(cudaError_t e, const char* what) {
+  return fail(AKGB_CUDA_ERROR, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+  std::mutex mu;
+  void* gelu_lut = nullptr;   // device copy of the f16 tanh table
+  uint32_t* err_word = nullptr;
+  int sm_count = 0;
+};
+DeviceState g_dev[kMaxDevices];
+
+int query_sm_count(int device) {
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    return 148;  // planning without a device: a B200 has 148 SMs
+  }
+  return n;
+}
+}  // namespace
+
+struct akgb_kernel {
+  Graph graph;
+  Plan plan;
+  int device = 0;
+  int sm_count = 148;
+  int shard_rank = 0, shard_world = 1;
+  std::vector<akgb_tensor_desc> descs;
+  int n_inputs = 0;
+  // host-pointer entry points: staging buffers kept between calls
+  std::vector<void*> d_tensors;
+  void* d_workspace = nullptr;
+  cudaStream_t stream = nullptr;
+  bool staged = false;
+};
+
+namespace {
+
+akgb_status ensure_device_state(akgb_kernel* k) {
+  int dev = k->device;
+  if (dev < 0 || dev >= kMaxDevices) return fail(AKGB_INVALID_ARG, "device ordinal out of range");
+  DeviceState& ds = g_dev[dev];
+  std::lock_guard<std::mutex> lock(ds.mu);
+  if (k->plan.needs_gelu_lut && !ds.gelu_lut) {
+    std::vector<uint16_t> h(gelu_lut_entries());
+    gelu_lut_build(h.data());
+    void* d = nullptr;
+    cudaError_t e = cudaMalloc(&d, h.size() * sizeof(uint16_t));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(tanh table)");
+    e = cudaMemcpy(d, h.data(), h.size() * sizeof(uint16_t), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(tanh table)");
+    ds.gelu_lut = d;
+  }
+  if (!ds.err_word) {
+    void* d = nullptr;
+    cudaError_t e = cudaMalloc(&d, 256);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(error word)");
+    e = cudaMemset(d, 0, 256);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemset(error word)");
+    ds.err_word = reinterpret_cast<uint32_t*>(d);
+  }
+  return AKGB_OK;
+}
+
+void* resolve(const Ref& r, void* const* tensors, void* ws) {
+  if (r.arg >= 0) return tensors[r.arg];
+  if (r.ws_off >= 0) return reinterpret_cast<char*>(ws) + r.ws_off;
+  return nullptr;
+}
+
+akgb_status run_plan(akgb_kernel* k, void* const* tensors, void* ws, cudaStream_t s) {
+  DeviceState& ds = g_dev[k->device];
+  for (Step& st : k->plan.steps) {
+    cudaError_t e = cudaSuccess;
+    void* a = resolve(st.a, tensors, ws);
+    void* b = resolve(st.b, tensors, ws);
+    void* c = resolve(st.c, tensors, ws);
+    void* o = resolve(st.out, tensors, ws);
+    void* o2 = resolve(st.out2, tensors, ws);
+    void* o3 = resolve(st.out3, tensors, ws);
+    void* scratch = resolve(st.scratch, tensors, ws);
+    switch (st.kind) {
+      case StepK::GeluChain:
+        e = gelu_chain_f16(st.gelu, a, b, c, o, ds.gelu_lut, s, &st.dims);
+        break;
+      case StepK::LayerNorm:
+        e = layernorm_f32(st.ln, (const float*)a, (const float*)b, (const float*)c, (float*)o, (float*)o2, (float*)o3, s,
+                          &st.dims);
+        break;
+      case StepK::Softmax:
+        e = softmax_rows(st.sm, a, b, o, s, &st.dims);
+        break;
+      case StepK::ReduceCol:
+        e = reduce_col_f32(st.red_op, (const float*)a, (float*)o, st.red_len, st.red_inner, scratch, k->sm_count, s,
+                           &st.dims);
+        break;
+      case StepK::ReduceAll:
+        e = reduce_all_f32(st.red_op, (const float*)a, (float*)o, st.red_len, scratch, k->sm_count, s, &st.dims);
+        break;
+      case StepK::ReduceRow:
+        e = reduce_row_f32(st.red_op, (const float*)a, (float*)o, st.red_outer, st.red_len, s, &st.dims);
+        break;
+      case StepK::Transpose:
+        e = transpose_nd(st.tp, a, o, s, &st.dims);
+        break;
+      case StepK::Matmul:
+        e = matmul_bf16(st.mm, a, b, c, o, ds.err_word, k->sm_count, s, &st.dims);
+        break;
+    }
+    if (e != cudaSuccess) return cuda_fail(e, st.kernel_name.c_str());
+  }
+  return AKGB_OK;
+}
+
+int launches_of(const akgb_kernel* k) {
+  int n = 0;
+  for (const Step& st : k->plan.steps) {
+    switch (st.kind) {
+      case StepK::ReduceCol:
+        n += reduce_col_workspace(st.red_len, st.red_inner, k->sm_count) ? 2 : 1;
+        break;
+      case StepK::ReduceAll:
+        n += 2;
+        break;
+      case StepK::GeluChain:
+        n += (st.gelu.n % 8) ? 2 : 1;
+        break;
+      default:
+        n += 1;
+    }
+  }
+  return n;
+}
+
+akgb_status stage(akgb_kernel* k) {
+  if (k->staged) return AKGB_OK;
+  cudaError_t e = cudaSetDevice(k->device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  k->d_tensors.assign(k->descs.size(), nullptr);
+  for (size_t i = 0; i < k->descs.size(); ++i) {
+    size_t bytes = (size_t)std::max<int64_t>(k->descs[i].nbytes, 16);
+    e = cudaMalloc(&k->d_tensors[i], bytes);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(staging tensor)");
+  }
+  if (k->plan.workspace_bytes) {
+    e = cudaMalloc(&k->d_workspace, k->plan.workspace_bytes);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(workspace)");
+  }
+  e = cudaStreamCreateWithFlags(&k->stream, cudaStreamNonBlocking);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamCreate");
+  k->staged = true;
+  return AKGB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* akgb_last_error(void) { return g_err.c_str(); }
+const char* akgb_version(void) { return "akgb 0.1 (sm_100a)"; }
+
+akgb_status akgb_compile(const char* info_json, size_t len, const akgb_options* opt, akgb_kernel** out) {
+  if (!info_json || !out) return fail(AKGB_INVALID_ARG, "null argument");
+  *out = nullptr;
+  int device = -1, rank = 0, world = 1;
+  if (opt) {
+    if (opt->struct_size < (int32_t)sizeof(akgb_options)) return fail(AKGB_INVALID_ARG, "akgb_options.struct_size");
+    device = opt->device;
+    rank = opt->shard_rank;
+    world = opt->shard_world <= 0 ? 1 : opt->shard_world;
+  }
+  if (device < 0) {
+    if (cudaGetDevice(&device) != cudaSuccess) {
+      cudaGetLastError();
+      device = 0;
+    }
+  }
+  akgb_kernel* k = nullptr;
+  try {
+    k = new akgb_kernel();
+    k->device = device;
+    k->sm_count = query_sm_count(device);
+    k->shard_rank = rank;
+    k->shard_world = world;
+    k->graph = parse_info(info_json, len);
+    infer_sharding(k->graph, rank, world);
+    k->plan = build_plan(k->graph, k->sm_count);
+    const Graph& g = k->graph;
+    k->n_inputs = (int)g.inputs.size();
+    auto add = [&](int vid, bool is_out) {
+      const Value& v = g.v(vid);
+      akgb_tensor_desc d;
+      std::memset(&d, 0, sizeof(d));
+      std::snprintf(d.name, sizeof(d.name), "%s", v.name.c_str());
+      d.dtype = (int32_t)v.dt;
+      d.rank = (int32_t)std::min<size_t>(v.shape.size(), AKGB_MAX_RANK);
+      if (v.shape.size() > AKGB_MAX_RANK) throw Unsupported("tensor rank above 8");
+      for (int i = 0; i < d.rank; ++i) d.shape[i] = v.shape[i];
+      d.nbytes = v.numel() * (int64_t)dt_size(v.dt);
+      d.is_output = is_out;
+      d.shard_kind = v.partial ? v.partial : (v.split0 ? AKGB_SPLIT_AXIS0 : AKGB_REPLICATED);
+      k->descs.push_back(d);
+    };
+    for (int vid : g.inputs) add(vid, false);
+    for (int vid : g.outputs) add(vid, true);
+  } catch (const JsonError& e) {
+    delete k;
+    return fail(AKGB_INVALID_JSON, e.what());
+  } catch (const Unsupported& e) {
+    delete k;
+    return fail(AKGB_UNSUPPORTED, e.what());
+  } catch (const std::exception& e) {
+    delete k;
+    return fail(AKGB_INVALID_ARG, e.what());
+  }
+  *out = k;
+  return AKGB_OK;
+}
+
+void akgb_release(akgb_kernel* k) {
+  if (!k) return;
+  if (k->staged) {
+    cudaSetDevice(k->device);
+    for (void* p : k->d_tensors)
+      if (p) cudaFree(p);
+    if (k->d_workspace) cudaFree(k->d_workspace);
+    if (k->stream) cudaStreamDestroy(k->stream);
+  }
+  delete k;
+}
+
+int32_t akgb_num_tensors(const akgb_kernel* k) { return k ? (int32_t)k->descs.size() : 0; }
+int32_t akgb_num_inputs(const akgb_kernel* k) { return k ? k->n_inputs : 0; }
+
+akgb_status akgb_tensor_info(const akgb_kernel* k, int32_t index, akgb_tensor_desc* out) {
+  if (!k || !out) return fail(AKGB_INVALID_ARG, "null argument");
+  if (index < 0 || index >= (int32_t)k->descs.size()) return fail(AKGB_INVALID_ARG, "tensor index out of range");
+  *out = k->descs[index];
+  return AKGB_OK;
+}
+
+size_t akgb_workspace_size(const akgb_kernel* k) { return k ? k->plan.workspace_bytes : 0; }
+int32_t akgb_launch_count(const akgb_kernel* k) { return k ? launches_of(k) : 0; }
+const char* akgb_kernel_class(const akgb_kernel* k) { return k ? k->plan.klass.c_str() : ""; }
+int64_t akgb_kernel_bytes(const akgb_kernel* k) { return k ? k->plan.bytes : 0; }
+int64_t akgb_kernel_flops(const akgb_kernel* k) { return k ? k->plan.flops : 0; }
+
+akgb_status akgb_launch(akgb_kernel* k, void* const* tensors, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!k || !tensors) return fail(AKGB_INVALID_ARG, "null argument");
+  if (workspace_bytes < k->plan.workspace_bytes || (k->plan.workspace_bytes && !workspace))
+    return fail(AKGB_INVALID_ARG, "workspace smaller than akgb_workspace_size()");
+  for (size_t i = 0; i < k->descs.size(); ++i) {
+    if (!tensors[i] && k->descs[i].nbytes) return fail(AKGB_INVALID_ARG, "null tensor pointer");
+  }
+  if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return fail(AKGB_MISALIGNED, "workspace must be 256-byte aligned");
+  akgb_status st = ensure_device_state(k);
+  if (st != AKGB_OK) return st;
+  return run_plan(k, tensors, workspace, reinterpret_cast<cudaStream_t>(stream));
+}
+
+akgb_status akgb_run_host(akgb_kernel* k, void* const* host) {
+  if (!k || !host) return fail(AKGB_INVALID_ARG, "null argument");
+  akgb_status st = stage(k);
+  if (st != AKGB_OK) return st;
+  st = ensure_device_state(k);
+  if (st != AKGB_OK) return st;
+  cudaError_t e;
+  for (int i = 0; i < k->n_inputs; ++i) {
+    if (!k->descs[i].nbytes) continue;
+    e = cudaMemcpyAsync(k->d_tensors[i], host[i], (size_t)k->descs[i].nbytes, cudaMemcpyHostToDevice, k->stream);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(H2D)");
+  }
+  st = run_plan(k, k->d_tensors.data(), k->d_workspace, k->stream);
+  if (st != AKGB_OK) return st;
+  for (size_t i = k->n_inputs; i < k->descs.size(); ++i) {
+    if (!k->descs[i].nbytes) continue;
+    e = cudaMemcpyAsync(host[i], k->d_tensors[i], (size_t)k->descs[i].nbytes, cudaMemcpyDeviceToHost, k->stream);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(D2H)");
+  }
+  e = cudaStreamSynchronize(k->stream);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+  return AKGB_OK;
+}
+
+akgb_status akgb_profile_host(akgb_kernel* k, void* const* host, int32_t number, int32_t repeat, double* avg_us) {
+  if (!k || !host || !avg_us || number <= 0 || repeat <= 0) return fail(AKGB_INVALID_ARG, "bad argument");
+  akgb_status st = akgb_run_host(k, host);  // stages, copies inputs, one warm-up launch
+  if (st != AKGB_OK) return st;
+  cudaEvent_t t0, t1;
+  cudaEventCreate(&t0);
+  cudaEventCreate(&t1);
+  cudaEventRecord(t0, k->stream);
+  for (int i = 0; i < number * repeat; ++i) {
+    st = run_plan(k, k->d_tensors.data(), k->d_workspace, k->stream);
+    if (st != AKGB_OK) break;
+  }
+  cudaEventRecord(t1, k->stream);
+  cudaError_t e = cudaEventSynchronize(t1);
+  float ms = 0.f;
+  if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, t0, t1);
+  cudaEventDestroy(t0);
+  cudaEventDestroy(t1);
+  if (st != AKGB_OK) return st;
+  if (e != cudaSuccess) return cuda_fail(e, "profiling");
+  *avg_us = (double)ms * 1000.0 / ((double)number * repeat);
+  return AKGB_OK;
+}
+
+akgb_status akgb_check_device_error(akgb_kernel* k, uint32_t* word) {
+  if (!k || !word) return fail(AKGB_INVALID_ARG, "null argument");
+  *word = 0;
+  DeviceState& ds = g_dev[k->device];
+  if (!ds.err_word) return AKGB_OK;
+  cudaError_t e = cudaMemcpy(word, ds.err_word, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(error word)");
+  if (*word) {
+    cudaMemset(ds.err_word, 0, sizeof(uint32_t));
+    return fail(AKGB_DEVICE_TIMEOUT, "a bounded device-side wait gave up");
+  }
+  return AKGB_OK;
+}
+
+akgb_status akgb_kernel_meta(const akgb_kernel* k, char* buf, size_t cap, size_t* needed) {
+  if (!k) return fail(AKGB_INVALID_ARG, "null argument");
+  // the keys the reference writes to <kernel>.json (GPUMapping.cpp:645-703,
+  // mlir_driver.py:776-815); grid/block are those of the dominant (first) step
+  const Step& st = k->plan.steps.front();
+  LaunchDims d = st.dims;
+  std::ostringstream o;
+  o << "{\"kernelName\": \"" << k->graph.kernel_name << "_kernel\", "
+    << "\"blockIdx.x\": " << d.grid[0] << ", \"blockIdx.y\": " << d.grid[1] << ", \"blockIdx.z\": " << d.grid[2]
+    << ", \"threadIdx.x\": " << d.block[0] << ", \"threadIdx.y\": " << d.block[1]
+    << ", \"threadIdx.z\": " << d.block[2] << ", \"is_dynamic\": false, \"sha256\": \"" << k->graph.sha256_hex
+    << "\", \"class\": \"" << k->plan.klass << "\", \"template\": \"" << st.kernel_name
+    << "\", \"bytes\": " << k->plan.bytes << ", \"flops\": " << k->plan.flops << ", \"smem\": " << d.smem
+    << ", \"workspace\": " << k->plan.workspace_bytes << ", \"launches\": " << launches_of(k) << "}";
+  std::string s = o.str();
+  if (needed) *needed = s.size() + 1;
+  if (!buf || cap < s.size() + 1) return buf ? fail(AKGB_INVALID_ARG, "buffer too small") : AKGB_OK;
+  std::memcpy(buf, s.c_str(), s.size() + 1);
+  return AKGB_OK;
+}
+
+}  // extern "C"

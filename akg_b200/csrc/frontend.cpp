@@ -1,0 +1,476 @@
+// JSON front end, class tagging and leading-axis shard inference.
+#include <algorithm>
+#include <cstring>
+#include <set>
+
+#include "graph.hpp"
+
+namespace akgb {
+
+const char* dt_name(DT d) {
+  switch (d) {
+    case DT::Bool: return "bool";
+    case DT::I8: return "int8";
+    case DT::I16: return "int16";
+    case DT::I32: return "int32";
+    case DT::I64: return "int64";
+    case DT::F16: return "float16";
+    case DT::F32: return "float32";
+    case DT::F64: return "float64";
+    case DT::BF16: return "bfloat16";
+    default: return "invalid";
+  }
+}
+
+DT dt_from_name(const std::string& s) {
+  if (s == "bool" || s == "int1") return DT::Bool;
+  if (s == "int8" || s == "uint8" || s == "sint8") return DT::I8;
+  if (s == "int16") return DT::I16;
+  if (s == "int32") return DT::I32;
+  if (s == "int64") return DT::I64;
+  if (s == "float16") return DT::F16;
+  if (s == "float32") return DT::F32;
+  if (s == "float64") return DT::F64;
+  if (s == "bfloat16") return DT::BF16;
+  return DT::Invalid;
+}
+
+namespace {
+struct OpEntry {
+  const char* name;
+  OpK kind;
+};
+// JSON operator names the reference's factory knows
+// (TranslateToMindsporeDialect.cpp:417-486) that this library places on
+// kernels; every other name is kept as OpK::Unknown, like the reference's
+// UnknownOp (:939-946), and rejected by the matcher.
+const OpEntry kOps[] = {
+    {"Abs", OpK::Abs},           {"Neg", OpK::Neg},           {"Exp", OpK::Exp},
+    {"Log", OpK::Log},           {"Tanh", OpK::Tanh},         {"Rsqrt", OpK::Rsqrt},
+    {"Sqrt", OpK::Sqrt},         {"Reciprocal", OpK::Reciprocal}, {"Floor", OpK::Floor},
+    {"Square", OpK::Square},     {"Sin", OpK::Sin},           {"Cos", OpK::Cos},
+    {"Asinh", OpK::Asinh},       {"Acosh", OpK::Acosh},       {"Atan", OpK::Atan},
+    {"ASin", OpK::ASin},         {"ACos", OpK::ACos},         {"IsInf", OpK::IsInf},
+    {"IsFinite", OpK::IsFinite}, {"IsNan", OpK::IsNan},       {"LogicalNot", OpK::LogicalNot},
+    {"Cast", OpK::Cast},         {"Add", OpK::Add},           {"TensorAdd", OpK::Add},
+    {"Sub", OpK::Sub},           {"Mul", OpK::Mul},           {"Div", OpK::Div},
+    {"RealDiv", OpK::Div},       {"Maximum", OpK::Maximum},   {"Minimum", OpK::Minimum},
+    {"Pow", OpK::Pow},           {"Atan2", OpK::Atan2},       {"Equal", OpK::Equal},
+    {"NotEqual", OpK::NotEqual}, {"Greater", OpK::Greater},   {"GreaterEqual", OpK::GreaterEqual},
+    {"Less", OpK::Less},         {"LessEqual", OpK::LessEqual}, {"LogicalAnd", OpK::LogicalAnd},
+    {"LogicalOr", OpK::LogicalOr}, {"Select", OpK::Select},   {"BroadcastTo", OpK::BroadcastTo},
+    {"Reshape", OpK::Reshape},   {"Transpose", OpK::Transpose}, {"ReduceSum", OpK::ReduceSum},
+    {"ReduceMax", OpK::ReduceMax}, {"ReduceMin", OpK::ReduceMin}, {"ReducePrd", OpK::ReduceProd},
+    {"ReduceProd", OpK::ReduceProd}, {"ReduceAll", OpK::ReduceAll}, {"ReduceAny", OpK::ReduceAny},
+    {"ElemAny", OpK::ReduceAny}, {"MatMul", OpK::MatMul},     {"BatchMatMul", OpK::BatchMatMul},
+    {"Assign", OpK::Assign},     {"InplaceAssign", OpK::Assign},
+};
+}  // namespace
+
+const char* opk_name(OpK k) {
+  for (auto& e : kOps)
+    if (e.kind == k) return e.name;
+  return "Unknown";
+}
+bool opk_is_unary(OpK k) { return (int)k >= (int)OpK::Abs && (int)k <= (int)OpK::Cast; }
+bool opk_is_binary(OpK k) { return (int)k >= (int)OpK::Add && (int)k <= (int)OpK::LogicalOr; }
+bool opk_is_reduce(OpK k) { return (int)k >= (int)OpK::ReduceSum && (int)k <= (int)OpK::ReduceAny; }
+bool opk_is_elementwise(OpK k) { return opk_is_unary(k) || opk_is_binary(k) || k == OpK::Select; }
+
+namespace {
+
+std::vector<int64_t> shape_of(const Json& d) {
+  // a missing "shape" means [1] (TranslateToMindsporeDialect.cpp:322-325)
+  if (!d.contains("shape")) return {1};
+  std::vector<int64_t> s = d.at("shape").as_int_list();
+  if (s.empty()) s.push_back(1);
+  for (auto x : s)
+    if (x < 0) throw Unsupported("dynamic shape (negative extent) is not supported");
+  return s;
+}
+
+const Json* find_attr(const Json& attrs, const char* name) {
+  if (!attrs.is_array()) return nullptr;
+  for (auto& a : attrs.arr) {
+    if (a.is_object() && a.contains("name") && a.at("name").is_string() && a.at("name").str == name &&
+        a.contains("value"))
+      return &a.at("value");
+  }
+  return nullptr;
+}
+
+// Ops whose second operand carries an attribute as a 1-D constant
+// (TranslateToMindsporeDialect.cpp:123-125).
+bool attr_as_second_input(const std::string& op) {
+  static const char* k[] = {"Reshape",   "BroadcastTo", "ReduceMax", "ReduceMin", "ReduceSum", "ReducePrd",
+                            "ReduceAll", "ReduceAny",   "ArgMax",    "Transpose", "Tile"};
+  for (auto s : k)
+    if (op == s) return true;
+  return false;
+}
+
+}  // namespace
+
+Graph parse_info(const char* text, size_t len) {
+  Json root = Json::parse(text, len);
+  if (!root.is_object()) throw JsonError("top level must be an object");
+  Graph g;
+  g.sha256_hex = sha256_hex(text, len);
+  g.kernel_name = root.at("op").as_string();
+  g.process = root.at("process").as_string();
+  if (const Json* ti = root.find("target_info")) {
+    if (ti->is_object() && ti->contains("compute_capability") && ti->at("compute_capability").is_string())
+      g.compute_capability = ti->at("compute_capability").str;
+  }
+  if (root.contains("symbol_calc_expr") && root.at("symbol_calc_expr").size() > 0)
+    throw Unsupported("dynamic-shape description (symbol_calc_expr) is not supported");
+
+  std::map<std::string, int> by_name;
+  auto new_value = [&](const std::string& name, std::vector<int64_t> shape, DT dt) {
+    Value v;
+    v.name = name;
+    v.shape = std::move(shape);
+    v.dt = dt;
+    g.values.push_back(std::move(v));
+    return (int)g.values.size() - 1;
+  };
+
+  // inputs: a list of one-element lists
+  const Json& ind = root.at("input_desc");
+  if (!ind.is_null()) {
+    if (!ind.is_array()) throw JsonError("input_desc must be a list");
+    for (size_t i = 0; i < ind.size(); ++i) {
+      const Json& d = ind[i].is_array() ? ind[i][0] : ind[i];
+      if (d.contains("symbolic_shape") && d.at("symbolic_shape").size() > 0) {
+        // static descriptions sometimes repeat the extents as strings; only reject real symbols
+        for (auto& s : d.at("symbolic_shape").arr)
+          if (s.is_string() && !s.str.empty() && !(s.str[0] >= '0' && s.str[0] <= '9'))
+            throw Unsupported("symbolic shapes are not supported");
+      }
+      DT dt = dt_from_name(d.at("data_type").as_string());
+      if (dt == DT::Invalid) throw Unsupported("data type '" + d.at("data_type").str + "' is not supported");
+      const std::string& name = d.at("tensor_name").as_string();
+      int id = new_value(name, shape_of(d), dt);
+      g.values[id].input_index = (int)i;
+      if (d.contains("value") && d.at("value").is_number()) {
+        // a graph input with a literal value stays a runtime argument (the
+        // harness materialises it with np.full) — keep the value for matching
+        g.values[id].cval = {d.at("value").as_double()};
+      }
+      by_name[name] = id;
+      g.inputs.push_back(id);
+    }
+  }
+
+  const Json& ops = root.at("op_desc");
+  if (!ops.is_array()) throw JsonError("op_desc must be a list");
+  for (size_t i = 0; i < ops.size(); ++i) {
+    const Json& od = ops[i];
+    Node n;
+    n.name = od.at("name").as_string();
+    n.kind = OpK::Unknown;
+    for (auto& e : kOps)
+      if (n.name == e.name) n.kind = e.kind;
+    static const Json kNull;
+    const Json& attrs = od.contains("attr") ? od.at("attr") : kNull;
+    const Json& ins = od.at("input_desc");
+    const Json& outs = od.at("output_desc");
+    if (!ins.is_array() || ins.size() == 0) throw JsonError("op '" + n.name + "' has no input_desc");
+    if (!outs.is_array() || outs.size() == 0) throw JsonError("op '" + n.name + "' has no output_desc");
+    if (const Json* fo = find_attr(attrs, "fake_output"))
+      if (fo->is_bool() && fo->b) throw Unsupported("fake_output aliasing is not supported");
+
+    for (size_t j = 0; j < ins.size(); ++j) {
+      const Json& d = ins[j].is_array() ? ins[j][0] : ins[j];
+      if (j == 1 && attr_as_second_input(n.name)) continue;  // attribute operand, read below
+      const std::string& tn = d.at("tensor_name").as_string();
+      auto it = by_name.find(tn);
+      bool has_value = d.contains("value") && !d.at("value").is_null();
+      if (it != by_name.end() && !(has_value && g.values[it->second].is_const)) {
+        n.in.push_back(it->second);
+        continue;
+      }
+      // an operand no earlier op or input defines is a constant (:776-789)
+      if (!has_value) throw JsonError("operand '" + tn + "' of op '" + n.name + "' is undefined");
+      DT dt = dt_from_name(d.at("data_type").as_string());
+      if (dt == DT::Invalid) throw Unsupported("data type '" + d.at("data_type").str + "' is not supported");
+      int id = new_value(tn, shape_of(d), dt);
+      g.values[id].is_const = true;
+      const Json& val = d.at("value");
+      if (val.is_number() || val.is_bool()) g.values[id].cval = {val.as_double()};
+      else if (val.is_array())
+        for (auto& e : val.arr) g.values[id].cval.push_back(e.as_double());
+      else throw JsonError("constant operand '" + tn + "' has a non-numeric value");
+      // constants are not entered in by_name: two ops may reuse a name with different literals
+      n.in.push_back(id);
+    }
+
+    const Json& o0 = outs[0];
+    DT odt = dt_from_name(o0.at("data_type").as_string());
+    if (odt == DT::Invalid) throw Unsupported("data type '" + o0.at("data_type").str + "' is not supported");
+    int out_id = new_value(o0.at("tensor_name").as_string(), shape_of(o0), odt);
+    g.values[out_id].producer = (int)g.nodes.size();
+    n.out = out_id;
+
+    const Json& in0 = ins[0].is_array() ? ins[0][0] : ins[0];
+    int64_t in_rank = (int64_t)shape_of(in0).size();
+    if (opk_is_reduce(n.kind)) {
+      // axes from the second operand or the "axis" attribute; negatives wrap
+      // (TranslateToMindsporeDialect.cpp:1282-1300); keep_dims defaults to false (:1302)
+      std::vector<int64_t> ax;
+      if (ins.size() == 2) {
+        const Json& d1 = ins[1].is_array() ? ins[1][0] : ins[1];
+        ax = d1.at("value").as_int_list();
+      } else if (n.name == "ElemAny") {
+        for (int64_t a = 0; a < in_rank; ++a) ax.push_back(a);
+      } else if (const Json* a = find_attr(attrs, "axis")) {
+        ax = a->as_int_list();
+      } else {
+        throw JsonError("reduction '" + n.name + "' has no axis");
+      }
+      if (ax.empty())
+        for (int64_t a = 0; a < in_rank; ++a) ax.push_back(a);
+      for (auto& a : ax) {
+        if (a < 0) a += in_rank;
+        if (a < 0 || a >= in_rank) throw JsonError("reduction axis out of range");
+      }
+      std::sort(ax.begin(), ax.end());
+      ax.erase(std::unique(ax.begin(), ax.end()), ax.end());
+      n.axes = ax;
+      const Json* kd = find_attr(attrs, "keep_dims");
+      n.keep_dims = (n.name == "ElemAny") ? true : (kd ? kd->as_bool() : false);
+      const Json* at = find_attr(attrs, "enable_atomic_add");
+      n.enable_atomic_add = at ? at->as_bool() : false;
+    } else if (n.kind == OpK::Transpose) {
+      // perm from the second operand or the "perm" attribute (:965-978)
+      if (ins.size() == 2) {
+        const Json& d1 = ins[1].is_array() ? ins[1][0] : ins[1];
+        n.perm = d1.at("value").as_int_list();
+      } else if (const Json* p = find_attr(attrs, "perm")) {
+        n.perm = p->as_int_list();
+      } else {
+        throw JsonError("Transpose has no perm");
+      }
+      if ((int64_t)n.perm.size() != in_rank) throw JsonError("Transpose perm rank mismatch");
+      std::vector<bool> seen(in_rank, false);
+      for (auto& p : n.perm) {
+        if (p < 0) p += in_rank;
+        if (p < 0 || p >= in_rank || seen[p]) throw JsonError("Transpose perm is not a permutation");
+        seen[p] = true;
+      }
+    } else if (n.kind == OpK::MatMul || n.kind == OpK::BatchMatMul) {
+      // transpose_a / transpose_b default to false (:1331-1349)
+      const Json* ta = find_attr(attrs, "transpose_a");
+      const Json* tb = find_attr(attrs, "transpose_b");
+      n.transpose_a = ta ? ta->as_bool() : false;
+      n.transpose_b = tb ? tb->as_bool() : false;
+    }
+    by_name[g.values[out_id].name] = out_id;
+    for (int vid : n.in) g.values[vid].users.push_back((int)g.nodes.size());
+    g.nodes.push_back(std::move(n));
+  }
+
+  const Json& outd = root.at("output_desc");
+  if (!outd.is_array() || outd.size() == 0) throw JsonError("output_desc must be a non-empty list");
+  for (size_t i = 0; i < outd.size(); ++i) {
+    const Json& d = outd[i];
+    const std::string& name = d.at("tensor_name").as_string();
+    auto it = by_name.find(name);
+    if (it == by_name.end()) throw JsonError("output '" + name + "' is not produced by any op");
+    Value& v = g.values[it->second];
+    if (v.output_index >= 0) throw Unsupported("a tensor listed twice in output_desc");
+    v.output_index = (int)i;
+    // the declared output shape may differ from the op's by a trailing view
+    // change only; keep the op's shape when the element counts agree
+    std::vector<int64_t> s = shape_of(d);
+    int64_t n = 1;
+    for (auto x : s) n *= x;
+    if (n != v.numel()) throw JsonError("output '" + name + "' shape disagrees with its producer");
+    g.outputs.push_back(it->second);
+  }
+  classify(g);
+  return g;
+}
+
+void classify(Graph& g) {
+  OpClass c = OpClass::Elementwise;
+  ReduceDir dir = ReduceDir::None;
+  for (auto& n : g.nodes) {
+    OpClass oc = OpClass::Elementwise;
+    if (opk_is_elementwise(n.kind)) {
+      // Elementwise when every operand has the result's shape, else Broadcast
+      // (OperatorIdentify.cpp:38-60)
+      bool same = true;
+      for (int vid : n.in)
+        if (g.v(vid).shape != g.v(n.out).shape) same = false;
+      oc = same ? OpClass::Elementwise : OpClass::Broadcast;
+    } else if (n.kind == OpK::BroadcastTo) {
+      oc = OpClass::Broadcast;
+    } else if (n.kind == OpK::Reshape) {
+      oc = OpClass::Reshape;
+    } else if (n.kind == OpK::Transpose) {
+      oc = OpClass::Transpose;
+    } else if (opk_is_reduce(n.kind)) {
+      oc = OpClass::Reduction;
+      int64_t rank = (int64_t)g.v(n.in[0]).shape.size();
+      ReduceDir d;
+      if ((int64_t)n.axes.size() == rank) d = ReduceDir::All;
+      else if (!n.axes.empty() && n.axes.back() == rank - 1) d = ReduceDir::X;
+      else d = ReduceDir::Y;
+      // the last reduction walked wins, as in the reference's global setter
+      dir = d;
+    } else if (n.kind == OpK::MatMul || n.kind == OpK::BatchMatMul) {
+      oc = OpClass::Matmul;
+    }
+    if ((int)oc > (int)c) c = oc;
+  }
+  g.op_class = c;
+  g.reduce_dir = dir;
+}
+
+void infer_sharding(Graph& g, int rank, int world) {
+  if (world <= 1) return;
+  if (rank < 0 || rank >= world) throw Unsupported("shard_rank outside [0, shard_world)");
+  // The split extent S is axis 0 of the highest-rank, largest graph input.
+  int lead = -1;
+  for (int vid : g.inputs) {
+    const Value& v = g.v(vid);
+    if (lead < 0 || v.shape.size() > g.v(lead).shape.size() ||
+        (v.shape.size() == g.v(lead).shape.size() && v.numel() > g.v(lead).numel()))
+      lead = vid;
+  }
+  if (lead < 0) throw Unsupported("sharding needs at least one tensor input");
+  const int64_t S = g.v(lead).shape[0];
+  const size_t R = g.v(lead).shape.size();
+  if (S % world != 0) throw Unsupported("leading extent is not divisible by shard_world");
+  const int64_t Sl = S / world;
+
+  bool has_matmul = false;
+  for (auto& n : g.nodes)
+    if (n.kind == OpK::MatMul || n.kind == OpK::BatchMatMul) has_matmul = true;
+
+  auto mark = [&](Value& v) {
+    v.split0 = true;
+    v.shape[0] = Sl;
+  };
+  if (has_matmul) {
+    // only the left operand's rows (M) are split; everything the matmul result
+    // meets afterwards is split iff it has full rank and S leading rows
+    mark(g.v(lead));
+  } else {
+    for (int vid : g.inputs) {
+      Value& v = g.v(vid);
+      if (v.shape.size() == R && v.shape[0] == S) mark(v);
+    }
+  }
+  for (auto& n : g.nodes) {
+    Value& out = g.v(n.out);
+    bool any_split = false;
+    for (int vid : n.in) {
+      if (g.v(vid).partial) throw Unsupported("a reduction over the sharded axis feeds another op: replicas only");
+      any_split |= g.v(vid).split0;
+    }
+    if (!any_split) continue;
+    if (opk_is_elementwise(n.kind)) {
+      // a replicated operand of full rank with S leading rows would need slicing
+      for (int vid : n.in) {
+        const Value& v = g.v(vid);
+        if (!v.split0 && !v.is_const && v.shape.size() == out.shape.size() && v.shape[0] == S && S != 1)
+          throw Unsupported("replicated operand spans the sharded axis");
+      }
+      mark(out);
+    } else if (opk_is_reduce(n.kind)) {
+      bool over0 = !n.axes.empty() && n.axes[0] == 0;
+      if (!over0) {
+        mark(out);
+      } else {
+        switch (n.kind) {
+          case OpK::ReduceSum: out.partial = 2; break;
+          case OpK::ReduceMax: out.partial = 3; break;
+          case OpK::ReduceMin: out.partial = 4; break;
+          case OpK::ReduceProd: out.partial = 5; break;
+          default: throw Unsupported("this reduction cannot be split over ranks");
+        }
+        if (out.output_index < 0)
+          throw Unsupported("a reduction over the sharded axis feeds another op: replicas only");
+      }
+    } else if (n.kind == OpK::Transpose) {
+      if (n.perm[0] != 0) throw Unsupported("transpose moves the sharded axis");
+      mark(out);
+    } else if (n.kind == OpK::Reshape) {
+      // a view change that keeps the leading extent keeps the split
+      if (out.shape[0] != S) {
+        // allow merging/splitting that keeps S as a factor of the leading extent
+        if (out.shape[0] % S != 0 && S % out.shape[0] != 0) throw Unsupported("reshape mixes the sharded axis");
+        if (out.shape[0] % world != 0) throw Unsupported("reshape mixes the sharded axis");
+        out.split0 = true;
+        out.shape[0] /= world;
+      } else {
+        mark(out);
+      }
+    } else if (n.kind == OpK::MatMul || n.kind == OpK::BatchMatMul) {
+      if (n.transpose_a) throw Unsupported("transpose_a matmul cannot be split on rows");
+      if (g.v(n.in[1]).split0 && n.kind == OpK::MatMul) throw Unsupported("right matmul operand is split");
+      mark(out);
+    } else if (n.kind == OpK::BroadcastTo) {
+      mark(out);
+    } else {
+      throw Unsupported(std::string("op '") + n.name + "' cannot be sharded");
+    }
+  }
+  (void)rank;
+}
+
+// ----------------------------------------------------------------------------
+// SHA-256 (FIPS 180-4) of the description text; the reference stamps the same
+// digest of its kernel file into the metadata JSON (mlir_driver.py:776-815).
+namespace {
+inline uint32_t rotr(uint32_t x, int n) { return (x >> n) | (x << (32 - n)); }
+}  // namespace
+
+std::string sha256_hex(const char* data, size_t len) {
+  static const uint32_t K[64] = {
+      0x428a2f98, 0x71374491, 0xb5c0fbcf, 0xe9b5dba5, 0x3956c25b, 0x59f111f1, 0x923f82a4, 0xab1c5ed5,
+      0xd807aa98, 0x12835b01, 0x243185be, 0x550c7dc3, 0x72be5d74, 0x80deb1fe, 0x9bdc06a7, 0xc19bf174,
+      0xe49b69c1, 0xefbe4786, 0x0fc19dc6, 0x240ca1cc, 0x2de92c6f, 0x4a7484aa, 0x5cb0a9dc, 0x76f988da,
+      0x983e5152, 0xa831c66d, 0xb00327c8, 0xbf597fc7, 0xc6e00bf3, 0xd5a79147, 0x06ca6351, 0x14292967,
+      0x27b70a85, 0x2e1b2138, 0x4d2c6dfc, 0x53380d13, 0x650a7354, 0x766a0abb, 0x81c2c92e, 0x92722c85,
+      0xa2bfe8a1, 0xa81a664b, 0xc24b8b70, 0xc76c51a3, 0xd192e819, 0xd6990624, 0xf40e3585, 0x106aa070,
+      0x19a4c116, 0x1e376c08, 0x2748774c, 0x34b0bcb5, 0x391c0cb3, 0x4ed8aa4a, 0x5b9cca4f, 0x682e6ff3,
+      0x748f82ee, 0x78a5636f, 0x84c87814, 0x8cc70208, 0x90befffa, 0xa4506ceb, 0xbef9a3f7, 0xc67178f2};
+  uint32_t h[8] = {0x6a09e667, 0xbb67ae85, 0x3c6ef372, 0xa54ff53a, 0x510e527f, 0x9b05688c, 0x1f83d9ab, 0x5be0cd19};
+  std::vector<uint8_t> msg(data, data + len);
+  msg.push_back(0x80);
+  while (msg.size() % 64 != 56) msg.push_back(0);
+  uint64_t bits = (uint64_t)len * 8;
+  for (int i = 7; i >= 0; --i) msg.push_back((uint8_t)(bits >> (8 * i)));
+  for (size_t off = 0; off < msg.size(); off += 64) {
+    uint32_t w[64];
+    for (int i = 0; i < 16; ++i)
+      w[i] = (uint32_t)msg[off + 4 * i] << 24 | (uint32_t)msg[off + 4 * i + 1] << 16 |
+             (uint32_t)msg[off + 4 * i + 2] << 8 | (uint32_t)msg[off + 4 * i + 3];
+    for (int i = 16; i < 64; ++i) {
+      uint32_t s0 = rotr(w[i - 15], 7) ^ rotr(w[i - 15], 18) ^ (w[i - 15] >> 3);
+      uint32_t s1 = rotr(w[i - 2], 17) ^ rotr(w[i - 2], 19) ^ (w[i - 2] >> 10);
+      w[i] = w[i - 16] + s0 + w[i - 7] + s1;
+    }
+    uint32_t a = h[0], b = h[1], c = h[2], d = h[3], e = h[4], f = h[5], gg = h[6], hh = h[7];
+    for (int i = 0; i < 64; ++i) {
+      uint32_t S1 = rotr(e, 6) ^ rotr(e, 11) ^ rotr(e, 25);
+      uint32_t ch = (e & f) ^ (~e & gg);
+      uint32_t t1 = hh + S1 + ch + K[i] + w[i];
+      uint32_t S0 = rotr(a, 2) ^ rotr(a, 13) ^ rotr(a, 22);
+      uint32_t mj = (a & b) ^ (a & c) ^ (b & c);
+      uint32_t t2 = S0 + mj;
+      hh = gg; gg = f; f = e; e = d + t1; d = c; c = b; b = a; a = t1 + t2;
+    }
+    h[0] += a; h[1] += b; h[2] += c; h[3] += d; h[4] += e; h[5] += f; h[6] += gg; h[7] += hh;
+  }
+  static const char* hex = "0123456789abcdef";
+  std::string out;
+  for (int i = 0; i < 8; ++i)
+    for (int j = 28; j >= 0; j -= 4) out.push_back(hex[(h[i] >> j) & 0xF]);
+  return out;
+}
+
+}  // namespace akgb

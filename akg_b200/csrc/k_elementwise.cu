@@ -1,0 +1,221 @@
+// Elementwise / broadcast class: the float16 bias + tanh-GELU (+ multiply)
+// (+ cast to float32) chain.
+//
+// The reference lowers every op of the chain to arithmetic in the op's own
+// element type (akg-mlir/lib/Conversion/MindSporeToLinalg/MindSporeToLinalg.cpp:377-483,
+// akg-mlir/lib/Conversion/MindSporeToTosa/MindSporeToTosa.cpp:475-504), so a
+// float16 chain rounds to float16 after each op.  The kernel replays exactly
+// that: native f16x2 add/mul with round-to-nearest (an f16 add or mul rounded
+// once equals the f32 operation rounded to f16, because 24 >= 2*11+2 bits), and
+// tanh through a table of correctly rounded f16 results, so the output is
+// bit-identical to a per-op evaluation.
+#include <cmath>
+#include <vector>
+
+#include "common.cuh"
+#include "hostconv.hpp"
+#include "kernels.hpp"
+
+namespace akgb {
+
+namespace {
+// f16 magnitudes below kLutLo map to themselves (x - x^3/3 rounds to x), at or
+// above kLutHi to 1.0; in between the table holds RN_f16(tanh(x)).
+constexpr unsigned kLutLo = 0x2400;  // 2^-6
+constexpr unsigned kLutHi = 0x4500;  // 5.0
+constexpr int kLutN = (int)(kLutHi - kLutLo);
+
+}  // namespace
+
+int gelu_lut_entries() { return kLutN; }
+void gelu_lut_build(uint16_t* out) {
+  for (int i = 0; i < kLutN; ++i) out[i] = f64_to_f16_bits(std::tanh(f16_bits_to_f64((uint16_t)(kLutLo + i))));
+}
+
+namespace {
+
+__device__ __forceinline__ unsigned tanh_bits(unsigned bits, const uint16_t* lut) {
+  const unsigned mag = bits & 0x7fffu, sign = bits & 0x8000u;
+  unsigned idx = min(max(mag, kLutLo), kLutHi - 1) - kLutLo;
+  unsigned r = lut[idx];
+  r = mag < kLutLo ? mag : r;
+  r = mag >= kLutHi ? (mag > 0x7c00u ? mag : 0x3c00u) : r;
+  return r | sign;
+}
+__device__ __forceinline__ __half2 tanh2(__half2 d, const uint16_t* lut) {
+  const uint32_t w = *reinterpret_cast<uint32_t*>(&d);
+  const uint32_t r = tanh_bits(w & 0xffffu, lut) | (tanh_bits(w >> 16, lut) << 16);
+  return *reinterpret_cast<const __half2*>(&r);
+}
+
+struct Consts {
+  __half2 c0, c1, c2, one;
+};
+
+template <bool BIAS, bool MUL>
+__device__ __forceinline__ __half2 chain2(__half2 x, __half2 bias, __half2 y, const Consts& k, const uint16_t* lut) {
+  const __half2 t = BIAS ? __hadd2_rn(x, bias) : x;
+  const __half2 a = __hmul2_rn(t, t);
+  const __half2 t3 = __hmul2_rn(a, t);
+  const __half2 b = __hmul2_rn(t3, k.c0);
+  const __half2 c = __hadd2_rn(t, b);
+  const __half2 d = __hmul2_rn(c, k.c1);
+  const __half2 e = tanh2(d, lut);
+  const __half2 f = __hadd2_rn(e, k.one);
+  const __half2 g = __hmul2_rn(t, k.c2);
+  __half2 h = __hmul2_rn(g, f);
+  if (MUL) h = __hmul2_rn(h, y);
+  return h;
+}
+
+template <bool BIAS, bool MUL, bool OUTF32>
+__device__ __forceinline__ void do_vec(uint4 xv, uint4 bv, uint4 yv, void* out, int64_t i, const Consts& k,
+                                       const uint16_t* lut) {
+  const __half2* xs = reinterpret_cast<const __half2*>(&xv);
+  const __half2* bs = reinterpret_cast<const __half2*>(&bv);
+  const __half2* ys = reinterpret_cast<const __half2*>(&yv);
+  __half2 r[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) r[j] = chain2<BIAS, MUL>(xs[j], bs[j], ys[j], k, lut);
+  if (OUTF32) {
+    const float2 f0 = __half22float2(r[0]), f1 = __half22float2(r[1]);
+    const float2 f2 = __half22float2(r[2]), f3 = __half22float2(r[3]);
+    float4* o = reinterpret_cast<float4*>(out) + 2 * i;
+    st_stream_f4(o, make_float4(f0.x, f0.y, f1.x, f1.y));
+    st_stream_f4(o + 1, make_float4(f2.x, f2.y, f3.x, f3.y));
+  } else {
+    st_stream(reinterpret_cast<uint4*>(out) + i, *reinterpret_cast<uint4*>(r));
+  }
+}
+
+// One thread handles vectors of 8 consecutive elements, two per iteration.
+template <bool BIAS, bool MUL, bool OUTF32>
+__global__ void __launch_bounds__(256) gelu_chain_f16_kernel(const uint4* __restrict__ x, const uint4* __restrict__ bias,
+                                                             const uint4* __restrict__ y, void* __restrict__ out,
+                                                             int64_t nvec, int64_t inner_vec, float c0, float c1,
+                                                             float c2, float c_one,
+                                                             const uint16_t* __restrict__ lut_g) {
+  __shared__ __align__(16) uint16_t lut[kLutN];
+  for (int i = threadIdx.x; i < kLutN / 8; i += blockDim.x)
+    reinterpret_cast<uint4*>(lut)[i] = __ldg(reinterpret_cast<const uint4*>(lut_g) + i);
+  __syncthreads();
+  Consts k;
+  k.c0 = __float2half2_rn(c0);
+  k.c1 = __float2half2_rn(c1);
+  k.c2 = __float2half2_rn(c2);
+  k.one = __float2half2_rn(c_one);
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint4 z = make_uint4(0, 0, 0, 0);
+  // bias vector index of element vector i, advanced without 64-bit division
+  const uint32_t iv = BIAS ? (uint32_t)inner_vec : 1u;
+  uint32_t bi = BIAS ? (uint32_t)(i % inner_vec) : 0u;
+  const uint32_t bstep = BIAS ? (uint32_t)(stride % inner_vec) : 0u;
+  for (; i + stride < nvec; i += 2 * stride) {
+    const int64_t j = i + stride;
+    uint32_t bj = bi + bstep;
+    bj = bj >= iv ? bj - iv : bj;
+    const uint4 x0 = ld_stream(x + i), x1 = ld_stream(x + j);
+    const uint4 y0 = MUL ? ld_stream(y + i) : z, y1 = MUL ? ld_stream(y + j) : z;
+    const uint4 b0 = BIAS ? ld_cached(bias + bi) : z, b1 = BIAS ? ld_cached(bias + bj) : z;
+    do_vec<BIAS, MUL, OUTF32>(x0, b0, y0, out, i, k, lut);
+    do_vec<BIAS, MUL, OUTF32>(x1, b1, y1, out, j, k, lut);
+    bi = bj + bstep;
+    bi = bi >= iv ? bi - iv : bi;
+  }
+  if (i < nvec) {
+    const uint4 x0 = ld_stream(x + i);
+    const uint4 y0 = MUL ? ld_stream(y + i) : z;
+    const uint4 b0 = BIAS ? ld_cached(bias + bi) : z;
+    do_vec<BIAS, MUL, OUTF32>(x0, b0, y0, out, i, k, lut);
+  }
+}
+
+// Any length / alignment: one element per thread-iteration, same arithmetic.
+__global__ void __launch_bounds__(256) gelu_chain_f16_scalar_kernel(const __half* __restrict__ x,
+                                                                    const __half* __restrict__ bias,
+                                                                    const __half* __restrict__ y, void* __restrict__ out,
+                                                                    int64_t begin, int64_t n, int64_t inner, int has_mul,
+                                                                    int out_f32, float c0, float c1, float c2,
+                                                                    float c_one, const uint16_t* __restrict__ lut_g) {
+  Consts k;
+  k.c0 = __float2half2_rn(c0);
+  k.c1 = __float2half2_rn(c1);
+  k.c2 = __float2half2_rn(c2);
+  k.one = __float2half2_rn(c_one);
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = begin + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const __half2 xv = __half2half2(x[i]);
+    const __half2 bv = inner ? __half2half2(bias[i % inner]) : xv;
+    const __half2 yv = has_mul ? __half2half2(y[i]) : xv;
+    __half2 h;
+    if (inner) h = has_mul ? chain2<true, true>(xv, bv, yv, k, lut_g) : chain2<true, false>(xv, bv, yv, k, lut_g);
+    else h = has_mul ? chain2<false, true>(xv, bv, yv, k, lut_g) : chain2<false, false>(xv, bv, yv, k, lut_g);
+    if (out_f32) reinterpret_cast<float*>(out)[i] = __low2float(h);
+    else reinterpret_cast<__half*>(out)[i] = __low2half(h);
+  }
+}
+
+template <bool BIAS, bool MUL, bool OUTF32>
+cudaError_t launch_vec(const GeluChainParams& p, const void* x, const void* bias, const void* y, void* out,
+                       const void* lut, int64_t nvec, int grid, cudaStream_t s) {
+  gelu_chain_f16_kernel<BIAS, MUL, OUTF32><<<grid, 256, 0, s>>>(
+      (const uint4*)x, (const uint4*)bias, (const uint4*)y, out, nvec, p.inner / 8, p.c0, p.c1, p.c2, p.c_one,
+      (const uint16_t*)lut);
+  return cudaGetLastError();
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+cudaError_t gelu_chain_f16(const GeluChainParams& p, const void* x, const void* bias, const void* y, void* out,
+                           const void* lut, cudaStream_t s, LaunchDims* dims) {
+  if (p.n == 0) return cudaSuccess;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const bool vec_ok = aligned16(x) && aligned16(out) && (!p.has_mul || aligned16(y)) &&
+                      (!p.inner || (aligned16(bias) && p.inner % 8 == 0));
+  int64_t nvec = vec_ok ? p.n / 8 : 0;
+  cudaError_t e = cudaSuccess;
+  if (nvec > 0) {
+    // persistent CTAs: the table is staged into shared memory once per CTA
+    int64_t want = (nvec + 255) / 256;
+    int grid = (int)std::min<int64_t>(want, (int64_t)sms * 8);
+    if (dims) {
+      dims->grid[0] = grid;
+      dims->block[0] = 256;
+      dims->smem = kLutN * 2;
+    }
+    const bool B = p.inner != 0, Mu = p.has_mul != 0, F = p.out_f32 != 0;
+#define AKGB_GELU_CASE(b, m, f) \
+  if (B == b && Mu == m && F == f) e = launch_vec<b, m, f>(p, x, bias, y, out, lut, nvec, grid, s);
+    AKGB_GELU_CASE(true, true, true)
+    AKGB_GELU_CASE(true, true, false)
+    AKGB_GELU_CASE(true, false, true)
+    AKGB_GELU_CASE(true, false, false)
+    AKGB_GELU_CASE(false, true, true)
+    AKGB_GELU_CASE(false, true, false)
+    AKGB_GELU_CASE(false, false, true)
+    AKGB_GELU_CASE(false, false, false)
+#undef AKGB_GELU_CASE
+    if (e != cudaSuccess) return e;
+  }
+  const int64_t done = nvec * 8;
+  if (done < p.n) {
+    int64_t rest = p.n - done;
+    int grid = (int)std::min<int64_t>((rest + 255) / 256, (int64_t)sms * 8);
+    if (dims && nvec == 0) {
+      dims->grid[0] = grid;
+      dims->block[0] = 256;
+    }
+    gelu_chain_f16_scalar_kernel<<<grid, 256, 0, s>>>((const __half*)x, (const __half*)bias, (const __half*)y, out, done,
+                                                      p.n, p.inner, p.has_mul, p.out_f32, p.c0, p.c1, p.c2, p.c_one,
+                                                      (const uint16_t*)lut);
+    e = cudaGetLastError();
+  }
+  return e;
+}
+
+}  // namespace akgb

@@ -1,0 +1,270 @@
+// Reduction class: column (reduce-Y), global (reduce-ALL) and plain row
+// (reduce-X) reductions of float32 tensors.
+//
+// Init values and combiners follow the reference lowering
+// (akg-mlir/lib/Conversion/MindSporeToLinalg/MindSporeToLinalg.cpp:791-843 and
+// :845-901): sum 0, prod 1, max -FLT_MAX, min +FLT_MAX; max/min skip NaN
+// operands.  The reference's GPU schedule walks the reduced axis sequentially
+// per thread and combines with atomics
+// (akg-mlir/lib/Dialect/Affine/Analysis/GpuTemplateTilingSolver.cpp:458-542);
+// here every stage is a fixed tree, so results do not depend on scheduling:
+// per-thread strided partials -> shared-memory tree -> per-CTA partial in
+// scratch -> a small second kernel folds the partials in a fixed order.
+#include <algorithm>
+
+#include "common.cuh"
+#include "kernels.hpp"
+
+namespace akgb {
+namespace {
+
+constexpr int kColTx = 32;   // threads across columns (each owns a float4)
+constexpr int kColTy = 8;    // threads across rows
+constexpr int kColTile = kColTx * 4;
+
+inline int64_t col_row_splits(int64_t red, int64_t inner, int sm_count) {
+  const int64_t col_tiles = (inner + kColTile - 1) / kColTile;
+  int64_t want = ((int64_t)sm_count * 8 + col_tiles - 1) / col_tiles;
+  // each split should own at least a few sweeps of kColTy rows
+  const int64_t max_splits = std::max<int64_t>(1, red / (kColTy * 4));
+  return std::max<int64_t>(1, std::min(want, max_splits));
+}
+
+template <class Op>
+__device__ __forceinline__ float4 apply4(float4 a, float4 b) {
+  return make_float4(Op::apply(a.x, b.x), Op::apply(a.y, b.y), Op::apply(a.z, b.z), Op::apply(a.w, b.w));
+}
+
+// x[red, inner] -> partial[split, inner]; VEC: inner % 4 == 0 and 16-byte aligned rows
+template <class Op, bool VEC>
+__global__ void __launch_bounds__(kColTx* kColTy) reduce_col_f32_kernel(const float* __restrict__ x,
+                                                                        float* __restrict__ partial, int64_t red,
+                                                                        int64_t inner, int64_t rows_per_split) {
+  __shared__ float4 sm[kColTy][kColTx];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int64_t col = ((int64_t)blockIdx.x * kColTx + tx) * 4;
+  const int64_t r0 = (int64_t)blockIdx.y * rows_per_split;
+  const int64_t r1 = min(red, r0 + rows_per_split);
+  const float id = Op::identity();
+  float4 acc0 = make_float4(id, id, id, id), acc1 = acc0, acc2 = acc0, acc3 = acc0;
+  if (VEC) {
+    if (col < inner) {
+      const float* base = x + col;
+      int64_t r = r0 + ty;
+      for (; r + 3 * kColTy < r1; r += 4 * kColTy) {
+        const float4 a = ld_stream_f4(base + r * inner);
+        const float4 b = ld_stream_f4(base + (r + kColTy) * inner);
+        const float4 c = ld_stream_f4(base + (r + 2 * kColTy) * inner);
+        const float4 d = ld_stream_f4(base + (r + 3 * kColTy) * inner);
+        acc0 = apply4<Op>(acc0, a);
+        acc1 = apply4<Op>(acc1, b);
+        acc2 = apply4<Op>(acc2, c);
+        acc3 = apply4<Op>(acc3, d);
+      }
+      for (; r < r1; r += kColTy) acc0 = apply4<Op>(acc0, ld_stream_f4(base + r * inner));
+    }
+  } else {
+    for (int64_t r = r0 + ty; r < r1; r += kColTy) {
+      const float* row = x + r * inner;
+      float4 a = make_float4(id, id, id, id);
+      if (col + 0 < inner) a.x = row[col + 0];
+      if (col + 1 < inner) a.y = row[col + 1];
+      if (col + 2 < inner) a.z = row[col + 2];
+      if (col + 3 < inner) a.w = row[col + 3];
+      acc0 = apply4<Op>(acc0, a);
+    }
+  }
+  acc0 = apply4<Op>(apply4<Op>(acc0, acc1), apply4<Op>(acc2, acc3));
+  sm[ty][tx] = acc0;
+  __syncthreads();
+#pragma unroll
+  for (int h = kColTy / 2; h > 0; h >>= 1) {
+    if (ty < h) sm[ty][tx] = apply4<Op>(sm[ty][tx], sm[ty + h][tx]);
+    __syncthreads();
+  }
+  if (ty == 0) {
+    const float4 r = sm[0][tx];
+    float* o = partial + (int64_t)blockIdx.y * inner + col;
+    if (col + 0 < inner) o[0] = r.x;
+    if (col + 1 < inner) o[1] = r.y;
+    if (col + 2 < inner) o[2] = r.z;
+    if (col + 3 < inner) o[3] = r.w;
+  }
+}
+
+// partial[splits, inner] -> out[inner], fixed order
+template <class Op>
+__global__ void __launch_bounds__(256) reduce_col_finish_kernel(const float* __restrict__ partial,
+                                                                float* __restrict__ out, int64_t splits,
+                                                                int64_t inner) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= inner) return;
+  float a = Op::identity();
+  for (int64_t s = 0; s < splits; ++s) a = Op::apply(a, partial[s * inner + c]);
+  out[c] = a;
+}
+
+// x[n] -> partial[grid]
+template <class Op, bool VEC>
+__global__ void __launch_bounds__(256) reduce_all_f32_kernel(const float* __restrict__ x, float* __restrict__ partial,
+                                                             int64_t n) {
+  __shared__ float red[32];
+  const float id = Op::identity();
+  float a0 = id, a1 = id, a2 = id, a3 = id;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  if (VEC) {
+    const int64_t n4 = n >> 2;
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    int64_t i = tid;
+    for (; i + 3 * stride < n4; i += 4 * stride) {
+      const float4 p = ld_stream_f4(x4 + i), q = ld_stream_f4(x4 + i + stride);
+      const float4 r = ld_stream_f4(x4 + i + 2 * stride), t = ld_stream_f4(x4 + i + 3 * stride);
+      a0 = Op::apply(a0, Op::apply(Op::apply(p.x, p.y), Op::apply(p.z, p.w)));
+      a1 = Op::apply(a1, Op::apply(Op::apply(q.x, q.y), Op::apply(q.z, q.w)));
+      a2 = Op::apply(a2, Op::apply(Op::apply(r.x, r.y), Op::apply(r.z, r.w)));
+      a3 = Op::apply(a3, Op::apply(Op::apply(t.x, t.y), Op::apply(t.z, t.w)));
+    }
+    for (; i < n4; i += stride) {
+      const float4 p = ld_stream_f4(x4 + i);
+      a0 = Op::apply(a0, Op::apply(Op::apply(p.x, p.y), Op::apply(p.z, p.w)));
+    }
+    for (int64_t j = (n4 << 2) + tid; j < n; j += stride) a1 = Op::apply(a1, x[j]);
+  } else {
+    for (int64_t j = tid; j < n; j += stride) a0 = Op::apply(a0, x[j]);
+  }
+  float a = Op::apply(Op::apply(a0, a1), Op::apply(a2, a3));
+  a = block_reduce<Op>(a, red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = a;
+}
+
+template <class Op>
+__global__ void __launch_bounds__(1024) reduce_all_finish_kernel(const float* __restrict__ partial,
+                                                                 float* __restrict__ out, int n) {
+  __shared__ float red[32];
+  float a = Op::identity();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) a = Op::apply(a, partial[i]);
+  a = block_reduce<Op>(a, red);
+  if (threadIdx.x == 0) out[0] = a;
+}
+
+// x[rows, cols] -> out[rows]; one warp per row
+template <class Op>
+__global__ void __launch_bounds__(256) reduce_row_f32_kernel(const float* __restrict__ x, float* __restrict__ out,
+                                                             int64_t rows, int64_t cols, int vec) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * 8;
+  for (int64_t row = warp; row < rows; row += nwarps) {
+    const float* xr = x + row * cols;
+    float a = Op::identity(), b = Op::identity();
+    if (vec) {
+      const float4* x4 = reinterpret_cast<const float4*>(xr);
+      const int64_t c4 = cols >> 2;
+      int64_t i = lane;
+      for (; i + 32 < c4; i += 64) {
+        const float4 p = ld_stream_f4(x4 + i), q = ld_stream_f4(x4 + i + 32);
+        a = Op::apply(a, Op::apply(Op::apply(p.x, p.y), Op::apply(p.z, p.w)));
+        b = Op::apply(b, Op::apply(Op::apply(q.x, q.y), Op::apply(q.z, q.w)));
+      }
+      for (; i < c4; i += 32) {
+        const float4 p = ld_stream_f4(x4 + i);
+        a = Op::apply(a, Op::apply(Op::apply(p.x, p.y), Op::apply(p.z, p.w)));
+      }
+    } else {
+      for (int64_t i = lane; i < cols; i += 32) a = Op::apply(a, xr[i]);
+    }
+    a = warp_reduce<Op>(Op::apply(a, b));
+    if (lane == 0) out[row] = a;
+  }
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <class Op>
+cudaError_t col_impl(const float* x, float* out, int64_t red, int64_t inner, void* ws, int sm_count, cudaStream_t s,
+                     LaunchDims* dims) {
+  const int64_t splits = col_row_splits(red, inner, sm_count);
+  const int64_t rows_per_split = (red + splits - 1) / splits;
+  dim3 grid((unsigned)((inner + kColTile - 1) / kColTile), (unsigned)splits), block(kColTx, kColTy);
+  if (dims) {
+    dims->grid[0] = grid.x;
+    dims->grid[1] = grid.y;
+    dims->block[0] = block.x;
+    dims->block[1] = block.y;
+    dims->smem = sizeof(float4) * kColTx * kColTy;
+  }
+  float* partial = splits == 1 ? out : reinterpret_cast<float*>(ws);
+  if (inner % 4 == 0 && aligned16(x))
+    reduce_col_f32_kernel<Op, true><<<grid, block, 0, s>>>(x, partial, red, inner, rows_per_split);
+  else
+    reduce_col_f32_kernel<Op, false><<<grid, block, 0, s>>>(x, partial, red, inner, rows_per_split);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess || splits == 1) return e;
+  reduce_col_finish_kernel<Op><<<(unsigned)((inner + 255) / 256), 256, 0, s>>>(partial, out, splits, inner);
+  return cudaGetLastError();
+}
+
+template <class Op>
+cudaError_t all_impl(const float* x, float* out, int64_t n, void* ws, int sm_count, cudaStream_t s, LaunchDims* dims) {
+  const int64_t want = (n / 4 + 255) / 256;
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)sm_count * 8));
+  if (dims) {
+    dims->grid[0] = grid;
+    dims->block[0] = 256;
+  }
+  float* partial = reinterpret_cast<float*>(ws);
+  if (aligned16(x)) reduce_all_f32_kernel<Op, true><<<grid, 256, 0, s>>>(x, partial, n);
+  else reduce_all_f32_kernel<Op, false><<<grid, 256, 0, s>>>(x, partial, n);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  reduce_all_finish_kernel<Op><<<1, 1024, 0, s>>>(partial, out, grid);
+  return cudaGetLastError();
+}
+
+template <class Op>
+cudaError_t row_impl(const float* x, float* out, int64_t rows, int64_t cols, cudaStream_t s, LaunchDims* dims) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((rows + 7) / 8, (int64_t)sms * 8));
+  if (dims) {
+    dims->grid[0] = grid;
+    dims->block[0] = 256;
+  }
+  const int vec = cols % 4 == 0 && aligned16(x);
+  reduce_row_f32_kernel<Op><<<grid, 256, 0, s>>>(x, out, rows, cols, vec);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+size_t reduce_col_workspace(int64_t red, int64_t inner, int sm_count) {
+  const int64_t splits = col_row_splits(red, inner, sm_count);
+  return splits == 1 ? 0 : (size_t)(splits * inner) * sizeof(float);
+}
+size_t reduce_all_workspace(int sm_count) { return (size_t)sm_count * 8 * sizeof(float); }
+
+#define AKGB_DISPATCH(fn, ...)                         \
+  switch (op) {                                        \
+    case RedOp::Sum: return fn<SumOp>(__VA_ARGS__);    \
+    case RedOp::Max: return fn<MaxOp>(__VA_ARGS__);    \
+    case RedOp::Min: return fn<MinOp>(__VA_ARGS__);    \
+    case RedOp::Prod: return fn<ProdOp>(__VA_ARGS__);  \
+  }                                                    \
+  return cudaErrorInvalidValue;
+
+cudaError_t reduce_col_f32(RedOp op, const float* x, float* out, int64_t red, int64_t inner, void* ws, int sm_count,
+                           cudaStream_t s, LaunchDims* dims) {
+  AKGB_DISPATCH(col_impl, x, out, red, inner, ws, sm_count, s, dims)
+}
+cudaError_t reduce_all_f32(RedOp op, const float* x, float* out, int64_t n, void* ws, int sm_count, cudaStream_t s,
+                           LaunchDims* dims) {
+  AKGB_DISPATCH(all_impl, x, out, n, ws, sm_count, s, dims)
+}
+cudaError_t reduce_row_f32(RedOp op, const float* x, float* out, int64_t rows, int64_t cols, cudaStream_t s,
+                           LaunchDims* dims) {
+  AKGB_DISPATCH(row_impl, x, out, rows, cols, s, dims)
+}
+
+}  // namespace akgb

@@ -1,0 +1,229 @@
+// Transpose class: bit-exact permutation copies.
+//
+// The host folds the permutation (extent-1 axes dropped, axes that stay
+// adjacent merged) into at most 6 output dims with an input stride each.  Two
+// kernels cover every case:
+//   * row mode — the innermost output dim is also contiguous in the input, so
+//     the copy moves 16-byte vectors and both sides are coalesced;
+//   * tile mode — the innermost output dim is strided in the input: 32x32
+//     tiles go through shared memory so that reads run along the input's
+//     contiguous axis and writes along the output's (the reference maps a
+//     32x32 thread tile onto the same two axes,
+//     akg-mlir/lib/Analysis/TilingStrategy.cpp:330-408).
+#include <algorithm>
+
+#include "common.cuh"
+#include "kernels.hpp"
+
+namespace akgb {
+namespace {
+
+struct Shape6 {
+  int rank;
+  int64_t ext[6];
+  int64_t istr[6];
+};
+
+// Division by a run-time constant as multiply-high + shift; exact for
+// numerators below 2^31.
+struct FastDiv6 {
+  uint32_t mul[6];
+  uint32_t shr[6];
+};
+inline void fastdiv_init(uint32_t d, uint32_t* mul, uint32_t* shr) {
+  if (d <= 1) {
+    *mul = 0;
+    *shr = 0;
+    return;
+  }
+  uint32_t sh = 0;
+  while ((1ull << sh) < d) ++sh;
+  *shr = sh;
+  *mul = (uint32_t)((((1ull << 32) * ((1ull << sh) - d)) / d) + 1);
+}
+
+// row mode: one 16-byte vector per thread-iteration, 4 in flight.  FAST: the
+// vector count fits 31 bits, so the index split uses 32-bit multiply-shift.
+template <bool FAST>
+__global__ void __launch_bounds__(256) transpose_rows_kernel(Shape6 sh, FastDiv6 fd, const uint4* __restrict__ x,
+                                                             uint4* __restrict__ out, int64_t nvec) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t base = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; base < nvec; base += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t o = base + u * stride;
+      if (o < nvec) {
+        int64_t off = 0;
+        if (FAST) {
+          uint32_t rem = (uint32_t)o, acc = 0;
+#pragma unroll
+          for (int d = 5; d >= 0; --d) {
+            if (d < sh.rank) {
+              const uint32_t q = (__umulhi(rem, fd.mul[d]) + rem) >> fd.shr[d];
+              acc += (rem - q * (uint32_t)sh.ext[d]) * (uint32_t)sh.istr[d];
+              rem = q;
+            }
+          }
+          off = acc;
+        } else {
+          int64_t rem = o;
+#pragma unroll
+          for (int d = 5; d >= 0; --d) {
+            if (d < sh.rank) {
+              const int64_t q = rem / sh.ext[d];
+              off += (rem - q * sh.ext[d]) * sh.istr[d];
+              rem = q;
+            }
+          }
+        }
+        v[u] = ld_stream(x + off);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t o = base + u * stride;
+      if (o < nvec) st_stream(out + o, v[u]);
+    }
+  }
+}
+
+// tile mode over elements of T; dim `pin` of the output is the input's contiguous axis
+template <typename T>
+__global__ void __launch_bounds__(256) transpose_tile_kernel(Shape6 sh, int pin, const T* __restrict__ x,
+                                                             T* __restrict__ out, int64_t ostr_pin) {
+  __shared__ T tile[32][33];
+  const int last = sh.rank - 1;
+  const int64_t W = sh.ext[last], H = sh.ext[pin];
+  const int64_t w0 = (int64_t)blockIdx.x * 32, h0 = (int64_t)blockIdx.y * 32;
+  // batch offset from blockIdx.z over the remaining dims
+  int64_t rem = blockIdx.z, ioff = 0, ooff = 0, ostride = 1;
+  // output strides: contiguous row-major over sh.ext
+  int64_t ostr[6];
+  for (int d = sh.rank - 1; d >= 0; --d) {
+    ostr[d] = ostride;
+    ostride *= sh.ext[d];
+  }
+  for (int d = sh.rank - 2; d >= 0; --d) {
+    if (d == pin) continue;
+    const int64_t q = rem / sh.ext[d];
+    const int64_t i = rem - q * sh.ext[d];
+    ioff += i * sh.istr[d];
+    ooff += i * ostr[d];
+    rem = q;
+  }
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  // read: threads run along the input-contiguous axis (h)
+  for (int r = ty; r < 32; r += 8) {
+    const int64_t w = w0 + r, h = h0 + tx;
+    if (w < W && h < H) tile[r][tx] = x[ioff + w * sh.istr[last] + h];
+  }
+  __syncthreads();
+  // write: threads run along the output-contiguous axis (w)
+  for (int r = ty; r < 32; r += 8) {
+    const int64_t h = h0 + r, w = w0 + tx;
+    if (w < W && h < H) out[ooff + h * ostr_pin + w] = tile[tx][r];
+  }
+}
+
+// scalar fallback for anything else (odd element sizes are handled bytewise by the caller's esize)
+template <typename T>
+__global__ void __launch_bounds__(256) transpose_scalar_kernel(Shape6 sh, const T* __restrict__ x, T* __restrict__ out,
+                                                               int64_t n) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < n; o += stride) {
+    int64_t rem = o, off = 0;
+    for (int d = sh.rank - 1; d >= 0; --d) {
+      const int64_t q = rem / sh.ext[d];
+      off += (rem - q * sh.ext[d]) * sh.istr[d];
+      rem = q;
+    }
+    out[o] = x[off];
+  }
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <typename T>
+cudaError_t tile_or_scalar(const Shape6& sh, const void* x, void* out, int sms, cudaStream_t s, LaunchDims* dims) {
+  int64_t n = 1;
+  for (int d = 0; d < sh.rank; ++d) n *= sh.ext[d];
+  int pin = -1;
+  for (int d = 0; d < sh.rank - 1; ++d)
+    if (sh.istr[d] == 1) pin = d;
+  if (pin >= 0 && sh.rank >= 2) {
+    int64_t batch = 1, ostr_pin = 1;
+    for (int d = 0; d < sh.rank - 1; ++d)
+      if (d != pin) batch *= sh.ext[d];
+    for (int d = sh.rank - 1; d > pin; --d) ostr_pin *= sh.ext[d];
+    const int64_t gx = (sh.ext[sh.rank - 1] + 31) / 32, gy = (sh.ext[pin] + 31) / 32;
+    if (gy <= 65535 && batch <= 65535) {
+      dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)batch);
+      if (dims) {
+        dims->grid[0] = grid.x;
+        dims->grid[1] = grid.y;
+        dims->grid[2] = grid.z;
+        dims->block[0] = 256;
+        dims->smem = sizeof(T) * 32 * 33;
+      }
+      transpose_tile_kernel<T><<<grid, 256, 0, s>>>(sh, pin, (const T*)x, (T*)out, ostr_pin);
+      return cudaGetLastError();
+    }
+  }
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((n + 255) / 256, (int64_t)sms * 16));
+  if (dims) {
+    dims->grid[0] = grid;
+    dims->block[0] = 256;
+  }
+  transpose_scalar_kernel<T><<<grid, 256, 0, s>>>(sh, (const T*)x, (T*)out, n);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t transpose_nd(const TransposeParams& p, const void* x, void* out, cudaStream_t s, LaunchDims* dims) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  Shape6 sh;
+  sh.rank = p.rank;
+  int64_t n = 1;
+  for (int d = 0; d < 6; ++d) {
+    sh.ext[d] = d < p.rank ? p.out_shape[d] : 1;
+    sh.istr[d] = d < p.rank ? p.in_stride[d] : 0;
+    n *= sh.ext[d];
+  }
+  if (n == 0) return cudaSuccess;
+  const int last = p.rank - 1;
+  const int per_vec = 16 / p.esize;
+  bool row_mode = p.in_stride[last] == 1 && (p.out_shape[last] % per_vec) == 0 && aligned16(x) && aligned16(out);
+  for (int d = 0; d < last && row_mode; ++d)
+    if (p.in_stride[d] % per_vec != 0) row_mode = false;
+  if (row_mode) {
+    Shape6 v = sh;
+    v.ext[last] = sh.ext[last] / per_vec;
+    for (int d = 0; d < last; ++d) v.istr[d] = sh.istr[d] / per_vec;
+    const int64_t nvec = n / per_vec;
+    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((nvec + 1023) / 1024, (int64_t)sms * 16));
+    if (dims) {
+      dims->grid[0] = grid;
+      dims->block[0] = 256;
+    }
+    FastDiv6 fd;
+    for (int d = 0; d < 6; ++d) fastdiv_init((uint32_t)std::min<int64_t>(v.ext[d], 0x7fffffff), &fd.mul[d], &fd.shr[d]);
+    if (nvec < (1ll << 31))
+      transpose_rows_kernel<true><<<grid, 256, 0, s>>>(v, fd, (const uint4*)x, (uint4*)out, nvec);
+    else
+      transpose_rows_kernel<false><<<grid, 256, 0, s>>>(v, fd, (const uint4*)x, (uint4*)out, nvec);
+    return cudaGetLastError();
+  }
+  switch (p.esize) {
+    case 1: return tile_or_scalar<uint8_t>(sh, x, out, sms, s, dims);
+    case 2: return tile_or_scalar<uint16_t>(sh, x, out, sms, s, dims);
+    case 4: return tile_or_scalar<uint32_t>(sh, x, out, sms, s, dims);
+    case 8: return tile_or_scalar<uint64_t>(sh, x, out, sms, s, dims);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace akgb

@@ -1,0 +1,89 @@
+// Host-callable launchers of the sm_100a kernel templates.  Each returns the
+// cudaError_t of its launch; none allocates or synchronises.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace akgb {
+
+struct LaunchDims {
+  unsigned grid[3] = {1, 1, 1};
+  unsigned block[3] = {1, 1, 1};
+  unsigned smem = 0;
+};
+
+enum class RedOp : int { Sum = 0, Max = 1, Min = 2, Prod = 3 };
+
+// ---- elementwise: (x [+ bias]) -> tanh-GELU [* y] -> cast ---------------------
+// Per-op rounding in the chain's element type is replayed:
+//   t=x+bias; a=t*t; t3=a*t; b=t3*c0; c=t+b; d=c*c1; e=tanh(d); f=e+1; g=t*c2; h=g*f; k=h*y
+struct GeluChainParams {
+  int64_t n = 0;         // elements
+  int64_t inner = 0;     // bias length (bias index = element index % inner); 0 = no bias
+  int has_mul = 0;       // multiply by y
+  int out_f32 = 0;       // final Cast to float32 (else output stays float16)
+  float c0 = 0.044715f, c1 = 0.7978845608f, c2 = 0.5f, c_one = 1.0f;  // already rounded to f16
+};
+cudaError_t gelu_chain_f16(const GeluChainParams& p, const void* x, const void* bias, const void* y, void* out,
+                           const void* tanh_lut, cudaStream_t s, LaunchDims* dims);
+// 16-bit table of correctly rounded tanh over the f16 magnitudes the kernel
+// looks up; built on the host, `out` needs gelu_lut_entries() uint16 slots.
+int gelu_lut_entries();
+void gelu_lut_build(uint16_t* out);
+
+// ---- row-wise fused patterns ---------------------------------------------------
+struct LayerNormParams {
+  int64_t rows = 0, cols = 0;
+  float inv_n = 0.f, eps = 0.f;
+  int has_gamma = 0, has_beta = 0, write_mean = 0, write_var = 0;
+};
+cudaError_t layernorm_f32(const LayerNormParams& p, const float* x, const float* gamma, const float* beta, float* y,
+                          float* mean, float* var, cudaStream_t s, LaunchDims* dims);
+
+struct SoftmaxParams {
+  int64_t rows = 0, cols = 0;
+  int in_dt = 0, out_dt = 0, mask_dt = 0;  // DT codes: F16/F32/BF16
+  int has_scale = 0, has_mask = 0;
+  float scale = 1.f;
+  int64_t mask_rows = 1;  // mask row = row % mask_rows
+};
+cudaError_t softmax_rows(const SoftmaxParams& p, const void* x, const void* mask, void* out, cudaStream_t s,
+                         LaunchDims* dims);
+
+// ---- reductions ----------------------------------------------------------------
+// x[outer, red, inner] -> out[outer, inner]; f32 only.
+size_t reduce_col_workspace(int64_t red, int64_t inner, int sm_count);
+cudaError_t reduce_col_f32(RedOp op, const float* x, float* out, int64_t red, int64_t inner, void* ws, int sm_count,
+                           cudaStream_t s, LaunchDims* dims);
+size_t reduce_all_workspace(int sm_count);
+cudaError_t reduce_all_f32(RedOp op, const float* x, float* out, int64_t n, void* ws, int sm_count, cudaStream_t s,
+                           LaunchDims* dims);
+cudaError_t reduce_row_f32(RedOp op, const float* x, float* out, int64_t rows, int64_t cols, cudaStream_t s,
+                           LaunchDims* dims);
+
+// ---- transpose -----------------------------------------------------------------
+// General permutation of up to 6 folded dims over elements of `esize` bytes.
+struct TransposeParams {
+  int rank = 0;                 // folded rank, <= 6
+  int64_t out_shape[6] = {0};   // output extents
+  int64_t in_stride[6] = {0};   // input stride (elements) of each OUTPUT dim
+  int esize = 0;                // element size in bytes
+};
+cudaError_t transpose_nd(const TransposeParams& p, const void* x, void* out, cudaStream_t s, LaunchDims* dims);
+
+// ---- matmul + epilogue -----------------------------------------------------------
+struct MatmulParams {
+  int64_t M = 0, N = 0, K = 0;
+  int transpose_b = 0;  // 0: B is [K,N]; 1: B is [N,K]
+  int has_bias = 0;     // bias[N] added in f32
+  int bias_dt = 0;      // DT code of bias (BF16 or F32)
+  int relu = 0;         // max(., 0)
+  int out_dt = 0;       // DT code of the output: BF16 or F32
+};
+// Encodes the TMA descriptors for (A, B) and launches the tcgen05 kernel.
+cudaError_t matmul_bf16(const MatmulParams& p, const void* A, const void* B, const void* bias, void* out,
+                        uint32_t* err_word, int sm_count, cudaStream_t s, LaunchDims* dims);
+bool matmul_bf16_supported(const MatmulParams& p, const char** why);
+
+}  // namespace akgb

@@ -1,0 +1,692 @@
+// Pattern matcher over the fused region: decides which kernel template(s) run
+// it.  Replaces the affine/GPU-dialect mapping of the reference's --gpu-opt
+// pipeline (akg-mlir/lib/Pipelines/GPUPipelines/GPUOpt.cpp:45-132).
+//
+// LayerNorm, GELU and softmax do not arrive as single operators: the JSON
+// factory has no entry for them (TranslateToMindsporeDialect.cpp:417-486), so
+// they are recognised here from their primitive-op spellings, the same DAG
+// shapes mfusion's fusion passes look for
+// (mfusion/lib/Dialect/Mfuse/Transforms/Fusion/Passes/Norm/FuseLayerNorm.cc:131-192,
+//  .../FuseGelu.cc:159-236, mfusion/include/mfusion/Analysis/DvmFusion/SafeSoftmax/SafeSoftmaxDvmUtils.h:29-41).
+// Operand order of commutative ops is free; the association order is not,
+// because every op rounds to its declared element type.
+#include <algorithm>
+#include <cmath>
+#include <set>
+
+#include "hostconv.hpp"
+#include "plan.hpp"
+
+namespace akgb {
+namespace {
+
+struct M {
+  const Graph& g;
+  std::set<int> used;  // node indices consumed by the current pattern
+  explicit M(const Graph& gr) : g(gr) {}
+  M(const M&) = default;
+  M& operator=(const M& o) {
+    used = o.used;
+    return *this;
+  }
+
+  int n_inputs() const { return (int)g.inputs.size(); }
+  Ref ref_of(int vid) const {
+    const Value& v = g.v(vid);
+    Ref r;
+    if (v.input_index >= 0) r.arg = v.input_index;
+    else if (v.output_index >= 0) r.arg = n_inputs() + v.output_index;
+    return r;
+  }
+  bool is_input(int vid) const { return g.v(vid).input_index >= 0; }
+  // node producing vid if it has kind k
+  const Node* prod(int vid, OpK k) {
+    int p = g.v(vid).producer;
+    if (p < 0 || g.nodes[p].kind != k) return nullptr;
+    return &g.nodes[p];
+  }
+  void take(const Node* n) { used.insert((int)(n - &g.nodes[0])); }
+  bool cst(int vid, double* val) const {
+    const Value& v = g.v(vid);
+    if (!v.is_const || v.cval.size() != 1) return false;
+    *val = v.cval[0];
+    return true;
+  }
+  // binary op with one constant operand (either side when commutative)
+  bool bin_const(int vid, OpK k, bool commutative, int* other, double* c) {
+    const Node* n = prod(vid, k);
+    if (!n || n->in.size() != 2) return false;
+    if (cst(n->in[1], c)) {
+      *other = n->in[0];
+      take(n);
+      return true;
+    }
+    if (commutative && cst(n->in[0], c)) {
+      *other = n->in[1];
+      take(n);
+      return true;
+    }
+    return false;
+  }
+  bool bin(int vid, OpK k, int* a, int* b) {
+    const Node* n = prod(vid, k);
+    if (!n || n->in.size() != 2) return false;
+    *a = n->in[0];
+    *b = n->in[1];
+    take(n);
+    return true;
+  }
+  bool un(int vid, OpK k, int* a) {
+    const Node* n = prod(vid, k);
+    if (!n || n->in.empty()) return false;
+    *a = n->in[0];
+    take(n);
+    return true;
+  }
+  // skip view-only ops (Reshape) upwards
+  int through_reshape(int vid) {
+    for (;;) {
+      const Node* n = prod(vid, OpK::Reshape);
+      if (!n) return vid;
+      take(n);
+      vid = n->in[0];
+    }
+  }
+  bool all_used() const { return used.size() == g.nodes.size(); }
+};
+
+int64_t prod_of(const std::vector<int64_t>& s, size_t b, size_t e) {
+  int64_t n = 1;
+  for (size_t i = b; i < e; ++i) n *= s[i];
+  return n;
+}
+
+int64_t io_bytes(const Graph& g) {
+  int64_t b = 0;
+  for (int v : g.inputs) b += g.v(v).numel() * (int64_t)dt_size(g.v(v).dt);
+  for (int v : g.outputs) b += g.v(v).numel() * (int64_t)dt_size(g.v(v).dt);
+  return b;
+}
+
+// reduction over the last axis with keep_dims, returning its operand
+bool row_reduce(M& m, int vid, OpK k, int* src) {
+  const Node* n = m.prod(vid, k);
+  if (!n) return false;
+  const Value& in = m.g.v(n->in[0]);
+  if (n->axes.size() != 1 || n->axes[0] != (int64_t)in.shape.size() - 1) return false;
+  // keep_dims or not, the result has one value per row
+  *src = n->in[0];
+  m.take(n);
+  return true;
+}
+
+// ---------------------------------------------------------------- LayerNorm --
+bool match_layernorm(const Graph& g, Plan& plan) {
+  if (g.outputs.empty()) return false;
+  M m(g);
+  int y = g.outputs[0];
+  const Value& yv = g.v(y);
+  if (yv.dt != DT::F32 || yv.shape.size() < 2) return false;
+  const int64_t cols = yv.shape.back();
+  const int64_t rows = yv.numel() / cols;
+  auto is_row_vec = [&](int vid) {  // a [cols] (or [1,..,cols]) graph input
+    const Value& v = g.v(vid);
+    return m.is_input(vid) && v.dt == DT::F32 && v.numel() == cols && v.shape.back() == cols;
+  };
+  int cur = y, a, b, gamma = -1, beta = -1;
+  {
+    M probe = m;
+    if (probe.bin(cur, OpK::Add, &a, &b) && (is_row_vec(a) || is_row_vec(b))) {
+      m = probe;
+      beta = is_row_vec(b) ? b : a;
+      cur = is_row_vec(b) ? a : b;
+    }
+  }
+  {
+    M probe = m;
+    if (probe.bin(cur, OpK::Mul, &a, &b) && (is_row_vec(a) || is_row_vec(b))) {
+      m = probe;
+      gamma = is_row_vec(b) ? b : a;
+      cur = is_row_vec(b) ? a : b;
+    }
+  }
+  if (!m.bin(cur, OpK::Mul, &a, &b)) return false;
+  // one side is d [rows, cols], the other rstd [rows, 1]
+  int d = a, rstd = b;
+  if (g.v(a).numel() == rows && g.v(b).numel() == rows * cols) std::swap(d, rstd);
+  if (g.v(d).numel() != rows * cols || g.v(rstd).numel() != rows) return false;
+  int ve;
+  if (!m.un(rstd, OpK::Rsqrt, &ve)) return false;
+  int var;
+  double eps;
+  if (!m.bin_const(ve, OpK::Add, true, &var, &eps)) return false;
+  int s2;
+  double inv_n2;
+  if (!m.bin_const(var, OpK::Mul, true, &s2, &inv_n2)) return false;
+  int sq;
+  if (!row_reduce(m, s2, OpK::ReduceSum, &sq)) return false;
+  if (!m.bin(sq, OpK::Mul, &a, &b) || a != d || b != d) return false;
+  int x, mean;
+  if (!m.bin(d, OpK::Sub, &x, &mean)) return false;
+  if (!m.is_input(x) || g.v(x).dt != DT::F32) return false;
+  int s1;
+  double inv_n1;
+  if (!m.bin_const(mean, OpK::Mul, true, &s1, &inv_n1)) return false;
+  int x2;
+  if (!row_reduce(m, s1, OpK::ReduceSum, &x2) || x2 != x) return false;
+  if ((float)inv_n1 != (float)inv_n2) return false;
+
+  // optional extra outputs: mean and var, possibly through a Reshape
+  Ref mean_ref, var_ref;
+  for (size_t i = 1; i < g.outputs.size(); ++i) {
+    int o = g.outputs[i];
+    int src = m.through_reshape(o);
+    if (src == mean && !mean_ref.valid()) mean_ref = m.ref_of(o);
+    else if (src == var && !var_ref.valid()) var_ref = m.ref_of(o);
+    else return false;
+  }
+  if (!m.all_used()) return false;
+  // intermediate values other than mean/var must not be graph outputs
+  Step st;
+  st.kind = StepK::LayerNorm;
+  st.kernel_name = "layernorm_rows_f32";
+  st.a = m.ref_of(x);
+  if (gamma >= 0) st.b = m.ref_of(gamma);
+  if (beta >= 0) st.c = m.ref_of(beta);
+  st.out = m.ref_of(y);
+  st.out2 = mean_ref;
+  st.out3 = var_ref;
+  st.ln.rows = rows;
+  st.ln.cols = cols;
+  st.ln.inv_n = (float)inv_n1;
+  st.ln.eps = (float)eps;
+  st.ln.has_gamma = gamma >= 0;
+  st.ln.has_beta = beta >= 0;
+  st.ln.write_mean = mean_ref.valid();
+  st.ln.write_var = var_ref.valid();
+  plan.klass = "layernorm";
+  plan.steps.push_back(st);
+  return true;
+}
+
+// ------------------------------------------------------------------ Softmax --
+bool match_softmax(const Graph& g, Plan& plan) {
+  if (g.outputs.size() != 1) return false;
+  M m(g);
+  int out = g.outputs[0];
+  const Value& ov = g.v(out);
+  if (ov.shape.empty()) return false;
+  if (ov.dt != DT::F16 && ov.dt != DT::F32 && ov.dt != DT::BF16) return false;
+  const int64_t cols = ov.shape.back();
+  const int64_t rows = ov.numel() / cols;
+  int cur = out, t;
+  if (ov.dt != DT::F32) {
+    if (!m.un(cur, OpK::Cast, &t)) return false;
+    cur = t;
+  }
+  if (g.v(cur).dt != DT::F32) return false;
+  int e, sum;
+  if (!m.bin(cur, OpK::Div, &e, &sum)) return false;
+  int e2;
+  if (!row_reduce(m, sum, OpK::ReduceSum, &e2) || e2 != e) return false;
+  int sh;
+  if (!m.un(e, OpK::Exp, &sh)) return false;
+  int s, mx;
+  if (!m.bin(sh, OpK::Sub, &s, &mx)) return false;
+  int s2;
+  if (!row_reduce(m, mx, OpK::ReduceMax, &s2) || s2 != s) return false;
+  if (g.v(s).numel() != rows * cols) return false;
+
+  // pre-chain: s = [Add(., mask)]([Mul(., scale)]([Cast](x)))
+  int mask = -1;
+  DT mask_dt = DT::F32;
+  int a, b;
+  {
+    M probe = m;
+    if (probe.bin(s, OpK::Add, &a, &b)) {
+      auto mask_src = [&](int vid, int* src) {
+        M p2 = probe;
+        int c = vid, q;
+        if (p2.un(c, OpK::Cast, &q)) c = q;
+        if (!p2.is_input(c)) return false;
+        if (g.v(c).numel() == rows * cols) return false;  // that is the data operand
+        probe = p2;
+        *src = c;
+        return true;
+      };
+      int src;
+      if (mask_src(b, &src)) {
+        mask = src;
+        s = a;
+        m = probe;
+      } else if (mask_src(a, &src)) {
+        mask = src;
+        s = b;
+        m = probe;
+      }
+    }
+  }
+  double scale = 1.0;
+  int has_scale = 0;
+  {
+    M probe = m;
+    int other;
+    double c;
+    if (probe.bin_const(s, OpK::Mul, true, &other, &c)) {
+      m = probe;
+      s = other;
+      scale = c;
+      has_scale = 1;
+    }
+  }
+  int x = s;
+  if (!m.is_input(x)) {
+    int q;
+    if (!m.un(x, OpK::Cast, &q) || !m.is_input(q)) return false;
+    x = q;
+  }
+  const Value& xv = g.v(x);
+  if (xv.numel() != rows * cols) return false;
+  if (xv.dt != DT::F16 && xv.dt != DT::F32 && xv.dt != DT::BF16) return false;
+  int64_t mask_rows = 1;
+  if (mask >= 0) {
+    const Value& mv = g.v(mask);
+    mask_dt = mv.dt;
+    if (mask_dt != DT::F16 && mask_dt != DT::F32 && mask_dt != DT::BF16) return false;
+    if (mv.shape.back() != cols) return false;
+    // the mask's dims must be the trailing dims of x (leading 1s allowed)
+    std::vector<int64_t> ms = mv.shape;
+    while (ms.size() > 1 && ms.front() == 1) ms.erase(ms.begin());
+    if (ms.size() > xv.shape.size()) return false;
+    for (size_t i = 0; i < ms.size(); ++i)
+      if (ms[ms.size() - 1 - i] != xv.shape[xv.shape.size() - 1 - i]) return false;
+    mask_rows = mv.numel() / cols;
+  }
+  if (!m.all_used()) return false;
+
+  Step st;
+  st.kind = StepK::Softmax;
+  st.kernel_name = "softmax_rows";
+  st.a = m.ref_of(x);
+  if (mask >= 0) st.b = m.ref_of(mask);
+  st.out = m.ref_of(out);
+  st.sm.rows = rows;
+  st.sm.cols = cols;
+  st.sm.in_dt = (int)xv.dt;
+  st.sm.out_dt = (int)ov.dt;
+  st.sm.mask_dt = (int)mask_dt;
+  st.sm.has_scale = has_scale;
+  st.sm.has_mask = mask >= 0;
+  st.sm.scale = (float)scale;
+  st.sm.mask_rows = mask_rows;
+  plan.klass = "softmax";
+  plan.steps.push_back(st);
+  return true;
+}
+
+// --------------------------------------------------------------- reductions --
+bool match_reduce(const Graph& g, Plan& plan, int sm_count) {
+  M m(g);
+  std::vector<Step> steps;
+  size_t ws = 0;
+  std::string klass;
+  for (int o : g.outputs) {
+    int src = m.through_reshape(o);
+    int p = g.v(src).producer;
+    if (p < 0) return false;
+    const Node& n = g.nodes[p];
+    RedOp op;
+    switch (n.kind) {
+      case OpK::ReduceSum: op = RedOp::Sum; break;
+      case OpK::ReduceMax: op = RedOp::Max; break;
+      case OpK::ReduceMin: op = RedOp::Min; break;
+      case OpK::ReduceProd: op = RedOp::Prod; break;
+      default: return false;
+    }
+    m.take(&n);
+    int x = n.in[0];
+    // a view change of the input is free
+    x = m.through_reshape(x);
+    if (!m.is_input(x) || g.v(x).dt != DT::F32 || g.v(o).dt != DT::F32) return false;
+    const std::vector<int64_t>& xs = g.v(n.in[0]).shape;
+    // reduced axes must form one contiguous range once extent-1 axes are ignored
+    std::vector<bool> red(xs.size(), false);
+    for (auto a : n.axes) red[a] = true;
+    int64_t outer = 1, len = 1, inner = 1;
+    int phase = 0;  // 0 outer, 1 reduce, 2 inner
+    for (size_t i = 0; i < xs.size(); ++i) {
+      if (xs[i] == 1) continue;
+      if (red[i]) {
+        if (phase == 2) return false;
+        phase = 1;
+        len *= xs[i];
+      } else {
+        if (phase == 1) phase = 2;
+        if (phase == 0) outer *= xs[i];
+        else inner *= xs[i];
+      }
+    }
+    Step st;
+    st.red_op = op;
+    st.red_outer = outer;
+    st.red_len = len;
+    st.red_inner = inner;
+    st.a = m.ref_of(x);
+    st.out = m.ref_of(o);
+    if (inner == 1 && outer == 1) {
+      st.kind = StepK::ReduceAll;
+      st.kernel_name = "reduce_all_f32";
+      st.scratch.ws_off = (int64_t)ws;
+      ws += (reduce_all_workspace(sm_count) + 255) / 256 * 256;
+      if (klass.empty()) klass = "reduce_all";
+    } else if (inner == 1) {
+      st.kind = StepK::ReduceRow;
+      st.kernel_name = "reduce_row_f32";
+      if (klass.empty()) klass = "reduce_x";
+    } else {
+      st.kind = StepK::ReduceCol;
+      st.kernel_name = "reduce_col_f32";
+      if (outer != 1) return false;  // batched column reductions: not yet placed
+      st.scratch.ws_off = (int64_t)ws;
+      ws += (reduce_col_workspace(len, inner, sm_count) + 255) / 256 * 256;
+      if (klass.empty()) klass = "reduce_y";
+    }
+    steps.push_back(st);
+  }
+  if (!m.all_used()) return false;
+  plan.klass = klass;
+  plan.steps = steps;
+  plan.workspace_bytes = ws;
+  return true;
+}
+
+// ---------------------------------------------------------------- transpose --
+bool match_transpose(const Graph& g, Plan& plan) {
+  if (g.outputs.size() != 1) return false;
+  M m(g);
+  int o = m.through_reshape(g.outputs[0]);
+  const Node* n = m.prod(o, OpK::Transpose);
+  if (!n) return false;
+  m.take(n);
+  int x = m.through_reshape(n->in[0]);
+  if (!m.is_input(x) || !m.all_used()) return false;
+  const std::vector<int64_t>& xs = g.v(n->in[0]).shape;
+  const size_t R = xs.size();
+  std::vector<int64_t> xstride(R, 1);
+  for (int i = (int)R - 2; i >= 0; --i) xstride[i] = xstride[i + 1] * xs[i + 1];
+  // output dims in order, dropping extent-1 dims, merging dims that are also
+  // adjacent (and in order) in the input
+  std::vector<int64_t> oshape, istride;
+  std::vector<int64_t> src_axis;
+  for (size_t i = 0; i < R; ++i) {
+    int64_t ax = n->perm[i];
+    if (xs[ax] == 1) continue;
+    if (!src_axis.empty() && src_axis.back() + 1 == ax) {
+      // merge unless an extent-1 axis sits between them — extent-1 never breaks adjacency
+      oshape.back() *= xs[ax];
+      istride.back() = xstride[ax];
+      src_axis.back() = ax;
+    } else {
+      oshape.push_back(xs[ax]);
+      istride.push_back(xstride[ax]);
+      src_axis.push_back(ax);
+    }
+  }
+  // adjacency across dropped extent-1 axes
+  if (oshape.empty()) {
+    oshape.push_back(1);
+    istride.push_back(1);
+  }
+  if (oshape.size() > 6) return false;
+  Step st;
+  st.kind = StepK::Transpose;
+  st.kernel_name = "transpose_nd";
+  st.a = m.ref_of(x);
+  st.out = m.ref_of(g.outputs[0]);
+  st.tp.rank = (int)oshape.size();
+  for (size_t i = 0; i < oshape.size(); ++i) {
+    st.tp.out_shape[i] = oshape[i];
+    st.tp.in_stride[i] = istride[i];
+  }
+  st.tp.esize = (int)dt_size(g.v(x).dt);
+  plan.klass = "transpose";
+  plan.steps.push_back(st);
+  return true;
+}
+
+// ------------------------------------------------------- matmul + epilogue --
+bool match_matmul(const Graph& g, Plan& plan) {
+  if (g.outputs.size() != 1) return false;
+  M m(g);
+  int out = g.outputs[0];
+  int cur = out, t;
+  DT out_dt = g.v(out).dt;
+  if (out_dt == DT::BF16) {
+    M probe = m;
+    if (probe.un(cur, OpK::Cast, &t) && g.v(t).dt == DT::F32) {
+      m = probe;
+      cur = t;
+    }
+  } else if (out_dt != DT::F32) {
+    return false;
+  }
+  int relu = 0;
+  {
+    M probe = m;
+    int other;
+    double c;
+    if (probe.bin_const(cur, OpK::Maximum, true, &other, &c) && c == 0.0) {
+      m = probe;
+      relu = 1;
+      cur = other;
+    }
+  }
+  int bias = -1;
+  DT bias_dt = DT::F32;
+  {
+    M probe = m;
+    int a, b;
+    if (probe.bin(cur, OpK::Add, &a, &b)) {
+      auto bias_src = [&](int vid, int* src) {
+        M p2 = probe;
+        int c = vid, q;
+        if (p2.un(c, OpK::Cast, &q)) c = q;
+        if (!p2.is_input(c)) return false;
+        probe = p2;
+        *src = c;
+        return true;
+      };
+      int src;
+      bool a_mm = g.v(a).producer >= 0 && (g.nodes[g.v(a).producer].kind == OpK::MatMul);
+      bool b_mm = g.v(b).producer >= 0 && (g.nodes[g.v(b).producer].kind == OpK::MatMul);
+      if (a_mm && bias_src(b, &src)) {
+        bias = src;
+        cur = a;
+        m = probe;
+      } else if (b_mm && bias_src(a, &src)) {
+        bias = src;
+        cur = b;
+        m = probe;
+      }
+    }
+  }
+  const Node* mmn = m.prod(cur, OpK::MatMul);
+  if (!mmn) return false;
+  m.take(mmn);
+  if (mmn->transpose_a) throw Unsupported("MatMul with transpose_a is rejected (as by the reference lowering)");
+  int A = mmn->in[0], B = mmn->in[1];
+  if (!m.is_input(A) || !m.is_input(B) || !m.all_used()) return false;
+  const Value& av = g.v(A);
+  const Value& bv = g.v(B);
+  if (av.dt != DT::BF16 || bv.dt != DT::BF16) return false;
+  if (av.shape.size() != 2 || bv.shape.size() != 2) return false;
+  // accumulation happens in the MatMul's declared result type; only f32 is placed
+  if (g.v(cur).dt != DT::F32) return false;
+  MatmulParams p;
+  p.M = av.shape[0];
+  p.K = av.shape[1];
+  p.transpose_b = mmn->transpose_b;
+  p.N = mmn->transpose_b ? bv.shape[0] : bv.shape[1];
+  int64_t kb = mmn->transpose_b ? bv.shape[1] : bv.shape[0];
+  if (kb != p.K) throw JsonError("MatMul inner extents disagree");
+  if (bias >= 0) {
+    const Value& biasv = g.v(bias);
+    if (biasv.numel() != p.N || biasv.shape.back() != p.N) return false;
+    bias_dt = biasv.dt;
+    if (bias_dt != DT::BF16 && bias_dt != DT::F32) return false;
+    p.has_bias = 1;
+  }
+  p.bias_dt = (int)bias_dt;
+  p.relu = relu;
+  p.out_dt = (int)out_dt;
+  const char* why = nullptr;
+  if (!matmul_bf16_supported(p, &why)) throw Unsupported(std::string("matmul shape not placed: ") + why);
+  Step st;
+  st.kind = StepK::Matmul;
+  st.kernel_name = "matmul_bf16_tcgen05";
+  st.a = m.ref_of(A);
+  st.b = m.ref_of(B);
+  if (bias >= 0) st.c = m.ref_of(bias);
+  st.out = m.ref_of(out);
+  st.mm = p;
+  plan.klass = "matmul";
+  plan.flops = 2 * p.M * p.N * p.K;
+  plan.steps.push_back(st);
+  return true;
+}
+
+// --------------------------------------------------------------- GELU chain --
+bool match_gelu_chain(const Graph& g, Plan& plan) {
+  if (g.outputs.size() != 1) return false;
+  M m(g);
+  int out = g.outputs[0];
+  int cur = out, q;
+  int out_f32 = 0;
+  if (g.v(out).dt == DT::F32) {
+    if (!m.un(cur, OpK::Cast, &q) || g.v(q).dt != DT::F16) return false;
+    cur = q;
+    out_f32 = 1;
+  } else if (g.v(out).dt != DT::F16) {
+    return false;
+  }
+  const int64_t n = g.v(out).numel();
+  // k = Mul(h, y) with y a full-size graph input — optional
+  int ymul = -1, a, b;
+  {
+    M probe = m;
+    if (probe.bin(cur, OpK::Mul, &a, &b)) {
+      if (probe.is_input(b) && g.v(b).numel() == n && g.v(b).dt == DT::F16 && !probe.is_input(a)) {
+        ymul = b;
+        cur = a;
+        m = probe;
+      } else if (probe.is_input(a) && g.v(a).numel() == n && g.v(a).dt == DT::F16 && !probe.is_input(b)) {
+        ymul = a;
+        cur = b;
+        m = probe;
+      }
+    }
+  }
+  // h = Mul(g_, f); g_ = Mul(t, 0.5); f = Add(e, 1)
+  int gh, f;
+  if (!m.bin(cur, OpK::Mul, &gh, &f)) return false;
+  double c2, c_one;
+  int t_a, e;
+  {
+    M probe = m;
+    if (!(probe.bin_const(gh, OpK::Mul, true, &t_a, &c2) && probe.bin_const(f, OpK::Add, true, &e, &c_one))) {
+      probe = m;
+      std::swap(gh, f);
+      if (!(probe.bin_const(gh, OpK::Mul, true, &t_a, &c2) && probe.bin_const(f, OpK::Add, true, &e, &c_one)))
+        return false;
+    }
+    m = probe;
+  }
+  int d;
+  if (!m.un(e, OpK::Tanh, &d)) return false;
+  int c;
+  double c1;
+  if (!m.bin_const(d, OpK::Mul, true, &c, &c1)) return false;
+  int t_b, bb;
+  if (!m.bin(c, OpK::Add, &t_b, &bb)) return false;
+  if (t_b != t_a) std::swap(t_b, bb);
+  if (t_b != t_a) return false;
+  int t3;
+  double c0;
+  if (!m.bin_const(bb, OpK::Mul, true, &t3, &c0)) return false;
+  int sq, t_c;
+  if (!m.bin(t3, OpK::Mul, &sq, &t_c)) return false;
+  if (t_c != t_a) std::swap(sq, t_c);
+  if (t_c != t_a) return false;
+  int s_a, s_b;
+  if (!m.bin(sq, OpK::Mul, &s_a, &s_b) || s_a != t_a || s_b != t_a) return false;
+  // t = Add(x, bias) or t = x
+  int x = t_a, bias = -1;
+  int64_t inner = 0;
+  if (!m.is_input(x)) {
+    if (!m.bin(t_a, OpK::Add, &a, &b)) return false;
+    if (!m.is_input(a) || !m.is_input(b)) return false;
+    if (g.v(a).numel() != n) std::swap(a, b);
+    x = a;
+    bias = b;
+    const Value& bv = g.v(bias);
+    const Value& xv = g.v(x);
+    if (bv.dt != DT::F16 || bv.shape.back() != xv.shape.back() || bv.numel() != xv.shape.back()) return false;
+    inner = bv.numel();
+  }
+  if (g.v(x).dt != DT::F16 || g.v(x).numel() != n) return false;
+  if (g.v(d).dt != DT::F16 || g.v(e).dt != DT::F16) return false;
+  if (!m.all_used()) return false;
+
+  Step st;
+  st.kind = StepK::GeluChain;
+  st.kernel_name = "gelu_chain_f16";
+  st.a = m.ref_of(x);
+  if (bias >= 0) st.b = m.ref_of(bias);
+  if (ymul >= 0) st.c = m.ref_of(ymul);
+  st.out = m.ref_of(out);
+  st.gelu.n = n;
+  st.gelu.inner = inner;
+  st.gelu.has_mul = ymul >= 0;
+  st.gelu.out_f32 = out_f32;
+  st.gelu.c0 = round_f64_to_f16(c0);
+  st.gelu.c1 = round_f64_to_f16(c1);
+  st.gelu.c2 = round_f64_to_f16(c2);
+  st.gelu.c_one = round_f64_to_f16(c_one);
+  plan.klass = inner ? "broadcast" : "elementwise";
+  plan.needs_gelu_lut = true;
+  plan.steps.push_back(st);
+  return true;
+}
+
+}  // namespace
+
+Plan build_plan(const Graph& g, int sm_count) {
+  for (auto& n : g.nodes)
+    if (n.kind == OpK::Unknown)
+      throw Unsupported("operator '" + n.name + "' is not supported");
+  Plan plan;
+  bool ok = false;
+  switch (g.op_class) {
+    case OpClass::Matmul:
+      ok = match_matmul(g, plan);
+      break;
+    case OpClass::Reduction:
+      ok = match_layernorm(g, plan) || match_softmax(g, plan) || match_reduce(g, plan, sm_count);
+      break;
+    case OpClass::Transpose:
+      ok = match_transpose(g, plan);
+      break;
+    default:
+      ok = match_gelu_chain(g, plan);
+      break;
+  }
+  if (!ok) {
+    plan = Plan();
+    throw Unsupported("no kernel template matches this fused region (class " +
+                      std::to_string((int)g.op_class) + ")");
+  }
+  plan.bytes = io_bytes(g);
+  return plan;
+}
+
+}  // namespace akgb

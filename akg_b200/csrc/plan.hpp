@@ -1,0 +1,49 @@
+// Execution plan of one fused region: an ordered list of kernel-template
+// instantiations over argument slots and workspace offsets.
+#pragma once
+#include <string>
+#include <vector>
+
+#include "graph.hpp"
+#include "kernels.hpp"
+
+namespace akgb {
+
+// Where a kernel operand lives at launch: a caller tensor (index into the
+// inputs-then-outputs list) or an offset into the caller's workspace.
+struct Ref {
+  int arg = -1;
+  int64_t ws_off = -1;
+  bool valid() const { return arg >= 0 || ws_off >= 0; }
+};
+
+enum class StepK : int { GeluChain, LayerNorm, Softmax, ReduceCol, ReduceAll, ReduceRow, Transpose, Matmul };
+
+struct Step {
+  StepK kind;
+  std::string kernel_name;  // device symbol family, for the metadata JSON
+  Ref a, b, c, out, out2, out3;
+  Ref scratch;              // partials
+  GeluChainParams gelu;
+  LayerNormParams ln;
+  SoftmaxParams sm;
+  RedOp red_op = RedOp::Sum;
+  int64_t red_outer = 1, red_len = 1, red_inner = 1;
+  TransposeParams tp;
+  MatmulParams mm;
+  LaunchDims dims;          // filled at first launch
+};
+
+struct Plan {
+  std::string klass;        // operator class reported to the caller
+  std::vector<Step> steps;
+  size_t workspace_bytes = 0;
+  int64_t bytes = 0;        // algorithmic bytes: inputs read once + outputs written once
+  int64_t flops = 0;
+  bool needs_gelu_lut = false;
+};
+
+// Pattern matcher: places the region on kernel templates or throws Unsupported.
+Plan build_plan(const Graph& g, int sm_count);
+
+}  // namespace akgb

@@ -1,0 +1,215 @@
+"""Builders of fused-op descriptions (``.info`` JSON) for the benchmarked operator classes.
+
+The schema is the one MindSpore's graph-kernel module emits and
+``akg-mlir/lib/Target/MindsporeDialect/TranslateToMindsporeDialect.cpp:295-415``
+reads: ``op``, ``process``, ``input_desc`` (list of one-element lists),
+``op_desc`` (name, attr, input_desc, output_desc) and ``output_desc``.
+LayerNorm, GELU and softmax are spelled with primitive ops because the JSON
+factory has no entry for them (``:417-486``).  Constants are operands that carry
+a ``value`` (``:650-658``).
+"""
+from __future__ import annotations
+
+import math
+from typing import Sequence
+
+
+def _t(name: str, shape: Sequence[int], dtype: str, value=None) -> dict:
+    d = {"data_type": dtype, "format": "DefaultFormat", "shape": list(shape), "tensor_name": name}
+    if value is not None:
+        d["value"] = value
+    return d
+
+
+def _attr(name: str, dtype: str, value) -> dict:
+    return {"name": name, "data_type": dtype, "value": value}
+
+
+class _Builder:
+    def __init__(self, op: str):
+        self.op = op
+        self.inputs: list[dict] = []
+        self.ops: list[dict] = []
+        self.outputs: list[dict] = []
+        self._n = 0
+
+    def input(self, name, shape, dtype):
+        t = _t(name, shape, dtype)
+        self.inputs.append(t)
+        return t
+
+    def const(self, value, dtype):
+        self._n += 1
+        return _t(f"const_{self._n}", [1], dtype, value)
+
+    def emit(self, name, ins, shape, dtype, attr=None, out_name=None):
+        self._n += 1
+        out = _t(out_name or f"t{self._n}_{name.lower()}", shape, dtype)
+        self.ops.append({"name": name, "attr": attr, "impl_path": "",
+                         "input_desc": [[dict(i)] for i in ins], "output_desc": [dict(out)]})
+        return out
+
+    def output(self, t):
+        self.outputs.append(dict(t))
+
+    def build(self) -> dict:
+        return {"composite": True, "op": self.op, "process": "cuda", "platform": "AKG", "version": 2,
+                "target_info": {"compute_capability": "10.0", "sm_count": 148},
+                "input_desc": [[dict(i)] for i in self.inputs], "op_desc": self.ops,
+                "output_desc": self.outputs}
+
+
+def _reduce_attr(axes, keep_dims):
+    return [_attr("axis", "listInt", list(axes)), _attr("keep_dims", "bool", bool(keep_dims))]
+
+
+def layernorm(rows: int, cols: int, eps: float = 1e-5, with_stats: bool = True) -> dict:
+    """x f32[rows, cols], gamma/beta f32[cols] -> y, mean[rows], var[rows]."""
+    b = _Builder(f"Fused_LayerNorm_{rows}x{cols}_1")
+    f = "float32"
+    x = b.input("x", [rows, cols], f)
+    gamma = b.input("gamma", [cols], f)
+    beta = b.input("beta", [cols], f)
+    inv_n = 1.0 / cols
+    s1 = b.emit("ReduceSum", [x], [rows, 1], f, _reduce_attr([1], True))
+    mean = b.emit("Mul", [s1, b.const(inv_n, f)], [rows, 1], f)
+    d = b.emit("Sub", [x, mean], [rows, cols], f)
+    sq = b.emit("Mul", [d, d], [rows, cols], f)
+    s2 = b.emit("ReduceSum", [sq], [rows, 1], f, _reduce_attr([1], True))
+    var = b.emit("Mul", [s2, b.const(inv_n, f)], [rows, 1], f)
+    ve = b.emit("Add", [var, b.const(eps, f)], [rows, 1], f)
+    rstd = b.emit("Rsqrt", [ve], [rows, 1], f)
+    n0 = b.emit("Mul", [d, rstd], [rows, cols], f)
+    n1 = b.emit("Mul", [n0, gamma], [rows, cols], f)
+    y = b.emit("Add", [n1, beta], [rows, cols], f, out_name="y")
+    b.output(y)
+    if with_stats:
+        shp = [_attr("shape", "listInt", [rows])]
+        b.output(b.emit("Reshape", [mean], [rows], f, shp, out_name="mean_out"))
+        b.output(b.emit("Reshape", [var], [rows], f, shp, out_name="var_out"))
+    return b.build()
+
+
+GELU_C0 = 0.044715
+GELU_C1 = 0.7978845608
+GELU_C2 = 0.5
+
+
+def gelu_chain(shape: Sequence[int], with_bias: bool = True, with_mul: bool = True, cast_f32: bool = True) -> dict:
+    """x f16[shape] (+ bias f16[shape[-1]]) -> tanh-GELU (* y f16[shape]) (-> f32); all math in f16."""
+    shape = list(shape)
+    b = _Builder("Fused_BiasAdd_Gelu_Mul_Cast_" + "x".join(map(str, shape)) + "_2")
+    h = "float16"
+    x = b.input("x", shape, h)
+    t = x
+    if with_bias:
+        bias = b.input("bias", [shape[-1]], h)
+        t = b.emit("Add", [x, bias], shape, h)
+    y = b.input("y", shape, h) if with_mul else None
+    a = b.emit("Mul", [t, t], shape, h)
+    t3 = b.emit("Mul", [a, t], shape, h)
+    bb = b.emit("Mul", [t3, b.const(GELU_C0, h)], shape, h)
+    c = b.emit("Add", [t, bb], shape, h)
+    d = b.emit("Mul", [c, b.const(GELU_C1, h)], shape, h)
+    e = b.emit("Tanh", [d], shape, h)
+    f = b.emit("Add", [e, b.const(1.0, h)], shape, h)
+    g = b.emit("Mul", [t, b.const(GELU_C2, h)], shape, h)
+    out = b.emit("Mul", [g, f], shape, h)
+    if with_mul:
+        out = b.emit("Mul", [out, y], shape, h)
+    if cast_f32:
+        out = b.emit("Cast", [out], shape, "float32", [_attr("dst_type", "str", "float32")])
+    b.output(out)
+    return b.build()
+
+
+def masked_softmax(batch: int, rows: int, cols: int, scale: float = 1.0 / math.sqrt(128.0), dtype: str = "float16",
+                   with_mask: bool = True) -> dict:
+    """scores[batch, rows, cols] * scale + mask[rows, cols] -> softmax over the last axis, same dtype out."""
+    b = _Builder(f"Fused_Cast_Mul_Add_Softmax_Cast_{batch}x{rows}x{cols}_3")
+    f = "float32"
+    full = [batch, rows, cols]
+    red = [batch, rows, 1]
+    x = b.input("scores", full, dtype)
+    s = x
+    if dtype != f:
+        s = b.emit("Cast", [s], full, f, [_attr("dst_type", "str", f)])
+    s = b.emit("Mul", [s, b.const(scale, f)], full, f)
+    if with_mask:
+        m = b.input("mask", [rows, cols], dtype)
+        mf = m
+        if dtype != f:
+            mf = b.emit("Cast", [m], [rows, cols], f, [_attr("dst_type", "str", f)])
+        s = b.emit("Add", [s, mf], full, f)
+    mx = b.emit("ReduceMax", [s], red, f, _reduce_attr([2], True))
+    sh = b.emit("Sub", [s, mx], full, f)
+    e = b.emit("Exp", [sh], full, f)
+    sm = b.emit("ReduceSum", [e], red, f, _reduce_attr([2], True))
+    out = b.emit("RealDiv", [e, sm], full, f)
+    if dtype != f:
+        out = b.emit("Cast", [out], full, dtype, [_attr("dst_type", "str", dtype)])
+    b.output(out)
+    return b.build()
+
+
+def reduce_sum_axis0(rows: int, cols: int) -> dict:
+    """x f32[rows, cols] -> sum over axis 0 -> f32[cols] (reduce-Y class)."""
+    b = _Builder(f"Fused_ReduceSum_axis0_{rows}x{cols}_4")
+    x = b.input("x", [rows, cols], "float32")
+    b.output(b.emit("ReduceSum", [x], [cols], "float32", _reduce_attr([0], False), out_name="colsum"))
+    return b.build()
+
+
+def reduce_max_all(rows: int, cols: int) -> dict:
+    """x f32[rows, cols] -> global max -> f32[1] (reduce-ALL class)."""
+    b = _Builder(f"Fused_ReduceMax_all_{rows}x{cols}_5")
+    x = b.input("x", [rows, cols], "float32")
+    b.output(b.emit("ReduceMax", [x], [1], "float32", _reduce_attr([0, 1], False), out_name="gmax"))
+    return b.build()
+
+
+def reduce_sum_and_max(rows: int, cols: int) -> dict:
+    """Both reductions of the same input in one fused region."""
+    b = _Builder(f"Fused_ReduceSum_ReduceMax_{rows}x{cols}_6")
+    x = b.input("x", [rows, cols], "float32")
+    b.output(b.emit("ReduceSum", [x], [cols], "float32", _reduce_attr([0], False), out_name="colsum"))
+    b.output(b.emit("ReduceMax", [x], [1], "float32", _reduce_attr([0, 1], False), out_name="gmax"))
+    return b.build()
+
+
+def matmul_bias_relu(m: int, k: int, n: int, transpose_b: bool = False, with_bias: bool = True,
+                     relu: bool = True) -> dict:
+    """A bf16[m,k] x B bf16[k,n] -> f32 accumulate (+ bias bf16[n]) (ReLU) -> bf16[m,n]."""
+    b = _Builder(f"Fused_MatMul_BiasAdd_ReLU_Cast_{m}x{k}x{n}_7")
+    h, f = "bfloat16", "float32"
+    a = b.input("a", [m, k], h)
+    bm = b.input("b", [n, k] if transpose_b else [k, n], h)
+    attr = [_attr("transpose_a", "bool", False), _attr("transpose_b", "bool", bool(transpose_b))]
+    c = b.emit("MatMul", [a, bm], [m, n], f, attr)
+    if with_bias:
+        bias = b.input("bias", [n], h)
+        bf = b.emit("Cast", [bias], [n], f, [_attr("dst_type", "str", f)])
+        c = b.emit("Add", [c, bf], [m, n], f)
+    if relu:
+        c = b.emit("Maximum", [c, b.const(0.0, f)], [m, n], f)
+    out = b.emit("Cast", [c], [m, n], h, [_attr("dst_type", "str", h)], out_name="out")
+    b.output(out)
+    return b.build()
+
+
+def transpose(shape: Sequence[int], perm: Sequence[int], dtype: str = "float16") -> dict:
+    shape, perm = list(shape), list(perm)
+    b = _Builder("Fused_Transpose_" + "x".join(map(str, shape)) + "_8")
+    x = b.input("x", shape, dtype)
+    oshape = [shape[p] for p in perm]
+    b.output(b.emit("Transpose", [x], oshape, dtype, [_attr("perm", "listInt", perm)], out_name="xt"))
+    return b.build()
+
+
+def unary(op: str, shape: Sequence[int], dtype: str) -> dict:
+    """A single unary operator over one tensor."""
+    shape = list(shape)
+    b = _Builder(f"Fused_{op}_" + "x".join(map(str, shape)) + "_9")
+    x = b.input("x", shape, dtype)
+    b.output(b.emit(op, [x], shape, dtype, out_name="out"))
+    return b.build()

@@ -1,0 +1,153 @@
+/*
+ * akgb.h — C ABI of the B200 fused-operator library.
+ *
+ * The library takes the MindSpore graph-kernel fused-op description (the
+ * ".info" JSON that AKG-MLIR's `mindspore-translate` reads) and runs it on an
+ * sm_100a device.  Every entry point below replaces one step of the
+ * reference's GPU lowering + launch path; the reference interface it stands in
+ * for is cited as <file within akg-mlir>:<line>.
+ *
+ * Conventions
+ *   - plain C types only; tensors are bare pointers, dense row-major, offset 0
+ *     (python/akg_mlir/mlir_driver.py:211-216, lib/Pipelines/GPUPipelines/GPUCodegen.cpp:50)
+ *   - argument order of every tensor list: `input_desc` order, then
+ *     `output_desc` order (lib/Target/MindsporeDialect/TranslateToMindsporeDialect.cpp:581-611)
+ *   - every call returns an akgb_status; nothing here exits the process
+ *     (the reference launcher calls exit(1) on a CUDA error,
+ *     python/akg_mlir/utils/code_template.py:47-56)
+ *   - there is no CPU fallback: a fused region the matcher cannot place on a
+ *     kernel template yields AKGB_UNSUPPORTED.
+ */
+#ifndef AKGB_H_
+#define AKGB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum akgb_status {
+  AKGB_OK = 0,
+  AKGB_INVALID_JSON = 1,   /* malformed text or a key the schema requires is missing */
+  AKGB_UNSUPPORTED = 2,    /* valid description, but no kernel template covers it */
+  AKGB_INVALID_ARG = 3,    /* null pointer, short buffer, bad option */
+  AKGB_CUDA_ERROR = 4,     /* a CUDA runtime/driver call failed; see akgb_last_error() */
+  AKGB_MISALIGNED = 5,     /* a tensor pointer is not 16-byte aligned */
+  AKGB_DEVICE_TIMEOUT = 6, /* a bounded device-side wait gave up (error word set) */
+  AKGB_TOO_LARGE = 7       /* size beyond a fixed-capacity entry point's limit */
+} akgb_status;
+
+/* Element types of the .info schema (TranslateToMindsporeDialect.cpp:488-502). */
+typedef enum akgb_dtype {
+  AKGB_BOOL = 0, AKGB_INT8 = 1, AKGB_INT16 = 2, AKGB_INT32 = 3, AKGB_INT64 = 4,
+  AKGB_FLOAT16 = 5, AKGB_FLOAT32 = 6, AKGB_FLOAT64 = 7, AKGB_BFLOAT16 = 8
+} akgb_dtype;
+
+/* How a tensor argument relates to the leading-axis shard this kernel was
+ * compiled for (see akgb_options.shard_world). */
+typedef enum akgb_shard_kind {
+  AKGB_REPLICATED = 0,   /* every rank passes the whole tensor */
+  AKGB_SPLIT_AXIS0 = 1,  /* each rank passes its contiguous slice of axis 0 */
+  AKGB_PARTIAL_SUM = 2,  /* output holds a per-rank partial: all-reduce(sum) it */
+  AKGB_PARTIAL_MAX = 3,  /* all-reduce(max) */
+  AKGB_PARTIAL_MIN = 4,  /* all-reduce(min) */
+  AKGB_PARTIAL_PROD = 5  /* all-reduce(prod) */
+} akgb_shard_kind;
+
+#define AKGB_MAX_RANK 8
+
+typedef struct akgb_tensor_desc {
+  char name[64];
+  int32_t dtype;                 /* akgb_dtype */
+  int32_t rank;
+  int64_t shape[AKGB_MAX_RANK];  /* the LOCAL shape (after sharding) */
+  int64_t nbytes;                /* local size in bytes */
+  int32_t is_output;
+  int32_t shard_kind;            /* akgb_shard_kind */
+} akgb_tensor_desc;
+
+typedef struct akgb_options {
+  int32_t struct_size;  /* sizeof(akgb_options); lets the struct grow */
+  int32_t device;       /* CUDA device ordinal; -1 = current device */
+  int32_t shard_rank;   /* this rank's index in the leading-axis split */
+  int32_t shard_world;  /* number of ranks the leading axis is split over; 0/1 = no split */
+  int32_t flags;        /* reserved, 0 */
+} akgb_options;
+
+typedef struct akgb_kernel akgb_kernel;
+
+/* Parse + classify + match + plan.  Replaces `mindspore-translate`,
+ * `akg-opt --gpu-opt`, `--gpu-codegen`, `akg-translate -gen-ptx` and
+ * `akg-ptx-replace` (python/akg_mlir/mlir_driver.py:337-374).  Needs no GPU. */
+akgb_status akgb_compile(const char* info_json, size_t len, const akgb_options* opt,
+                         akgb_kernel** out);
+
+/* Frees the plan and any staging memory the library allocated for it. */
+void akgb_release(akgb_kernel* k);
+
+/* Number of tensor arguments (inputs then outputs) and their descriptions. */
+int32_t akgb_num_tensors(const akgb_kernel* k);
+int32_t akgb_num_inputs(const akgb_kernel* k);
+akgb_status akgb_tensor_info(const akgb_kernel* k, int32_t index, akgb_tensor_desc* out);
+
+/* Bytes of device scratch a launch needs (partials of split reductions, ...). */
+size_t akgb_workspace_size(const akgb_kernel* k);
+
+/* Number of device kernels one akgb_launch enqueues. */
+int32_t akgb_launch_count(const akgb_kernel* k);
+
+/* Enqueue the fused op on `stream` (a cudaStream_t, may be NULL).  `tensors`
+ * are DEVICE pointers, inputs then outputs.  `workspace` must hold at least
+ * akgb_workspace_size() bytes (may be NULL when that is 0).  Asynchronous.
+ * Replaces cuLaunchKernel of the generated kernel
+ * (python/akg_mlir/utils/code_template.py:204). */
+akgb_status akgb_launch(akgb_kernel* k, void* const* tensors, void* workspace,
+                        size_t workspace_bytes, void* stream);
+
+/* Same contract as the generated launcher's `cuda_runtime_exec`
+ * (python/akg_mlir/utils/code_template.py:160-211): `host_tensors` are HOST
+ * pointers, inputs then outputs; inputs are copied to the device, the fused op
+ * runs, outputs are copied back; synchronous.  Device staging buffers are kept
+ * in the kernel object between calls instead of being re-allocated. */
+akgb_status akgb_run_host(akgb_kernel* k, void* const* host_tensors);
+
+/* Same contract as `cuda_runtime_profiling`
+ * (python/akg_mlir/utils/code_template.py:68-157): one warm-up, then
+ * `number * repeat` launches; writes the average device time of one launch in
+ * microseconds (CUDA events, not the reference's host clock). */
+akgb_status akgb_profile_host(akgb_kernel* k, void* const* host_tensors, int32_t number,
+                              int32_t repeat, double* avg_us);
+
+/* The launch metadata the reference writes to <kernel>.json
+ * (lib/Dialect/GPU/Transforms/GPUMapping.cpp:645-703,
+ * python/akg_mlir/mlir_driver.py:776-815): blockIdx.{x,y,z}, threadIdx.{x,y,z},
+ * kernelName, is_dynamic, sha256 — plus class, bytes, flops.  Writes a
+ * NUL-terminated JSON text; `*needed` receives the size including the NUL. */
+akgb_status akgb_kernel_meta(const akgb_kernel* k, char* buf, size_t cap, size_t* needed);
+
+/* Operator class the matcher assigned, as a static string
+ * ("elementwise", "broadcast", "reduce_x", "reduce_y", "reduce_all",
+ * "layernorm", "softmax", "transpose", "matmul", "generic"). */
+const char* akgb_kernel_class(const akgb_kernel* k);
+
+/* Algorithmic bytes (every input read once, every output written once) and
+ * floating-point operations (2*M*N*K for matmul, else 0) of one launch. */
+int64_t akgb_kernel_bytes(const akgb_kernel* k);
+int64_t akgb_kernel_flops(const akgb_kernel* k);
+
+/* Reads and clears the device-side error word of the last launches of `k`
+ * (bounded waits that gave up).  0 = none. */
+akgb_status akgb_check_device_error(akgb_kernel* k, uint32_t* word);
+
+/* Text of the last error on the calling thread. */
+const char* akgb_last_error(void);
+
+/* Library version string. */
+const char* akgb_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AKGB_H_ */

@@ -1,0 +1,242 @@
+"""CPU oracle for fused-op descriptions — TEST INFRASTRUCTURE, not a product path.
+
+Only ``tests/``, ``__graft_entry__.smoke()`` and the CPU-baseline legs of
+``bench.py`` may import this module; the library itself never does.
+
+It restates, in NumPy, what the reference computes for a ``.info`` JSON: the op
+list is walked in order and every op is evaluated **in its declared element
+type** (one rounding per op), which is what both of the reference's CPU-side
+evaluators do:
+
+* the MLIR CPU pipeline lowers each op to arithmetic in the op's element type
+  (``akg-mlir/lib/Conversion/MindSporeToLinalg/MindSporeToLinalg.cpp:377-483``,
+  ``akg-mlir/lib/Conversion/MindSporeToTosa/MindSporeToTosa.cpp:475-504``);
+* the expected-value generator of ``akg_benchmark`` emits one NumPy statement
+  per op (``akg-mlir/python/akg_mlir/utils/op_dsl.py:1154-1244``,
+  ``composite_op_helper.py:757-775``).
+
+Pinning: ``tests/test_oracle_golden.py`` checks this module against fixtures
+recorded from the reference's generator itself (``tests/golden/``).
+
+Where the two reference evaluators differ, or where last bits depend on a
+math library that is not part of the reference checkout (upstream MLIR
+TOSA->Linalg and libm/libdevice), this oracle fixes one documented choice:
+
+* transcendental ops (Exp, Log, Tanh, ...) are evaluated in float64 and rounded
+  once to the op's type.  For float16/bfloat16 this is the correctly rounded
+  result; NumPy's own float16 loop goes through float32 and agrees except on
+  double-rounding ties.  Parity at the last bit of float32 transcendentals is
+  unpinned (no golden vectors exist in the reference).
+* Rsqrt is ``1/sqrt(x)`` with two roundings (``op_dsl.py:792-794``).
+* reductions of float16/bfloat16 accumulate in float32 and cast back
+  (``op_dsl.py:126-154``); float32 reductions use NumPy's pairwise sum.  With
+  ``accum="float64"`` sums run in float64 and are rounded once — the "truth"
+  that bounds compare against.  ``accum="sequential"`` reproduces the MLIR CPU
+  loop order (``MindSporeToLinalg.cpp:1401-1426``) for small cases.
+* ReduceMax/Min ignore NaN like ``arith.maxnumf`` (``:878-879``); inputs in the
+  tests are NaN-free.
+* MatMul upcasts float16/bfloat16 operands to float32 and accumulates in
+  float32 (``op_dsl.py:295-327``); descriptions give MatMul a float32 result.
+* float -> int Cast truncates like NumPy; the MLIR route rounds to nearest even
+  (upstream TOSA), so that case is unpinned and raises here.
+"""
+from __future__ import annotations
+
+import json
+from typing import Sequence
+
+import numpy as np
+
+try:  # bfloat16 support
+    import ml_dtypes
+
+    BF16 = np.dtype(ml_dtypes.bfloat16)
+except Exception:  # pragma: no cover
+    BF16 = None
+
+
+def np_dtype(name: str) -> np.dtype:
+    if name == "uint8":  # read as int8, TranslateToMindsporeDialect.cpp:331-333
+        name = "int8"
+    if name == "bfloat16":
+        if BF16 is None:
+            raise RuntimeError("bfloat16 needs ml_dtypes")
+        return BF16
+    return np.dtype(name)
+
+
+def _is_low_float(dt: np.dtype) -> bool:
+    return dt == np.float16 or (BF16 is not None and dt == BF16)
+
+
+def _round_to(a64: np.ndarray, dt: np.dtype) -> np.ndarray:
+    """One rounding from float64 to dt."""
+    if BF16 is not None and dt == BF16:
+        # float64 -> bf16 in one step: round the float64 to 8 significant bits
+        a64 = np.asarray(a64, dtype=np.float64)
+        out = np.empty(a64.shape, dtype=np.float32)
+        finite = np.isfinite(a64) & (a64 != 0)
+        m, e = np.frexp(np.where(finite, a64, 1.0))
+        r = np.ldexp(np.rint(np.ldexp(m, 8)), e - 8)
+        out[...] = np.where(finite, r, a64)
+        return out.astype(BF16)
+    return np.asarray(a64, dtype=np.float64).astype(dt)
+
+
+def _transcendental(fn, x: np.ndarray, dt: np.dtype) -> np.ndarray:
+    with np.errstate(all="ignore"):
+        return _round_to(fn(x.astype(np.float64)), dt)
+
+
+_UNARY = {
+    "Exp": np.exp, "Log": np.log, "Tanh": np.tanh, "Sin": np.sin, "Cos": np.cos, "Asinh": np.arcsinh,
+    "Acosh": np.arccosh, "Atan": np.arctan, "ASin": np.arcsin, "ACos": np.arccos,
+}
+_BINARY = {
+    "Add": np.add, "TensorAdd": np.add, "Sub": np.subtract, "Mul": np.multiply, "RealDiv": np.divide,
+    "Div": np.divide, "Maximum": np.maximum, "Minimum": np.minimum,
+}
+_COMPARE = {
+    "Equal": np.equal, "NotEqual": np.not_equal, "Greater": np.greater, "GreaterEqual": np.greater_equal,
+    "Less": np.less, "LessEqual": np.less_equal,
+}
+_REDUCE = {"ReduceSum": "sum", "ReduceMax": "max", "ReduceMin": "min", "ReducePrd": "prod", "ReduceProd": "prod"}
+
+
+def _attr(attrs, name, default=None):
+    for a in attrs or []:
+        if a.get("name") == name:
+            return a.get("value")
+    return default
+
+
+def _reduce(kind: str, x: np.ndarray, axes: tuple, keep: bool, accum: str) -> np.ndarray:
+    dt = x.dtype
+    if kind in ("max", "min"):
+        fn = np.nanmax if kind == "max" else np.nanmin  # maxnumf/minnumf skip NaN
+        with np.errstate(all="ignore"):
+            return fn(x.astype(np.float32) if _is_low_float(dt) else x, axis=axes, keepdims=keep).astype(dt)
+    if accum == "float64":
+        r = getattr(np, kind)(x.astype(np.float64), axis=axes, keepdims=keep)
+        return _round_to(r, dt)
+    if accum == "sequential":
+        # the MLIR CPU loop nest: accumulate in the result type, walking the
+        # reduced axes in row-major order
+        moved = np.moveaxis(x, axes, range(len(axes)))
+        flat = moved.reshape((-1,) + moved.shape[len(axes):])
+        acc = np.zeros(flat.shape[1:], dtype=dt) if kind == "sum" else np.ones(flat.shape[1:], dtype=dt)
+        for i in range(flat.shape[0]):
+            acc = (acc + flat[i]).astype(dt) if kind == "sum" else (acc * flat[i]).astype(dt)
+        if keep:
+            shape = list(x.shape)
+            for a in axes:
+                shape[a] = 1
+            acc = acc.reshape(shape)
+        return acc
+    src = x.astype(np.float32) if _is_low_float(dt) else x
+    return getattr(np, kind)(src, axis=axes, keepdims=keep).astype(dt)
+
+
+def evaluate(desc: dict | str, inputs: Sequence[np.ndarray], accum: str = "numpy") -> list[np.ndarray]:
+    """Evaluates the description on `inputs` (input_desc order); returns outputs in output_desc order."""
+    if isinstance(desc, (str, bytes)):
+        desc = json.loads(desc)
+    env: dict[str, np.ndarray] = {}
+    for (d,), a in zip(desc["input_desc"] or [], inputs):
+        dt = np_dtype(d["data_type"])
+        a = np.asarray(a)
+        if a.dtype != dt:
+            raise TypeError(f"input {d['tensor_name']}: expected {dt}, got {a.dtype}")
+        env[d["tensor_name"]] = a.reshape(d.get("shape") or [1])
+
+    def operand(d):
+        name = d["tensor_name"]
+        if name in env and d.get("value") is None:
+            return env[name]
+        if d.get("value") is None:
+            raise KeyError(f"operand {name} is undefined")
+        # a literal is a typed constant: one rounding from the JSON double
+        return _round_to(np.asarray(d["value"], dtype=np.float64), np_dtype(d["data_type"])) \
+            if np_dtype(d["data_type"]).kind == "f" or np_dtype(d["data_type"]) == BF16 \
+            else np.asarray(d["value"]).astype(np_dtype(d["data_type"]))
+
+    for op in desc["op_desc"]:
+        name = op["name"]
+        ins = [i[0] for i in op["input_desc"]]
+        out = op["output_desc"][0]
+        odt = np_dtype(out["data_type"])
+        oshape = out.get("shape") or [1]
+        attrs = op.get("attr")
+        with np.errstate(all="ignore"):
+            if name in _BINARY:
+                a, b = operand(ins[0]), operand(ins[1])
+                r = _BINARY[name](a, b).astype(odt)
+            elif name in _COMPARE:
+                r = _COMPARE[name](operand(ins[0]), operand(ins[1]))
+            elif name in _UNARY:
+                r = _transcendental(_UNARY[name], operand(ins[0]), odt)
+            elif name == "Rsqrt":
+                x = operand(ins[0])
+                r = (np.asarray(1.0, dtype=x.dtype) / np.sqrt(x)).astype(odt)
+            elif name == "Sqrt":
+                r = np.sqrt(operand(ins[0])).astype(odt)
+            elif name == "Reciprocal":
+                x = operand(ins[0])
+                r = (np.asarray(1.0, dtype=x.dtype) / x).astype(odt)
+            elif name == "Abs":
+                r = np.abs(operand(ins[0]))
+            elif name == "Neg":
+                r = np.negative(operand(ins[0]))
+            elif name == "Floor":
+                r = np.floor(operand(ins[0]))
+            elif name == "Square":
+                x = operand(ins[0])
+                r = np.multiply(x, x)
+            elif name == "Pow":
+                r = np.power(operand(ins[0]), operand(ins[1])).astype(odt)
+            elif name == "Cast":
+                x = operand(ins[0])
+                if x.dtype.kind == "f" or (BF16 is not None and x.dtype == BF16):
+                    if odt.kind in "iu":
+                        raise NotImplementedError("float->int Cast: rounding differs between the reference's "
+                                                  "evaluators (parity unpinned)")
+                    # widening is exact; narrowing rounds to nearest even (arith.truncf)
+                    r = x.astype(np.float32).astype(odt) if _is_low_float(x.dtype) else x.astype(odt)
+                else:
+                    r = x.astype(odt)
+            elif name == "Select":
+                r = np.where(operand(ins[0]), operand(ins[1]), operand(ins[2])).astype(odt)
+            elif name in _REDUCE:
+                x = operand(ins[0])
+                axes = _attr(attrs, "axis")
+                if (axes is None or axes == []) and len(ins) == 2:
+                    axes = ins[1]["value"]
+                if axes is None or axes == []:
+                    axes = list(range(x.ndim))
+                if not isinstance(axes, (list, tuple)):
+                    axes = [axes]
+                axes = tuple(sorted({a + x.ndim if a < 0 else a for a in axes}))
+                keep = bool(_attr(attrs, "keep_dims", False))
+                r = _reduce(_REDUCE[name], x, axes, keep, accum)
+            elif name == "Reshape":
+                r = operand(ins[0])
+            elif name == "BroadcastTo":
+                r = np.broadcast_to(operand(ins[0]), oshape)
+            elif name == "Transpose":
+                perm = _attr(attrs, "perm")
+                if perm is None and len(ins) == 2:
+                    perm = ins[1]["value"]
+                r = np.ascontiguousarray(np.transpose(operand(ins[0]), axes=perm))
+            elif name in ("MatMul", "BatchMatMul"):
+                a, b = operand(ins[0]), operand(ins[1])
+                if _attr(attrs, "transpose_a", False):
+                    raise NotImplementedError("transpose_a is rejected by the reference lowering "
+                                              "(MindSporeToLinalg.cpp:1508-1510)")
+                if _attr(attrs, "transpose_b", False):
+                    b = np.swapaxes(b, -1, -2)
+                r = np.matmul(a.astype(np.float32), b.astype(np.float32)).astype(odt)
+            else:
+                raise NotImplementedError(f"op {name}")
+        env[out["tensor_name"]] = np.ascontiguousarray(np.asarray(r, dtype=odt if name not in _COMPARE else None)
+                                                       ).reshape(oshape)
+    return [env[o["tensor_name"]].reshape(o.get("shape") or [1]) for o in desc["output_desc"]]

@@ -1,0 +1,133 @@
+"""Host-side checks that need no GPU: the library loads, exports every symbol the header declares,
+parses the reference's JSON schema, tags operator classes by the reference's rules and plans."""
+import ctypes
+import json
+import re
+from pathlib import Path
+
+import pytest
+
+from akg_b200 import FusedKernel, UnsupportedError, AkgbError, descs, _capi
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_library_exports_every_declared_symbol(lib):
+    header = (ROOT / "include" / "akgb.h").read_text()
+    declared = set(re.findall(r"\b(akgb_[a-z_0-9]+)\s*\(", header))
+    assert declared, "no prototypes found in include/akgb.h"
+    bound = {name for name, _, _ in _capi._SIGNATURES}
+    assert declared <= bound | {"akgb_no_alloc"}, declared - bound
+    for name in declared:
+        assert getattr(lib, name) is not None
+
+
+def test_version_and_error_text(lib):
+    assert b"sm_100a" in lib.akgb_version()
+    h = ctypes.c_void_p()
+    st = lib.akgb_compile(b"{not json", 9, None, ctypes.byref(h))
+    assert st == _capi.AKGB_INVALID_JSON
+    assert lib.akgb_last_error()
+
+
+CONFIGS = {
+    "layernorm": (descs.layernorm(8192, 1024), "layernorm", 67182592),
+    "gelu": (descs.gelu_chain([64, 512, 4096]), "broadcast", 1073750016),
+    "softmax": (descs.masked_softmax(256, 2048, 2048), "softmax", 4303355904),
+    "colsum": (descs.reduce_sum_axis0(65536, 4096), "reduce_y", 1073758208),
+    "gmax": (descs.reduce_max_all(65536, 4096), "reduce_all", 1073741828),
+    "transpose": (descs.transpose([32, 2048, 32, 128], [0, 2, 1, 3]), "transpose", 1073741824),
+}
+
+
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_benchmark_configs_plan_without_a_gpu(lib, name):
+    desc, klass, nbytes = CONFIGS[name]
+    k = FusedKernel(desc)
+    assert k.op_class == klass
+    assert k.bytes == nbytes  # the algorithmic bytes the roofline is computed from
+    assert k.num_inputs == len(desc["input_desc"])
+    assert [t.name for t in k.outputs] == [o["tensor_name"] for o in desc["output_desc"]]
+    meta = k.meta()
+    for key in ("kernelName", "blockIdx.x", "threadIdx.x", "is_dynamic", "sha256", "class", "bytes"):
+        assert key in meta
+    assert meta["kernelName"] == desc["op"] + "_kernel"
+    assert len(meta["sha256"]) == 64
+    k.close()
+
+
+def test_sha256_matches_hashlib(lib):
+    import hashlib
+    text = json.dumps(descs.reduce_max_all(4, 8))
+    k = FusedKernel(text)
+    assert k.meta()["sha256"] == hashlib.sha256(text.encode()).hexdigest()
+
+
+def test_schema_defaults_and_variants(lib):
+    d = descs.reduce_sum_axis0(16, 8)
+    # axis as a constant second operand instead of an attribute (TranslateToMindsporeDialect.cpp:1282-1300)
+    op = d["op_desc"][0]
+    op["attr"] = [{"name": "keep_dims", "data_type": "bool", "value": False}]
+    op["input_desc"].append([{"data_type": "int64", "format": "DefaultFormat", "shape": [1],
+                              "tensor_name": "axis_c", "value": [0]}])
+    k = FusedKernel(d)
+    assert k.op_class == "reduce_y"
+    # negative axis wraps
+    d2 = descs.reduce_sum_axis0(16, 8)
+    d2["op_desc"][0]["attr"][0]["value"] = [-2]
+    assert FusedKernel(d2).op_class == "reduce_y"
+    # uint8 is read as int8 (:331-333): a transpose of bytes plans
+    d3 = descs.transpose([4, 6], [1, 0], "uint8")
+    assert FusedKernel(d3).tensors[0].dtype == "int8"
+
+
+def test_commutative_spellings_match_and_reassociation_does_not(lib):
+    d = descs.gelu_chain([2, 64])
+    for op in d["op_desc"]:
+        if op["name"] in ("Mul", "Add"):
+            op["input_desc"].reverse()
+    assert FusedKernel(d).op_class == "broadcast"
+    # (t*t)*t spelled t*(t*t) is the same; but dropping the rounding step of t3*c0 changes results
+    d = descs.gelu_chain([2, 64])
+    del d["op_desc"][3]  # remove Mul(t3, c0) and rewire: no template may claim this graph silently
+    d["op_desc"][3]["input_desc"][1][0]["tensor_name"] = d["op_desc"][2]["output_desc"][0]["tensor_name"]
+    with pytest.raises(UnsupportedError):
+        FusedKernel(d)
+
+
+def test_unsupported_and_malformed(lib):
+    d = descs.unary("Erf", [8], "float32")  # not in the JSON factory: UnknownOp in the reference
+    with pytest.raises(UnsupportedError):
+        FusedKernel(d)
+    d = descs.reduce_max_all(4, 4)
+    del d["op_desc"][0]["output_desc"]
+    with pytest.raises(AkgbError) as e:
+        FusedKernel(d)
+    assert e.value.status == _capi.AKGB_INVALID_JSON
+    d = descs.matmul_bias_relu(128, 64, 128)
+    d["op_desc"][0]["attr"][0]["value"] = True  # transpose_a is rejected like MindSporeToLinalg.cpp:1508-1510
+    with pytest.raises(UnsupportedError):
+        FusedKernel(d)
+
+
+def test_leading_axis_sharding_plans(lib):
+    k = FusedKernel(descs.gelu_chain([64, 512, 4096]), shard_rank=1, shard_world=4)
+    by = {t.name: t for t in k.tensors}
+    assert by["x"].shape == (16, 512, 4096) and by["x"].shard_kind == _capi.SHARD_SPLIT_AXIS0
+    assert by["bias"].shape == (4096,) and by["bias"].shard_kind == _capi.SHARD_REPLICATED
+    assert k.outputs[0].shape == (16, 512, 4096)
+    k = FusedKernel(descs.reduce_sum_axis0(65536, 4096), shard_rank=0, shard_world=8)
+    assert k.inputs[0].shape == (8192, 4096)
+    assert k.outputs[0].shape == (4096,) and k.outputs[0].shard_kind == _capi.SHARD_PARTIAL_SUM
+    k = FusedKernel(descs.reduce_max_all(65536, 4096), shard_rank=0, shard_world=2)
+    assert k.outputs[0].shard_kind == _capi.SHARD_PARTIAL_MAX
+    k = FusedKernel(descs.masked_softmax(256, 2048, 2048), shard_rank=3, shard_world=8)
+    assert k.inputs[0].shape == (32, 2048, 2048) and k.inputs[1].shard_kind == _capi.SHARD_REPLICATED
+    k = FusedKernel(descs.layernorm(8192, 1024), shard_rank=0, shard_world=8)
+    assert [t.shape for t in k.outputs] == [(1024, 1024), (1024,), (1024,)]
+    k = FusedKernel(descs.transpose([32, 2048, 32, 128], [0, 2, 1, 3]), shard_rank=0, shard_world=8)
+    assert k.outputs[0].shape == (4, 32, 2048, 128)
+    with pytest.raises(UnsupportedError):  # the split axis moves
+        FusedKernel(descs.transpose([8, 16], [1, 0]), shard_rank=0, shard_world=2)
+    with pytest.raises(UnsupportedError):  # 7 rows over 2 ranks
+        FusedKernel(descs.layernorm(7, 100), shard_rank=0, shard_world=2)
