@@ -1,11 +1,497 @@
+// Matmul class: C = A x B with the bias / ReLU / cast epilogue fused, on the
+// 5th-generation tensor cores (tcgen05) with the accumulator in tensor memory.
+//
+// The reference lowers MatMul to a plain linalg loop nest that the GPU mapping
+// spreads over CUDA cores (akg-mlir/lib/Conversion/MindSporeToLinalg/MindSporeToLinalg.cpp:1453-1546),
+// with the epilogue ops fused elementwise behind it.  Here:
+//   * one persistent CTA per SM walks 128x256 output tiles;
+//   * warp 0 streams 128x64 (A) and 64x256 (B) bf16 tiles through a 4-stage
+//     shared-memory ring with TMA (cp.async.bulk.tensor, 128-byte swizzle,
+//     no multicast);
+//   * warp 1 issues tcgen05.mma (M=128, N=256, K=16) into one of two 256-column
+//     TMEM accumulators, so the epilogue of tile i overlaps the MMAs of tile i+1;
+//   * warps 2-5 read the accumulator with tcgen05.ld, add the bias in f32,
+//     apply max(.,0), round to the output type and store.
+// Accumulation is f32 (the description gives MatMul an f32 result); bias Add,
+// Maximum and Cast follow in that order, one rounding each.
+//
+// Every wait on an mbarrier is bounded: when a limit is hit the kernel writes
+// an error word, drains its copies and MMAs, frees its TMEM and returns.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdlib>
+#include <mutex>
+
+#include "common.cuh"
 #include "kernels.hpp"
+
 namespace akgb {
-bool matmul_bf16_supported(const MatmulParams&, const char** why) {
-  if (why) *why = "matmul template not built yet";
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;          // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;          // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int B_BOX_N = 64;                   // N-major B arrives as 4 boxes of 64(n) x 64(k)
+constexpr int B_BOX_BYTES = B_BOX_N * BK * 2; // 8 KiB
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int THREADS = 192;
+constexpr uint32_t kSpinLimit = 1u << 20;
+
+struct Bars {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  uint32_t abort;
+};
+
+struct MatmulDev {
+  int M, N, K;
+  int transpose_b, has_bias, bias_dt, relu, out_dt;
+  const void* bias;
+  void* out;
+  uint32_t* err;
+  uint32_t b_lbo, b_sbo;  // descriptor offsets of the N-major B tile, in bytes
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait.  Returns false when the limit is hit or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (i > 64) {
+      __nanosleep(64);
+      if ((i & 255) == 0 && *abort_flag) return false;
+    }
+  }
   return false;
 }
-cudaError_t matmul_bf16(const MatmulParams&, const void*, const void*, const void*, void*, uint32_t*, int, cudaStream_t,
-                        LaunchDims*) {
-  return cudaErrorNotSupported;
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
 }
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100): start address, leading/stride byte
+// offsets in 16-byte units, version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int* m_tile, int* n_tile) {
+  // groups of 16 M-tiles sweep N together, so that the CTAs running at the
+  // same time share A and B tiles in L2
+  constexpr int G = 16;
+  const int per_group = G * num_n;
+  const int group = tile / per_group;
+  const int first_m = group * G;
+  const int rows = min(G, num_m - first_m);
+  const int in_group = tile - group * per_group;
+  *m_tile = first_m + in_group % rows;
+  *n_tile = in_group / rows;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                           const MatmulDev p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  Bars* bars = reinterpret_cast<Bars*>(smem + STAGES * STAGE_BYTES);
+  volatile uint32_t* abort_flag = &bars->abort;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&bars->full[s]), 1);
+      mbar_init(smem_u32(&bars->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&bars->tmem_full[a]), 1);
+      mbar_init(smem_u32(&bars->tmem_empty[a]), 4);  // one arrival per epilogue warp
+    }
+    mbar_init(smem_u32(&bars->drain), 1);
+    bars->abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_k = (p.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ TMA producer
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int issued = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int mt, nt;
+        tile_coords(tile, num_m, num_n, &mt, &nt);
+        const int m0 = mt * BM, n0 = nt * BN;
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = smem_u32(&bars->full[stage]);
+          const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_BYTES;
+          mbar_expect_tx(full, STAGE_BYTES);
+          tma_load_2d(sa, &tmA, full, kb * BK, m0);
+          if (p.transpose_b) {
+            tma_load_2d(sb, &tmB, full, kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / B_BOX_N; ++j) tma_load_2d(sb + j * B_BOX_BYTES, &tmB, full, n0 + j * B_BOX_N, kb * BK);
+          }
+          ++issued;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicOr(p.err, 1u);
+        // let the copies already issued land before the CTA gives up its shared memory
+        const int pending = min(issued, STAGES);
+        int s = stage;
+        uint32_t ph = phase;
+        for (int i = 0; i < pending; ++i) {
+          if (--s < 0) {
+            s = STAGES - 1;
+            ph ^= 1u;
+          }
+          volatile uint32_t none = 0;
+          mbar_wait(smem_u32(&bars->full[s]), ph, &none);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ MMA issuer
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((p.transpose_b ? 0u : 1u) << 16) |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(smem_u32(&bars->tmem_empty[acc]), acc_phase ^ 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)acc * BN;
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // A, K-major: 8-row groups are 1024 B apart; 16 elements of K = 32 B inside the swizzled row
+            const uint64_t adesc = make_desc(sa + k * 32, 16, 1024);
+            const uint64_t bdesc = p.transpose_b ? make_desc(sb + k * 32, 16, 1024)
+                                                 : make_desc(sb + k * 2048, p.b_lbo, p.b_sbo);
+            umma_f16(tmem_d, adesc, bdesc, idesc, (kb | k) != 0);
+          }
+          umma_commit(smem_u32(&bars->empty[stage]));  // frees the stage once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(smem_u32(&bars->tmem_full[acc]));
+        if ((acc ^= 1) == 0) acc_phase ^= 1u;
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicOr(p.err, 2u);
+      }
+      // every MMA issued has completed before TMEM is released
+      umma_commit(smem_u32(&bars->drain));
+      volatile uint32_t none = 0;
+      mbar_wait(smem_u32(&bars->drain), 0, &none);
+    }
+  } else {
+    // -------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are visible to this warp
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int mt, nt;
+      tile_coords(tile, num_m, num_n, &mt, &nt);
+      const int row = mt * BM + quarter * 32 + lane;
+      const int n0 = nt * BN;
+      if (!mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_phase, abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (p.has_bias) {
+          if (col0 + 32 <= p.N) {
+            if (p.bias_dt == kBF16) {
+              const uint4* bp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + col0);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                float b8[8];
+                unpack8(__ldg(bp + q), kBF16, b8);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[q * 8 + j] = __fadd_rn(v[q * 8 + j], b8[j]);
+              }
+            } else {
+              const float4* bp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + col0);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const float4 b = __ldg(bp + q);
+                v[q * 4 + 0] = __fadd_rn(v[q * 4 + 0], b.x);
+                v[q * 4 + 1] = __fadd_rn(v[q * 4 + 1], b.y);
+                v[q * 4 + 2] = __fadd_rn(v[q * 4 + 2], b.z);
+                v[q * 4 + 3] = __fadd_rn(v[q * 4 + 3], b.w);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col0 + j < p.N) {
+                const float b = p.bias_dt == kBF16
+                                    ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(p.bias)[col0 + j])
+                                    : reinterpret_cast<const float*>(p.bias)[col0 + j];
+                v[j] = __fadd_rn(v[j], b);
+              }
+            }
+          }
+        }
+        if (p.relu) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+        }
+        if (row < p.M) {
+          if (p.out_dt == kBF16) {
+            uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + (size_t)row * p.N + col0;
+            if (col0 + 32 <= p.N) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 w;
+                w.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+                w.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+                w.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+                w.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+                *reinterpret_cast<uint4*>(o + q * 8) = w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) o[j] = (uint16_t)f32_to_bf16_bits(v[j]);
+            }
+          } else {
+            float* o = reinterpret_cast<float*>(p.out) + (size_t)row * p.N + col0;
+            if (col0 + 32 <= p.N) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<float4*>(o + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) o[j] = v[j];
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[acc]));
+      if ((acc ^= 1) == 0) acc_phase ^= 1u;
+    }
+    if (!ok && lane == 0) {
+      *abort_flag = 1;
+      atomicOr(p.err, 4u);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows.
+bool encode_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_inner,
+               uint32_t box_outer) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {inner * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool matmul_bf16_supported(const MatmulParams& p, const char** why) {
+  const char* w = nullptr;
+  if (p.M <= 0 || p.N <= 0 || p.K <= 0) w = "empty extent";
+  else if (p.K % 8 != 0) w = "K must be a multiple of 8 (16-byte TMA row pitch)";
+  else if (p.N % 8 != 0) w = "N must be a multiple of 8 (16-byte rows of B and of the output)";
+  else if (p.M > (1 << 30) || p.N > (1 << 30) || p.K > (1 << 30)) w = "extent above 2^30";
+  if (why) *why = w;
+  return w == nullptr;
+}
+
+cudaError_t matmul_bf16(const MatmulParams& p, const void* A, const void* B, const void* bias, void* out,
+                        uint32_t* err_word, int sm_count, cudaStream_t s, LaunchDims* dims) {
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(out) |
+       reinterpret_cast<uintptr_t>(bias)) & 15)
+    return cudaErrorMisalignedAddress;
+  CUtensorMap tmA, tmB;
+  if (!encode_2d(&tmA, A, (uint64_t)p.K, (uint64_t)p.M, BK, BM)) return cudaErrorInvalidValue;
+  const bool okb = p.transpose_b ? encode_2d(&tmB, B, (uint64_t)p.K, (uint64_t)p.N, BK, BN)
+                                 : encode_2d(&tmB, B, (uint64_t)p.N, (uint64_t)p.K, B_BOX_N, BK);
+  if (!okb) return cudaErrorInvalidValue;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(matmul_bf16_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    SMEM_BYTES);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  MatmulDev d;
+  d.M = (int)p.M;
+  d.N = (int)p.N;
+  d.K = (int)p.K;
+  d.transpose_b = p.transpose_b;
+  d.has_bias = p.has_bias;
+  d.bias_dt = p.bias_dt;
+  d.relu = p.relu;
+  d.out_dt = p.out_dt;
+  d.bias = bias;
+  d.out = out;
+  d.err = err_word;
+  // N-major B tile: 64-element N atoms are one TMA box (8 KiB) apart, 8-row K groups 1 KiB apart
+  d.b_lbo = B_BOX_BYTES;
+  d.b_sbo = 1024;
+  const int64_t tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = (int)std::min<int64_t>(tiles, sm_count);
+  if (dims) {
+    dims->grid[0] = grid;
+    dims->block[0] = THREADS;
+    dims->smem = SMEM_BYTES;
+  }
+  matmul_bf16_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(tmA, tmB, d);
+  return cudaGetLastError();
+}
+
 }  // namespace akgb

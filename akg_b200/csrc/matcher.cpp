@@ -244,25 +244,27 @@ bool match_softmax(const Graph& g, Plan& plan) {
   {
     M probe = m;
     if (probe.bin(s, OpK::Add, &a, &b)) {
-      auto mask_src = [&](int vid, int* src) {
-        M p2 = probe;
+      // the mask is a graph input (possibly behind a Cast) that broadcasts against the scores;
+      // when both operands qualify, the smaller one is the mask, then the right-hand one
+      auto mask_src = [&](int vid, M* trial, int* src) {
         int c = vid, q;
-        if (p2.un(c, OpK::Cast, &q)) c = q;
-        if (!p2.is_input(c)) return false;
-        if (g.v(c).numel() == rows * cols) return false;  // that is the data operand
-        probe = p2;
+        if (trial->un(c, OpK::Cast, &q)) c = q;
+        if (!trial->is_input(c)) return false;
         *src = c;
         return true;
       };
-      int src;
-      if (mask_src(b, &src)) {
-        mask = src;
+      M pa = probe, pb = probe;
+      int sa = -1, sb = -1;
+      const bool a_ok = mask_src(a, &pa, &sa), b_ok = mask_src(b, &pb, &sb);
+      const bool pick_b = b_ok && (!a_ok || g.v(sb).numel() <= g.v(sa).numel());
+      if (pick_b) {
+        mask = sb;
         s = a;
-        m = probe;
-      } else if (mask_src(a, &src)) {
-        mask = src;
+        m = pb;
+      } else if (a_ok) {
+        mask = sa;
         s = b;
-        m = probe;
+        m = pa;
       }
     }
   }
