@@ -110,14 +110,14 @@ akgb_status run_plan(akgb_kernel* k, void* const* tensors, void* ws, cudaStream_
     void* scratch = resolve(st.scratch, tensors, ws);
     switch (st.kind) {
       case StepK::GeluChain:
-        e = gelu_chain_f16(st.gelu, a, b, c, o, ds.gelu_lut, s, &st.dims);
+        e = gelu_chain_f16(st.gelu, a, b, c, o, ds.gelu_lut, ds.err_word, s, &st.dims);
         break;
       case StepK::LayerNorm:
         e = layernorm_f32(st.ln, (const float*)a, (const float*)b, (const float*)c, (float*)o, (float*)o2, (float*)o3, s,
                           &st.dims);
         break;
       case StepK::Softmax:
-        e = softmax_rows(st.sm, a, b, o, s, &st.dims);
+        e = softmax_rows(st.sm, a, b, o, ds.err_word, s, &st.dims);
         break;
       case StepK::ReduceCol:
         e = reduce_col_f32(st.red_op, (const float*)a, (float*)o, st.red_len, st.red_inner, scratch, k->sm_count, s,

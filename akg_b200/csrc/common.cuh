@@ -91,6 +91,19 @@ __device__ __forceinline__ uint4 pack8(const float* f, int dt) {
   return v;
 }
 
+// ---- launch sizing ---------------------------------------------------------------
+// CTAs of `kernel` that fit on one SM at once.  Persistent (grid-stride) kernels launch exactly
+// sm_count * this many CTAs, so that no partial second wave trails the first.
+template <class Kernel>
+inline int resident_ctas_per_sm(Kernel kernel, int block_threads, size_t dyn_smem = 0) {
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, block_threads, dyn_smem) != cudaSuccess || n < 1) {
+    cudaGetLastError();
+    n = 1;
+  }
+  return n;
+}
+
 // ---- reduction trees -------------------------------------------------------------
 struct SumOp {
   __device__ __forceinline__ static float identity() { return 0.f; }

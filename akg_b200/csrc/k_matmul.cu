@@ -23,6 +23,7 @@
 #include <cstdlib>
 #include <mutex>
 
+#include "async.cuh"
 #include "common.cuh"
 #include "kernels.hpp"
 
@@ -38,7 +39,6 @@ constexpr int B_BOX_BYTES = B_BOX_N * BK * 2; // 8 KiB
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int THREADS = 192;
-constexpr uint32_t kSpinLimit = 1u << 20;
 
 struct Bars {
   uint64_t full[STAGES];
@@ -58,44 +58,6 @@ struct MatmulDev {
   uint32_t* err;
   uint32_t b_lbo, b_sbo;  // descriptor offsets of the N-major B tile, in bytes
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// Bounded wait.  Returns false when the limit is hit or another role aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (ok) return true;
-    if (i > 64) {
-      __nanosleep(64);
-      if ((i & 255) == 0 && *abort_flag) return false;
-    }
-  }
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -174,7 +136,7 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
     }
     mbar_init(smem_u32(&bars->drain), 1);
     bars->abort = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_fence_init();
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
@@ -236,8 +198,7 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
             s = STAGES - 1;
             ph ^= 1u;
           }
-          volatile uint32_t none = 0;
-          mbar_wait(smem_u32(&bars->full[s]), ph, &none);
+          mbar_wait(smem_u32(&bars->full[s]), ph, nullptr);
         }
       }
     }
@@ -287,8 +248,7 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
       }
       // every MMA issued has completed before TMEM is released
       umma_commit(smem_u32(&bars->drain));
-      volatile uint32_t none = 0;
-      mbar_wait(smem_u32(&bars->drain), 0, &none);
+      mbar_wait(smem_u32(&bars->drain), 0, nullptr);
     }
   } else {
     // -------------------------------------------------------------- epilogue

@@ -208,7 +208,8 @@ cudaError_t col_impl(const float* x, float* out, int64_t red, int64_t inner, voi
 template <class Op>
 cudaError_t all_impl(const float* x, float* out, int64_t n, void* ws, int sm_count, cudaStream_t s, LaunchDims* dims) {
   const int64_t want = (n / 4 + 255) / 256;
-  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)sm_count * 8));
+  static const int per_sm = std::min(8, resident_ctas_per_sm(reduce_all_f32_kernel<Op, true>, 256));
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)sm_count * per_sm));
   if (dims) {
     dims->grid[0] = grid;
     dims->block[0] = 256;

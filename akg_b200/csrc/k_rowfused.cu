@@ -12,7 +12,9 @@
 // order differs from a sequential loop
 // (akg-mlir/lib/Conversion/MindSporeToLinalg/MindSporeToLinalg.cpp:1401-1426).
 #include <algorithm>
+#include <mutex>
 
+#include "async.cuh"
 #include "common.cuh"
 #include "kernels.hpp"
 
@@ -213,6 +215,186 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) softmax_rows_kernel(Softmax
   }
 }
 
+// ---- softmax, staged variant for 16-bit scores/mask/output and rows of at most 4 KiB -------------
+// Every warp runs its own two-slot pipeline of bulk asynchronous copies (global -> shared, completing
+// on an mbarrier): while it works on row i out of registers, rows i+1 and i+2 are in flight, so a
+// 16-warp CTA keeps up to 128 KiB of HBM reads outstanding per SM without spending registers on them.
+// Rows are visited mask-row-major (all batches of mask row m, then m+1): a warp stages the mask row
+// into shared memory once and reuses it for every batch, so the mask is read from L2 once per warp.
+constexpr int kStWarps = 16;
+constexpr int kStRowBytes = 4096;
+constexpr int kStSlotBytes = 3 * kStRowBytes;  // two score slots + the mask row, per warp
+constexpr int kStSmem = kStWarps * kStSlotBytes + kStWarps * 4 * 8 + 128;
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kStWarps * 32, 1) softmax_rows_staged_kernel(SoftmaxParams p,
+                                                                               const uint16_t* __restrict__ x,
+                                                                               const uint16_t* __restrict__ mask,
+                                                                               uint16_t* __restrict__ out,
+                                                                               uint32_t* __restrict__ err,
+                                                                               int rows_per_warp) {
+  constexpr int VPL = 8;  // groups of 8 elements per lane: rows up to 2048 elements
+  extern __shared__ __align__(128) uint8_t st_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t sbase = smem_u32(st_smem) + warp * kStSlotBytes;
+  const uint32_t mbuf = sbase + 2 * kStRowBytes;
+  const uint32_t bar0 = smem_u32(st_smem) + kStWarps * kStSlotBytes + warp * 32;
+  const uint32_t barm = bar0 + 16;  // completion of the mask row copy
+  if (lane == 0) {
+    mbar_init(bar0, 1);
+    mbar_init(bar0 + 8, 1);
+    mbar_init(barm, 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+
+  const int groups = (int)(p.cols >> 3);
+  const uint32_t row_bytes = (uint32_t)p.cols * 2u;
+  const int64_t nb = p.rows / p.mask_rows;  // batches per mask row
+  const int64_t per = rows_per_warp;
+  const int64_t v0 = ((int64_t)blockIdx.x * kStWarps + warp) * per;
+  const int64_t v1 = min(p.rows, v0 + per);
+  if (v0 >= v1) return;
+
+  // virtual index v = m * nb + b  <->  row = b * mask_rows + m
+  int64_t m = v0 / nb, b = v0 - m * nb;
+  auto row_of = [&](int64_t mm, int64_t bb) { return bb * p.mask_rows + mm; };
+  // (m, b) of v0+1 and v0+2 for the prefetches
+  int64_t pm = m, pb = b;  // position of the next row to request
+  auto advance = [&](int64_t& mm, int64_t& bb) {
+    if (++bb == nb) {
+      bb = 0;
+      ++mm;
+    }
+  };
+  auto request = [&](int slot) {
+    if (lane == 0) {
+      const uint32_t bar = bar0 + slot * 8;
+      mbar_expect_tx(bar, row_bytes);
+      bulk_load(sbase + slot * kStRowBytes, x + row_of(pm, pb) * p.cols, row_bytes, bar);
+    }
+    advance(pm, pb);
+  };
+  int64_t requested = 0;
+  request(0);
+  ++requested;
+  if (v0 + 1 < v1) {
+    request(1);
+    ++requested;
+  }
+  uint32_t phase[2] = {0u, 0u};
+  uint32_t mphase = 0u;
+  int64_t cur_m = -1;
+  bool ok = true;
+  const float log2e = 1.4426950408889634f;
+  int64_t done = 0;
+  for (int64_t v = v0; v < v1; ++v, ++done) {
+    const int slot = (int)(done & 1);
+    if (p.has_mask && m != cur_m) {
+      // stage mask row m (an L2-resident operand) for all batches that follow: one bulk copy
+      __syncwarp();  // every lane is done with the previous mask row
+      if (lane == 0) {
+        fence_proxy_async_smem();
+        mbar_expect_tx(barm, row_bytes);
+        bulk_load(mbuf, mask + m * p.cols, row_bytes, barm);
+      }
+      if (!mbar_wait(barm, mphase, nullptr)) {
+        ok = false;
+        break;
+      }
+      mphase ^= 1u;
+      cur_m = m;
+    }
+    if (!mbar_wait(bar0 + slot * 8, phase[slot], nullptr)) {
+      ok = false;
+      break;
+    }
+    phase[slot] ^= 1u;
+    float s[VPL][8];
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const int gidx = lane + 32 * k;
+      if (gidx < groups) unpack8(lds128(sbase + slot * kStRowBytes + gidx * 16), DT, s[k]);
+    }
+    __syncwarp();  // every lane has taken its part of the slot
+    if (requested < v1 - v0) {
+      fence_proxy_async_smem();
+      request(slot);
+      ++requested;
+    }
+    float mx = -FLT_MAX;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const int gidx = lane + 32 * k;
+      if (gidx < groups) {
+        float mk[8];
+        if (p.has_mask) unpack8(lds128(mbuf + gidx * 16), DT, mk);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          // Mul then Add of the description, contracted: the 16-bit result absorbs the difference
+          const float t = p.has_mask ? fmaf(s[k][j], p.scale, mk[j]) : s[k][j] * p.scale;
+          s[k][j] = t;
+          mx = fmaxf(mx, t);
+        }
+      }
+    }
+    mx = warp_reduce<MaxOp>(mx);
+    const float neg_mxl = -mx * log2e;
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const int gidx = lane + 32 * k;
+      if (gidx < groups) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float e = ex2_approx(fmaf(s[k][j], log2e, neg_mxl));
+          s[k][j] = e;
+          sum += e;
+        }
+      }
+    }
+    sum = warp_reduce<SumOp>(sum);
+    const float inv = __fdiv_rn(1.0f, sum);
+    uint16_t* orow = out + row_of(m, b) * p.cols;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const int gidx = lane + 32 * k;
+      if (gidx < groups) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s[k][j] *= inv;
+        st_stream(orow + 8 * gidx, pack8(s[k], DT));
+      }
+    }
+    advance(m, b);
+  }
+  if (!ok) {
+    // a copy never completed: report, then give the copies still in flight a bounded chance to land
+    if (lane == 0) {
+      atomicOr(err, 8u);
+      const int64_t pending = requested - done;
+      for (int64_t i = 0; i < pending && i < 2; ++i) {
+        const int slot = (int)((done + i) & 1);
+        mbar_wait(bar0 + slot * 8, phase[slot], nullptr);
+      }
+    }
+    __syncwarp();
+  }
+}
+
 __device__ __forceinline__ float load1(const void* base, int64_t i, int dt) {
   if (dt == kF32) return reinterpret_cast<const float*>(base)[i];
   if (dt == kF16) return __half2float(reinterpret_cast<const __half*>(base)[i]);
@@ -296,12 +478,50 @@ cudaError_t layernorm_f32(const LayerNormParams& p, const float* x, const float*
   return cudaGetLastError();
 }
 
-cudaError_t softmax_rows(const SoftmaxParams& p, const void* x, const void* mask, void* out, cudaStream_t s,
-                         LaunchDims* dims) {
+cudaError_t softmax_rows(const SoftmaxParams& p, const void* x, const void* mask, void* out, uint32_t* err_word,
+                         cudaStream_t s, LaunchDims* dims) {
   if (p.rows == 0 || p.cols == 0) return cudaSuccess;
   const int sms = sm_count_now();
   const bool vec = p.cols % 8 == 0 && p.cols <= 256 * 16 && aligned16(x) && aligned16(out) &&
                    (!p.has_mask || aligned16(mask));
+  const bool staged = vec && err_word && p.cols <= 2048 && (p.in_dt == kF16 || p.in_dt == kBF16) &&
+                      p.out_dt == p.in_dt && (!p.has_mask || p.mask_dt == p.in_dt) && p.rows >= 4 * kStWarps &&
+                      p.rows % p.mask_rows == 0;
+  if (staged) {
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+      attr_err = cudaFuncSetAttribute(softmax_rows_staged_kernel<kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kStSmem);
+      if (attr_err == cudaSuccess)
+        attr_err = cudaFuncSetAttribute(softmax_rows_staged_kernel<kBF16>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kStSmem);
+    });
+    if (attr_err != cudaSuccess) return attr_err;
+    // short-lived CTAs: a warp takes a few consecutive rows (of one mask row where possible) and exits
+    // about 32 rows per warp (measured optimum on B200: fewer leaves the two-slot pipeline mostly in its
+    // prologue, many more lets the single resident CTA per SM run as one long wave), rounded so that the
+    // CTAs fill whole waves
+    const int64_t waves = std::max<int64_t>(1, (p.rows + (int64_t)sms * kStWarps * 16) / ((int64_t)sms * kStWarps * 32));
+    const int rpw = (int)((p.rows + (int64_t)sms * kStWarps * waves - 1) / ((int64_t)sms * kStWarps * waves));
+    const int64_t warps = (p.rows + rpw - 1) / rpw;
+    const int64_t grid = (warps + kStWarps - 1) / kStWarps;
+    if (dims) {
+      dims->grid[0] = (unsigned)grid;
+      dims->block[0] = kStWarps * 32;
+      dims->smem = kStSmem;
+    }
+    SoftmaxParams q = p;
+    if (!q.has_scale) q.scale = 1.0f;
+    if (!q.has_mask) q.mask_rows = 1;
+    if (p.in_dt == kF16)
+      softmax_rows_staged_kernel<kF16><<<(unsigned)grid, kStWarps * 32, kStSmem, s>>>(
+          q, (const uint16_t*)x, (const uint16_t*)mask, (uint16_t*)out, err_word, rpw);
+    else
+      softmax_rows_staged_kernel<kBF16><<<(unsigned)grid, kStWarps * 32, kStSmem, s>>>(
+          q, (const uint16_t*)x, (const uint16_t*)mask, (uint16_t*)out, err_word, rpw);
+    return cudaGetLastError();
+  }
   if (vec) {
     const int64_t want = (p.rows + kWarpsPerCta - 1) / kWarpsPerCta;
     const int grid = (int)std::min<int64_t>(want, (int64_t)sms * 8);

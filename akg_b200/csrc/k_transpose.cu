@@ -42,49 +42,49 @@ inline void fastdiv_init(uint32_t d, uint32_t* mul, uint32_t* shr) {
   *mul = (uint32_t)((((1ull << 32) * ((1ull << sh) - d)) / d) + 1);
 }
 
-// row mode: one 16-byte vector per thread-iteration, 4 in flight.  FAST: the
-// vector count fits 31 bits, so the index split uses 32-bit multiply-shift.
+// row mode: 16-byte vectors, 4 per thread.  FAST: the vector count fits 31 bits, so the index split
+// uses 32-bit multiply-shift.
 template <bool FAST>
 __global__ void __launch_bounds__(256) transpose_rows_kernel(Shape6 sh, FastDiv6 fd, const uint4* __restrict__ x,
                                                              uint4* __restrict__ out, int64_t nvec) {
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t base = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; base < nvec; base += 4 * stride) {
-    uint4 v[4];
+  // one-shot CTAs (no grid-stride loop): each owns 1024 consecutive output vectors, 4 per thread,
+  // all four loads issued before the first store
+  const int64_t base = (int64_t)blockIdx.x * 1024 + threadIdx.x;
+  uint4 v[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int64_t o = base + u * stride;
-      if (o < nvec) {
-        int64_t off = 0;
-        if (FAST) {
-          uint32_t rem = (uint32_t)o, acc = 0;
+  for (int u = 0; u < 4; ++u) {
+    const int64_t o = base + u * 256;
+    if (o < nvec) {
+      int64_t off = 0;
+      if (FAST) {
+        uint32_t rem = (uint32_t)o, acc = 0;
 #pragma unroll
-          for (int d = 5; d >= 0; --d) {
-            if (d < sh.rank) {
-              const uint32_t q = (__umulhi(rem, fd.mul[d]) + rem) >> fd.shr[d];
-              acc += (rem - q * (uint32_t)sh.ext[d]) * (uint32_t)sh.istr[d];
-              rem = q;
-            }
-          }
-          off = acc;
-        } else {
-          int64_t rem = o;
-#pragma unroll
-          for (int d = 5; d >= 0; --d) {
-            if (d < sh.rank) {
-              const int64_t q = rem / sh.ext[d];
-              off += (rem - q * sh.ext[d]) * sh.istr[d];
-              rem = q;
-            }
+        for (int d = 5; d >= 0; --d) {
+          if (d < sh.rank) {
+            const uint32_t q = (__umulhi(rem, fd.mul[d]) + rem) >> fd.shr[d];
+            acc += (rem - q * (uint32_t)sh.ext[d]) * (uint32_t)sh.istr[d];
+            rem = q;
           }
         }
-        v[u] = ld_stream(x + off);
-      }
-    }
+        off = acc;
+      } else {
+        int64_t rem = o;
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int64_t o = base + u * stride;
-      if (o < nvec) st_stream(out + o, v[u]);
+        for (int d = 5; d >= 0; --d) {
+          if (d < sh.rank) {
+            const int64_t q = rem / sh.ext[d];
+            off += (rem - q * sh.ext[d]) * sh.istr[d];
+            rem = q;
+          }
+        }
+      }
+      v[u] = ld_stream(x + off);
     }
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int64_t o = base + u * 256;
+    if (o < nvec) st_stream(out + o, v[u]);
   }
 }
 
@@ -204,7 +204,7 @@ cudaError_t transpose_nd(const TransposeParams& p, const void* x, void* out, cud
     v.ext[last] = sh.ext[last] / per_vec;
     for (int d = 0; d < last; ++d) v.istr[d] = sh.istr[d] / per_vec;
     const int64_t nvec = n / per_vec;
-    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((nvec + 1023) / 1024, (int64_t)sms * 16));
+    const unsigned grid = (unsigned)((nvec + 1023) / 1024);
     if (dims) {
       dims->grid[0] = grid;
       dims->block[0] = 256;

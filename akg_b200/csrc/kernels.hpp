@@ -26,7 +26,7 @@ struct GeluChainParams {
   float c0 = 0.044715f, c1 = 0.7978845608f, c2 = 0.5f, c_one = 1.0f;  // already rounded to f16
 };
 cudaError_t gelu_chain_f16(const GeluChainParams& p, const void* x, const void* bias, const void* y, void* out,
-                           const void* tanh_lut, cudaStream_t s, LaunchDims* dims);
+                           const void* tanh_lut, uint32_t* err_word, cudaStream_t s, LaunchDims* dims);
 // 16-bit table of correctly rounded tanh over the f16 magnitudes the kernel
 // looks up; built on the host, `out` needs gelu_lut_entries() uint16 slots.
 int gelu_lut_entries();
@@ -48,8 +48,8 @@ struct SoftmaxParams {
   float scale = 1.f;
   int64_t mask_rows = 1;  // mask row = row % mask_rows
 };
-cudaError_t softmax_rows(const SoftmaxParams& p, const void* x, const void* mask, void* out, cudaStream_t s,
-                         LaunchDims* dims);
+cudaError_t softmax_rows(const SoftmaxParams& p, const void* x, const void* mask, void* out, uint32_t* err_word,
+                         cudaStream_t s, LaunchDims* dims);
 
 // ---- reductions ----------------------------------------------------------------
 // x[outer, red, inner] -> out[outer, inner]; f32 only.

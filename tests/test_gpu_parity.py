@@ -92,7 +92,9 @@ def test_layernorm(lib, rows, cols, stats):
 # ------------------------------------------------------------------ softmax
 @pytest.mark.parametrize("b,r,c,dt,mask", [(2, 64, 128, "float16", True), (1, 2048, 2048, "float16", True),
                                            (3, 8, 40, "float32", False), (2, 16, 24, "bfloat16", True),
-                                           (1, 5, 5000, "float16", True), (2, 3, 7, "float16", True)])
+                                           (1, 5, 5000, "float16", True), (2, 3, 7, "float16", True),
+                                           (4, 32, 256, "bfloat16", True), (3, 100, 1000, "float16", False),
+                                           (5, 77, 2048, "float16", True), (1, 300, 8, "bfloat16", False)])
 def test_softmax(lib, b, r, c, dt, mask):
     d = descs.masked_softmax(b, r, c, dtype=dt, with_mask=mask)
     ins = make_inputs(d, 13, KINDS["softmax"])
