@@ -89,6 +89,7 @@ _SIGNATURES = [
     ("akgb_kernel_bytes", ctypes.c_int64, [_vp]),
     ("akgb_kernel_flops", ctypes.c_int64, [_vp]),
     ("akgb_check_device_error", ctypes.c_int, [_vp, ctypes.POINTER(ctypes.c_uint32)]),
+    ("akgb_reduce_sum_axis0_f32_noalloc", ctypes.c_int, [_vp, _vp, ctypes.c_int64, ctypes.c_int64, _vp]),
     ("akgb_last_error", ctypes.c_char_p, []),
     ("akgb_version", ctypes.c_char_p, []),
 ]

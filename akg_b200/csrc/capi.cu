@@ -21,6 +21,10 @@ using namespace akgb;
 
 namespace {
 thread_local std::string g_err;
+}
+void akgb::set_last_error(const char* text) { g_err = text ? text : ""; }
+
+namespace {
 akgb_status fail(akgb_status st, const std::string& msg) {
   g_err = msg;
   return st;

@@ -11,7 +11,10 @@
 // per-thread strided partials -> shared-memory tree -> per-CTA partial in
 // scratch -> a small second kernel folds the partials in a fixed order.
 #include <algorithm>
+#include <cstdio>
+#include <mutex>
 
+#include "../../include/akgb.h"
 #include "common.cuh"
 #include "kernels.hpp"
 
@@ -269,3 +272,89 @@ cudaError_t reduce_row_f32(RedOp op, const float* x, float* out, int64_t rows, i
 }
 
 }  // namespace akgb
+
+// ---------------------------------------------------------------------------------------------------
+// Column sum without any allocation.
+//
+// Some callers may not allocate device memory at the point where they need a reduction: code running
+// inside a framework's memory-planned region (every buffer was sized and placed ahead of time), an
+// allocator that is itself being torn down or is out of memory, or a real-time loop where cudaMalloc's
+// implicit device synchronisation is not acceptable.  For them the split partials of the column
+// reduction live in the fixed array below instead of a caller- or library-allocated workspace.
+//
+// The array is part of the library image: every GPU that loads the library holds these 1 MiB until the
+// process exits.  All calls on a device share it.  Nothing in it has to start at zero — each launch
+// overwrites every partial it later reads — so stale contents of the previous call are harmless; two
+// calls whose kernels overlap on the GPU (different streams, no ordering) would overwrite each other's
+// partials and must not be issued.
+namespace akgb {
+namespace {
+constexpr size_t kNoAllocScratchFloats = 262144;  // 1 MiB
+constexpr int64_t kNoAllocMaxCols = 65536;        // widest row the entry point accepts
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+
+struct NoAllocDevice {
+  bool ready = false;
+  float* scratch = nullptr;  // DEVICE address of g_noalloc_scratch on this device
+  int sm_count = 0;
+};
+NoAllocDevice g_noalloc_dev[64];
+std::mutex g_noalloc_mu;
+}  // namespace
+}  // namespace akgb
+
+extern "C" akgb_status akgb_reduce_sum_axis0_f32_noalloc(const float* x, float* out, int64_t rows, int64_t cols,
+                                                         void* stream) {
+  using namespace akgb;
+  if (!x || !out || rows <= 0 || cols <= 0) {
+    set_last_error("akgb_reduce_sum_axis0_f32_noalloc: null pointer or empty extent");
+    return AKGB_INVALID_ARG;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    set_last_error("akgb_reduce_sum_axis0_f32_noalloc: no current CUDA device");
+    return AKGB_CUDA_ERROR;
+  }
+  NoAllocDevice& d = g_noalloc_dev[dev];
+  {
+    // First call on this device: translate the array's name into its device address.  In host code the
+    // name g_noalloc_scratch is only a handle for the runtime, not something a kernel can dereference.
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (!d.ready) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+      if (e != cudaSuccess || !p) {
+        set_last_error("akgb_reduce_sum_axis0_f32_noalloc: cudaGetSymbolAddress failed");
+        return AKGB_CUDA_ERROR;
+      }
+      int sms = 0;
+      e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      if (e != cudaSuccess || sms <= 0) {
+        set_last_error("akgb_reduce_sum_axis0_f32_noalloc: cannot query the SM count");
+        return AKGB_CUDA_ERROR;
+      }
+      d.scratch = static_cast<float*>(p);
+      d.sm_count = sms;
+      d.ready = true;
+    }
+  }
+  const size_t need = reduce_col_workspace(rows, cols, d.sm_count);  // bytes of partials, 0 = single split
+  if (cols > kNoAllocMaxCols || need > kNoAllocScratchFloats * sizeof(float)) {
+    char msg[224];
+    std::snprintf(msg, sizeof(msg),
+                  "akgb_reduce_sum_axis0_f32_noalloc: %lld x %lld is beyond the built-in scratch (at most %lld "
+                  "columns, %zu bytes of partials; this shape needs %zu); use akgb_launch with a caller workspace",
+                  (long long)rows, (long long)cols, (long long)kNoAllocMaxCols,
+                  kNoAllocScratchFloats * sizeof(float), need);
+    set_last_error(msg);
+    return AKGB_TOO_LARGE;
+  }
+  e = reduce_col_f32(RedOp::Sum, x, out, rows, cols, d.scratch, d.sm_count, reinterpret_cast<cudaStream_t>(stream),
+                     nullptr);
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return AKGB_CUDA_ERROR;
+  }
+  return AKGB_OK;
+}

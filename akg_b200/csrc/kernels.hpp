@@ -7,6 +7,9 @@
 
 namespace akgb {
 
+// Records the text akgb_last_error() returns on the calling thread (defined beside the C ABI).
+void set_last_error(const char* text);
+
 struct LaunchDims {
   unsigned grid[3] = {1, 1, 1};
   unsigned block[3] = {1, 1, 1};

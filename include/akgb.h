@@ -141,6 +141,21 @@ int64_t akgb_kernel_flops(const akgb_kernel* k);
  * (bounded waits that gave up).  0 = none. */
 akgb_status akgb_check_device_error(akgb_kernel* k, uint32_t* word);
 
+/* Column sum x[rows, cols] -> out[cols] (float32, device pointers, asynchronous on `stream`) that
+ * allocates nothing: no cudaMalloc/cudaFree, no workspace argument.  It has no counterpart in the
+ * reference; it exists for callers that cannot allocate device memory where they need the reduction
+ * (inside a memory-planned region of a framework, while an allocator is exhausted or shutting down,
+ * in a loop that cannot afford cudaMalloc's implicit synchronisation).  The partial sums live in a
+ * 1 MiB array built into the library (resident on every GPU that loads it, until the process exits).
+ *   - Limit: cols <= 65536 (any row count); wider inputs, or a device with so many SMs that the
+ *     partials would not fit the 1 MiB, return AKGB_TOO_LARGE: use akgb_launch with a workspace.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
+ *     that first call outside any stream capture.  The current device must be the one holding x/out.
+ *   - All calls on a device share the array: issue them so that their kernels do not overlap on the
+ *     GPU (same stream, or ordered by events).  No clearing is needed between calls.
+ * Results are bit-identical to akgb_launch of the same ReduceSum(axis 0) description. */
+akgb_status akgb_reduce_sum_axis0_f32_noalloc(const float* x, float* out, int64_t rows, int64_t cols, void* stream);
+
 /* Text of the last error on the calling thread. */
 const char* akgb_last_error(void);
 
