@@ -55,7 +55,7 @@ def measured_peaks():
 
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, scaled to the full
 # workload where the capture ran a smaller case; filled in from profiles/ (None = not captured yet)
-NCU_TRAFFIC_BYTES = {"gelu": None}
+NCU_TRAFFIC_BYTES = {"gelu": 537201152 + 483198720}  # profiles/gelu_chain_f16_64x512x4096.md, full-size capture
 
 
 class ClockSampler:
@@ -322,7 +322,7 @@ def gpu_arm(args):
         "gpu_launches": k.launch_count * args.steps,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
                      "frac": round(achieved / hbm_peak, 4), "traffic": NCU_TRAFFIC_BYTES["gelu"],
-                     "peak_source": peak_src, "kernel": "gelu_chain_f16_kernel",
+                     "peak_source": peak_src, "kernel": "gelu_chain_f16_oneshot_kernel",
                      "frac_of_8TBs": round(achieved / 8000.0, 4)},
     }
     del bufs, host, host_np
