@@ -65,6 +65,15 @@ struct akgb_kernel {
   void* d_workspace = nullptr;
   cudaStream_t stream = nullptr;
   bool staged = false;
+  // chunked pipeline of akgb_run_host: the same region planned on 1/nchunks of axis 0, so that the
+  // host->device copy of chunk c+1, the kernels of chunk c and the device->host copy of chunk c-1 overlap
+  std::string json_text;
+  int nchunks = 0;  // 0 = not pipelined
+  Plan chunk_plan;
+  std::vector<char> chunk_split;     // per argument: 1 = axis 0 is cut into chunks
+  std::vector<size_t> chunk_bytes;   // per argument: bytes of one chunk
+  cudaStream_t s_in = nullptr, s_out = nullptr;
+  std::vector<cudaEvent_t> ev_in, ev_done;
 };
 
 namespace {
@@ -165,6 +174,97 @@ int launches_of(const akgb_kernel* k) {
   return n;
 }
 
+// Tries to plan the region on a fraction of axis 0.  Any failure simply leaves nchunks at 0 (one-shot path).
+void plan_chunks(akgb_kernel* k) {
+  k->nchunks = 0;
+  int64_t moved = 0;
+  for (auto& d : k->descs) moved += d.nbytes;
+  if (moved < (int64_t)64 << 20) return;  // too small to be worth several copies
+  for (int n : {32, 16, 8, 4, 2}) {
+    if (moved / n < ((int64_t)8 << 20)) continue;  // keep every copy large enough to run at full PCIe rate
+    try {
+      Graph g = parse_info(k->json_text.data(), k->json_text.size());
+      infer_sharding(g, 0, k->shard_world * n);
+      bool ok = true;
+      std::vector<char> split;
+      std::vector<size_t> bytes;
+      auto visit = [&](int vid) {
+        const Value& v = g.v(vid);
+        if (v.partial) ok = false;
+        split.push_back(v.split0 ? 1 : 0);
+        bytes.push_back((size_t)v.numel() * dt_size(v.dt));
+      };
+      for (int vid : g.inputs) visit(vid);
+      for (int vid : g.outputs) {
+        visit(vid);
+        if (!g.v(vid).split0) ok = false;  // every output must be produced chunk by chunk
+      }
+      if (!ok) return;
+      Plan p = build_plan(g, k->sm_count);
+      if (p.workspace_bytes > k->plan.workspace_bytes) return;
+      if (cudaStreamCreateWithFlags(&k->s_in, cudaStreamNonBlocking) != cudaSuccess) return;
+      if (cudaStreamCreateWithFlags(&k->s_out, cudaStreamNonBlocking) != cudaSuccess) return;
+      k->ev_in.assign(n, nullptr);
+      k->ev_done.assign(n, nullptr);
+      for (int i = 0; i < n; ++i) {
+        if (cudaEventCreateWithFlags(&k->ev_in[i], cudaEventDisableTiming) != cudaSuccess) return;
+        if (cudaEventCreateWithFlags(&k->ev_done[i], cudaEventDisableTiming) != cudaSuccess) return;
+      }
+      k->chunk_plan = std::move(p);
+      k->chunk_split = std::move(split);
+      k->chunk_bytes = std::move(bytes);
+      k->nchunks = n;
+      return;
+    } catch (const std::exception&) {
+      // not divisible by this chunk count, or the region does not split on axis 0: try fewer chunks
+    }
+  }
+}
+
+akgb_status run_host_chunked(akgb_kernel* k, void* const* host) {
+  const int n = k->nchunks;
+  const size_t nt = k->descs.size();
+  cudaError_t e;
+  // operands that are not cut (bias, gamma, mask, the right matmul operand) go first, whole
+  for (int i = 0; i < k->n_inputs; ++i) {
+    if (k->chunk_split[i] || !k->descs[i].nbytes) continue;
+    e = cudaMemcpyAsync(k->d_tensors[i], host[i], (size_t)k->descs[i].nbytes, cudaMemcpyHostToDevice, k->s_in);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(H2D)");
+  }
+  std::vector<void*> ptrs(nt);
+  for (int c = 0; c < n; ++c) {
+    for (int i = 0; i < k->n_inputs; ++i) {
+      if (!k->chunk_split[i]) continue;
+      const size_t off = (size_t)c * k->chunk_bytes[i];
+      e = cudaMemcpyAsync((char*)k->d_tensors[i] + off, (const char*)host[i] + off, k->chunk_bytes[i],
+                          cudaMemcpyHostToDevice, k->s_in);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(H2D chunk)");
+    }
+    cudaEventRecord(k->ev_in[c], k->s_in);
+    cudaStreamWaitEvent(k->stream, k->ev_in[c], 0);
+    for (size_t i = 0; i < nt; ++i)
+      ptrs[i] = k->chunk_split[i] ? (void*)((char*)k->d_tensors[i] + (size_t)c * k->chunk_bytes[i]) : k->d_tensors[i];
+    // run_plan works on k->plan: swap the chunk plan in for the call
+    std::swap(k->plan, k->chunk_plan);
+    akgb_status st = run_plan(k, ptrs.data(), k->d_workspace, k->stream);
+    std::swap(k->plan, k->chunk_plan);
+    if (st != AKGB_OK) return st;
+    cudaEventRecord(k->ev_done[c], k->stream);
+    cudaStreamWaitEvent(k->s_out, k->ev_done[c], 0);
+    for (size_t i = k->n_inputs; i < nt; ++i) {
+      const size_t off = (size_t)c * k->chunk_bytes[i];
+      e = cudaMemcpyAsync((char*)host[i] + off, (const char*)k->d_tensors[i] + off, k->chunk_bytes[i],
+                          cudaMemcpyDeviceToHost, k->s_out);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(D2H chunk)");
+    }
+  }
+  e = cudaStreamSynchronize(k->s_out);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(k->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(k->s_in);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+  return AKGB_OK;
+}
+
 akgb_status stage(akgb_kernel* k) {
   if (k->staged) return AKGB_OK;
   cudaError_t e = cudaSetDevice(k->device);
@@ -181,6 +281,7 @@ akgb_status stage(akgb_kernel* k) {
   }
   e = cudaStreamCreateWithFlags(&k->stream, cudaStreamNonBlocking);
   if (e != cudaSuccess) return cuda_fail(e, "cudaStreamCreate");
+  plan_chunks(k);
   k->staged = true;
   return AKGB_OK;
 }
@@ -215,6 +316,7 @@ akgb_status akgb_compile(const char* info_json, size_t len, const akgb_options* 
     k->sm_count = query_sm_count(device);
     k->shard_rank = rank;
     k->shard_world = world;
+    k->json_text.assign(info_json, len);
     k->graph = parse_info(info_json, len);
     infer_sharding(k->graph, rank, world);
     k->plan = build_plan(k->graph, k->sm_count);
@@ -258,6 +360,12 @@ void akgb_release(akgb_kernel* k) {
       if (p) cudaFree(p);
     if (k->d_workspace) cudaFree(k->d_workspace);
     if (k->stream) cudaStreamDestroy(k->stream);
+    if (k->s_in) cudaStreamDestroy(k->s_in);
+    if (k->s_out) cudaStreamDestroy(k->s_out);
+    for (auto ev : k->ev_in)
+      if (ev) cudaEventDestroy(ev);
+    for (auto ev : k->ev_done)
+      if (ev) cudaEventDestroy(ev);
   }
   delete k;
 }
@@ -298,6 +406,7 @@ akgb_status akgb_run_host(akgb_kernel* k, void* const* host) {
   if (st != AKGB_OK) return st;
   st = ensure_device_state(k);
   if (st != AKGB_OK) return st;
+  if (k->nchunks > 1) return run_host_chunked(k, host);
   cudaError_t e;
   for (int i = 0; i < k->n_inputs; ++i) {
     if (!k->descs[i].nbytes) continue;

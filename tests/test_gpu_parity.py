@@ -205,3 +205,28 @@ def test_matmul_epilogue(lib, m, k, n, tb, bias, relu):
     outs32 = k32.empty_outputs()
     k32.run_host(list(ins) + outs32)
     np.testing.assert_allclose(outs32[0], ref32, rtol=2e-3, atol=atol)
+
+
+@pytest.mark.parametrize("name,desc,kinds", [
+    ("gelu", descs.gelu_chain([16, 512, 4096]), KINDS["gelu"]),
+    ("softmax", descs.masked_softmax(32, 512, 2048), KINDS["softmax"]),
+    ("transpose", descs.transpose([16, 1024, 32, 128], [0, 2, 1, 3]), {}),
+    ("layernorm", descs.layernorm(16384, 1024), KINDS["layernorm"]),
+])
+def test_chunked_host_entry_point_matches_device_launch(lib, name, desc, kinds):
+    """Above 64 MB akgb_run_host cuts axis 0 into chunks and overlaps copies with kernels; the bytes it returns
+    must be those of one launch over the whole tensors."""
+    import torch
+    ins = make_inputs(desc, 21, kinds)
+    got, k = run_host(desc, ins)
+    dev = [torch.from_numpy(a).cuda() for a in ins]
+    outs = [torch.empty(t.nbytes, dtype=torch.uint8, device="cuda") for t in k.outputs]
+    k.launch(dev + outs)
+    torch.cuda.synchronize()
+    for g, o in zip(got, outs):
+        assert np.array_equal(np.ascontiguousarray(g).view(np.uint8).reshape(-1), o.cpu().numpy())
+    # and a second call reuses the staging buffers
+    got2 = k.empty_outputs()
+    k.run_host(list(ins) + got2)
+    for a, b in zip(got, got2):
+        assert bits_equal(a, b)
