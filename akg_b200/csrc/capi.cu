@@ -133,9 +133,18 @@ akgb_status run_plan(akgb_kernel* k, void* const* tensors, void* ws, cudaStream_
         e = softmax_rows(st.sm, a, b, o, ds.err_word, s, &st.dims);
         break;
       case StepK::ReduceCol:
-        e = reduce_col_f32(st.red_op, (const float*)a, (float*)o, st.red_len, st.red_inner, scratch, k->sm_count, s,
-                           &st.dims);
+        for (int64_t bi = 0; bi < st.red_outer && e == cudaSuccess; ++bi)
+          e = reduce_col_f32(st.red_op, (const float*)a + bi * st.red_batch_in, (float*)o + bi * st.red_batch_out,
+                             st.red_len, st.red_inner, scratch, k->sm_count, s, &st.dims);
         break;
+      case StepK::Ew: {
+        const void* ins[kEwMaxIn];
+        void* outs[kEwMaxOut];
+        for (size_t i = 0; i < st.ew_in.size(); ++i) ins[i] = resolve(st.ew_in[i], tensors, ws);
+        for (size_t i = 0; i < st.ew_out.size(); ++i) outs[i] = resolve(st.ew_out[i], tensors, ws);
+        e = ew_generic(st.ew, ins, outs, s, &st.dims);
+        break;
+      }
       case StepK::ReduceAll:
         e = reduce_all_f32(st.red_op, (const float*)a, (float*)o, st.red_len, scratch, k->sm_count, s, &st.dims);
         break;
@@ -159,7 +168,7 @@ int launches_of(const akgb_kernel* k) {
   for (const Step& st : k->plan.steps) {
     switch (st.kind) {
       case StepK::ReduceCol:
-        n += reduce_col_workspace(st.red_len, st.red_inner, k->sm_count) ? 2 : 1;
+        n += (int)st.red_outer * (reduce_col_workspace(st.red_len, st.red_inner, k->sm_count) ? 2 : 1);
         break;
       case StepK::ReduceAll:
         n += 2;

@@ -1,0 +1,57 @@
+// Program of the generic elementwise/broadcast kernel: a straight-line list of
+// typed ops over a small register file, one value per register per element.
+// Built on the host from any group of elementwise ops of a fused region that no
+// specialised template claims; executed by ew_generic_kernel.
+#pragma once
+#include <cstdint>
+
+namespace akgb {
+
+enum EwOp : uint8_t {
+  EW_COPY = 0,  // BroadcastTo / identity
+  // unary
+  EW_ABS, EW_NEG, EW_EXP, EW_LOG, EW_TANH, EW_RSQRT, EW_SQRT, EW_RECIP, EW_FLOOR, EW_SQUARE, EW_SIN, EW_COS,
+  EW_ASINH, EW_ACOSH, EW_ATAN, EW_ASIN, EW_ACOS, EW_ISINF, EW_ISFINITE, EW_ISNAN, EW_NOT, EW_CAST,
+  // binary
+  EW_ADD, EW_SUB, EW_MUL, EW_DIV, EW_MAX, EW_MIN, EW_POW, EW_ATAN2, EW_EQ, EW_NE, EW_GT, EW_GE, EW_LT, EW_LE,
+  EW_AND, EW_OR,
+  // ternary
+  EW_SELECT
+};
+
+// how a register holds its value
+enum EwClass : uint8_t { EWC_FLOAT = 0, EWC_INT = 1, EWC_BOOL = 2 };
+
+struct EwInstr {
+  uint8_t op;       // EwOp
+  uint8_t dt;       // DT code of the result (rounding target)
+  uint8_t cls;      // EwClass of the result
+  uint8_t src_cls;  // EwClass of the operands (compares, casts)
+  uint8_t dst, a, b, c;
+};
+
+enum EwIndexKind : int32_t { EWI_FULL = 0, EWI_MOD = 1, EWI_SCALAR = 2, EWI_STRIDED = 3 };
+
+constexpr int kEwMaxIn = 10, kEwMaxOut = 6, kEwMaxInstr = 96, kEwMaxReg = 48, kEwMaxConst = 24, kEwMaxRank = 6;
+
+struct EwOperand {
+  int32_t dt;          // DT code of the tensor in memory
+  int32_t kind;        // EwIndexKind
+  int32_t reg;         // register loaded from / stored to
+  int32_t pad;
+  int64_t mod;         // EWI_MOD: index = e % mod
+  int64_t stride[kEwMaxRank];  // EWI_STRIDED: element stride per iteration dim (0 = broadcast)
+};
+
+struct EwProgram {
+  int32_t n_in, n_out, n_instr, n_reg, n_const, rank;
+  int64_t n;                     // elements of the iteration space
+  int64_t shape[kEwMaxRank];     // iteration space (folded), row-major
+  EwOperand in[kEwMaxIn];
+  EwOperand out[kEwMaxOut];
+  uint32_t const_bits[kEwMaxConst];  // already rounded to the constant's declared type
+  uint8_t const_reg[kEwMaxConst];
+  EwInstr instr[kEwMaxInstr];
+};
+
+}  // namespace akgb

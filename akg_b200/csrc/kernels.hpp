@@ -65,6 +65,11 @@ cudaError_t reduce_all_f32(RedOp op, const float* x, float* out, int64_t n, void
 cudaError_t reduce_row_f32(RedOp op, const float* x, float* out, int64_t rows, int64_t cols, cudaStream_t s,
                            LaunchDims* dims);
 
+// ---- generic elementwise/broadcast interpreter (program in ew_program.hpp) ----------
+struct EwProgram;
+size_t ew_generic_smem(const EwProgram& p);
+cudaError_t ew_generic(const EwProgram& p, const void* const* in, void* const* out, cudaStream_t s, LaunchDims* dims);
+
 // ---- transpose -----------------------------------------------------------------
 // General permutation of up to 6 folded dims over elements of `esize` bytes.
 struct TransposeParams {

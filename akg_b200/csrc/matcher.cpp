@@ -682,11 +682,7 @@ Plan build_plan(const Graph& g, int sm_count) {
       ok = match_gelu_chain(g, plan);
       break;
   }
-  if (!ok) {
-    plan = Plan();
-    throw Unsupported("no kernel template matches this fused region (class " +
-                      std::to_string((int)g.op_class) + ")");
-  }
+  if (!ok) plan = build_generic_plan(g, sm_count);
   plan.bytes = io_bytes(g);
   return plan;
 }

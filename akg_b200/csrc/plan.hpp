@@ -4,6 +4,7 @@
 #include <string>
 #include <vector>
 
+#include "ew_program.hpp"
 #include "graph.hpp"
 #include "kernels.hpp"
 
@@ -17,7 +18,7 @@ struct Ref {
   bool valid() const { return arg >= 0 || ws_off >= 0; }
 };
 
-enum class StepK : int { GeluChain, LayerNorm, Softmax, ReduceCol, ReduceAll, ReduceRow, Transpose, Matmul };
+enum class StepK : int { GeluChain, LayerNorm, Softmax, ReduceCol, ReduceAll, ReduceRow, Transpose, Matmul, Ew };
 
 struct Step {
   StepK kind;
@@ -31,6 +32,9 @@ struct Step {
   int64_t red_outer = 1, red_len = 1, red_inner = 1;
   TransposeParams tp;
   MatmulParams mm;
+  EwProgram ew;              // StepK::Ew
+  std::vector<Ref> ew_in, ew_out;
+  int64_t red_batch_in = 0, red_batch_out = 0;  // batched column reductions: element stride per outer index
   LaunchDims dims;          // filled at first launch
 };
 
@@ -45,5 +49,8 @@ struct Plan {
 
 // Pattern matcher: places the region on kernel templates or throws Unsupported.
 Plan build_plan(const Graph& g, int sm_count);
+// Fallback of build_plan: splits the region into elementwise groups (generic kernel), reductions, transposes and
+// matmuls that run one after the other with intermediates in the workspace.
+Plan build_generic_plan(const Graph& g, int sm_count);
 
 }  // namespace akgb

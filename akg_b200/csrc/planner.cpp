@@ -1,0 +1,483 @@
+// Generic planner: runs any region made of supported ops as a sequence of kernels.
+//
+// The reference compiles every fused region into one kernel through its polyhedral pipeline
+// (akg-mlir/lib/Pipelines/GPUPipelines/GPUOpt.cpp:45-132).  Here the specialised templates cover the shapes that
+// matter for bandwidth; everything else is split at the points where the iteration space changes:
+//   * consecutive elementwise / BroadcastTo ops over one iteration shape -> one launch of the generic
+//     elementwise kernel (per-op typed arithmetic, broadcast by dropped dims);
+//   * each reduction, transpose and matmul -> its own template launch;
+//   * Reshape is a view (EliminateReshape in the reference drops boundary reshapes the same way).
+// Values that cross a launch boundary live in the caller's workspace.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <map>
+#include <set>
+
+#include "hostconv.hpp"
+#include "plan.hpp"
+
+namespace akgb {
+namespace {
+
+EwClass cls_of(DT d) { return dt_is_float(d) ? EWC_FLOAT : (d == DT::Bool ? EWC_BOOL : EWC_INT); }
+
+bool ew_opcode(OpK k, EwOp* op) {
+  switch (k) {
+    case OpK::Abs: *op = EW_ABS; return true;
+    case OpK::Neg: *op = EW_NEG; return true;
+    case OpK::Exp: *op = EW_EXP; return true;
+    case OpK::Log: *op = EW_LOG; return true;
+    case OpK::Tanh: *op = EW_TANH; return true;
+    case OpK::Rsqrt: *op = EW_RSQRT; return true;
+    case OpK::Sqrt: *op = EW_SQRT; return true;
+    case OpK::Reciprocal: *op = EW_RECIP; return true;
+    case OpK::Floor: *op = EW_FLOOR; return true;
+    case OpK::Square: *op = EW_SQUARE; return true;
+    case OpK::Sin: *op = EW_SIN; return true;
+    case OpK::Cos: *op = EW_COS; return true;
+    case OpK::Asinh: *op = EW_ASINH; return true;
+    case OpK::Acosh: *op = EW_ACOSH; return true;
+    case OpK::Atan: *op = EW_ATAN; return true;
+    case OpK::ASin: *op = EW_ASIN; return true;
+    case OpK::ACos: *op = EW_ACOS; return true;
+    case OpK::IsInf: *op = EW_ISINF; return true;
+    case OpK::IsFinite: *op = EW_ISFINITE; return true;
+    case OpK::IsNan: *op = EW_ISNAN; return true;
+    case OpK::LogicalNot: *op = EW_NOT; return true;
+    case OpK::Cast: *op = EW_CAST; return true;
+    case OpK::Add: *op = EW_ADD; return true;
+    case OpK::Sub: *op = EW_SUB; return true;
+    case OpK::Mul: *op = EW_MUL; return true;
+    case OpK::Div: *op = EW_DIV; return true;
+    case OpK::Maximum: *op = EW_MAX; return true;
+    case OpK::Minimum: *op = EW_MIN; return true;
+    case OpK::Pow: *op = EW_POW; return true;
+    case OpK::Atan2: *op = EW_ATAN2; return true;
+    case OpK::Equal: *op = EW_EQ; return true;
+    case OpK::NotEqual: *op = EW_NE; return true;
+    case OpK::Greater: *op = EW_GT; return true;
+    case OpK::GreaterEqual: *op = EW_GE; return true;
+    case OpK::Less: *op = EW_LT; return true;
+    case OpK::LessEqual: *op = EW_LE; return true;
+    case OpK::LogicalAnd: *op = EW_AND; return true;
+    case OpK::LogicalOr: *op = EW_OR; return true;
+    case OpK::Select: *op = EW_SELECT; return true;
+    case OpK::BroadcastTo: *op = EW_COPY; return true;
+    default: return false;
+  }
+}
+
+bool ew_dtype_ok(DT d) { return d != DT::I64 && d != DT::F64 && d != DT::Invalid; }
+
+uint32_t const_bits(double v, DT d) {
+  float f;
+  switch (d) {
+    case DT::F16: f = round_f64_to_f16(v); break;
+    case DT::BF16: f = round_f64_to_bf16(v); break;
+    case DT::F32: f = (float)v; break;
+    case DT::Bool: return v != 0.0 ? 1u : 0u;
+    default: return (uint32_t)(int32_t)std::llround(v);
+  }
+  uint32_t b;
+  std::memcpy(&b, &f, 4);
+  return b;
+}
+
+struct Builder {
+  const Graph& g;
+  int sm_count;
+  Plan plan;
+  std::map<int, Ref> where;     // value id -> buffer (only materialised values)
+  std::map<int, int> alias;     // value id -> value id it is a view of
+  size_t ws = 0;
+  std::vector<int> group;       // node indices of the open elementwise group
+  std::vector<int64_t> group_shape;
+
+  Builder(const Graph& gr, int sms) : g(gr), sm_count(sms) {}
+
+  int root(int v) const {
+    auto it = alias.find(v);
+    while (it != alias.end()) {
+      v = it->second;
+      it = alias.find(v);
+    }
+    return v;
+  }
+  Ref arg_ref(int vid) const {
+    const Value& v = g.v(vid);
+    Ref r;
+    if (v.input_index >= 0) r.arg = v.input_index;
+    else if (v.output_index >= 0) r.arg = (int)g.inputs.size() + v.output_index;
+    return r;
+  }
+  // buffer holding value vid (allocating workspace for intermediates on first use)
+  Ref buffer(int vid) {
+    vid = root(vid);
+    auto it = where.find(vid);
+    if (it != where.end()) return it->second;
+    Ref r = arg_ref(vid);
+    if (!r.valid()) {
+      // a view of this value may be a graph output: then the producer writes there directly
+      for (auto& kv : alias)
+        if (root(kv.first) == vid && g.v(kv.first).output_index >= 0) r = arg_ref(kv.first);
+    }
+    if (!r.valid()) {
+      r.ws_off = (int64_t)ws;
+      ws += ((size_t)g.v(vid).numel() * dt_size(g.v(vid).dt) + 255) / 256 * 256;
+    }
+    where[vid] = r;
+    return r;
+  }
+  bool produced_in_group(int vid) const {
+    int p = g.v(vid).producer;
+    return p >= 0 && std::find(group.begin(), group.end(), p) != group.end();
+  }
+  bool used_outside_group(int vid) const {
+    const Value& v = g.v(vid);
+    if (v.output_index >= 0) return true;
+    for (int u : v.users)
+      if (std::find(group.begin(), group.end(), u) == group.end()) return true;
+    for (auto& kv : alias)  // a view of it is needed later (or is an output)
+      if (kv.second == vid) return true;
+    return false;
+  }
+
+  void flush_group() {
+    if (group.empty()) return;
+    Step st;
+    st.kind = StepK::Ew;
+    st.kernel_name = "ew_generic";
+    EwProgram& P = st.ew;
+    std::memset(&P, 0, sizeof(P));
+    const std::vector<int64_t>& S = group_shape;
+    if (S.size() > (size_t)kEwMaxRank) throw Unsupported("elementwise group of rank above 6");
+    P.rank = (int)S.size();
+    P.n = 1;
+    for (size_t i = 0; i < S.size(); ++i) {
+      P.shape[i] = S[i];
+      P.n *= S[i];
+    }
+    // last use of every value inside the group, for register reuse
+    std::map<int, int> last_use;
+    for (size_t gi = 0; gi < group.size(); ++gi)
+      for (int vid : g.nodes[group[gi]].in) last_use[vid] = (int)gi;
+    std::map<int, int> reg_of;  // value id -> register
+    std::set<int> external;     // operands that come from outside the group
+    std::vector<int> free_regs;
+    int next_reg = 0;
+    auto alloc_reg = [&]() {
+      if (!free_regs.empty()) {
+        int r = free_regs.back();
+        free_regs.pop_back();
+        return r;
+      }
+      if (next_reg >= kEwMaxReg) throw Unsupported("elementwise group needs more than 48 live values");
+      return next_reg++;
+    };
+    auto operand_reg = [&](int vid) -> int {
+      auto it = reg_of.find(vid);
+      if (it != reg_of.end()) return it->second;
+      const Value& v = g.v(vid);
+      if (!ew_dtype_ok(v.dt)) throw Unsupported(std::string("generic elementwise kernel: type ") + dt_name(v.dt));
+      // operands from outside the group are loaded before the first instruction runs, so their registers are
+      // never shared with values computed in the group
+      if (next_reg >= kEwMaxReg) throw Unsupported("elementwise group needs more than 48 live values");
+      int r = next_reg++;
+      reg_of[vid] = r;
+      external.insert(vid);
+      if (v.is_const) {
+        if (v.cval.size() != 1) throw Unsupported("constant tensors with more than one element");
+        if (P.n_const >= kEwMaxConst) throw Unsupported("too many constants in one elementwise group");
+        P.const_bits[P.n_const] = const_bits(v.cval[0], v.dt);
+        P.const_reg[P.n_const] = (uint8_t)r;
+        ++P.n_const;
+        return r;
+      }
+      // external tensor operand
+      if (P.n_in >= kEwMaxIn) throw Unsupported("elementwise group with more than 10 tensor operands");
+      EwOperand& o = P.in[P.n_in];
+      o.dt = (int)v.dt;
+      o.reg = r;
+      std::vector<int64_t> vs = v.shape;
+      const int64_t vn = v.numel();
+      if (vn == P.n) o.kind = EWI_FULL;
+      else if (vn == 1) o.kind = EWI_SCALAR;
+      else {
+        while (vs.size() > 1 && vs.front() == 1) vs.erase(vs.begin());
+        bool trailing = vs.size() <= S.size();
+        for (size_t i = 0; trailing && i < vs.size(); ++i)
+          if (vs[vs.size() - 1 - i] != S[S.size() - 1 - i]) trailing = false;
+        if (trailing) {
+          o.kind = EWI_MOD;
+          o.mod = vn;
+        } else {
+          if (vs.size() > S.size()) throw Unsupported("operand rank above the iteration space");
+          o.kind = EWI_STRIDED;
+          int64_t stride = 1;
+          for (int i = (int)S.size() - 1, j = (int)vs.size() - 1; i >= 0; --i, --j) {
+            if (j >= 0) {
+              if (vs[j] == S[i]) o.stride[i] = stride;
+              else if (vs[j] == 1) o.stride[i] = 0;
+              else throw Unsupported("operand does not broadcast to the iteration space");
+              stride *= vs[j];
+            } else {
+              o.stride[i] = 0;
+            }
+          }
+        }
+      }
+      st.ew_in.push_back(buffer(vid));
+      ++P.n_in;
+      return r;
+    };
+    for (size_t gi = 0; gi < group.size(); ++gi)  // all outside operands first
+      for (int vid : g.nodes[group[gi]].in)
+        if (!produced_in_group(vid)) operand_reg(vid);
+    for (size_t gi = 0; gi < group.size(); ++gi) {
+      const Node& n = g.nodes[group[gi]];
+      const Value& out = g.v(n.out);
+      if (!ew_dtype_ok(out.dt)) throw Unsupported(std::string("generic elementwise kernel: type ") + dt_name(out.dt));
+      EwInstr ins;
+      std::memset(&ins, 0, sizeof(ins));
+      EwOp op;
+      if (n.kind == OpK::Reshape) op = EW_COPY;
+      else if (!ew_opcode(n.kind, &op)) throw Unsupported(std::string("op '") + n.name + "' in an elementwise group");
+      ins.op = op;
+      ins.dt = (uint8_t)out.dt;
+      ins.cls = cls_of(out.dt);
+      ins.src_cls = cls_of(g.v(n.in[0]).dt);
+      if (op == EW_SELECT) ins.src_cls = cls_of(g.v(n.in[1]).dt);
+      if (op == EW_CAST && ins.src_cls == EWC_FLOAT && ins.cls == EWC_INT)
+        throw Unsupported("float -> integer Cast: the reference's CPU pipeline rounds to nearest even, its expected-value "
+                          "generator truncates; parity unpinned");
+      int regs[3] = {0, 0, 0};
+      const size_t nin = std::min<size_t>(n.in.size(), 3);
+      for (size_t j = 0; j < nin; ++j) regs[j] = operand_reg(n.in[j]);
+      // operands whose last use is this instruction give their register back (unless they must be stored)
+      for (size_t j = 0; j < nin; ++j) {
+        int vid = n.in[j];
+        if (last_use[vid] == (int)gi && !(produced_in_group(vid) && used_outside_group(vid)) && reg_of.count(vid)) {
+          bool dup = false;
+          for (size_t q = 0; q < j; ++q) dup |= n.in[q] == vid;
+          if (!dup && !external.count(vid)) free_regs.push_back(reg_of[vid]);
+        }
+      }
+      int dst = alloc_reg();
+      reg_of[n.out] = dst;
+      ins.dst = (uint8_t)dst;
+      ins.a = (uint8_t)regs[0];
+      ins.b = (uint8_t)regs[1];
+      ins.c = (uint8_t)regs[2];
+      if (P.n_instr >= kEwMaxInstr) throw Unsupported("elementwise group with more than 96 ops");
+      P.instr[P.n_instr++] = ins;
+      if (used_outside_group(n.out)) {
+        if (P.n_out >= kEwMaxOut) throw Unsupported("elementwise group with more than 6 results");
+        EwOperand& o = P.out[P.n_out++];
+        o.dt = (int)out.dt;
+        o.kind = EWI_FULL;
+        o.reg = dst;
+        st.ew_out.push_back(buffer(n.out));
+      }
+    }
+    P.n_reg = next_reg;
+    if (ew_generic_smem(P) > 200 * 1024) throw Unsupported("elementwise group needs too many live values");
+    plan.steps.push_back(std::move(st));
+    group.clear();
+    group_shape.clear();
+  }
+
+  void add_reduce(const Node& n) {
+    RedOp op;
+    switch (n.kind) {
+      case OpK::ReduceSum: op = RedOp::Sum; break;
+      case OpK::ReduceMax: op = RedOp::Max; break;
+      case OpK::ReduceMin: op = RedOp::Min; break;
+      case OpK::ReduceProd: op = RedOp::Prod; break;
+      default: throw Unsupported(std::string("reduction '") + n.name + "' is not placed");
+    }
+    const Value& x = g.v(n.in[0]);
+    if (x.dt != DT::F32 || g.v(n.out).dt != DT::F32)
+      throw Unsupported("only float32 reductions are placed (cast before reducing, as the float16 accumulator of the "
+                        "reference's CPU pipeline and its float32 expected-value generator disagree)");
+    std::vector<bool> red(x.shape.size(), false);
+    for (auto a : n.axes) red[a] = true;
+    int64_t outer = 1, len = 1, inner = 1;
+    int phase = 0;
+    for (size_t i = 0; i < x.shape.size(); ++i) {
+      if (x.shape[i] == 1) continue;
+      if (red[i]) {
+        if (phase == 2) throw Unsupported("reduction over non-adjacent axes");
+        phase = 1;
+        len *= x.shape[i];
+      } else {
+        if (phase == 1) phase = 2;
+        (phase == 0 ? outer : inner) *= x.shape[i];
+      }
+    }
+    Step st;
+    st.red_op = op;
+    st.red_outer = outer;
+    st.red_len = len;
+    st.red_inner = inner;
+    st.a = buffer(n.in[0]);
+    st.out = buffer(n.out);
+    if (inner == 1 && outer == 1) {
+      st.kind = StepK::ReduceAll;
+      st.kernel_name = "reduce_all_f32";
+      st.scratch.ws_off = (int64_t)ws;
+      ws += (reduce_all_workspace(sm_count) + 255) / 256 * 256;
+    } else if (inner == 1) {
+      st.kind = StepK::ReduceRow;
+      st.kernel_name = "reduce_row_f32";
+    } else {
+      st.kind = StepK::ReduceCol;
+      st.kernel_name = "reduce_col_f32";
+      if (outer > 4096) throw Unsupported("batched column reduction with more than 4096 batches");
+      st.red_batch_in = len * inner;
+      st.red_batch_out = inner;
+      st.scratch.ws_off = (int64_t)ws;
+      ws += (reduce_col_workspace(len, inner, sm_count) + 255) / 256 * 256;
+    }
+    plan.steps.push_back(std::move(st));
+  }
+
+  void add_transpose(const Node& n) {
+    const std::vector<int64_t>& xs = g.v(n.in[0]).shape;
+    const size_t R = xs.size();
+    std::vector<int64_t> xstride(R, 1);
+    for (int i = (int)R - 2; i >= 0; --i) xstride[i] = xstride[i + 1] * xs[i + 1];
+    std::vector<int64_t> oshape, istride, src_axis;
+    for (size_t i = 0; i < R; ++i) {
+      int64_t ax = n.perm[i];
+      if (xs[ax] == 1) continue;
+      if (!src_axis.empty() && src_axis.back() + 1 == ax) {
+        oshape.back() *= xs[ax];
+        istride.back() = xstride[ax];
+        src_axis.back() = ax;
+      } else {
+        oshape.push_back(xs[ax]);
+        istride.push_back(xstride[ax]);
+        src_axis.push_back(ax);
+      }
+    }
+    if (oshape.empty()) {
+      oshape.push_back(1);
+      istride.push_back(1);
+    }
+    if (oshape.size() > 6) throw Unsupported("transpose of more than 6 independent axes");
+    Step st;
+    st.kind = StepK::Transpose;
+    st.kernel_name = "transpose_nd";
+    st.a = buffer(n.in[0]);
+    st.out = buffer(n.out);
+    st.tp.rank = (int)oshape.size();
+    for (size_t i = 0; i < oshape.size(); ++i) {
+      st.tp.out_shape[i] = oshape[i];
+      st.tp.in_stride[i] = istride[i];
+    }
+    st.tp.esize = (int)dt_size(g.v(n.in[0]).dt);
+    plan.steps.push_back(std::move(st));
+  }
+
+  void add_matmul(const Node& n) {
+    if (n.kind != OpK::MatMul) throw Unsupported("BatchMatMul is not placed");
+    if (n.transpose_a) throw Unsupported("MatMul with transpose_a is rejected (as by the reference lowering)");
+    const Value& a = g.v(n.in[0]);
+    const Value& b = g.v(n.in[1]);
+    const Value& o = g.v(n.out);
+    if (a.dt != DT::BF16 || b.dt != DT::BF16 || a.shape.size() != 2 || b.shape.size() != 2)
+      throw Unsupported("only 2-D bfloat16 MatMul is placed");
+    if (o.dt != DT::F32 && o.dt != DT::BF16) throw Unsupported("MatMul result type");
+    MatmulParams p;
+    p.M = a.shape[0];
+    p.K = a.shape[1];
+    p.transpose_b = n.transpose_b;
+    p.N = n.transpose_b ? b.shape[0] : b.shape[1];
+    p.out_dt = (int)o.dt;
+    p.bias_dt = (int)DT::F32;
+    const char* why = nullptr;
+    if (!matmul_bf16_supported(p, &why)) throw Unsupported(std::string("matmul shape not placed: ") + why);
+    Step st;
+    st.kind = StepK::Matmul;
+    st.kernel_name = "matmul_bf16_tcgen05";
+    st.a = buffer(n.in[0]);
+    st.b = buffer(n.in[1]);
+    st.out = buffer(n.out);
+    st.mm = p;
+    plan.flops += 2 * p.M * p.N * p.K;
+    plan.steps.push_back(std::move(st));
+  }
+
+  // Decides, before any buffer is assigned, which Reshape ops are views and which need a copy, and binds the
+  // buffer of a viewed intermediate to the graph output that views it.
+  std::set<int> reshape_copy;  // node indices
+  void plan_reshapes() {
+    std::map<int, int> bound_output;  // root value -> output value already bound to it
+    for (size_t i = 0; i < g.nodes.size(); ++i) {
+      const Node& n = g.nodes[i];
+      if (n.kind != OpK::Reshape) continue;
+      const int r = root(n.in[0]);
+      const Value& rv = g.v(r);
+      const bool out_is_output = g.v(n.out).output_index >= 0;
+      const bool root_is_io = rv.input_index >= 0 || rv.output_index >= 0;
+      if (out_is_output && (root_is_io || bound_output.count(r))) {
+        reshape_copy.insert((int)i);  // two caller buffers must hold the same values
+        continue;
+      }
+      alias[n.out] = n.in[0];
+      if (out_is_output) {
+        bound_output[r] = n.out;
+        where[r] = arg_ref(n.out);  // the producer of the viewed value writes into the output directly
+      }
+    }
+  }
+
+  Plan run() {
+    plan_reshapes();
+    for (size_t i = 0; i < g.nodes.size(); ++i) {
+      const Node& n = g.nodes[i];
+      if (n.kind == OpK::Reshape && !reshape_copy.count((int)i)) continue;  // a view
+      if (opk_is_elementwise(n.kind) || n.kind == OpK::BroadcastTo || n.kind == OpK::Reshape) {
+        const std::vector<int64_t>& S = g.v(n.out).shape;
+        if (!group.empty() && group_shape != S) flush_group();
+        // an operand that views a value still being computed in the open group must be materialised first
+        for (int vid : n.in)
+          if (!group.empty() && !produced_in_group(vid) && produced_in_group(root(vid))) flush_group();
+        // a Reshape copy consumes its source by flat index: the source must have the group's element order
+        if (n.kind == OpK::Reshape && produced_in_group(n.in[0]) && g.v(n.in[0]).shape != S) flush_group();
+        if (group.empty()) group_shape = S;
+        group.push_back((int)i);
+        continue;
+      }
+      flush_group();
+      if (opk_is_reduce(n.kind)) add_reduce(n);
+      else if (n.kind == OpK::Transpose) add_transpose(n);
+      else if (n.kind == OpK::MatMul || n.kind == OpK::BatchMatMul) add_matmul(n);
+      else throw Unsupported(std::string("operator '") + n.name + "' is not supported");
+    }
+    flush_group();
+    plan.workspace_bytes = ws;
+    return std::move(plan);
+  }
+};
+
+}  // namespace
+
+Plan build_generic_plan(const Graph& g, int sm_count) {
+  Builder b(g, sm_count);
+  Plan p = b.run();
+  if (p.steps.empty()) throw Unsupported("the region has no computing op");
+  switch (g.op_class) {
+    case OpClass::Elementwise: p.klass = "elementwise"; break;
+    case OpClass::Broadcast: p.klass = "broadcast"; break;
+    case OpClass::Reshape: p.klass = "reshape"; break;
+    case OpClass::Transpose: p.klass = "transpose"; break;
+    case OpClass::Matmul: p.klass = "matmul"; break;
+    default:
+      p.klass = g.reduce_dir == ReduceDir::All ? "reduce_all" : g.reduce_dir == ReduceDir::Y ? "reduce_y" : "reduce_x";
+  }
+  return p;
+}
+
+}  // namespace akgb

@@ -87,12 +87,14 @@ def test_commutative_spellings_match_and_reassociation_does_not(lib):
         if op["name"] in ("Mul", "Add"):
             op["input_desc"].reverse()
     assert FusedKernel(d).op_class == "broadcast"
-    # (t*t)*t spelled t*(t*t) is the same; but dropping the rounding step of t3*c0 changes results
+    # dropping the rounding step of t3*c0 changes results: the GELU template must not claim this graph;
+    # it runs through the generic elementwise kernel, op by op, instead
     d = descs.gelu_chain([2, 64])
-    del d["op_desc"][3]  # remove Mul(t3, c0) and rewire: no template may claim this graph silently
+    del d["op_desc"][3]  # remove Mul(t3, c0) and rewire
     d["op_desc"][3]["input_desc"][1][0]["tensor_name"] = d["op_desc"][2]["output_desc"][0]["tensor_name"]
-    with pytest.raises(UnsupportedError):
-        FusedKernel(d)
+    k = FusedKernel(d)
+    assert k.meta()["template"] == "ew_generic" and k.op_class == "broadcast"
+    assert FusedKernel(descs.gelu_chain([2, 64])).meta()["template"] == "gelu_chain_f16"
 
 
 def test_unsupported_and_malformed(lib):

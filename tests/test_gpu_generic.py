@@ -1,0 +1,243 @@
+"""Regions that no specialised template claims run through the generic plan (elementwise interpreter + reduction /
+transpose / matmul launches).  The shapes and op mixes follow the kinds of fused regions in the reference's own
+system-test corpus (akg-mlir/tests/st/**: add chains, Cast+Mul, Sub+RealDiv with a broadcast operand, Mul+RealDiv+Exp,
+LessEqual, Select, Mul->ReduceSum over X/ALL, ReduceSum over Y with keep_dims, [1,1]->[1,N] broadcasts)."""
+import numpy as np
+import pytest
+
+from akg_b200 import FusedKernel, descs
+from akg_b200.descs import _Builder, _attr, _reduce_attr
+from oracle import akg_oracle as O
+from helpers import BF16, bits_equal, make_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def run(desc, ins):
+    k = FusedKernel(desc)
+    outs = k.empty_outputs()
+    for o in outs:
+        o.view(np.uint8)[...] = 0xCD
+    k.run_host(list(ins) + outs)
+    assert k.check_device_error() == 0
+    return outs, k
+
+
+def check(desc, ins, rtol=0.0, atol=0.0, exact=False):
+    got, k = run(desc, ins)
+    want = O.evaluate(desc, ins)
+    for g, w in zip(got, want):
+        assert g.shape == w.shape and g.dtype == w.dtype
+        if exact:
+            assert bits_equal(g, w)
+        else:
+            np.testing.assert_allclose(g.astype(np.float64), w.astype(np.float64), rtol=rtol, atol=atol)
+    return k
+
+
+def test_add_chain_f32_exact(lib):
+    b = _Builder("Fused_AddChain_1")
+    f = "float32"
+    xs = [b.input(f"x{i}", [37, 129], f) for i in range(5)]
+    t = xs[0]
+    for x in xs[1:]:
+        t = b.emit("Add", [t, x], [37, 129], f)
+    b.output(t)
+    d = b.build()
+    k = check(d, make_inputs(d, 1), exact=True)
+    assert k.meta()["template"] == "ew_generic" and k.launch_count == 1
+
+
+def test_cast_mul_int_to_float_and_bf16(lib):
+    b = _Builder("Fused_Cast_Mul_2")
+    x = b.input("x", [64, 100], "int32")
+    y = b.input("y", [64, 100], "float32")
+    c = b.emit("Cast", [x], [64, 100], "float32", [_attr("dst_type", "str", "float32")])
+    m = b.emit("Mul", [c, y], [64, 100], "float32")
+    h = b.emit("Cast", [m], [64, 100], "bfloat16", [_attr("dst_type", "str", "bfloat16")])
+    b.output(m)
+    b.output(h)
+    d = b.build()
+    rng = np.random.default_rng(2)
+    ins = [rng.integers(-1000, 1000, (64, 100)).astype(np.int32), rng.standard_normal((64, 100)).astype(np.float32)]
+    check(d, ins, exact=True)
+
+
+def test_sub_realdiv_with_broadcast_operands(lib):
+    b = _Builder("Fused_Sub_RealDiv_3")
+    f = "float32"
+    x = b.input("x", [8, 33, 70], f)
+    m = b.input("m", [8, 33, 1], f)   # broadcast over the last axis
+    s = b.input("s", [70], f)         # broadcast over the leading axes
+    c = b.input("c", [1, 1], f)       # scalar-like
+    t = b.emit("Sub", [x, m], [8, 33, 70], f)
+    t = b.emit("RealDiv", [t, s], [8, 33, 70], f)
+    t = b.emit("Add", [t, c], [8, 33, 70], f)
+    b.output(t)
+    d = b.build()
+    ins = make_inputs(d, 3)
+    ins[2] = np.abs(ins[2]) + np.float32(0.5)
+    check(d, ins, exact=True)
+
+
+def test_mul_realdiv_exp_f16(lib):
+    b = _Builder("Fused_Mul_RealDiv_Exp_4")
+    h = "float16"
+    x = b.input("x", [1000, 40], h)
+    y = b.input("y", [1000, 40], h)
+    t = b.emit("Mul", [x, b.const(0.5, h)], [1000, 40], h)
+    t = b.emit("RealDiv", [t, y], [1000, 40], h)
+    t = b.emit("Exp", [t], [1000, 40], h)
+    b.output(t)
+    d = b.build()
+    ins = make_inputs(d, 4)
+    ins[1] = (np.abs(ins[1]) + np.float16(1.0)).astype(np.float16)
+    # Mul and RealDiv are exact per op; Exp is a transcendental: 2e-3
+    check(d, ins, rtol=2e-3, atol=1e-6)
+
+
+def test_compare_select_maximum_bool_outputs(lib):
+    b = _Builder("Fused_LessEqual_Select_5")
+    f = "float32"
+    x = b.input("x", [17, 300], f)
+    y = b.input("y", [17, 300], f)
+    le = b.emit("LessEqual", [x, y], [17, 300], "bool")
+    mx = b.emit("Maximum", [x, b.const(0.0, f)], [17, 300], f)
+    sel = b.emit("Select", [le, mx, y], [17, 300], f)
+    ne = b.emit("NotEqual", [sel, y], [17, 300], "bool")
+    b.output(le)
+    b.output(sel)
+    b.output(ne)
+    d = b.build()
+    check(d, make_inputs(d, 5), exact=True)
+
+
+def test_int32_arithmetic(lib):
+    b = _Builder("Fused_IntOps_6")
+    i = "int32"
+    x = b.input("x", [4096], i)
+    y = b.input("y", [4096], i)
+    t = b.emit("Add", [x, y], [4096], i)
+    t = b.emit("Mul", [t, b.const(3, i)], [4096], i)
+    t = b.emit("Sub", [t, x], [4096], i)
+    a = b.emit("Abs", [t], [4096], i)
+    b.output(a)
+    d = b.build()
+    rng = np.random.default_rng(6)
+    check(d, [rng.integers(-9999, 9999, 4096).astype(np.int32) for _ in range(2)], exact=True)
+
+
+def test_mul_reduce_sum_x_and_all(lib):
+    # Square -> ReduceSum over all axes ([768,512] -> [1]) and over the last axis
+    for axes, oshape in (([0, 1], [1]), ([1], [768])):
+        b = _Builder("Fused_Mul_ReduceSum_7")
+        f = "float32"
+        x = b.input("x", [768, 512], f)
+        sq = b.emit("Mul", [x, x], [768, 512], f)
+        r = b.emit("ReduceSum", [sq], oshape, f, _reduce_attr(axes, False))
+        b.output(r)
+        d = b.build()
+        ins = make_inputs(d, 7)
+        got, k = run(d, ins)
+        truth = (ins[0].astype(np.float64) ** 2).sum(axis=tuple(axes)).reshape(oshape)
+        assert np.all(np.abs(got[0] - truth) <= 1e-5 * truth)
+        assert k.launch_count >= 2
+
+
+def test_reduce_sum_y_keep_dims_and_batched(lib):
+    b = _Builder("Fused_ReduceSum_8")
+    f = "float32"
+    x = b.input("x", [1, 510, 3072], f)
+    r = b.emit("ReduceSum", [x], [1, 1, 3072], f, _reduce_attr([1], True))
+    b.output(r)
+    d = b.build()
+    ins = make_inputs(d, 8)
+    got, _ = run(d, ins)
+    truth = ins[0].astype(np.float64).sum(axis=1, keepdims=True)
+    assert np.all(np.abs(got[0] - truth) <= 1e-5 * np.abs(ins[0]).sum(axis=1, keepdims=True))
+    # batched: reduce the middle axis of [6, 200, 96]
+    b = _Builder("Fused_ReduceMax_9")
+    x = b.input("x", [6, 200, 96], f)
+    b.output(b.emit("ReduceMax", [x], [6, 96], f, _reduce_attr([1], False)))
+    d = b.build()
+    ins = make_inputs(d, 9)
+    got, _ = run(d, ins)
+    assert np.array_equal(got[0], ins[0].max(axis=1))
+
+
+def test_broadcast_to_and_reshape_views(lib):
+    b = _Builder("Fused_BroadcastTo_10")
+    f = "float32"
+    x = b.input("x", [1, 1], f)
+    y = b.input("y", [1, 5000], f)
+    bx = b.emit("BroadcastTo", [x], [1, 5000], f, [_attr("shape", "listInt", [1, 5000])])
+    t = b.emit("Mul", [bx, y], [1, 5000], f)
+    r = b.emit("Reshape", [t], [50, 100], f, [_attr("shape", "listInt", [50, 100])])
+    u = b.emit("Add", [r, b.const(1.0, f)], [50, 100], f)
+    b.output(u)
+    b.output(b.emit("Reshape", [u], [5000], f, [_attr("shape", "listInt", [5000])], out_name="u_flat"))
+    d = b.build()
+    check(d, make_inputs(d, 10), exact=True)
+
+
+def test_layernorm_other_spelling_runs_as_generic_plan(lib):
+    # variance via E[x^2] - mean^2 and division instead of multiplication: not the template's spelling
+    rows, cols = 48, 200
+    b = _Builder("Fused_LayerNormVariant_11")
+    f = "float32"
+    x = b.input("x", [rows, cols], f)
+    s1 = b.emit("ReduceSum", [x], [rows, 1], f, _reduce_attr([1], True))
+    mean = b.emit("RealDiv", [s1, b.const(float(cols), f)], [rows, 1], f)
+    sq = b.emit("Mul", [x, x], [rows, cols], f)
+    s2 = b.emit("ReduceSum", [sq], [rows, 1], f, _reduce_attr([1], True))
+    ex2 = b.emit("RealDiv", [s2, b.const(float(cols), f)], [rows, 1], f)
+    var = b.emit("Sub", [ex2, b.emit("Mul", [mean, mean], [rows, 1], f)], [rows, 1], f)
+    rstd = b.emit("Rsqrt", [b.emit("Add", [var, b.const(1e-5, f)], [rows, 1], f)], [rows, 1], f)
+    y = b.emit("Mul", [b.emit("Sub", [x, mean], [rows, cols], f), rstd], [rows, cols], f)
+    b.output(y)
+    d = b.build()
+    ins = make_inputs(d, 11)
+    got, k = run(d, ins)
+    want = O.evaluate(d, ins, accum="float64")
+    np.testing.assert_allclose(got[0], want[0], rtol=2e-4, atol=2e-5)  # E[x^2]-mean^2 cancels: looser than 1e-5
+    assert k.op_class == "reduce_x" and k.launch_count >= 5
+
+
+def test_matmul_with_unfused_epilogue(lib):
+    # MatMul -> Mul by a constant -> Add bias: not the bias/ReLU/cast template, runs as matmul + elementwise
+    m, k_, n = 256, 192, 264
+    b = _Builder("Fused_MatMul_Mul_Add_12")
+    h, f = "bfloat16", "float32"
+    a = b.input("a", [m, k_], h)
+    w = b.input("b", [k_, n], h)
+    bias = b.input("bias", [n], f)
+    c = b.emit("MatMul", [a, w], [m, n], f, [_attr("transpose_a", "bool", False), _attr("transpose_b", "bool", False)])
+    c = b.emit("Mul", [c, b.const(0.125, f)], [m, n], f)
+    c = b.emit("Add", [c, bias], [m, n], f)
+    b.output(c)
+    d = b.build()
+    ins = make_inputs(d, 12, {"a": "normal_small", "b": "normal_small"})
+    got, kern = run(d, ins)
+    want = O.evaluate(d, ins)[0]
+    np.testing.assert_allclose(got[0], want, rtol=2e-3, atol=1e-3 * float(np.abs(want).max()))
+    assert kern.launch_count == 2 and kern.flops == 2 * m * k_ * n
+
+
+def test_transpose_then_elementwise(lib):
+    b = _Builder("Fused_Transpose_Add_13")
+    h = "float16"
+    x = b.input("x", [12, 34, 56], h)
+    y = b.input("y", [56, 12, 34], h)
+    t = b.emit("Transpose", [x], [56, 12, 34], h, [_attr("perm", "listInt", [2, 0, 1])])
+    b.output(b.emit("Add", [t, y], [56, 12, 34], h))
+    d = b.build()
+    check(d, make_inputs(d, 13), exact=True)
+
+
+def test_float_to_int_cast_is_refused(lib):
+    from akg_b200 import UnsupportedError
+    b = _Builder("Fused_CastToInt_14")
+    x = b.input("x", [16], "float32")
+    b.output(b.emit("Cast", [x], [16], "int32", [_attr("dst_type", "str", "int32")]))
+    with pytest.raises(UnsupportedError):
+        FusedKernel(b.build())
