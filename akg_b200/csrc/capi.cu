@@ -126,8 +126,8 @@ akgb_status run_plan(akgb_kernel* k, void* const* tensors, void* ws, cudaStream_
         e = gelu_chain_f16(st.gelu, a, b, c, o, ds.gelu_lut, ds.err_word, s, &st.dims);
         break;
       case StepK::LayerNorm:
-        e = layernorm_f32(st.ln, (const float*)a, (const float*)b, (const float*)c, (float*)o, (float*)o2, (float*)o3, s,
-                          &st.dims);
+        e = layernorm_f32(st.ln, (const float*)a, (const float*)b, (const float*)c, (float*)o, (float*)o2, (float*)o3,
+                          ds.err_word, s, &st.dims);
         break;
       case StepK::Softmax:
         e = softmax_rows(st.sm, a, b, o, ds.err_word, s, &st.dims);

@@ -42,7 +42,7 @@ struct LayerNormParams {
   int has_gamma = 0, has_beta = 0, write_mean = 0, write_var = 0;
 };
 cudaError_t layernorm_f32(const LayerNormParams& p, const float* x, const float* gamma, const float* beta, float* y,
-                          float* mean, float* var, cudaStream_t s, LaunchDims* dims);
+                          float* mean, float* var, uint32_t* err_word, cudaStream_t s, LaunchDims* dims);
 
 struct SoftmaxParams {
   int64_t rows = 0, cols = 0;

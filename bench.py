@@ -159,23 +159,43 @@ def device_outputs(kernel, device):
     return [torch.empty(t.shape, dtype=torch_dtype(t.dtype), device=device) for t in kernel.outputs]
 
 
-def time_launches(kernel, buffer_sets, steps, warmup, barrier=None):
-    """Average device time of one launch in ms: CUDA events on the launch stream, sync on both sides."""
+def time_launches(kernel, buffer_sets, steps, warmup, barrier=None, use_graph=True):
+    """Average device time of one step in ms: CUDA events on the launch stream, sync on both sides.
+
+    The `steps` launches are captured once into a CUDA graph and the graph is what gets timed, so that short
+    kernels are not paced by the Python/ctypes call path; if capture is not possible (a collective in the step)
+    the launches are issued directly.
+    """
     import torch
-    stream = torch.cuda.current_stream()
-    for i in range(warmup):
-        kernel.launch(buffer_sets[i % len(buffer_sets)], stream)
-    torch.cuda.synchronize()
-    if barrier:
-        barrier()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record(stream)
-    for i in range(steps):
-        kernel.launch(buffer_sets[i % len(buffer_sets)], stream)
-    t1.record(stream)
-    torch.cuda.synchronize()
-    if barrier:
-        barrier()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for i in range(warmup):
+            kernel.launch(buffer_sets[i % len(buffer_sets)], stream)
+        stream.synchronize()
+        graph = None
+        if use_graph:
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    for i in range(steps):
+                        kernel.launch(buffer_sets[i % len(buffer_sets)], torch.cuda.current_stream())
+                graph.replay()  # one untimed replay
+            except Exception:
+                graph = None
+        torch.cuda.synchronize()
+        if barrier:
+            barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
+        if graph is not None:
+            graph.replay()
+        else:
+            for i in range(steps):
+                kernel.launch(buffer_sets[i % len(buffer_sets)], stream)
+        t1.record(stream)
+        torch.cuda.synchronize()
+        if barrier:
+            barrier()
     return t0.elapsed_time(t1) / steps
 
 
@@ -221,7 +241,7 @@ def run_classes(rank, world, device, steps, warmup, hbm_peak, tf_peak, barrier, 
 
         class _K:  # adapter so that time_launches includes the exchange step
             launch = staticmethod(step_launch)
-        ms = time_launches(_K, sets, steps, warmup, barrier)
+        ms = time_launches(_K, sets, steps, warmup, barrier, use_graph=not (partial and world > 1))
         ms_max = allreduce_max_scalar(ms, world)
         row = {"class": k.op_class, "ms": round(ms_max, 5), "launches_per_step": k.launch_count}
         if k.flops:
@@ -403,6 +423,77 @@ def reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def cpu_classes_table():
+    """Times the C restatement of the reference CPU pipeline on a bounded slice of every benchmark config:
+    R1 = the driver-default scalar single-thread loop nest, RP = OpenMP over all host threads.  Prints one JSON
+    line; slices are stated per row (throughput is per algorithmic byte/FLOP of the slice)."""
+    import ml_dtypes
+    from oracle import cpu_ref as C
+    rng = np.random.default_rng(0)
+    cores = C.num_threads()
+
+    def med(fn, reps=3):
+        fn()
+        ts = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            ts.append(time.perf_counter() - t0)
+        return float(np.median(ts))
+
+    rows = {}
+    f32 = lambda *s: rng.standard_normal(s, dtype=np.float32)
+    # C1 LayerNorm, full size
+    x, g, b = f32(8192, 1024), rng.uniform(0.5, 1.5, 1024).astype(np.float32), rng.uniform(-.1, .1, 1024).astype(np.float32)
+    nb = 67182592
+    rows["layernorm_f32_8192x1024"] = {"slice": "full", "bytes": nb,
+        "r1_gbs": nb / med(lambda: C.layernorm(x, g, b, variant="r1")) / 1e9,
+        "rp_gbs": nb / med(lambda: C.layernorm(x, g, b, variant="rp")) / 1e9}
+    # C2 GELU chain, 4 of 64 slices
+    xh, bias, yh = cpu_workload(4)
+    nb = xh.nbytes * 2 + bias.nbytes + xh.size * 4
+    rows["gelu_chain_f16_64x512x4096"] = {"slice": "4 of 64 leading slices", "bytes": nb,
+        "r1_gbs": nb / med(lambda: C.gelu_chain(xh, bias, yh, variant="r1"), 1) / 1e9,
+        "rp_gbs": nb / med(lambda: C.gelu_chain(xh, bias, yh, variant="rp")) / 1e9}
+    # C3 softmax, 4 of 256 batches
+    s = f32(4, 2048, 2048).astype(np.float16)
+    mask = np.where(np.tril(np.ones((2048, 2048), bool)), 0, -np.inf).astype(np.float16)
+    nb = s.nbytes * 2 + mask.nbytes
+    rows["masked_softmax_f16_256x2048x2048"] = {"slice": "4 of 256 batches", "bytes": nb,
+        "r1_gbs": nb / med(lambda: C.softmax(s, mask, 1 / np.sqrt(128.0), variant="r1"), 1) / 1e9,
+        "rp_gbs": nb / med(lambda: C.softmax(s, mask, 1 / np.sqrt(128.0), variant="rp")) / 1e9}
+    # C4 reductions, 8192 of 65536 rows
+    xr = f32(8192, 4096)
+    nb = xr.nbytes + 16384
+    rows["reduce_sum_axis0_f32_65536x4096"] = {"slice": "8192 of 65536 rows", "bytes": nb,
+        "r1_gbs": nb / med(lambda: C.reduce_sum_axis0(xr, variant="r1")) / 1e9,
+        "rp_gbs": nb / med(lambda: C.reduce_sum_axis0(xr, variant="rp")) / 1e9}
+    rows["reduce_max_all_f32_65536x4096"] = {"slice": "8192 of 65536 rows", "bytes": xr.nbytes + 4,
+        "r1_gbs": (xr.nbytes + 4) / med(lambda: C.reduce_max_all(xr, variant="r1")) / 1e9,
+        "rp_gbs": (xr.nbytes + 4) / med(lambda: C.reduce_max_all(xr, variant="rp")) / 1e9}
+    # C5b transpose, 4 of 32 batches
+    xt = f32(4, 2048, 32, 128).astype(np.float16)
+    rows["transpose_f16_32x2048x32x128"] = {"slice": "4 of 32 batches", "bytes": xt.nbytes * 2,
+        "r1_gbs": xt.nbytes * 2 / med(lambda: C.transpose4(xt, [0, 2, 1, 3], variant="r1")) / 1e9,
+        "rp_gbs": xt.nbytes * 2 / med(lambda: C.transpose4(xt, [0, 2, 1, 3], variant="rp")) / 1e9}
+    # C5a matmul, 128 of 8192 rows of A (RP) / 16 rows (R1)
+    A = (f32(128, 4096) * 0.02).astype(ml_dtypes.bfloat16)
+    B = (f32(4096, 8192) * 0.02).astype(ml_dtypes.bfloat16)
+    bi = (f32(8192) * 0.02).astype(ml_dtypes.bfloat16)
+    fl = 2.0 * 128 * 4096 * 8192
+    t_rp = med(lambda: C.matmul_bias_relu(A, B, bi, variant="rp"), 1)
+    t_r1 = med(lambda: C.matmul_bias_relu(A[:16], B, bi, variant="r1"), 1)
+    rows["matmul_bias_relu_bf16_8192x4096x8192"] = {"slice": "128 rows of A (RP), 16 rows (R1)",
+        "r1_tflops": 2.0 * 16 * 4096 * 8192 / t_r1 / 1e12, "rp_tflops": fl / t_rp / 1e12}
+    for r in rows.values():
+        for k_, v in list(r.items()):
+            if isinstance(v, float):
+                r[k_] = float(f"{v:.4g}")
+    print(json.dumps({"cpu_classes": rows, "cores": cores, "kind": "port",
+                      "note": "C restatement of the reference CPU pipeline (oracle/cpu_ref.c); R1 scalar single "
+                              "thread, RP OpenMP over all host threads"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -410,8 +501,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-classes", action="store_true", help="skip the per-class table")
+    ap.add_argument("--cpu-classes", action="store_true",
+                    help="time the CPU restatement on a slice of every class (no GPU work) and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.cpu_classes:
+        cpu_classes_table()
+        return
     if args.impl == "reference":
         reference_arm(args)
     else:
