@@ -162,7 +162,7 @@ def test_device_launch_matches_host_run_and_reports_dims(lib):
     for o, w in zip(outs, want):
         assert bits_equal(o.cpu().numpy(), w)
     meta = k.meta()
-    assert meta["blockIdx.x"] >= 1 and meta["threadIdx.x"] == 256
+    assert meta["blockIdx.x"] >= 1 and meta["threadIdx.x"] in (128, 256)
     us = k.profile_host(list(ins) + [w.copy() for w in want], number=5, repeat=2)
     assert 0 < us < 1e5
 
