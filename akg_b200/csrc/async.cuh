@@ -1,6 +1,6 @@
 // PTX wrappers for the asynchronous-copy machinery of sm_90+/sm_100: shared
 // memory barriers (mbarrier) with BOUNDED waits, bulk copies and tensor-map
-// (TMA) loads that complete on such a barrier.  No multicast forms.
+// (TMA) loads that complete on such a barrier.  Every CTA issues its own copies.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>

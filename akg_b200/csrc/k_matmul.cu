@@ -6,8 +6,8 @@
 // with the epilogue ops fused elementwise behind it.  Here:
 //   * one persistent CTA per SM walks 128x256 output tiles;
 //   * warp 0 streams 128x64 (A) and 64x256 (B) bf16 tiles through a 4-stage
-//     shared-memory ring with TMA (cp.async.bulk.tensor, 128-byte swizzle,
-//     no multicast);
+//     shared-memory ring with TMA (tiled tensor-map copies, 128-byte swizzle;
+//     every CTA fetches its own tiles);
 //   * warp 1 issues tcgen05.mma (M=128, N=256, K=16) into one of two 256-column
 //     TMEM accumulators, so the epilogue of tile i overlaps the MMAs of tile i+1;
 //   * warps 2-5 read the accumulator with tcgen05.ld, add the bias in f32,
@@ -15,12 +15,14 @@
 // Accumulation is f32 (the description gives MatMul an f32 result); bias Add,
 // Maximum and Cast follow in that order, one rounding each.
 //
+// Two variants share the epilogue: a single-CTA kernel (128x256 tiles, used when M <= 128) and a CTA-pair
+// kernel (tcgen05 cta_group::2, 256x256 tiles over two SMs, 6-stage ring), which is the default.
+//
 // Every wait on an mbarrier is bounded: when a limit is hit the kernel writes
 // an error word, drains its copies and MMAs, frees its TMEM and returns.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
-#include <cstdlib>
 #include <mutex>
 
 #include "async.cuh"
@@ -112,6 +114,91 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int*
   const int in_group = tile - group * per_group;
   *m_tile = first_m + in_group % rows;
   *n_tile = in_group / rows;
+}
+
+// Reads one 128x256 accumulator (this warp's 32 lanes) in chunks of 32 columns, applies bias / ReLU / cast in
+// that order and stores the row segment.
+__device__ __forceinline__ void epilogue_tile(const MatmulDev& p, uint32_t taddr, int row, int n0) {
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld32(taddr + c * 32, r);
+    tmem_ld_wait();
+    const int col0 = n0 + c * 32;
+    if (col0 >= p.N) continue;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    if (p.has_bias) {
+      if (col0 + 32 <= p.N) {
+        if (p.bias_dt == kBF16) {
+          const uint4* bp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + col0);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float b8[8];
+            unpack8(__ldg(bp + q), kBF16, b8);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[q * 8 + j] = __fadd_rn(v[q * 8 + j], b8[j]);
+          }
+        } else {
+          const float4* bp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + col0);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float4 b = __ldg(bp + q);
+            v[q * 4 + 0] = __fadd_rn(v[q * 4 + 0], b.x);
+            v[q * 4 + 1] = __fadd_rn(v[q * 4 + 1], b.y);
+            v[q * 4 + 2] = __fadd_rn(v[q * 4 + 2], b.z);
+            v[q * 4 + 3] = __fadd_rn(v[q * 4 + 3], b.w);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (col0 + j < p.N) {
+            const float b = p.bias_dt == kBF16
+                                ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(p.bias)[col0 + j])
+                                : reinterpret_cast<const float*>(p.bias)[col0 + j];
+            v[j] = __fadd_rn(v[j], b);
+          }
+        }
+      }
+    }
+    if (p.relu) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = v[j] != v[j] ? v[j] : fmaxf(v[j], 0.f);  // NaN stays NaN
+    }
+    if (row < p.M) {
+      if (p.out_dt == kBF16) {
+        uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + (size_t)row * p.N + col0;
+        if (col0 + 32 <= p.N) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 w;
+            w.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+            w.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+            w.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+            w.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+            *reinterpret_cast<uint4*>(o + q * 8) = w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) o[j] = (uint16_t)f32_to_bf16_bits(v[j]);
+        }
+      } else {
+        float* o = reinterpret_cast<float*>(p.out) + (size_t)row * p.N + col0;
+        if (col0 + 32 <= p.N) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<float4*>(o + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) o[j] = v[j];
+        }
+      }
+    }
+  }
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -267,86 +354,7 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
-        tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (col0 >= p.N) continue;
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (p.has_bias) {
-          if (col0 + 32 <= p.N) {
-            if (p.bias_dt == kBF16) {
-              const uint4* bp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + col0);
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                float b8[8];
-                unpack8(__ldg(bp + q), kBF16, b8);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[q * 8 + j] = __fadd_rn(v[q * 8 + j], b8[j]);
-              }
-            } else {
-              const float4* bp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + col0);
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                const float4 b = __ldg(bp + q);
-                v[q * 4 + 0] = __fadd_rn(v[q * 4 + 0], b.x);
-                v[q * 4 + 1] = __fadd_rn(v[q * 4 + 1], b.y);
-                v[q * 4 + 2] = __fadd_rn(v[q * 4 + 2], b.z);
-                v[q * 4 + 3] = __fadd_rn(v[q * 4 + 3], b.w);
-              }
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (col0 + j < p.N) {
-                const float b = p.bias_dt == kBF16
-                                    ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(p.bias)[col0 + j])
-                                    : reinterpret_cast<const float*>(p.bias)[col0 + j];
-                v[j] = __fadd_rn(v[j], b);
-              }
-            }
-          }
-        }
-        if (p.relu) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
-        }
-        if (row < p.M) {
-          if (p.out_dt == kBF16) {
-            uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + (size_t)row * p.N + col0;
-            if (col0 + 32 <= p.N) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                uint4 w;
-                w.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-                w.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-                w.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-                w.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-                *reinterpret_cast<uint4*>(o + q * 8) = w;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) o[j] = (uint16_t)f32_to_bf16_bits(v[j]);
-            }
-          } else {
-            float* o = reinterpret_cast<float*>(p.out) + (size_t)row * p.N + col0;
-            if (col0 + 32 <= p.N) {
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                *reinterpret_cast<float4*>(o + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) o[j] = v[j];
-            }
-          }
-        }
-      }
+      epilogue_tile(p, taddr, row, n0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[acc]));
@@ -363,6 +371,235 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
     __syncwarp();
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ CTA-pair variant
+// Two CTAs of a cluster (two SMs) work on one 256x256 tile: each loads its own 128 rows of A and its own 128
+// columns of B, the pair's leader issues tcgen05.mma.cta_group::2 (M=256, N=256, K=16) that reads both CTAs'
+// shared memory, and each CTA's TMEM receives its 128 rows of the accumulator.  Per CTA a stage is 32 KiB
+// instead of 48, so the ring is 6 deep, and B is fetched from L2 once per pair.  Every CTA issues its own plain
+// tensor-map copies; only the MMA-completion signal (tcgen05.commit) is delivered to both CTAs' barriers.
+constexpr int STAGES2 = 6;
+constexpr int B2_BYTES = (BN / 2) * BK * 2;             // this CTA's half of B: 16 KiB
+constexpr int STAGE2_BYTES = A_BYTES + B2_BYTES;        // 32 KiB
+constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + 512;
+constexpr uint32_t kPeerMask = 0xFEFFFFFFu;             // shared::cluster address of the same offset in the pair's leader
+
+struct Bars2 {
+  uint64_t full[STAGES2];    // leader's copy is the one in use: both CTAs' loads complete on it
+  uint64_t empty[STAGES2];   // per CTA: the leader's commit signals both CTAs
+  uint64_t tmem_full[2];     // per CTA: same
+  uint64_t tmem_empty[2];    // leader's copy in use: 8 arrivals (4 epilogue warps x 2 CTAs)
+  uint64_t drain;
+  uint32_t tmem_base;
+  uint32_t abort;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives on the barrier at this offset in BOTH CTAs of the pair once the MMAs issued so far have completed
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"(mask)
+               : "memory");
+}
+// same completion signal, delivered to the issuing CTA's barrier only
+__device__ __forceinline__ void umma_commit_pair_local(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// arrive on the barrier at the same shared-memory offset in CTA `target_rank` of the cluster
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t local_addr, uint32_t target_rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(target_rank));
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+matmul_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                                const MatmulDev p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  Bars2* bars = reinterpret_cast<Bars2*>(smem + STAGES2 * STAGE2_BYTES);
+  volatile uint32_t* abort_flag = &bars->abort;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) {
+      mbar_init(smem_u32(&bars->full[s]), 1);
+      mbar_init(smem_u32(&bars->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&bars->tmem_full[a]), 1);
+      mbar_init(smem_u32(&bars->tmem_empty[a]), 8);
+    }
+    mbar_init(smem_u32(&bars->drain), 1);
+    bars->abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {  // both CTAs of the pair execute the paired allocation
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  const int num_m = (p.M + 2 * BM - 1) / (2 * BM), num_n = (p.N + BN - 1) / BN;  // 256 x 256 tiles
+  const int num_tiles = num_m * num_n;
+  const int num_k = (p.K + BK - 1) / BK;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ TMA producer (both CTAs)
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        int mt, nt;
+        tile_coords(tile, num_m, num_n, &mt, &nt);
+        const int m0 = mt * 2 * BM + (int)rank * BM, n0 = nt * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full_leader = smem_u32(&bars->full[stage]) & kPeerMask;
+          const uint32_t sa = base + stage * STAGE2_BYTES, sb = sa + A_BYTES;
+          if (leader) mbar_expect_tx(smem_u32(&bars->full[stage]), 2 * STAGE2_BYTES);
+          tma_load_2d_pair(sa, &tmA, full_leader, kb * BK, m0);
+          if (p.transpose_b) {
+            tma_load_2d_pair(sb, &tmB, full_leader, kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < (BN / 2) / B_BOX_N; ++j)
+              tma_load_2d_pair(sb + j * B_BOX_BYTES, &tmB, full_leader, n0 + j * B_BOX_N, kb * BK);
+          }
+          if (++stage == STAGES2) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicOr(p.err, 1u);
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);  // bounded grace period for copies already issued
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      // ------------------------------------------------------------ MMA issuer (leader CTA only)
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((p.transpose_b ? 0u : 1u) << 16) |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        if (!mbar_wait(smem_u32(&bars->tmem_empty[acc]), acc_phase ^ 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)acc * BN;
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = base + stage * STAGE2_BYTES, sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = make_desc(sa + k * 32, 16, 1024);
+            const uint64_t bdesc = p.transpose_b ? make_desc(sb + k * 32, 16, 1024)
+                                                 : make_desc(sb + k * 2048, p.b_lbo, p.b_sbo);
+            umma_f16_pair(tmem_d, adesc, bdesc, idesc, (kb | k) != 0);
+          }
+          umma_commit_pair(smem_u32(&bars->empty[stage]));  // frees the stage in both CTAs
+          if (++stage == STAGES2) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(smem_u32(&bars->tmem_full[acc]));  // both CTAs' epilogues may read their halves
+        if ((acc ^= 1) == 0) acc_phase ^= 1u;
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicOr(p.err, 2u);
+      }
+      umma_commit_pair_local(smem_u32(&bars->drain));
+      mbar_wait(smem_u32(&bars->drain), 0, nullptr);
+    }
+  } else {
+    // -------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      int mt, nt;
+      tile_coords(tile, num_m, num_n, &mt, &nt);
+      const int row = mt * 2 * BM + (int)rank * BM + quarter * 32 + lane;
+      const int n0 = nt * BN;
+      if (!mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_phase, abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * BN;
+      epilogue_tile(p, taddr, row, n0);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(smem_u32(&bars->tmem_empty[acc]), 0);
+      if ((acc ^= 1) == 0) acc_phase ^= 1u;
+    }
+    if (!ok && lane == 0) {
+      *abort_flag = 1;
+      atomicOr(p.err, 4u);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA releases TMEM or exits while its peer may still use it
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -443,6 +680,28 @@ cudaError_t matmul_bf16(const MatmulParams& p, const void* A, const void* B, con
   // N-major B tile: 64-element N atoms are one TMA box (8 KiB) apart, 8-row K groups 1 KiB apart
   d.b_lbo = B_BOX_BYTES;
   d.b_sbo = 1024;
+  // two-CTA tiles whenever there is more than one 128-row block and the device has SM pairs to run them
+  if (p.M > BM && sm_count >= 2) {
+    static std::once_flag once2;
+    static cudaError_t attr_err2 = cudaSuccess;
+    std::call_once(once2, [] {
+      attr_err2 = cudaFuncSetAttribute(matmul_bf16_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       SMEM2_BYTES);
+    });
+    if (attr_err2 != cudaSuccess) return attr_err2;
+    // the pair kernel's B tile per CTA is 128 columns: re-encode B with the narrower box for the K-major case
+    CUtensorMap tmB2 = tmB;
+    if (p.transpose_b && !encode_2d(&tmB2, B, (uint64_t)p.K, (uint64_t)p.N, BK, BN / 2)) return cudaErrorInvalidValue;
+    const int64_t tiles2 = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN);
+    const int grid2 = 2 * (int)std::min<int64_t>(tiles2, sm_count / 2);
+    if (dims) {
+      dims->grid[0] = grid2;
+      dims->block[0] = THREADS;
+      dims->smem = SMEM2_BYTES;
+    }
+    matmul_bf16_tcgen05_pair_kernel<<<grid2, THREADS, SMEM2_BYTES, s>>>(tmA, tmB2, d);
+    return cudaGetLastError();
+  }
   const int64_t tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = (int)std::min<int64_t>(tiles, sm_count);
   if (dims) {
