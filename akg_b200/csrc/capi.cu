@@ -155,7 +155,9 @@ akgb_status run_plan(akgb_kernel* k, void* const* tensors, void* ws, cudaStream_
         e = transpose_nd(st.tp, a, o, s, &st.dims);
         break;
       case StepK::Matmul:
-        e = matmul_bf16(st.mm, a, b, c, o, ds.err_word, k->sm_count, s, &st.dims);
+        for (int64_t bi = 0; bi < st.mm_batch && e == cudaSuccess; ++bi)
+          e = matmul_bf16(st.mm, (const char*)a + bi * st.mm_stride_a, (const char*)b + bi * st.mm_stride_b, c,
+                          (char*)o + bi * st.mm_stride_o, ds.err_word, k->sm_count, s, &st.dims);
         break;
     }
     if (e != cudaSuccess) return cuda_fail(e, st.kernel_name.c_str());
@@ -175,6 +177,9 @@ int launches_of(const akgb_kernel* k) {
         break;
       case StepK::GeluChain:
         n += (st.gelu.n % 8) ? 2 : 1;
+        break;
+      case StepK::Matmul:
+        n += (int)st.mm_batch;
         break;
       default:
         n += 1;

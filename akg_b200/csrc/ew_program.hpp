@@ -40,7 +40,9 @@ struct EwOperand {
   int32_t reg;         // register loaded from / stored to
   int32_t pad;
   int64_t mod;         // EWI_MOD: index = e % mod
+  int64_t offset;      // EWI_STRIDED: first element (Slice / StridedSlice begin, Concat position)
   int64_t stride[kEwMaxRank];  // EWI_STRIDED: element stride per iteration dim (0 = broadcast)
+  int64_t wrap[kEwMaxRank];    // EWI_STRIDED: if non-zero the dim's index is taken modulo this (Tile)
 };
 
 struct EwProgram {

@@ -63,7 +63,9 @@ const OpEntry kOps[] = {
     {"ReduceMax", OpK::ReduceMax}, {"ReduceMin", OpK::ReduceMin}, {"ReducePrd", OpK::ReduceProd},
     {"ReduceProd", OpK::ReduceProd}, {"ReduceAll", OpK::ReduceAll}, {"ReduceAny", OpK::ReduceAny},
     {"ElemAny", OpK::ReduceAny}, {"MatMul", OpK::MatMul},     {"BatchMatMul", OpK::BatchMatMul},
-    {"Assign", OpK::Assign},     {"InplaceAssign", OpK::Assign},
+    {"Assign", OpK::Assign},     {"InplaceAssign", OpK::Assign}, {"AddN", OpK::AddN},
+    {"Tile", OpK::Tile},         {"Slice", OpK::Slice},       {"StridedSlice", OpK::StridedSlice},
+    {"Concat", OpK::Concat},
 };
 }  // namespace
 
@@ -75,7 +77,7 @@ const char* opk_name(OpK k) {
 bool opk_is_unary(OpK k) { return (int)k >= (int)OpK::Abs && (int)k <= (int)OpK::Cast; }
 bool opk_is_binary(OpK k) { return (int)k >= (int)OpK::Add && (int)k <= (int)OpK::LogicalOr; }
 bool opk_is_reduce(OpK k) { return (int)k >= (int)OpK::ReduceSum && (int)k <= (int)OpK::ReduceAny; }
-bool opk_is_elementwise(OpK k) { return opk_is_unary(k) || opk_is_binary(k) || k == OpK::Select; }
+bool opk_is_elementwise(OpK k) { return opk_is_unary(k) || opk_is_binary(k) || k == OpK::Select || k == OpK::AddN; }
 
 namespace {
 
@@ -180,9 +182,20 @@ Graph parse_info(const char* text, size_t len) {
     if (const Json* fo = find_attr(attrs, "fake_output"))
       if (fo->is_bool() && fo->b) throw Unsupported("fake_output aliasing is not supported");
 
-    for (size_t j = 0; j < ins.size(); ++j) {
-      const Json& d = ins[j].is_array() ? ins[j][0] : ins[j];
-      if (j == 1 && attr_as_second_input(n.name)) continue;  // attribute operand, read below
+    // Concat and AddN list all their tensors inside the first input entry
+    // (TranslateToMindsporeDialect.cpp:719-727, :766-783); StridedSlice may carry begin/end/strides as inputs 1..3
+    std::vector<const Json*> operand_descs;
+    if ((n.kind == OpK::Concat || n.kind == OpK::AddN) && ins[0].is_array()) {
+      for (auto& e : ins[0].arr) operand_descs.push_back(&e);
+    } else {
+      for (size_t j = 0; j < ins.size(); ++j) {
+        if (j == 1 && attr_as_second_input(n.name)) continue;  // attribute operand, read below
+        if (j >= 1 && n.kind == OpK::StridedSlice) continue;
+        operand_descs.push_back(ins[j].is_array() ? &ins[j][0] : &ins[j]);
+      }
+    }
+    for (const Json* dp : operand_descs) {
+      const Json& d = *dp;
       const std::string& tn = d.at("tensor_name").as_string();
       auto it = by_name.find(tn);
       bool has_value = d.contains("value") && !d.at("value").is_null();
@@ -264,6 +277,68 @@ Graph parse_info(const char* text, size_t len) {
       const Json* tb = find_attr(attrs, "transpose_b");
       n.transpose_a = ta ? ta->as_bool() : false;
       n.transpose_b = tb ? tb->as_bool() : false;
+    } else if (n.kind == OpK::Tile) {
+      // multiples from the second operand or the attribute (:1151-1160)
+      if (ins.size() == 2) {
+        const Json& d1 = ins[1].is_array() ? ins[1][0] : ins[1];
+        n.multiples = d1.at("value").as_int_list();
+      } else if (const Json* m = find_attr(attrs, "multiples")) {
+        n.multiples = m->as_int_list();
+      } else {
+        throw JsonError("Tile has no multiples");
+      }
+    } else if (n.kind == OpK::Slice) {
+      const Json* b = find_attr(attrs, "begin");
+      const Json* sz = find_attr(attrs, "size");
+      if (!b || !sz) throw JsonError("Slice needs begin and size");
+      n.begin = b->as_int_list();
+      n.size = sz->as_int_list();
+    } else if (n.kind == OpK::StridedSlice) {
+      // begin/end/strides from attributes or inputs 1..3 (:1037-1049); negative ends wrap (:1051-1055)
+      auto from = [&](const char* attr_name, size_t idx) {
+        if (ins.size() == 1) {
+          const Json* a = find_attr(attrs, attr_name);
+          if (!a) throw JsonError(std::string("StridedSlice needs ") + attr_name);
+          return a->as_int_list();
+        }
+        if (ins.size() <= idx) throw JsonError("StridedSlice needs begin, end and strides");
+        const Json& d = ins[idx].is_array() ? ins[idx][0] : ins[idx];
+        return d.at("value").as_int_list();
+      };
+      n.begin = from("begin", 1);
+      n.end = from("end", 2);
+      n.strides = from("strides", 3);
+      for (const char* mk : {"ellipsis_mask", "new_axis_mask", "shrink_axis_mask", "ellipsisMask", "newAxisMask",
+                             "shrinkAxisMask"}) {
+        const Json* m = find_attr(attrs, mk);
+        if (m && m->as_int() != 0) throw Unsupported("StridedSlice with ellipsis/new-axis/shrink masks");
+      }
+      auto mask_of = [&](const char* a, const char* b2) {
+        const Json* m = find_attr(attrs, a);
+        if (!m) m = find_attr(attrs, b2);
+        return m ? m->as_int() : (int64_t)0;
+      };
+      const int64_t bm = mask_of("begin_mask", "beginMask"), em = mask_of("end_mask", "endMask");
+      const std::vector<int64_t> xs = shape_of(in0);
+      if (n.begin.size() > xs.size() || n.end.size() != n.begin.size() || n.strides.size() != n.begin.size())
+        throw JsonError("StridedSlice begin/end/strides disagree");
+      for (size_t i = 0; i < n.begin.size(); ++i) {
+        if (n.strides[i] <= 0) throw Unsupported("StridedSlice with non-positive strides");
+        if (n.begin[i] < 0) n.begin[i] += xs[i];
+        if (n.end[i] < 0) n.end[i] += xs[i];
+        if ((bm >> i) & 1) n.begin[i] = 0;
+        if ((em >> i) & 1) n.end[i] = xs[i];
+        n.end[i] = std::min(n.end[i], xs[i]);
+      }
+      for (size_t i = n.begin.size(); i < xs.size(); ++i) {
+        n.begin.push_back(0);
+        n.end.push_back(xs[i]);
+        n.strides.push_back(1);
+      }
+    } else if (n.kind == OpK::Concat) {
+      const Json* a = find_attr(attrs, "axis");
+      n.axis = a ? a->as_int() : 0;
+      if (n.axis < 0) n.axis += in_rank;
     }
     by_name[g.values[out_id].name] = out_id;
     for (int vid : n.in) g.values[vid].users.push_back((int)g.nodes.size());
@@ -304,8 +379,8 @@ void classify(Graph& g) {
       for (int vid : n.in)
         if (g.v(vid).shape != g.v(n.out).shape) same = false;
       oc = same ? OpClass::Elementwise : OpClass::Broadcast;
-    } else if (n.kind == OpK::BroadcastTo) {
-      oc = OpClass::Broadcast;
+    } else if (n.kind == OpK::BroadcastTo || n.kind == OpK::Tile) {
+      oc = OpClass::Broadcast;  // tosa.tile counts as Broadcast (OperatorIdentify.cpp:61-62)
     } else if (n.kind == OpK::Reshape) {
       oc = OpClass::Reshape;
     } else if (n.kind == OpK::Transpose) {

@@ -39,8 +39,10 @@ enum class OpK : int {
   LogicalAnd, LogicalOr,
   // ternary
   Select,
+  // n-ary elementwise
+  AddN,
   // shape
-  BroadcastTo, Reshape, Transpose,
+  BroadcastTo, Reshape, Transpose, Tile, Slice, StridedSlice, Concat,
   // reductions
   ReduceSum, ReduceMax, ReduceMin, ReduceProd, ReduceAll, ReduceAny,
   // contractions
@@ -94,6 +96,9 @@ struct Node {
   bool keep_dims = false;
   std::vector<int64_t> perm; // transpose
   bool transpose_a = false, transpose_b = false;
+  // Tile: multiples; Slice: begin/size; StridedSlice: begin/end/strides (masks already applied); Concat: axis
+  std::vector<int64_t> multiples, begin, size, end, strides;
+  int64_t axis = 0;
   bool enable_atomic_add = false;
 };
 

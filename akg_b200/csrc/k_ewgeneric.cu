@@ -64,10 +64,12 @@ __device__ __forceinline__ int64_t operand_index(const EwProgram& P, const EwOpe
   if (o.kind == EWI_FULL) return e;
   if (o.kind == EWI_SCALAR) return 0;
   if (o.kind == EWI_MOD) return e % o.mod;
-  int64_t rem = e, idx = 0;
+  int64_t rem = e, idx = o.offset;
   for (int d = P.rank - 1; d >= 0; --d) {
     const int64_t q = rem / P.shape[d];
-    idx += (rem - q * P.shape[d]) * o.stride[d];
+    int64_t i = rem - q * P.shape[d];
+    if (o.wrap[d]) i %= o.wrap[d];
+    idx += i * o.stride[d];
     rem = q;
   }
   return idx;
@@ -208,7 +210,7 @@ __global__ void __launch_bounds__(kEwThreads) ew_generic_kernel(const __grid_con
 #pragma unroll
     for (int v = 0; v < kEwVec; ++v) {
       const int64_t e = base + (int64_t)v * kEwThreads;
-      if (e < P.n) store_elem(ptrs.out[i], e, o.dt, EW_R(o.reg, v));
+      if (e < P.n) store_elem(ptrs.out[i], operand_index(P, o, e), o.dt, EW_R(o.reg, v));
     }
   }
 #undef EW_R

@@ -34,6 +34,7 @@ struct Step {
   MatmulParams mm;
   EwProgram ew;              // StepK::Ew
   std::vector<Ref> ew_in, ew_out;
+  int64_t mm_batch = 1, mm_stride_a = 0, mm_stride_b = 0, mm_stride_o = 0;  // BatchMatMul: byte strides per entry
   int64_t red_batch_in = 0, red_batch_out = 0;  // batched column reductions: element stride per outer index
   LaunchDims dims;          // filled at first launch
 };

@@ -231,9 +231,12 @@ struct Builder {
       ++P.n_in;
       return r;
     };
-    for (size_t gi = 0; gi < group.size(); ++gi)  // all outside operands first
-      for (int vid : g.nodes[group[gi]].in)
+    for (size_t gi = 0; gi < group.size(); ++gi) {  // all outside operands first
+      const Node& gn = g.nodes[group[gi]];
+      if (gn.kind == OpK::Tile || gn.kind == OpK::Slice || gn.kind == OpK::StridedSlice) continue;
+      for (int vid : gn.in)
         if (!produced_in_group(vid)) operand_reg(vid);
+    }
     for (size_t gi = 0; gi < group.size(); ++gi) {
       const Node& n = g.nodes[group[gi]];
       const Value& out = g.v(n.out);
@@ -241,8 +244,87 @@ struct Builder {
       EwInstr ins;
       std::memset(&ins, 0, sizeof(ins));
       EwOp op;
-      if (n.kind == OpK::Reshape) op = EW_COPY;
+      const bool view_copy = n.kind == OpK::Tile || n.kind == OpK::Slice || n.kind == OpK::StridedSlice;
+      if (n.kind == OpK::Reshape || view_copy) op = EW_COPY;
+      else if (n.kind == OpK::AddN) op = EW_ADD;
       else if (!ew_opcode(n.kind, &op)) throw Unsupported(std::string("op '") + n.name + "' in an elementwise group");
+      if (view_copy) {
+        // the source is read through its own index map: a dedicated operand and register
+        const Value& src = g.v(n.in[0]);
+        if (!ew_dtype_ok(src.dt)) throw Unsupported(std::string("generic elementwise kernel: type ") + dt_name(src.dt));
+        if (P.n_in >= kEwMaxIn) throw Unsupported("elementwise group with more than 10 tensor operands");
+        if (next_reg >= kEwMaxReg) throw Unsupported("elementwise group needs more than 48 live values");
+        if (src.shape.size() != S.size()) throw Unsupported(std::string(n.name) + " that changes the rank");
+        EwOperand& o = P.in[P.n_in++];
+        o.dt = (int)src.dt;
+        o.kind = EWI_STRIDED;
+        o.reg = next_reg++;
+        int64_t stride = 1;
+        for (int d = (int)S.size() - 1; d >= 0; --d) {
+          if (n.kind == OpK::Tile) {
+            o.stride[d] = stride;
+            o.wrap[d] = src.shape[d];
+          } else if (n.kind == OpK::Slice) {
+            o.stride[d] = stride;
+            o.offset += n.begin[d] * stride;
+          } else {
+            o.stride[d] = stride * n.strides[d];
+            o.offset += n.begin[d] * stride;
+          }
+          stride *= src.shape[d];
+        }
+        st.ew_in.push_back(buffer(n.in[0]));
+        EwInstr ins;
+        std::memset(&ins, 0, sizeof(ins));
+        ins.op = EW_COPY;
+        ins.dt = (uint8_t)out.dt;
+        ins.cls = cls_of(out.dt);
+        ins.src_cls = cls_of(src.dt);
+        ins.a = (uint8_t)o.reg;
+        const int dst = alloc_reg();
+        reg_of[n.out] = dst;
+        ins.dst = (uint8_t)dst;
+        if (P.n_instr >= kEwMaxInstr) throw Unsupported("elementwise group with more than 96 ops");
+        P.instr[P.n_instr++] = ins;
+        if (used_outside_group(n.out)) {
+          if (P.n_out >= kEwMaxOut) throw Unsupported("elementwise group with more than 6 results");
+          EwOperand& oo = P.out[P.n_out++];
+          oo.dt = (int)out.dt;
+          oo.kind = EWI_FULL;
+          oo.reg = dst;
+          st.ew_out.push_back(buffer(n.out));
+        }
+        continue;
+      }
+      if (n.kind == OpK::AddN && n.in.size() > 2) {
+        // a left-to-right chain of adds in the result type, like the expected-value generator's "a + b + c"
+        int acc = operand_reg(n.in[0]);
+        for (size_t j = 1; j < n.in.size(); ++j) {
+          EwInstr a2;
+          std::memset(&a2, 0, sizeof(a2));
+          a2.op = EW_ADD;
+          a2.dt = (uint8_t)out.dt;
+          a2.cls = cls_of(out.dt);
+          a2.src_cls = a2.cls;
+          a2.a = (uint8_t)acc;
+          a2.b = (uint8_t)operand_reg(n.in[j]);
+          const int dst = alloc_reg();
+          a2.dst = (uint8_t)dst;
+          if (P.n_instr >= kEwMaxInstr) throw Unsupported("elementwise group with more than 96 ops");
+          P.instr[P.n_instr++] = a2;
+          acc = dst;
+        }
+        reg_of[n.out] = acc;
+        if (used_outside_group(n.out)) {
+          if (P.n_out >= kEwMaxOut) throw Unsupported("elementwise group with more than 6 results");
+          EwOperand& oo = P.out[P.n_out++];
+          oo.dt = (int)out.dt;
+          oo.kind = EWI_FULL;
+          oo.reg = acc;
+          st.ew_out.push_back(buffer(n.out));
+        }
+        continue;
+      }
       ins.op = op;
       ins.dt = (uint8_t)out.dt;
       ins.cls = cls_of(out.dt);
@@ -380,8 +462,50 @@ struct Builder {
     plan.steps.push_back(std::move(st));
   }
 
+  // Concat: one copy launch per input, each writing its slab of the output
+  void add_concat(const Node& n) {
+    const Value& out = g.v(n.out);
+    if (!ew_dtype_ok(out.dt)) throw Unsupported(std::string("generic elementwise kernel: type ") + dt_name(out.dt));
+    const size_t R = out.shape.size();
+    if (R > (size_t)kEwMaxRank || n.axis < 0 || n.axis >= (int64_t)R) throw Unsupported("Concat rank/axis");
+    std::vector<int64_t> ostride(R, 1);
+    for (int d = (int)R - 2; d >= 0; --d) ostride[d] = ostride[d + 1] * out.shape[d + 1];
+    int64_t pos = 0;
+    for (int vid : n.in) {
+      const Value& x = g.v(vid);
+      if (x.shape.size() != R || x.dt != out.dt) throw Unsupported("Concat operands must share rank and type");
+      Step st;
+      st.kind = StepK::Ew;
+      st.kernel_name = "ew_generic";
+      EwProgram& P = st.ew;
+      std::memset(&P, 0, sizeof(P));
+      P.rank = (int)R;
+      P.n = x.numel();
+      for (size_t d = 0; d < R; ++d) P.shape[d] = x.shape[d];
+      P.n_in = 1;
+      P.in[0].dt = (int)x.dt;
+      P.in[0].kind = EWI_FULL;
+      P.in[0].reg = 0;
+      P.n_out = 1;
+      P.out[0].dt = (int)out.dt;
+      P.out[0].kind = EWI_STRIDED;
+      P.out[0].reg = 0;
+      P.out[0].offset = pos * ostride[n.axis];
+      for (size_t d = 0; d < R; ++d) P.out[0].stride[d] = ostride[d];
+      P.n_reg = 1;
+      st.ew_in.push_back(buffer(vid));
+      st.ew_out.push_back(buffer(n.out));
+      plan.steps.push_back(std::move(st));
+      pos += x.shape[n.axis];
+    }
+    if (pos != out.shape[n.axis]) throw JsonError("Concat extents do not add up to the output");
+  }
+
   void add_matmul(const Node& n) {
-    if (n.kind != OpK::MatMul) throw Unsupported("BatchMatMul is not placed");
+    if (n.kind == OpK::BatchMatMul) {
+      add_batch_matmul(n);
+      return;
+    }
     if (n.transpose_a) throw Unsupported("MatMul with transpose_a is rejected (as by the reference lowering)");
     const Value& a = g.v(n.in[0]);
     const Value& b = g.v(n.in[1]);
@@ -433,12 +557,61 @@ struct Builder {
     }
   }
 
+  // BatchMatMul: the 2-D kernel once per batch entry (leading dims of both operands must agree, or the right
+  // operand may be 2-D and shared)
+  void add_batch_matmul(const Node& n) {
+    if (n.transpose_a) throw Unsupported("BatchMatMul with transpose_a is rejected (as by the reference lowering)");
+    const Value& a = g.v(n.in[0]);
+    const Value& b = g.v(n.in[1]);
+    const Value& o = g.v(n.out);
+    if (a.dt != DT::BF16 || b.dt != DT::BF16 || a.shape.size() < 2 || b.shape.size() < 2)
+      throw Unsupported("only bfloat16 BatchMatMul is placed");
+    if (o.dt != DT::F32 && o.dt != DT::BF16) throw Unsupported("BatchMatMul result type");
+    const size_t ra = a.shape.size(), rb = b.shape.size();
+    int64_t batch = 1;
+    for (size_t i = 0; i + 2 < ra; ++i) batch *= a.shape[i];
+    int64_t bbatch = 1;
+    for (size_t i = 0; i + 2 < rb; ++i) bbatch *= b.shape[i];
+    if (bbatch != batch && bbatch != 1) throw Unsupported("BatchMatMul operands with different batch extents");
+    if (batch > 4096) throw Unsupported("BatchMatMul with more than 4096 batch entries");
+    MatmulParams p;
+    p.M = a.shape[ra - 2];
+    p.K = a.shape[ra - 1];
+    p.transpose_b = n.transpose_b;
+    p.N = n.transpose_b ? b.shape[rb - 2] : b.shape[rb - 1];
+    p.out_dt = (int)o.dt;
+    p.bias_dt = (int)DT::F32;
+    const char* why = nullptr;
+    if (!matmul_bf16_supported(p, &why)) throw Unsupported(std::string("matmul shape not placed: ") + why);
+    if ((p.M * p.K) % 8 || (p.K * p.N) % 8 || (p.M * p.N) % 8) throw Unsupported("BatchMatMul slices must stay 16-byte aligned");
+    Step st;
+    st.kind = StepK::Matmul;
+    st.kernel_name = "matmul_bf16_tcgen05";
+    st.a = buffer(n.in[0]);
+    st.b = buffer(n.in[1]);
+    st.out = buffer(n.out);
+    st.mm = p;
+    st.mm_batch = batch;
+    st.mm_stride_a = p.M * p.K * 2;
+    st.mm_stride_b = bbatch == 1 ? 0 : p.K * p.N * 2;
+    st.mm_stride_o = p.M * p.N * (int64_t)dt_size(o.dt);
+    plan.flops += 2 * p.M * p.N * p.K * batch;
+    plan.steps.push_back(std::move(st));
+  }
+
   Plan run() {
     plan_reshapes();
     for (size_t i = 0; i < g.nodes.size(); ++i) {
       const Node& n = g.nodes[i];
       if (n.kind == OpK::Reshape && !reshape_copy.count((int)i)) continue;  // a view
-      if (opk_is_elementwise(n.kind) || n.kind == OpK::BroadcastTo || n.kind == OpK::Reshape) {
+      const bool view_copy = n.kind == OpK::Tile || n.kind == OpK::Slice || n.kind == OpK::StridedSlice;
+      if (view_copy && produced_in_group(n.in[0])) flush_group();  // the source is read from memory
+      if (n.kind == OpK::Concat) {
+        flush_group();
+        add_concat(n);
+        continue;
+      }
+      if (opk_is_elementwise(n.kind) || n.kind == OpK::BroadcastTo || n.kind == OpK::Reshape || view_copy) {
         const std::vector<int64_t>& S = g.v(n.out).shape;
         if (!group.empty() && group_shape != S) flush_group();
         // an operand that views a value still being computed in the open group must be materialised first

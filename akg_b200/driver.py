@@ -163,6 +163,13 @@ def compile_info(info_json, **kw) -> FusedKernel:
     return FusedKernel(info_json, **kw)
 
 
+def get_kernel_meta_path() -> str:
+    """Directory of the kernel metadata files, resolved from the same environment variables as the reference
+    (``KERNEL_META_DIR``, ``MS_COMPILER_CACHE_PATH``; ``akg-mlir/python/akg_mlir/mlir_driver.py:47-53``)."""
+    kernel_meta_dir = os.getenv("KERNEL_META_DIR", default=os.path.expanduser("~/.akg"))
+    return os.path.join(os.path.realpath(os.getenv("MS_COMPILER_CACHE_PATH", "")), kernel_meta_dir)
+
+
 class MlirDriver:
     """Drop-in for the GPU branch of the reference's ``MlirDriver``."""
 
@@ -174,7 +181,7 @@ class MlirDriver:
             raise RuntimeError("dynamic shapes are not supported")
         self.kernel_name = kernel_name
         self.input_file = input_file
-        self.output_dir = output_dir
+        self.output_dir = get_kernel_meta_path() if output_dir == "" else str(output_dir)
         self.profiling_trails = profiling_trails
         self.backend = backend
         self.device = device
@@ -185,10 +192,11 @@ class MlirDriver:
         with open(self.input_file, "r", encoding="utf-8") as f:
             text = f.read()
         self.kernel = FusedKernel(text, device=self.device)
-        if self.output_dir:
-            os.makedirs(self.output_dir, exist_ok=True)
-            with open(os.path.join(self.output_dir, self.kernel_name + ".json"), "w", encoding="utf-8") as f:
-                json.dump(self.kernel.meta(), f)
+        # <kernel>.json beside where the reference writes <kernel>.ptx/.json: launch dims, kernelName, sha256 ...
+        # (the launch dims are those of the planned template and are refined at the first launch)
+        os.makedirs(self.output_dir, exist_ok=True)
+        with open(os.path.join(self.output_dir, self.kernel_name + ".json"), "w", encoding="utf-8") as f:
+            json.dump(self.kernel.meta(), f)
 
     def run(self, input_for_mod, output_indexes=None):
         if self.kernel is None:

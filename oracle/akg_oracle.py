@@ -163,6 +163,8 @@ def evaluate(desc: dict | str, inputs: Sequence[np.ndarray], accum: str = "numpy
     for op in desc["op_desc"]:
         name = op["name"]
         ins = [i[0] for i in op["input_desc"]]
+        if name in ("Concat", "AddN"):  # all tensors sit in the first input entry (op_dsl.py:197-207, :901-907)
+            ins = list(op["input_desc"][0])
         out = op["output_desc"][0]
         odt = np_dtype(out["data_type"])
         oshape = out.get("shape") or [1]
@@ -218,6 +220,38 @@ def evaluate(desc: dict | str, inputs: Sequence[np.ndarray], accum: str = "numpy
                 axes = tuple(sorted({a + x.ndim if a < 0 else a for a in axes}))
                 keep = bool(_attr(attrs, "keep_dims", False))
                 r = _reduce(_REDUCE[name], x, axes, keep, accum)
+            elif name == "AddN":
+                r = operand(ins[0])
+                for other in ins[1:]:
+                    r = np.add(r, operand(other)).astype(odt)  # "a + b + c", left to right (op_dsl.py:901-907)
+            elif name == "Tile":
+                mult = _attr(attrs, "multiples")
+                if mult is None and len(op["input_desc"]) == 2:
+                    mult = op["input_desc"][1][0]["value"]
+                r = np.tile(operand(ins[0]), mult)  # op_dsl.py:910-915
+            elif name == "Slice":
+                begin, size = _attr(attrs, "begin"), _attr(attrs, "size")
+                r = operand(ins[0])[tuple(slice(b, b + s) for b, s in zip(begin, size))]  # op_dsl.py:397-413
+            elif name == "StridedSlice":
+                # masks other than begin/end are not evaluated here (the library rejects them)
+                def val(key, idx):
+                    v = _attr(attrs, key)
+                    if v:
+                        return list(v)
+                    v = op["input_desc"][idx][0]["value"]
+                    return list(v) if isinstance(v, (list, tuple)) else [v]
+                x = operand(ins[0])
+                begin, end, strides = val("begin", 1), val("end", 2), val("strides", 3)
+                bm = _attr(attrs, "begin_mask", 0) or 0
+                em = _attr(attrs, "end_mask", 0) or 0
+                sl = []
+                for i in range(len(begin)):
+                    b = None if (bm >> i) & 1 else begin[i]
+                    e = None if (em >> i) & 1 else end[i]
+                    sl.append(slice(b, e, strides[i]))  # op_dsl.py:340-394
+                r = x[tuple(sl)]
+            elif name == "Concat":
+                r = np.concatenate([operand(i) for i in ins], axis=_attr(attrs, "axis", 0))  # op_dsl.py:197-207
             elif name == "Reshape":
                 r = operand(ins[0])
             elif name == "BroadcastTo":

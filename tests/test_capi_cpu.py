@@ -133,3 +133,36 @@ def test_leading_axis_sharding_plans(lib):
         FusedKernel(descs.transpose([8, 16], [1, 0]), shard_rank=0, shard_world=2)
     with pytest.raises(UnsupportedError):  # 7 rows over 2 ranks
         FusedKernel(descs.layernorm(7, 100), shard_rank=0, shard_world=2)
+
+
+def test_mlir_driver_writes_kernel_meta_like_the_reference(lib, tmp_path, monkeypatch):
+    from akg_b200 import MlirDriver
+    from akg_b200.driver import get_kernel_meta_path
+    d = descs.reduce_sum_axis0(64, 32)
+    info = tmp_path / (d["op"] + ".info")
+    info.write_text(json.dumps(d))
+    monkeypatch.setenv("KERNEL_META_DIR", "akg_meta")
+    monkeypatch.setenv("MS_COMPILER_CACHE_PATH", str(tmp_path))
+    assert get_kernel_meta_path() == str(tmp_path / "akg_meta")
+    drv = MlirDriver(d["op"], str(info), backend="gpu")
+    drv.compile()
+    meta = json.loads((tmp_path / "akg_meta" / (d["op"] + ".json")).read_text())
+    assert meta["kernelName"] == d["op"] + "_kernel" and meta["is_dynamic"] is False and len(meta["sha256"]) == 64
+    with pytest.raises(RuntimeError):
+        MlirDriver(d["op"], str(info), backend="ascend")
+
+
+def test_generic_plan_splits_at_shape_changes(lib):
+    """Elementwise groups, reductions and data-movement ops become separate launches; Reshape is a view."""
+    from akg_b200.descs import _Builder, _attr, _reduce_attr
+    b = _Builder("Fused_Generic_30")
+    f = "float32"
+    x = b.input("x", [32, 64], f)
+    t = b.emit("Mul", [x, x], [32, 64], f)
+    r = b.emit("ReduceSum", [t], [32, 1], f, _reduce_attr([1], True))
+    u = b.emit("Sub", [x, r], [32, 64], f)
+    v = b.emit("Reshape", [u], [2048], f, [_attr("shape", "listInt", [2048])])
+    b.output(v)
+    k = FusedKernel(b.build())
+    assert k.launch_count == 3 and k.workspace_size > 0 and k.op_class == "reduce_x"
+    assert k.meta()["template"] == "ew_generic"

@@ -241,3 +241,64 @@ def test_float_to_int_cast_is_refused(lib):
     b.output(b.emit("Cast", [x], [16], "int32", [_attr("dst_type", "str", "int32")]))
     with pytest.raises(UnsupportedError):
         FusedKernel(b.build())
+
+
+def test_tile_slice_strided_slice_concat_addn(lib):
+    """Data-movement ops of the JSON factory (TranslateToMindsporeDialect.cpp:1037-1160): bit-exact copies."""
+    f = "float32"
+    # Tile then an elementwise op on the tiled value
+    b = _Builder("Fused_Tile_Div_20")
+    x = b.input("x", [3, 5], f)
+    y = b.input("y", [6, 15], f)
+    t = b.emit("Tile", [x], [6, 15], f, [_attr("multiples", "listInt", [2, 3])])
+    b.output(b.emit("RealDiv", [y, t], [6, 15], f))
+    d = b.build()
+    ins = make_inputs(d, 20)
+    ins[0] = np.abs(ins[0]) + np.float32(1)
+    check(d, ins, exact=True)
+    # Slice and StridedSlice of the same input, plus AddN of three tensors
+    b = _Builder("Fused_Slice_StridedSlice_AddN_21")
+    x = b.input("x", [8, 10, 12], "float16")
+    s1 = b.emit("Slice", [x], [4, 5, 6], "float16",
+                [_attr("begin", "listInt", [2, 1, 3]), _attr("size", "listInt", [4, 5, 6])])
+    s2 = b.emit("StridedSlice", [x], [4, 5, 6], "float16",
+                [_attr("begin", "listInt", [0, 0, 0]), _attr("end", "listInt", [8, 10, 12]),
+                 _attr("strides", "listInt", [2, 2, 2])])
+    s3 = b.emit("StridedSlice", [x], [4, 5, 6], "float16",
+                [_attr("begin", "listInt", [4, 5, 0]), _attr("end", "listInt", [8, -1, 6]),
+                 _attr("strides", "listInt", [1, 1, 1]), _attr("end_mask", "int", 2)])
+    node = {"name": "AddN", "attr": None, "impl_path": "", "input_desc": [[dict(s1), dict(s2), dict(s3)]],
+            "output_desc": [{"data_type": "float16", "format": "DefaultFormat", "shape": [4, 5, 6], "tensor_name": "sum3"}]}
+    b.ops.append(node)
+    b.outputs.append(dict(node["output_desc"][0]))
+    b.output(s2)
+    d = b.build()
+    check(d, make_inputs(d, 21), exact=True)
+    # Concat along the middle axis, then a cast
+    b = _Builder("Fused_Concat_Cast_22")
+    p_, q_, r_ = b.input("p", [4, 3, 16], f), b.input("q", [4, 5, 16], f), b.input("r", [4, 1, 16], f)
+    node = {"name": "Concat", "attr": [_attr("axis", "int", 1)], "impl_path": "",
+            "input_desc": [[dict(p_), dict(q_), dict(r_)]],
+            "output_desc": [{"data_type": f, "format": "DefaultFormat", "shape": [4, 9, 16], "tensor_name": "cat"}]}
+    b.ops.append(node)
+    cat = dict(node["output_desc"][0])
+    b.output(b.emit("Cast", [cat], [4, 9, 16], "float16", [_attr("dst_type", "str", "float16")]))
+    d = b.build()
+    check(d, make_inputs(d, 22), exact=True)
+
+
+def test_batch_matmul(lib):
+    bsz, m, k_, n = 3, 128, 64, 256
+    b = _Builder("Fused_BatchMatMul_23")
+    h = "bfloat16"
+    a = b.input("a", [bsz, m, k_], h)
+    w = b.input("w", [bsz, k_, n], h)
+    c = b.emit("BatchMatMul", [a, w], [bsz, m, n], "float32",
+               [_attr("transpose_a", "bool", False), _attr("transpose_b", "bool", False)])
+    b.output(c)
+    d = b.build()
+    ins = make_inputs(d, 23, {"a": "normal_small", "w": "normal_small"})
+    got, kern = run(d, ins)
+    want = O.evaluate(d, ins)[0]
+    np.testing.assert_allclose(got[0], want, rtol=2e-3, atol=1e-3 * float(np.abs(want).max()))
+    assert kern.launch_count == bsz
