@@ -32,6 +32,7 @@ DTYPE_NAMES = {0: "bool", 1: "int8", 2: "int16", 3: "int32", 4: "int64",
 SHARD_REPLICATED, SHARD_SPLIT_AXIS0, SHARD_PARTIAL_SUM, SHARD_PARTIAL_MAX, SHARD_PARTIAL_MIN, SHARD_PARTIAL_PROD = range(6)
 
 AKGB_MAX_RANK = 8
+AKGB_FLAG_NO_JIT = 1
 
 
 class TensorDesc(ctypes.Structure):
@@ -85,6 +86,8 @@ _SIGNATURES = [
     ("akgb_profile_host", ctypes.c_int, [_vp, ctypes.POINTER(_vp), ctypes.c_int32, ctypes.c_int32,
                                           ctypes.POINTER(ctypes.c_double)]),
     ("akgb_kernel_meta", ctypes.c_int, [_vp, ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t)]),
+    ("akgb_dump_jit_source", ctypes.c_int, [_vp, ctypes.c_int32, ctypes.c_char_p, ctypes.c_size_t,
+                                             ctypes.POINTER(ctypes.c_size_t)]),
     ("akgb_kernel_class", ctypes.c_char_p, [_vp]),
     ("akgb_kernel_bytes", ctypes.c_int64, [_vp]),
     ("akgb_kernel_flops", ctypes.c_int64, [_vp]),

@@ -58,6 +58,7 @@ struct akgb_kernel {
   int device = 0;
   int sm_count = 148;
   int shard_rank = 0, shard_world = 1;
+  bool no_jit = false;  // AKGB_FLAG_NO_JIT
   std::vector<akgb_tensor_desc> descs;
   int n_inputs = 0;
   // host-pointer entry points: staging buffers kept between calls
@@ -142,7 +143,7 @@ akgb_status run_plan(akgb_kernel* k, void* const* tensors, void* ws, cudaStream_
         void* outs[kEwMaxOut];
         for (size_t i = 0; i < st.ew_in.size(); ++i) ins[i] = resolve(st.ew_in[i], tensors, ws);
         for (size_t i = 0; i < st.ew_out.size(); ++i) outs[i] = resolve(st.ew_out[i], tensors, ws);
-        e = ew_generic(st.ew, ins, outs, s, &st.dims);
+        e = ew_generic(st.ew, ins, outs, !k->no_jit, s, &st.dims);
         break;
       }
       case StepK::ReduceAll:
@@ -310,12 +311,13 @@ const char* akgb_version(void) { return "akgb 0.1 (sm_100a)"; }
 akgb_status akgb_compile(const char* info_json, size_t len, const akgb_options* opt, akgb_kernel** out) {
   if (!info_json || !out) return fail(AKGB_INVALID_ARG, "null argument");
   *out = nullptr;
-  int device = -1, rank = 0, world = 1;
+  int device = -1, rank = 0, world = 1, flags = 0;
   if (opt) {
     if (opt->struct_size < (int32_t)sizeof(akgb_options)) return fail(AKGB_INVALID_ARG, "akgb_options.struct_size");
     device = opt->device;
     rank = opt->shard_rank;
     world = opt->shard_world <= 0 ? 1 : opt->shard_world;
+    flags = opt->flags;
   }
   if (device < 0) {
     if (cudaGetDevice(&device) != cudaSuccess) {
@@ -330,6 +332,7 @@ akgb_status akgb_compile(const char* info_json, size_t len, const akgb_options* 
     k->sm_count = query_sm_count(device);
     k->shard_rank = rank;
     k->shard_world = world;
+    k->no_jit = (flags & AKGB_FLAG_NO_JIT) != 0;
     k->json_text.assign(info_json, len);
     k->graph = parse_info(info_json, len);
     infer_sharding(k->graph, rank, world);
@@ -474,6 +477,21 @@ akgb_status akgb_check_device_error(akgb_kernel* k, uint32_t* word) {
     cudaMemset(ds.err_word, 0, sizeof(uint32_t));
     return fail(AKGB_DEVICE_TIMEOUT, "a bounded device-side wait gave up");
   }
+  return AKGB_OK;
+}
+
+akgb_status akgb_dump_jit_source(const akgb_kernel* k, int32_t vectorised, char* buf, size_t cap, size_t* needed) {
+  if (!k) return fail(AKGB_INVALID_ARG, "null argument");
+  std::string src;
+  for (const Step& st : k->plan.steps) {
+    if (st.kind != StepK::Ew) continue;
+    src = ew_jit_source(st.ew, vectorised != 0);
+    if (!src.empty()) break;
+  }
+  if (needed) *needed = src.size() + 1;
+  if (!buf) return AKGB_OK;
+  if (cap < src.size() + 1) return fail(AKGB_INVALID_ARG, "buffer too small");
+  std::memcpy(buf, src.c_str(), src.size() + 1);
   return AKGB_OK;
 }
 

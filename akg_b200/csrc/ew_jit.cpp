@@ -1,0 +1,504 @@
+// Run-time instantiation of the elementwise template for one fused chain.
+//
+// The interpreter in k_ewgeneric.cu runs any chain but pays a decode per op.  Here the same EwProgram is
+// printed as straight-line CUDA C++ inside a fixed, hand-written kernel skeleton (one-shot CTAs, 128-bit
+// streaming loads/stores, 8 consecutive elements per thread-vector, two vectors per thread), compiled once
+// with NVRTC for sm_100a and cached.  Arithmetic is emitted with the same primitives as the interpreter
+// (typed rounding after every op, __f*_rn, no contraction), so both paths give identical results; the
+// interpreter remains the fallback when NVRTC is not present or a chain uses strided operands.
+//
+// This takes the place of the reference's NVVM/PTX emission for the elementwise class
+// (akg-mlir/lib/Target/PTX/GPUKernelToPTX.cpp:108-172) with a far smaller surface: only the op chain is
+// generated, never the loop structure or the memory access pattern.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "ew_program.hpp"
+#include "graph.hpp"
+#include "kernels.hpp"
+
+namespace akgb {
+namespace {
+
+// ---- NVRTC and driver entry points, resolved at run time -----------------------------------------
+typedef struct _nvrtcProgram* nvrtcProgram;
+typedef int nvrtcResult;
+struct Nvrtc {
+  void* lib = nullptr;
+  nvrtcResult (*CreateProgram)(nvrtcProgram*, const char*, const char*, int, const char* const*, const char* const*);
+  nvrtcResult (*CompileProgram)(nvrtcProgram, int, const char* const*);
+  nvrtcResult (*GetCUBINSize)(nvrtcProgram, size_t*);
+  nvrtcResult (*GetCUBIN)(nvrtcProgram, char*);
+  nvrtcResult (*GetProgramLogSize)(nvrtcProgram, size_t*);
+  nvrtcResult (*GetProgramLog)(nvrtcProgram, char*);
+  nvrtcResult (*DestroyProgram)(nvrtcProgram*);
+  bool ok = false;
+};
+struct Driver {
+  CUresult (*ModuleLoadData)(CUmodule*, const void*);
+  CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*);
+  CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
+                           void**, void**);
+  bool ok = false;
+};
+
+Nvrtc& nvrtc() {
+  static Nvrtc n;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    const char* names[] = {"libnvrtc.so.12", "/usr/local/cuda/lib64/libnvrtc.so.12", "libnvrtc.so"};
+    for (const char* nm : names) {
+      n.lib = dlopen(nm, RTLD_NOW | RTLD_LOCAL);
+      if (n.lib) break;
+    }
+    if (!n.lib) return;
+#define AKGB_SYM(field, name)                                     \
+  *reinterpret_cast<void**>(&n.field) = dlsym(n.lib, name);       \
+  if (!n.field) return;
+    AKGB_SYM(CreateProgram, "nvrtcCreateProgram")
+    AKGB_SYM(CompileProgram, "nvrtcCompileProgram")
+    AKGB_SYM(GetCUBINSize, "nvrtcGetCUBINSize")
+    AKGB_SYM(GetCUBIN, "nvrtcGetCUBIN")
+    AKGB_SYM(GetProgramLogSize, "nvrtcGetProgramLogSize")
+    AKGB_SYM(GetProgramLog, "nvrtcGetProgramLog")
+    AKGB_SYM(DestroyProgram, "nvrtcDestroyProgram")
+#undef AKGB_SYM
+    n.ok = true;
+  });
+  return n;
+}
+
+Driver& driver() {
+  static Driver d;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    auto get = [](const char* name, void** out) {
+      cudaDriverEntryPointQueryResult q;
+      return cudaGetDriverEntryPoint(name, out, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess &&
+             *out;
+    };
+    if (!get("cuModuleLoadData", reinterpret_cast<void**>(&d.ModuleLoadData))) return;
+    if (!get("cuModuleGetFunction", reinterpret_cast<void**>(&d.ModuleGetFunction))) return;
+    if (!get("cuLaunchKernel", reinterpret_cast<void**>(&d.LaunchKernel))) return;
+    d.ok = true;
+  });
+  return d;
+}
+
+// ---- source generation ---------------------------------------------------------------------------
+const char* kPreamble = R"SRC(
+typedef unsigned int u32; typedef unsigned short u16; typedef unsigned char u8; typedef long long i64;
+struct __align__(16) U4 { u32 x, y, z, w; };
+struct __align__(8) U2 { u32 x, y; };
+__device__ __forceinline__ U4 ld16s(const void* p) { U4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p)); return v; }
+__device__ __forceinline__ U4 ld16c(const void* p) { U4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p)); return v; }
+__device__ __forceinline__ U2 ld8s(const void* p) { U2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p)); return v; }
+__device__ __forceinline__ void st16(void* p, U4 v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory"); }
+__device__ __forceinline__ void st8(void* p, U2 v) {
+  asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" :: "l"(p), "r"(v.x), "r"(v.y) : "memory"); }
+__device__ __forceinline__ float h2f(u16 h) { float f; asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h)); return f; }
+__device__ __forceinline__ u16 f2h(float f) { u16 h; asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(f)); return h; }
+__device__ __forceinline__ float b2f(u16 b) { return __uint_as_float(((u32)b) << 16); }
+__device__ __forceinline__ u16 f2b(float f) { u16 h; asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(h) : "f"(f)); return h; }
+__device__ __forceinline__ float rn_f16(float x) { return h2f(f2h(x)); }
+__device__ __forceinline__ float rn_bf16(float x) { return b2f(f2b(x)); }
+__device__ __forceinline__ float rn_f32(float x) { return x; }
+__device__ __forceinline__ int wr_i8(int x) { return (int)(signed char)x; }
+__device__ __forceinline__ int wr_i16(int x) { return (int)(short)x; }
+__device__ __forceinline__ int wr_i32(int x) { return x; }
+__device__ __forceinline__ float mx_f(float a, float b) { return (a != a || b != b) ? __int_as_float(0x7fc00000) : fmaxf(a, b); }
+__device__ __forceinline__ float mn_f(float a, float b) { return (a != a || b != b) ? __int_as_float(0x7fc00000) : fminf(a, b); }
+// 8 consecutive elements starting at element e0 (e0 % 8 == 0, base 16-byte aligned)
+#define LD8_16(NAME, CVT) __device__ __forceinline__ void NAME(const void* p, i64 e0, float* r, bool stream) { \
+  const U4 v = stream ? ld16s((const u16*)p + e0) : ld16c((const u16*)p + e0); const u32 w[4] = {v.x, v.y, v.z, v.w}; \
+  _Pragma("unroll") for (int i = 0; i < 4; ++i) { r[2*i] = CVT((u16)(w[i] & 0xffffu)); r[2*i+1] = CVT((u16)(w[i] >> 16)); } }
+LD8_16(ld8_f16, h2f)
+LD8_16(ld8_bf16, b2f)
+__device__ __forceinline__ void ld8_f32(const void* p, i64 e0, float* r, bool stream) {
+  const U4 a = stream ? ld16s((const float*)p + e0) : ld16c((const float*)p + e0);
+  const U4 b = stream ? ld16s((const float*)p + e0 + 4) : ld16c((const float*)p + e0 + 4);
+  r[0] = __uint_as_float(a.x); r[1] = __uint_as_float(a.y); r[2] = __uint_as_float(a.z); r[3] = __uint_as_float(a.w);
+  r[4] = __uint_as_float(b.x); r[5] = __uint_as_float(b.y); r[6] = __uint_as_float(b.z); r[7] = __uint_as_float(b.w); }
+__device__ __forceinline__ void ld8_i32(const void* p, i64 e0, int* r, bool stream) {
+  const U4 a = stream ? ld16s((const int*)p + e0) : ld16c((const int*)p + e0);
+  const U4 b = stream ? ld16s((const int*)p + e0 + 4) : ld16c((const int*)p + e0 + 4);
+  r[0] = (int)a.x; r[1] = (int)a.y; r[2] = (int)a.z; r[3] = (int)a.w; r[4] = (int)b.x; r[5] = (int)b.y; r[6] = (int)b.z; r[7] = (int)b.w; }
+__device__ __forceinline__ void ld8_i16(const void* p, i64 e0, int* r, bool stream) {
+  const U4 v = stream ? ld16s((const u16*)p + e0) : ld16c((const u16*)p + e0); const u32 w[4] = {v.x, v.y, v.z, v.w};
+  _Pragma("unroll") for (int i = 0; i < 4; ++i) { r[2*i] = (int)(short)(w[i] & 0xffffu); r[2*i+1] = (int)(short)(w[i] >> 16); } }
+__device__ __forceinline__ void ld8_i8(const void* p, i64 e0, int* r, bool stream) {
+  const U2 v = ld8s((const u8*)p + e0); const u32 w[2] = {v.x, v.y};
+  _Pragma("unroll") for (int i = 0; i < 8; ++i) r[i] = (int)(signed char)((w[i >> 2] >> (8 * (i & 3))) & 0xffu); }
+__device__ __forceinline__ void ld8_bool(const void* p, i64 e0, int* r, bool stream) {
+  const U2 v = ld8s((const u8*)p + e0); const u32 w[2] = {v.x, v.y};
+  _Pragma("unroll") for (int i = 0; i < 8; ++i) r[i] = ((w[i >> 2] >> (8 * (i & 3))) & 0xffu) ? 1 : 0; }
+#define ST8_16(NAME, CVT) __device__ __forceinline__ void NAME(void* p, i64 e0, const float* r) { U4 v; \
+  v.x = (u32)CVT(r[0]) | ((u32)CVT(r[1]) << 16); v.y = (u32)CVT(r[2]) | ((u32)CVT(r[3]) << 16); \
+  v.z = (u32)CVT(r[4]) | ((u32)CVT(r[5]) << 16); v.w = (u32)CVT(r[6]) | ((u32)CVT(r[7]) << 16); st16((u16*)p + e0, v); }
+ST8_16(st8_f16, f2h)
+ST8_16(st8_bf16, f2b)
+__device__ __forceinline__ void st8_f32(void* p, i64 e0, const float* r) {
+  U4 a, b; a.x = __float_as_uint(r[0]); a.y = __float_as_uint(r[1]); a.z = __float_as_uint(r[2]); a.w = __float_as_uint(r[3]);
+  b.x = __float_as_uint(r[4]); b.y = __float_as_uint(r[5]); b.z = __float_as_uint(r[6]); b.w = __float_as_uint(r[7]);
+  st16((float*)p + e0, a); st16((float*)p + e0 + 4, b); }
+__device__ __forceinline__ void st8_i32(void* p, i64 e0, const int* r) {
+  U4 a, b; a.x = r[0]; a.y = r[1]; a.z = r[2]; a.w = r[3]; b.x = r[4]; b.y = r[5]; b.z = r[6]; b.w = r[7];
+  st16((int*)p + e0, a); st16((int*)p + e0 + 4, b); }
+__device__ __forceinline__ void st8_i16(void* p, i64 e0, const int* r) { U4 v;
+  v.x = (u32)(u16)r[0] | ((u32)(u16)r[1] << 16); v.y = (u32)(u16)r[2] | ((u32)(u16)r[3] << 16);
+  v.z = (u32)(u16)r[4] | ((u32)(u16)r[5] << 16); v.w = (u32)(u16)r[6] | ((u32)(u16)r[7] << 16); st16((u16*)p + e0, v); }
+__device__ __forceinline__ void st8_i8(void* p, i64 e0, const int* r) { U2 v; v.x = 0; v.y = 0;
+  _Pragma("unroll") for (int i = 0; i < 4; ++i) { v.x |= ((u32)(u8)r[i]) << (8 * i); v.y |= ((u32)(u8)r[4 + i]) << (8 * i); } st8((u8*)p + e0, v); }
+__device__ __forceinline__ void st8_bool(void* p, i64 e0, const int* r) { U2 v; v.x = 0; v.y = 0;
+  _Pragma("unroll") for (int i = 0; i < 4; ++i) { v.x |= (r[i] ? 1u : 0u) << (8 * i); v.y |= (r[4 + i] ? 1u : 0u) << (8 * i); } st8((u8*)p + e0, v); }
+// scalar element access (any alignment)
+__device__ __forceinline__ float ld1_f16(const void* p, i64 i) { return h2f(((const u16*)p)[i]); }
+__device__ __forceinline__ float ld1_bf16(const void* p, i64 i) { return b2f(((const u16*)p)[i]); }
+__device__ __forceinline__ float ld1_f32(const void* p, i64 i) { return ((const float*)p)[i]; }
+__device__ __forceinline__ int ld1_i32(const void* p, i64 i) { return ((const int*)p)[i]; }
+__device__ __forceinline__ int ld1_i16(const void* p, i64 i) { return (int)((const short*)p)[i]; }
+__device__ __forceinline__ int ld1_i8(const void* p, i64 i) { return (int)((const signed char*)p)[i]; }
+__device__ __forceinline__ int ld1_bool(const void* p, i64 i) { return ((const u8*)p)[i] ? 1 : 0; }
+__device__ __forceinline__ void st1_f16(void* p, i64 i, float v) { ((u16*)p)[i] = f2h(v); }
+__device__ __forceinline__ void st1_bf16(void* p, i64 i, float v) { ((u16*)p)[i] = f2b(v); }
+__device__ __forceinline__ void st1_f32(void* p, i64 i, float v) { ((float*)p)[i] = v; }
+__device__ __forceinline__ void st1_i32(void* p, i64 i, int v) { ((int*)p)[i] = v; }
+__device__ __forceinline__ void st1_i16(void* p, i64 i, int v) { ((short*)p)[i] = (short)v; }
+__device__ __forceinline__ void st1_i8(void* p, i64 i, int v) { ((signed char*)p)[i] = (signed char)v; }
+__device__ __forceinline__ void st1_bool(void* p, i64 i, int v) { ((u8*)p)[i] = v ? 1 : 0; }
+)SRC";
+
+const char* dt_tag(int dt) {
+  switch ((DT)dt) {
+    case DT::F16: return "f16";
+    case DT::BF16: return "bf16";
+    case DT::F32: return "f32";
+    case DT::I32: return "i32";
+    case DT::I16: return "i16";
+    case DT::I8: return "i8";
+    default: return "bool";
+  }
+}
+bool is_float_dt(int dt) { return (DT)dt == DT::F16 || (DT)dt == DT::BF16 || (DT)dt == DT::F32; }
+const char* round_fn(int dt) { return (DT)dt == DT::F16 ? "rn_f16" : (DT)dt == DT::BF16 ? "rn_bf16" : "rn_f32"; }
+const char* wrap_fn(int dt) { return (DT)dt == DT::I8 ? "wr_i8" : (DT)dt == DT::I16 ? "wr_i16" : "wr_i32"; }
+
+struct Var {
+  std::string name;
+  bool is_float = true;
+  bool is_const = false;
+  std::string literal;
+};
+
+std::string float_unary(int op, const std::string& a) {
+  switch (op) {
+    case EW_ABS: return "fabsf(" + a + ")";
+    case EW_NEG: return "(-" + a + ")";
+    case EW_EXP: return "expf(" + a + ")";
+    case EW_LOG: return "logf(" + a + ")";
+    case EW_TANH: return "tanhf(" + a + ")";
+    case EW_RSQRT: return "__fdiv_rn(1.0f, __fsqrt_rn(" + a + "))";
+    case EW_SQRT: return "__fsqrt_rn(" + a + ")";
+    case EW_RECIP: return "__fdiv_rn(1.0f, " + a + ")";
+    case EW_FLOOR: return "floorf(" + a + ")";
+    case EW_SQUARE: return "__fmul_rn(" + a + ", " + a + ")";
+    case EW_SIN: return "sinf(" + a + ")";
+    case EW_COS: return "cosf(" + a + ")";
+    case EW_ASINH: return "asinhf(" + a + ")";
+    case EW_ACOSH: return "acoshf(" + a + ")";
+    case EW_ATAN: return "atanf(" + a + ")";
+    case EW_ASIN: return "asinf(" + a + ")";
+    case EW_ACOS: return "acosf(" + a + ")";
+    default: return a;
+  }
+}
+std::string float_binary(int op, const std::string& a, const std::string& b) {
+  switch (op) {
+    case EW_ADD: return "__fadd_rn(" + a + ", " + b + ")";
+    case EW_SUB: return "__fsub_rn(" + a + ", " + b + ")";
+    case EW_MUL: return "__fmul_rn(" + a + ", " + b + ")";
+    case EW_DIV: return "__fdiv_rn(" + a + ", " + b + ")";
+    case EW_MAX: return "mx_f(" + a + ", " + b + ")";
+    case EW_MIN: return "mn_f(" + a + ", " + b + ")";
+    case EW_POW: return "powf(" + a + ", " + b + ")";
+    default: return "atan2f(" + a + ", " + b + ")";
+  }
+}
+std::string int_binary(int op, const std::string& a, const std::string& b) {
+  switch (op) {
+    case EW_ADD: return "(" + a + " + " + b + ")";
+    case EW_SUB: return "(" + a + " - " + b + ")";
+    case EW_MUL: return "(" + a + " * " + b + ")";
+    case EW_DIV: return "(" + b + " == 0 ? 0 : " + a + " / " + b + ")";
+    case EW_MAX: return "max(" + a + ", " + b + ")";
+    default: return "min(" + a + ", " + b + ")";
+  }
+}
+const char* cmp_op(int op) {
+  switch (op) {
+    case EW_EQ: return "==";
+    case EW_GT: return ">";
+    case EW_GE: return ">=";
+    case EW_LT: return "<";
+    default: return "<=";
+  }
+}
+
+// Emits the op chain for element lane `j` of vector slot `u`.  `ref(reg)` yields the expression of a register.
+bool generate(const EwProgram& P, bool vec, std::string* out) {
+  for (int i = 0; i < P.n_in; ++i)
+    if (P.in[i].kind == EWI_STRIDED) return false;
+  for (int i = 0; i < P.n_out; ++i)
+    if (P.out[i].kind != EWI_FULL) return false;
+  std::ostringstream s;
+  s << kPreamble;
+  s << "extern \"C\" __global__ void __launch_bounds__(256) akgb_ew_jit(";
+  for (int i = 0; i < P.n_in; ++i) s << "const void* __restrict__ in" << i << ", ";
+  for (int i = 0; i < P.n_out; ++i) s << "void* __restrict__ out" << i << ", ";
+  s << "i64 n) {\n";
+  const int U = vec ? 2 : 4, E = vec ? 8 : 1;
+  s << "  constexpr int U = " << U << ", E = " << E << ";\n";
+  s << "  const i64 nv = n / E;\n";
+  s << "  const i64 vbase = (i64)blockIdx.x * (256 * U) + threadIdx.x;\n";
+  // register -> current variable
+  std::vector<Var> regs(kEwMaxReg);
+  for (int c = 0; c < P.n_const; ++c) {
+    Var v;
+    v.is_const = true;
+    char buf[64];
+    std::snprintf(buf, sizeof(buf), "0x%08xu", P.const_bits[c]);
+    v.literal = buf;
+    regs[P.const_reg[c]] = v;  // class decided at use (float bits or int)
+  }
+  // loads
+  for (int i = 0; i < P.n_in; ++i) {
+    const EwOperand& o = P.in[i];
+    const bool fl = is_float_dt(o.dt);
+    s << "  " << (fl ? "float" : "int") << " a" << i << "[U][E];\n";
+    Var v;
+    v.name = "a" + std::to_string(i);
+    v.is_float = fl;
+    regs[o.reg] = v;
+  }
+  s << "  #pragma unroll\n  for (int u = 0; u < U; ++u) {\n    const i64 v = vbase + (i64)u * 256;\n    if (v < nv) {\n";
+  for (int i = 0; i < P.n_in; ++i) {
+    const EwOperand& o = P.in[i];
+    const char* tag = dt_tag(o.dt);
+    if (vec) {
+      if (o.kind == EWI_FULL) s << "      ld8_" << tag << "(in" << i << ", v * 8, a" << i << "[u], true);\n";
+      else if (o.kind == EWI_MOD && o.mod % 8 == 0)
+        s << "      ld8_" << tag << "(in" << i << ", (v * 8) % " << o.mod << "LL, a" << i << "[u], false);\n";
+      else if (o.kind == EWI_MOD)
+        s << "      #pragma unroll\n      for (int j = 0; j < 8; ++j) a" << i << "[u][j] = ld1_" << tag << "(in" << i
+          << ", (v * 8 + j) % " << o.mod << "LL);\n";
+      else  // scalar
+        s << "      { const " << (is_float_dt(o.dt) ? "float" : "int") << " t = ld1_" << tag << "(in" << i
+          << ", 0);\n        #pragma unroll\n        for (int j = 0; j < 8; ++j) a" << i << "[u][j] = t; }\n";
+    } else {
+      if (o.kind == EWI_FULL) s << "      a" << i << "[u][0] = ld1_" << tag << "(in" << i << ", v);\n";
+      else if (o.kind == EWI_MOD) s << "      a" << i << "[u][0] = ld1_" << tag << "(in" << i << ", v % " << o.mod << "LL);\n";
+      else s << "      a" << i << "[u][0] = ld1_" << tag << "(in" << i << ", 0);\n";
+    }
+  }
+  s << "    }\n  }\n";
+  // compute + store
+  s << "  #pragma unroll\n  for (int u = 0; u < U; ++u) {\n    const i64 v = vbase + (i64)u * 256;\n    if (v < nv) {\n";
+  auto ref = [&](int reg, bool want_float) -> std::string {
+    const Var& v = regs[reg];
+    if (v.is_const) return want_float ? "__uint_as_float(" + v.literal + ")" : "(int)" + v.literal;
+    return v.name + "[u][j]";
+  };
+  int tcount = 0;
+  for (int k = 0; k < P.n_instr; ++k) {
+    const EwInstr& ins = P.instr[k];
+    const bool fl = ins.cls == EWC_FLOAT;
+    const bool sfl = ins.src_cls == EWC_FLOAT;
+    std::string name = "t" + std::to_string(tcount++);
+    std::string expr;
+    const int op = ins.op;
+    if (op == EW_CAST) {
+      if (fl) expr = std::string(round_fn(ins.dt)) + "(" + (sfl ? ref(ins.a, true) : "(float)" + ref(ins.a, false)) + ")";
+      else if (ins.cls == EWC_BOOL) expr = sfl ? "(" + ref(ins.a, true) + " != 0.f ? 1 : 0)" : "(" + ref(ins.a, false) + " != 0 ? 1 : 0)";
+      else expr = std::string(wrap_fn(ins.dt)) + "(" + ref(ins.a, false) + ")";
+    } else if (op <= EW_ACOS) {
+      if (fl) expr = std::string(round_fn(ins.dt)) + "(" + float_unary(op, ref(ins.a, true)) + ")";
+      else if (op == EW_ABS) expr = std::string(wrap_fn(ins.dt)) + "(abs(" + ref(ins.a, false) + "))";
+      else if (op == EW_NEG) expr = std::string(wrap_fn(ins.dt)) + "(-" + ref(ins.a, false) + ")";
+      else if (op == EW_SQUARE) expr = std::string(wrap_fn(ins.dt)) + "(" + ref(ins.a, false) + " * " + ref(ins.a, false) + ")";
+      else expr = ref(ins.a, false);
+    } else if (op <= EW_ISNAN) {
+      const std::string a = ref(ins.a, true);
+      expr = op == EW_ISINF ? "(isinf(" + a + ") ? 1 : 0)" : op == EW_ISFINITE ? "(isfinite(" + a + ") ? 1 : 0)"
+                                                                                  : "(" + a + " != " + a + " ? 1 : 0)";
+    } else if (op == EW_NOT) {
+      expr = "(" + ref(ins.a, false) + " ? 0 : 1)";
+    } else if (op <= EW_ATAN2) {
+      if (fl) expr = std::string(round_fn(ins.dt)) + "(" + float_binary(op, ref(ins.a, true), ref(ins.b, true)) + ")";
+      else expr = std::string(wrap_fn(ins.dt)) + "(" + int_binary(op, ref(ins.a, false), ref(ins.b, false)) + ")";
+    } else if (op <= EW_LE) {
+      const std::string a = ref(ins.a, sfl), b = ref(ins.b, sfl);
+      if (op == EW_NE) expr = "(!(" + a + " == " + b + ") ? 1 : 0)";
+      else expr = "((" + a + " " + cmp_op(op) + " " + b + ") ? 1 : 0)";
+    } else if (op == EW_AND) {
+      expr = "((" + ref(ins.a, false) + " && " + ref(ins.b, false) + ") ? 1 : 0)";
+    } else if (op == EW_OR) {
+      expr = "((" + ref(ins.a, false) + " || " + ref(ins.b, false) + ") ? 1 : 0)";
+    } else {  // select: a = condition
+      expr = "(" + ref(ins.a, false) + " ? " + ref(ins.b, fl) + " : " + ref(ins.c, fl) + ")";
+    }
+    s << "      " << (fl ? "float " : "int ") << name << "[E];\n";
+    s << "      #pragma unroll\n      for (int j = 0; j < E; ++j) " << name << "[j] = " << expr << ";\n";
+    Var nv;
+    nv.name = name;
+    nv.is_float = fl;
+    regs[ins.dst] = nv;
+    // later references use name[j], not name[u][j]
+    regs[ins.dst].name = name + "#";
+  }
+  // fix-up of references: temporaries are indexed [j] only
+  std::string body = s.str();
+  {
+    std::string fixed;
+    fixed.reserve(body.size());
+    for (size_t i = 0; i < body.size(); ++i) {
+      if (body[i] == '#' && body.compare(i, 7, "#[u][j]") == 0) {
+        fixed += "[j]";
+        i += 6;
+      } else {
+        fixed.push_back(body[i]);
+      }
+    }
+    body.swap(fixed);
+  }
+  std::ostringstream t;
+  t << body;
+  for (int i = 0; i < P.n_out; ++i) {
+    const EwOperand& o = P.out[i];
+    const Var& v = regs[o.reg];
+    const char* tag = dt_tag(o.dt);
+    const bool fl = is_float_dt(o.dt);
+    std::string src;
+    if (v.is_const) {
+      t << "      " << (fl ? "float" : "int") << " oc" << i << "[E];\n      #pragma unroll\n      for (int j = 0; j < E; ++j) oc"
+        << i << "[j] = " << (fl ? "__uint_as_float(" + v.literal + ")" : "(int)" + v.literal) << ";\n";
+      src = "oc" + std::to_string(i);
+    } else if (!v.name.empty() && v.name.back() == '#') {
+      src = v.name.substr(0, v.name.size() - 1);
+    } else {
+      src = v.name + "[u]";
+    }
+    if (vec) t << "      st8_" << tag << "(out" << i << ", v * 8, " << src << ");\n";
+    else t << "      st1_" << tag << "(out" << i << ", v, " << src << "[0]);\n";
+  }
+  t << "    }\n  }\n}\n";
+  *out = t.str();
+  return true;
+}
+
+struct JitKernel {
+  CUfunction fn = nullptr;
+  bool failed = false;
+};
+std::mutex g_mu;
+std::map<std::string, JitKernel> g_cache;  // source text -> kernel (per process; modules live until exit)
+
+JitKernel* compile(const std::string& src) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  auto it = g_cache.find(src);
+  if (it != g_cache.end()) return &it->second;
+  JitKernel& k = g_cache[src];
+  k.failed = true;
+  Nvrtc& n = nvrtc();
+  Driver& d = driver();
+  if (!n.ok || !d.ok) return &k;
+  nvrtcProgram prog = nullptr;
+  if (n.CreateProgram(&prog, src.c_str(), "akgb_ew_jit.cu", 0, nullptr, nullptr) != 0) return &k;
+  const char* opts[] = {"--gpu-architecture=sm_100a", "-std=c++17", "--fmad=false", "-default-device"};
+  const nvrtcResult r = n.CompileProgram(prog, 4, opts);
+  if (r != 0) {
+    size_t ls = 0;
+    if (n.GetProgramLogSize(prog, &ls) == 0 && ls > 1) {
+      std::string log(ls, '\0');
+      n.GetProgramLog(prog, &log[0]);
+      set_last_error(("elementwise JIT: " + log.substr(0, 400)).c_str());
+    }
+    n.DestroyProgram(&prog);
+    return &k;
+  }
+  size_t sz = 0;
+  std::vector<char> cubin;
+  if (n.GetCUBINSize(prog, &sz) == 0 && sz > 0) {
+    cubin.resize(sz);
+    if (n.GetCUBIN(prog, cubin.data()) != 0) cubin.clear();
+  }
+  n.DestroyProgram(&prog);
+  if (cubin.empty()) return &k;
+  CUmodule mod = nullptr;
+  if (d.ModuleLoadData(&mod, cubin.data()) != CUDA_SUCCESS) return &k;
+  if (d.ModuleGetFunction(&k.fn, mod, "akgb_ew_jit") != CUDA_SUCCESS) return &k;
+  k.failed = false;
+  return &k;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+// The CUDA C++ text that would be compiled for this program (empty when the program needs the interpreter).
+std::string ew_jit_source(const EwProgram& P, bool vec) {
+  std::string src;
+  if (!generate(P, vec, &src)) src.clear();
+  return src;
+}
+
+// Tries the run-time instantiated kernel; returns cudaErrorNotSupported when the caller should interpret.
+cudaError_t ew_jit_launch(const EwProgram& P, const void* const* in, void* const* out, cudaStream_t s, LaunchDims* dims) {
+  if (P.n == 0) return cudaSuccess;
+  bool vec = P.n % 8 == 0;
+  for (int i = 0; i < P.n_in && vec; ++i) vec = aligned16(in[i]);
+  for (int i = 0; i < P.n_out && vec; ++i) vec = aligned16(out[i]);
+  std::string src;
+  if (!generate(P, vec, &src)) return cudaErrorNotSupported;
+  JitKernel* k = compile(src);
+  if (!k || k->failed) return cudaErrorNotSupported;
+  const int U = vec ? 2 : 4, E = vec ? 8 : 1;
+  const int64_t nv = P.n / E;
+  const int64_t grid = (nv + 256 * U - 1) / (256 * U);
+  if (grid > 0x7fffffff) return cudaErrorNotSupported;
+  long long n = P.n;
+  void* args[kEwMaxIn + kEwMaxOut + 1];
+  const void* inp[kEwMaxIn];
+  void* outp[kEwMaxOut];
+  int a = 0;
+  for (int i = 0; i < P.n_in; ++i) {
+    inp[i] = in[i];
+    args[a++] = &inp[i];
+  }
+  for (int i = 0; i < P.n_out; ++i) {
+    outp[i] = out[i];
+    args[a++] = &outp[i];
+  }
+  args[a++] = &n;
+  if (dims) {
+    dims->grid[0] = (unsigned)grid;
+    dims->block[0] = 256;
+    dims->smem = 0;
+  }
+  const CUresult r = driver().LaunchKernel(k->fn, (unsigned)grid, 1, 1, 256, 1, 1, 0, (CUstream)s, args, nullptr);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorLaunchFailure;
+}
+
+}  // namespace akgb

@@ -220,8 +220,13 @@ __global__ void __launch_bounds__(kEwThreads) ew_generic_kernel(const __grid_con
 
 size_t ew_generic_smem(const EwProgram& p) { return (size_t)p.n_reg * kEwVec * kEwThreads * sizeof(uint32_t); }
 
-cudaError_t ew_generic(const EwProgram& p, const void* const* in, void* const* out, cudaStream_t s, LaunchDims* dims) {
+cudaError_t ew_generic(const EwProgram& p, const void* const* in, void* const* out, bool allow_jit, cudaStream_t s,
+                       LaunchDims* dims) {
   if (p.n == 0) return cudaSuccess;
+  if (allow_jit) {
+    const cudaError_t je = ew_jit_launch(p, in, out, s, dims);
+    if (je != cudaErrorNotSupported) return je;
+  }
   EwPtrs ptrs;
   for (int i = 0; i < kEwMaxIn; ++i) ptrs.in[i] = i < p.n_in ? in[i] : nullptr;
   for (int i = 0; i < kEwMaxOut; ++i) ptrs.out[i] = i < p.n_out ? out[i] : nullptr;

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <string>
 
 namespace akgb {
 
@@ -68,7 +69,11 @@ cudaError_t reduce_row_f32(RedOp op, const float* x, float* out, int64_t rows, i
 // ---- generic elementwise/broadcast interpreter (program in ew_program.hpp) ----------
 struct EwProgram;
 size_t ew_generic_smem(const EwProgram& p);
-cudaError_t ew_generic(const EwProgram& p, const void* const* in, void* const* out, cudaStream_t s, LaunchDims* dims);
+cudaError_t ew_generic(const EwProgram& p, const void* const* in, void* const* out, bool allow_jit, cudaStream_t s,
+                       LaunchDims* dims);
+// run-time instantiated variant (ew_jit.cpp); cudaErrorNotSupported = fall back to the interpreter
+std::string ew_jit_source(const EwProgram& p, bool vec);
+cudaError_t ew_jit_launch(const EwProgram& p, const void* const* in, void* const* out, cudaStream_t s, LaunchDims* dims);
 
 // ---- transpose -----------------------------------------------------------------
 // General permutation of up to 6 folded dims over elements of `esize` bytes.

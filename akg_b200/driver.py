@@ -43,7 +43,8 @@ def _np_dtype(name: str):
 class FusedKernel:
     """One fused-op description compiled to a launch plan (``akgb_compile``)."""
 
-    def __init__(self, info_json: str | bytes | dict, device: int = -1, shard_rank: int = 0, shard_world: int = 1):
+    def __init__(self, info_json: str | bytes | dict, device: int = -1, shard_rank: int = 0, shard_world: int = 1,
+                 flags: int = 0):
         lib = _capi.load()
         if isinstance(info_json, dict):
             info_json = json.dumps(info_json)
@@ -51,7 +52,7 @@ class FusedKernel:
             info_json = info_json.encode("utf-8")
         self._lib = lib
         self._handle = ctypes.c_void_p()
-        opt = _capi.Options(ctypes.sizeof(_capi.Options), device, shard_rank, shard_world, 0)
+        opt = _capi.Options(ctypes.sizeof(_capi.Options), device, shard_rank, shard_world, flags)
         _capi.check(lib.akgb_compile(info_json, len(info_json), ctypes.byref(opt), ctypes.byref(self._handle)))
         self.tensors: list[TensorInfo] = []
         for i in range(lib.akgb_num_tensors(self._handle)):
@@ -99,6 +100,14 @@ class FusedKernel:
         buf = ctypes.create_string_buffer(need.value)
         _capi.check(self._lib.akgb_kernel_meta(self._handle, buf, need.value, ctypes.byref(need)))
         return json.loads(buf.value.decode())
+
+    def jit_source(self, vectorised: bool = True) -> str:
+        """CUDA C++ compiled at run time for the first generic elementwise group ('' if none)."""
+        need = ctypes.c_size_t(0)
+        _capi.check(self._lib.akgb_dump_jit_source(self._handle, int(vectorised), None, 0, ctypes.byref(need)))
+        buf = ctypes.create_string_buffer(need.value)
+        _capi.check(self._lib.akgb_dump_jit_source(self._handle, int(vectorised), buf, need.value, ctypes.byref(need)))
+        return buf.value.decode()
 
     def check_device_error(self) -> int:
         word = ctypes.c_uint32(0)

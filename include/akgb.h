@@ -73,8 +73,13 @@ typedef struct akgb_options {
   int32_t device;       /* CUDA device ordinal; -1 = current device */
   int32_t shard_rank;   /* this rank's index in the leading-axis split */
   int32_t shard_world;  /* number of ranks the leading axis is split over; 0/1 = no split */
-  int32_t flags;        /* reserved, 0 */
+  int32_t flags;        /* bit set of AKGB_FLAG_* */
 } akgb_options;
+
+/* Run generic elementwise groups with the interpreting kernel only, never the run-time instantiated
+ * (NVRTC-compiled) variant of the same template.  Results are identical; this is for hosts without NVRTC
+ * and for tests. */
+#define AKGB_FLAG_NO_JIT 1
 
 typedef struct akgb_kernel akgb_kernel;
 
@@ -126,6 +131,12 @@ akgb_status akgb_profile_host(akgb_kernel* k, void* const* host_tensors, int32_t
  * kernelName, is_dynamic, sha256 — plus class, bytes, flops.  Writes a
  * NUL-terminated JSON text; `*needed` receives the size including the NUL. */
 akgb_status akgb_kernel_meta(const akgb_kernel* k, char* buf, size_t cap, size_t* needed);
+
+/* The CUDA C++ text that is compiled at run time for the first generic elementwise group of the region
+ * (`vectorised` != 0: the 16-byte-vector variant, else the scalar one); an empty text means the region has
+ * no such group or it runs on the interpreting kernel.  The counterpart of the reference's IR/PTX dumps
+ * (AKG_DUMP_IR, python/akg_mlir/mlir_driver.py:711-721). */
+akgb_status akgb_dump_jit_source(const akgb_kernel* k, int32_t vectorised, char* buf, size_t cap, size_t* needed);
 
 /* Operator class the matcher assigned, as a static string
  * ("elementwise", "broadcast", "reduce_x", "reduce_y", "reduce_all",

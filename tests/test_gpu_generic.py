@@ -13,8 +13,17 @@ from helpers import BF16, bits_equal, make_inputs
 pytestmark = pytest.mark.gpu
 
 
+FLAGS = [0]  # set by the fixture below: 0 = run-time instantiated elementwise kernels, 1 = interpreter only
+
+
+@pytest.fixture(autouse=True, params=[0, 1], ids=["jit", "interp"])
+def _both_elementwise_paths(request):
+    FLAGS[0] = request.param
+    yield
+
+
 def run(desc, ins):
-    k = FusedKernel(desc)
+    k = FusedKernel(desc, flags=FLAGS[0])
     outs = k.empty_outputs()
     for o in outs:
         o.view(np.uint8)[...] = 0xCD
