@@ -82,6 +82,10 @@ _SIGNATURES = [
     ("akgb_workspace_size", ctypes.c_size_t, [_vp]),
     ("akgb_launch_count", ctypes.c_int32, [_vp]),
     ("akgb_launch", ctypes.c_int, [_vp, ctypes.POINTER(_vp), _vp, ctypes.c_size_t, _vp]),
+    ("akgb_bind_shapes", ctypes.c_int, [_vp, ctypes.POINTER(ctypes.c_int64), ctypes.c_size_t,
+                                         ctypes.POINTER(ctypes.c_size_t)]),
+    ("akgb_launch_dynamic", ctypes.c_int, [_vp, ctypes.POINTER(_vp), ctypes.POINTER(ctypes.c_int64), ctypes.c_size_t,
+                                            _vp, ctypes.c_size_t, _vp]),
     ("akgb_run_host", ctypes.c_int, [_vp, ctypes.POINTER(_vp)]),
     ("akgb_profile_host", ctypes.c_int, [_vp, ctypes.POINTER(_vp), ctypes.c_int32, ctypes.c_int32,
                                           ctypes.POINTER(ctypes.c_double)]),

@@ -7,6 +7,8 @@
 
 #include <cstdio>
 #include <cstring>
+#include <map>
+#include <memory>
 #include <mutex>
 #include <sstream>
 #include <string>
@@ -59,6 +61,13 @@ struct akgb_kernel {
   int sm_count = 148;
   int shard_rank = 0, shard_world = 1;
   bool no_jit = false;  // AKGB_FLAG_NO_JIT
+  // dynamic-shape regions: one plan per set of launch-time extents
+  struct Bound {
+    Graph graph;
+    Plan plan;
+  };
+  std::map<std::vector<int64_t>, std::unique_ptr<Bound>> bound;
+  std::mutex bound_mu;
   std::vector<akgb_tensor_desc> descs;
   int n_inputs = 0;
   // host-pointer entry points: staging buffers kept between calls
@@ -79,12 +88,12 @@ struct akgb_kernel {
 
 namespace {
 
-akgb_status ensure_device_state(akgb_kernel* k) {
+akgb_status ensure_device_state(akgb_kernel* k, bool need_lut) {
   int dev = k->device;
   if (dev < 0 || dev >= kMaxDevices) return fail(AKGB_INVALID_ARG, "device ordinal out of range");
   DeviceState& ds = g_dev[dev];
   std::lock_guard<std::mutex> lock(ds.mu);
-  if (k->plan.needs_gelu_lut && !ds.gelu_lut) {
+  if (need_lut && !ds.gelu_lut) {
     std::vector<uint16_t> h(gelu_lut_entries());
     gelu_lut_build(h.data());
     void* d = nullptr;
@@ -111,9 +120,9 @@ void* resolve(const Ref& r, void* const* tensors, void* ws) {
   return nullptr;
 }
 
-akgb_status run_plan(akgb_kernel* k, void* const* tensors, void* ws, cudaStream_t s) {
+akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws, cudaStream_t s) {
   DeviceState& ds = g_dev[k->device];
-  for (Step& st : k->plan.steps) {
+  for (Step& st : plan.steps) {
     cudaError_t e = cudaSuccess;
     void* a = resolve(st.a, tensors, ws);
     void* b = resolve(st.b, tensors, ws);
@@ -146,6 +155,18 @@ akgb_status run_plan(akgb_kernel* k, void* const* tensors, void* ws, cudaStream_
         e = ew_generic(st.ew, ins, outs, !k->no_jit, s, &st.dims);
         break;
       }
+      case StepK::ReduceColDual:
+        if (reduce_col_dual_supported(st.red_inner, a)) {
+          e = reduce_col_dual_f32(st.red_op, st.red_op2, (const float*)a, (float*)o, (float*)o2, st.red_len, st.red_inner,
+                                  scratch, k->sm_count, s, &st.dims);
+        } else {  // unaligned input: the two single reductions, one after the other
+          e = reduce_col_f32(st.red_op, (const float*)a, (float*)o, st.red_len, st.red_inner, scratch, k->sm_count, s,
+                             &st.dims);
+          if (e == cudaSuccess)
+            e = reduce_all_f32(st.red_op2, (const float*)a, (float*)o2, st.red_len * st.red_inner, scratch, k->sm_count, s,
+                               nullptr);
+        }
+        break;
       case StepK::ReduceAll:
         e = reduce_all_f32(st.red_op, (const float*)a, (float*)o, st.red_len, scratch, k->sm_count, s, &st.dims);
         break;
@@ -175,6 +196,9 @@ int launches_of(const akgb_kernel* k) {
         break;
       case StepK::ReduceAll:
         n += 2;
+        break;
+      case StepK::ReduceColDual:
+        n += 3;
         break;
       case StepK::GeluChain:
         n += (st.gelu.n % 8) ? 2 : 1;
@@ -259,10 +283,7 @@ akgb_status run_host_chunked(akgb_kernel* k, void* const* host) {
     cudaStreamWaitEvent(k->stream, k->ev_in[c], 0);
     for (size_t i = 0; i < nt; ++i)
       ptrs[i] = k->chunk_split[i] ? (void*)((char*)k->d_tensors[i] + (size_t)c * k->chunk_bytes[i]) : k->d_tensors[i];
-    // run_plan works on k->plan: swap the chunk plan in for the call
-    std::swap(k->plan, k->chunk_plan);
-    akgb_status st = run_plan(k, ptrs.data(), k->d_workspace, k->stream);
-    std::swap(k->plan, k->chunk_plan);
+    akgb_status st = run_plan(k, k->chunk_plan, ptrs.data(), k->d_workspace, k->stream);
     if (st != AKGB_OK) return st;
     cudaEventRecord(k->ev_done[c], k->stream);
     cudaStreamWaitEvent(k->s_out, k->ev_done[c], 0);
@@ -335,8 +356,15 @@ akgb_status akgb_compile(const char* info_json, size_t len, const akgb_options* 
     k->no_jit = (flags & AKGB_FLAG_NO_JIT) != 0;
     k->json_text.assign(info_json, len);
     k->graph = parse_info(info_json, len);
-    infer_sharding(k->graph, rank, world);
-    k->plan = build_plan(k->graph, k->sm_count);
+    if (k->graph.dynamic) {
+      if (world > 1) throw Unsupported("dynamic-shape regions cannot be sharded at compile time");
+      for (auto& n : k->graph.nodes)
+        if (n.kind == OpK::Unknown) throw Unsupported("operator '" + n.name + "' is not supported");
+      k->plan.klass = "dynamic";
+    } else {
+      infer_sharding(k->graph, rank, world);
+      k->plan = build_plan(k->graph, k->sm_count);
+    }
     const Graph& g = k->graph;
     k->n_inputs = (int)g.inputs.size();
     auto add = [&](int vid, bool is_out) {
@@ -349,6 +377,8 @@ akgb_status akgb_compile(const char* info_json, size_t len, const akgb_options* 
       if (v.shape.size() > AKGB_MAX_RANK) throw Unsupported("tensor rank above 8");
       for (int i = 0; i < d.rank; ++i) d.shape[i] = v.shape[i];
       d.nbytes = v.numel() * (int64_t)dt_size(v.dt);
+      for (auto e : v.shape)
+        if (e < 0) d.nbytes = -1;  // bound at launch
       d.is_output = is_out;
       d.shard_kind = v.partial ? v.partial : (v.split0 ? AKGB_SPLIT_AXIS0 : AKGB_REPLICATED);
       k->descs.push_back(d);
@@ -403,8 +433,68 @@ const char* akgb_kernel_class(const akgb_kernel* k) { return k ? k->plan.klass.c
 int64_t akgb_kernel_bytes(const akgb_kernel* k) { return k ? k->plan.bytes : 0; }
 int64_t akgb_kernel_flops(const akgb_kernel* k) { return k ? k->plan.flops : 0; }
 
+namespace {
+// plan of a dynamic-shape kernel for the given extents (flat: all extents of argument 0, then argument 1, ...)
+akgb_status bound_plan(akgb_kernel* k, const int64_t* shapes, size_t count, akgb_kernel::Bound** out) {
+  if (!k->graph.dynamic) return fail(AKGB_INVALID_ARG, "this kernel has static shapes: use akgb_launch");
+  size_t need = 0;
+  for (auto& d : k->descs) need += (size_t)d.rank;
+  if (!shapes || count != need) return fail(AKGB_INVALID_ARG, "shapes must list every extent of every argument");
+  std::vector<int64_t> key(shapes, shapes + count);
+  std::lock_guard<std::mutex> lock(k->bound_mu);
+  auto it = k->bound.find(key);
+  if (it == k->bound.end()) {
+    try {
+      std::vector<std::vector<int64_t>> per;
+      size_t pos = 0;
+      for (auto& d : k->descs) {
+        per.emplace_back(shapes + pos, shapes + pos + d.rank);
+        pos += (size_t)d.rank;
+      }
+      std::unique_ptr<akgb_kernel::Bound> b(new akgb_kernel::Bound());
+      b->graph = bind_shapes(k->graph, per);
+      b->plan = build_plan(b->graph, k->sm_count);
+      it = k->bound.emplace(std::move(key), std::move(b)).first;
+    } catch (const JsonError& e) {
+      return fail(AKGB_INVALID_ARG, e.what());
+    } catch (const Unsupported& e) {
+      return fail(AKGB_UNSUPPORTED, e.what());
+    } catch (const std::exception& e) {
+      return fail(AKGB_INVALID_ARG, e.what());
+    }
+  }
+  *out = it->second.get();
+  return AKGB_OK;
+}
+}  // namespace
+
+extern "C" akgb_status akgb_bind_shapes(akgb_kernel* k, const int64_t* shapes, size_t count, size_t* workspace_bytes) {
+  if (!k) return fail(AKGB_INVALID_ARG, "null argument");
+  akgb_kernel::Bound* b = nullptr;
+  akgb_status st = bound_plan(k, shapes, count, &b);
+  if (st != AKGB_OK) return st;
+  if (workspace_bytes) *workspace_bytes = b->plan.workspace_bytes;
+  return AKGB_OK;
+}
+
+extern "C" akgb_status akgb_launch_dynamic(akgb_kernel* k, void* const* tensors, const int64_t* shapes, size_t count,
+                                           void* workspace, size_t workspace_bytes, void* stream) {
+  if (!k || !tensors) return fail(AKGB_INVALID_ARG, "null argument");
+  akgb_kernel::Bound* b = nullptr;
+  akgb_status st = bound_plan(k, shapes, count, &b);
+  if (st != AKGB_OK) return st;
+  if (workspace_bytes < b->plan.workspace_bytes || (b->plan.workspace_bytes && !workspace))
+    return fail(AKGB_INVALID_ARG, "workspace smaller than akgb_bind_shapes() reported");
+  if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return fail(AKGB_MISALIGNED, "workspace must be 256-byte aligned");
+  st = ensure_device_state(k, b->plan.needs_gelu_lut);
+  if (st != AKGB_OK) return st;
+  return run_plan(k, b->plan, tensors, workspace, reinterpret_cast<cudaStream_t>(stream));
+}
+
 akgb_status akgb_launch(akgb_kernel* k, void* const* tensors, void* workspace, size_t workspace_bytes, void* stream) {
   if (!k || !tensors) return fail(AKGB_INVALID_ARG, "null argument");
+  if (k->graph.dynamic) return fail(AKGB_INVALID_ARG, "this kernel has dynamic shapes: use akgb_launch_dynamic");
   if (workspace_bytes < k->plan.workspace_bytes || (k->plan.workspace_bytes && !workspace))
     return fail(AKGB_INVALID_ARG, "workspace smaller than akgb_workspace_size()");
   for (size_t i = 0; i < k->descs.size(); ++i) {
@@ -412,16 +502,17 @@ akgb_status akgb_launch(akgb_kernel* k, void* const* tensors, void* workspace, s
   }
   if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255))
     return fail(AKGB_MISALIGNED, "workspace must be 256-byte aligned");
-  akgb_status st = ensure_device_state(k);
+  akgb_status st = ensure_device_state(k, k->plan.needs_gelu_lut);
   if (st != AKGB_OK) return st;
-  return run_plan(k, tensors, workspace, reinterpret_cast<cudaStream_t>(stream));
+  return run_plan(k, k->plan, tensors, workspace, reinterpret_cast<cudaStream_t>(stream));
 }
 
 akgb_status akgb_run_host(akgb_kernel* k, void* const* host) {
   if (!k || !host) return fail(AKGB_INVALID_ARG, "null argument");
+  if (k->graph.dynamic) return fail(AKGB_INVALID_ARG, "this kernel has dynamic shapes: use akgb_launch_dynamic");
   akgb_status st = stage(k);
   if (st != AKGB_OK) return st;
-  st = ensure_device_state(k);
+  st = ensure_device_state(k, k->plan.needs_gelu_lut);
   if (st != AKGB_OK) return st;
   if (k->nchunks > 1) return run_host_chunked(k, host);
   cudaError_t e;
@@ -430,7 +521,7 @@ akgb_status akgb_run_host(akgb_kernel* k, void* const* host) {
     e = cudaMemcpyAsync(k->d_tensors[i], host[i], (size_t)k->descs[i].nbytes, cudaMemcpyHostToDevice, k->stream);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(H2D)");
   }
-  st = run_plan(k, k->d_tensors.data(), k->d_workspace, k->stream);
+  st = run_plan(k, k->plan, k->d_tensors.data(), k->d_workspace, k->stream);
   if (st != AKGB_OK) return st;
   for (size_t i = k->n_inputs; i < k->descs.size(); ++i) {
     if (!k->descs[i].nbytes) continue;
@@ -451,7 +542,7 @@ akgb_status akgb_profile_host(akgb_kernel* k, void* const* host, int32_t number,
   cudaEventCreate(&t1);
   cudaEventRecord(t0, k->stream);
   for (int i = 0; i < number * repeat; ++i) {
-    st = run_plan(k, k->d_tensors.data(), k->d_workspace, k->stream);
+    st = run_plan(k, k->plan, k->d_tensors.data(), k->d_workspace, k->stream);
     if (st != AKGB_OK) break;
   }
   cudaEventRecord(t1, k->stream);
@@ -499,13 +590,14 @@ akgb_status akgb_kernel_meta(const akgb_kernel* k, char* buf, size_t cap, size_t
   if (!k) return fail(AKGB_INVALID_ARG, "null argument");
   // the keys the reference writes to <kernel>.json (GPUMapping.cpp:645-703,
   // mlir_driver.py:776-815); grid/block are those of the dominant (first) step
-  const Step& st = k->plan.steps.front();
+  static const Step kNoStep{};
+  const Step& st = k->plan.steps.empty() ? kNoStep : k->plan.steps.front();
   LaunchDims d = st.dims;
   std::ostringstream o;
   o << "{\"kernelName\": \"" << k->graph.kernel_name << "_kernel\", "
     << "\"blockIdx.x\": " << d.grid[0] << ", \"blockIdx.y\": " << d.grid[1] << ", \"blockIdx.z\": " << d.grid[2]
     << ", \"threadIdx.x\": " << d.block[0] << ", \"threadIdx.y\": " << d.block[1]
-    << ", \"threadIdx.z\": " << d.block[2] << ", \"is_dynamic\": false, \"sha256\": \"" << k->graph.sha256_hex
+    << ", \"threadIdx.z\": " << d.block[2] << ", \"is_dynamic\": " << (k->graph.dynamic ? "true" : "false") << ", \"sha256\": \"" << k->graph.sha256_hex
     << "\", \"class\": \"" << k->plan.klass << "\", \"template\": \"" << st.kernel_name
     << "\", \"bytes\": " << k->plan.bytes << ", \"flops\": " << k->plan.flops << ", \"smem\": " << d.smem
     << ", \"workspace\": " << k->plan.workspace_bytes << ", \"launches\": " << launches_of(k) << "}";

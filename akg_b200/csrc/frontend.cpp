@@ -87,7 +87,7 @@ std::vector<int64_t> shape_of(const Json& d) {
   std::vector<int64_t> s = d.at("shape").as_int_list();
   if (s.empty()) s.push_back(1);
   for (auto x : s)
-    if (x < 0) throw Unsupported("dynamic shape (negative extent) is not supported");
+    if (x < -1) throw JsonError("negative extent");
   return s;
 }
 
@@ -124,8 +124,7 @@ Graph parse_info(const char* text, size_t len) {
     if (ti->is_object() && ti->contains("compute_capability") && ti->at("compute_capability").is_string())
       g.compute_capability = ti->at("compute_capability").str;
   }
-  if (root.contains("symbol_calc_expr") && root.at("symbol_calc_expr").size() > 0)
-    throw Unsupported("dynamic-shape description (symbol_calc_expr) is not supported");
+  // symbol_calc_expr / symbolic_shape only name the unknown extents; they are bound from the launch-time shapes
 
   std::map<std::string, int> by_name;
   auto new_value = [&](const std::string& name, std::vector<int64_t> shape, DT dt) {
@@ -143,12 +142,6 @@ Graph parse_info(const char* text, size_t len) {
     if (!ind.is_array()) throw JsonError("input_desc must be a list");
     for (size_t i = 0; i < ind.size(); ++i) {
       const Json& d = ind[i].is_array() ? ind[i][0] : ind[i];
-      if (d.contains("symbolic_shape") && d.at("symbolic_shape").size() > 0) {
-        // static descriptions sometimes repeat the extents as strings; only reject real symbols
-        for (auto& s : d.at("symbolic_shape").arr)
-          if (s.is_string() && !s.str.empty() && !(s.str[0] >= '0' && s.str[0] <= '9'))
-            throw Unsupported("symbolic shapes are not supported");
-      }
       DT dt = dt_from_name(d.at("data_type").as_string());
       if (dt == DT::Invalid) throw Unsupported("data type '" + d.at("data_type").str + "' is not supported");
       const std::string& name = d.at("tensor_name").as_string();
@@ -359,10 +352,18 @@ Graph parse_info(const char* text, size_t len) {
     // change only; keep the op's shape when the element counts agree
     std::vector<int64_t> s = shape_of(d);
     int64_t n = 1;
-    for (auto x : s) n *= x;
-    if (n != v.numel()) throw JsonError("output '" + name + "' shape disagrees with its producer");
+    bool unknown = false;
+    for (auto x : s) {
+      n *= x;
+      unknown |= x < 0;
+    }
+    for (auto x : v.shape) unknown |= x < 0;
+    if (!unknown && n != v.numel()) throw JsonError("output '" + name + "' shape disagrees with its producer");
     g.outputs.push_back(it->second);
   }
+  for (auto& v : g.values)
+    for (auto x : v.shape)
+      if (x < 0) g.dynamic = true;
   classify(g);
   return g;
 }
@@ -494,6 +495,107 @@ void infer_sharding(Graph& g, int rank, int world) {
     }
   }
   (void)rank;
+}
+
+namespace {
+void merge_shape(std::vector<int64_t>& have, const std::vector<int64_t>& inferred, const std::string& what) {
+  if (have.size() != inferred.size()) {
+    // a declared shape of another rank wins only when it is fully known (e.g. Reshape targets)
+    for (auto x : have)
+      if (x < 0) throw JsonError("cannot infer the shape of '" + what + "'");
+    return;
+  }
+  for (size_t i = 0; i < have.size(); ++i) {
+    if (have[i] < 0) have[i] = inferred[i];
+    else if (inferred[i] >= 0 && have[i] != inferred[i])
+      throw JsonError("shape of '" + what + "' contradicts the launch-time extents");
+  }
+}
+}  // namespace
+
+Graph bind_shapes(const Graph& src, const std::vector<std::vector<int64_t>>& shapes) {
+  Graph g = src;
+  if (shapes.size() != g.inputs.size() + g.outputs.size()) throw JsonError("bind_shapes: wrong number of arguments");
+  auto bind_arg = [&](int vid, const std::vector<int64_t>& given) {
+    Value& v = g.v(vid);
+    if (given.size() != v.shape.size()) throw JsonError("argument '" + v.name + "': rank differs from the description");
+    for (size_t i = 0; i < given.size(); ++i) {
+      if (given[i] < 0) throw JsonError("argument '" + v.name + "': negative extent");
+      if (v.shape[i] >= 0 && v.shape[i] != given[i])
+        throw JsonError("argument '" + v.name + "': extent differs from the static extent of the description");
+      v.shape[i] = given[i];
+    }
+  };
+  for (size_t i = 0; i < g.inputs.size(); ++i) bind_arg(g.inputs[i], shapes[i]);
+  for (size_t i = 0; i < g.outputs.size(); ++i) bind_arg(g.outputs[i], shapes[g.inputs.size() + i]);
+  for (auto& n : g.nodes) {
+    Value& out = g.v(n.out);
+    std::vector<int64_t> inf;
+    const std::vector<int64_t>& x = g.v(n.in[0]).shape;
+    for (int vid : n.in)
+      for (auto e : g.v(vid).shape)
+        if (e < 0) throw JsonError("cannot infer the shape of operand '" + g.v(vid).name + "'");
+    if (opk_is_elementwise(n.kind)) {
+      size_t rank = 0;
+      for (int vid : n.in) rank = std::max(rank, g.v(vid).shape.size());
+      inf.assign(rank, 1);
+      for (int vid : n.in) {
+        const auto& s = g.v(vid).shape;
+        for (size_t i = 0; i < s.size(); ++i) {
+          int64_t& d = inf[rank - s.size() + i];
+          if (d == 1) d = s[i];
+          else if (s[i] != 1 && s[i] != d) throw JsonError("operands of '" + n.name + "' do not broadcast");
+        }
+      }
+    } else if (opk_is_reduce(n.kind)) {
+      std::vector<bool> red(x.size(), false);
+      for (auto a : n.axes) red[a] = true;
+      for (size_t i = 0; i < x.size(); ++i) {
+        if (!red[i]) inf.push_back(x[i]);
+        else if (n.keep_dims) inf.push_back(1);
+      }
+      if (inf.empty()) inf.push_back(1);
+    } else if (n.kind == OpK::Transpose) {
+      for (auto p : n.perm) inf.push_back(x[p]);
+    } else if (n.kind == OpK::MatMul || n.kind == OpK::BatchMatMul) {
+      const auto& b = g.v(n.in[1]).shape;
+      inf.assign(x.begin(), x.end() - 1);
+      inf.push_back(n.transpose_b ? b[b.size() - 2] : b[b.size() - 1]);
+    } else if (n.kind == OpK::Tile) {
+      for (size_t i = 0; i < x.size(); ++i) inf.push_back(x[i] * (i < n.multiples.size() ? n.multiples[i] : 1));
+    } else if (n.kind == OpK::Concat) {
+      inf = x;
+      inf[n.axis] = 0;
+      for (int vid : n.in) inf[n.axis] += g.v(vid).shape[n.axis];
+    } else if (n.kind == OpK::Reshape || n.kind == OpK::BroadcastTo) {
+      // the target is the declared output shape; one unknown extent follows from the element count
+      inf = out.shape;
+      int unknown = -1;
+      int64_t known = 1;
+      for (size_t i = 0; i < inf.size(); ++i) {
+        if (inf[i] < 0) {
+          if (unknown >= 0) throw JsonError("cannot infer the shape of '" + out.name + "'");
+          unknown = (int)i;
+        } else {
+          known *= inf[i];
+        }
+      }
+      if (unknown >= 0) {
+        if (n.kind != OpK::Reshape || known == 0) throw JsonError("cannot infer the shape of '" + out.name + "'");
+        int64_t total = 1;
+        for (auto e : x) total *= e;
+        inf[unknown] = total / known;
+      }
+    } else {
+      inf = out.shape;  // Slice / StridedSlice and the rest: static extents only
+    }
+    merge_shape(out.shape, inf, out.name);
+    for (auto e : out.shape)
+      if (e < 0) throw JsonError("cannot infer the shape of '" + out.name + "'");
+  }
+  g.dynamic = false;
+  classify(g);
+  return g;
 }
 
 // ----------------------------------------------------------------------------

@@ -113,6 +113,7 @@ struct Graph {
   OpClass op_class = OpClass::Elementwise;
   ReduceDir reduce_dir = ReduceDir::None;
   std::string sha256_hex;    // of the JSON text
+  bool dynamic = false;      // some extent is -1: shapes are bound at launch (bind_shapes)
 
   const Value& v(int id) const { return values[id]; }
   Value& v(int id) { return values[id]; }
@@ -134,6 +135,12 @@ void classify(Graph& g);
 // `world` and marks values as split / partial.  Throws Unsupported when the
 // region cannot be split on axis 0 without more than an all-reduce of outputs.
 void infer_sharding(Graph& g, int rank, int world);
+
+// Dynamic-shape regions (extents written as -1, the form MindSpore emits and the reference's --gpu-dyn-opt
+// pipeline consumes, akg-mlir/lib/Pipelines/GPUPipelines/GPUDynOpt.cpp:47-143): substitutes the extents of every
+// argument (inputs then outputs, `shapes[i]` = extents of argument i) and infers the shapes in between, op by op.
+// Returns a static copy of the graph; throws JsonError when the extents contradict the description.
+Graph bind_shapes(const Graph& g, const std::vector<std::vector<int64_t>>& shapes);
 
 std::string sha256_hex(const char* data, size_t len);
 

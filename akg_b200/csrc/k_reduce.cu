@@ -95,6 +95,73 @@ __global__ void __launch_bounds__(kColTx* kColTy) reduce_col_f32_kernel(const fl
   }
 }
 
+// Column reduction with Op1 and, in the same pass over x, a reduction of every element with Op2
+// (e.g. column sums and the global maximum of one tensor): x is read from HBM once.
+template <class Op1, class Op2>
+__global__ void __launch_bounds__(kColTx* kColTy) reduce_col_dual_f32_kernel(const float* __restrict__ x,
+                                                                             float* __restrict__ partial,
+                                                                             float* __restrict__ partial2, int64_t red,
+                                                                             int64_t inner, int64_t rows_per_split) {
+  __shared__ float4 sm[kColTy][kColTx];
+  __shared__ float red2[32];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int64_t col = ((int64_t)blockIdx.x * kColTx + tx) * 4;
+  const int64_t r0 = (int64_t)blockIdx.y * rows_per_split;
+  const int64_t r1 = min(red, r0 + rows_per_split);
+  const float id = Op1::identity(), id2 = Op2::identity();
+  float4 acc0 = make_float4(id, id, id, id), acc1 = acc0, acc2 = acc0, acc3 = acc0;
+  float4 b0 = make_float4(id2, id2, id2, id2), b1 = b0;
+  if (col < inner) {
+    const float* base = x + col;
+    int64_t r = r0 + ty;
+    for (; r + 3 * kColTy < r1; r += 4 * kColTy) {
+      const float4 a = ld_stream_f4(base + r * inner);
+      const float4 b = ld_stream_f4(base + (r + kColTy) * inner);
+      const float4 c = ld_stream_f4(base + (r + 2 * kColTy) * inner);
+      const float4 d = ld_stream_f4(base + (r + 3 * kColTy) * inner);
+      acc0 = apply4<Op1>(acc0, a);
+      acc1 = apply4<Op1>(acc1, b);
+      acc2 = apply4<Op1>(acc2, c);
+      acc3 = apply4<Op1>(acc3, d);
+      b0 = apply4<Op2>(b0, apply4<Op2>(a, b));
+      b1 = apply4<Op2>(b1, apply4<Op2>(c, d));
+    }
+    for (; r < r1; r += kColTy) {
+      const float4 a = ld_stream_f4(base + r * inner);
+      acc0 = apply4<Op1>(acc0, a);
+      b0 = apply4<Op2>(b0, a);
+    }
+  }
+  acc0 = apply4<Op1>(apply4<Op1>(acc0, acc1), apply4<Op1>(acc2, acc3));
+  sm[ty][tx] = acc0;
+  __syncthreads();
+#pragma unroll
+  for (int h = kColTy / 2; h > 0; h >>= 1) {
+    if (ty < h) sm[ty][tx] = apply4<Op1>(sm[ty][tx], sm[ty + h][tx]);
+    __syncthreads();
+  }
+  if (ty == 0) {
+    const float4 r = sm[0][tx];
+    float* o = partial + (int64_t)blockIdx.y * inner + col;
+    if (col + 0 < inner) o[0] = r.x;
+    if (col + 1 < inner) o[1] = r.y;
+    if (col + 2 < inner) o[2] = r.z;
+    if (col + 3 < inner) o[3] = r.w;
+  }
+  // second reduction: fold the CTA's values, one partial per CTA
+  b0 = apply4<Op2>(b0, b1);
+  float s2 = Op2::apply(Op2::apply(b0.x, b0.y), Op2::apply(b0.z, b0.w));
+  s2 = warp_reduce<Op2>(s2);
+  const int tid = ty * kColTx + tx, lane = tid & 31, warp = tid >> 5;
+  if (lane == 0) red2[warp] = s2;
+  __syncthreads();
+  if (warp == 0) {
+    float v = lane < (kColTx * kColTy) / 32 ? red2[lane] : id2;
+    v = warp_reduce<Op2>(v);
+    if (lane == 0) partial2[(int64_t)blockIdx.y * gridDim.x + blockIdx.x] = v;
+  }
+}
+
 // partial[splits, inner] -> out[inner], fixed order
 template <class Op>
 __global__ void __launch_bounds__(256) reduce_col_finish_kernel(const float* __restrict__ partial,
@@ -248,6 +315,63 @@ size_t reduce_col_workspace(int64_t red, int64_t inner, int sm_count) {
   return splits == 1 ? 0 : (size_t)(splits * inner) * sizeof(float);
 }
 size_t reduce_all_workspace(int sm_count) { return (size_t)sm_count * 8 * sizeof(float); }
+
+namespace {
+template <class Op1, class Op2>
+cudaError_t dual_impl(const float* x, float* out1, float* out2, int64_t red, int64_t inner, void* ws, int sm_count,
+                      cudaStream_t s, LaunchDims* dims) {
+  const int64_t splits = col_row_splits(red, inner, sm_count);
+  const int64_t rows_per_split = (red + splits - 1) / splits;
+  dim3 grid((unsigned)((inner + kColTile - 1) / kColTile), (unsigned)splits), block(kColTx, kColTy);
+  if (dims) {
+    dims->grid[0] = grid.x;
+    dims->grid[1] = grid.y;
+    dims->block[0] = block.x;
+    dims->block[1] = block.y;
+    dims->smem = sizeof(float4) * kColTx * kColTy + 128;
+  }
+  float* partial = reinterpret_cast<float*>(ws);
+  float* partial2 = partial + splits * inner;
+  reduce_col_dual_f32_kernel<Op1, Op2><<<grid, block, 0, s>>>(x, partial, partial2, red, inner, rows_per_split);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  reduce_col_finish_kernel<Op1><<<(unsigned)((inner + 255) / 256), 256, 0, s>>>(partial, out1, splits, inner);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  reduce_all_finish_kernel<Op2><<<1, 1024, 0, s>>>(partial2, out2, (int)(grid.x * grid.y));
+  return cudaGetLastError();
+}
+template <class Op1>
+cudaError_t dual_pick(RedOp op2, const float* x, float* o1, float* o2, int64_t red, int64_t inner, void* ws, int sms,
+                      cudaStream_t s, LaunchDims* dims) {
+  switch (op2) {
+    case RedOp::Sum: return dual_impl<Op1, SumOp>(x, o1, o2, red, inner, ws, sms, s, dims);
+    case RedOp::Max: return dual_impl<Op1, MaxOp>(x, o1, o2, red, inner, ws, sms, s, dims);
+    case RedOp::Min: return dual_impl<Op1, MinOp>(x, o1, o2, red, inner, ws, sms, s, dims);
+    case RedOp::Prod: return dual_impl<Op1, ProdOp>(x, o1, o2, red, inner, ws, sms, s, dims);
+  }
+  return cudaErrorInvalidValue;
+}
+}  // namespace
+
+bool reduce_col_dual_supported(int64_t inner, const void* x) {
+  return inner % 4 == 0 && (x == nullptr || aligned16(x));
+}
+size_t reduce_col_dual_workspace(int64_t red, int64_t inner, int sm_count) {
+  const int64_t splits = col_row_splits(red, inner, sm_count);
+  const int64_t ctas = splits * ((inner + kColTile - 1) / kColTile);
+  return (size_t)(splits * inner + ctas) * sizeof(float);
+}
+cudaError_t reduce_col_dual_f32(RedOp op1, RedOp op2, const float* x, float* out1, float* out2, int64_t red,
+                                int64_t inner, void* ws, int sm_count, cudaStream_t s, LaunchDims* dims) {
+  switch (op1) {
+    case RedOp::Sum: return dual_pick<SumOp>(op2, x, out1, out2, red, inner, ws, sm_count, s, dims);
+    case RedOp::Max: return dual_pick<MaxOp>(op2, x, out1, out2, red, inner, ws, sm_count, s, dims);
+    case RedOp::Min: return dual_pick<MinOp>(op2, x, out1, out2, red, inner, ws, sm_count, s, dims);
+    case RedOp::Prod: return dual_pick<ProdOp>(op2, x, out1, out2, red, inner, ws, sm_count, s, dims);
+  }
+  return cudaErrorInvalidValue;
+}
 
 #define AKGB_DISPATCH(fn, ...)                         \
   switch (op) {                                        \

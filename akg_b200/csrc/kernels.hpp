@@ -60,6 +60,12 @@ cudaError_t softmax_rows(const SoftmaxParams& p, const void* x, const void* mask
 size_t reduce_col_workspace(int64_t red, int64_t inner, int sm_count);
 cudaError_t reduce_col_f32(RedOp op, const float* x, float* out, int64_t red, int64_t inner, void* ws, int sm_count,
                            cudaStream_t s, LaunchDims* dims);
+// one pass over x: column reduction with op1 into out1[inner] and reduction of all elements with op2 into out2[1]
+// (inner % 4 == 0, x 16-byte aligned)
+bool reduce_col_dual_supported(int64_t inner, const void* x);
+size_t reduce_col_dual_workspace(int64_t red, int64_t inner, int sm_count);
+cudaError_t reduce_col_dual_f32(RedOp op1, RedOp op2, const float* x, float* out1, float* out2, int64_t red,
+                                int64_t inner, void* ws, int sm_count, cudaStream_t s, LaunchDims* dims);
 size_t reduce_all_workspace(int sm_count);
 cudaError_t reduce_all_f32(RedOp op, const float* x, float* out, int64_t n, void* ws, int sm_count, cudaStream_t s,
                            LaunchDims* dims);

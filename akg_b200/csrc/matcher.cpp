@@ -396,6 +396,23 @@ bool match_reduce(const Graph& g, Plan& plan, int sm_count) {
     steps.push_back(st);
   }
   if (!m.all_used()) return false;
+  // a column reduction and a reduction of all elements of the same tensor share one pass over it
+  if (steps.size() == 2) {
+    int ci = steps[0].kind == StepK::ReduceCol ? 0 : steps[1].kind == StepK::ReduceCol ? 1 : -1;
+    int ai = steps[0].kind == StepK::ReduceAll ? 0 : steps[1].kind == StepK::ReduceAll ? 1 : -1;
+    if (ci >= 0 && ai >= 0 && steps[ci].a.arg == steps[ai].a.arg && steps[ci].red_outer == 1 &&
+        steps[ai].red_len == steps[ci].red_len * steps[ci].red_inner && reduce_col_dual_supported(steps[ci].red_inner, nullptr)) {
+      Step st = steps[ci];
+      st.kind = StepK::ReduceColDual;
+      st.kernel_name = "reduce_col_dual_f32";
+      st.red_op2 = steps[ai].red_op;
+      st.out2 = steps[ai].out;
+      st.scratch.ws_off = 0;
+      ws = (std::max(reduce_col_dual_workspace(st.red_len, st.red_inner, sm_count),
+                     reduce_col_workspace(st.red_len, st.red_inner, sm_count) + reduce_all_workspace(sm_count)) + 255) / 256 * 256;
+      steps.assign(1, st);
+    }
+  }
   plan.klass = klass;
   plan.steps = steps;
   plan.workspace_bytes = ws;

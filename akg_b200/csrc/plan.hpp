@@ -18,7 +18,7 @@ struct Ref {
   bool valid() const { return arg >= 0 || ws_off >= 0; }
 };
 
-enum class StepK : int { GeluChain, LayerNorm, Softmax, ReduceCol, ReduceAll, ReduceRow, Transpose, Matmul, Ew };
+enum class StepK : int { GeluChain, LayerNorm, Softmax, ReduceCol, ReduceAll, ReduceRow, ReduceColDual, Transpose, Matmul, Ew };
 
 struct Step {
   StepK kind;
@@ -28,7 +28,7 @@ struct Step {
   GeluChainParams gelu;
   LayerNormParams ln;
   SoftmaxParams sm;
-  RedOp red_op = RedOp::Sum;
+  RedOp red_op = RedOp::Sum, red_op2 = RedOp::Max;
   int64_t red_outer = 1, red_len = 1, red_inner = 1;
   TransposeParams tp;
   MatmulParams mm;

@@ -66,6 +66,7 @@ class FusedKernel:
         self.op_class = lib.akgb_kernel_class(self._handle).decode()
         self.bytes = int(lib.akgb_kernel_bytes(self._handle))
         self.flops = int(lib.akgb_kernel_flops(self._handle))
+        self.is_dynamic = any(e < 0 for t in self.tensors for e in t.shape)
         self._workspace = None
 
     # -- lifetime ---------------------------------------------------------------
@@ -130,6 +131,8 @@ class FusedKernel:
         import torch
         if len(tensors) != len(self.tensors):
             raise ValueError(f"expected {len(self.tensors)} tensors, got {len(tensors)}")
+        if self.is_dynamic:
+            return self._launch_dynamic(tensors, stream)
         for t, d in zip(tensors, self.tensors):
             if not t.is_cuda or not t.is_contiguous():
                 raise ValueError(f"tensor '{d.name}' must be a contiguous CUDA tensor")
@@ -142,6 +145,35 @@ class FusedKernel:
             ws_ptr = (self._workspace.data_ptr() + 255) // 256 * 256
         s = stream if stream is not None else torch.cuda.current_stream(tensors[0].device)
         self.launch_ptrs([t.data_ptr() for t in tensors], ws_ptr, self.workspace_size, s.cuda_stream)
+
+    def bind_shapes(self, shapes: Sequence[Sequence[int]]) -> int:
+        """``akgb_bind_shapes``: plans a dynamic-shape region for these extents; returns the workspace bytes."""
+        flat = [int(e) for s in shapes for e in s]
+        arr = (ctypes.c_int64 * len(flat))(*flat)
+        ws = ctypes.c_size_t(0)
+        _capi.check(self._lib.akgb_bind_shapes(self._handle, arr, len(flat), ctypes.byref(ws)))
+        return int(ws.value)
+
+    def _launch_dynamic(self, tensors: Sequence, stream=None):
+        import torch
+        for t, d in zip(tensors, self.tensors):
+            if not t.is_cuda or not t.is_contiguous():
+                raise ValueError(f"tensor '{d.name}' must be a contiguous CUDA tensor")
+            if t.dim() != len(d.shape):
+                raise ValueError(f"tensor '{d.name}' has rank {t.dim()}, expected {len(d.shape)}")
+        flat = [int(e) for t in tensors for e in t.shape]
+        arr = (ctypes.c_int64 * len(flat))(*flat)
+        need = ctypes.c_size_t(0)
+        _capi.check(self._lib.akgb_bind_shapes(self._handle, arr, len(flat), ctypes.byref(need)))
+        ws_ptr = 0
+        if need.value:
+            if self._workspace is None or self._workspace.numel() < need.value + 256:
+                self._workspace = torch.empty(need.value + 256, dtype=torch.uint8, device=tensors[0].device)
+            ws_ptr = (self._workspace.data_ptr() + 255) // 256 * 256
+        s = stream if stream is not None else torch.cuda.current_stream(tensors[0].device)
+        ptrs = (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+        _capi.check(self._lib.akgb_launch_dynamic(self._handle, ptrs, arr, len(flat), ctypes.c_void_p(ws_ptr),
+                                                  need.value, ctypes.c_void_p(s.cuda_stream)))
 
     def _host_ptrs(self, arrays: Sequence[np.ndarray]):
         if len(arrays) != len(self.tensors):

@@ -209,6 +209,7 @@ def class_configs(world):
         ("masked_softmax_f16_256x2048x2048", descs.masked_softmax(256 * w, 2048, 2048), {"mask": "causal"}),
         ("reduce_sum_axis0_f32_65536x4096", descs.reduce_sum_axis0(65536 * w, 4096), {}),
         ("reduce_max_all_f32_65536x4096", descs.reduce_max_all(65536 * w, 4096), {}),
+        ("reduce_sum_and_max_f32_65536x4096", descs.reduce_sum_and_max(65536 * w, 4096), {}),
         ("transpose_f16_32x2048x32x128", descs.transpose([32 * w, 2048, 32, 128], [0, 2, 1, 3]), {}),
         ("matmul_bias_relu_bf16_8192x4096x8192", descs.matmul_bias_relu(8192 * w, 4096, 8192),
          {"a": "normal_small", "b": "normal_small", "bias": "normal_small"}),

@@ -111,6 +111,17 @@ int32_t akgb_launch_count(const akgb_kernel* k);
 akgb_status akgb_launch(akgb_kernel* k, void* const* tensors, void* workspace,
                         size_t workspace_bytes, void* stream);
 
+/* Dynamic-shape regions: descriptions whose extents contain -1 (the form MindSpore emits for unknown
+ * dims; the reference handles them with its --gpu-dyn-opt pipeline and passes sizes and strides of every
+ * tensor to the launcher, lib/Pipelines/GPUPipelines/GPUDynOpt.cpp:47-143,
+ * python/akg_mlir/utils/gen_runtime_code.py:39-58).  akgb_compile parses and classifies them; the kernel
+ * templates are chosen when the extents are known.  `shapes` lists, for every argument in order (inputs
+ * then outputs), all of its extents; `count` is their total number.  Plans are cached per set of extents.
+ * akgb_bind_shapes reports the workspace a launch with these extents needs. */
+akgb_status akgb_bind_shapes(akgb_kernel* k, const int64_t* shapes, size_t count, size_t* workspace_bytes);
+akgb_status akgb_launch_dynamic(akgb_kernel* k, void* const* tensors, const int64_t* shapes, size_t count,
+                                void* workspace, size_t workspace_bytes, void* stream);
+
 /* Same contract as the generated launcher's `cuda_runtime_exec`
  * (python/akg_mlir/utils/code_template.py:160-211): `host_tensors` are HOST
  * pointers, inputs then outputs; inputs are copied to the device, the fused op

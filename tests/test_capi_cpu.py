@@ -166,3 +166,39 @@ def test_generic_plan_splits_at_shape_changes(lib):
     k = FusedKernel(b.build())
     assert k.launch_count == 3 and k.workspace_size > 0 and k.op_class == "reduce_x"
     assert k.meta()["template"] == "ew_generic"
+
+
+def _dynamic_sub_mul_cast():
+    """The shape of region the reference's gpu_dynamic_shape test holds: Sub with a broadcast operand, Mul, Cast,
+    extents [32,16,-1,-1] and [32,16,-1,1]."""
+    from akg_b200.descs import _Builder, _attr
+    b = _Builder("Fused_Sub_Mul_Cast_dyn_40")
+    f = "float32"
+    x = b.input("input_0", [32, 16, -1, -1], f)
+    m = b.input("input_1", [32, 16, -1, 1], f)
+    y = b.input("input_2", [32, 16, -1, -1], f)
+    t = b.emit("Sub", [x, m], [32, 16, -1, -1], f)
+    t = b.emit("Mul", [y, t], [32, 16, -1, -1], f)
+    b.output(b.emit("Cast", [t], [32, 16, -1, -1], "float16", [_attr("dst_type", "str", "float16")]))
+    return b.build()
+
+
+def test_dynamic_shape_region_plans_per_extent_set(lib):
+    d = _dynamic_sub_mul_cast()
+    k = FusedKernel(d)
+    assert k.is_dynamic and k.meta()["is_dynamic"] is True
+    assert k.tensors[0].shape == (32, 16, -1, -1) and k.tensors[0].nbytes == -1
+    shapes = [[32, 16, 40, 24], [32, 16, 40, 1], [32, 16, 40, 24], [32, 16, 40, 24]]
+    assert k.bind_shapes(shapes) == 0            # one elementwise group: no workspace
+    assert k.bind_shapes(shapes) == 0            # cached
+    with pytest.raises(AkgbError):               # a static extent contradicted
+        k.bind_shapes([[31, 16, 40, 24], [32, 16, 40, 1], [32, 16, 40, 24], [32, 16, 40, 24]])
+    with pytest.raises(AkgbError):               # operands that do not broadcast
+        k.bind_shapes([[32, 16, 40, 24], [32, 16, 39, 1], [32, 16, 40, 24], [32, 16, 40, 24]])
+    with pytest.raises(AkgbError):               # wrong number of extents
+        k.bind_shapes([[32, 16, 40, 24]])
+    # a dynamic softmax: the row templates are chosen once the extents are known
+    s = descs.masked_softmax(-1, -1, 256)
+    ks = FusedKernel(s)
+    assert ks.is_dynamic
+    ks.bind_shapes([[4, 8, 256], [8, 256], [4, 8, 256]])

@@ -311,3 +311,48 @@ def test_batch_matmul(lib):
     want = O.evaluate(d, ins)[0]
     np.testing.assert_allclose(got[0], want, rtol=2e-3, atol=1e-3 * float(np.abs(want).max()))
     assert kern.launch_count == bsz
+
+
+def test_dynamic_shapes_match_the_static_plan(lib):
+    """A region described with -1 extents, launched with two different sets of extents, against the same region
+    compiled statically for each."""
+    import copy
+    import torch
+    from akg_b200.descs import _Builder, _attr
+
+    def region(s2, s3):
+        b = _Builder("Fused_Sub_Mul_Cast_dyn_40")
+        f = "float32"
+        x = b.input("input_0", [32, 16, s2, s3], f)
+        m = b.input("input_1", [32, 16, s2, 1], f)
+        y = b.input("input_2", [32, 16, s2, s3], f)
+        t = b.emit("Sub", [x, m], [32, 16, s2, s3], f)
+        t = b.emit("Mul", [y, t], [32, 16, s2, s3], f)
+        b.output(b.emit("Cast", [t], [32, 16, s2, s3], "float16", [_attr("dst_type", "str", "float16")]))
+        return b.build()
+
+    kd = FusedKernel(region(-1, -1), flags=FLAGS[0])
+    assert kd.is_dynamic
+    for s2, s3 in ((40, 24), (7, 129)):
+        static = region(s2, s3)
+        ins = make_inputs(static, 40 + s2)
+        want = O.evaluate(static, ins)[0]
+        dev = [torch.from_numpy(a).cuda() for a in ins]
+        out = torch.empty(want.shape, dtype=torch.float16, device="cuda")
+        kd.launch(dev + [out])
+        torch.cuda.synchronize()
+        assert bits_equal(out.cpu().numpy(), want)
+    # dynamic softmax and LayerNorm pick the row templates at launch
+    for desc_dyn, desc_static, kinds in (
+            (descs.masked_softmax(-1, -1, 256), descs.masked_softmax(6, 32, 256), {"mask": "causal"}),
+            (descs.layernorm(-1, 512), descs.layernorm(96, 512), {"gamma": "gamma", "beta": "beta"})):
+        k = FusedKernel(desc_dyn, flags=FLAGS[0])
+        ins = make_inputs(desc_static, 41, kinds)
+        want = O.evaluate(desc_static, ins)
+        dev = [torch.from_numpy(a).cuda() for a in ins]
+        outs = [torch.empty(w.shape, dtype=torch.float16 if w.dtype == np.float16 else torch.float32, device="cuda")
+                for w in want]
+        k.launch(dev + outs)
+        torch.cuda.synchronize()
+        for o, w in zip(outs, want):
+            np.testing.assert_allclose(o.cpu().numpy().astype(np.float32), w.astype(np.float32), rtol=2e-3, atol=1e-5)
