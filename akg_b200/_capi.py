@@ -44,6 +44,8 @@ class TensorDesc(ctypes.Structure):
         ("nbytes", ctypes.c_int64),
         ("is_output", ctypes.c_int32),
         ("shard_kind", ctypes.c_int32),
+        ("written_in_place", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
     ]
 
 

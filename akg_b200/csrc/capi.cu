@@ -219,6 +219,8 @@ void plan_chunks(akgb_kernel* k) {
   int64_t moved = 0;
   for (auto& d : k->descs) moved += d.nbytes;
   if (moved < (int64_t)64 << 20) return;  // too small to be worth several copies
+  for (auto& d : k->descs)
+    if (d.written_in_place) return;
   for (int n : {32, 16, 8, 4, 2}) {
     if (moved / n < ((int64_t)8 << 20)) continue;  // keep every copy large enough to run at full PCIe rate
     try {
@@ -385,6 +387,8 @@ akgb_status akgb_compile(const char* info_json, size_t len, const akgb_options* 
     };
     for (int vid : g.inputs) add(vid, false);
     for (int vid : g.outputs) add(vid, true);
+    for (auto& n : g.nodes)
+      if (n.kind == OpK::Assign && g.v(n.in[0]).input_index >= 0) k->descs[g.v(n.in[0]).input_index].written_in_place = 1;
   } catch (const JsonError& e) {
     delete k;
     return fail(AKGB_INVALID_JSON, e.what());
@@ -523,8 +527,9 @@ akgb_status akgb_run_host(akgb_kernel* k, void* const* host) {
   }
   st = run_plan(k, k->plan, k->d_tensors.data(), k->d_workspace, k->stream);
   if (st != AKGB_OK) return st;
-  for (size_t i = k->n_inputs; i < k->descs.size(); ++i) {
+  for (size_t i = 0; i < k->descs.size(); ++i) {
     if (!k->descs[i].nbytes) continue;
+    if ((int)i < k->n_inputs && !k->descs[i].written_in_place) continue;
     e = cudaMemcpyAsync(host[i], k->d_tensors[i], (size_t)k->descs[i].nbytes, cudaMemcpyDeviceToHost, k->stream);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(D2H)");
   }

@@ -162,6 +162,9 @@ struct Builder {
     std::map<int, int> last_use;
     for (size_t gi = 0; gi < group.size(); ++gi)
       for (int vid : g.nodes[group[gi]].in) last_use[vid] = (int)gi;
+    for (size_t gi = 0; gi < group.size(); ++gi)  // values stored by an Assign stay live to the end
+      if (g.nodes[group[gi]].kind == OpK::Assign)
+        for (int vid : g.nodes[group[gi]].in) last_use[vid] = (int)group.size();
     std::map<int, int> reg_of;  // value id -> register
     std::set<int> external;     // operands that come from outside the group
     std::vector<int> free_regs;
@@ -245,6 +248,34 @@ struct Builder {
       std::memset(&ins, 0, sizeof(ins));
       EwOp op;
       const bool view_copy = n.kind == OpK::Tile || n.kind == OpK::Slice || n.kind == OpK::StridedSlice;
+      if (n.kind == OpK::Assign) {
+        // Assign(dst, value): the value is stored into the caller's dst tensor and is also the op's result;
+        // InplaceAssign(dst, value, passthrough): same store, the result is the third operand
+        // (MindSporeToLinalg.cpp:495-524; op_dsl.py:956-961, 1032-1037)
+        const int dstv = n.in[0];
+        const Value& dv = g.v(dstv);
+        if (dv.input_index < 0) throw Unsupported("Assign target must be an input of the region");
+        if (dv.shape != S || n.in.size() < 2 || g.v(n.in[1]).dt != dv.dt)
+          throw Unsupported("Assign needs a value of the target's shape and type");
+        const int val_reg = operand_reg(n.in[1]);
+        const int res_reg = n.in.size() >= 3 ? operand_reg(n.in[2]) : val_reg;
+        if (P.n_out + 2 > kEwMaxOut) throw Unsupported("elementwise group with more than 6 results");
+        EwOperand& od = P.out[P.n_out++];
+        od.dt = (int)dv.dt;
+        od.kind = EWI_FULL;
+        od.reg = val_reg;
+        st.ew_out.push_back(arg_ref(dstv));
+        reg_of[n.out] = res_reg;
+        external.insert(n.out);  // shares a register with its source: never recycled
+        if (used_outside_group(n.out)) {
+          EwOperand& oo = P.out[P.n_out++];
+          oo.dt = (int)out.dt;
+          oo.kind = EWI_FULL;
+          oo.reg = res_reg;
+          st.ew_out.push_back(buffer(n.out));
+        }
+        continue;
+      }
       if (n.kind == OpK::Reshape || view_copy) op = EW_COPY;
       else if (n.kind == OpK::AddN) op = EW_ADD;
       else if (!ew_opcode(n.kind, &op)) throw Unsupported(std::string("op '") + n.name + "' in an elementwise group");
@@ -376,12 +407,37 @@ struct Builder {
       case OpK::ReduceMax: op = RedOp::Max; break;
       case OpK::ReduceMin: op = RedOp::Min; break;
       case OpK::ReduceProd: op = RedOp::Prod; break;
+      case OpK::ReduceAll: op = RedOp::Min; break;  // over 0/1 values
+      case OpK::ReduceAny: op = RedOp::Max; break;
       default: throw Unsupported(std::string("reduction '") + n.name + "' is not placed");
     }
     const Value& x = g.v(n.in[0]);
-    if (x.dt != DT::F32 || g.v(n.out).dt != DT::F32)
-      throw Unsupported("only float32 reductions are placed (cast before reducing, as the float16 accumulator of the "
-                        "reference's CPU pipeline and its float32 expected-value generator disagree)");
+    const Value& ov = g.v(n.out);
+    const bool narrow = x.dt == DT::F16 || x.dt == DT::BF16 || x.dt == DT::Bool;
+    if (!(x.dt == DT::F32 || narrow) || ov.dt != x.dt)
+      throw Unsupported(std::string("reduction over ") + dt_name(x.dt) + " is not placed");
+    if ((n.kind == OpK::ReduceAll || n.kind == OpK::ReduceAny) != (x.dt == DT::Bool))
+      throw Unsupported("ReduceAll/ReduceAny take bool, the arithmetic reductions do not");
+    // float16 / bfloat16 / bool inputs are widened to float32, reduced there and narrowed once at the end: the
+    // accumulator type of the reference's expected-value generator (op_dsl.py:126-154).  Its CPU pipeline
+    // accumulates in the narrow type instead (MindSporeToLinalg.cpp:1344, 1401-1426); descriptions that need
+    // that behaviour pinned should cast explicitly.
+    Ref src = buffer(n.in[0]), dst = buffer(n.out);
+    if (narrow) {
+      Ref wide_in, wide_out;
+      wide_in.ws_off = (int64_t)ws;
+      ws += ((size_t)x.numel() * 4 + 255) / 256 * 256;
+      wide_out.ws_off = (int64_t)ws;
+      ws += ((size_t)ov.numel() * 4 + 255) / 256 * 256;
+      add_convert(src, (int)x.dt, wide_in, (int)DT::F32, x.numel());
+      pending_narrow = true;
+      narrow_src = wide_out;
+      narrow_dst = dst;
+      narrow_dt = (int)ov.dt;
+      narrow_n = ov.numel();
+      src = wide_in;
+      dst = wide_out;
+    }
     std::vector<bool> red(x.shape.size(), false);
     for (auto a : n.axes) red[a] = true;
     int64_t outer = 1, len = 1, inner = 1;
@@ -402,8 +458,8 @@ struct Builder {
     st.red_outer = outer;
     st.red_len = len;
     st.red_inner = inner;
-    st.a = buffer(n.in[0]);
-    st.out = buffer(n.out);
+    st.a = src;
+    st.out = dst;
     if (inner == 1 && outer == 1) {
       st.kind = StepK::ReduceAll;
       st.kernel_name = "reduce_all_f32";
@@ -421,6 +477,49 @@ struct Builder {
       st.scratch.ws_off = (int64_t)ws;
       ws += (reduce_col_workspace(len, inner, sm_count) + 255) / 256 * 256;
     }
+    plan.steps.push_back(std::move(st));
+    if (pending_narrow) {
+      add_convert(narrow_src, (int)DT::F32, narrow_dst, narrow_dt, narrow_n);
+      pending_narrow = false;
+    }
+  }
+
+  bool pending_narrow = false;
+  Ref narrow_src, narrow_dst;
+  int narrow_dt = 0;
+  int64_t narrow_n = 0;
+
+  // one elementwise launch that converts n elements from one type to another (Cast semantics)
+  void add_convert(const Ref& from, int from_dt, const Ref& to, int to_dt, int64_t n) {
+    Step st;
+    st.kind = StepK::Ew;
+    st.kernel_name = "ew_generic";
+    EwProgram& P = st.ew;
+    std::memset(&P, 0, sizeof(P));
+    P.rank = 1;
+    P.n = n;
+    P.shape[0] = n;
+    P.n_in = 1;
+    P.in[0].dt = from_dt;
+    P.in[0].kind = EWI_FULL;
+    P.in[0].reg = 0;
+    EwInstr ins;
+    std::memset(&ins, 0, sizeof(ins));
+    ins.op = EW_CAST;
+    ins.dt = (uint8_t)to_dt;
+    ins.cls = cls_of((DT)to_dt);
+    ins.src_cls = cls_of((DT)from_dt);
+    ins.a = 0;
+    ins.dst = 1;
+    P.instr[0] = ins;
+    P.n_instr = 1;
+    P.n_out = 1;
+    P.out[0].dt = to_dt;
+    P.out[0].kind = EWI_FULL;
+    P.out[0].reg = 1;
+    P.n_reg = 2;
+    st.ew_in.push_back(from);
+    st.ew_out.push_back(to);
     plan.steps.push_back(std::move(st));
   }
 
@@ -611,7 +710,8 @@ struct Builder {
         add_concat(n);
         continue;
       }
-      if (opk_is_elementwise(n.kind) || n.kind == OpK::BroadcastTo || n.kind == OpK::Reshape || view_copy) {
+      if (opk_is_elementwise(n.kind) || n.kind == OpK::BroadcastTo || n.kind == OpK::Reshape || view_copy ||
+          n.kind == OpK::Assign) {
         const std::vector<int64_t>& S = g.v(n.out).shape;
         if (!group.empty() && group_shape != S) flush_group();
         // an operand that views a value still being computed in the open group must be materialised first

@@ -31,6 +31,7 @@ class TensorInfo:
     nbytes: int
     is_output: bool
     shard_kind: int
+    written_in_place: bool = False
 
 
 def _np_dtype(name: str):
@@ -60,7 +61,7 @@ class FusedKernel:
             _capi.check(lib.akgb_tensor_info(self._handle, i, ctypes.byref(d)))
             self.tensors.append(TensorInfo(d.name.decode(), _capi.DTYPE_NAMES[d.dtype],
                                            tuple(d.shape[j] for j in range(d.rank)), int(d.nbytes),
-                                           bool(d.is_output), int(d.shard_kind)))
+                                           bool(d.is_output), int(d.shard_kind), bool(d.written_in_place)))
         self.num_inputs = lib.akgb_num_inputs(self._handle)
         self.workspace_size = int(lib.akgb_workspace_size(self._handle))
         self.op_class = lib.akgb_kernel_class(self._handle).decode()

@@ -66,6 +66,10 @@ typedef struct akgb_tensor_desc {
   int64_t nbytes;                /* local size in bytes */
   int32_t is_output;
   int32_t shard_kind;            /* akgb_shard_kind */
+  int32_t written_in_place;      /* an INPUT that an Assign/InplaceAssign of the region stores into; the reference
+                                    harness treats such inputs as extra outputs
+                                    (python/akg_mlir/utils/composite_op_helper.py:791-805) */
+  int32_t reserved;
 } akgb_tensor_desc;
 
 typedef struct akgb_options {

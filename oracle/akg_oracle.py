@@ -137,8 +137,9 @@ def _reduce(kind: str, x: np.ndarray, axes: tuple, keep: bool, accum: str) -> np
     return getattr(np, kind)(src, axis=axes, keepdims=keep).astype(dt)
 
 
-def evaluate(desc: dict | str, inputs: Sequence[np.ndarray], accum: str = "numpy") -> list[np.ndarray]:
-    """Evaluates the description on `inputs` (input_desc order); returns outputs in output_desc order."""
+def evaluate(desc: dict | str, inputs: Sequence[np.ndarray], accum: str = "numpy", return_inputs: bool = False):
+    """Evaluates the description on `inputs` (input_desc order); returns outputs in output_desc order (and, with
+    `return_inputs`, the inputs as they stand afterwards: Assign/InplaceAssign store into them)."""
     if isinstance(desc, (str, bytes)):
         desc = json.loads(desc)
     env: dict[str, np.ndarray] = {}
@@ -220,6 +221,24 @@ def evaluate(desc: dict | str, inputs: Sequence[np.ndarray], accum: str = "numpy
                 axes = tuple(sorted({a + x.ndim if a < 0 else a for a in axes}))
                 keep = bool(_attr(attrs, "keep_dims", False))
                 r = _reduce(_REDUCE[name], x, axes, keep, accum)
+            elif name in ("Assign", "InplaceAssign"):
+                # the value lands in the caller's first operand; the result is the value (Assign) or the third
+                # operand (InplaceAssign) — op_dsl.py:956-961, 1032-1037
+                val = operand(ins[1])
+                env[ins[0]["tensor_name"]] = np.array(val, dtype=val.dtype).reshape(env[ins[0]["tensor_name"]].shape)
+                r = val if name == "Assign" or len(ins) < 3 else operand(ins[2])
+            elif name in ("ReduceAll", "ReduceAny", "ElemAny"):
+                x = operand(ins[0])
+                axes = _attr(attrs, "axis")
+                if (axes is None or axes == []) and len(ins) == 2:
+                    axes = ins[1]["value"]
+                if axes is None or axes == [] or name == "ElemAny":
+                    axes = list(range(x.ndim))
+                if not isinstance(axes, (list, tuple)):
+                    axes = [axes]
+                axes = tuple(sorted({a + x.ndim if a < 0 else a for a in axes}))
+                fn = np.all if name == "ReduceAll" else np.any
+                r = fn(x, axis=axes, keepdims=bool(_attr(attrs, "keep_dims", False)) or name == "ElemAny")
             elif name == "AddN":
                 r = operand(ins[0])
                 for other in ins[1:]:
@@ -273,4 +292,7 @@ def evaluate(desc: dict | str, inputs: Sequence[np.ndarray], accum: str = "numpy
                 raise NotImplementedError(f"op {name}")
         env[out["tensor_name"]] = np.ascontiguousarray(np.asarray(r, dtype=odt if name not in _COMPARE else None)
                                                        ).reshape(oshape)
-    return [env[o["tensor_name"]].reshape(o.get("shape") or [1]) for o in desc["output_desc"]]
+    outs = [env[o["tensor_name"]].reshape(o.get("shape") or [1]) for o in desc["output_desc"]]
+    if return_inputs:
+        return outs, [env[d["tensor_name"]] for (d,) in desc["input_desc"] or []]
+    return outs

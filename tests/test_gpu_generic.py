@@ -356,3 +356,65 @@ def test_dynamic_shapes_match_the_static_plan(lib):
         torch.cuda.synchronize()
         for o, w in zip(outs, want):
             np.testing.assert_allclose(o.cpu().numpy().astype(np.float32), w.astype(np.float32), rtol=2e-3, atol=1e-5)
+
+
+def test_assign_writes_the_input_in_place(lib):
+    # x <- x + 1 (the reference's Fused_AssignAdd) and an optimizer-like update with Select
+    b = _Builder("Fused_AssignAdd_50")
+    i = "int32"
+    x = b.input("input_0", [1], i)
+    t = b.emit("Add", [x, b.const(1, i)], [1], i)
+    b.output(b.emit("Assign", [x, t], [1], i))
+    d = b.build()
+    k = FusedKernel(d, flags=FLAGS[0])
+    assert k.inputs[0].written_in_place
+    xin = np.array([41], dtype=np.int32)
+    out = np.zeros(1, np.int32)
+    k.run_host([xin, out])
+    assert xin[0] == 42 and out[0] == 42
+
+    b = _Builder("Fused_Mul_Maximum_Select_Assign_51")
+    f = "float32"
+    w = b.input("w", [300, 40], f)
+    g_ = b.input("g", [300, 40], f)
+    m = b.input("m", [300, 40], "bool")
+    t = b.emit("Mul", [g_, b.const(0.5, f)], [300, 40], f)
+    t = b.emit("Maximum", [t, b.const(-0.25, f)], [300, 40], f)
+    t = b.emit("Select", [m, b.emit("Sub", [w, t], [300, 40], f), w], [300, 40], f)
+    b.output(b.emit("Assign", [w, t], [300, 40], f))
+    d = b.build()
+    rng = np.random.default_rng(51)
+    ins = [rng.standard_normal((300, 40)).astype(np.float32), rng.standard_normal((300, 40)).astype(np.float32),
+           rng.integers(0, 2, (300, 40)).astype(bool)]
+    want_out, want_in = O.evaluate(d, [a.copy() for a in ins], return_inputs=True)
+    k = FusedKernel(d, flags=FLAGS[0])
+    host = [a.copy() for a in ins] + k.empty_outputs()
+    k.run_host(host)
+    assert bits_equal(host[3], want_out[0]) and bits_equal(host[0], want_in[0])
+    assert bits_equal(host[1], ins[1])  # other inputs untouched
+
+
+def test_narrow_and_bool_reductions(lib):
+    """float16 / bfloat16 reductions accumulate in float32 and round once (the expected-value generator's rule,
+    op_dsl.py:126-154); ReduceAll / ReduceAny over bool."""
+    for dt, tol in (("float16", 2e-3), ("bfloat16", 1e-2)):
+        b = _Builder("Fused_ReduceSum_f16_52")
+        x = b.input("x", [64, 300], dt)
+        b.output(b.emit("ReduceSum", [x], [64, 1], dt, _reduce_attr([1], True)))
+        b.output(b.emit("ReduceMax", [x], [300], dt, _reduce_attr([0], False)))
+        d = b.build()
+        ins = make_inputs(d, 52)
+        got, _ = run(d, ins)
+        want = O.evaluate(d, ins)
+        np.testing.assert_allclose(got[0].astype(np.float32), want[0].astype(np.float32), rtol=tol, atol=tol)
+        assert bits_equal(got[1], want[1])
+    b = _Builder("Fused_ReduceAll_53")
+    x = b.input("x", [50, 70], "bool")
+    b.output(b.emit("ReduceAll", [x], [50], "bool", _reduce_attr([1], False)))
+    b.output(b.emit("ReduceAny", [x], [1], "bool", _reduce_attr([0, 1], False)))
+    d = b.build()
+    rng = np.random.default_rng(53)
+    xb = rng.random((50, 70)) < 0.97
+    xb[3, :] = True
+    got, _ = run(d, [xb])
+    assert np.array_equal(got[0], xb.all(axis=1)) and bool(got[1][0]) == bool(xb.any())
