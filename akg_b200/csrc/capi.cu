@@ -147,6 +147,13 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
           e = reduce_col_f32(st.red_op, (const float*)a + bi * st.red_batch_in, (float*)o + bi * st.red_batch_out,
                              st.red_len, st.red_inner, scratch, k->sm_count, s, &st.dims);
         break;
+      case StepK::Gather:
+        e = gather_rows(a, b, o, st.ix_outer, st.ix_dim, st.ix_n, st.ix_inner, st.ix_esize, st.ix_idx64, s, &st.dims);
+        break;
+      case StepK::SegmentSum:
+        e = segment_sum_f32((const float*)a, b, (float*)o, st.ix_n, st.ix_inner, st.ix_segments, st.ix_idx64, s,
+                            &st.dims);
+        break;
       case StepK::Ew: {
         const void* ins[kEwMaxIn];
         void* outs[kEwMaxOut];

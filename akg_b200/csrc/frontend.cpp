@@ -65,7 +65,7 @@ const OpEntry kOps[] = {
     {"ElemAny", OpK::ReduceAny}, {"MatMul", OpK::MatMul},     {"BatchMatMul", OpK::BatchMatMul},
     {"Assign", OpK::Assign},     {"InplaceAssign", OpK::Assign}, {"AddN", OpK::AddN},
     {"Tile", OpK::Tile},         {"Slice", OpK::Slice},       {"StridedSlice", OpK::StridedSlice},
-    {"Concat", OpK::Concat},
+    {"Concat", OpK::Concat},     {"Gather", OpK::Gather},     {"UnsortedSegmentSum", OpK::UnsortedSegmentSum},
 };
 }  // namespace
 
@@ -184,6 +184,7 @@ Graph parse_info(const char* text, size_t len) {
       for (size_t j = 0; j < ins.size(); ++j) {
         if (j == 1 && attr_as_second_input(n.name)) continue;  // attribute operand, read below
         if (j >= 1 && n.kind == OpK::StridedSlice) continue;
+        if (j >= 2 && (n.kind == OpK::Gather || n.kind == OpK::UnsortedSegmentSum)) continue;  // axis / num_segments
         operand_descs.push_back(ins[j].is_array() ? &ins[j][0] : &ins[j]);
       }
     }
@@ -328,6 +329,27 @@ Graph parse_info(const char* text, size_t len) {
         n.end.push_back(xs[i]);
         n.strides.push_back(1);
       }
+    } else if (n.kind == OpK::Gather) {
+      // axis from a constant third operand or the attribute; batch_dims must be 0 (MindSporeToLinalg.cpp:543-550)
+      if (ins.size() > 2) {
+        const Json& d2 = ins[2].is_array() ? ins[2][0] : ins[2];
+        n.axis = d2.at("value").as_int();
+      } else if (const Json* a = find_attr(attrs, "axis")) {
+        n.axis = a->as_int();
+      }
+      if (n.axis < 0) n.axis += in_rank;
+      const Json* bd = find_attr(attrs, "batch_dims");
+      if (bd && bd->as_int() != 0) throw Unsupported("Gather with batch_dims != 0");
+    } else if (n.kind == OpK::UnsortedSegmentSum) {
+      if (ins.size() > 2) {
+        const Json& d2 = ins[2].is_array() ? ins[2][0] : ins[2];
+        n.num_segments = d2.at("value").as_int();
+      } else if (const Json* a = find_attr(attrs, "num_segments")) {
+        n.num_segments = a->as_int();
+      } else if (const Json* a2 = find_attr(attrs, "numSegments")) {
+        n.num_segments = a2->as_int();
+      }
+      if (n.num_segments <= 0) throw JsonError("UnsortedSegmentSum needs num_segments");
     } else if (n.kind == OpK::Concat) {
       const Json* a = find_attr(attrs, "axis");
       n.axis = a ? a->as_int() : 0;
@@ -563,6 +585,15 @@ Graph bind_shapes(const Graph& src, const std::vector<std::vector<int64_t>>& sha
       inf.push_back(n.transpose_b ? b[b.size() - 2] : b[b.size() - 1]);
     } else if (n.kind == OpK::Tile) {
       for (size_t i = 0; i < x.size(); ++i) inf.push_back(x[i] * (i < n.multiples.size() ? n.multiples[i] : 1));
+    } else if (n.kind == OpK::Gather) {
+      const auto& ix = g.v(n.in[1]).shape;
+      inf.assign(x.begin(), x.begin() + n.axis);
+      inf.insert(inf.end(), ix.begin(), ix.end());
+      inf.insert(inf.end(), x.begin() + n.axis + 1, x.end());
+    } else if (n.kind == OpK::UnsortedSegmentSum) {
+      const auto& ix = g.v(n.in[1]).shape;
+      inf.push_back(n.num_segments);
+      inf.insert(inf.end(), x.begin() + ix.size(), x.end());
     } else if (n.kind == OpK::Concat) {
       inf = x;
       inf[n.axis] = 0;

@@ -47,6 +47,8 @@ enum class OpK : int {
   ReduceSum, ReduceMax, ReduceMin, ReduceProd, ReduceAll, ReduceAny,
   // contractions
   MatMul, BatchMatMul,
+  // index ops
+  Gather, UnsortedSegmentSum,
   // in-place
   Assign,
   Unknown
@@ -99,6 +101,7 @@ struct Node {
   // Tile: multiples; Slice: begin/size; StridedSlice: begin/end/strides (masks already applied); Concat: axis
   std::vector<int64_t> multiples, begin, size, end, strides;
   int64_t axis = 0;
+  int64_t num_segments = 0;  // UnsortedSegmentSum
   bool enable_atomic_add = false;
 };
 

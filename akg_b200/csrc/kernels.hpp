@@ -81,6 +81,14 @@ cudaError_t ew_generic(const EwProgram& p, const void* const* in, void* const* o
 std::string ew_jit_source(const EwProgram& p, bool vec);
 cudaError_t ew_jit_launch(const EwProgram& p, const void* const* in, void* const* out, cudaStream_t s, LaunchDims* dims);
 
+// ---- index ops ---------------------------------------------------------------------
+// out[o, i, r] = data[o, idx[i], r]; data is [outer, dim, inner] elements of `esize` bytes; idx int32 or int64
+cudaError_t gather_rows(const void* data, const void* idx, void* out, int64_t outer, int64_t dim, int64_t nidx,
+                        int64_t inner, int esize, int idx64, cudaStream_t s, LaunchDims* dims);
+// out[num_segments, inner] = 0; out[ids[i], :] += data[i, :]
+cudaError_t segment_sum_f32(const float* data, const void* ids, float* out, int64_t nids, int64_t inner,
+                            int64_t num_segments, int idx64, cudaStream_t s, LaunchDims* dims);
+
 // ---- transpose -----------------------------------------------------------------
 // General permutation of up to 6 folded dims over elements of `esize` bytes.
 struct TransposeParams {

@@ -18,7 +18,7 @@ struct Ref {
   bool valid() const { return arg >= 0 || ws_off >= 0; }
 };
 
-enum class StepK : int { GeluChain, LayerNorm, Softmax, ReduceCol, ReduceAll, ReduceRow, ReduceColDual, Transpose, Matmul, Ew };
+enum class StepK : int { GeluChain, LayerNorm, Softmax, ReduceCol, ReduceAll, ReduceRow, ReduceColDual, Transpose, Matmul, Ew, Gather, SegmentSum };
 
 struct Step {
   StepK kind;
@@ -34,6 +34,8 @@ struct Step {
   MatmulParams mm;
   EwProgram ew;              // StepK::Ew
   std::vector<Ref> ew_in, ew_out;
+  int64_t ix_outer = 1, ix_dim = 1, ix_n = 1, ix_inner = 1, ix_segments = 0;  // Gather / SegmentSum extents
+  int ix_esize = 4, ix_idx64 = 0;
   int64_t mm_batch = 1, mm_stride_a = 0, mm_stride_b = 0, mm_stride_o = 0;  // BatchMatMul: byte strides per entry
   int64_t red_batch_in = 0, red_batch_out = 0;  // batched column reductions: element stride per outer index
   LaunchDims dims;          // filled at first launch

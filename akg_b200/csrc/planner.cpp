@@ -600,6 +600,47 @@ struct Builder {
     if (pos != out.shape[n.axis]) throw JsonError("Concat extents do not add up to the output");
   }
 
+  void add_gather(const Node& n) {
+    const Value& data = g.v(n.in[0]);
+    const Value& idx = g.v(n.in[1]);
+    if (idx.dt != DT::I32 && idx.dt != DT::I64) throw Unsupported("Gather indices must be int32 or int64");
+    if (n.axis < 0 || n.axis >= (int64_t)data.shape.size()) throw JsonError("Gather axis out of range");
+    Step st;
+    st.kind = StepK::Gather;
+    st.kernel_name = "gather_rows";
+    st.a = buffer(n.in[0]);
+    st.b = buffer(n.in[1]);
+    st.out = buffer(n.out);
+    for (int64_t i = 0; i < n.axis; ++i) st.ix_outer *= data.shape[i];
+    st.ix_dim = data.shape[n.axis];
+    for (size_t i = n.axis + 1; i < data.shape.size(); ++i) st.ix_inner *= data.shape[i];
+    st.ix_n = idx.numel();
+    st.ix_esize = (int)dt_size(data.dt);
+    st.ix_idx64 = idx.dt == DT::I64;
+    if (g.v(n.out).numel() != st.ix_outer * st.ix_n * st.ix_inner) throw JsonError("Gather output shape");
+    plan.steps.push_back(std::move(st));
+  }
+
+  void add_segment_sum(const Node& n) {
+    const Value& data = g.v(n.in[0]);
+    const Value& ids = g.v(n.in[1]);
+    if (data.dt != DT::F32 || g.v(n.out).dt != DT::F32) throw Unsupported("UnsortedSegmentSum over float32 only");
+    if (ids.dt != DT::I32 && ids.dt != DT::I64) throw Unsupported("segment ids must be int32 or int64");
+    Step st;
+    st.kind = StepK::SegmentSum;
+    st.kernel_name = "segment_sum_f32";
+    st.a = buffer(n.in[0]);
+    st.b = buffer(n.in[1]);
+    st.out = buffer(n.out);
+    st.ix_n = ids.numel();
+    if (st.ix_n == 0 || data.numel() % st.ix_n) throw JsonError("UnsortedSegmentSum: ids do not divide the data");
+    st.ix_inner = data.numel() / st.ix_n;
+    st.ix_segments = n.num_segments;
+    st.ix_idx64 = ids.dt == DT::I64;
+    if (g.v(n.out).numel() != st.ix_segments * st.ix_inner) throw JsonError("UnsortedSegmentSum output shape");
+    plan.steps.push_back(std::move(st));
+  }
+
   void add_matmul(const Node& n) {
     if (n.kind == OpK::BatchMatMul) {
       add_batch_matmul(n);
@@ -727,6 +768,8 @@ struct Builder {
       if (opk_is_reduce(n.kind)) add_reduce(n);
       else if (n.kind == OpK::Transpose) add_transpose(n);
       else if (n.kind == OpK::MatMul || n.kind == OpK::BatchMatMul) add_matmul(n);
+      else if (n.kind == OpK::Gather) add_gather(n);
+      else if (n.kind == OpK::UnsortedSegmentSum) add_segment_sum(n);
       else throw Unsupported(std::string("operator '") + n.name + "' is not supported");
     }
     flush_group();

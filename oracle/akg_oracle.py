@@ -239,6 +239,19 @@ def evaluate(desc: dict | str, inputs: Sequence[np.ndarray], accum: str = "numpy
                 axes = tuple(sorted({a + x.ndim if a < 0 else a for a in axes}))
                 fn = np.all if name == "ReduceAll" else np.any
                 r = fn(x, axis=axes, keepdims=bool(_attr(attrs, "keep_dims", False)) or name == "ElemAny")
+            elif name == "Gather":
+                axis = _attr(attrs, "axis", 0)
+                if len(op["input_desc"]) > 2:
+                    axis = op["input_desc"][2][0]["value"]
+                r = np.take(operand(ins[0]), operand(ins[1]), axis)  # op_dsl.py:101-104, 1119-1125
+            elif name == "UnsortedSegmentSum":
+                data, ids = operand(ins[0]), operand(ins[1])
+                nseg = _attr(attrs, "num_segments") or _attr(attrs, "numSegments")
+                if nseg is None and len(op["input_desc"]) > 2:
+                    nseg = op["input_desc"][2][0]["value"]
+                r = np.zeros([nseg] + list(data.shape[ids.ndim:]), dtype=np.float64)
+                np.add.at(r, ids, data.astype(np.float64))  # op_dsl.py:1109-1116, accumulated in float64 here
+                r = r.astype(odt)
             elif name == "AddN":
                 r = operand(ins[0])
                 for other in ins[1:]:

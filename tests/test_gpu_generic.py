@@ -418,3 +418,34 @@ def test_narrow_and_bool_reductions(lib):
     xb[3, :] = True
     got, _ = run(d, [xb])
     assert np.array_equal(got[0], xb.all(axis=1)) and bool(got[1][0]) == bool(xb.any())
+
+
+def test_gather_and_unsorted_segment_sum(lib):
+    rng = np.random.default_rng(60)
+    # embedding lookup (axis 0) followed by a scale, and a gather along a middle axis with int64 indices
+    b = _Builder("Fused_Gather_Mul_60")
+    table = b.input("table", [1000, 64], "float16")
+    idx = b.input("idx", [7, 33], "int32")
+    g_ = b.emit("Gather", [table, idx], [7, 33, 64], "float16", [_attr("axis", "int", 0), _attr("batch_dims", "int", 0)])
+    b.output(b.emit("Mul", [g_, b.const(8.0, "float16")], [7, 33, 64], "float16"))
+    d = b.build()
+    ins = [rng.standard_normal((1000, 64)).astype(np.float16), rng.integers(0, 1000, (7, 33)).astype(np.int32)]
+    check(d, ins, exact=True)
+    b = _Builder("Fused_Gather_61")
+    x = b.input("x", [5, 40, 3], "float32")
+    idx = b.input("idx", [11], "int64")
+    b.output(b.emit("Gather", [x, idx], [5, 11, 3], "float32", [_attr("axis", "int", 1), _attr("batch_dims", "int", 0)]))
+    d = b.build()
+    check(d, [rng.standard_normal((5, 40, 3)).astype(np.float32), rng.integers(0, 40, 11).astype(np.int64)], exact=True)
+    # scatter-add by segment id
+    b = _Builder("Fused_UnsortedSegmentSum_62")
+    data = b.input("data", [4000, 48], "float32")
+    ids = b.input("ids", [4000], "int32")
+    b.output(b.emit("UnsortedSegmentSum", [data, ids], [37, 48], "float32", [_attr("num_segments", "int", 37)]))
+    d = b.build()
+    ins = [rng.standard_normal((4000, 48)).astype(np.float32), rng.integers(0, 37, 4000).astype(np.int32)]
+    got, _ = run(d, ins)
+    want = O.evaluate(d, ins)[0]
+    absum = np.zeros((37, 48))
+    np.add.at(absum, ins[1], np.abs(ins[0]).astype(np.float64))
+    assert np.all(np.abs(got[0] - want) <= 1e-5 * absum + 1e-30)  # atomics: order-dependent last bits
