@@ -150,6 +150,9 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
       case StepK::Gather:
         e = gather_rows(a, b, o, st.ix_outer, st.ix_dim, st.ix_n, st.ix_inner, st.ix_esize, st.ix_idx64, s, &st.dims);
         break;
+      case StepK::ArgMax:
+        e = argmax_axis(a, o, st.ix_outer, st.ix_dim, st.ix_inner, st.ix_esize, st.ix_idx64, s, &st.dims);
+        break;
       case StepK::SegmentSum:
         e = segment_sum_f32((const float*)a, b, (float*)o, st.ix_n, st.ix_inner, st.ix_segments, st.ix_idx64, s,
                             &st.dims);

@@ -66,6 +66,7 @@ const OpEntry kOps[] = {
     {"Assign", OpK::Assign},     {"InplaceAssign", OpK::Assign}, {"AddN", OpK::AddN},
     {"Tile", OpK::Tile},         {"Slice", OpK::Slice},       {"StridedSlice", OpK::StridedSlice},
     {"Concat", OpK::Concat},     {"Gather", OpK::Gather},     {"UnsortedSegmentSum", OpK::UnsortedSegmentSum},
+    {"ArgMax", OpK::ArgMax},     {"Pad", OpK::Pad},
 };
 }  // namespace
 
@@ -221,7 +222,7 @@ Graph parse_info(const char* text, size_t len) {
 
     const Json& in0 = ins[0].is_array() ? ins[0][0] : ins[0];
     int64_t in_rank = (int64_t)shape_of(in0).size();
-    if (opk_is_reduce(n.kind)) {
+    if (opk_is_reduce(n.kind) || n.kind == OpK::ArgMax) {
       // axes from the second operand or the "axis" attribute; negatives wrap
       // (TranslateToMindsporeDialect.cpp:1282-1300); keep_dims defaults to false (:1302)
       std::vector<int64_t> ax;
@@ -248,6 +249,10 @@ Graph parse_info(const char* text, size_t len) {
       n.keep_dims = (n.name == "ElemAny") ? true : (kd ? kd->as_bool() : false);
       const Json* at = find_attr(attrs, "enable_atomic_add");
       n.enable_atomic_add = at ? at->as_bool() : false;
+      if (n.kind == OpK::ArgMax) {
+        if (n.axes.size() != 1) throw Unsupported("ArgMax over more than one axis");
+        n.axis = n.axes[0];
+      }
     } else if (n.kind == OpK::Transpose) {
       // perm from the second operand or the "perm" attribute (:965-978)
       if (ins.size() == 2) {
@@ -354,6 +359,70 @@ Graph parse_info(const char* text, size_t len) {
       const Json* a = find_attr(attrs, "axis");
       n.axis = a ? a->as_int() : 0;
       if (n.axis < 0) n.axis += in_rank;
+    } else if (n.kind == OpK::Pad) {
+      // Two spellings: the factory reads "padding" = [low, high] pairs starting at the LAST dimension and an integer
+      // "value" (TranslateToMindsporeDialect.cpp:1168-1180, MindSporeToTosa.cpp:339-357); the expected-value generator
+      // reads "head"/"tail" per dimension and "pad_val" (op_dsl.py:623-634). Mode is constant in both.
+      n.pad_low.assign(in_rank, 0);
+      n.pad_high.assign(in_rank, 0);
+      if (const Json* pd = find_attr(attrs, "padding")) {
+        std::vector<int64_t> v = pd->as_int_list();
+        if (v.size() % 2 || (int64_t)v.size() / 2 > in_rank) throw JsonError("Pad: bad padding list");
+        for (size_t i = 0; i < v.size() / 2; ++i) {
+          n.pad_low[in_rank - 1 - i] = v[2 * i];
+          n.pad_high[in_rank - 1 - i] = v[2 * i + 1];
+        }
+        if (const Json* pv = find_attr(attrs, "value")) n.pad_value = pv->as_double();
+      } else {
+        const Json* hd = find_attr(attrs, "head");
+        const Json* tl = find_attr(attrs, "tail");
+        if (!hd || !tl) throw JsonError("Pad needs padding, or head and tail");
+        n.pad_low = hd->as_int_list();
+        n.pad_high = tl->as_int_list();
+        if ((int64_t)n.pad_low.size() != in_rank || (int64_t)n.pad_high.size() != in_rank)
+          throw JsonError("Pad: head/tail rank differs from the input");
+        if (const Json* pv = find_attr(attrs, "pad_val")) n.pad_value = pv->as_double();
+      }
+      if (const Json* md = find_attr(attrs, "mode"))
+        if (md->is_string() && md->str != "constant") throw Unsupported("Pad mode '" + md->str + "'");
+      for (int64_t i = 0; i < in_rank; ++i)
+        if (n.pad_low[i] < 0 || n.pad_high[i] < 0) throw Unsupported("Pad with negative widths");
+    }
+    if (n.name == "Split") {
+      // One Slice per entry of output_desc; the extents along the axis come from the declared output shapes, which both
+      // attribute spellings ("split_size_or_sections", :1206-1233; "output_num", op_dsl.py:416-425) must agree with.
+      if (n.in.size() != 1) throw JsonError("Split takes one tensor");
+      const Json* a = find_attr(attrs, "axis");
+      int64_t axis = a ? a->as_int() : 0;
+      if (axis < 0) axis += in_rank;
+      if (axis < 0 || axis >= in_rank) throw JsonError("Split axis out of range");
+      const std::vector<int64_t> xs = shape_of(in0);
+      int64_t pos = 0;
+      for (size_t k = 0; k < outs.size(); ++k) {
+        Node sl;
+        sl.name = "Slice";
+        sl.kind = OpK::Slice;
+        sl.in = n.in;
+        int oid = out_id;
+        if (k > 0) {
+          DT kdt = dt_from_name(outs[k].at("data_type").as_string());
+          if (kdt != odt) throw JsonError("Split outputs must share the input type");
+          oid = new_value(outs[k].at("tensor_name").as_string(), shape_of(outs[k]), kdt);
+        }
+        const std::vector<int64_t>& os = g.values[oid].shape;
+        if ((int64_t)os.size() != in_rank) throw JsonError("Split output rank differs from the input");
+        sl.begin.assign(in_rank, 0);
+        sl.begin[axis] = pos;
+        sl.size = os;
+        pos += os[axis];
+        g.values[oid].producer = (int)g.nodes.size();
+        sl.out = oid;
+        by_name[g.values[oid].name] = oid;
+        for (int vid : sl.in) g.values[vid].users.push_back((int)g.nodes.size());
+        g.nodes.push_back(std::move(sl));
+      }
+      if (pos != xs[axis]) throw JsonError("Split extents do not add up to the input");
+      continue;
     }
     by_name[g.values[out_id].name] = out_id;
     for (int vid : n.in) g.values[vid].users.push_back((int)g.nodes.size());
@@ -577,6 +646,14 @@ Graph bind_shapes(const Graph& src, const std::vector<std::vector<int64_t>>& sha
         else if (n.keep_dims) inf.push_back(1);
       }
       if (inf.empty()) inf.push_back(1);
+    } else if (n.kind == OpK::ArgMax) {
+      for (size_t i = 0; i < x.size(); ++i) {
+        if ((int64_t)i != n.axis) inf.push_back(x[i]);
+        else if (n.keep_dims) inf.push_back(1);
+      }
+      if (inf.empty()) inf.push_back(1);
+    } else if (n.kind == OpK::Pad) {
+      for (size_t i = 0; i < x.size(); ++i) inf.push_back(x[i] + n.pad_low[i] + n.pad_high[i]);
     } else if (n.kind == OpK::Transpose) {
       for (auto p : n.perm) inf.push_back(x[p]);
     } else if (n.kind == OpK::MatMul || n.kind == OpK::BatchMatMul) {

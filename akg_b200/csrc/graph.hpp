@@ -48,7 +48,7 @@ enum class OpK : int {
   // contractions
   MatMul, BatchMatMul,
   // index ops
-  Gather, UnsortedSegmentSum,
+  Gather, UnsortedSegmentSum, ArgMax, Pad,
   // in-place
   Assign,
   Unknown
@@ -102,6 +102,8 @@ struct Node {
   std::vector<int64_t> multiples, begin, size, end, strides;
   int64_t axis = 0;
   int64_t num_segments = 0;  // UnsortedSegmentSum
+  std::vector<int64_t> pad_low, pad_high;  // Pad, per dimension
+  double pad_value = 0.0;
   bool enable_atomic_add = false;
 };
 

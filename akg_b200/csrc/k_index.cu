@@ -6,7 +6,13 @@
 // axis is undefined in the reference (tensor.extract out of bounds); here such a row reads as zeros / is skipped, so
 // that bad indices can never fault the device.  Segment sums use float atomics: the order of additions, and with
 // it the last bits, is not fixed.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include <algorithm>
+#include <type_traits>
+
+#include "graph.hpp"
 
 #include "common.cuh"
 #include "kernels.hpp"
@@ -51,6 +57,87 @@ __global__ void __launch_bounds__(256) segment_sum_f32_kernel(const float* __res
   }
 }
 
+template <typename T>
+__device__ __forceinline__ float as_key(T v);
+template <>
+__device__ __forceinline__ float as_key<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float as_key<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float as_key<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// (value, index) pairs ordered as np.argmax orders them: a NaN beats everything, then the larger value, then the
+// smaller index
+template <typename K>
+__device__ __forceinline__ bool better(K v, int64_t i, K bv, int64_t bi) {
+  const bool vn = v != v, bn = bv != bv;
+  if (vn || bn) return vn && (!bn || i < bi);
+  return v > bv || (v == bv && i < bi);
+}
+
+// inner == 1: one warp per row, lanes stride over the row (coalesced), then a shuffle tree over (value, index)
+template <typename T, typename K>
+__global__ void __launch_bounds__(256) argmax_rows_kernel(const T* __restrict__ data, void* __restrict__ out,
+                                                          int64_t rows, int64_t dim, int out64) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t r = warp; r < rows; r += nwarps) {
+    const T* row = data + r * dim;
+    K bv{};
+    int64_t bi = -1;
+    for (int64_t j = lane; j < dim; j += 32) {
+      K v;
+      if constexpr (sizeof(K) == sizeof(T) && !std::is_same<T, __half>::value && !std::is_same<T, __nv_bfloat16>::value)
+        v = row[j];
+      else
+        v = as_key(row[j]);
+      if (bi < 0 || better(v, j, bv, bi)) {
+        bv = v;
+        bi = j;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      K ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      int64_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (oi >= 0 && (bi < 0 || better(ov, oi, bv, bi))) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0) {
+      if (out64) reinterpret_cast<int64_t*>(out)[r] = bi;
+      else reinterpret_cast<int32_t*>(out)[r] = (int32_t)bi;
+    }
+  }
+}
+
+// inner > 1: one thread per (outer, inner) column walking the axis; neighbouring threads read neighbouring addresses
+template <typename T, typename K>
+__global__ void __launch_bounds__(256) argmax_cols_kernel(const T* __restrict__ data, void* __restrict__ out,
+                                                          int64_t outer, int64_t dim, int64_t inner, int out64) {
+  const int64_t total = outer * inner;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+    const int64_t o = e / inner, r = e - o * inner;
+    const T* col = data + o * dim * inner + r;
+    K bv{};
+    int64_t bi = -1;
+    for (int64_t j = 0; j < dim; ++j) {
+      K v;
+      if constexpr (std::is_same<T, __half>::value || std::is_same<T, __nv_bfloat16>::value) v = as_key(col[j * inner]);
+      else v = col[j * inner];
+      if (bi < 0 || better(v, j, bv, bi)) {
+        bv = v;
+        bi = j;
+      }
+    }
+    if (out64) reinterpret_cast<int64_t*>(out)[e] = bi;
+    else reinterpret_cast<int32_t*>(out)[e] = (int32_t)bi;
+  }
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 int grid_for(int64_t n) {
   int dev = 0, sms = 148;
@@ -89,6 +176,36 @@ cudaError_t gather_rows(const void* data, const void* idx, void* out, int64_t ou
     default: return cudaErrorInvalidValue;
   }
   return cudaGetLastError();
+}
+
+template <typename T, typename K>
+cudaError_t argmax_launch(const void* data, void* out, int64_t outer, int64_t dim, int64_t inner, int out64,
+                          cudaStream_t s, LaunchDims* dims) {
+  int grid;
+  if (inner == 1) {
+    grid = grid_for(outer * 32);
+    argmax_rows_kernel<T, K><<<grid, 256, 0, s>>>((const T*)data, out, outer, dim, out64);
+  } else {
+    grid = grid_for(outer * inner);
+    argmax_cols_kernel<T, K><<<grid, 256, 0, s>>>((const T*)data, out, outer, dim, inner, out64);
+  }
+  if (dims) {
+    dims->grid[0] = grid;
+    dims->block[0] = 256;
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t argmax_axis(const void* data, void* out, int64_t outer, int64_t dim, int64_t inner, int in_dt, int out64,
+                        cudaStream_t s, LaunchDims* dims) {
+  if (outer * inner == 0 || dim == 0) return cudaSuccess;
+  switch ((DT)in_dt) {
+    case DT::F32: return argmax_launch<float, float>(data, out, outer, dim, inner, out64, s, dims);
+    case DT::F16: return argmax_launch<__half, float>(data, out, outer, dim, inner, out64, s, dims);
+    case DT::BF16: return argmax_launch<__nv_bfloat16, float>(data, out, outer, dim, inner, out64, s, dims);
+    case DT::I32: return argmax_launch<int32_t, int32_t>(data, out, outer, dim, inner, out64, s, dims);
+    default: return cudaErrorInvalidValue;
+  }
 }
 
 cudaError_t segment_sum_f32(const float* data, const void* ids, float* out, int64_t nids, int64_t inner,

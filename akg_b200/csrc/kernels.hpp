@@ -89,6 +89,11 @@ cudaError_t gather_rows(const void* data, const void* idx, void* out, int64_t ou
 cudaError_t segment_sum_f32(const float* data, const void* ids, float* out, int64_t nids, int64_t inner,
                             int64_t num_segments, int idx64, cudaStream_t s, LaunchDims* dims);
 
+// index of the first maximum along `dim` of a [outer, dim, inner] tensor (NaN counts as the maximum, as np.argmax);
+// in_dt is the DT code of the data (float32, float16, bfloat16, int32), out64 selects int64 indices
+cudaError_t argmax_axis(const void* data, void* out, int64_t outer, int64_t dim, int64_t inner, int in_dt, int out64,
+                        cudaStream_t s, LaunchDims* dims);
+
 // ---- transpose -----------------------------------------------------------------
 // General permutation of up to 6 folded dims over elements of `esize` bytes.
 struct TransposeParams {

@@ -18,7 +18,7 @@ struct Ref {
   bool valid() const { return arg >= 0 || ws_off >= 0; }
 };
 
-enum class StepK : int { GeluChain, LayerNorm, Softmax, ReduceCol, ReduceAll, ReduceRow, ReduceColDual, Transpose, Matmul, Ew, Gather, SegmentSum };
+enum class StepK : int { GeluChain, LayerNorm, Softmax, ReduceCol, ReduceAll, ReduceRow, ReduceColDual, Transpose, Matmul, Ew, Gather, SegmentSum, ArgMax };
 
 struct Step {
   StepK kind;

@@ -621,6 +621,84 @@ struct Builder {
     plan.steps.push_back(std::move(st));
   }
 
+  void add_argmax(const Node& n) {
+    const Value& x = g.v(n.in[0]);
+    const Value& out = g.v(n.out);
+    if (x.dt != DT::F32 && x.dt != DT::F16 && x.dt != DT::BF16 && x.dt != DT::I32)
+      throw Unsupported(std::string("ArgMax over ") + dt_name(x.dt));
+    if (out.dt != DT::I32 && out.dt != DT::I64) throw Unsupported("ArgMax result must be int32 or int64");
+    Step st;
+    st.kind = StepK::ArgMax;
+    st.kernel_name = "argmax_axis";
+    st.a = buffer(n.in[0]);
+    st.out = buffer(n.out);
+    for (int64_t i = 0; i < n.axis; ++i) st.ix_outer *= x.shape[i];
+    st.ix_dim = x.shape[n.axis];
+    for (size_t i = n.axis + 1; i < x.shape.size(); ++i) st.ix_inner *= x.shape[i];
+    st.ix_esize = (int)x.dt;  // carries the element type of the data
+    st.ix_idx64 = out.dt == DT::I64;
+    if (out.numel() != st.ix_outer * st.ix_inner) throw JsonError("ArgMax output shape");
+    plan.steps.push_back(std::move(st));
+  }
+
+  // Pad = fill the whole output with the constant, then copy the input into its window
+  void add_pad(const Node& n) {
+    const Value& x = g.v(n.in[0]);
+    const Value& out = g.v(n.out);
+    if (!ew_dtype_ok(out.dt) || x.dt != out.dt) throw Unsupported(std::string("Pad of ") + dt_name(out.dt));
+    const size_t R = out.shape.size();
+    if (R > (size_t)kEwMaxRank || x.shape.size() != R) throw Unsupported("Pad rank");
+    std::vector<int64_t> ostride(R, 1);
+    for (int d = (int)R - 2; d >= 0; --d) ostride[d] = ostride[d + 1] * out.shape[d + 1];
+    int64_t off = 0;
+    for (size_t d = 0; d < R; ++d) {
+      if (out.shape[d] != x.shape[d] + n.pad_low[d] + n.pad_high[d]) throw JsonError("Pad output shape");
+      off += n.pad_low[d] * ostride[d];
+    }
+    {
+      Step st;
+      st.kind = StepK::Ew;
+      st.kernel_name = "ew_generic";
+      EwProgram& P = st.ew;
+      std::memset(&P, 0, sizeof(P));
+      P.rank = 1;
+      P.n = out.numel();
+      P.shape[0] = P.n;
+      P.n_const = 1;
+      P.const_bits[0] = const_bits(n.pad_value, out.dt);
+      P.const_reg[0] = 0;
+      P.n_out = 1;
+      P.out[0].dt = (int)out.dt;
+      P.out[0].kind = EWI_FULL;
+      P.out[0].reg = 0;
+      P.n_reg = 1;
+      st.ew_out.push_back(buffer(n.out));
+      plan.steps.push_back(std::move(st));
+    }
+    Step st;
+    st.kind = StepK::Ew;
+    st.kernel_name = "ew_generic";
+    EwProgram& P = st.ew;
+    std::memset(&P, 0, sizeof(P));
+    P.rank = (int)R;
+    P.n = x.numel();
+    for (size_t d = 0; d < R; ++d) P.shape[d] = x.shape[d];
+    P.n_in = 1;
+    P.in[0].dt = (int)x.dt;
+    P.in[0].kind = EWI_FULL;
+    P.in[0].reg = 0;
+    P.n_out = 1;
+    P.out[0].dt = (int)out.dt;
+    P.out[0].kind = EWI_STRIDED;
+    P.out[0].reg = 0;
+    P.out[0].offset = off;
+    for (size_t d = 0; d < R; ++d) P.out[0].stride[d] = ostride[d];
+    P.n_reg = 1;
+    st.ew_in.push_back(buffer(n.in[0]));
+    st.ew_out.push_back(buffer(n.out));
+    plan.steps.push_back(std::move(st));
+  }
+
   void add_segment_sum(const Node& n) {
     const Value& data = g.v(n.in[0]);
     const Value& ids = g.v(n.in[1]);
@@ -769,6 +847,8 @@ struct Builder {
       else if (n.kind == OpK::Transpose) add_transpose(n);
       else if (n.kind == OpK::MatMul || n.kind == OpK::BatchMatMul) add_matmul(n);
       else if (n.kind == OpK::Gather) add_gather(n);
+      else if (n.kind == OpK::ArgMax) add_argmax(n);
+      else if (n.kind == OpK::Pad) add_pad(n);
       else if (n.kind == OpK::UnsortedSegmentSum) add_segment_sum(n);
       else throw Unsupported(std::string("operator '") + n.name + "' is not supported");
     }

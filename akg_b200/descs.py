@@ -49,6 +49,14 @@ class _Builder:
                          "input_desc": [[dict(i)] for i in ins], "output_desc": [dict(out)]})
         return out
 
+    def emit_multi(self, name, ins, outs, attr=None):
+        """An op with several results (Split): `outs` is a list of (shape, dtype)."""
+        self._n += 1
+        res = [_t(f"t{self._n}_{name.lower()}_{k}", shape, dtype) for k, (shape, dtype) in enumerate(outs)]
+        self.ops.append({"name": name, "attr": attr, "impl_path": "",
+                         "input_desc": [[dict(i)] for i in ins], "output_desc": [dict(o) for o in res]})
+        return res
+
     def output(self, t):
         self.outputs.append(dict(t))
 

@@ -166,6 +166,13 @@ def evaluate(desc: dict | str, inputs: Sequence[np.ndarray], accum: str = "numpy
         ins = [i[0] for i in op["input_desc"]]
         if name in ("Concat", "AddN"):  # all tensors sit in the first input entry (op_dsl.py:197-207, :901-907)
             ins = list(op["input_desc"][0])
+        if name == "Split":  # several results: pieces of the declared extents along the axis (op_dsl.py:416-425)
+            axis = _attr(op.get("attr"), "axis", 0)
+            x = operand(ins[0])
+            cuts = np.cumsum([(o.get("shape") or [1])[axis] for o in op["output_desc"]])[:-1]
+            for o, piece in zip(op["output_desc"], np.split(x, cuts, axis)):
+                env[o["tensor_name"]] = np.ascontiguousarray(piece)
+            continue
         out = op["output_desc"][0]
         odt = np_dtype(out["data_type"])
         oshape = out.get("shape") or [1]
@@ -239,6 +246,29 @@ def evaluate(desc: dict | str, inputs: Sequence[np.ndarray], accum: str = "numpy
                 axes = tuple(sorted({a + x.ndim if a < 0 else a for a in axes}))
                 fn = np.all if name == "ReduceAll" else np.any
                 r = fn(x, axis=axes, keepdims=bool(_attr(attrs, "keep_dims", False)) or name == "ElemAny")
+            elif name == "ArgMax":
+                axis = _attr(attrs, "axis")
+                if len(op["input_desc"]) > 1:
+                    axis = op["input_desc"][1][0]["value"]
+                axis = axis[0] if isinstance(axis, (list, tuple)) else axis
+                x = operand(ins[0])
+                x = x.astype(np.float32) if x.dtype.itemsize == 2 else x
+                r = np.argmax(x, axis=axis)  # op_dsl.py:1345 spells the index the same way
+                if _attr(attrs, "keep_dims", False):
+                    r = np.expand_dims(r, axis)
+                r = r.astype(odt)
+            elif name == "Pad":
+                x = operand(ins[0])
+                padding = _attr(attrs, "padding")
+                if padding is not None:  # MindSporeToTosa.cpp:339-357: pairs from the last dimension backwards
+                    width = [(0, 0)] * x.ndim
+                    for i in range(len(padding) // 2):
+                        width[x.ndim - 1 - i] = (padding[2 * i], padding[2 * i + 1])
+                    value = _attr(attrs, "value", 0)
+                else:  # op_dsl.py:623-634
+                    width = list(zip(_attr(attrs, "head"), _attr(attrs, "tail")))
+                    value = _attr(attrs, "pad_val", 0)
+                r = np.pad(x, width, mode="constant", constant_values=np.asarray(value).astype(x.dtype))
             elif name == "Gather":
                 axis = _attr(attrs, "axis", 0)
                 if len(op["input_desc"]) > 2:

@@ -449,3 +449,39 @@ def test_gather_and_unsorted_segment_sum(lib):
     absum = np.zeros((37, 48))
     np.add.at(absum, ins[1], np.abs(ins[0]).astype(np.float64))
     assert np.all(np.abs(got[0] - want) <= 1e-5 * absum + 1e-30)  # atomics: order-dependent last bits
+
+
+def test_pad_split_argmax(lib):
+    rng = np.random.default_rng(70)
+    # Pad, both attribute spellings, followed by an elementwise op
+    for spelling in ("padding", "head_tail"):
+        b = _Builder("Fused_Pad_Add_70")
+        x = b.input("x", [3, 5, 16], "float16")
+        if spelling == "padding":  # pairs from the last dimension backwards
+            attrs = [_attr("padding", "listInt", [8, 0, 1, 2]), _attr("value", "int", 0), _attr("mode", "str", "constant")]
+        else:
+            attrs = [_attr("head", "listInt", [0, 1, 8]), _attr("tail", "listInt", [0, 2, 0]), _attr("pad_val", "float", 0.0)]
+        p = b.emit("Pad", [x], [3, 8, 24], "float16", attrs)
+        b.output(b.emit("Add", [p, b.const(1.5, "float16")], [3, 8, 24], "float16"))
+        check(b.build(), [rng.standard_normal((3, 5, 16)).astype(np.float16)], exact=True)
+    # Split into three uneven pieces along axis 1, each used afterwards
+    b = _Builder("Fused_Split_71")
+    x = b.input("x", [4, 10, 8], "float32")
+    pieces = b.emit_multi("Split", [x], [([4, 2, 8], "float32"), ([4, 5, 8], "float32"), ([4, 3, 8], "float32")],
+                          [_attr("axis", "int", 1), _attr("split_size_or_sections", "listInt", [2, 5, 3])])
+    b.output(b.emit("Neg", [pieces[0]], [4, 2, 8], "float32"))
+    b.output(b.emit("Abs", [pieces[1]], [4, 5, 8], "float32"))
+    b.output(pieces[2])
+    check(b.build(), [rng.standard_normal((4, 10, 8)).astype(np.float32)], exact=True)
+    # ArgMax along the last axis (ties and NaN resolve to the first index) and along a middle axis
+    b = _Builder("Fused_ArgMax_72")
+    x = b.input("x", [6, 7, 333], "float32")
+    b.output(b.emit("ArgMax", [x], [6, 7], "int32", _reduce_attr([2], False)))
+    xv = rng.integers(-4, 5, (6, 7, 333)).astype(np.float32)  # many ties
+    xv[2, 3, 100] = np.nan
+    xv[2, 3, 200] = np.nan
+    check(b.build(), [xv], exact=True)
+    b = _Builder("Fused_ArgMax_73")
+    x = b.input("x", [5, 40, 9], "float16")
+    b.output(b.emit("ArgMax", [x], [5, 1, 9], "int32", _reduce_attr([1], True)))
+    check(b.build(), [rng.standard_normal((5, 40, 9)).astype(np.float16)], exact=True)
