@@ -187,6 +187,11 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
         e = transpose_nd(st.tp, a, o, s, &st.dims);
         break;
       case StepK::Matmul:
+        if (st.mm.in_dt == (int)DT::F32) {
+          e = matmul_f32(st.mm, a, b, c, o, st.mm_batch, st.mm_stride_a / 4, st.mm_stride_b / 4, st.mm_stride_o / 4, s,
+                         &st.dims);
+          break;
+        }
         for (int64_t bi = 0; bi < st.mm_batch && e == cudaSuccess; ++bi)
           e = matmul_bf16(st.mm, (const char*)a + bi * st.mm_stride_a, (const char*)b + bi * st.mm_stride_b, c,
                           (char*)o + bi * st.mm_stride_o, ds.err_word, k->sm_count, s, &st.dims);
@@ -214,7 +219,7 @@ int launches_of(const akgb_kernel* k) {
         n += (st.gelu.n % 8) ? 2 : 1;
         break;
       case StepK::Matmul:
-        n += (int)st.mm_batch;
+        n += st.mm.in_dt == (int)DT::F32 ? 1 : (int)st.mm_batch;
         break;
       default:
         n += 1;

@@ -55,6 +55,7 @@ struct Bars {
 struct MatmulDev {
   int M, N, K;
   int transpose_b, has_bias, bias_dt, relu, out_dt;
+  int in_f16;  // operands are float16 instead of bfloat16
   const void* bias;
   void* out;
   uint32_t* err;
@@ -131,12 +132,12 @@ __device__ __forceinline__ void epilogue_tile(const MatmulDev& p, uint32_t taddr
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
     if (p.has_bias) {
       if (col0 + 32 <= p.N) {
-        if (p.bias_dt == kBF16) {
+        if (p.bias_dt != kF32) {
           const uint4* bp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + col0);
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             float b8[8];
-            unpack8(__ldg(bp + q), kBF16, b8);
+            unpack8(__ldg(bp + q), p.bias_dt, b8);
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[q * 8 + j] = __fadd_rn(v[q * 8 + j], b8[j]);
           }
@@ -157,7 +158,8 @@ __device__ __forceinline__ void epilogue_tile(const MatmulDev& p, uint32_t taddr
           if (col0 + j < p.N) {
             const float b = p.bias_dt == kBF16
                                 ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(p.bias)[col0 + j])
-                                : reinterpret_cast<const float*>(p.bias)[col0 + j];
+                                : p.bias_dt == kF16 ? __half2float(reinterpret_cast<const __half*>(p.bias)[col0 + j])
+                                                    : reinterpret_cast<const float*>(p.bias)[col0 + j];
             v[j] = __fadd_rn(v[j], b);
           }
         }
@@ -168,22 +170,16 @@ __device__ __forceinline__ void epilogue_tile(const MatmulDev& p, uint32_t taddr
       for (int j = 0; j < 32; ++j) v[j] = v[j] != v[j] ? v[j] : fmaxf(v[j], 0.f);  // NaN stays NaN
     }
     if (row < p.M) {
-      if (p.out_dt == kBF16) {
+      if (p.out_dt != kF32) {
         uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + (size_t)row * p.N + col0;
         if (col0 + 32 <= p.N) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 w;
-            w.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-            w.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-            w.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-            w.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-            *reinterpret_cast<uint4*>(o + q * 8) = w;
-          }
+          for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(o + q * 8) = pack8(v + q * 8, p.out_dt);
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) o[j] = (uint16_t)f32_to_bf16_bits(v[j]);
+            if (col0 + j < p.N)
+              o[j] = p.out_dt == kBF16 ? (uint16_t)f32_to_bf16_bits(v[j]) : __half_as_ushort(__float2half_rn(v[j]));
         }
       } else {
         float* o = reinterpret_cast<float*>(p.out) + (size_t)row * p.N + col0;
@@ -292,7 +288,8 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
   } else if (warp == 1) {
     if (lane == 0) {
       // ------------------------------------------------------------ MMA issuer
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((p.transpose_b ? 0u : 1u) << 16) |
+      const uint32_t fmt = p.in_f16 ? 0u : 1u;  // operand format field: 0 = f16, 1 = bf16
+      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((p.transpose_b ? 0u : 1u) << 16) |
                              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
@@ -522,7 +519,8 @@ matmul_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const _
   } else if (warp == 1) {
     if (lane == 0 && leader) {
       // ------------------------------------------------------------ MMA issuer (leader CTA only)
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((p.transpose_b ? 0u : 1u) << 16) |
+      const uint32_t fmt = p.in_f16 ? 0u : 1u;  // operand format field: 0 = f16, 1 = bf16
+      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((p.transpose_b ? 0u : 1u) << 16) |
                              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
@@ -621,16 +619,16 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows.
+// 2-D tensor map over 16-bit elements: `inner` contiguous elements per row, `outer` rows.
 bool encode_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_inner,
-               uint32_t box_outer) {
+               uint32_t box_outer, bool f16 = false) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {inner * 2};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+  CUresult r = fn(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
@@ -654,9 +652,10 @@ cudaError_t matmul_bf16(const MatmulParams& p, const void* A, const void* B, con
        reinterpret_cast<uintptr_t>(bias)) & 15)
     return cudaErrorMisalignedAddress;
   CUtensorMap tmA, tmB;
-  if (!encode_2d(&tmA, A, (uint64_t)p.K, (uint64_t)p.M, BK, BM)) return cudaErrorInvalidValue;
-  const bool okb = p.transpose_b ? encode_2d(&tmB, B, (uint64_t)p.K, (uint64_t)p.N, BK, BN)
-                                 : encode_2d(&tmB, B, (uint64_t)p.N, (uint64_t)p.K, B_BOX_N, BK);
+  const bool f16 = p.in_dt == kF16;
+  if (!encode_2d(&tmA, A, (uint64_t)p.K, (uint64_t)p.M, BK, BM, f16)) return cudaErrorInvalidValue;
+  const bool okb = p.transpose_b ? encode_2d(&tmB, B, (uint64_t)p.K, (uint64_t)p.N, BK, BN, f16)
+                                 : encode_2d(&tmB, B, (uint64_t)p.N, (uint64_t)p.K, B_BOX_N, BK, f16);
   if (!okb) return cudaErrorInvalidValue;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
@@ -674,6 +673,7 @@ cudaError_t matmul_bf16(const MatmulParams& p, const void* A, const void* B, con
   d.bias_dt = p.bias_dt;
   d.relu = p.relu;
   d.out_dt = p.out_dt;
+  d.in_f16 = f16;
   d.bias = bias;
   d.out = out;
   d.err = err_word;
@@ -691,7 +691,7 @@ cudaError_t matmul_bf16(const MatmulParams& p, const void* A, const void* B, con
     if (attr_err2 != cudaSuccess) return attr_err2;
     // the pair kernel's B tile per CTA is 128 columns: re-encode B with the narrower box for the K-major case
     CUtensorMap tmB2 = tmB;
-    if (p.transpose_b && !encode_2d(&tmB2, B, (uint64_t)p.K, (uint64_t)p.N, BK, BN / 2)) return cudaErrorInvalidValue;
+    if (p.transpose_b && !encode_2d(&tmB2, B, (uint64_t)p.K, (uint64_t)p.N, BK, BN / 2, f16)) return cudaErrorInvalidValue;
     const int64_t tiles2 = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN);
     const int grid2 = 2 * (int)std::min<int64_t>(tiles2, sm_count / 2);
     if (dims) {

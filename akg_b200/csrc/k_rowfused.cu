@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, kMinCtas) layernorm_rows_f3
 #pragma unroll
     for (int k = 0; k < VPL; ++k) s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
     s = warp_reduce<SumOp>(s);
-    const float mean = __fmul_rn(s, p.inv_n);
+    const float mean = p.div_n != 0.f ? __fdiv_rn(s, p.div_n) : __fmul_rn(s, p.inv_n);
     float q = 0.f;
 #pragma unroll
     for (int k = 0; k < VPL; ++k) {
@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, kMinCtas) layernorm_rows_f3
              (__fmul_rn(v[k].z, v[k].z) + __fmul_rn(v[k].w, v[k].w));
     }
     q = warp_reduce<SumOp>(q);
-    const float var = __fmul_rn(q, p.inv_n);
+    const float var = p.div_n != 0.f ? __fdiv_rn(q, p.div_n) : __fmul_rn(q, p.inv_n);
     const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, p.eps)));
     float4* yr = reinterpret_cast<float4*>(y + row * p.cols);
 #pragma unroll
@@ -104,14 +104,14 @@ __global__ void __launch_bounds__(256) layernorm_rows_f32_generic_kernel(
     float s = 0.f;
     for (int64_t c = threadIdx.x; c < p.cols; c += blockDim.x) s += xr[c];
     s = block_reduce<SumOp>(s, red);
-    const float mean = __fmul_rn(s, p.inv_n);
+    const float mean = p.div_n != 0.f ? __fdiv_rn(s, p.div_n) : __fmul_rn(s, p.inv_n);
     float q = 0.f;
     for (int64_t c = threadIdx.x; c < p.cols; c += blockDim.x) {
       const float d = __fsub_rn(xr[c], mean);
       q += __fmul_rn(d, d);
     }
     q = block_reduce<SumOp>(q, red);
-    const float var = __fmul_rn(q, p.inv_n);
+    const float var = p.div_n != 0.f ? __fdiv_rn(q, p.div_n) : __fmul_rn(q, p.inv_n);
     const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, p.eps)));
     for (int64_t c = threadIdx.x; c < p.cols; c += blockDim.x) {
       float o = __fmul_rn(__fsub_rn(xr[c], mean), rstd);

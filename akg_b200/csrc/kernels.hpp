@@ -40,6 +40,7 @@ void gelu_lut_build(uint16_t* out);
 struct LayerNormParams {
   int64_t rows = 0, cols = 0;
   float inv_n = 0.f, eps = 0.f;
+  float div_n = 0.f;  // non-zero: the description divides the sums by this count instead of multiplying by inv_n
   int has_gamma = 0, has_beta = 0, write_mean = 0, write_var = 0;
 };
 cudaError_t layernorm_f32(const LayerNormParams& p, const float* x, const float* gamma, const float* beta, float* y,
@@ -109,13 +110,18 @@ struct MatmulParams {
   int64_t M = 0, N = 0, K = 0;
   int transpose_b = 0;  // 0: B is [K,N]; 1: B is [N,K]
   int has_bias = 0;     // bias[N] added in f32
-  int bias_dt = 0;      // DT code of bias (BF16 or F32)
+  int bias_dt = 0;      // DT code of bias (BF16, F16 or F32)
   int relu = 0;         // max(., 0)
-  int out_dt = 0;       // DT code of the output: BF16 or F32
+  int out_dt = 0;       // DT code of the output: the operand type (BF16 / F16) or F32
+  int in_dt = 8;        // DT code of A and B: BF16 (8) or F16 (5) on the tensor cores, F32 (6) on the CUDA cores
 };
 // Encodes the TMA descriptors for (A, B) and launches the tcgen05 kernel.
 cudaError_t matmul_bf16(const MatmulParams& p, const void* A, const void* B, const void* bias, void* out,
                         uint32_t* err_word, int sm_count, cudaStream_t s, LaunchDims* dims);
 bool matmul_bf16_supported(const MatmulParams& p, const char** why);
+// float32 operands and result on the CUDA cores (in_dt = F32); `batch` entries `stride_*` elements apart, one launch
+cudaError_t matmul_f32(const MatmulParams& p, const void* A, const void* B, const void* bias, void* out,
+                       int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_o, cudaStream_t s,
+                       LaunchDims* dims);
 
 }  // namespace akgb

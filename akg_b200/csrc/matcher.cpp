@@ -160,9 +160,21 @@ bool match_layernorm(const Graph& g, Plan& plan) {
   int var;
   double eps;
   if (!m.bin_const(ve, OpK::Add, true, &var, &eps)) return false;
+  // sum -> mean either as a multiplication by 1/N or as a division by N (the spelling PyTorch's mean decomposes to);
+  // a power-of-two N makes the two identical, any other N keeps the division
+  auto scaled = [&](int vid, int* src, double* inv, double* divn) {
+    *divn = 0.0;
+    if (m.bin_const(vid, OpK::Mul, true, src, inv)) return true;
+    double c;
+    if (!m.bin_const(vid, OpK::Div, false, src, &c) || c <= 0.0) return false;
+    int e;
+    if (std::frexp(c, &e) == 0.5) *inv = 1.0 / c;
+    else *divn = c, *inv = 1.0 / c;
+    return true;
+  };
   int s2;
-  double inv_n2;
-  if (!m.bin_const(var, OpK::Mul, true, &s2, &inv_n2)) return false;
+  double inv_n2, div_n2;
+  if (!scaled(var, &s2, &inv_n2, &div_n2)) return false;
   int sq;
   if (!row_reduce(m, s2, OpK::ReduceSum, &sq)) return false;
   if (!m.bin(sq, OpK::Mul, &a, &b) || a != d || b != d) return false;
@@ -170,11 +182,11 @@ bool match_layernorm(const Graph& g, Plan& plan) {
   if (!m.bin(d, OpK::Sub, &x, &mean)) return false;
   if (!m.is_input(x) || g.v(x).dt != DT::F32) return false;
   int s1;
-  double inv_n1;
-  if (!m.bin_const(mean, OpK::Mul, true, &s1, &inv_n1)) return false;
+  double inv_n1, div_n1;
+  if (!scaled(mean, &s1, &inv_n1, &div_n1)) return false;
   int x2;
   if (!row_reduce(m, s1, OpK::ReduceSum, &x2) || x2 != x) return false;
-  if ((float)inv_n1 != (float)inv_n2) return false;
+  if ((float)inv_n1 != (float)inv_n2 || (float)div_n1 != (float)div_n2) return false;
 
   // optional extra outputs: mean and var, possibly through a Reshape
   Ref mean_ref, var_ref;
@@ -199,6 +211,7 @@ bool match_layernorm(const Graph& g, Plan& plan) {
   st.ln.rows = rows;
   st.ln.cols = cols;
   st.ln.inv_n = (float)inv_n1;
+  st.ln.div_n = (float)div_n1;
   st.ln.eps = (float)eps;
   st.ln.has_gamma = gamma >= 0;
   st.ln.has_beta = beta >= 0;
@@ -480,7 +493,7 @@ bool match_matmul(const Graph& g, Plan& plan) {
   int out = g.outputs[0];
   int cur = out, t;
   DT out_dt = g.v(out).dt;
-  if (out_dt == DT::BF16) {
+  if (out_dt == DT::BF16 || out_dt == DT::F16) {
     M probe = m;
     if (probe.un(cur, OpK::Cast, &t) && g.v(t).dt == DT::F32) {
       m = probe;
@@ -537,7 +550,8 @@ bool match_matmul(const Graph& g, Plan& plan) {
   if (!m.is_input(A) || !m.is_input(B) || !m.all_used()) return false;
   const Value& av = g.v(A);
   const Value& bv = g.v(B);
-  if (av.dt != DT::BF16 || bv.dt != DT::BF16) return false;
+  if ((av.dt != DT::BF16 && av.dt != DT::F16 && av.dt != DT::F32) || bv.dt != av.dt) return false;
+  if (out_dt != DT::F32 && out_dt != av.dt) return false;
   if (av.shape.size() != 2 || bv.shape.size() != 2) return false;
   // accumulation happens in the MatMul's declared result type; only f32 is placed
   if (g.v(cur).dt != DT::F32) return false;
@@ -552,17 +566,19 @@ bool match_matmul(const Graph& g, Plan& plan) {
     const Value& biasv = g.v(bias);
     if (biasv.numel() != p.N || biasv.shape.back() != p.N) return false;
     bias_dt = biasv.dt;
-    if (bias_dt != DT::BF16 && bias_dt != DT::F32) return false;
+    if (bias_dt != av.dt && bias_dt != DT::F32) return false;
     p.has_bias = 1;
   }
   p.bias_dt = (int)bias_dt;
   p.relu = relu;
   p.out_dt = (int)out_dt;
+  p.in_dt = (int)av.dt;
   const char* why = nullptr;
-  if (!matmul_bf16_supported(p, &why)) throw Unsupported(std::string("matmul shape not placed: ") + why);
+  if (av.dt != DT::F32 && !matmul_bf16_supported(p, &why))
+    throw Unsupported(std::string("matmul shape not placed: ") + why);
   Step st;
   st.kind = StepK::Matmul;
-  st.kernel_name = "matmul_bf16_tcgen05";
+  st.kernel_name = av.dt == DT::F32 ? "sgemm_f32" : "matmul_bf16_tcgen05";
   st.a = m.ref_of(A);
   st.b = m.ref_of(B);
   if (bias >= 0) st.c = m.ref_of(bias);

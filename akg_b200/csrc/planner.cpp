@@ -728,21 +728,24 @@ struct Builder {
     const Value& a = g.v(n.in[0]);
     const Value& b = g.v(n.in[1]);
     const Value& o = g.v(n.out);
-    if (a.dt != DT::BF16 || b.dt != DT::BF16 || a.shape.size() != 2 || b.shape.size() != 2)
-      throw Unsupported("only 2-D bfloat16 MatMul is placed");
-    if (o.dt != DT::F32 && o.dt != DT::BF16) throw Unsupported("MatMul result type");
+    if ((a.dt != DT::BF16 && a.dt != DT::F16 && a.dt != DT::F32) || b.dt != a.dt || a.shape.size() != 2 ||
+        b.shape.size() != 2)
+      throw Unsupported("only 2-D bfloat16 / float16 / float32 MatMul is placed");
+    if (o.dt != DT::F32 && o.dt != a.dt) throw Unsupported("MatMul result type");
     MatmulParams p;
     p.M = a.shape[0];
     p.K = a.shape[1];
     p.transpose_b = n.transpose_b;
     p.N = n.transpose_b ? b.shape[0] : b.shape[1];
     p.out_dt = (int)o.dt;
+    p.in_dt = (int)a.dt;
     p.bias_dt = (int)DT::F32;
     const char* why = nullptr;
-    if (!matmul_bf16_supported(p, &why)) throw Unsupported(std::string("matmul shape not placed: ") + why);
+    if (a.dt != DT::F32 && !matmul_bf16_supported(p, &why))
+      throw Unsupported(std::string("matmul shape not placed: ") + why);
     Step st;
     st.kind = StepK::Matmul;
-    st.kernel_name = "matmul_bf16_tcgen05";
+    st.kernel_name = a.dt == DT::F32 ? "sgemm_f32" : "matmul_bf16_tcgen05";
     st.a = buffer(n.in[0]);
     st.b = buffer(n.in[1]);
     st.out = buffer(n.out);
@@ -782,9 +785,10 @@ struct Builder {
     const Value& a = g.v(n.in[0]);
     const Value& b = g.v(n.in[1]);
     const Value& o = g.v(n.out);
-    if (a.dt != DT::BF16 || b.dt != DT::BF16 || a.shape.size() < 2 || b.shape.size() < 2)
-      throw Unsupported("only bfloat16 BatchMatMul is placed");
-    if (o.dt != DT::F32 && o.dt != DT::BF16) throw Unsupported("BatchMatMul result type");
+    if ((a.dt != DT::BF16 && a.dt != DT::F16 && a.dt != DT::F32) || b.dt != a.dt || a.shape.size() < 2 ||
+        b.shape.size() < 2)
+      throw Unsupported("only bfloat16 / float16 / float32 BatchMatMul is placed");
+    if (o.dt != DT::F32 && o.dt != a.dt) throw Unsupported("BatchMatMul result type");
     const size_t ra = a.shape.size(), rb = b.shape.size();
     int64_t batch = 1;
     for (size_t i = 0; i + 2 < ra; ++i) batch *= a.shape[i];
@@ -798,20 +802,23 @@ struct Builder {
     p.transpose_b = n.transpose_b;
     p.N = n.transpose_b ? b.shape[rb - 2] : b.shape[rb - 1];
     p.out_dt = (int)o.dt;
+    p.in_dt = (int)a.dt;
     p.bias_dt = (int)DT::F32;
     const char* why = nullptr;
-    if (!matmul_bf16_supported(p, &why)) throw Unsupported(std::string("matmul shape not placed: ") + why);
-    if ((p.M * p.K) % 8 || (p.K * p.N) % 8 || (p.M * p.N) % 8) throw Unsupported("BatchMatMul slices must stay 16-byte aligned");
+    const bool f32 = a.dt == DT::F32;
+    if (!f32 && !matmul_bf16_supported(p, &why)) throw Unsupported(std::string("matmul shape not placed: ") + why);
+    if (!f32 && ((p.M * p.K) % 8 || (p.K * p.N) % 8 || (p.M * p.N) % 8))
+      throw Unsupported("BatchMatMul slices must stay 16-byte aligned");
     Step st;
     st.kind = StepK::Matmul;
-    st.kernel_name = "matmul_bf16_tcgen05";
+    st.kernel_name = f32 ? "sgemm_f32" : "matmul_bf16_tcgen05";
     st.a = buffer(n.in[0]);
     st.b = buffer(n.in[1]);
     st.out = buffer(n.out);
     st.mm = p;
     st.mm_batch = batch;
-    st.mm_stride_a = p.M * p.K * 2;
-    st.mm_stride_b = bbatch == 1 ? 0 : p.K * p.N * 2;
+    st.mm_stride_a = p.M * p.K * (int64_t)dt_size(a.dt);
+    st.mm_stride_b = bbatch == 1 ? 0 : p.K * p.N * (int64_t)dt_size(a.dt);
     st.mm_stride_o = p.M * p.N * (int64_t)dt_size(o.dt);
     plan.flops += 2 * p.M * p.N * p.K * batch;
     plan.steps.push_back(std::move(st));

@@ -1,0 +1,596 @@
+"""Front door for PyTorch programs: clusters fusable aten ops and runs each cluster as one fused-operator description.
+
+The reference reaches its kernel generator from PyTorch through an MLIR pipeline: torch dialect -> decomposition to
+meta ops -> clustering of the ops the generator can take (``mfusion/lib/Dialect/Mfuse/Transforms/Cluster/AKGCluster.cc:30-118``:
+static shapes only, no empty tensors, no complex types) -> outlining of every cluster -> one ``akg_call`` custom call
+per cluster that carries the serialised subgraph (``mfusion/include/mfusion/Dialect/Mfuse/IR/MfuseOps.td:26-51``,
+``mfusion/python/mfusion/torch/inductor.py:86-211``).  This module does the same steps on a ``torch.fx`` graph of aten
+ops and hands every cluster to the library as the JSON description it compiles:
+
+    trace (make_fx + decompositions)  ->  cluster  ->  one description per cluster  ->  graph with akg_call nodes
+
+Differences from the reference's cluster list, both deliberate: reductions, matmuls, casts and shape ops are
+clusterable too (the kernel library takes them), and a cluster must contain at least one op that computes something.
+
+torch is used for tracing, device memory and streams.  All arithmetic of a cluster runs in the CUDA library; there
+is no eager fallback for a cluster once it has been formed (a description the library refuses raises).
+"""
+from __future__ import annotations
+
+import json
+import math
+import operator
+from typing import Callable, Sequence
+
+import torch
+from torch import fx
+
+from .descs import _attr, _Builder, _reduce_attr
+
+aten = torch.ops.aten
+
+_DTYPE_NAMES = {torch.float32: "float32", torch.float16: "float16", torch.bfloat16: "bfloat16",
+                torch.int32: "int32", torch.int8: "int8", torch.int16: "int16", torch.bool: "bool"}
+_FLOATS = (torch.float32, torch.float16, torch.bfloat16)
+
+
+# --------------------------------------------------------------------------------------------------------------------
+# aten op -> description ops.  Every lowering receives a _Lower context, the fx node and the already lowered operands
+# (a tensor entry of the description, or a Python scalar) and returns the tensor entry of the result.
+# --------------------------------------------------------------------------------------------------------------------
+class _Lower:
+    def __init__(self, name: str):
+        self.b = _Builder(name)
+
+    @staticmethod
+    def shape(node) -> list[int]:
+        return [int(s) for s in node.meta["val"].shape] or [1]
+
+    @staticmethod
+    def dtype(node) -> str:
+        return _DTYPE_NAMES[node.meta["val"].dtype]
+
+    def emit(self, name, ins, node, attr=None, shape=None, dtype=None):
+        return self.b.emit(name, ins, shape if shape is not None else self.shape(node),
+                           dtype or self.dtype(node), attr)
+
+    def as_tensor(self, v, dtype: str):
+        """Operand of a description op: tensors pass, scalars become typed constants."""
+        if isinstance(v, dict):
+            return v
+        return self.b.const(float(v) if not isinstance(v, bool) else (1.0 if v else 0.0), dtype)
+
+    def cast_to(self, t, dtype: str):
+        if not isinstance(t, dict) or t["data_type"] == dtype:
+            return t
+        return self.b.emit("Cast", [t], t["shape"], dtype, [_attr("dst_type", "str", dtype)])
+
+
+def _compute_dtype(node, operands) -> str:
+    """The type torch computes a binary op in: the promoted type of its operands."""
+    vals = []
+    for a in node.args[:2]:
+        if isinstance(a, fx.Node):
+            vals.append(a.meta["val"])
+        else:
+            vals.append(a)
+    return _DTYPE_NAMES[torch.result_type(*vals)]
+
+
+def _unary(name):
+    def lower(L: _Lower, node, x):
+        return L.emit(name, [x], node)
+    return lower
+
+
+def _binary(name, alpha_arg=False):
+    def lower(L: _Lower, node, a, b, **kw):
+        dt = L.dtype(node)
+        alpha = kw.get("alpha", 1)
+        a, b = L.cast_to(a, dt), L.cast_to(b, dt)
+        if alpha_arg and alpha != 1:
+            b = (L.b.emit("Mul", [b, L.b.const(float(alpha), dt)], b["shape"], dt) if isinstance(b, dict)
+                 else b * alpha)
+        return L.emit(name, [L.as_tensor(a, dt), L.as_tensor(b, dt)], node)
+    return lower
+
+
+def _compare(name):
+    def lower(L: _Lower, node, a, b):
+        dt = _compute_dtype(node, (a, b))
+        a, b = L.cast_to(a, dt), L.cast_to(b, dt)
+        return L.emit(name, [L.as_tensor(a, dt), L.as_tensor(b, dt)], node)
+    return lower
+
+
+def _relu(L, node, x):
+    return L.emit("Maximum", [x, L.b.const(0.0, L.dtype(node))], node)
+
+
+def _sigmoid(L, node, x):
+    dt = L.dtype(node)
+    e = L.emit("Exp", [L.emit("Neg", [x], node)], node)
+    return L.emit("Reciprocal", [L.emit("Add", [e, L.b.const(1.0, dt)], node)], node)
+
+
+def _rsub(L, node, a, b, alpha=1):  # b - alpha * a
+    dt = L.dtype(node)
+    a = L.cast_to(a, dt)
+    if alpha != 1:
+        a = L.b.emit("Mul", [a, L.b.const(float(alpha), dt)], a["shape"], dt)
+    return L.emit("Sub", [L.as_tensor(b, dt), L.as_tensor(a, dt)], node)
+
+
+def _div(L, node, a, b, rounding_mode=None):
+    return _binary("RealDiv")(L, node, a, b)
+
+
+def _where(L, node, c, a, b):
+    dt = L.dtype(node)
+    return L.emit("Select", [c, L.as_tensor(L.cast_to(a, dt), dt), L.as_tensor(L.cast_to(b, dt), dt)], node)
+
+
+def _to_copy(L, node, x, **kw):
+    dt = L.dtype(node)
+    if x["data_type"] == dt:
+        return L.emit("Reshape", [x], node, [_attr("shape", "listInt", L.shape(node))])
+    return L.emit("Cast", [x], node, [_attr("dst_type", "str", dt)])
+
+
+def _reshape(L, node, x, *_):
+    return L.emit("Reshape", [x], node, [_attr("shape", "listInt", L.shape(node))])
+
+
+def _expand(L, node, x, *_):
+    shape = L.shape(node)
+    if list(x["shape"]) == shape:
+        return _reshape(L, node, x)
+    # BroadcastTo keeps the rank of its operand's trailing dims; add leading 1s first when the rank grows
+    if len(x["shape"]) < len(shape):
+        lead = [1] * (len(shape) - len(x["shape"])) + list(x["shape"])
+        x = L.b.emit("Reshape", [x], lead, x["data_type"], [_attr("shape", "listInt", lead)])
+    return L.emit("BroadcastTo", [x], node, [_attr("shape", "listInt", shape)])
+
+
+def _permute(L, node, x, perm):
+    r = len(x["shape"])
+    return L.emit("Transpose", [x], node, [_attr("perm", "listInt", [int(p) % r for p in perm])])
+
+
+def _transpose_int(L, node, x, d0, d1):
+    r = len(x["shape"])
+    perm = list(range(r))
+    perm[d0 % r], perm[d1 % r] = perm[d1 % r], perm[d0 % r]
+    return _permute(L, node, x, perm)
+
+
+def _t(L, node, x):
+    return _permute(L, node, x, [1, 0]) if len(x["shape"]) == 2 else _reshape(L, node, x)
+
+
+def _axes(x, dims):
+    r = len(x["shape"])
+    if dims is None or (isinstance(dims, (list, tuple)) and len(dims) == 0):
+        return list(range(r))
+    dims = [dims] if isinstance(dims, int) else list(dims)
+    return sorted({int(d) % r for d in dims})
+
+
+def _reduce(name):
+    def lower(L: _Lower, node, x, dims=None, keepdim=False, **kw):
+        dt = L.dtype(node)
+        x = L.cast_to(x, dt)  # sum(dtype=...) converts first
+        return L.emit(name, [x], node, _reduce_attr(_axes(x, dims), bool(keepdim)))
+    return lower
+
+
+def _mean(L, node, x, dims=None, keepdim=False, **kw):
+    dt = L.dtype(node)
+    x = L.cast_to(x, dt)
+    axes = _axes(x, dims)
+    count = math.prod(x["shape"][a] for a in axes)
+    s = L.emit("ReduceSum", [x], node, _reduce_attr(axes, bool(keepdim)))
+    return L.emit("RealDiv", [s, L.b.const(float(count), dt)], node)
+
+
+def _mm(L, node, a, b):
+    return L.emit("MatMul", [a, b], node, [_attr("transpose_a", "bool", False), _attr("transpose_b", "bool", False)])
+
+
+def _bmm(L, node, a, b):
+    return L.emit("BatchMatMul", [a, b], node,
+                  [_attr("transpose_a", "bool", False), _attr("transpose_b", "bool", False)])
+
+
+def _addmm(L, node, bias, a, b, beta=1, alpha=1):
+    if beta != 1 or alpha != 1:
+        raise NotImplementedError("addmm with beta/alpha other than 1")
+    return L.emit("Add", [_mm(L, node, a, b), bias], node)
+
+
+def _cat(L, node, tensors, dim=0):
+    r = len(tensors[0]["shape"])
+    L.b._n += 1
+    out = {"tensor_name": f"t{L.b._n}_concat", "shape": L.shape(node), "data_type": L.dtype(node),
+           "format": "DefaultFormat"}
+    L.b.ops.append({"name": "Concat", "attr": [_attr("axis", "int", int(dim) % r)], "impl_path": "",
+                    "input_desc": [[dict(t) for t in tensors]], "output_desc": [dict(out)]})
+    return out
+
+
+def _slice(L, node, x, dim=0, start=None, end=None, step=1):
+    shape = list(x["shape"])
+    r = len(shape)
+    dim = int(dim) % r
+    n = shape[dim]
+    start = 0 if start is None else int(start)
+    end = n if end is None else int(end)
+    start = max(0, min(n, start + n if start < 0 else start))
+    end = max(0, min(n, end + n if end < 0 else end))
+    begin, stop, strides = [0] * r, list(shape), [1] * r
+    begin[dim], stop[dim], strides[dim] = start, end, int(step)
+    return L.emit("StridedSlice", [x], node, [_attr("begin", "listInt", begin), _attr("end", "listInt", stop),
+                                              _attr("strides", "listInt", strides)])
+
+
+def _pow_scalar(L, node, x, e):
+    dt = L.dtype(node)
+    return L.emit("Pow", [L.cast_to(x, dt), L.b.const(float(e), dt)], node)
+
+
+_LOWERINGS: dict = {}
+
+
+def _register():
+    def put(ops, fn, compute=True):
+        for op in ops if isinstance(ops, (list, tuple)) else [ops]:
+            _LOWERINGS[op] = (fn, compute)
+    for a, n in [(aten.abs.default, "Abs"), (aten.neg.default, "Neg"), (aten.exp.default, "Exp"),
+                 (aten.log.default, "Log"), (aten.tanh.default, "Tanh"), (aten.sqrt.default, "Sqrt"),
+                 (aten.rsqrt.default, "Rsqrt"), (aten.reciprocal.default, "Reciprocal"), (aten.floor.default, "Floor"),
+                 (aten.sin.default, "Sin"), (aten.cos.default, "Cos"), (aten.asinh.default, "Asinh"),
+                 (aten.acosh.default, "Acosh"), (aten.atan.default, "Atan"), (aten.asin.default, "ASin"),
+                 (aten.acos.default, "ACos"), (aten.isinf.default, "IsInf"), (aten.isnan.default, "IsNan"),
+                 (aten.isfinite.default, "IsFinite"), (aten.logical_not.default, "LogicalNot")]:
+        put(a, _unary(n))
+    put(aten.relu.default, _relu)
+    put(aten.sigmoid.default, _sigmoid)
+    put([aten.add.Tensor, aten.add.Scalar], _binary("Add", alpha_arg=True))
+    put([aten.sub.Tensor, aten.sub.Scalar], _binary("Sub", alpha_arg=True))
+    put([aten.rsub.Scalar, aten.rsub.Tensor], _rsub)
+    put([aten.mul.Tensor, aten.mul.Scalar], _binary("Mul"))
+    put([aten.div.Tensor, aten.div.Scalar], _div)
+    put(aten.maximum.default, _binary("Maximum"))
+    put(aten.minimum.default, _binary("Minimum"))
+    put(aten.pow.Tensor_Scalar, _pow_scalar)
+    put(aten.pow.Tensor_Tensor, _binary("Pow"))
+    put(aten.atan2.default, _binary("Atan2"))
+    for base, n in [("eq", "Equal"), ("ne", "NotEqual"), ("gt", "Greater"), ("ge", "GreaterEqual"), ("lt", "Less"),
+                    ("le", "LessEqual")]:
+        put([getattr(aten, base).Tensor, getattr(aten, base).Scalar], _compare(n))
+    put(aten.logical_and.default, _binary("LogicalAnd"))
+    put(aten.logical_or.default, _binary("LogicalOr"))
+    put(aten.where.self, _where)
+    put(aten._to_copy.default, _to_copy)
+    put([aten.view.default, aten._unsafe_view.default, aten.reshape.default, aten.unsqueeze.default,
+         aten.squeeze.dim, aten.squeeze.dims, aten.squeeze.default, aten.clone.default, aten.alias.default,
+         aten.detach.default], _reshape, compute=False)
+    put(aten.expand.default, _expand, compute=False)
+    put(aten.permute.default, _permute)
+    put(aten.transpose.int, _transpose_int)
+    put(aten.t.default, _t)
+    put(aten.sum.dim_IntList, _reduce("ReduceSum"))
+    put(aten.sum.default, _reduce("ReduceSum"))
+    put(aten.amax.default, _reduce("ReduceMax"))
+    put(aten.amin.default, _reduce("ReduceMin"))
+    put(aten.mean.dim, _mean)
+    put(aten.mm.default, _mm)
+    put(aten.bmm.default, _bmm)
+    put(aten.addmm.default, _addmm)
+    put(aten.cat.default, _cat)
+    put(aten.slice.Tensor, _slice)
+
+
+_register()
+
+
+def _native_layer_norm(x, normalized_shape, weight, bias, eps):
+    """LayerNorm as the op chain the fused row kernel recognises: mean, centred values, their mean square, rsqrt."""
+    dims = list(range(x.dim() - len(normalized_shape), x.dim()))
+    xf = x.float() if x.dtype in (torch.float16, torch.bfloat16) else x
+    mean = xf.mean(dims, keepdim=True)
+    d = xf - mean
+    var = (d * d).mean(dims, keepdim=True)
+    rstd = torch.rsqrt(var + eps)
+    y = d * rstd
+    if weight is not None:
+        y = y * weight
+    if bias is not None:
+        y = y + bias
+    return y.to(x.dtype), mean, rstd
+
+
+def _decompositions():
+    from torch._decomp import get_decompositions
+    table = _stock_decompositions()
+    table[aten.native_layer_norm.default] = _native_layer_norm
+    return table
+
+
+def _stock_decompositions():
+    from torch._decomp import get_decompositions
+    return get_decompositions([
+        aten.gelu, aten.native_layer_norm, aten.layer_norm, aten._softmax, aten._log_softmax, aten.var_mean,
+        aten.var, aten.std, aten.silu, aten.addcmul, aten.addcdiv, aten.hardtanh, aten.leaky_relu, aten.elu,
+        aten.softplus, aten.square, aten.rsub, aten.mse_loss, aten.masked_fill, aten.native_dropout,
+        aten.clamp, aten.clamp_min, aten.clamp_max, aten.sigmoid_backward, aten.tanh_backward,
+        aten.threshold_backward, aten.gelu_backward, aten.linear, aten.matmul, aten.expand_as, aten.ones_like,
+        aten.zeros_like, aten.full_like, aten.log_sigmoid_forward, aten.hardswish, aten.hardsigmoid,
+    ])
+
+
+# --------------------------------------------------------------------------------------------------------------------
+# clustering
+# --------------------------------------------------------------------------------------------------------------------
+def _tensor_ok(val) -> bool:
+    if not isinstance(val, torch.Tensor):
+        return False
+    if val.dtype not in _DTYPE_NAMES:
+        return False
+    for s in val.shape:
+        if not isinstance(s, int) or s == 0:  # static, non-empty extents only (AKGCluster.cc:78-110)
+            return False
+    return True
+
+
+def _float_to_int_cast(node) -> bool:
+    if node.target is not aten._to_copy.default:
+        return False
+    src, dst = node.args[0].meta["val"].dtype, node.meta["val"].dtype
+    return src in _FLOATS and dst not in _FLOATS and dst != torch.bool
+
+
+def is_clusterable(node: fx.Node) -> bool:
+    """The op has a lowering, every tensor it touches is static, non-empty and of a supported type."""
+    if node.op != "call_function" or node.target not in _LOWERINGS:
+        return False
+    if not _tensor_ok(node.meta.get("val")):
+        return False
+    for a in node.all_input_nodes:
+        if not _tensor_ok(a.meta.get("val")):
+            return False
+    if _float_to_int_cast(node):
+        return False
+    if node.target is aten._to_copy.default and any(k in node.kwargs and node.kwargs[k] is not None
+                                                    for k in ("device", "layout", "memory_format")):
+        return False
+    if node.target in (aten.div.Tensor, aten.div.Scalar) and node.meta["val"].dtype not in _FLOATS:
+        return False
+    if node.target in (aten.mm.default, aten.bmm.default, aten.addmm.default) and \
+            node.meta["val"].dtype not in _FLOATS:
+        return False
+    if node.target is aten.addmm.default and (node.kwargs.get("beta", 1) != 1 or node.kwargs.get("alpha", 1) != 1):
+        return False
+    return True
+
+
+def cluster_nodes(graph: fx.Graph) -> list[list[fx.Node]]:
+    """Groups clusterable nodes into maximal convex clusters (merging along producer->consumer edges whenever the
+    merged cluster would not have a path that leaves it and comes back)."""
+    nodes = list(graph.nodes)
+    cid = {n: i for i, n in enumerate(nodes)}          # cluster id of every node (singletons at first)
+    members = {i: [n] for i, n in enumerate(nodes)}
+    ok = {n: is_clusterable(n) for n in nodes}
+
+    def successors(c):
+        out = set()
+        for n in members[c]:
+            for u in n.users:
+                if cid[u] != c:
+                    out.add(cid[u])
+        return out
+
+    def reaches_around(a, b):
+        """Is there a path a -> x -> ... -> b with x outside {a, b}?"""
+        stack = [s for s in successors(a) if s != b]
+        seen = set(stack)
+        while stack:
+            c = stack.pop()
+            for s in successors(c):
+                if s == b:
+                    return True
+                if s not in seen:
+                    seen.add(s)
+                    stack.append(s)
+        return False
+
+    for n in nodes:
+        if not ok[n]:
+            continue
+        for p in n.all_input_nodes:
+            if not ok[p] or cid[p] == cid[n]:
+                continue
+            a, b = cid[p], cid[n]
+            if reaches_around(a, b):
+                continue
+            for m in members[b]:
+                cid[m] = a
+            members[a].extend(members.pop(b))
+    order = {n: i for i, n in enumerate(nodes)}
+    clusters = []
+    for c, ms in members.items():
+        if not ok[ms[0]]:
+            continue
+        if not any(_LOWERINGS[m.target][1] for m in ms):
+            continue  # views only: nothing to compute
+        clusters.append(sorted(ms, key=order.__getitem__))
+    return clusters
+
+
+# --------------------------------------------------------------------------------------------------------------------
+# cluster -> description
+# --------------------------------------------------------------------------------------------------------------------
+class FusedSubgraph:
+    """One cluster: its description, the fx nodes that feed it and the fx nodes it produces."""
+
+    def __init__(self, name: str, desc: dict, inputs: list[fx.Node], outputs: list[fx.Node]):
+        self.name, self.desc, self.inputs, self.outputs = name, desc, inputs, outputs
+        self.out_meta = [(tuple(int(s) for s in o.meta["val"].shape), o.meta["val"].dtype) for o in outputs]
+        self.desc_json = json.dumps(desc)
+
+
+def lower_cluster(cluster: Sequence[fx.Node], index: int) -> FusedSubgraph:
+    inside = set(cluster)
+    names = "_".join(dict.fromkeys(str(n.target).split(".")[1].capitalize() for n in cluster
+                                   if _LOWERINGS[n.target][1]))
+    L = _Lower(f"Fused_{names[:80]}_{index}")
+    env: dict[fx.Node, dict] = {}
+    inputs: list[fx.Node] = []
+
+    def operand(a):
+        if isinstance(a, fx.Node):
+            if a not in env:
+                env[a] = L.b.input(f"in{len(inputs)}_{a.name}", _Lower.shape(a), _Lower.dtype(a))
+                inputs.append(a)
+            return env[a]
+        if isinstance(a, (list, tuple)) and a and isinstance(a[0], fx.Node):
+            return [operand(x) for x in a]
+        return a
+
+    for n in cluster:
+        fn, _ = _LOWERINGS[n.target]
+        env[n] = fn(L, n, *[operand(a) for a in n.args], **{k: operand(v) for k, v in n.kwargs.items()})
+    outputs = [n for n in cluster if any(u not in inside for u in n.users)]
+    seen = set()
+    for n in outputs:
+        t = env[n]
+        if t["tensor_name"] in seen or t["tensor_name"] in {env[i]["tensor_name"] for i in inputs}:
+            # a result listed twice, or an input passed straight through: give it a node of its own
+            t = L.b.emit("Reshape", [t], t["shape"], t["data_type"], [_attr("shape", "listInt", list(t["shape"]))])
+        seen.add(t["tensor_name"])
+        L.b.output(t)
+    return FusedSubgraph(L.b.op, L.b.build(), inputs, outputs)
+
+
+# --------------------------------------------------------------------------------------------------------------------
+# execution of one cluster
+# --------------------------------------------------------------------------------------------------------------------
+class AkgExecutor:
+    """Compiles a cluster's description with the CUDA library on first use and launches it on torch's current stream."""
+
+    def __init__(self):
+        self._kernels: dict[str, object] = {}
+
+    def kernel(self, sub: FusedSubgraph, device: torch.device):
+        from .driver import FusedKernel
+        key = (sub.name, device.index)
+        k = self._kernels.get(key)
+        if k is None:
+            k = self._kernels[key] = FusedKernel(sub.desc_json, device=device.index if device.index is not None else -1)
+        return k
+
+    def __call__(self, sub: FusedSubgraph, *tensors: torch.Tensor):
+        dev = tensors[0].device
+        if dev.type != "cuda":
+            raise RuntimeError("akg_call runs on CUDA tensors only; there is no host path")
+        k = self.kernel(sub, dev)
+        ins = [t.contiguous() for t in tensors]
+        outs = [torch.empty(shape, dtype=dt, device=dev) for shape, dt in sub.out_meta]
+        k.launch(ins + outs)
+        return tuple(outs)
+
+
+_default_executor = AkgExecutor()
+
+
+def akg_call(sub: FusedSubgraph, *tensors: torch.Tensor, executor: Callable | None = None):
+    """The custom call a fused cluster is replaced by (the counterpart of ``mfuse.akg_call``): runs the cluster's
+    description on the given tensors and returns its results as a tuple."""
+    return (executor or _default_executor)(sub, *tensors)
+
+
+def _bound_call(sub: FusedSubgraph, executor, index: int):
+    def call(*tensors):
+        return akg_call(sub, *tensors, executor=executor)
+    call.__name__ = call.__qualname__ = f"akg_call_{index}"
+    return call
+
+
+# --------------------------------------------------------------------------------------------------------------------
+# whole-graph rewrite
+# --------------------------------------------------------------------------------------------------------------------
+class FusedModule(torch.nn.Module):
+    """Result of `fuse_and_optimize`: call it like the original function."""
+
+    def __init__(self, gm: fx.GraphModule, subgraphs: list[FusedSubgraph], n_clustered: int, n_total: int):
+        super().__init__()
+        self.gm = gm
+        self.subgraphs = subgraphs
+        self.clustered_ops = n_clustered
+        self.total_ops = n_total
+
+    def forward(self, *args):
+        return self.gm(*args)
+
+    def descriptions(self) -> list[dict]:
+        return [s.desc for s in self.subgraphs]
+
+
+def trace(fn: Callable, example_inputs: Sequence[torch.Tensor]) -> fx.GraphModule:
+    """aten-level graph of `fn` with shapes and types recorded on every node (no kernels run: fake tensors)."""
+    from torch.fx.experimental.proxy_tensor import make_fx
+    return make_fx(fn, decomposition_table=_decompositions(), tracing_mode="fake")(*example_inputs)
+
+
+def fuse_and_optimize(fn: Callable, example_inputs: Sequence[torch.Tensor],
+                      executor: Callable | None = None) -> FusedModule:
+    """Traces `fn`, clusters what the kernel library can run and returns a module in which every cluster is one
+    ``akg_call``.  Shapes are those of `example_inputs` (static, like the reference's clustering)."""
+    gm = trace(fn, example_inputs)
+    gm.graph.eliminate_dead_code()
+    clusters = cluster_nodes(gm.graph)
+    subs = [lower_cluster(c, i) for i, c in enumerate(clusters)]
+    owner = {n: i for i, c in enumerate(clusters) for n in c}
+
+    # Rebuild the graph in dependency order with one call per cluster (a cluster's first outside user may sit before
+    # the cluster's last node in the traced order).
+    new = fx.Graph()
+    env: dict[fx.Node, fx.Node] = {}
+    emitted: set[int] = set()
+    old_nodes = list(gm.graph.nodes)
+
+    def emit_cluster(i):
+        if i in emitted:
+            return
+        emitted.add(i)
+        sub = subs[i]
+        for a in sub.inputs:
+            ensure(a)
+        call = new.call_function(_bound_call(sub, executor, i), tuple(env[a] for a in sub.inputs))
+        for k, o in enumerate(sub.outputs):
+            env[o] = new.call_function(operator.getitem, (call, k))
+
+    def ensure(n):
+        if n in env:
+            return
+        if n in owner:
+            emit_cluster(owner[n])
+            return
+        for a in n.all_input_nodes:
+            ensure(a)
+        env[n] = new.node_copy(n, lambda x: env[x])
+
+    for n in old_nodes:
+        if n.op == "placeholder":
+            ensure(n)
+    for n in old_nodes:
+        if n.op == "output":
+            for a in n.all_input_nodes:
+                ensure(a)
+            new.output(fx.node.map_arg(n.args[0], lambda x: env[x]))
+        elif n not in owner:
+            ensure(n)
+    new.lint()
+    out = fx.GraphModule(gm, new)
+    n_total = sum(1 for n in old_nodes if n.op == "call_function")
+    return FusedModule(out, subs, sum(len(c) for c in clusters), n_total)

@@ -485,3 +485,52 @@ def test_pad_split_argmax(lib):
     x = b.input("x", [5, 40, 9], "float16")
     b.output(b.emit("ArgMax", [x], [5, 1, 9], "int32", _reduce_attr([1], True)))
     check(b.build(), [rng.standard_normal((5, 40, 9)).astype(np.float16)], exact=True)
+
+
+def test_matmul_float16_and_float32_operands(lib):
+    rng = np.random.default_rng(80)
+    mm_attr = [_attr("transpose_a", "bool", False), _attr("transpose_b", "bool", False)]
+    # float16 operands on the tensor cores, f32 accumulation, fused bias + ReLU + cast back to float16
+    m, k_, n = 300, 136, 264
+    b = _Builder("Fused_MatMul_Add_Max_Cast_80")
+    a = b.input("a", [m, k_], "float16")
+    w = b.input("w", [k_, n], "float16")
+    bias = b.input("bias", [n], "float32")
+    c = b.emit("MatMul", [a, w], [m, n], "float32", mm_attr)
+    c = b.emit("Add", [c, bias], [m, n], "float32")
+    c = b.emit("Maximum", [c, b.const(0.0, "float32")], [m, n], "float32")
+    b.output(b.emit("Cast", [c], [m, n], "float16", [_attr("dst_type", "str", "float16")]))
+    d = b.build()
+    ins = [(rng.standard_normal((m, k_)) * 0.1).astype(np.float16), (rng.standard_normal((k_, n)) * 0.1).astype(np.float16),
+           rng.standard_normal(n).astype(np.float32) * 0.1]
+    got, kern = run(d, ins)
+    want = np.maximum(ins[0].astype(np.float64) @ ins[1].astype(np.float64) + ins[2], 0.0)
+    assert kern.launch_count == 1 and got[0].dtype == np.float16
+    np.testing.assert_allclose(got[0].astype(np.float64), want, rtol=2e-3, atol=2e-3)
+    # float32 operands: one fused-multiply-add chain per element in k order -> bit-exact against that chain
+    for tb in (False, True):
+        m, k_, n = 150, 77, 203  # ragged in every extent, rows not 16-byte aligned
+        b = _Builder("Fused_MatMul_81")
+        a = b.input("a", [m, k_], "float32")
+        w = b.input("w", [n, k_] if tb else [k_, n], "float32")
+        b.output(b.emit("MatMul", [a, w], [m, n], "float32",
+                        [_attr("transpose_a", "bool", False), _attr("transpose_b", "bool", tb)]))
+        d = b.build()
+        av = rng.standard_normal((m, k_)).astype(np.float32)
+        wv = rng.standard_normal((k_, n)).astype(np.float32)
+        got, kern = run(d, [av, np.ascontiguousarray(wv.T) if tb else wv])
+        acc = np.zeros((m, n), dtype=np.float64)
+        for kk in range(k_):  # fma in float32: exact product + accumulator, rounded once (float64 holds it exactly)
+            acc = (av[:, kk:kk + 1].astype(np.float64) * wv[kk:kk + 1, :].astype(np.float64) + acc).astype(np.float32).astype(np.float64)
+        assert bits_equal(got[0], acc.astype(np.float32))
+        np.testing.assert_allclose(got[0], O.evaluate(d, [av, np.ascontiguousarray(wv.T) if tb else wv])[0], rtol=1e-4, atol=1e-4)
+    # batched float32 with a shared right operand
+    b = _Builder("Fused_BatchMatMul_82")
+    a = b.input("a", [5, 64, 48], "float32")
+    w = b.input("w", [48, 96], "float32")
+    b.output(b.emit("BatchMatMul", [a, w], [5, 64, 96], "float32", mm_attr))
+    d = b.build()
+    ins = [rng.standard_normal((5, 64, 48)).astype(np.float32), rng.standard_normal((48, 96)).astype(np.float32)]
+    got, kern = run(d, ins)
+    assert kern.launch_count == 1
+    np.testing.assert_allclose(got[0], O.evaluate(d, ins)[0], rtol=1e-4, atol=1e-4)

@@ -1,0 +1,151 @@
+"""The PyTorch front door: tracing, clustering and the descriptions it emits.
+
+CPU tests run every cluster through the NumPy restatement (the checker) in place of the CUDA library and compare the
+whole program with torch eager; GPU tests run the clusters on the device through the library.
+"""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from akg_b200 import torch_frontend as TF  # noqa: E402
+from oracle import akg_oracle as O  # noqa: E402
+
+_NP = {torch.float32: np.float32, torch.float16: np.float16, torch.int32: np.int32, torch.bool: np.bool_,
+       torch.int8: np.int8}
+
+
+def oracle_executor(sub, *tensors):
+    ins = [t.detach().cpu().contiguous().numpy() for t in tensors]
+    ins = [a.reshape(d[0]["shape"]) for a, d in zip(ins, sub.desc["input_desc"])]
+    outs = O.evaluate(sub.desc, ins)
+    return tuple(torch.from_numpy(np.ascontiguousarray(o)).reshape(shape).to(tensors[0].device)
+                 for o, (shape, _) in zip(outs, sub.out_meta))
+
+
+def gelu_bias(x, bias, y):
+    return torch.nn.functional.gelu(x + bias, approximate="tanh") * y
+
+
+def layer_norm(x, g, b):
+    return torch.nn.functional.layer_norm(x, (x.shape[-1],), g, b, 1e-5)
+
+
+def masked_softmax(s, mask):
+    return torch.softmax(s * 0.125 + mask, dim=-1)
+
+
+def mlp(x, w1, b1, w2):
+    h = torch.relu(x @ w1 + b1)
+    return (h @ w2).sum(dim=0)
+
+
+def mixed(x, idx, y):
+    # an op the library does not take (index_select) between two fusable regions
+    a = torch.tanh(x) * 2.0
+    g = torch.index_select(a, 0, idx)
+    return torch.where(g > 0.5, g, y) - 1.0, a.amax(dim=1)
+
+
+CASES = {
+    "gelu_bias": (gelu_bias, lambda g: [torch.randn(4, 64, 128, generator=g), torch.randn(128, generator=g) * 0.02,
+                                       torch.randn(4, 64, 128, generator=g)], 1e-5),
+    "layer_norm": (layer_norm, lambda g: [torch.randn(64, 256, generator=g), torch.rand(256, generator=g) + 0.5,
+                                         torch.randn(256, generator=g) * 0.1], 1e-5),
+    "masked_softmax": (masked_softmax, lambda g: [torch.randn(3, 32, 32, generator=g),
+                                                 torch.triu(torch.full((32, 32), float("-inf")), 1)], 1e-6),
+    "mlp": (mlp, lambda g: [torch.randn(48, 64, generator=g), torch.randn(64, 96, generator=g) * 0.1,
+                            torch.randn(96, generator=g), torch.randn(96, 32, generator=g) * 0.1], 1e-4),
+    "mixed": (mixed, lambda g: [torch.randn(16, 40, generator=g), torch.tensor([3, 1, 7, 7, 0, 15]),
+                                torch.randn(6, 40, generator=g)], 1e-6),
+}
+
+
+def _close(got, want, tol):
+    got = got if isinstance(got, (tuple, list)) else [got]
+    want = want if isinstance(want, (tuple, list)) else [want]
+    assert len(got) == len(want)
+    for a, b in zip(got, want):
+        assert a.shape == b.shape and a.dtype == b.dtype
+        torch.testing.assert_close(a.cpu(), b.cpu(), rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_clusters_reproduce_eager_on_the_checker(name):
+    fn, make, tol = CASES[name]
+    ins = make(torch.Generator().manual_seed(0))
+    fused = TF.fuse_and_optimize(fn, ins, executor=oracle_executor)
+    assert fused.subgraphs, "nothing was clustered"
+    _close(fused(*ins), fn(*ins), tol)
+    # fresh values through the same module
+    ins2 = make(torch.Generator().manual_seed(1))
+    _close(fused(*ins2), fn(*ins2), tol)
+
+
+def test_cluster_structure():
+    g = torch.Generator().manual_seed(0)
+    # one cluster for a pure elementwise/broadcast chain, with exactly the external tensors as inputs
+    fn, make, _ = CASES["gelu_bias"]
+    fused = TF.fuse_and_optimize(fn, make(g), executor=oracle_executor)
+    assert len(fused.subgraphs) == 1 and fused.clustered_ops == fused.total_ops
+    d = fused.subgraphs[0].desc
+    assert len(d["input_desc"]) == 3 and len(d["output_desc"]) == 1
+    assert {o["name"] for o in d["op_desc"]} >= {"Add", "Mul", "Tanh"}
+    # the unsupported op splits the program in two clusters and stays a torch call
+    fn, make, _ = CASES["mixed"]
+    fused = TF.fuse_and_optimize(fn, make(g), executor=oracle_executor)
+    assert len(fused.subgraphs) == 2
+    targets = [n.target for n in fused.gm.graph.nodes if n.op == "call_function"]
+    assert torch.ops.aten.index_select.default in targets
+    assert sum(1 for t in targets if getattr(t, "__name__", "").startswith("akg_call_")) == 2
+
+
+def test_what_is_not_clustered():
+    g = torch.Generator().manual_seed(0)
+
+    def f(x):  # float -> int conversion: its rounding is not pinned, so it stays with torch
+        return (x * 3.0).to(torch.int32) + 1
+
+    fused = TF.fuse_and_optimize(f, [torch.randn(8, 8, generator=g)], executor=oracle_executor)
+    kept = [n.target for n in fused.gm.graph.nodes if n.op == "call_function"]
+    assert torch.ops.aten._to_copy.default in kept
+    x = torch.randn(8, 8, generator=g)
+    _close(fused(x), f(x), 0)
+
+    def views_only(x):
+        return x.reshape(4, 16).unsqueeze(0)
+
+    fused = TF.fuse_and_optimize(views_only, [torch.randn(8, 8, generator=g)], executor=oracle_executor)
+    assert not fused.subgraphs
+
+
+def test_default_executor_has_no_host_path():
+    fn, make, _ = CASES["gelu_bias"]
+    ins = make(torch.Generator().manual_seed(0))
+    fused = TF.fuse_and_optimize(fn, ins)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        fused(*ins)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", list(CASES))
+def test_fused_module_on_the_device(name):
+    fn, make, tol = CASES[name]
+    ins = [t.cuda() for t in make(torch.Generator().manual_seed(2))]
+    fused = TF.fuse_and_optimize(fn, ins)
+    assert fused.subgraphs
+    _close(fused(*ins), fn(*ins), max(tol, 2e-5))
+
+
+@pytest.mark.gpu
+def test_fused_half_precision_chain_on_the_device():
+    g = torch.Generator().manual_seed(3)
+    ins = [torch.randn(8, 256, 512, generator=g).half().cuda(), (torch.randn(512, generator=g) * 0.02).half().cuda(),
+           torch.randn(8, 256, 512, generator=g).half().cuda()]
+    fused = TF.fuse_and_optimize(gelu_bias, ins)
+    got, want = fused(*ins), gelu_bias(*ins)
+    assert got.dtype == torch.float16
+    torch.testing.assert_close(got.float(), want.float(), rtol=2e-3, atol=2e-3)
