@@ -92,6 +92,8 @@ _SIGNATURES = [
     ("akgb_profile_host", ctypes.c_int, [_vp, ctypes.POINTER(_vp), ctypes.c_int32, ctypes.c_int32,
                                           ctypes.POINTER(ctypes.c_double)]),
     ("akgb_kernel_meta", ctypes.c_int, [_vp, ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t)]),
+    ("akgb_set_cache_dir", ctypes.c_int, [ctypes.c_char_p]),
+    ("akgb_jit_cache_stats", ctypes.c_int, [ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]),
     ("akgb_dump_jit_source", ctypes.c_int, [_vp, ctypes.c_int32, ctypes.c_char_p, ctypes.c_size_t,
                                              ctypes.POINTER(ctypes.c_size_t)]),
     ("akgb_kernel_class", ctypes.c_char_p, [_vp]),

@@ -591,6 +591,16 @@ akgb_status akgb_check_device_error(akgb_kernel* k, uint32_t* word) {
   return AKGB_OK;
 }
 
+akgb_status akgb_set_cache_dir(const char* dir) {
+  jit_set_cache_dir(dir);
+  return AKGB_OK;
+}
+
+akgb_status akgb_jit_cache_stats(uint64_t* compiled, uint64_t* loaded_from_disk) {
+  jit_cache_stats(compiled, loaded_from_disk);
+  return AKGB_OK;
+}
+
 akgb_status akgb_dump_jit_source(const akgb_kernel* k, int32_t vectorised, char* buf, size_t cap, size_t* needed) {
   if (!k) return fail(AKGB_INVALID_ARG, "null argument");
   std::string src;

@@ -13,6 +13,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <dlfcn.h>
+#include <unistd.h>
 
 #include <cstdio>
 #include <cstring>
@@ -408,22 +409,84 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
   return true;
 }
 
+constexpr const char* kJitOptionsTag = "akgb-ew-jit-1 sm_100a c++17 fmad=false";
+
 struct JitKernel {
   CUfunction fn = nullptr;
   bool failed = false;
 };
 std::mutex g_mu;
-std::map<std::string, JitKernel> g_cache;  // source text -> kernel (per process; modules live until exit)
+std::map<std::string, JitKernel> g_cache;  // device + source text -> kernel (per process; modules live until exit)
+std::string g_cache_dir;                   // set by jit_set_cache_dir; empty = look at the environment
+bool g_cache_dir_set = false;
+uint64_t g_n_compiled = 0, g_n_from_disk = 0;
+
+// Directory of the on-disk cubin cache: the explicit setting, else AKGB_JIT_CACHE_DIR, else KERNEL_META_DIR (where
+// the reference keeps its compiled kernels, akg-mlir/python/akg_mlir/mlir_driver.py:47-53); empty = no disk cache.
+std::string cache_dir() {
+  if (g_cache_dir_set) return g_cache_dir;
+  for (const char* name : {"AKGB_JIT_CACHE_DIR", "KERNEL_META_DIR"}) {
+    const char* v = std::getenv(name);
+    if (v && *v) return v;
+  }
+  return "";
+}
+
+bool read_file(const std::string& path, std::vector<char>* out) {
+  FILE* f = std::fopen(path.c_str(), "rb");
+  if (!f) return false;
+  std::fseek(f, 0, SEEK_END);
+  const long n = std::ftell(f);
+  std::fseek(f, 0, SEEK_SET);
+  bool ok = n > 4;
+  if (ok) {
+    out->resize((size_t)n);
+    ok = std::fread(out->data(), 1, (size_t)n, f) == (size_t)n;
+  }
+  std::fclose(f);
+  // an ELF image, as NVRTC produced it; anything else (a torn or foreign file) is ignored
+  return ok && (*out)[0] == 0x7f && (*out)[1] == 'E' && (*out)[2] == 'L' && (*out)[3] == 'F';
+}
+
+void write_file_atomically(const std::string& path, const std::vector<char>& data) {
+  const std::string tmp = path + ".tmp." + std::to_string((long long)getpid());
+  FILE* f = std::fopen(tmp.c_str(), "wb");
+  if (!f) return;
+  const bool ok = std::fwrite(data.data(), 1, data.size(), f) == data.size();
+  std::fclose(f);
+  if (!ok || std::rename(tmp.c_str(), path.c_str()) != 0) std::remove(tmp.c_str());
+}
 
 JitKernel* compile(const std::string& src) {
   std::lock_guard<std::mutex> lock(g_mu);
-  auto it = g_cache.find(src);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const std::string key = std::to_string(dev) + ":" + src;  // a loaded function belongs to one device's context
+  auto it = g_cache.find(key);
   if (it != g_cache.end()) return &it->second;
-  JitKernel& k = g_cache[src];
+  JitKernel& k = g_cache[key];
   k.failed = true;
   Nvrtc& n = nvrtc();
   Driver& d = driver();
-  if (!n.ok || !d.ok) return &k;
+  if (!d.ok) return &k;
+  // on-disk cache, keyed by the digest of the generated text and the compile options
+  const std::string dir = cache_dir();
+  std::string path;
+  if (!dir.empty()) {
+    const std::string tagged = std::string(kJitOptionsTag) + "\n" + src;
+    path = dir + "/akgb_ew_" + sha256_hex(tagged.data(), tagged.size()) + ".sm_100a.cubin";
+    std::vector<char> image;
+    if (read_file(path, &image)) {
+      CUmodule mod = nullptr;
+      if (d.ModuleLoadData(&mod, image.data()) == CUDA_SUCCESS &&
+          d.ModuleGetFunction(&k.fn, mod, "akgb_ew_jit") == CUDA_SUCCESS) {
+        k.failed = false;
+        ++g_n_from_disk;
+        return &k;
+      }
+    }
+  }
+  if (!n.ok) return &k;
   nvrtcProgram prog = nullptr;
   if (n.CreateProgram(&prog, src.c_str(), "akgb_ew_jit.cu", 0, nullptr, nullptr) != 0) return &k;
   const char* opts[] = {"--gpu-architecture=sm_100a", "-std=c++17", "--fmad=false", "-default-device"};
@@ -450,12 +513,26 @@ JitKernel* compile(const std::string& src) {
   if (d.ModuleLoadData(&mod, cubin.data()) != CUDA_SUCCESS) return &k;
   if (d.ModuleGetFunction(&k.fn, mod, "akgb_ew_jit") != CUDA_SUCCESS) return &k;
   k.failed = false;
+  ++g_n_compiled;
+  if (!path.empty()) write_file_atomically(path, cubin);
   return &k;
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace
+
+void jit_set_cache_dir(const char* dir) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  g_cache_dir = dir ? dir : "";
+  g_cache_dir_set = dir != nullptr;
+}
+
+void jit_cache_stats(uint64_t* compiled, uint64_t* from_disk) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (compiled) *compiled = g_n_compiled;
+  if (from_disk) *from_disk = g_n_from_disk;
+}
 
 // The CUDA C++ text that would be compiled for this program (empty when the program needs the interpreter).
 std::string ew_jit_source(const EwProgram& P, bool vec) {

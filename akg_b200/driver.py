@@ -205,6 +205,19 @@ def compile_info(info_json, **kw) -> FusedKernel:
     return FusedKernel(info_json, **kw)
 
 
+def set_cache_dir(path: str | None):
+    """``akgb_set_cache_dir``: where run-time compiled kernels are kept between processes (None: the environment's
+    choice, "": no disk cache)."""
+    _capi.check(_capi.load().akgb_set_cache_dir(None if path is None else os.fsencode(path)))
+
+
+def jit_cache_stats() -> tuple[int, int]:
+    """(kernels compiled by this process, kernels loaded from the on-disk cache)."""
+    a, b = ctypes.c_uint64(0), ctypes.c_uint64(0)
+    _capi.check(_capi.load().akgb_jit_cache_stats(ctypes.byref(a), ctypes.byref(b)))
+    return int(a.value), int(b.value)
+
+
 def get_kernel_meta_path() -> str:
     """Directory of the kernel metadata files, resolved from the same environment variables as the reference
     (``KERNEL_META_DIR``, ``MS_COMPILER_CACHE_PATH``; ``akg-mlir/python/akg_mlir/mlir_driver.py:47-53``)."""
@@ -236,7 +249,9 @@ class MlirDriver:
         self.kernel = FusedKernel(text, device=self.device)
         # <kernel>.json beside where the reference writes <kernel>.ptx/.json: launch dims, kernelName, sha256 ...
         # (the launch dims are those of the planned template and are refined at the first launch)
+        # kernels generated at the first launch are cached there too, as the reference's <kernel>.ptx is
         os.makedirs(self.output_dir, exist_ok=True)
+        set_cache_dir(self.output_dir)
         with open(os.path.join(self.output_dir, self.kernel_name + ".json"), "w", encoding="utf-8") as f:
             json.dump(self.kernel.meta(), f)
 

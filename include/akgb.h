@@ -153,6 +153,17 @@ akgb_status akgb_kernel_meta(const akgb_kernel* k, char* buf, size_t cap, size_t
  * (AKG_DUMP_IR, python/akg_mlir/mlir_driver.py:711-721). */
 akgb_status akgb_dump_jit_source(const akgb_kernel* k, int32_t vectorised, char* buf, size_t cap, size_t* needed);
 
+/* Directory of the on-disk cache of run-time compiled kernels.  The reference keeps its compiled kernels
+ * (<kernel>.ptx / .json) under KERNEL_META_DIR and reuses them by name (python/akg_mlir/mlir_driver.py:47-53,
+ * 337-374); here every generated elementwise kernel is stored as
+ * `<dir>/akgb_ew_<sha256 of the generated text and options>.sm_100a.cubin` and loaded from there by later
+ * processes instead of being compiled again.  Without this call the directory is $AKGB_JIT_CACHE_DIR, else
+ * $KERNEL_META_DIR, else there is no disk cache.  NULL returns to the environment's choice, "" disables. */
+akgb_status akgb_set_cache_dir(const char* dir);
+
+/* How many generated kernels this process compiled, and how many it loaded from the on-disk cache. */
+akgb_status akgb_jit_cache_stats(uint64_t* compiled, uint64_t* loaded_from_disk);
+
 /* Operator class the matcher assigned, as a static string
  * ("elementwise", "broadcast", "reduce_x", "reduce_y", "reduce_all",
  * "layernorm", "softmax", "transpose", "matmul", "generic"). */

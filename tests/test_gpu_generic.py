@@ -2,6 +2,8 @@
 transpose / matmul launches).  The shapes and op mixes follow the kinds of fused regions in the reference's own
 system-test corpus (akg-mlir/tests/st/**: add chains, Cast+Mul, Sub+RealDiv with a broadcast operand, Mul+RealDiv+Exp,
 LessEqual, Select, Mul->ReduceSum over X/ALL, ReduceSum over Y with keep_dims, [1,1]->[1,N] broadcasts)."""
+import os
+
 import numpy as np
 import pytest
 
@@ -534,3 +536,41 @@ def test_matmul_float16_and_float32_operands(lib):
     got, kern = run(d, ins)
     assert kern.launch_count == 1
     np.testing.assert_allclose(got[0], O.evaluate(d, ins)[0], rtol=1e-4, atol=1e-4)
+
+
+def test_generated_kernels_are_reused_from_disk(tmp_path):
+    """Two processes in a row with the same cache directory: the first compiles and stores the kernel, the second
+    loads the stored image and compiles nothing; both produce the same bits."""
+    import subprocess
+    import sys
+    script = r'''
+import sys, numpy as np
+sys.path.insert(0, sys.argv[1])
+from akg_b200.driver import FusedKernel, set_cache_dir, jit_cache_stats
+from akg_b200.descs import _Builder
+set_cache_dir(sys.argv[2])
+b = _Builder("Fused_Mul_Add_Exp_90")
+x = b.input("x", [64, 1000], "float32"); y = b.input("y", [1000], "float32")
+t = b.emit("Mul", [x, y], [64, 1000], "float32")
+t = b.emit("Add", [t, b.const(0.25, "float32")], [64, 1000], "float32")
+b.output(b.emit("Exp", [t], [64, 1000], "float32"))
+k = FusedKernel(b.build())
+rng = np.random.default_rng(5)
+ins = [rng.standard_normal((64, 1000)).astype(np.float32), rng.standard_normal(1000).astype(np.float32)]
+out = k.empty_outputs()
+k.run_host(ins + out)
+compiled, from_disk = jit_cache_stats()
+print(compiled, from_disk, out[0].view(np.uint32).sum(dtype=np.uint64))
+'''
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    runs = []
+    for _ in range(2):
+        r = subprocess.run([sys.executable, "-c", script, root, str(tmp_path)], capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr
+        runs.append(r.stdout.split())
+    assert runs[0][:2] == ["1", "0"], runs
+    assert runs[1][:2] == ["0", "1"], runs
+    assert runs[0][2] == runs[1][2]
+    files = [f for f in os.listdir(tmp_path) if f.startswith("akgb_ew_") and f.endswith(".sm_100a.cubin")]
+    assert len(files) == 1
+
