@@ -186,6 +186,7 @@ Graph parse_info(const char* text, size_t len) {
         if (j == 1 && attr_as_second_input(n.name)) continue;  // attribute operand, read below
         if (j >= 1 && n.kind == OpK::StridedSlice) continue;
         if (j >= 2 && (n.kind == OpK::Gather || n.kind == OpK::UnsortedSegmentSum)) continue;  // axis / num_segments
+        if (j >= 1 && n.kind == OpK::Cast) continue;  // a type id some producers append; the result type decides
         operand_descs.push_back(ins[j].is_array() ? &ins[j][0] : &ins[j]);
       }
     }
@@ -436,8 +437,23 @@ Graph parse_info(const char* text, size_t len) {
     const std::string& name = d.at("tensor_name").as_string();
     auto it = by_name.find(name);
     if (it == by_name.end()) throw JsonError("output '" + name + "' is not produced by any op");
+    if (g.values[it->second].output_index >= 0) {
+      // listed twice: the second caller buffer receives a copy (a Reshape to the same shape, planned as a copy)
+      const int src = it->second;
+      Node cp;
+      cp.name = "Reshape";
+      cp.kind = OpK::Reshape;
+      cp.in = {src};
+      const int dup = new_value(name + "#" + std::to_string(i), g.values[src].shape, g.values[src].dt);
+      g.values[dup].producer = (int)g.nodes.size();
+      cp.out = dup;
+      g.values[src].users.push_back((int)g.nodes.size());
+      g.nodes.push_back(std::move(cp));
+      g.values[dup].output_index = (int)i;
+      g.outputs.push_back(dup);
+      continue;
+    }
     Value& v = g.values[it->second];
-    if (v.output_index >= 0) throw Unsupported("a tensor listed twice in output_desc");
     v.output_index = (int)i;
     // the declared output shape may differ from the op's by a trailing view
     // change only; keep the op's shape when the element counts agree

@@ -143,6 +143,35 @@ struct Builder {
     return false;
   }
 
+  // Would the open group, with node `cand` added, still fit one launch of the elementwise kernel (tensor operands,
+  // constants, results, instructions)?  Results are counted as "used by something not in the group so far", which
+  // over-counts values whose consumers have not been visited yet; that only splits a very wide group early.
+  bool group_fits_with(int cand) const {
+    std::vector<int> list = group;
+    list.push_back(cand);
+    std::set<int> inside, ext, consts;
+    for (int ni : list) inside.insert(g.nodes[ni].out);
+    int instr = 0, outs = 0;
+    for (int ni : list) {
+      const Node& n = g.nodes[ni];
+      instr += n.kind == OpK::AddN ? (int)n.in.size() : 1;
+      for (int vid : n.in) {
+        if (inside.count(vid)) continue;
+        if (g.v(vid).is_const) consts.insert(vid);
+        else ext.insert(vid);
+      }
+      const Value& o = g.v(n.out);
+      bool outside = o.output_index >= 0 || n.kind == OpK::Assign;
+      for (int u : o.users)
+        if (std::find(list.begin(), list.end(), u) == list.end()) outside = true;
+      for (auto& kv : alias)
+        if (kv.second == n.out) outside = true;
+      outs += outside;
+    }
+    return (int)ext.size() <= kEwMaxIn && (int)consts.size() <= kEwMaxConst && outs <= kEwMaxOut &&
+           instr <= kEwMaxInstr - 8 && (int)(ext.size() + consts.size()) <= kEwMaxReg - 8;
+  }
+
   void flush_group() {
     if (group.empty()) return;
     Step st;
@@ -845,6 +874,7 @@ struct Builder {
           if (!group.empty() && !produced_in_group(vid) && produced_in_group(root(vid))) flush_group();
         // a Reshape copy consumes its source by flat index: the source must have the group's element order
         if (n.kind == OpK::Reshape && produced_in_group(n.in[0]) && g.v(n.in[0]).shape != S) flush_group();
+        if (!group.empty() && !group_fits_with((int)i)) flush_group();
         if (group.empty()) group_shape = S;
         group.push_back((int)i);
         continue;

@@ -4,7 +4,8 @@ expected-value generator.
 Run in a container where the reference checkout is mounted (default
 ``/root/reference``, override with ``AKG_REFERENCE``)::
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py          # the benchmark classes
+    python tests/golden/make_golden.py corpus   # the reference's own system-test descriptions -> corpus/
 
 For every case it builds a fused-op description, draws seeded inputs, feeds
 both through ``gen_json_data`` of
@@ -31,6 +32,8 @@ REPO = HERE.parent.parent
 sys.path.insert(0, str(REPO))
 
 from akg_b200 import descs  # noqa: E402
+sys.path.insert(0, str(HERE.parent))
+from helpers import corpus_inputs  # noqa: E402
 
 
 def _import_reference():
@@ -117,6 +120,85 @@ def main():
         os.chdir(cwd)
 
 
+def _bind_by_position(desc: dict) -> dict:
+    by_pos = {1: 24, 2: 10, 3: 12, 4: 32}
+
+    def fix(t):
+        if isinstance(t, dict):
+            if isinstance(t.get("shape"), list):
+                r = len(t["shape"])
+                t["shape"] = [by_pos.get(r - i, 8) if e < 0 else e for i, e in enumerate(t["shape"])]
+            for v in t.values():
+                fix(v)
+        elif isinstance(t, list):
+            for v in t:
+                fix(v)
+
+    d = json.loads(json.dumps(desc))
+    fix(d)
+    return d
+
+
+def corpus(max_bytes: int = 2 << 20):
+    """Golden vectors for the fused-operator descriptions of the reference's own system tests
+    (akg-mlir/tests/st/**/*.info*): static shapes, at most `max_bytes` of tensors, evaluated by the reference's
+    expected-value generator on seeded inputs.  Stored under corpus/ as description + input seed + expected outputs."""
+    helper = _import_reference()
+    ref = Path(os.environ.get("AKG_REFERENCE", "/root/reference")) / "akg-mlir" / "tests" / "st"
+    outdir = HERE / "corpus"
+    outdir.mkdir(exist_ok=True)
+    cwd = os.getcwd()
+    os.chdir("/tmp")
+    made = 0
+    try:
+        for f in sorted(ref.rglob("*.info*")):
+            desc = json.loads(f.read_text())
+            tensors = [d for (d,) in desc["input_desc"] or []] + list(desc["output_desc"])
+            shapes = [t.get("shape") or [1] for t in tensors]
+            dynamic_text = None
+            if any(e < 0 for s in shapes for e in s):
+                # dynamic extents: the expected values are computed on a static copy in which an unknown extent
+                # becomes 24 / 10 / 12 / 32 by its position from the end; the fixture keeps the dynamic description
+                # too, for the launch-time binding path
+                dynamic_text = json.dumps(desc)
+                desc = _bind_by_position(desc)
+                tensors = [d for (d,) in desc["input_desc"] or []] + list(desc["output_desc"])
+                shapes = [t.get("shape") or [1] for t in tensors]
+            itemsize = {"bool": 1, "int8": 1, "uint8": 1, "float16": 2, "bfloat16": 2, "int16": 2, "float64": 8,
+                        "int64": 8}
+            total = sum(int(np.prod(s)) * itemsize.get(t["data_type"], 4) for s, t in zip(shapes, tensors))
+            if total > max_bytes:
+                print(f"skip {f.name}: {total} bytes of tensors")
+                continue
+            seed = 100 + made
+            inputs = corpus_inputs(desc, seed)
+            text = json.dumps(desc)
+            try:
+                _, expect, _ = helper.gen_json_data(text, True, input_for_mod=[a.copy() for a in inputs])
+            except Exception as e:  # the reference's generator itself fails on some of its disabled cases
+                print(f"skip {f.name}: expected-value generator raised {type(e).__name__}: {str(e)[:80]}")
+                continue
+            expect = expect if isinstance(expect, (list, tuple)) else [expect]
+            blob = {"desc": np.frombuffer(text.encode(), dtype=np.uint8)}
+            if dynamic_text is not None:
+                blob["desc_dynamic"] = np.frombuffer(dynamic_text.encode(), dtype=np.uint8)
+            blob["seed"] = np.asarray(seed)  # the inputs are redrawn from it (tests/helpers.py::corpus_inputs)
+            try:
+                for i, e in enumerate(expect):
+                    shape = desc["output_desc"][i].get("shape") or [1]
+                    _store(blob, f"out{i}", np.ascontiguousarray(np.asarray(e)).reshape(shape))
+            except ValueError as e:
+                print(f"skip {f.name}: expected values do not have the declared shapes ({e})")
+                continue
+            name = f.name.split(".info")[0]
+            np.savez_compressed(outdir / f"{name}.npz", **blob)
+            made += 1
+            print(f"{name}: {len(inputs)} inputs, {len(expect)} outputs, {total} bytes")
+    finally:
+        os.chdir(cwd)
+    print(made, "corpus fixtures")
+
+
 def _store(blob, key, a):
     if a.dtype.name == "bfloat16":
         blob[key + "__bf16"] = a.view(np.uint16)
@@ -125,4 +207,7 @@ def _store(blob, key, a):
 
 
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) > 1 and sys.argv[1] == "corpus":
+        corpus()
+    else:
+        main()

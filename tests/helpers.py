@@ -54,6 +54,51 @@ def make_inputs(desc, seed=0, kinds=None):
     return out
 
 
+def corpus_inputs(desc: dict, seed: int) -> list[np.ndarray]:
+    """Seeded inputs for a description of the reference's system-test corpus, by type; indices of
+    UnsortedSegmentSum / Gather stay inside their axis."""
+    rng = np.random.default_rng(seed)
+    index_limit = {}
+    for op in desc["op_desc"]:
+        if op["name"] == "UnsortedSegmentSum":
+            ids = op["input_desc"][1][0]["tensor_name"]
+            index_limit[ids] = op["output_desc"][0]["shape"][0]
+        if op["name"] == "Gather":
+            axis = next((a["value"] for a in (op.get("attr") or []) if a["name"] == "axis"), 0)
+            index_limit[op["input_desc"][1][0]["tensor_name"]] = op["input_desc"][0][0]["shape"][axis]
+    positive = any(op["name"] in ("Sqrt", "Rsqrt", "Log") for op in desc["op_desc"])
+    out = []
+    for (d,) in desc["input_desc"]:
+        shape, dt, name = d.get("shape") or [1], d["data_type"], d["tensor_name"]
+        if name in index_limit:
+            a = rng.integers(0, index_limit[name], shape)
+        elif dt == "bool":
+            a = rng.integers(0, 2, shape)
+        elif dt.startswith("int") or dt.startswith("uint"):
+            a = rng.integers(-5, 6, shape)
+        else:
+            a = rng.uniform(0.25, 1.75, shape)  # away from 0: the corpus divides
+            if not positive:
+                a = a * rng.choice([-1.0, 1.0], shape)
+        npdt = BF16 if dt == "bfloat16" else np.dtype(dt)
+        out.append(np.ascontiguousarray(a.astype(npdt)))
+    return out
+
+
+def corpus_cases():
+    return sorted(p.stem for p in (GOLDEN / "corpus").glob("*.npz"))
+
+
+def load_corpus(name):
+    """(static description, dynamic description or None, inputs, expected outputs) of one corpus fixture."""
+    z = np.load(GOLDEN / "corpus" / f"{name}.npz")
+    desc = json.loads(bytes(z["desc"]).decode())
+    dyn = json.loads(bytes(z["desc_dynamic"]).decode()) if "desc_dynamic" in z else None
+    ins = corpus_inputs(desc, int(z["seed"]))
+    outs = [z[f"out{i}"] if f"out{i}" in z else z[f"out{i}__bf16"].view(BF16) for i in range(len(desc["output_desc"]))]
+    return desc, dyn, ins, outs
+
+
 KINDS = {
     "layernorm": {"gamma": "gamma", "beta": "beta"},
     "gelu": {"bias": "normal_small"},
