@@ -28,7 +28,7 @@ CASES = {
     "colsum": (lambda s: descs.reduce_sum_axis0(s[0], s[1]), {}),
     "gmax": (lambda s: descs.reduce_max_all(s[0], s[1]), {}),
     "transpose": (lambda s: descs.transpose(s, [0, 2, 1, 3]), {}),
-    "matmul": (lambda s: descs.matmul_bias_relu(s[0], s[1], s[2]),
+    "matmul": (lambda s, dtype="bfloat16": descs.matmul_bias_relu(s[0], s[1], s[2], dtype=dtype),
                {"a": "normal_small", "b": "normal_small", "bias": "normal_small"}),
 }
 
@@ -76,6 +76,7 @@ def main(argv=None):
     ap.add_argument("-f", "--file", help="fused-op description (.info JSON)")
     ap.add_argument("--case", choices=sorted(CASES), help="build a benchmarked description instead")
     ap.add_argument("--shape", default="", help="comma-separated extents for --case")
+    ap.add_argument("--dtype", default="", help="operand type for --case matmul (bfloat16, float16, float32)")
     ap.add_argument("--repeat", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--device", type=int, default=0)
@@ -89,7 +90,7 @@ def main(argv=None):
     else:
         shape = [int(x) for x in args.shape.split(",") if x]
         build, kinds = CASES[args.case]
-        desc = build(shape)
+        desc = build(shape, args.dtype) if args.dtype and args.case == "matmul" else build(shape)
     torch.cuda.set_device(args.device)
     device = torch.device("cuda", args.device)
     k = FusedKernel(desc, device=args.device)

@@ -186,21 +186,21 @@ def reduce_sum_and_max(rows: int, cols: int) -> dict:
 
 
 def matmul_bias_relu(m: int, k: int, n: int, transpose_b: bool = False, with_bias: bool = True,
-                     relu: bool = True) -> dict:
-    """A bf16[m,k] x B bf16[k,n] -> f32 accumulate (+ bias bf16[n]) (ReLU) -> bf16[m,n]."""
+                     relu: bool = True, dtype: str = "bfloat16") -> dict:
+    """A[m,k] x B[k,n] -> f32 accumulate (+ bias[n]) (ReLU) -> [m,n] in the operand type (bfloat16, float16, float32)."""
     b = _Builder(f"Fused_MatMul_BiasAdd_ReLU_Cast_{m}x{k}x{n}_7")
-    h, f = "bfloat16", "float32"
+    h, f = dtype, "float32"
     a = b.input("a", [m, k], h)
     bm = b.input("b", [n, k] if transpose_b else [k, n], h)
     attr = [_attr("transpose_a", "bool", False), _attr("transpose_b", "bool", bool(transpose_b))]
     c = b.emit("MatMul", [a, bm], [m, n], f, attr)
     if with_bias:
         bias = b.input("bias", [n], h)
-        bf = b.emit("Cast", [bias], [n], f, [_attr("dst_type", "str", f)])
+        bf = bias if h == f else b.emit("Cast", [bias], [n], f, [_attr("dst_type", "str", f)])
         c = b.emit("Add", [c, bf], [m, n], f)
     if relu:
         c = b.emit("Maximum", [c, b.const(0.0, f)], [m, n], f)
-    out = b.emit("Cast", [c], [m, n], h, [_attr("dst_type", "str", h)], out_name="out")
+    out = c if h == f else b.emit("Cast", [c], [m, n], h, [_attr("dst_type", "str", h)], out_name="out")
     b.output(out)
     return b.build()
 
