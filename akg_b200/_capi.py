@@ -73,6 +73,8 @@ class UnsupportedError(AkgbError):
 
 _lib = None
 
+COMM_ID_BYTES = 128
+
 # every symbol include/akgb.h declares: (name, restype, argtypes)
 _vp = ctypes.c_void_p
 _SIGNATURES = [
@@ -92,6 +94,15 @@ _SIGNATURES = [
     ("akgb_profile_host", ctypes.c_int, [_vp, ctypes.POINTER(_vp), ctypes.c_int32, ctypes.c_int32,
                                           ctypes.POINTER(ctypes.c_double)]),
     ("akgb_kernel_meta", ctypes.c_int, [_vp, ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t)]),
+    ("akgb_comm_unique_id", ctypes.c_int, [ctypes.c_void_p, ctypes.c_size_t]),
+    ("akgb_comm_create", ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                        ctypes.POINTER(ctypes.c_void_p)]),
+    ("akgb_comm_wrap", ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
+                                      ctypes.POINTER(ctypes.c_void_p)]),
+    ("akgb_comm_destroy", None, [ctypes.c_void_p]),
+    ("akgb_allreduce_partials", ctypes.c_int, [_vp, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]),
+    ("akgb_launch_sharded", ctypes.c_int, [_vp, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p,
+                                           ctypes.c_size_t, ctypes.c_void_p]),
     ("akgb_set_cache_dir", ctypes.c_int, [ctypes.c_char_p]),
     ("akgb_jit_cache_stats", ctypes.c_int, [ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]),
     ("akgb_dump_jit_source", ctypes.c_int, [_vp, ctypes.c_int32, ctypes.c_char_p, ctypes.c_size_t,

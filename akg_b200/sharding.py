@@ -57,3 +57,64 @@ def gather_split_outputs(kernel, outputs: Sequence, world: int, group=None) -> l
         else:
             res.append(t)
     return res
+
+
+class Communicator:
+    """``akgb_comm``: the library's own NCCL communicator for the exchange step, one per process (one process per GPU).
+
+    `Communicator.from_process_group()` does the rendezvous over an initialised ``torch.distributed`` group (rank 0
+    creates the id, a broadcast carries its 128 bytes); after that the data path does not go through torch:
+    `launch_sharded` enqueues the kernel and the all-reduce of its partial outputs on one stream."""
+
+    def __init__(self, id_bytes: bytes, rank: int, world: int, device: int = -1):
+        import ctypes
+        self._lib = _capi.load()
+        self._handle = ctypes.c_void_p()
+        buf = ctypes.create_string_buffer(bytes(id_bytes), _capi.COMM_ID_BYTES)
+        _capi.check(self._lib.akgb_comm_create(buf, rank, world, device, ctypes.byref(self._handle)))
+        self.rank, self.world = rank, world
+
+    @staticmethod
+    def unique_id() -> bytes:
+        import ctypes
+        buf = ctypes.create_string_buffer(_capi.COMM_ID_BYTES)
+        _capi.check(_capi.load().akgb_comm_unique_id(buf, _capi.COMM_ID_BYTES))
+        return buf.raw
+
+    @classmethod
+    def from_process_group(cls, device: int = -1, group=None):
+        import torch
+        import torch.distributed as dist
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        on_gpu = dist.get_backend(group) == "nccl"
+        dev = torch.device("cuda", torch.cuda.current_device()) if on_gpu else torch.device("cpu")
+        t = torch.zeros(_capi.COMM_ID_BYTES, dtype=torch.uint8, device=dev)
+        if rank == 0:
+            t.copy_(torch.frombuffer(bytearray(cls.unique_id()), dtype=torch.uint8))
+        dist.broadcast(t, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        return cls(bytes(t.cpu().numpy().tobytes()), rank, world, device)
+
+    def close(self):
+        if getattr(self, "_handle", None) and self._handle.value:
+            self._lib.akgb_comm_destroy(self._handle)
+            self._handle.value = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def launch_sharded(self, kernel, tensors: Sequence, stream=None):
+        """``akgb_launch_sharded`` on contiguous torch CUDA tensors (inputs then outputs)."""
+        import ctypes
+        import torch
+        ws_ptr = 0
+        if kernel.workspace_size:
+            if kernel._workspace is None or kernel._workspace.device != tensors[0].device:
+                kernel._workspace = torch.empty(kernel.workspace_size + 256, dtype=torch.uint8, device=tensors[0].device)
+            ws_ptr = (kernel._workspace.data_ptr() + 255) // 256 * 256
+        s = stream if stream is not None else torch.cuda.current_stream(tensors[0].device)
+        ptrs = (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+        _capi.check(self._lib.akgb_launch_sharded(kernel._handle, self._handle, ptrs, ctypes.c_void_p(ws_ptr),
+                                                  kernel.workspace_size, ctypes.c_void_p(s.cuda_stream)))

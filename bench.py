@@ -217,7 +217,7 @@ def class_configs(world):
     return cfgs
 
 
-def run_classes(rank, world, device, steps, warmup, hbm_peak, tf_peak, barrier, allreduce):
+def run_classes(rank, world, device, steps, warmup, hbm_peak, tf_peak, barrier, comm):
     """One row per class: GB/s (or TFLOP/s) per GPU and aggregate, fraction of the measured peak."""
     import torch
     from akg_b200 import FusedKernel, UnsupportedError
@@ -236,9 +236,10 @@ def run_classes(rank, world, device, steps, warmup, hbm_peak, tf_peak, barrier, 
         partial = [i for i, t in enumerate(k.tensors) if t.shard_kind >= 2]
 
         def step_launch(bufs, stream=None, k=k, partial=partial):
-            k.launch(bufs, stream)
-            for i in partial:
-                allreduce(bufs[i], k.tensors[i].shard_kind)
+            if partial and comm is not None:
+                comm.launch_sharded(k, bufs, stream)  # kernel + NCCL all-reduce of the partials, one stream
+            else:
+                k.launch(bufs, stream)
 
         class _K:  # adapter so that time_launches includes the exchange step
             launch = staticmethod(step_launch)
@@ -280,6 +281,7 @@ def gpu_arm(args):
         raise SystemExit(f"WORLD_SIZE={world} but --gpus {args.gpus}")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    comm = None
     if world > 1:
         # NCCL may print its version banner on stdout when the communicator is created: keep stdout for the one
         # JSON line by pointing fd 1 at stderr until the first collective has run
@@ -291,6 +293,9 @@ def gpu_arm(args):
             warm = torch.zeros(1, device=device)
             dist.all_reduce(warm)
             torch.cuda.synchronize()
+            # the library's own communicator carries the exchange step of the sharded reductions
+            from akg_b200.sharding import Communicator
+            comm = Communicator.from_process_group(device=local)
         finally:
             sys.stdout.flush()
             os.dup2(saved_stdout, 1)
@@ -300,12 +305,6 @@ def gpu_arm(args):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-
-    def allreduce(t, kind):
-        if world == 1:
-            return
-        op = {2: dist.ReduceOp.SUM, 3: dist.ReduceOp.MAX, 4: dist.ReduceOp.MIN, 5: dist.ReduceOp.PRODUCT}[kind]
-        dist.all_reduce(t, op=op)
 
     hbm_peak, tf_peak, peak_src = measured_peaks()
     desc = descs.gelu_chain([64 * world, 512, 4096])
@@ -365,7 +364,7 @@ def gpu_arm(args):
         line["cpu_baseline"] = cpu_baseline_sample()
     if not args.no_classes:
         line["classes"] = run_classes(rank, world, device, max(3, min(args.steps, 10)), max(3, min(args.warmup, 3)),
-                                      hbm_peak, tf_peak, barrier, allreduce)
+                                      hbm_peak, tf_peak, barrier, comm)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

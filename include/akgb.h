@@ -153,6 +153,28 @@ akgb_status akgb_kernel_meta(const akgb_kernel* k, char* buf, size_t cap, size_t
  * (AKG_DUMP_IR, python/akg_mlir/mlir_driver.py:711-721). */
 akgb_status akgb_dump_jit_source(const akgb_kernel* k, int32_t vectorised, char* buf, size_t cap, size_t* needed);
 
+/* ---- multi-GPU: the exchange step of a sharded kernel --------------------------------------------------------
+ * A kernel compiled with akgb_options.shard_world > 1 computes on its rank's slice of the leading axis; outputs whose
+ * shard_kind is AKGB_PARTIAL_* hold per-rank partials that one all-reduce completes.  The reference runs a fused
+ * operator on one device only (python/akg_mlir/utils/code_template.py:181); these entry points have no counterpart
+ * there.  NCCL is loaded at run time (the copy already in the process, else the system's libnccl.so.2). */
+typedef struct akgb_comm akgb_comm;
+#define AKGB_COMM_ID_BYTES 128
+
+/* Rank 0 creates the rendezvous id and hands its AKGB_COMM_ID_BYTES bytes to the other ranks by any means. */
+akgb_status akgb_comm_unique_id(void* id, size_t cap);
+/* Collective over all `world` ranks (one process per GPU); `device` < 0 keeps the current device. */
+akgb_status akgb_comm_create(const void* id, int32_t rank, int32_t world, int32_t device, akgb_comm** out);
+/* Uses a communicator the caller already has (an ncclComm_t); it is not destroyed by akgb_comm_destroy. */
+akgb_status akgb_comm_wrap(void* nccl_comm, int32_t rank, int32_t world, akgb_comm** out);
+void akgb_comm_destroy(akgb_comm* c);
+/* All-reduces, in place and on `stream`, every tensor of `tensors` (inputs then outputs, device pointers) whose
+ * shard_kind is a partial; one NCCL group for all of them.  No-op for kernels without partial outputs. */
+akgb_status akgb_allreduce_partials(const akgb_kernel* k, akgb_comm* c, void* const* tensors, void* stream);
+/* akgb_launch followed by akgb_allreduce_partials on the same stream. */
+akgb_status akgb_launch_sharded(akgb_kernel* k, akgb_comm* c, void* const* tensors, void* workspace,
+                                size_t workspace_bytes, void* stream);
+
 /* Directory of the on-disk cache of run-time compiled kernels.  The reference keeps its compiled kernels
  * (<kernel>.ptx / .json) under KERNEL_META_DIR and reuses them by name (python/akg_mlir/mlir_driver.py:47-53,
  * 337-374); here every generated elementwise kernel is stored as

@@ -1,0 +1,47 @@
+"""Worker of tests/test_gpu_comm.py: one process per GPU (launched by torch.distributed.run).  Every rank reduces its
+slice of a [rows, cols] tensor with a sharded kernel, the library's communicator all-reduces the partials, and rank 0
+checks the result against the whole-tensor reduction."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from akg_b200 import FusedKernel, descs  # noqa: E402
+from akg_b200.sharding import Communicator  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    comm = Communicator.from_process_group(device=local)
+    rows, cols = 512 * world, 1000
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(rows, cols, generator=g)  # the same on every rank
+    mine = x[rank * (rows // world):(rank + 1) * (rows // world)].contiguous().cuda()
+    ok = True
+    for build, ref in ((descs.reduce_sum_axis0, lambda t: t.double().sum(0)),
+                       (descs.reduce_max_all, lambda t: t.max().reshape(1))):
+        k = FusedKernel(build(rows, cols), device=local, shard_rank=rank, shard_world=world)
+        assert any(t.shard_kind >= 2 for t in k.outputs)
+        out = torch.empty(k.outputs[0].shape, dtype=torch.float32, device="cuda")
+        for _ in range(2):
+            comm.launch_sharded(k, [mine, out])
+        torch.cuda.synchronize()
+        want = ref(x)
+        got = out.cpu().double().reshape(want.shape)
+        ok = ok and bool(torch.allclose(got, want.double(), rtol=1e-5, atol=1e-5 * float(x.abs().sum(0).max())))
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    comm.close()
+    dist.destroy_process_group()
+    if rank == 0:
+        print("COMM_OK" if int(flag.item()) == 1 else "COMM_MISMATCH", flush=True)
+    sys.exit(0 if int(flag.item()) == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()
