@@ -748,7 +748,93 @@ struct Builder {
     plan.steps.push_back(std::move(st));
   }
 
-  void add_matmul(const Node& n) {
+  // Epilogues the matmul kernels apply to their accumulators: bias[N] added in float32, max(., 0), conversion to the
+  // operand type.  Found before planning, so that the ops they replace (and a Cast that only widens the bias) are
+  // skipped wherever they stand in the op list.
+  struct Epilogue {
+    int bias = -1;  // value id of the bias as it lies in memory
+    int relu = 0;
+    int out = -1;   // value the kernel writes instead of the MatMul's own result
+  };
+  std::map<int, Epilogue> epilogue;  // MatMul node index -> epilogue
+  std::set<int> eaten;               // node indices folded into a matmul launch
+
+  bool sole_user(int vid, int* user) const {
+    const Value& v = g.v(vid);
+    if (v.output_index >= 0 || v.users.size() != 1) return false;
+    for (auto& kv : alias)
+      if (kv.second == vid) return false;
+    *user = v.users[0];
+    return true;
+  }
+
+  void plan_matmul_epilogues() {
+    for (size_t i = 0; i < g.nodes.size(); ++i) {
+      const Node& n = g.nodes[i];
+      if (n.kind != OpK::MatMul || n.transpose_a) continue;
+      const Value& a = g.v(n.in[0]);
+      if (g.v(n.out).dt != DT::F32 || a.shape.size() != 2) continue;
+      const DT in_dt = a.dt;
+      const int64_t N = g.v(n.out).shape.back();
+      Epilogue e;
+      std::vector<int> taken;
+      int cur = n.out, u;
+      if (sole_user(cur, &u) && g.nodes[u].kind == OpK::Add) {
+        const Node& add = g.nodes[u];
+        const int other = add.in[0] == cur ? add.in[1] : add.in[0];
+        const Value& ov = g.v(other);
+        int src = -1, cast_node = -1;
+        if (ov.input_index >= 0 && ov.dt == DT::F32) {
+          src = other;
+        } else if (ov.producer >= 0 && g.nodes[ov.producer].kind == OpK::Cast && ov.dt == DT::F32 &&
+                   ov.users.size() == 1 && ov.output_index < 0) {
+          const int s0 = g.nodes[ov.producer].in[0];
+          if (g.v(s0).input_index >= 0 && g.v(s0).dt == in_dt && in_dt != DT::F32) {
+            src = s0;
+            cast_node = ov.producer;
+          }
+        }
+        if (src >= 0 && add.in[0] != add.in[1] && ov.numel() == N && ov.shape.back() == N &&
+            g.v(add.out).shape == g.v(n.out).shape) {
+          e.bias = src;
+          taken.push_back(u);
+          if (cast_node >= 0) taken.push_back(cast_node);
+          cur = add.out;
+        }
+      }
+      if (sole_user(cur, &u) && g.nodes[u].kind == OpK::Maximum) {
+        const Node& mx = g.nodes[u];
+        const int other = mx.in[0] == cur ? mx.in[1] : mx.in[0];
+        const Value& ov = g.v(other);
+        if (ov.is_const && ov.cval.size() == 1 && ov.cval[0] == 0.0 && mx.in[0] != mx.in[1]) {
+          e.relu = 1;
+          taken.push_back(u);
+          cur = mx.out;
+        }
+      }
+      if (in_dt != DT::F32 && sole_user(cur, &u) && g.nodes[u].kind == OpK::Cast && g.v(g.nodes[u].out).dt == in_dt) {
+        taken.push_back(u);
+        cur = g.nodes[u].out;
+        // max(., 0) after the conversion equals the conversion after max(., 0): rounding is monotonic and keeps 0
+        if (!e.relu && sole_user(cur, &u) && g.nodes[u].kind == OpK::Maximum) {
+          const Node& mx = g.nodes[u];
+          const int other = mx.in[0] == cur ? mx.in[1] : mx.in[0];
+          const Value& ov = g.v(other);
+          if (ov.is_const && ov.cval.size() == 1 && ov.cval[0] == 0.0 && mx.in[0] != mx.in[1]) {
+            e.relu = 1;
+            taken.push_back(u);
+            cur = mx.out;
+          }
+        }
+      }
+      if (taken.empty()) continue;
+      e.out = cur;
+      epilogue[(int)i] = e;
+      eaten.insert(taken.begin(), taken.end());
+    }
+  }
+
+  void add_matmul(const Node& n, int node_index) {
     if (n.kind == OpK::BatchMatMul) {
       add_batch_matmul(n);
       return;
@@ -756,7 +842,9 @@ struct Builder {
     if (n.transpose_a) throw Unsupported("MatMul with transpose_a is rejected (as by the reference lowering)");
     const Value& a = g.v(n.in[0]);
     const Value& b = g.v(n.in[1]);
-    const Value& o = g.v(n.out);
+    auto ep = epilogue.find(node_index);
+    const int out_vid = ep != epilogue.end() ? ep->second.out : n.out;
+    const Value& o = g.v(out_vid);
     if ((a.dt != DT::BF16 && a.dt != DT::F16 && a.dt != DT::F32) || b.dt != a.dt || a.shape.size() != 2 ||
         b.shape.size() != 2)
       throw Unsupported("only 2-D bfloat16 / float16 / float32 MatMul is placed");
@@ -769,6 +857,13 @@ struct Builder {
     p.out_dt = (int)o.dt;
     p.in_dt = (int)a.dt;
     p.bias_dt = (int)DT::F32;
+    if (ep != epilogue.end()) {
+      p.relu = ep->second.relu;
+      if (ep->second.bias >= 0) {
+        p.has_bias = 1;
+        p.bias_dt = (int)g.v(ep->second.bias).dt;
+      }
+    }
     const char* why = nullptr;
     if (a.dt != DT::F32 && !matmul_bf16_supported(p, &why))
       throw Unsupported(std::string("matmul shape not placed: ") + why);
@@ -777,7 +872,8 @@ struct Builder {
     st.kernel_name = a.dt == DT::F32 ? "sgemm_f32" : "matmul_bf16_tcgen05";
     st.a = buffer(n.in[0]);
     st.b = buffer(n.in[1]);
-    st.out = buffer(n.out);
+    if (p.has_bias) st.c = buffer(ep->second.bias);
+    st.out = buffer(out_vid);
     st.mm = p;
     plan.flops += 2 * p.M * p.N * p.K;
     plan.steps.push_back(std::move(st));
@@ -855,8 +951,10 @@ struct Builder {
 
   Plan run() {
     plan_reshapes();
+    plan_matmul_epilogues();
     for (size_t i = 0; i < g.nodes.size(); ++i) {
       const Node& n = g.nodes[i];
+      if (eaten.count((int)i)) continue;  // runs inside a matmul launch
       if (n.kind == OpK::Reshape && !reshape_copy.count((int)i)) continue;  // a view
       const bool view_copy = n.kind == OpK::Tile || n.kind == OpK::Slice || n.kind == OpK::StridedSlice;
       if (view_copy && produced_in_group(n.in[0])) flush_group();  // the source is read from memory
@@ -882,7 +980,7 @@ struct Builder {
       flush_group();
       if (opk_is_reduce(n.kind)) add_reduce(n);
       else if (n.kind == OpK::Transpose) add_transpose(n);
-      else if (n.kind == OpK::MatMul || n.kind == OpK::BatchMatMul) add_matmul(n);
+      else if (n.kind == OpK::MatMul || n.kind == OpK::BatchMatMul) add_matmul(n, (int)i);
       else if (n.kind == OpK::Gather) add_gather(n);
       else if (n.kind == OpK::ArgMax) add_argmax(n);
       else if (n.kind == OpK::Pad) add_pad(n);

@@ -193,19 +193,42 @@ def _mean(L, node, x, dims=None, keepdim=False, **kw):
     return L.emit("RealDiv", [s, L.b.const(float(count), dt)], node)
 
 
+def _untransposed(L: _Lower, b):
+    """If `b` is the transpose of its last two dims inside this cluster, the tensor it was transposed from (the MatMul
+    then reads it with transpose_b instead of materialising the transpose)."""
+    for op in L.b.ops:
+        if op["output_desc"][0]["tensor_name"] != b["tensor_name"] or op["name"] != "Transpose":
+            continue
+        perm = next(a["value"] for a in op["attr"] if a["name"] == "perm")
+        r = len(perm)
+        if r >= 2 and perm == list(range(r - 2)) + [r - 1, r - 2]:
+            return op["input_desc"][0][0]
+    return None
+
+
+def _matmul(L, node, a, b, name, shape=None, dtype=None):
+    src = _untransposed(L, b)
+    attr = [_attr("transpose_a", "bool", False), _attr("transpose_b", "bool", src is not None)]
+    return L.emit(name, [a, src if src is not None else b], node, attr, shape=shape, dtype=dtype)
+
+
 def _mm(L, node, a, b):
-    return L.emit("MatMul", [a, b], node, [_attr("transpose_a", "bool", False), _attr("transpose_b", "bool", False)])
+    return _matmul(L, node, a, b, "MatMul")
 
 
 def _bmm(L, node, a, b):
-    return L.emit("BatchMatMul", [a, b], node,
-                  [_attr("transpose_a", "bool", False), _attr("transpose_b", "bool", False)])
+    return _matmul(L, node, a, b, "BatchMatMul")
 
 
 def _addmm(L, node, bias, a, b, beta=1, alpha=1):
-    if beta != 1 or alpha != 1:
-        raise NotImplementedError("addmm with beta/alpha other than 1")
-    return L.emit("Add", [_mm(L, node, a, b), bias], node)
+    dt = L.dtype(node)
+    if dt == "float32":
+        return L.emit("Add", [_mm(L, node, a, b), bias], node)
+    # half types: accumulate and add the bias in float32, round once (what the library GEMM epilogues do)
+    f = "float32"
+    c = _matmul(L, node, a, b, "MatMul", dtype=f)
+    c = L.emit("Add", [c, L.cast_to(bias, f)], node, dtype=f)
+    return L.emit("Cast", [c], node, [_attr("dst_type", "str", dt)])
 
 
 def _cat(L, node, tensors, dim=0):
@@ -469,6 +492,18 @@ def lower_cluster(cluster: Sequence[fx.Node], index: int) -> FusedSubgraph:
             t = L.b.emit("Reshape", [t], t["shape"], t["data_type"], [_attr("shape", "listInt", list(t["shape"]))])
         seen.add(t["tensor_name"])
         L.b.output(t)
+    # drop ops nothing reads any more (a transpose folded into its MatMul) and the inputs only they read
+    live = {o["tensor_name"] for o in L.b.outputs}
+    kept = []
+    for op in reversed(L.b.ops):
+        if any(o["tensor_name"] in live for o in op["output_desc"]):
+            kept.append(op)
+            for group in op["input_desc"]:
+                live.update(t["tensor_name"] for t in group)
+    L.b.ops = kept[::-1]
+    keep_in = [i for i, t in enumerate(L.b.inputs) if t["tensor_name"] in live]
+    L.b.inputs = [L.b.inputs[i] for i in keep_in]
+    inputs = [inputs[i] for i in keep_in]
     return FusedSubgraph(L.b.op, L.b.build(), inputs, outputs)
 
 

@@ -574,3 +574,31 @@ print(compiled, from_disk, out[0].view(np.uint32).sum(dtype=np.uint64))
     files = [f for f in os.listdir(tmp_path) if f.startswith("akgb_ew_") and f.endswith(".sm_100a.cubin")]
     assert len(files) == 1
 
+
+
+def test_matmul_epilogue_is_folded_inside_a_larger_region(lib):
+    """Two matmuls in one region: bias + ReLU + cast after the first run in its launch, the rest as planned."""
+    rng = np.random.default_rng(95)
+    m, k_, n, n2 = 256, 128, 192, 64
+    mm = [_attr("transpose_a", "bool", False), _attr("transpose_b", "bool", False)]
+    b = _Builder("Fused_MatMul_Add_Max_Cast_MatMul_ReduceSum_95")
+    h, f = "bfloat16", "float32"
+    a = b.input("a", [m, k_], h)
+    w1 = b.input("w1", [k_, n], h)
+    bias = b.input("bias", [n], h)
+    w2 = b.input("w2", [n, n2], h)
+    bf = b.emit("Cast", [bias], [n], f, [_attr("dst_type", "str", f)])
+    c = b.emit("MatMul", [a, w1], [m, n], f, mm)
+    c = b.emit("Add", [c, bf], [m, n], f)
+    c = b.emit("Maximum", [c, b.const(0.0, f)], [m, n], f)
+    hcast = b.emit("Cast", [c], [m, n], h, [_attr("dst_type", "str", h)])
+    o = b.emit("MatMul", [hcast, w2], [m, n2], f, mm)
+    b.output(o)
+    b.output(b.emit("ReduceSum", [o], [n2], f, _reduce_attr([0], False)))
+    d = b.build()
+    ins = [(rng.standard_normal(s) * 0.1).astype(BF16) for s in ((m, k_), (k_, n), (n,), (n, n2))]
+    got, kern = run(d, ins)
+    want = O.evaluate(d, ins)
+    assert kern.launch_count == 2 + FusedKernel(descs.reduce_sum_axis0(m, n2)).launch_count  # no elementwise launch
+    for g_, w_ in zip(got, want):
+        np.testing.assert_allclose(g_, w_, rtol=2e-2, atol=2e-2 * float(np.abs(w_).max()))

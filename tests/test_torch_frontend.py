@@ -141,6 +141,27 @@ def test_fused_module_on_the_device(name):
 
 
 @pytest.mark.gpu
+def test_bfloat16_linear_layers_on_the_device():
+    """F.linear in bfloat16: the transposes fold into the matmuls, bias and ReLU into their launches."""
+    g = torch.Generator().manual_seed(4)
+
+    def net(x, w1, b1, w2, b2):
+        h = torch.relu(torch.nn.functional.linear(x, w1, b1))
+        return torch.nn.functional.linear(h, w2, b2)
+
+    ins = [(torch.randn(s, generator=g) * 0.1).bfloat16().cuda() for s in ((256, 128), (192, 128), (192,), (64, 192), (64,))]
+    fused = TF.fuse_and_optimize(net, ins)
+    assert len(fused.subgraphs) == 1
+    names = [o["name"] for o in fused.subgraphs[0].desc["op_desc"]]
+    assert "Transpose" not in names and names.count("MatMul") == 2
+    got, want = fused(*ins), net(*ins)
+    assert got.dtype == torch.bfloat16
+    torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+    from akg_b200.driver import FusedKernel
+    assert FusedKernel(fused.subgraphs[0].desc_json).launch_count == 2
+
+
+@pytest.mark.gpu
 def test_fused_half_precision_chain_on_the_device():
     g = torch.Generator().manual_seed(3)
     ins = [torch.randn(8, 256, 512, generator=g).half().cuda(), (torch.randn(512, generator=g) * 0.02).half().cuda(),
