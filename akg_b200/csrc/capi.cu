@@ -192,9 +192,7 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
                          &st.dims);
           break;
         }
-        for (int64_t bi = 0; bi < st.mm_batch && e == cudaSuccess; ++bi)
-          e = matmul_bf16(st.mm, (const char*)a + bi * st.mm_stride_a, (const char*)b + bi * st.mm_stride_b, c,
-                          (char*)o + bi * st.mm_stride_o, ds.err_word, k->sm_count, s, &st.dims);
+        e = matmul_bf16(st.mm, a, b, c, o, st.mm_batch, st.mm_stride_b != 0, ds.err_word, k->sm_count, s, &st.dims);
         break;
     }
     if (e != cudaSuccess) return cuda_fail(e, st.kernel_name.c_str());
@@ -219,7 +217,7 @@ int launches_of(const akgb_kernel* k) {
         n += (st.gelu.n % 8) ? 2 : 1;
         break;
       case StepK::Matmul:
-        n += st.mm.in_dt == (int)DT::F32 ? 1 : (int)st.mm_batch;
+        n += 1;
         break;
       default:
         n += 1;

@@ -56,6 +56,9 @@ struct MatmulDev {
   int M, N, K;
   int transpose_b, has_bias, bias_dt, relu, out_dt;
   int in_f16;  // operands are float16 instead of bfloat16
+  int batch;             // independent products; tensor maps are 3-D with the batch outermost
+  int b_batched;         // 0: every batch entry multiplies by the same B
+  long long out_stride;  // elements between the outputs of consecutive batch entries
   const void* bias;
   void* out;
   uint32_t* err;
@@ -119,7 +122,7 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int*
 
 // Reads one 128x256 accumulator (this warp's 32 lanes) in chunks of 32 columns, applies bias / ReLU / cast in
 // that order and stores the row segment.
-__device__ __forceinline__ void epilogue_tile(const MatmulDev& p, uint32_t taddr, int row, int n0) {
+__device__ __forceinline__ void epilogue_tile(const MatmulDev& p, uint32_t taddr, int row, int n0, size_t out_off) {
 #pragma unroll 1
   for (int c = 0; c < BN / 32; ++c) {
     uint32_t r[32];
@@ -171,7 +174,7 @@ __device__ __forceinline__ void epilogue_tile(const MatmulDev& p, uint32_t taddr
     }
     if (row < p.M) {
       if (p.out_dt != kF32) {
-        uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + (size_t)row * p.N + col0;
+        uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + out_off + (size_t)row * p.N + col0;
         if (col0 + 32 <= p.N) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(o + q * 8) = pack8(v + q * 8, p.out_dt);
@@ -182,7 +185,7 @@ __device__ __forceinline__ void epilogue_tile(const MatmulDev& p, uint32_t taddr
               o[j] = p.out_dt == kBF16 ? (uint16_t)f32_to_bf16_bits(v[j]) : __half_as_ushort(__float2half_rn(v[j]));
         }
       } else {
-        float* o = reinterpret_cast<float*>(p.out) + (size_t)row * p.N + col0;
+        float* o = reinterpret_cast<float*>(p.out) + out_off + (size_t)row * p.N + col0;
         if (col0 + 32 <= p.N) {
 #pragma unroll
           for (int q = 0; q < 8; ++q)
@@ -233,7 +236,8 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
   const uint32_t tmem_base = bars->tmem_base;
 
   const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n;
+  const int per_batch = num_m * num_n;
+  const int num_tiles = per_batch * p.batch;
   const int num_k = (p.K + BK - 1) / BK;
 
   if (warp == 0) {
@@ -245,8 +249,9 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
       int issued = 0;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int mt, nt;
-        tile_coords(tile, num_m, num_n, &mt, &nt);
-        const int m0 = mt * BM, n0 = nt * BN;
+        const int bt = tile / per_batch;
+        tile_coords(tile - bt * per_batch, num_m, num_n, &mt, &nt);
+        const int m0 = mt * BM, n0 = nt * BN, bz = p.b_batched ? bt : 0;
         for (int kb = 0; kb < num_k; ++kb) {
           if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag)) {
             ok = false;
@@ -255,12 +260,13 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
           const uint32_t full = smem_u32(&bars->full[stage]);
           const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_BYTES;
           mbar_expect_tx(full, STAGE_BYTES);
-          tma_load_2d(sa, &tmA, full, kb * BK, m0);
+          tma_load_3d(sa, &tmA, full, kb * BK, m0, bt);
           if (p.transpose_b) {
-            tma_load_2d(sb, &tmB, full, kb * BK, n0);
+            tma_load_3d(sb, &tmB, full, kb * BK, n0, bz);
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / B_BOX_N; ++j) tma_load_2d(sb + j * B_BOX_BYTES, &tmB, full, n0 + j * B_BOX_N, kb * BK);
+            for (int j = 0; j < BN / B_BOX_N; ++j)
+              tma_load_3d(sb + j * B_BOX_BYTES, &tmB, full, n0 + j * B_BOX_N, kb * BK, bz);
           }
           ++issued;
           if (++stage == STAGES) {
@@ -342,7 +348,8 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int mt, nt;
-      tile_coords(tile, num_m, num_n, &mt, &nt);
+      const int bt = tile / per_batch;
+      tile_coords(tile - bt * per_batch, num_m, num_n, &mt, &nt);
       const int row = mt * BM + quarter * 32 + lane;
       const int n0 = nt * BN;
       if (!mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_phase, abort_flag)) {
@@ -351,7 +358,7 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * BN;
-      epilogue_tile(p, taddr, row, n0);
+      epilogue_tile(p, taddr, row, n0, (size_t)bt * (size_t)p.out_stride);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[acc]));
@@ -402,10 +409,11 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y) {
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y,
+                                                 int z) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(leader_bar), "r"(x), "r"(y)
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(leader_bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
 __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
@@ -474,7 +482,8 @@ matmul_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const _
   const uint32_t tmem_base = bars->tmem_base;
 
   const int num_m = (p.M + 2 * BM - 1) / (2 * BM), num_n = (p.N + BN - 1) / BN;  // 256 x 256 tiles
-  const int num_tiles = num_m * num_n;
+  const int per_batch = num_m * num_n;
+  const int num_tiles = per_batch * p.batch;
   const int num_k = (p.K + BK - 1) / BK;
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
 
@@ -486,8 +495,9 @@ matmul_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const _
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         int mt, nt;
-        tile_coords(tile, num_m, num_n, &mt, &nt);
-        const int m0 = mt * 2 * BM + (int)rank * BM, n0 = nt * BN + (int)rank * (BN / 2);
+        const int bt = tile / per_batch;
+        tile_coords(tile - bt * per_batch, num_m, num_n, &mt, &nt);
+        const int m0 = mt * 2 * BM + (int)rank * BM, n0 = nt * BN + (int)rank * (BN / 2), bz = p.b_batched ? bt : 0;
         for (int kb = 0; kb < num_k; ++kb) {
           if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, abort_flag)) {
             ok = false;
@@ -496,13 +506,13 @@ matmul_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const _
           const uint32_t full_leader = smem_u32(&bars->full[stage]) & kPeerMask;
           const uint32_t sa = base + stage * STAGE2_BYTES, sb = sa + A_BYTES;
           if (leader) mbar_expect_tx(smem_u32(&bars->full[stage]), 2 * STAGE2_BYTES);
-          tma_load_2d_pair(sa, &tmA, full_leader, kb * BK, m0);
+          tma_load_3d_pair(sa, &tmA, full_leader, kb * BK, m0, bt);
           if (p.transpose_b) {
-            tma_load_2d_pair(sb, &tmB, full_leader, kb * BK, n0);
+            tma_load_3d_pair(sb, &tmB, full_leader, kb * BK, n0, bz);
           } else {
 #pragma unroll
             for (int j = 0; j < (BN / 2) / B_BOX_N; ++j)
-              tma_load_2d_pair(sb + j * B_BOX_BYTES, &tmB, full_leader, n0 + j * B_BOX_N, kb * BK);
+              tma_load_3d_pair(sb + j * B_BOX_BYTES, &tmB, full_leader, n0 + j * B_BOX_N, kb * BK, bz);
           }
           if (++stage == STAGES2) {
             stage = 0;
@@ -571,7 +581,8 @@ matmul_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const _
     bool ok = true;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
       int mt, nt;
-      tile_coords(tile, num_m, num_n, &mt, &nt);
+      const int bt = tile / per_batch;
+      tile_coords(tile - bt * per_batch, num_m, num_n, &mt, &nt);
       const int row = mt * 2 * BM + (int)rank * BM + quarter * 32 + lane;
       const int n0 = nt * BN;
       if (!mbar_wait(smem_u32(&bars->tmem_full[acc]), acc_phase, abort_flag)) {
@@ -580,7 +591,7 @@ matmul_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const _
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * BN;
-      epilogue_tile(p, taddr, row, n0);
+      epilogue_tile(p, taddr, row, n0, (size_t)bt * (size_t)p.out_stride);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(smem_u32(&bars->tmem_empty[acc]), 0);
@@ -619,16 +630,17 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 2-D tensor map over 16-bit elements: `inner` contiguous elements per row, `outer` rows.
-bool encode_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_inner,
-               uint32_t box_outer, bool f16 = false) {
+// 3-D tensor map over 16-bit elements: `batch` matrices of `outer` rows of `inner` contiguous elements, one matrix
+// after the other; a box never spans two matrices, so rows beyond `outer` read as zeros in every batch entry.
+bool encode_3d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t batch, uint32_t box_inner,
+               uint32_t box_outer, bool f16) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
-  cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {inner * 2};
-  cuuint32_t box[2] = {box_inner, box_outer};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+  cuuint64_t dims[3] = {inner, outer, batch};
+  cuuint64_t strides[2] = {inner * 2, inner * outer * 2};
+  cuuint32_t box[3] = {box_inner, box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
@@ -647,15 +659,18 @@ bool matmul_bf16_supported(const MatmulParams& p, const char** why) {
 }
 
 cudaError_t matmul_bf16(const MatmulParams& p, const void* A, const void* B, const void* bias, void* out,
-                        uint32_t* err_word, int sm_count, cudaStream_t s, LaunchDims* dims) {
+                        int64_t batch, bool b_batched, uint32_t* err_word, int sm_count, cudaStream_t s,
+                        LaunchDims* dims) {
+  if (batch < 1 || batch > (1 << 20)) return cudaErrorInvalidValue;
+  const uint64_t bb = b_batched ? (uint64_t)batch : 1;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(out) |
        reinterpret_cast<uintptr_t>(bias)) & 15)
     return cudaErrorMisalignedAddress;
   CUtensorMap tmA, tmB;
   const bool f16 = p.in_dt == kF16;
-  if (!encode_2d(&tmA, A, (uint64_t)p.K, (uint64_t)p.M, BK, BM, f16)) return cudaErrorInvalidValue;
-  const bool okb = p.transpose_b ? encode_2d(&tmB, B, (uint64_t)p.K, (uint64_t)p.N, BK, BN, f16)
-                                 : encode_2d(&tmB, B, (uint64_t)p.N, (uint64_t)p.K, B_BOX_N, BK, f16);
+  if (!encode_3d(&tmA, A, (uint64_t)p.K, (uint64_t)p.M, (uint64_t)batch, BK, BM, f16)) return cudaErrorInvalidValue;
+  const bool okb = p.transpose_b ? encode_3d(&tmB, B, (uint64_t)p.K, (uint64_t)p.N, bb, BK, BN, f16)
+                                 : encode_3d(&tmB, B, (uint64_t)p.N, (uint64_t)p.K, bb, B_BOX_N, BK, f16);
   if (!okb) return cudaErrorInvalidValue;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
@@ -674,6 +689,9 @@ cudaError_t matmul_bf16(const MatmulParams& p, const void* A, const void* B, con
   d.relu = p.relu;
   d.out_dt = p.out_dt;
   d.in_f16 = f16;
+  d.batch = (int)batch;
+  d.b_batched = b_batched ? 1 : 0;
+  d.out_stride = (long long)p.M * p.N;
   d.bias = bias;
   d.out = out;
   d.err = err_word;
@@ -691,8 +709,8 @@ cudaError_t matmul_bf16(const MatmulParams& p, const void* A, const void* B, con
     if (attr_err2 != cudaSuccess) return attr_err2;
     // the pair kernel's B tile per CTA is 128 columns: re-encode B with the narrower box for the K-major case
     CUtensorMap tmB2 = tmB;
-    if (p.transpose_b && !encode_2d(&tmB2, B, (uint64_t)p.K, (uint64_t)p.N, BK, BN / 2, f16)) return cudaErrorInvalidValue;
-    const int64_t tiles2 = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN);
+    if (p.transpose_b && !encode_3d(&tmB2, B, (uint64_t)p.K, (uint64_t)p.N, bb, BK, BN / 2, f16)) return cudaErrorInvalidValue;
+    const int64_t tiles2 = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN) * batch;
     const int grid2 = 2 * (int)std::min<int64_t>(tiles2, sm_count / 2);
     if (dims) {
       dims->grid[0] = grid2;
@@ -702,7 +720,7 @@ cudaError_t matmul_bf16(const MatmulParams& p, const void* A, const void* B, con
     matmul_bf16_tcgen05_pair_kernel<<<grid2, THREADS, SMEM2_BYTES, s>>>(tmA, tmB2, d);
     return cudaGetLastError();
   }
-  const int64_t tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int64_t tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * batch;
   const int grid = (int)std::min<int64_t>(tiles, sm_count);
   if (dims) {
     dims->grid[0] = grid;

@@ -117,9 +117,11 @@ struct MatmulParams {
   int out_dt = 0;       // DT code of the output: the operand type (BF16 / F16) or F32
   int in_dt = 8;        // DT code of A and B: BF16 (8) or F16 (5) on the tensor cores, F32 (6) on the CUDA cores
 };
-// Encodes the TMA descriptors for (A, B) and launches the tcgen05 kernel.
+// Encodes the TMA descriptors for (A, B) and launches the tcgen05 kernel: `batch` independent products in one launch
+// (A and the output hold one matrix after the other; B too when b_batched, else every entry uses the same B).
 cudaError_t matmul_bf16(const MatmulParams& p, const void* A, const void* B, const void* bias, void* out,
-                        uint32_t* err_word, int sm_count, cudaStream_t s, LaunchDims* dims);
+                        int64_t batch, bool b_batched, uint32_t* err_word, int sm_count, cudaStream_t s,
+                        LaunchDims* dims);
 bool matmul_bf16_supported(const MatmulParams& p, const char** why);
 // float32 operands and result on the CUDA cores (in_dt = F32); `batch` entries `stride_*` elements apart, one launch
 cudaError_t matmul_f32(const MatmulParams& p, const void* A, const void* B, const void* bias, void* out,

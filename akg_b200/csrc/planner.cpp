@@ -903,8 +903,8 @@ struct Builder {
     }
   }
 
-  // BatchMatMul: the 2-D kernel once per batch entry (leading dims of both operands must agree, or the right
-  // operand may be 2-D and shared)
+  // BatchMatMul: one launch, the batch entry is a tile coordinate (leading dims of both operands must agree, or the
+  // right operand may be 2-D and shared)
   void add_batch_matmul(const Node& n) {
     if (n.transpose_a) throw Unsupported("BatchMatMul with transpose_a is rejected (as by the reference lowering)");
     const Value& a = g.v(n.in[0]);
@@ -920,7 +920,7 @@ struct Builder {
     int64_t bbatch = 1;
     for (size_t i = 0; i + 2 < rb; ++i) bbatch *= b.shape[i];
     if (bbatch != batch && bbatch != 1) throw Unsupported("BatchMatMul operands with different batch extents");
-    if (batch > 4096) throw Unsupported("BatchMatMul with more than 4096 batch entries");
+    if (batch > (1 << 20)) throw Unsupported("BatchMatMul with more than 2^20 batch entries");
     MatmulParams p;
     p.M = a.shape[ra - 2];
     p.K = a.shape[ra - 1];

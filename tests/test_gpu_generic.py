@@ -312,7 +312,41 @@ def test_batch_matmul(lib):
     got, kern = run(d, ins)
     want = O.evaluate(d, ins)[0]
     np.testing.assert_allclose(got[0], want, rtol=2e-3, atol=1e-3 * float(np.abs(want).max()))
-    assert kern.launch_count == bsz
+    assert kern.launch_count == 1  # the batch is a tile coordinate of one launch
+    # ragged rows (not a multiple of the 128-row tile) in every batch entry, one shared right operand, K-major B
+    rng = np.random.default_rng(24)
+    for shared, tb in ((True, False), (False, True), (True, True)):
+        bsz, m, k_, n = 7, 100, 72, 136
+        b = _Builder("Fused_BatchMatMul_24")
+        a = b.input("a", [bsz, m, k_], h)
+        wshape = ([n, k_] if tb else [k_, n]) if shared else ([bsz, n, k_] if tb else [bsz, k_, n])
+        w = b.input("w", wshape, h)
+        c = b.emit("BatchMatMul", [a, w], [bsz, m, n], "float32",
+                   [_attr("transpose_a", "bool", False), _attr("transpose_b", "bool", tb)])
+        b.output(c)
+        d = b.build()
+        av = (rng.standard_normal((bsz, m, k_)) * 0.1).astype(BF16)
+        wv = (rng.standard_normal(wshape) * 0.1).astype(BF16)
+        got, kern = run(d, [av, wv])
+        w64 = wv.astype(np.float64)
+        if tb:
+            w64 = np.swapaxes(w64, -1, -2)
+        want = av.astype(np.float64) @ w64
+        assert kern.launch_count == 1
+        np.testing.assert_allclose(got[0], want, rtol=2e-3, atol=2e-3 * float(np.abs(want).max()))
+    # larger rows: the CTA-pair kernel with a batch coordinate
+    bsz, m, k_, n = 3, 300, 64, 256
+    b = _Builder("Fused_BatchMatMul_25")
+    a = b.input("a", [bsz, m, k_], h)
+    w = b.input("w", [bsz, k_, n], h)
+    b.output(b.emit("BatchMatMul", [a, w], [bsz, m, n], h,
+                    [_attr("transpose_a", "bool", False), _attr("transpose_b", "bool", False)]))
+    d = b.build()
+    av = (rng.standard_normal((bsz, m, k_)) * 0.1).astype(BF16)
+    wv = (rng.standard_normal((bsz, k_, n)) * 0.1).astype(BF16)
+    got, kern = run(d, [av, wv])
+    want = av.astype(np.float64) @ wv.astype(np.float64)
+    np.testing.assert_allclose(got[0].astype(np.float64), want, rtol=1e-2, atol=1e-2 * float(np.abs(want).max()))
 
 
 def test_dynamic_shapes_match_the_static_plan(lib):
