@@ -259,11 +259,41 @@ const char* cmp_op(int op) {
 }
 
 // Emits the op chain for element lane `j` of vector slot `u`.  `ref(reg)` yields the expression of a register.
+// Element index of a strided operand for the linear index `e` of the iteration space: the coordinates of `e` (constant
+// divisors, which the compiler turns into multiply-shift) times the operand's strides, a wrapped coordinate for Tile.
+std::string strided_index(const EwProgram& P, const EwOperand& o, const std::string& e) {
+  std::ostringstream x;
+  x << "(" << o.offset << "LL";
+  int64_t suffix = 1;
+  for (int d = P.rank - 1; d >= 0; --d) {
+    if (o.stride[d] != 0 && P.shape[d] > 1) {
+      std::ostringstream c;
+      c << "(" << e;
+      if (suffix > 1) c << " / " << suffix << "LL";
+      c << ")";
+      std::string coord = c.str();
+      if (d > 0) coord = "(" + coord + " % " + std::to_string(P.shape[d]) + "LL)";
+      if (o.wrap[d] != 0) coord = "(" + coord + " % " + std::to_string(o.wrap[d]) + "LL)";
+      x << " + " << coord << " * " << o.stride[d] << "LL";
+    }
+    suffix *= P.shape[d];
+  }
+  x << ")";
+  return x.str();
+}
+// 8 consecutive elements of the iteration space are 8 consecutive, 16-byte aligned elements of the operand
+bool strided_vec8_ok(const EwProgram& P, const EwOperand& o) {
+  const int last = P.rank - 1;
+  if (last < 0 || P.shape[last] % 8 != 0 || o.stride[last] != 1 || o.offset % 8 != 0) return false;
+  if (o.wrap[last] != 0 && o.wrap[last] % 8 != 0) return false;
+  for (int d = 0; d < last; ++d)
+    if (o.stride[d] % 8 != 0) return false;
+  return true;
+}
+
 bool generate(const EwProgram& P, bool vec, std::string* out) {
-  for (int i = 0; i < P.n_in; ++i)
-    if (P.in[i].kind == EWI_STRIDED) return false;
   for (int i = 0; i < P.n_out; ++i)
-    if (P.out[i].kind != EWI_FULL) return false;
+    if (P.out[i].kind != EWI_FULL && P.out[i].kind != EWI_STRIDED) return false;
   std::ostringstream s;
   s << kPreamble;
   s << "extern \"C\" __global__ void __launch_bounds__(256) akgb_ew_jit(";
@@ -305,12 +335,19 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
       else if (o.kind == EWI_MOD)
         s << "      #pragma unroll\n      for (int j = 0; j < 8; ++j) a" << i << "[u][j] = ld1_" << tag << "(in" << i
           << ", (v * 8 + j) % " << o.mod << "LL);\n";
+      else if (o.kind == EWI_STRIDED && strided_vec8_ok(P, o))
+        s << "      ld8_" << tag << "(in" << i << ", " << strided_index(P, o, "(v * 8)") << ", a" << i << "[u], false);\n";
+      else if (o.kind == EWI_STRIDED)
+        s << "      #pragma unroll\n      for (int j = 0; j < 8; ++j) a" << i << "[u][j] = ld1_" << tag << "(in" << i
+          << ", " << strided_index(P, o, "(v * 8 + j)") << ");\n";
       else  // scalar
         s << "      { const " << (is_float_dt(o.dt) ? "float" : "int") << " t = ld1_" << tag << "(in" << i
           << ", 0);\n        #pragma unroll\n        for (int j = 0; j < 8; ++j) a" << i << "[u][j] = t; }\n";
     } else {
       if (o.kind == EWI_FULL) s << "      a" << i << "[u][0] = ld1_" << tag << "(in" << i << ", v);\n";
       else if (o.kind == EWI_MOD) s << "      a" << i << "[u][0] = ld1_" << tag << "(in" << i << ", v % " << o.mod << "LL);\n";
+      else if (o.kind == EWI_STRIDED)
+        s << "      a" << i << "[u][0] = ld1_" << tag << "(in" << i << ", " << strided_index(P, o, "v") << ");\n";
       else s << "      a" << i << "[u][0] = ld1_" << tag << "(in" << i << ", 0);\n";
     }
   }
@@ -401,8 +438,19 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
     } else {
       src = v.name + "[u]";
     }
-    if (vec) t << "      st8_" << tag << "(out" << i << ", v * 8, " << src << ");\n";
-    else t << "      st1_" << tag << "(out" << i << ", v, " << src << "[0]);\n";
+    if (o.kind == EWI_STRIDED) {
+      if (vec && strided_vec8_ok(P, o))
+        t << "      st8_" << tag << "(out" << i << ", " << strided_index(P, o, "(v * 8)") << ", " << src << ");\n";
+      else if (vec)
+        t << "      #pragma unroll\n      for (int j = 0; j < 8; ++j) st1_" << tag << "(out" << i << ", "
+          << strided_index(P, o, "(v * 8 + j)") << ", " << src << "[j]);\n";
+      else
+        t << "      st1_" << tag << "(out" << i << ", " << strided_index(P, o, "v") << ", " << src << "[0]);\n";
+    } else if (vec) {
+      t << "      st8_" << tag << "(out" << i << ", v * 8, " << src << ");\n";
+    } else {
+      t << "      st1_" << tag << "(out" << i << ", v, " << src << "[0]);\n";
+    }
   }
   t << "    }\n  }\n}\n";
   *out = t.str();
