@@ -121,6 +121,7 @@ void* resolve(const Ref& r, void* const* tensors, void* ws) {
 }
 
 akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws, cudaStream_t s) {
+  if (plan.fallback && plan.use_fallback) return run_plan(k, *plan.fallback, tensors, ws, s);
   DeviceState& ds = g_dev[k->device];
   for (Step& st : plan.steps) {
     cudaError_t e = cudaSuccess;
@@ -157,6 +158,18 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
         e = segment_sum_f32((const float*)a, b, (float*)o, st.ix_n, st.ix_inner, st.ix_segments, st.ix_idx64, s,
                             &st.dims);
         break;
+      case StepK::RowJit: {
+        const void* ins[16];
+        void* outs[16];
+        for (size_t i = 0; i < st.ew_in.size(); ++i) ins[i] = resolve(st.ew_in[i], tensors, ws);
+        for (size_t i = 0; i < st.ew_out.size(); ++i) outs[i] = resolve(st.ew_out[i], tensors, ws);
+        e = row_jit_launch(*st.row, ins, outs, s, &st.dims);
+        if (e == cudaErrorNotSupported && plan.fallback) {  // no run-time compiler here: the separate launches
+          plan.use_fallback = true;
+          return run_plan(k, *plan.fallback, tensors, ws, s);
+        }
+        break;
+      }
       case StepK::Ew: {
         const void* ins[kEwMaxIn];
         void* outs[kEwMaxOut];
@@ -200,9 +213,14 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
   return AKGB_OK;
 }
 
+// the plan launches go through: the generated row kernel, or the separate launches once it has been given up
+const Plan& active_plan(const akgb_kernel* k) {
+  return (k->plan.fallback && k->plan.use_fallback) ? *k->plan.fallback : k->plan;
+}
+
 int launches_of(const akgb_kernel* k) {
   int n = 0;
-  for (const Step& st : k->plan.steps) {
+  for (const Step& st : active_plan(k).steps) {
     switch (st.kind) {
       case StepK::ReduceCol:
         n += (int)st.red_outer * (reduce_col_workspace(st.red_len, st.red_inner, k->sm_count) ? 2 : 1);
@@ -254,7 +272,7 @@ void plan_chunks(akgb_kernel* k) {
         if (!g.v(vid).split0) ok = false;  // every output must be produced chunk by chunk
       }
       if (!ok) return;
-      Plan p = build_plan(g, k->sm_count);
+      Plan p = build_plan(g, k->sm_count, !k->no_jit);
       if (p.workspace_bytes > k->plan.workspace_bytes) return;
       if (cudaStreamCreateWithFlags(&k->s_in, cudaStreamNonBlocking) != cudaSuccess) return;
       if (cudaStreamCreateWithFlags(&k->s_out, cudaStreamNonBlocking) != cudaSuccess) return;
@@ -378,7 +396,7 @@ akgb_status akgb_compile(const char* info_json, size_t len, const akgb_options* 
       k->plan.klass = "dynamic";
     } else {
       infer_sharding(k->graph, rank, world);
-      k->plan = build_plan(k->graph, k->sm_count);
+      k->plan = build_plan(k->graph, k->sm_count, !k->no_jit);
     }
     const Graph& g = k->graph;
     k->n_inputs = (int)g.inputs.size();
@@ -470,7 +488,7 @@ akgb_status bound_plan(akgb_kernel* k, const int64_t* shapes, size_t count, akgb
       }
       std::unique_ptr<akgb_kernel::Bound> b(new akgb_kernel::Bound());
       b->graph = bind_shapes(k->graph, per);
-      b->plan = build_plan(b->graph, k->sm_count);
+      b->plan = build_plan(b->graph, k->sm_count, !k->no_jit);
       it = k->bound.emplace(std::move(key), std::move(b)).first;
     } catch (const JsonError& e) {
       return fail(AKGB_INVALID_ARG, e.what());
@@ -602,9 +620,9 @@ akgb_status akgb_jit_cache_stats(uint64_t* compiled, uint64_t* loaded_from_disk)
 akgb_status akgb_dump_jit_source(const akgb_kernel* k, int32_t vectorised, char* buf, size_t cap, size_t* needed) {
   if (!k) return fail(AKGB_INVALID_ARG, "null argument");
   std::string src;
-  for (const Step& st : k->plan.steps) {
-    if (st.kind != StepK::Ew) continue;
-    src = ew_jit_source(st.ew, vectorised != 0);
+  for (const Step& st : active_plan(k).steps) {
+    if (st.kind == StepK::RowJit) src = row_jit_source(*st.row, vectorised != 0);
+    else if (st.kind == StepK::Ew) src = ew_jit_source(st.ew, vectorised != 0);
     if (!src.empty()) break;
   }
   if (needed) *needed = src.size() + 1;
@@ -619,7 +637,8 @@ akgb_status akgb_kernel_meta(const akgb_kernel* k, char* buf, size_t cap, size_t
   // the keys the reference writes to <kernel>.json (GPUMapping.cpp:645-703,
   // mlir_driver.py:776-815); grid/block are those of the dominant (first) step
   static const Step kNoStep{};
-  const Step& st = k->plan.steps.empty() ? kNoStep : k->plan.steps.front();
+  const Plan& ap = active_plan(k);
+  const Step& st = ap.steps.empty() ? kNoStep : ap.steps.front();
   LaunchDims d = st.dims;
   std::ostringstream o;
   o << "{\"kernelName\": \"" << k->graph.kernel_name << "_kernel\", "

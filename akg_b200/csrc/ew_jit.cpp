@@ -15,6 +15,7 @@
 #include <dlfcn.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <map>
@@ -258,6 +259,47 @@ const char* cmp_op(int op) {
   }
 }
 
+// The expression of one elementwise op in generated code; `ref(value, want_float)` yields an operand's expression.
+template <class Ref>
+std::string instr_expr(int op, int dt, int cls, int src_cls, int a, int b, int c, Ref&& ref) {
+  const bool fl = cls == EWC_FLOAT;
+  const bool sfl = src_cls == EWC_FLOAT;
+  std::string expr;
+  if (op == EW_COPY) {
+    expr = ref(a, fl);
+  } else if (op == EW_CAST) {
+    if (fl) expr = std::string(round_fn(dt)) + "(" + (sfl ? ref(a, true) : "(float)" + ref(a, false)) + ")";
+    else if (cls == EWC_BOOL) expr = sfl ? "(" + ref(a, true) + " != 0.f ? 1 : 0)" : "(" + ref(a, false) + " != 0 ? 1 : 0)";
+    else expr = std::string(wrap_fn(dt)) + "(" + ref(a, false) + ")";
+  } else if (op <= EW_ACOS) {
+    if (fl) expr = std::string(round_fn(dt)) + "(" + float_unary(op, ref(a, true)) + ")";
+    else if (op == EW_ABS) expr = std::string(wrap_fn(dt)) + "(abs(" + ref(a, false) + "))";
+    else if (op == EW_NEG) expr = std::string(wrap_fn(dt)) + "(-" + ref(a, false) + ")";
+    else if (op == EW_SQUARE) expr = std::string(wrap_fn(dt)) + "(" + ref(a, false) + " * " + ref(a, false) + ")";
+    else expr = ref(a, false);
+  } else if (op <= EW_ISNAN) {
+    const std::string x = ref(a, true);
+    expr = op == EW_ISINF ? "(isinf(" + x + ") ? 1 : 0)" : op == EW_ISFINITE ? "(isfinite(" + x + ") ? 1 : 0)"
+                                                                              : "(" + x + " != " + x + " ? 1 : 0)";
+  } else if (op == EW_NOT) {
+    expr = "(" + ref(a, false) + " ? 0 : 1)";
+  } else if (op <= EW_ATAN2) {
+    if (fl) expr = std::string(round_fn(dt)) + "(" + float_binary(op, ref(a, true), ref(b, true)) + ")";
+    else expr = std::string(wrap_fn(dt)) + "(" + int_binary(op, ref(a, false), ref(b, false)) + ")";
+  } else if (op <= EW_LE) {
+    const std::string x = ref(a, sfl), y = ref(b, sfl);
+    if (op == EW_NE) expr = "(!(" + x + " == " + y + ") ? 1 : 0)";
+    else expr = "((" + x + " " + cmp_op(op) + " " + y + ") ? 1 : 0)";
+  } else if (op == EW_AND) {
+    expr = "((" + ref(a, false) + " && " + ref(b, false) + ") ? 1 : 0)";
+  } else if (op == EW_OR) {
+    expr = "((" + ref(a, false) + " || " + ref(b, false) + ") ? 1 : 0)";
+  } else {  // select: a = condition
+    expr = "(" + ref(a, false) + " ? " + ref(b, fl) + " : " + ref(c, fl) + ")";
+  }
+  return expr;
+}
+
 // Emits the op chain for element lane `j` of vector slot `u`.  `ref(reg)` yields the expression of a register.
 // Element index of a strided operand for the linear index `e` of the iteration space: the coordinates of `e` (constant
 // divisors, which the compiler turns into multiply-shift) times the operand's strides, a wrapped coordinate for Tile.
@@ -363,40 +405,8 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
   for (int k = 0; k < P.n_instr; ++k) {
     const EwInstr& ins = P.instr[k];
     const bool fl = ins.cls == EWC_FLOAT;
-    const bool sfl = ins.src_cls == EWC_FLOAT;
     std::string name = "t" + std::to_string(tcount++);
-    std::string expr;
-    const int op = ins.op;
-    if (op == EW_CAST) {
-      if (fl) expr = std::string(round_fn(ins.dt)) + "(" + (sfl ? ref(ins.a, true) : "(float)" + ref(ins.a, false)) + ")";
-      else if (ins.cls == EWC_BOOL) expr = sfl ? "(" + ref(ins.a, true) + " != 0.f ? 1 : 0)" : "(" + ref(ins.a, false) + " != 0 ? 1 : 0)";
-      else expr = std::string(wrap_fn(ins.dt)) + "(" + ref(ins.a, false) + ")";
-    } else if (op <= EW_ACOS) {
-      if (fl) expr = std::string(round_fn(ins.dt)) + "(" + float_unary(op, ref(ins.a, true)) + ")";
-      else if (op == EW_ABS) expr = std::string(wrap_fn(ins.dt)) + "(abs(" + ref(ins.a, false) + "))";
-      else if (op == EW_NEG) expr = std::string(wrap_fn(ins.dt)) + "(-" + ref(ins.a, false) + ")";
-      else if (op == EW_SQUARE) expr = std::string(wrap_fn(ins.dt)) + "(" + ref(ins.a, false) + " * " + ref(ins.a, false) + ")";
-      else expr = ref(ins.a, false);
-    } else if (op <= EW_ISNAN) {
-      const std::string a = ref(ins.a, true);
-      expr = op == EW_ISINF ? "(isinf(" + a + ") ? 1 : 0)" : op == EW_ISFINITE ? "(isfinite(" + a + ") ? 1 : 0)"
-                                                                                  : "(" + a + " != " + a + " ? 1 : 0)";
-    } else if (op == EW_NOT) {
-      expr = "(" + ref(ins.a, false) + " ? 0 : 1)";
-    } else if (op <= EW_ATAN2) {
-      if (fl) expr = std::string(round_fn(ins.dt)) + "(" + float_binary(op, ref(ins.a, true), ref(ins.b, true)) + ")";
-      else expr = std::string(wrap_fn(ins.dt)) + "(" + int_binary(op, ref(ins.a, false), ref(ins.b, false)) + ")";
-    } else if (op <= EW_LE) {
-      const std::string a = ref(ins.a, sfl), b = ref(ins.b, sfl);
-      if (op == EW_NE) expr = "(!(" + a + " == " + b + ") ? 1 : 0)";
-      else expr = "((" + a + " " + cmp_op(op) + " " + b + ") ? 1 : 0)";
-    } else if (op == EW_AND) {
-      expr = "((" + ref(ins.a, false) + " && " + ref(ins.b, false) + ") ? 1 : 0)";
-    } else if (op == EW_OR) {
-      expr = "((" + ref(ins.a, false) + " || " + ref(ins.b, false) + ") ? 1 : 0)";
-    } else {  // select: a = condition
-      expr = "(" + ref(ins.a, false) + " ? " + ref(ins.b, fl) + " : " + ref(ins.c, fl) + ")";
-    }
+    const std::string expr = instr_expr(ins.op, ins.dt, ins.cls, ins.src_cls, ins.a, ins.b, ins.c, ref);
     s << "      " << (fl ? "float " : "int ") << name << "[E];\n";
     s << "      #pragma unroll\n      for (int j = 0; j < E; ++j) " << name << "[j] = " << expr << ";\n";
     Var nv;
@@ -457,6 +467,172 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
   return true;
 }
 
+
+// ---- row programs --------------------------------------------------------------------------------------------------
+struct RowShape {
+  int vw = 8;    // elements per granule: 8 (16-byte accesses) or 1
+  int nv = 1;    // granules per thread
+  int t = 32;    // threads that own one row (a power of two)
+  int tpb = 128; // threads per CTA
+};
+
+int max_live_full(const RowProgram& P) {
+  const int n = P.n_val, ni = (int)P.instr.size();
+  std::vector<int> def(n, -1), last(n, -1);
+  for (int i = 0; i < ni; ++i) {
+    const RowInstr& x = P.instr[i];
+    def[x.dst] = i;
+    last[x.a] = i;
+    if (!x.reduce) {
+      last[x.b] = std::max(last[x.b], i);
+      last[x.c] = std::max(last[x.c], i);
+    }
+  }
+  for (auto& o : P.out) last[o.val] = ni;
+  int best = 1;
+  for (int i = 0; i <= ni; ++i) {
+    int live = 0;
+    for (int v = 0; v < n; ++v)
+      if (P.val_full[v] && def[v] < i && last[v] >= i) ++live;
+    best = std::max(best, live);
+  }
+  return best;
+}
+
+bool row_shape(const RowProgram& P, bool vec, RowShape* rs) {
+  rs->vw = vec ? 8 : 1;
+  const int64_t granules = (P.cols + rs->vw - 1) / rs->vw;
+  const int live = max_live_full(P);
+  int nv_max = std::max(1, 160 / (rs->vw * live));
+  nv_max = std::min(nv_max, vec ? 8 : 32);
+  int64_t t = 1;
+  while (t * nv_max < granules) t <<= 1;
+  int64_t coalesce = 1;
+  while (coalesce < granules && coalesce < 32) coalesce <<= 1;
+  t = std::max(t, coalesce);
+  if (t > 1024) return false;
+  rs->t = (int)t;
+  rs->nv = (int)((granules + t - 1) / t);
+  rs->tpb = std::max(128, rs->t);
+  return true;
+}
+
+bool row_generate(const RowProgram& P, bool vec, std::string* out, RowShape* shape) {
+  RowShape rs;
+  if (!row_shape(P, vec, &rs)) return false;
+  *shape = rs;
+  std::ostringstream s;
+  s << kPreamble;
+  s << "constexpr int C = " << P.cols << ", T = " << rs.t << ", TPB = " << rs.tpb << ", VW = " << rs.vw
+    << ", NV = " << rs.nv << ", RPB = TPB / T;\n";
+  s << R"SRC(
+template <int OP> __device__ __forceinline__ float comb(float a, float b) {
+  return OP == 0 ? __fadd_rn(a, b) : OP == 1 ? fmaxf(a, b) : OP == 2 ? fminf(a, b) : __fmul_rn(a, b);
+}
+// the same value in every thread of the row's group: butterfly inside a warp, then the group's warps through shared memory
+template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm) {
+#pragma unroll
+  for (int o = (T < 32 ? T : 32) / 2; o > 0; o >>= 1) v = comb<OP>(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if (T > 32) {
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = v;
+    __syncthreads();
+    const int first = (threadIdx.x / T) * (T / 32);
+    v = sm[first];
+#pragma unroll
+    for (int w = 1; w < T / 32; ++w) v = comb<OP>(v, sm[first + w]);
+  }
+  return v;
+}
+)SRC";
+  s << "extern \"C\" __global__ void __launch_bounds__(TPB) akgb_row_jit(";
+  for (size_t i = 0; i < P.in.size(); ++i) s << "const void* __restrict__ in" << i << ", ";
+  for (size_t i = 0; i < P.out.size(); ++i) s << "void* __restrict__ out" << i << ", ";
+  s << "i64 rows) {\n";
+  s << "  __shared__ float sm[TPB / 32];\n";
+  s << "  const int tr = threadIdx.x % T;\n";
+  s << "  const i64 row0 = (i64)blockIdx.x * RPB + threadIdx.x / T;\n";
+  s << "  const bool active = row0 < rows;\n";
+  s << "  const i64 r = active ? row0 : rows - 1;\n";
+  std::vector<std::string> name(P.n_val);
+  std::vector<char> is_float(P.n_val, 1), is_const(P.n_val, 0);
+  for (size_t c = 0; c < P.const_val.size(); ++c) {
+    char buf[32];
+    std::snprintf(buf, sizeof(buf), "0x%08xu", P.const_bits[c]);
+    name[P.const_val[c]] = buf;
+    is_const[P.const_val[c]] = 1;
+  }
+  // loads
+  for (size_t i = 0; i < P.in.size(); ++i) {
+    const RowOperand& o = P.in[i];
+    const bool fl = is_float_dt(o.dt);
+    const char* ty = fl ? "float" : "int";
+    const char* tag = dt_tag(o.dt);
+    const std::string v = "x" + std::to_string(i);
+    name[o.val] = v;
+    is_float[o.val] = fl;
+    if (o.kind == RK_ROW || o.kind == RK_SCALAR) {
+      s << "  const " << ty << " " << v << " = ld1_" << tag << "(in" << i << ", " << (o.kind == RK_ROW ? "r" : "0") << ");\n";
+      continue;
+    }
+    std::string base = o.kind == RK_FULL ? "r * C" : o.kind == RK_COL ? "(i64)0" : "(r % " + std::to_string(o.mod_rows) + "LL) * C";
+    s << "  " << ty << " " << v << "[NV][VW];\n";
+    s << "#pragma unroll\n  for (int k = 0; k < NV; ++k) {\n    const int c = (tr + T * k) * VW;\n";
+    if (vec) {
+      s << "    if (c < C) ld8_" << tag << "(in" << i << ", " << base << " + c, " << v << "[k], "
+        << (o.kind == RK_FULL ? "true" : "false") << ");\n";
+      s << "    else {\n#pragma unroll\n      for (int j = 0; j < VW; ++j) " << v << "[k][j] = 0; }\n";
+    } else {
+      s << "    " << v << "[k][0] = c < C ? ld1_" << tag << "(in" << i << ", " << base << " + c) : 0;\n";
+    }
+    s << "  }\n";
+  }
+  auto ref_full = [&](int val, bool want_float) -> std::string {
+    if (is_const[val]) return want_float ? "__uint_as_float(" + name[val] + ")" : "(int)" + name[val];
+    return P.val_full[val] ? name[val] + "[k][j]" : name[val];
+  };
+  for (size_t k = 0; k < P.instr.size(); ++k) {
+    const RowInstr& x = P.instr[k];
+    const bool fl = x.cls == EWC_FLOAT;
+    const std::string v = "t" + std::to_string(k);
+    name[x.dst] = v;
+    is_float[x.dst] = fl;
+    if (x.reduce) {
+      const char* ident = x.red_op == 0 ? "0.f" : x.red_op == 1 ? "-3.402823466e+38f" : x.red_op == 2 ? "3.402823466e+38f" : "1.f";
+      s << "  float " << v << ";\n  {\n    float acc = " << ident << ";\n";
+      s << "#pragma unroll\n    for (int k = 0; k < NV; ++k) {\n#pragma unroll\n      for (int j = 0; j < VW; ++j)\n";
+      s << "        if ((tr + T * k) * VW + j < C) acc = comb<" << x.red_op << ">(acc, " << name[x.a] << "[k][j]);\n    }\n";
+      s << "    " << v << " = " << round_fn(x.dt) << "(row_reduce<" << x.red_op << ">(acc, sm));\n  }\n";
+      continue;
+    }
+    const std::string expr = instr_expr(x.op, x.dt, x.cls, x.src_cls, x.a, x.b, x.c, ref_full);
+    if (x.full) {
+      s << "  " << (fl ? "float " : "int ") << v << "[NV][VW];\n";
+      s << "#pragma unroll\n  for (int k = 0; k < NV; ++k) {\n#pragma unroll\n    for (int j = 0; j < VW; ++j) " << v
+        << "[k][j] = " << expr << ";\n  }\n";
+    } else {
+      s << "  const " << (fl ? "float " : "int ") << v << " = " << expr << ";\n";
+    }
+  }
+  // stores
+  for (size_t i = 0; i < P.out.size(); ++i) {
+    const RowOperand& o = P.out[i];
+    const char* tag = dt_tag(o.dt);
+    if (o.kind == RK_ROW) {
+      const bool fl = is_float_dt(o.dt);
+      s << "  if (active && tr == 0) st1_" << tag << "(out" << i << ", r, " << ref_full(o.val, fl) << ");\n";
+      continue;
+    }
+    s << "  if (active) {\n#pragma unroll\n    for (int k = 0; k < NV; ++k) {\n      const int c = (tr + T * k) * VW;\n";
+    if (vec) s << "      if (c < C) st8_" << tag << "(out" << i << ", r * C + c, " << name[o.val] << "[k]);\n";
+    else s << "      if (c < C) st1_" << tag << "(out" << i << ", r * C + c, " << name[o.val] << "[k][0]);\n";
+    s << "    }\n  }\n";
+  }
+  s << "}\n";
+  *out = s.str();
+  return true;
+}
+
 constexpr const char* kJitOptionsTag = "akgb-ew-jit-1 sm_100a c++17 fmad=false";
 
 struct JitKernel {
@@ -505,7 +681,7 @@ void write_file_atomically(const std::string& path, const std::vector<char>& dat
   if (!ok || std::rename(tmp.c_str(), path.c_str()) != 0) std::remove(tmp.c_str());
 }
 
-JitKernel* compile(const std::string& src) {
+JitKernel* compile(const std::string& src, const char* entry = "akgb_ew_jit") {
   std::lock_guard<std::mutex> lock(g_mu);
   int dev = 0;
   cudaGetDevice(&dev);
@@ -527,7 +703,7 @@ JitKernel* compile(const std::string& src) {
     if (read_file(path, &image)) {
       CUmodule mod = nullptr;
       if (d.ModuleLoadData(&mod, image.data()) == CUDA_SUCCESS &&
-          d.ModuleGetFunction(&k.fn, mod, "akgb_ew_jit") == CUDA_SUCCESS) {
+          d.ModuleGetFunction(&k.fn, mod, entry) == CUDA_SUCCESS) {
         k.failed = false;
         ++g_n_from_disk;
         return &k;
@@ -559,7 +735,7 @@ JitKernel* compile(const std::string& src) {
   if (cubin.empty()) return &k;
   CUmodule mod = nullptr;
   if (d.ModuleLoadData(&mod, cubin.data()) != CUDA_SUCCESS) return &k;
-  if (d.ModuleGetFunction(&k.fn, mod, "akgb_ew_jit") != CUDA_SUCCESS) return &k;
+  if (d.ModuleGetFunction(&k.fn, mod, entry) != CUDA_SUCCESS) return &k;
   k.failed = false;
   ++g_n_compiled;
   if (!path.empty()) write_file_atomically(path, cubin);
@@ -580,6 +756,52 @@ void jit_cache_stats(uint64_t* compiled, uint64_t* from_disk) {
   std::lock_guard<std::mutex> lock(g_mu);
   if (compiled) *compiled = g_n_compiled;
   if (from_disk) *from_disk = g_n_from_disk;
+}
+
+std::string row_jit_source(const RowProgram& P, bool vec) {
+  std::string src;
+  RowShape rs;
+  if (!row_generate(P, vec, &src, &rs)) src.clear();
+  return src;
+}
+
+// One generated kernel for a whole reduce-X region; cudaErrorNotSupported when it cannot be generated or compiled (the
+// caller then runs the region as separate launches).
+cudaError_t row_jit_launch(const RowProgram& P, const void* const* in, void* const* out, cudaStream_t s, LaunchDims* dims) {
+  if (P.rows == 0) return cudaSuccess;
+  bool vec = P.cols % 8 == 0;
+  for (size_t i = 0; i < P.in.size() && vec; ++i)
+    if (P.in[i].kind != RK_ROW && P.in[i].kind != RK_SCALAR) vec = aligned16(in[i]);
+  for (size_t i = 0; i < P.out.size() && vec; ++i)
+    if (P.out[i].kind == RK_FULL) vec = aligned16(out[i]);
+  std::string src;
+  RowShape rs;
+  if (!row_generate(P, vec, &src, &rs)) return cudaErrorNotSupported;
+  JitKernel* k = compile(src, "akgb_row_jit");
+  if (!k || k->failed) return cudaErrorNotSupported;
+  const int rpb = rs.tpb / rs.t;
+  const int64_t grid = (P.rows + rpb - 1) / rpb;
+  if (grid > 0x7fffffff) return cudaErrorNotSupported;
+  long long rows = P.rows;
+  void* args[32];
+  const void* inp[16];
+  void* outp[16];
+  int a = 0;
+  for (size_t i = 0; i < P.in.size(); ++i) {
+    inp[i] = in[i];
+    args[a++] = &inp[i];
+  }
+  for (size_t i = 0; i < P.out.size(); ++i) {
+    outp[i] = out[i];
+    args[a++] = &outp[i];
+  }
+  args[a++] = &rows;
+  if (dims) {
+    dims->grid[0] = (unsigned)grid;
+    dims->block[0] = (unsigned)rs.tpb;
+  }
+  const CUresult r = driver().LaunchKernel(k->fn, (unsigned)grid, 1, 1, (unsigned)rs.tpb, 1, 1, 0, (CUstream)s, args, nullptr);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorLaunchFailure;
 }
 
 // The CUDA C++ text that would be compiled for this program (empty when the program needs the interpreter).

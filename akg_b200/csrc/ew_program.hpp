@@ -57,3 +57,48 @@ struct EwProgram {
 };
 
 }  // namespace akgb
+
+// ---- row program --------------------------------------------------------------------------------------------------
+// A fused region whose iteration space is [rows, cols] with reductions along cols only (the reduce-X class: softmax,
+// LayerNorm, RMSNorm, log-softmax, L2-normalise ... in any spelling).  Values are either per element of the row
+// ("full") or one per row; the program is a static single assignment list that the run-time generator prints as one
+// kernel in which a group of threads owns a row and keeps it in registers.  Host-side only.
+#include <vector>
+
+namespace akgb {
+
+enum RowKind : int32_t {
+  RK_FULL = 0,    // [rows, cols]
+  RK_ROW = 1,     // [rows] / [rows, 1]
+  RK_COL = 2,     // [cols], the same for every row
+  RK_SCALAR = 3,  // one element
+  RK_ROWMOD = 4   // [mod_rows, cols] with rows % mod_rows == 0: row r reads row r % mod_rows (a mask shared by batches)
+};
+
+struct RowOperand {
+  int32_t dt = 0;
+  int32_t kind = RK_FULL;
+  int32_t val = 0;  // value loaded into / stored from
+  int64_t mod_rows = 0;
+};
+
+struct RowInstr {
+  uint8_t op = 0;  // EwOp, unless `reduce`
+  uint8_t dt = 0, cls = 0, src_cls = 0;
+  bool reduce = false;  // dst (per row) = reduction of a (full) along the row
+  int32_t red_op = 0;   // 0 sum, 1 max, 2 min, 3 prod
+  bool full = false;    // the result is per element
+  int32_t dst = 0, a = 0, b = 0, c = 0;
+};
+
+struct RowProgram {
+  int64_t rows = 0, cols = 0;
+  int32_t n_val = 0;
+  std::vector<RowOperand> in, out;
+  std::vector<RowInstr> instr;
+  std::vector<int32_t> const_val;
+  std::vector<uint32_t> const_bits;
+  std::vector<uint8_t> val_full;  // per value: per element (1) or per row (0)
+};
+
+}  // namespace akgb

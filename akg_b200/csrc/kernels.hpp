@@ -80,6 +80,10 @@ cudaError_t ew_generic(const EwProgram& p, const void* const* in, void* const* o
                        LaunchDims* dims);
 // run-time instantiated variant (ew_jit.cpp); cudaErrorNotSupported = fall back to the interpreter
 std::string ew_jit_source(const EwProgram& p, bool vec);
+struct RowProgram;
+cudaError_t row_jit_launch(const RowProgram& p, const void* const* in, void* const* out, cudaStream_t s,
+                           LaunchDims* dims);
+std::string row_jit_source(const RowProgram& p, bool vec);
 void jit_set_cache_dir(const char* dir);  // nullptr: environment's choice; "": no disk cache
 void jit_cache_stats(uint64_t* compiled, uint64_t* from_disk);
 cudaError_t ew_jit_launch(const EwProgram& p, const void* const* in, void* const* out, cudaStream_t s, LaunchDims* dims);

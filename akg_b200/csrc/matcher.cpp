@@ -695,7 +695,7 @@ bool match_gelu_chain(const Graph& g, Plan& plan) {
 
 }  // namespace
 
-Plan build_plan(const Graph& g, int sm_count) {
+Plan build_plan(const Graph& g, int sm_count, bool allow_jit) {
   for (auto& n : g.nodes)
     if (n.kind == OpK::Unknown)
       throw Unsupported("operator '" + n.name + "' is not supported");
@@ -715,8 +715,38 @@ Plan build_plan(const Graph& g, int sm_count) {
       ok = match_gelu_chain(g, plan);
       break;
   }
-  if (!ok) plan = build_generic_plan(g, sm_count);
+  if (!ok) {
+    plan = build_generic_plan(g, sm_count);
+    // a reduce-X region that would take several launches: one generated row kernel, the launches as its fallback
+    auto rp = std::make_shared<RowProgram>();
+    std::vector<int> in_values, out_values;
+    if (allow_jit && plan.steps.size() > 1 && g.op_class == OpClass::Reduction &&
+        build_row_program(g, rp.get(), &in_values, &out_values)) {
+      Plan fused;
+      fused.klass = plan.klass;
+      fused.workspace_bytes = plan.workspace_bytes;
+      fused.flops = plan.flops;
+      Step st;
+      st.kind = StepK::RowJit;
+      st.kernel_name = "akgb_row_jit";
+      st.row = rp;
+      for (int vid : in_values) {
+        Ref r;
+        r.arg = g.v(vid).input_index;
+        st.ew_in.push_back(r);
+      }
+      for (int vid : out_values) {
+        Ref r;
+        r.arg = (int)g.inputs.size() + g.v(vid).output_index;
+        st.ew_out.push_back(r);
+      }
+      fused.steps.push_back(std::move(st));
+      fused.fallback = std::make_shared<Plan>(std::move(plan));
+      plan = std::move(fused);
+    }
+  }
   plan.bytes = io_bytes(g);
+  if (plan.fallback) plan.fallback->bytes = plan.bytes;
   return plan;
 }
 

@@ -1,6 +1,7 @@
 // Execution plan of one fused region: an ordered list of kernel-template
 // instantiations over argument slots and workspace offsets.
 #pragma once
+#include <memory>
 #include <string>
 #include <vector>
 
@@ -18,7 +19,7 @@ struct Ref {
   bool valid() const { return arg >= 0 || ws_off >= 0; }
 };
 
-enum class StepK : int { GeluChain, LayerNorm, Softmax, ReduceCol, ReduceAll, ReduceRow, ReduceColDual, Transpose, Matmul, Ew, Gather, SegmentSum, ArgMax };
+enum class StepK : int { GeluChain, LayerNorm, Softmax, ReduceCol, ReduceAll, ReduceRow, ReduceColDual, Transpose, Matmul, Ew, Gather, SegmentSum, ArgMax, RowJit };
 
 struct Step {
   StepK kind;
@@ -33,6 +34,7 @@ struct Step {
   TransposeParams tp;
   MatmulParams mm;
   EwProgram ew;              // StepK::Ew
+  std::shared_ptr<RowProgram> row;  // StepK::RowJit (operands in ew_in / ew_out)
   std::vector<Ref> ew_in, ew_out;
   int64_t ix_outer = 1, ix_dim = 1, ix_n = 1, ix_inner = 1, ix_segments = 0;  // Gather / SegmentSum extents
   int ix_esize = 4, ix_idx64 = 0;
@@ -48,10 +50,16 @@ struct Plan {
   int64_t bytes = 0;        // algorithmic bytes: inputs read once + outputs written once
   int64_t flops = 0;
   bool needs_gelu_lut = false;
+  // A plan made of one run-time generated row kernel carries the multi-launch plan of the same region; it takes over
+  // for good if the kernel cannot be generated or compiled on this host.
+  std::shared_ptr<Plan> fallback;
+  bool use_fallback = false;
 };
 
 // Pattern matcher: places the region on kernel templates or throws Unsupported.
-Plan build_plan(const Graph& g, int sm_count);
+Plan build_plan(const Graph& g, int sm_count, bool allow_jit = true);
+// Reduce-X regions as one row program (rowfuse.cpp); `in_values` / `out_values` receive the graph values of the operands.
+bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_values, std::vector<int>* out_values);
 // Fallback of build_plan: splits the region into elementwise groups (generic kernel), reductions, transposes and
 // matmuls that run one after the other with intermediates in the workspace.
 Plan build_generic_plan(const Graph& g, int sm_count);

@@ -84,6 +84,15 @@ uint32_t const_bits(double v, DT d) {
   return b;
 }
 
+}  // namespace
+
+// shared with the row-program builder (rowfuse.cpp)
+bool ew_opcode_of(OpK k, EwOp* op) { return ew_opcode(k, op); }
+uint32_t ew_const_bits(double v, DT d) { return const_bits(v, d); }
+bool ew_type_ok(DT d) { return ew_dtype_ok(d); }
+
+namespace {
+
 struct Builder {
   const Graph& g;
   int sm_count;

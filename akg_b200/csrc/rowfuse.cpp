@@ -1,0 +1,210 @@
+// Recognises regions of the reduce-X class that can run as ONE generated kernel with a row kept in registers.
+//
+// The reference fuses such regions (elementwise ops around reductions along the last axis) into one kernel through its
+// polyhedral schedule (reduce-X template: akg-mlir/lib/Dialect/Affine/Analysis/GpuTemplateTilingSolver.cpp:458-542,
+// block-level combine: GpuUseAllReduceWithAtomicReturn.cpp:168-224).  The hand-written LayerNorm and softmax templates
+// cover two spellings; this builder accepts any op list made of elementwise ops, BroadcastTo, view Reshapes and
+// reductions over the last axis whose tensors are [rows, cols], [rows], [cols], scalars or a [m, cols] tensor shared by
+// rows modulo m, and hands it to the run-time generator (ew_jit.cpp::row_jit_*).
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <map>
+
+#include "hostconv.hpp"
+#include "plan.hpp"
+
+namespace akgb {
+
+bool ew_opcode_of(OpK k, EwOp* op);           // planner.cpp
+uint32_t ew_const_bits(double v, DT d);       // planner.cpp
+bool ew_type_ok(DT d);                        // planner.cpp
+
+namespace {
+
+EwClass cls_of(DT d) { return dt_is_float(d) ? EWC_FLOAT : (d == DT::Bool ? EWC_BOOL : EWC_INT); }
+
+std::vector<int64_t> strip_leading_ones(std::vector<int64_t> s) {
+  while (s.size() > 1 && s.front() == 1) s.erase(s.begin());
+  return s;
+}
+
+}  // namespace
+
+bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_values, std::vector<int>* out_values) {
+  if (g.dynamic || g.nodes.empty()) return false;
+  // the row shape comes from the first reduction
+  const Node* first_red = nullptr;
+  for (auto& n : g.nodes)
+    if (opk_is_reduce(n.kind)) {
+      first_red = &n;
+      break;
+    }
+  if (!first_red) return false;
+  const std::vector<int64_t>& S = g.v(first_red->in[0]).shape;
+  if (S.empty()) return false;
+  const int64_t C = S.back();
+  int64_t R = 1;
+  for (size_t i = 0; i + 1 < S.size(); ++i) R *= S[i];
+  if (C < 2 || R < 1 || C > 16384) return false;
+  const std::vector<int64_t> S_lead(S.begin(), S.end() - 1);
+
+  RowProgram P;
+  P.rows = R;
+  P.cols = C;
+  std::map<int, int> val_of;  // graph value -> program value
+  auto new_val = [&](bool full) {
+    P.val_full.push_back(full ? 1 : 0);
+    return P.n_val++;
+  };
+  // class of a tensor by its shape: 0 full, 1 row, 2 col, 3 scalar, 4 rowmod, -1 none
+  auto shape_kind = [&](const std::vector<int64_t>& shp, int64_t* mod_rows) -> int {
+    int64_t n = 1;
+    for (auto e : shp) n *= e;
+    if (shp.empty()) return RK_SCALAR;
+    if (n == R * C && shp.back() == C) return RK_FULL;
+    if (n == 1) return RK_SCALAR;
+    if (n == C && shp.back() == C) return RK_COL;
+    if (n == R && (shp.back() == 1 || shp.size() + 1 == S.size() || S.size() == 1)) {
+      std::vector<int64_t> lead = shp;
+      if (lead.back() == 1 && lead.size() > 1) lead.pop_back();
+      if (strip_leading_ones(lead) == strip_leading_ones(S_lead) || lead == S_lead) return RK_ROW;
+      return -1;
+    }
+    if (shp.back() == C && n % C == 0 && R % (n / C) == 0) {
+      const std::vector<int64_t> t = strip_leading_ones(shp);
+      if (t.size() > S.size()) return -1;
+      for (size_t i = 0; i < t.size(); ++i)
+        if (t[t.size() - 1 - i] != S[S.size() - 1 - i]) return -1;
+      *mod_rows = n / C;
+      return RK_ROWMOD;
+    }
+    return -1;
+  };
+  auto operand = [&](int vid, int* val) -> bool {
+    auto it = val_of.find(vid);
+    if (it != val_of.end()) {
+      *val = it->second;
+      return true;
+    }
+    const Value& v = g.v(vid);
+    if (!ew_type_ok(v.dt)) return false;
+    if (v.is_const) {
+      if (v.cval.size() != 1) return false;
+      const int id = new_val(false);
+      P.const_val.push_back(id);
+      P.const_bits.push_back(ew_const_bits(v.cval[0], v.dt));
+      val_of[vid] = id;
+      *val = id;
+      return true;
+    }
+    if (v.input_index < 0) return false;  // produced by an op this builder did not take
+    int64_t mod_rows = 0;
+    const int kind = shape_kind(v.shape, &mod_rows);
+    if (kind < 0) return false;
+    RowOperand o;
+    o.dt = (int)v.dt;
+    o.kind = kind;
+    o.mod_rows = mod_rows;
+    o.val = new_val(kind == RK_FULL || kind == RK_COL || kind == RK_ROWMOD);
+    P.in.push_back(o);
+    in_values->push_back(vid);
+    val_of[vid] = o.val;
+    *val = o.val;
+    return true;
+  };
+
+  for (const Node& n : g.nodes) {
+    const Value& ov = g.v(n.out);
+    if (!ew_type_ok(ov.dt)) return false;
+    RowInstr ins;
+    ins.dt = (uint8_t)ov.dt;
+    ins.cls = cls_of(ov.dt);
+    if (opk_is_reduce(n.kind)) {
+      const Value& x = g.v(n.in[0]);
+      if (n.axes.size() != 1 || n.axes[0] != (int64_t)x.shape.size() - 1 || x.shape.back() != C || x.numel() != R * C)
+        return false;
+      switch (n.kind) {
+        case OpK::ReduceSum: ins.red_op = 0; break;
+        case OpK::ReduceMax: ins.red_op = 1; break;
+        case OpK::ReduceMin: ins.red_op = 2; break;
+        case OpK::ReduceProd: ins.red_op = 3; break;
+        default: return false;
+      }
+      if (!dt_is_float(x.dt) || ov.dt != x.dt || ov.numel() != R) return false;
+      if (!operand(n.in[0], &ins.a) || !P.val_full[ins.a]) return false;
+      ins.reduce = true;
+      ins.full = false;
+      ins.src_cls = EWC_FLOAT;
+    } else if (n.kind == OpK::Reshape || n.kind == OpK::BroadcastTo) {
+      if (!operand(n.in[0], &ins.a)) return false;
+      const bool src_full = P.val_full[ins.a] != 0;
+      int64_t dummy = 0;
+      const int kind = shape_kind(ov.shape, &dummy);
+      if (n.kind == OpK::Reshape) {
+        // a view: the class must survive (full stays [.., cols], per-row stays per-row)
+        if (src_full ? (ov.numel() != g.v(n.in[0]).numel() || ov.shape.back() != C) : (kind != RK_ROW && kind != RK_SCALAR))
+          return false;
+        ins.full = src_full;
+      } else {
+        if (kind != RK_FULL && kind != RK_ROW && kind != RK_SCALAR) return false;
+        if (src_full && kind != RK_FULL) return false;
+        ins.full = kind == RK_FULL;
+      }
+      ins.op = EW_COPY;
+      ins.src_cls = cls_of(g.v(n.in[0]).dt);
+      if (g.v(n.in[0]).dt != ov.dt) return false;
+    } else if (opk_is_elementwise(n.kind)) {
+      EwOp op;
+      if (!ew_opcode_of(n.kind, &op) || n.in.empty() || n.in.size() > 3) return false;
+      int regs[3] = {0, 0, 0};
+      bool any_full = false;
+      for (size_t j = 0; j < n.in.size(); ++j) {
+        if (!operand(n.in[j], &regs[j])) return false;
+        any_full |= P.val_full[regs[j]] != 0;
+      }
+      ins.op = (uint8_t)op;
+      ins.a = regs[0];
+      ins.b = regs[1];
+      ins.c = regs[2];
+      ins.src_cls = cls_of(g.v(n.in[op == EW_SELECT ? 1 : 0]).dt);
+      if (op == EW_CAST && ins.src_cls == EWC_FLOAT && ins.cls == EWC_INT) return false;  // unpinned rounding
+      ins.full = any_full;
+      int64_t dummy = 0;
+      const int kind = shape_kind(ov.shape, &dummy);
+      if (kind < 0) return false;
+      if (!any_full && kind != RK_ROW && kind != RK_SCALAR) return false;
+    } else {
+      return false;
+    }
+    ins.dst = new_val(ins.full);
+    val_of[n.out] = ins.dst;
+    P.instr.push_back(ins);
+    if (P.instr.size() > 160) return false;
+  }
+  for (int vid : g.outputs) {
+    auto it = val_of.find(vid);
+    const Value& v = g.v(vid);
+    if (it == val_of.end() || v.producer < 0) return false;  // an input or constant passed through
+    RowOperand o;
+    o.dt = (int)v.dt;
+    o.val = it->second;
+    if (P.val_full[o.val]) {
+      if (v.numel() != R * C) return false;  // a per-column value computed on the way cannot be a result
+      o.kind = RK_FULL;
+    } else {
+      if (v.numel() != R) return false;
+      o.kind = RK_ROW;
+    }
+    P.out.push_back(o);
+    out_values->push_back(vid);
+  }
+  if (P.in.size() > 12 || P.out.size() > 8 || P.in.empty()) return false;
+  bool any_full_in = false;
+  for (auto& o : P.in) any_full_in |= o.kind == RK_FULL;
+  if (!any_full_in) return false;
+  *out = std::move(P);
+  return true;
+}
+
+}  // namespace akgb
