@@ -165,6 +165,7 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
         for (size_t i = 0; i < st.ew_out.size(); ++i) outs[i] = resolve(st.ew_out[i], tensors, ws);
         e = row_jit_launch(*st.row, ins, outs, s, &st.dims);
         if (e == cudaErrorNotSupported && plan.fallback) {  // no run-time compiler here: the separate launches
+          // (the generated kernel is always the plan's first step, so nothing has been enqueued yet)
           plan.use_fallback = true;
           return run_plan(k, *plan.fallback, tensors, ws, s);
         }

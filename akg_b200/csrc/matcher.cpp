@@ -695,6 +695,84 @@ bool match_gelu_chain(const Graph& g, Plan& plan) {
 
 }  // namespace
 
+// An elementwise chain over equally shaped tensors that ends in a reduction over ALL axes reads its inputs once when
+// the n elements are viewed as [n / c, c] rows: one generated row kernel folds every row (the chain runs in registers)
+// and the hand-written global reduction folds the n / c row results.  Returns false when the region is not of that form.
+bool fused_reduce_all_plan(const Graph& g, int sm_count, Plan* out) {
+  if (g.dynamic || g.outputs.size() != 1 || g.nodes.empty()) return false;
+  const Node& red = g.nodes.back();
+  if (!opk_is_reduce(red.kind) || red.out != g.outputs[0]) return false;
+  RedOp op;
+  switch (red.kind) {
+    case OpK::ReduceSum: op = RedOp::Sum; break;
+    case OpK::ReduceMax: op = RedOp::Max; break;
+    case OpK::ReduceMin: op = RedOp::Min; break;
+    case OpK::ReduceProd: op = RedOp::Prod; break;
+    default: return false;
+  }
+  const Value& x = g.v(red.in[0]);
+  if (red.axes.size() != x.shape.size() || x.dt != DT::F32 || g.v(red.out).dt != DT::F32 || g.v(red.out).numel() != 1)
+    return false;
+  const int64_t n = x.numel();
+  if (n < (1 << 16)) return false;  // small tensors: the extra pass is not worth a generated kernel
+  for (size_t i = 0; i + 1 < g.nodes.size(); ++i) {
+    const Node& nd = g.nodes[i];
+    if (!opk_is_elementwise(nd.kind) || nd.kind == OpK::AddN) return false;
+    if (g.v(nd.out).numel() != n || g.v(nd.out).output_index >= 0) return false;
+    for (int vid : nd.in) {
+      const Value& v = g.v(vid);
+      if (!v.is_const && v.numel() != n) return false;  // broadcast operands would not survive the re-view
+    }
+  }
+  int64_t c = 0;
+  for (int64_t cand : {4096, 2048, 1024, 512, 256, 128, 64})
+    if (n % cand == 0) {
+      c = cand;
+      break;
+    }
+  if (c == 0) return false;
+  const int64_t r = n / c;
+  Graph g2 = g;
+  for (auto& v : g2.values)
+    if (!v.is_const && v.numel() == n) v.shape = {r, c};
+  Node& red2 = g2.nodes.back();
+  red2.axes = {1};
+  red2.keep_dims = false;
+  g2.v(red2.out).shape = {r};
+  auto rp = std::make_shared<RowProgram>();
+  std::vector<int> in_values, out_values;
+  if (!build_row_program(g2, rp.get(), &in_values, &out_values) || out_values.size() != 1) return false;
+  Plan p;
+  p.klass = "reduce_all";
+  Step st;
+  st.kind = StepK::RowJit;
+  st.kernel_name = "akgb_row_jit";
+  st.row = rp;
+  for (int vid : in_values) {
+    Ref ref;
+    ref.arg = g.v(vid).input_index;
+    st.ew_in.push_back(ref);
+  }
+  Ref partial;
+  partial.ws_off = 0;
+  st.ew_out.push_back(partial);
+  p.steps.push_back(std::move(st));
+  size_t ws = ((size_t)r * sizeof(float) + 255) / 256 * 256;
+  Step fin;
+  fin.kind = StepK::ReduceAll;
+  fin.kernel_name = "reduce_all_f32";
+  fin.red_op = op;
+  fin.red_len = r;
+  fin.a = partial;
+  fin.out.arg = (int)g.inputs.size();
+  fin.scratch.ws_off = (int64_t)ws;
+  ws += (reduce_all_workspace(sm_count) + 255) / 256 * 256;
+  p.steps.push_back(std::move(fin));
+  p.workspace_bytes = ws;
+  *out = std::move(p);
+  return true;
+}
+
 Plan build_plan(const Graph& g, int sm_count, bool allow_jit) {
   for (auto& n : g.nodes)
     if (n.kind == OpK::Unknown)
@@ -741,6 +819,11 @@ Plan build_plan(const Graph& g, int sm_count, bool allow_jit) {
         st.ew_out.push_back(r);
       }
       fused.steps.push_back(std::move(st));
+      fused.fallback = std::make_shared<Plan>(std::move(plan));
+      plan = std::move(fused);
+    } else if (Plan fused; allow_jit && plan.steps.size() >= 2 && fused_reduce_all_plan(g, sm_count, &fused)) {
+      fused.workspace_bytes = std::max(fused.workspace_bytes, plan.workspace_bytes);
+      fused.flops = plan.flops;
       fused.fallback = std::make_shared<Plan>(std::move(plan));
       plan = std::move(fused);
     }

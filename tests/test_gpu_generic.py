@@ -153,6 +153,8 @@ def test_mul_reduce_sum_x_and_all(lib):
         truth = (ins[0].astype(np.float64) ** 2).sum(axis=tuple(axes)).reshape(oshape)
         assert np.all(np.abs(got[0] - truth) <= 1e-5 * truth)
         assert k.launch_count >= (1 if FLAGS[0] == 0 and axes == [1] else 2)  # the row reduction: one generated kernel
+        if FLAGS[0] == 0:  # the square is folded into the reduction's pass in both cases
+            assert k.meta()["template"] == "akgb_row_jit"
 
 
 def test_reduce_sum_y_keep_dims_and_batched(lib):
