@@ -171,6 +171,16 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
         }
         break;
       }
+      case StepK::ColJit: {
+        const void* ins[16];
+        for (size_t i = 0; i < st.ew_in.size(); ++i) ins[i] = resolve(st.ew_in[i], tensors, ws);
+        e = col_jit_launch(*st.row, ins, (float*)o, st.red_len, s, &st.dims);
+        if (e == cudaErrorNotSupported && plan.fallback) {
+          plan.use_fallback = true;
+          return run_plan(k, *plan.fallback, tensors, ws, s);
+        }
+        break;
+      }
       case StepK::Ew: {
         const void* ins[kEwMaxIn];
         void* outs[kEwMaxOut];
@@ -622,7 +632,7 @@ akgb_status akgb_dump_jit_source(const akgb_kernel* k, int32_t vectorised, char*
   if (!k) return fail(AKGB_INVALID_ARG, "null argument");
   std::string src;
   for (const Step& st : active_plan(k).steps) {
-    if (st.kind == StepK::RowJit) src = row_jit_source(*st.row, vectorised != 0);
+    if (st.kind == StepK::RowJit || st.kind == StepK::ColJit) src = row_jit_source(*st.row, vectorised != 0);
     else if (st.kind == StepK::Ew) src = ew_jit_source(st.ew, vectorised != 0);
     if (!src.empty()) break;
   }

@@ -633,6 +633,111 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
   return true;
 }
 
+
+// ---- column programs: an elementwise chain folded over the rows of [rows, cols] in the pass that reads it --------
+struct ColShape {
+  int vw = 8, tx = 32, ty = 8;
+};
+
+bool col_generate(const RowProgram& P, bool vec, std::string* out, ColShape* shape) {
+  if (!P.col_reduce || P.out.size() != 1) return false;
+  ColShape cs;
+  cs.vw = vec ? 8 : 1;
+  const int64_t granules = (P.cols + cs.vw - 1) / cs.vw;
+  cs.tx = 1;
+  while (cs.tx < 32 && cs.tx < granules) cs.tx <<= 1;
+  cs.ty = 256 / cs.tx;
+  *shape = cs;
+  std::ostringstream s;
+  s << kPreamble;
+  s << "constexpr int C = " << P.cols << ", TX = " << cs.tx << ", TY = " << cs.ty << ", VW = " << cs.vw << ";\n";
+  s << R"SRC(
+template <int OP> __device__ __forceinline__ float comb(float a, float b) {
+  return OP == 0 ? __fadd_rn(a, b) : OP == 1 ? fmaxf(a, b) : OP == 2 ? fminf(a, b) : __fmul_rn(a, b);
+}
+)SRC";
+  const char* ident = P.col_red_op == 0 ? "0.f" : P.col_red_op == 1 ? "-3.402823466e+38f" : P.col_red_op == 2 ? "3.402823466e+38f" : "1.f";
+  s << "extern \"C\" __global__ void __launch_bounds__(256) akgb_col_jit(";
+  for (size_t i = 0; i < P.in.size(); ++i) s << "const void* __restrict__ in" << i << ", ";
+  s << "float* __restrict__ partial, i64 rows, i64 rows_per_split) {\n";
+  s << "  __shared__ float sm[TY][TX * VW + 1];\n";
+  s << "  const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;\n";
+  s << "  const i64 c = ((i64)blockIdx.x * TX + tx) * VW;\n";
+  s << "  const bool valid = c < C;\n";
+  s << "  const i64 r0 = (i64)blockIdx.y * rows_per_split;\n";
+  s << "  const i64 r1 = r0 + rows_per_split < rows ? r0 + rows_per_split : rows;\n";
+  std::vector<std::string> name(P.n_val);
+  std::vector<char> is_const(P.n_val, 0);
+  for (size_t k = 0; k < P.const_val.size(); ++k) {
+    char buf[32];
+    std::snprintf(buf, sizeof(buf), "0x%08xu", P.const_bits[k]);
+    name[P.const_val[k]] = buf;
+    is_const[P.const_val[k]] = 1;
+  }
+  auto load_full = [&](std::ostream& o, size_t i, const std::string& base) {
+    const RowOperand& op = P.in[i];
+    const char* tag = dt_tag(op.dt);
+    const std::string v = "x" + std::to_string(i);
+    if (vec) o << "ld8_" << tag << "(in" << i << ", " << base << " + c, " << v << ", " << (op.kind == RK_FULL ? "true" : "false") << ");\n";
+    else o << v << "[0] = ld1_" << tag << "(in" << i << ", " << base << " + c);\n";
+  };
+  // operands that do not change from row to row
+  for (size_t i = 0; i < P.in.size(); ++i) {
+    const RowOperand& op = P.in[i];
+    const bool fl = is_float_dt(op.dt);
+    const std::string v = "x" + std::to_string(i);
+    name[op.val] = v;
+    if (op.kind == RK_SCALAR) {
+      s << "  const " << (fl ? "float " : "int ") << v << " = ld1_" << dt_tag(op.dt) << "(in" << i << ", 0);\n";
+    } else if (op.kind == RK_COL) {
+      s << "  " << (fl ? "float " : "int ") << v << "[VW];\n#pragma unroll\n  for (int j = 0; j < VW; ++j) " << v << "[j] = 0;\n";
+      s << "  if (valid) { ";
+      load_full(s, i, "(i64)0");
+      s << "  }\n";
+    }
+  }
+  s << "  float acc[VW];\n#pragma unroll\n  for (int j = 0; j < VW; ++j) acc[j] = " << ident << ";\n";
+  s << "  if (valid) {\n#pragma unroll 4\n    for (i64 r = r0 + ty; r < r1; r += TY) {\n";
+  for (size_t i = 0; i < P.in.size(); ++i) {
+    const RowOperand& op = P.in[i];
+    const bool fl = is_float_dt(op.dt);
+    const std::string v = "x" + std::to_string(i);
+    if (op.kind == RK_ROW) {
+      s << "      const " << (fl ? "float " : "int ") << v << " = ld1_" << dt_tag(op.dt) << "(in" << i << ", r);\n";
+    } else if (op.kind == RK_FULL || op.kind == RK_ROWMOD) {
+      s << "      " << (fl ? "float " : "int ") << v << "[VW];\n      ";
+      load_full(s, i, op.kind == RK_FULL ? "r * C" : "(r % " + std::to_string(op.mod_rows) + "LL) * C");
+    }
+  }
+  auto ref = [&](int val, bool want_float) -> std::string {
+    if (is_const[val]) return want_float ? "__uint_as_float(" + name[val] + ")" : "(int)" + name[val];
+    return P.val_full[val] ? name[val] + "[j]" : name[val];
+  };
+  for (size_t k = 0; k < P.instr.size(); ++k) {
+    const RowInstr& x = P.instr[k];
+    if (x.reduce) return false;
+    const bool fl = x.cls == EWC_FLOAT;
+    const std::string v = "t" + std::to_string(k);
+    name[x.dst] = v;
+    const std::string expr = instr_expr(x.op, x.dt, x.cls, x.src_cls, x.a, x.b, x.c, ref);
+    if (x.full) {
+      s << "      " << (fl ? "float " : "int ") << v << "[VW];\n#pragma unroll\n      for (int j = 0; j < VW; ++j) " << v
+        << "[j] = " << expr << ";\n";
+    } else {
+      s << "      const " << (fl ? "float " : "int ") << v << " = " << expr << ";\n";
+    }
+  }
+  s << "#pragma unroll\n      for (int j = 0; j < VW; ++j) acc[j] = comb<" << P.col_red_op << ">(acc[j], " << name[P.out[0].val]
+    << "[j]);\n";
+  s << "    }\n  }\n";
+  s << "#pragma unroll\n  for (int j = 0; j < VW; ++j) sm[ty][tx * VW + j] = acc[j];\n  __syncthreads();\n";
+  s << "#pragma unroll\n  for (int h = TY / 2; h > 0; h >>= 1) {\n    if (ty < h) {\n#pragma unroll\n      for (int j = 0; j < VW; ++j) "
+       "sm[ty][tx * VW + j] = comb<" << P.col_red_op << ">(sm[ty][tx * VW + j], sm[ty + h][tx * VW + j]);\n    }\n    __syncthreads();\n  }\n";
+  s << "  if (ty == 0 && valid) {\n#pragma unroll\n    for (int j = 0; j < VW; ++j)\n      if (c + j < C) partial[(i64)blockIdx.y * C + c + j] = sm[0][tx * VW + j];\n  }\n}\n";
+  *out = s.str();
+  return true;
+}
+
 constexpr const char* kJitOptionsTag = "akgb-ew-jit-1 sm_100a c++17 fmad=false";
 
 struct JitKernel {
@@ -758,8 +863,60 @@ void jit_cache_stats(uint64_t* compiled, uint64_t* from_disk) {
   if (from_disk) *from_disk = g_n_from_disk;
 }
 
+// Column program: partial[splits, cols] (or the result itself when splits == 1); the caller folds the partials.
+int64_t col_jit_splits(const RowProgram& P, int sm_count) {
+  const int vw = P.cols % 8 == 0 ? 8 : 1;
+  const int64_t granules = (P.cols + vw - 1) / vw;
+  int tx = 1;
+  while (tx < 32 && tx < granules) tx <<= 1;
+  const int ty = 256 / tx;
+  const int64_t col_ctas = (granules + tx - 1) / tx;
+  const int64_t want = ((int64_t)sm_count * 8 + col_ctas - 1) / col_ctas;
+  const int64_t max_splits = std::max<int64_t>(1, P.rows / ((int64_t)ty * 4));
+  return std::max<int64_t>(1, std::min<int64_t>(std::min(want, max_splits), 1024));
+}
+
+cudaError_t col_jit_launch(const RowProgram& P, const void* const* in, float* partial, int64_t splits, cudaStream_t s,
+                           LaunchDims* dims) {
+  if (P.rows == 0 || P.cols == 0) return cudaSuccess;
+  bool vec = P.cols % 8 == 0;
+  for (size_t i = 0; i < P.in.size() && vec; ++i)
+    if (P.in[i].kind != RK_ROW && P.in[i].kind != RK_SCALAR) vec = aligned16(in[i]);
+  std::string src;
+  ColShape cs;
+  if (!col_generate(P, vec, &src, &cs)) return cudaErrorNotSupported;
+  JitKernel* k = compile(src, "akgb_col_jit");
+  if (!k || k->failed) return cudaErrorNotSupported;
+  const int64_t granules = (P.cols + cs.vw - 1) / cs.vw;
+  const int64_t gx = (granules + cs.tx - 1) / cs.tx;
+  if (gx > 0x7fffffff || splits > 65535) return cudaErrorNotSupported;
+  long long rows = P.rows, rps = (P.rows + splits - 1) / splits;
+  void* args[32];
+  const void* inp[16];
+  int a = 0;
+  for (size_t i = 0; i < P.in.size(); ++i) {
+    inp[i] = in[i];
+    args[a++] = &inp[i];
+  }
+  args[a++] = &partial;
+  args[a++] = &rows;
+  args[a++] = &rps;
+  if (dims) {
+    dims->grid[0] = (unsigned)gx;
+    dims->grid[1] = (unsigned)splits;
+    dims->block[0] = 256;
+  }
+  const CUresult r = driver().LaunchKernel(k->fn, (unsigned)gx, (unsigned)splits, 1, 256, 1, 1, 0, (CUstream)s, args, nullptr);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorLaunchFailure;
+}
+
 std::string row_jit_source(const RowProgram& P, bool vec) {
   std::string src;
+  if (P.col_reduce) {
+    ColShape cs;
+    if (!col_generate(P, vec, &src, &cs)) src.clear();
+    return src;
+  }
   RowShape rs;
   if (!row_generate(P, vec, &src, &rs)) src.clear();
   return src;

@@ -99,6 +99,10 @@ struct RowProgram {
   std::vector<int32_t> const_val;
   std::vector<uint32_t> const_bits;
   std::vector<uint8_t> val_full;  // per value: per element (1) or per row (0)
+  // column mode: the program's only reduction is its last op and folds the ROWS (axis 0 of [rows, cols]); the one
+  // result is [cols].  Generated as a kernel that walks rows and keeps 8 column accumulators per thread.
+  bool col_reduce = false;
+  int32_t col_red_op = 0;
 };
 
 }  // namespace akgb

@@ -773,6 +773,105 @@ bool fused_reduce_all_plan(const Graph& g, int sm_count, Plan* out) {
   return true;
 }
 
+// An elementwise chain that ends in a reduction over the LEADING axes: with the tensors viewed as [rows, cols] one
+// generated kernel walks the rows, runs the chain in registers and keeps column accumulators; partial results of the
+// row splits are folded by the hand-written column reduction.  Returns false when the region is not of that form.
+bool fused_reduce_col_plan(const Graph& g, int sm_count, Plan* out) {
+  if (g.dynamic || g.outputs.size() != 1 || g.nodes.size() < 2) return false;
+  const Node& red = g.nodes.back();
+  if (!opk_is_reduce(red.kind) || red.out != g.outputs[0]) return false;
+  RedOp op;
+  switch (red.kind) {
+    case OpK::ReduceSum: op = RedOp::Sum; break;
+    case OpK::ReduceMax: op = RedOp::Max; break;
+    case OpK::ReduceMin: op = RedOp::Min; break;
+    case OpK::ReduceProd: op = RedOp::Prod; break;
+    default: return false;
+  }
+  const Value& x = g.v(red.in[0]);
+  const size_t rank = x.shape.size(), k = red.axes.size();
+  if (k == 0 || k >= rank || x.dt != DT::F32 || g.v(red.out).dt != DT::F32) return false;
+  for (size_t i = 0; i < k; ++i)
+    if (red.axes[i] != (int64_t)i) return false;
+  int64_t R = 1, C = 1;
+  for (size_t i = 0; i < rank; ++i) (i < k ? R : C) *= x.shape[i];
+  if (R < 2 || C < 2 || R * C < (1 << 16) || g.v(red.out).numel() != C) return false;
+  const std::vector<int64_t> lead(x.shape.begin(), x.shape.begin() + k), trail(x.shape.begin() + k, x.shape.end());
+  auto strip = [](std::vector<int64_t> s) {
+    while (s.size() > 1 && s.front() == 1) s.erase(s.begin());
+    return s;
+  };
+  Graph g2 = g;
+  for (auto& v : g2.values) {
+    if (v.is_const) continue;
+    const int64_t n = v.numel();
+    if (&v == &g2.v(red.out)) {
+      v.shape = {C};
+    } else if (n == R * C && v.shape.size() == rank) {
+      v.shape = {R, C};
+    } else if (n == 1) {
+      v.shape = {1};
+    } else if (n == C && strip(v.shape) == strip(trail)) {
+      v.shape = {C};
+    } else if (n == R && v.shape.size() == rank && std::equal(lead.begin(), lead.end(), v.shape.begin())) {
+      v.shape = {R, 1};
+    } else {
+      return false;
+    }
+  }
+  for (size_t i = 0; i + 1 < g.nodes.size(); ++i) {
+    const Node& nd = g.nodes[i];
+    if (!opk_is_elementwise(nd.kind) || nd.kind == OpK::AddN || g.v(nd.out).output_index >= 0) return false;
+  }
+  Node& red2 = g2.nodes.back();
+  red2.axes = {0};
+  red2.keep_dims = false;
+  auto rp = std::make_shared<RowProgram>();
+  std::vector<int> in_values, out_values;
+  if (!build_row_program(g2, rp.get(), &in_values, &out_values, true)) return false;
+  const int64_t splits = col_jit_splits(*rp, sm_count);
+  Plan p;
+  p.klass = "reduce_y";
+  Step st;
+  st.kind = StepK::ColJit;
+  st.kernel_name = "akgb_col_jit";
+  st.row = rp;
+  st.red_len = splits;
+  for (int vid : in_values) {
+    Ref ref;
+    ref.arg = g.v(vid).input_index;
+    st.ew_in.push_back(ref);
+  }
+  Ref result;
+  result.arg = (int)g.inputs.size();
+  size_t ws = 0;
+  if (splits == 1) {
+    st.out = result;
+    p.steps.push_back(std::move(st));
+  } else {
+    Ref partial;
+    partial.ws_off = 0;
+    st.out = partial;
+    p.steps.push_back(std::move(st));
+    ws = ((size_t)(splits * C) * sizeof(float) + 255) / 256 * 256;
+    Step fin;
+    fin.kind = StepK::ReduceCol;
+    fin.kernel_name = "reduce_col_f32";
+    fin.red_op = op;
+    fin.red_outer = 1;
+    fin.red_len = splits;
+    fin.red_inner = C;
+    fin.a = partial;
+    fin.out = result;
+    fin.scratch.ws_off = (int64_t)ws;
+    ws += (reduce_col_workspace(splits, C, sm_count) + 255) / 256 * 256;
+    p.steps.push_back(std::move(fin));
+  }
+  p.workspace_bytes = ws;
+  *out = std::move(p);
+  return true;
+}
+
 Plan build_plan(const Graph& g, int sm_count, bool allow_jit) {
   for (auto& n : g.nodes)
     if (n.kind == OpK::Unknown)
@@ -821,7 +920,8 @@ Plan build_plan(const Graph& g, int sm_count, bool allow_jit) {
       fused.steps.push_back(std::move(st));
       fused.fallback = std::make_shared<Plan>(std::move(plan));
       plan = std::move(fused);
-    } else if (Plan fused; allow_jit && plan.steps.size() >= 2 && fused_reduce_all_plan(g, sm_count, &fused)) {
+    } else if (Plan fused; allow_jit && plan.steps.size() >= 2 &&
+               (fused_reduce_all_plan(g, sm_count, &fused) || fused_reduce_col_plan(g, sm_count, &fused))) {
       fused.workspace_bytes = std::max(fused.workspace_bytes, plan.workspace_bytes);
       fused.flops = plan.flops;
       fused.fallback = std::make_shared<Plan>(std::move(plan));

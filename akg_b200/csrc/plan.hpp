@@ -19,7 +19,7 @@ struct Ref {
   bool valid() const { return arg >= 0 || ws_off >= 0; }
 };
 
-enum class StepK : int { GeluChain, LayerNorm, Softmax, ReduceCol, ReduceAll, ReduceRow, ReduceColDual, Transpose, Matmul, Ew, Gather, SegmentSum, ArgMax, RowJit };
+enum class StepK : int { GeluChain, LayerNorm, Softmax, ReduceCol, ReduceAll, ReduceRow, ReduceColDual, Transpose, Matmul, Ew, Gather, SegmentSum, ArgMax, RowJit, ColJit };
 
 struct Step {
   StepK kind;
@@ -59,7 +59,8 @@ struct Plan {
 // Pattern matcher: places the region on kernel templates or throws Unsupported.
 Plan build_plan(const Graph& g, int sm_count, bool allow_jit = true);
 // Reduce-X regions as one row program (rowfuse.cpp); `in_values` / `out_values` receive the graph values of the operands.
-bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_values, std::vector<int>* out_values);
+bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_values, std::vector<int>* out_values,
+                       bool col_mode = false);
 // Fallback of build_plan: splits the region into elementwise groups (generic kernel), reductions, transposes and
 // matmuls that run one after the other with intermediates in the workspace.
 Plan build_generic_plan(const Graph& g, int sm_count);

@@ -31,7 +31,8 @@ std::vector<int64_t> strip_leading_ones(std::vector<int64_t> s) {
 
 }  // namespace
 
-bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_values, std::vector<int>* out_values) {
+bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_values, std::vector<int>* out_values,
+                       bool col_mode) {
   if (g.dynamic || g.nodes.empty()) return false;
   // the row shape comes from the first reduction
   const Node* first_red = nullptr;
@@ -43,6 +44,9 @@ bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_val
   if (!first_red) return false;
   const std::vector<int64_t>& S = g.v(first_red->in[0]).shape;
   if (S.empty()) return false;
+  if (col_mode && (S.size() != 2 || first_red != &g.nodes.back() || g.outputs.size() != 1 ||
+                   g.outputs[0] != first_red->out))
+    return false;  // column mode works on the caller's 2-D view: [rows, cols], one reduction over rows at the end
   const int64_t C = S.back();
   int64_t R = 1;
   for (size_t i = 0; i + 1 < S.size(); ++i) R *= S[i];
@@ -120,7 +124,29 @@ bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_val
     RowInstr ins;
     ins.dt = (uint8_t)ov.dt;
     ins.cls = cls_of(ov.dt);
-    if (opk_is_reduce(n.kind)) {
+    if (opk_is_reduce(n.kind) && col_mode) {
+      const Value& x = g.v(n.in[0]);
+      if (n.axes.size() != 1 || n.axes[0] != 0 || x.numel() != R * C || x.dt != DT::F32 || ov.dt != DT::F32 ||
+          ov.numel() != C)
+        return false;
+      int src = 0;
+      if (!operand(n.in[0], &src) || !P.val_full[src]) return false;
+      switch (n.kind) {
+        case OpK::ReduceSum: P.col_red_op = 0; break;
+        case OpK::ReduceMax: P.col_red_op = 1; break;
+        case OpK::ReduceMin: P.col_red_op = 2; break;
+        case OpK::ReduceProd: P.col_red_op = 3; break;
+        default: return false;
+      }
+      P.col_reduce = true;
+      RowOperand o;
+      o.dt = (int)DT::F32;
+      o.kind = RK_COL;
+      o.val = src;
+      P.out.push_back(o);
+      out_values->push_back(n.out);
+      break;  // the last node
+    } else if (opk_is_reduce(n.kind)) {
       const Value& x = g.v(n.in[0]);
       if (n.axes.size() != 1 || n.axes[0] != (int64_t)x.shape.size() - 1 || x.shape.back() != C || x.numel() != R * C)
         return false;
@@ -183,6 +209,7 @@ bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_val
     if (P.instr.size() > 160) return false;
   }
   for (int vid : g.outputs) {
+    if (col_mode) break;
     auto it = val_of.find(vid);
     const Value& v = g.v(vid);
     if (it == val_of.end() || v.producer < 0) return false;  // an input or constant passed through

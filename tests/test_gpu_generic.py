@@ -721,3 +721,39 @@ def test_reduce_x_regions_as_one_generated_kernel(lib, kind, rows_shape, cols, d
         assert "akgb_row_jit" in k.jit_source(cols % 8 == 0)
     else:
         assert k.launch_count > 1
+
+
+@pytest.mark.parametrize("shape,k,cols_kind", [
+    ([4096, 1024], 1, "plain"),       # dgamma-like: sum over rows of dy * xhat
+    ([8, 600, 768], 2, "with_col"),   # two leading axes folded, a [cols] operand in the chain
+    ([3000, 100], 1, "with_row"),     # cols not a multiple of 8, a per-row operand
+    ([70000, 8], 1, "max"),
+])
+def test_elementwise_chain_folded_into_a_reduction_over_leading_axes(lib, shape, k, cols_kind):
+    rng = np.random.default_rng(len(shape) * 100 + shape[-1])
+    f = "float32"
+    out_shape = shape[k:]
+    b = _Builder("Fused_Mul_ReduceSum_Y_97")
+    x = b.input("x", shape, f)
+    y = b.input("y", shape, f)
+    t = b.emit("Mul", [x, y], shape, f)
+    if cols_kind == "with_col":
+        g_ = b.input("g", out_shape, f)
+        t = b.emit("Add", [t, g_], shape, f)
+    if cols_kind == "with_row":
+        r_ = b.input("r", shape[:k] + [1] * (len(shape) - k), f)
+        t = b.emit("Sub", [t, r_], shape, f)
+    op = "ReduceMax" if cols_kind == "max" else "ReduceSum"
+    b.output(b.emit(op, [t], out_shape, f, _reduce_attr(list(range(k)), False)))
+    d = b.build()
+    ins = [rng.standard_normal(t_["shape"]).astype(np.float32) for (t_,) in d["input_desc"]]
+    got, kern = run(d, ins)
+    want = O.evaluate(d, ins, accum="float64")[0]
+    full = ins[0].astype(np.float64) * ins[1].astype(np.float64)
+    if cols_kind == "max":
+        assert bits_equal(got[0], want)
+    else:
+        bound = 1e-5 * np.abs(full).sum(axis=tuple(range(k))) + 1e-4 * (cols_kind != "plain") * np.prod(shape[:k])
+        assert np.all(np.abs(got[0].astype(np.float64) - want.astype(np.float64)) <= bound + 1e-6)
+    if FLAGS[0] == 0:
+        assert kern.meta()["template"] == "akgb_col_jit" and kern.launch_count <= 3
