@@ -137,7 +137,7 @@ def _to_copy(L, node, x, **kw):
     return L.emit("Cast", [x], node, [_attr("dst_type", "str", dt)])
 
 
-def _reshape(L, node, x, *_):
+def _reshape(L, node, x, *_, **__):
     return L.emit("Reshape", [x], node, [_attr("shape", "listInt", L.shape(node))])
 
 
@@ -333,10 +333,29 @@ def _native_layer_norm(x, normalized_shape, weight, bias, eps):
     return y.to(x.dtype), mean, rstd
 
 
+def _split(x, size, dim=0):
+    n = x.shape[dim]
+    return tuple(x.narrow(dim, s, min(size, n - s)) for s in range(0, n, size))
+
+
+def _split_with_sizes(x, sizes, dim=0):
+    out, s = [], 0
+    for z in sizes:
+        out.append(x.narrow(dim, s, z))
+        s += z
+    return tuple(out)
+
+
+_MATMULS = (aten.mm.default, aten.bmm.default, aten.addmm.default)
+_REDUCTIONS = (aten.sum.dim_IntList, aten.sum.default, aten.amax.default, aten.amin.default, aten.mean.dim)
+
+
 def _decompositions():
     from torch._decomp import get_decompositions
     table = _stock_decompositions()
     table[aten.native_layer_norm.default] = _native_layer_norm
+    table[aten.split.Tensor] = _split                       # pieces become slices the library takes
+    table[aten.split_with_sizes.default] = _split_with_sizes
     return table
 
 
@@ -427,6 +446,14 @@ def cluster_nodes(graph: fx.Graph) -> list[list[fx.Node]]:
                     stack.append(s)
         return False
 
+    # The counterpart of the reference's split stage (inductor.py "Mfuse Split"): a cluster holds at most one matmul
+    # (its bias / activation / cast run in the matmul's launch) and no reduction beside a matmul, so that LayerNorm-,
+    # softmax- and GELU-like parts stay regions of their own, each of which the library runs as one kernel.
+    def kind_counts(c):
+        mm = sum(1 for m in members[c] if m.target in _MATMULS)
+        red = sum(1 for m in members[c] if m.target in _REDUCTIONS)
+        return mm, red
+
     for n in nodes:
         if not ok[n]:
             continue
@@ -434,6 +461,9 @@ def cluster_nodes(graph: fx.Graph) -> list[list[fx.Node]]:
             if not ok[p] or cid[p] == cid[n]:
                 continue
             a, b = cid[p], cid[n]
+            (mm_a, red_a), (mm_b, red_b) = kind_counts(a), kind_counts(b)
+            if mm_a + mm_b > 1 or (mm_a + mm_b >= 1 and red_a + red_b >= 1):
+                continue
             if reaches_around(a, b):
                 continue
             for m in members[b]:
@@ -518,7 +548,7 @@ class AkgExecutor:
 
     def kernel(self, sub: FusedSubgraph, device: torch.device):
         from .driver import FusedKernel
-        key = (sub.name, device.index)
+        key = (sub.desc_json, device.index)  # the description itself: names repeat across programs
         k = self._kernels.get(key)
         if k is None:
             k = self._kernels[key] = FusedKernel(sub.desc_json, device=device.index if device.index is not None else -1)

@@ -50,6 +50,34 @@ def mixed(x, idx, y):
     return torch.where(g > 0.5, g, y) - 1.0, a.amax(dim=1)
 
 
+def transformer_block(x, ln1w, ln1b, wqkv, bqkv, wo, bo, ln2w, ln2b, w1, b1, w2, b2):
+    """Pre-norm attention + MLP block, 4 heads."""
+    import math
+    bsz, seq, dim = x.shape
+    heads = 4
+    h = torch.nn.functional.layer_norm(x, (dim,), ln1w, ln1b, 1e-5)
+    q, k, v = torch.nn.functional.linear(h, wqkv, bqkv).split(dim, dim=-1)
+    q, k, v = (t.reshape(bsz, seq, heads, dim // heads).permute(0, 2, 1, 3) for t in (q, k, v))
+    att = torch.softmax((q @ k.transpose(-1, -2)) * (1.0 / math.sqrt(dim // heads)), dim=-1)
+    o = (att @ v).permute(0, 2, 1, 3).reshape(bsz, seq, dim)
+    x = x + torch.nn.functional.linear(o, wo, bo)
+    h = torch.nn.functional.layer_norm(x, (dim,), ln2w, ln2b, 1e-5)
+    m = torch.nn.functional.gelu(torch.nn.functional.linear(h, w1, b1), approximate="tanh")
+    return x + torch.nn.functional.linear(m, w2, b2)
+
+
+def transformer_inputs(dtype, gen, bsz=2, seq=128, dim=256):
+    shapes = [(bsz, seq, dim), (dim,), (dim,), (3 * dim, dim), (3 * dim,), (dim, dim), (dim,), (dim,), (dim,),
+              (4 * dim, dim), (4 * dim,), (dim, 4 * dim), (dim,)]
+    ins = []
+    for i, s in enumerate(shapes):
+        t = torch.randn(s, generator=gen) * (1.0 if i == 0 else 0.05)
+        if i in (1, 7):
+            t = t + 1.0
+        ins.append(t.to(dtype))
+    return ins
+
+
 CASES = {
     "gelu_bias": (gelu_bias, lambda g: [torch.randn(4, 64, 128, generator=g), torch.randn(128, generator=g) * 0.02,
                                        torch.randn(4, 64, 128, generator=g)], 1e-5),
@@ -151,14 +179,15 @@ def test_bfloat16_linear_layers_on_the_device():
 
     ins = [(torch.randn(s, generator=g) * 0.1).bfloat16().cuda() for s in ((256, 128), (192, 128), (192,), (64, 192), (64,))]
     fused = TF.fuse_and_optimize(net, ins)
-    assert len(fused.subgraphs) == 1
-    names = [o["name"] for o in fused.subgraphs[0].desc["op_desc"]]
-    assert "Transpose" not in names and names.count("MatMul") == 2
+    assert len(fused.subgraphs) == 2  # one matmul per cluster
+    from akg_b200.driver import FusedKernel
+    for sub in fused.subgraphs:
+        names = [o["name"] for o in sub.desc["op_desc"]]
+        assert "Transpose" not in names and names.count("MatMul") == 1
+        assert FusedKernel(sub.desc_json).launch_count == 1
     got, want = fused(*ins), net(*ins)
     assert got.dtype == torch.bfloat16
     torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
-    from akg_b200.driver import FusedKernel
-    assert FusedKernel(fused.subgraphs[0].desc_json).launch_count == 2
 
 
 @pytest.mark.gpu
@@ -170,3 +199,30 @@ def test_fused_half_precision_chain_on_the_device():
     got, want = fused(*ins), gelu_bias(*ins)
     assert got.dtype == torch.float16
     torch.testing.assert_close(got.float(), want.float(), rtol=2e-3, atol=2e-3)
+
+
+def test_transformer_block_clusters():
+    """Every op of the block lands in a cluster; matmuls, LayerNorms, the softmax and the GELU get regions of their own."""
+    ins = transformer_inputs(torch.float32, torch.Generator().manual_seed(0))
+    fused = TF.fuse_and_optimize(transformer_block, ins, executor=oracle_executor)
+    assert fused.clustered_ops == fused.total_ops and len(fused.subgraphs) == 9
+    for sub in fused.subgraphs:
+        names = [o["name"] for o in sub.desc["op_desc"]]
+        n_mm = sum(n in ("MatMul", "BatchMatMul") for n in names)
+        n_red = sum(n.startswith("Reduce") for n in names)
+        assert n_mm <= 1 and not (n_mm and n_red)
+    _close(fused(*ins), transformer_block(*ins), 2e-4)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-4), (torch.bfloat16, 6e-2)])
+def test_transformer_block_on_the_device(dtype, tol):
+    ins = [t.cuda() for t in transformer_inputs(dtype, torch.Generator().manual_seed(5))]
+    fused = TF.fuse_and_optimize(transformer_block, ins)
+    assert fused.clustered_ops == fused.total_ops
+    got, want = fused(*ins), transformer_block(*ins)
+    assert got.dtype == dtype and got.shape == want.shape
+    torch.testing.assert_close(got.float(), want.float(), rtol=tol, atol=tol)
+    from akg_b200.driver import FusedKernel
+    launches = sum(FusedKernel(s.desc_json).launch_count for s in fused.subgraphs)
+    assert launches <= 22
