@@ -618,6 +618,20 @@ akgb_status akgb_check_device_error(akgb_kernel* k, uint32_t* word) {
   return AKGB_OK;
 }
 
+akgb_status akgb_prepare(akgb_kernel* k) {
+  if (!k) return fail(AKGB_INVALID_ARG, "null argument");
+  const cudaError_t e = cudaSetDevice(k->device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  akgb_status st = ensure_device_state(k, k->plan.needs_gelu_lut);
+  if (st != AKGB_OK) return st;
+  if (k->no_jit) return AKGB_OK;
+  for (const Step& step : active_plan(k).steps) {
+    if (step.kind == StepK::Ew) ew_jit_prepare(step.ew);
+    else if (step.kind == StepK::RowJit || step.kind == StepK::ColJit) row_jit_prepare(*step.row);
+  }
+  return AKGB_OK;
+}
+
 akgb_status akgb_set_cache_dir(const char* dir) {
   jit_set_cache_dir(dir);
   return AKGB_OK;

@@ -961,6 +961,24 @@ cudaError_t row_jit_launch(const RowProgram& P, const void* const* in, void* con
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorLaunchFailure;
 }
 
+// Compiles (or loads from the disk cache) the variant a launch on 16-byte aligned tensors will use, so that the first
+// launch does no compilation and no module load -- both are illegal while a stream is being captured into a graph.
+void ew_jit_prepare(const EwProgram& P) {
+  std::string src;
+  if (P.n > 0 && generate(P, P.n % 8 == 0, &src)) compile(src);
+}
+void row_jit_prepare(const RowProgram& P) {
+  std::string src;
+  const bool vec = P.cols % 8 == 0;
+  if (P.col_reduce) {
+    ColShape cs;
+    if (col_generate(P, vec, &src, &cs)) compile(src, "akgb_col_jit");
+  } else {
+    RowShape rs;
+    if (row_generate(P, vec, &src, &rs)) compile(src, "akgb_row_jit");
+  }
+}
+
 // The CUDA C++ text that would be compiled for this program (empty when the program needs the interpreter).
 std::string ew_jit_source(const EwProgram& P, bool vec) {
   std::string src;

@@ -87,6 +87,8 @@ std::string row_jit_source(const RowProgram& p, bool vec);
 int64_t col_jit_splits(const RowProgram& p, int sm_count);
 cudaError_t col_jit_launch(const RowProgram& p, const void* const* in, float* partial, int64_t splits, cudaStream_t s,
                            LaunchDims* dims);
+void ew_jit_prepare(const EwProgram& p);
+void row_jit_prepare(const RowProgram& p);
 void jit_set_cache_dir(const char* dir);  // nullptr: environment's choice; "": no disk cache
 void jit_cache_stats(uint64_t* compiled, uint64_t* from_disk);
 cudaError_t ew_jit_launch(const EwProgram& p, const void* const* in, void* const* out, cudaStream_t s, LaunchDims* dims);

@@ -116,6 +116,11 @@ class FusedKernel:
         _capi.check(self._lib.akgb_check_device_error(self._handle, ctypes.byref(word)))
         return int(word.value)
 
+    def prepare(self):
+        """``akgb_prepare``: device tables and generated kernels ahead of the first launch (needed before the launches
+        are captured into a CUDA graph)."""
+        _capi.check(self._lib.akgb_prepare(self._handle))
+
     # -- execution ----------------------------------------------------------------
     def launch_ptrs(self, ptrs: Sequence[int], workspace_ptr: int = 0, workspace_bytes: int = 0, stream: int = 0):
         """``akgb_launch`` on raw device addresses (inputs then outputs)."""

@@ -115,6 +115,12 @@ int32_t akgb_launch_count(const akgb_kernel* k);
 akgb_status akgb_launch(akgb_kernel* k, void* const* tensors, void* workspace,
                         size_t workspace_bytes, void* stream);
 
+/* Does ahead of time what the first akgb_launch would do lazily on the kernel's device: uploads the library's device
+ * tables and compiles (or loads from the on-disk cache) the kernels generated for this region.  Call it before
+ * capturing launches into a CUDA graph -- compilation and module loading are not allowed during capture.  The
+ * reference does all of this in compile_gpu (python/akg_mlir/mlir_driver.py:337-374), which needs no device. */
+akgb_status akgb_prepare(akgb_kernel* k);
+
 /* Dynamic-shape regions: descriptions whose extents contain -1 (the form MindSpore emits for unknown
  * dims; the reference handles them with its --gpu-dyn-opt pipeline and passes sizes and strides of every
  * tensor to the launcher, lib/Pipelines/GPUPipelines/GPUDynOpt.cpp:47-143,

@@ -757,3 +757,23 @@ def test_elementwise_chain_folded_into_a_reduction_over_leading_axes(lib, shape,
         assert np.all(np.abs(got[0].astype(np.float64) - want.astype(np.float64)) <= bound + 1e-6)
     if FLAGS[0] == 0:
         assert kern.meta()["template"] == "akgb_col_jit" and kern.launch_count <= 3
+
+
+def test_prepare_allows_capturing_the_first_launch(lib):
+    """After prepare() the first launch of a region with generated kernels can be recorded into a CUDA graph."""
+    import torch
+    d = _rows_region("rmsnorm", [64], 512)
+    k = FusedKernel(d, flags=FLAGS[0])
+    k.prepare()
+    x = torch.randn(64, 512, device="cuda")
+    g_ = torch.rand(512, device="cuda") + 0.5
+    out = torch.empty(64, 512, device="cuda")
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            k.launch([x, g_, out], torch.cuda.current_stream())
+        graph.replay()
+    torch.cuda.synchronize()
+    want = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-6) * g_
+    torch.testing.assert_close(out, want, rtol=1e-5, atol=1e-5)
