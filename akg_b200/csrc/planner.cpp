@@ -961,7 +961,22 @@ struct Builder {
   Plan run() {
     plan_reshapes();
     plan_matmul_epilogues();
-    for (size_t i = 0; i < g.nodes.size(); ++i) {
+    // Small elementwise ops on the region's inputs (a Cast of a bias vector, say) go first: between two ops of the
+    // large iteration shape they would close the open group and force its values through memory.
+    std::vector<size_t> order;
+    {
+      int64_t largest = 1;
+      for (auto& v : g.values) largest = std::max(largest, v.numel());
+      std::vector<size_t> later;
+      for (size_t i = 0; i < g.nodes.size(); ++i) {
+        const Node& n = g.nodes[i];
+        bool early = opk_is_elementwise(n.kind) && n.kind != OpK::AddN && g.v(n.out).numel() * 4 <= largest;
+        for (int vid : n.in) early = early && (g.v(vid).is_const || g.v(vid).input_index >= 0);
+        (early ? order : later).push_back(i);
+      }
+      order.insert(order.end(), later.begin(), later.end());
+    }
+    for (size_t i : order) {
       const Node& n = g.nodes[i];
       if (eaten.count((int)i)) continue;  // runs inside a matmul launch
       if (n.kind == OpK::Reshape && !reshape_copy.count((int)i)) continue;  // a view

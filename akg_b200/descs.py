@@ -103,17 +103,26 @@ GELU_C1 = 0.7978845608
 GELU_C2 = 0.5
 
 
-def gelu_chain(shape: Sequence[int], with_bias: bool = True, with_mul: bool = True, cast_f32: bool = True) -> dict:
-    """x f16[shape] (+ bias f16[shape[-1]]) -> tanh-GELU (* y f16[shape]) (-> f32); all math in f16."""
+def gelu_chain(shape: Sequence[int], with_bias: bool = True, with_mul: bool = True, cast_f32: bool = True,
+               f32_math: bool = False) -> dict:
+    """x f16[shape] (+ bias f16[shape[-1]]) -> tanh-GELU (* y f16[shape]) (-> f32); all math in f16, or, with
+    `f32_math`, the same tensors widened to float32 first and every op in float32 (same bytes moved)."""
     shape = list(shape)
-    b = _Builder("Fused_BiasAdd_Gelu_Mul_Cast_" + "x".join(map(str, shape)) + "_2")
+    b = _Builder("Fused_BiasAdd_Gelu_Mul_Cast_" + "x".join(map(str, shape)) + ("_f32math_2" if f32_math else "_2"))
     h = "float16"
     x = b.input("x", shape, h)
+    bias = b.input("bias", [shape[-1]], h) if with_bias else None
+    y = b.input("y", shape, h) if with_mul else None
+    if f32_math:
+        h = "float32"
+        widen = [_attr("dst_type", "str", h)]
+        x = b.emit("Cast", [x], shape, h, widen)
+        bias = b.emit("Cast", [bias], [shape[-1]], h, widen) if with_bias else None
+        y = b.emit("Cast", [y], shape, h, widen) if with_mul else None
+        cast_f32 = False
     t = x
     if with_bias:
-        bias = b.input("bias", [shape[-1]], h)
         t = b.emit("Add", [x, bias], shape, h)
-    y = b.input("y", shape, h) if with_mul else None
     a = b.emit("Mul", [t, t], shape, h)
     t3 = b.emit("Mul", [a, t], shape, h)
     bb = b.emit("Mul", [t3, b.const(GELU_C0, h)], shape, h)

@@ -206,6 +206,8 @@ def class_configs(world):
     cfgs = [
         ("layernorm_f32_8192x1024", descs.layernorm(8192 * w, 1024), {"gamma": "gamma", "beta": "beta"}),
         ("gelu_chain_f16_64x512x4096", descs.gelu_chain([64 * w, 512, 4096]), {"bias": "normal_small"}),
+        ("gelu_chain_f32math_64x512x4096", descs.gelu_chain([64 * w, 512, 4096], f32_math=True),
+         {"bias": "normal_small"}),
         ("masked_softmax_f16_256x2048x2048", descs.masked_softmax(256 * w, 2048, 2048), {"mask": "causal"}),
         ("reduce_sum_axis0_f32_65536x4096", descs.reduce_sum_axis0(65536 * w, 4096), {}),
         ("reduce_max_all_f32_65536x4096", descs.reduce_max_all(65536 * w, 4096), {}),
