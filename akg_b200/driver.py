@@ -237,8 +237,7 @@ class MlirDriver:
                  profiling_trails: int = 0, backend: str = "gpu", device: int = -1, **_ignored):
         if backend != "gpu":
             raise RuntimeError("Unsupported backend: " + backend + "!\n")
-        if dynamic_shape:
-            raise RuntimeError("dynamic shapes are not supported")
+        self.dynamic_shape = dynamic_shape
         self.kernel_name = kernel_name
         self.input_file = input_file
         self.output_dir = get_kernel_meta_path() if output_dir == "" else str(output_dir)
@@ -263,7 +262,17 @@ class MlirDriver:
     def run(self, input_for_mod, output_indexes=None):
         if self.kernel is None:
             raise RuntimeError("compile() must be called before run()")
-        if self.profiling_trails > 0:
+        if self.kernel.is_dynamic:
+            # extents come with the arrays (the reference passes them as extra kernel arguments,
+            # python/akg_mlir/utils/gen_runtime_code.py:39-58); device memory and copies through torch
+            import torch
+            dev = [torch.from_numpy(np.ascontiguousarray(a)).cuda() for a in input_for_mod]
+            self.kernel.launch(dev)
+            torch.cuda.synchronize()
+            for a, t, d in zip(input_for_mod, dev, self.kernel.tensors):
+                if d.is_output or d.written_in_place:
+                    a[...] = t.cpu().numpy()
+        elif self.profiling_trails > 0:
             self.last_profile_us = self.kernel.profile_host(input_for_mod, number=10, repeat=self.profiling_trails)
         else:
             self.kernel.run_host(input_for_mod)

@@ -71,3 +71,22 @@ def test_library_against_the_reference_values(name):
     kd.launch(dev_in + dev_out)
     torch.cuda.synchronize()
     _compare([t.cpu().numpy() for t in dev_out], want, desc)
+
+
+@pytest.mark.gpu
+def test_driver_runs_a_dynamic_shape_description_from_a_file(tmp_path):
+    """The host-side mirror of the reference driver on one of the reference's dynamic-shape descriptions: compile()
+    from the .info file, run() with host arrays whose extents bind the -1 dimensions."""
+    import json
+    from akg_b200 import MlirDriver
+    name = next(n for n in CASES if load_corpus(n)[1] is not None and n.startswith("Fused_Sub_Mul_Mul_Add_Softmax"))
+    desc, dyn, ins, want = load_corpus(name)
+    info = tmp_path / (dyn["op"] + ".info")
+    info.write_text(json.dumps(dyn))
+    drv = MlirDriver(dyn["op"], str(info), output_dir=str(tmp_path), dynamic_shape=True, backend="gpu")
+    drv.compile()
+    outs = [np.full(o.shape, np.nan, dtype=o.dtype) for o in want]
+    drv.run([a.copy() for a in ins] + outs)
+    _compare(outs, want, desc)
+    meta = json.loads((tmp_path / (dyn["op"] + ".json")).read_text())
+    assert meta["is_dynamic"] is True and meta["kernelName"] == dyn["op"] + "_kernel"
