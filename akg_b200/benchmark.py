@@ -28,6 +28,9 @@ CASES = {
     "colsum": (lambda s: descs.reduce_sum_axis0(s[0], s[1]), {}),
     "gmax": (lambda s: descs.reduce_max_all(s[0], s[1]), {}),
     "transpose": (lambda s: descs.transpose(s, [0, 2, 1, 3]), {}),
+    "rmsnorm": (lambda s: descs.rmsnorm(s[0], s[1]), {"g": "gamma"}),
+    "mulsum_rows": (lambda s: descs.mul_reduce_sum(s[0], s[1], [0]), {}),
+    "mulsum_all": (lambda s: descs.mul_reduce_sum(s[0], s[1], [0, 1]), {}),
     "matmul": (lambda s, dtype="bfloat16": descs.matmul_bias_relu(s[0], s[1], s[2], dtype=dtype),
                {"a": "normal_small", "b": "normal_small", "bias": "normal_small"}),
 }

@@ -214,6 +214,35 @@ def matmul_bias_relu(m: int, k: int, n: int, transpose_b: bool = False, with_bia
     return b.build()
 
 
+def rmsnorm(rows: int, cols: int, dtype: str = "float32", eps: float = 1e-6) -> dict:
+    """x[rows, cols] * rsqrt(mean(x^2) + eps) * g[cols]; float32 math, `dtype` in and out."""
+    f = "float32"
+    b = _Builder(f"Fused_RMSNorm_{rows}x{cols}_9")
+    x = b.input("x", [rows, cols], dtype)
+    g = b.input("g", [cols], f)
+    xf = x if dtype == f else b.emit("Cast", [x], [rows, cols], f, [_attr("dst_type", "str", f)])
+    ss = b.emit("ReduceSum", [b.emit("Mul", [xf, xf], [rows, cols], f)], [rows, 1], f, _reduce_attr([1], True))
+    ms = b.emit("RealDiv", [ss, b.const(float(cols), f)], [rows, 1], f)
+    r = b.emit("Rsqrt", [b.emit("Add", [ms, b.const(eps, f)], [rows, 1], f)], [rows, 1], f)
+    y = b.emit("Mul", [b.emit("Mul", [xf, r], [rows, cols], f), g], [rows, cols], f)
+    if dtype != f:
+        y = b.emit("Cast", [y], [rows, cols], dtype, [_attr("dst_type", "str", dtype)])
+    b.output(y)
+    return b.build()
+
+
+def mul_reduce_sum(rows: int, cols: int, axes: Sequence[int]) -> dict:
+    """sum over `axes` of x * y, both float32[rows, cols] (the shape of bias / scale gradients)."""
+    f = "float32"
+    axes = list(axes)
+    b = _Builder(f"Fused_Mul_ReduceSum_{rows}x{cols}_" + "".join(map(str, axes)) + "_10")
+    x = b.input("x", [rows, cols], f)
+    y = b.input("y", [rows, cols], f)
+    out = [1] if len(axes) == 2 else ([cols] if axes == [0] else [rows])
+    b.output(b.emit("ReduceSum", [b.emit("Mul", [x, y], [rows, cols], f)], out, f, _reduce_attr(axes, False)))
+    return b.build()
+
+
 def transpose(shape: Sequence[int], perm: Sequence[int], dtype: str = "float16") -> dict:
     shape, perm = list(shape), list(perm)
     b = _Builder("Fused_Transpose_" + "x".join(map(str, shape)) + "_8")
