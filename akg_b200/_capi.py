@@ -74,6 +74,7 @@ class UnsupportedError(AkgbError):
 _lib = None
 
 COMM_ID_BYTES = 128
+COMM_HANDLE_BYTES = 64
 
 # every symbol include/akgb.h declares: (name, restype, argtypes)
 _vp = ctypes.c_void_p
@@ -101,6 +102,11 @@ _SIGNATURES = [
     ("akgb_comm_wrap", ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
                                       ctypes.POINTER(ctypes.c_void_p)]),
     ("akgb_comm_destroy", None, [ctypes.c_void_p]),
+    ("akgb_comm_create_local", ctypes.c_int, [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(ctypes.c_void_p)]),
+    ("akgb_comm_set_peer_exchange", ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32]),
+    ("akgb_comm_exchange_handle", ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]),
+    ("akgb_comm_attach_peers", ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]),
+    ("akgb_comm_set_timeout_ms", ctypes.c_int, [ctypes.c_void_p, ctypes.c_double]),
     ("akgb_allreduce_partials", ctypes.c_int, [_vp, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]),
     ("akgb_launch_sharded", ctypes.c_int, [_vp, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p,
                                            ctypes.c_size_t, ctypes.c_void_p]),

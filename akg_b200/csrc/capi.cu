@@ -368,6 +368,11 @@ akgb_status stage(akgb_kernel* k) {
 
 }  // namespace
 
+uint32_t* akgb::kernel_error_word(akgb_kernel* k) {
+  if (!k || ensure_device_state(k, false) != AKGB_OK) return nullptr;
+  return g_dev[k->device].err_word;
+}
+
 extern "C" {
 
 const char* akgb_last_error(void) { return g_err.c_str(); }

@@ -93,7 +93,30 @@ struct akgb_comm {
   ncclComm_t comm = nullptr;
   int rank = 0, world = 1, device = 0;
   bool owned = false;
+  // exchange over peer memory (k_exchange.cu)
+  void* local_buf = nullptr;               // this rank's exchange buffer (cudaMalloc)
+  void* peer_buf[kExchangeMaxRanks] = {};  // every rank's buffer as mapped into this process
+  bool peers_ready = false;
+  double timeout_ms = 1000.0;
+  int clock_khz = 0;
 };
+
+namespace {
+akgb_status cuda_fail_comm(cudaError_t e, const char* what) {
+  set_last_error((std::string(what) + ": " + cudaGetErrorString(e)).c_str());
+  return AKGB_CUDA_ERROR;
+}
+akgb_status ensure_local_buffer(akgb_comm* c) {
+  if (c->local_buf) return AKGB_OK;
+  cudaError_t e = cudaSetDevice(c->device);
+  if (e != cudaSuccess) return cuda_fail_comm(e, "cudaSetDevice");
+  e = cudaMalloc(&c->local_buf, kExchangeBytes);
+  if (e != cudaSuccess) return cuda_fail_comm(e, "cudaMalloc (exchange buffer)");
+  e = cudaMemset(c->local_buf, 0, kExchangeBytes);
+  if (e != cudaSuccess) return cuda_fail_comm(e, "cudaMemset (exchange buffer)");
+  return AKGB_OK;
+}
+}  // namespace
 
 extern "C" {
 
@@ -169,8 +192,109 @@ akgb_status akgb_comm_wrap(void* nccl_comm, int32_t rank, int32_t world, akgb_co
 
 void akgb_comm_destroy(akgb_comm* c) {
   if (!c) return;
+  if (c->local_buf) {
+    cudaSetDevice(c->device);
+    cudaDeviceSynchronize();
+    for (int q = 0; q < c->world && q < kExchangeMaxRanks; ++q)
+      if (c->peer_buf[q] && c->peer_buf[q] != c->local_buf) cudaIpcCloseMemHandle(c->peer_buf[q]);
+    cudaFree(c->local_buf);
+  }
   if (c->owned && c->comm) nccl().CommDestroy(c->comm);
   delete c;
+}
+
+akgb_status akgb_comm_exchange_handle(akgb_comm* c, void* handle, size_t cap) {
+  if (!c || !handle || cap < AKGB_COMM_HANDLE_BYTES) {
+    set_last_error("akgb_comm_exchange_handle: buffer of AKGB_COMM_HANDLE_BYTES bytes required");
+    return AKGB_INVALID_ARG;
+  }
+  static_assert(sizeof(cudaIpcMemHandle_t) <= AKGB_COMM_HANDLE_BYTES, "handle size");
+  const akgb_status st = ensure_local_buffer(c);
+  if (st != AKGB_OK) return st;
+  cudaIpcMemHandle_t h;
+  const cudaError_t e = cudaIpcGetMemHandle(&h, c->local_buf);
+  if (e != cudaSuccess) return cuda_fail_comm(e, "cudaIpcGetMemHandle");
+  std::memset(handle, 0, AKGB_COMM_HANDLE_BYTES);
+  std::memcpy(handle, &h, sizeof(h));
+  return AKGB_OK;
+}
+
+akgb_status akgb_comm_attach_peers(akgb_comm* c, const void* handles, size_t bytes) {
+  if (!c) {
+    set_last_error("akgb_comm_attach_peers: null communicator");
+    return AKGB_INVALID_ARG;
+  }
+  if (c->world > kExchangeMaxRanks) {
+    set_last_error("akgb_comm_attach_peers: more than 8 ranks");
+    return AKGB_UNSUPPORTED;
+  }
+  const akgb_status st = ensure_local_buffer(c);
+  if (st != AKGB_OK) return st;
+  if (!handles) {
+    // loop-back: every slot owner is this process (single-rank use, and the bounded-wait test: with world > 1 the other
+    // ranks' flags are never raised)
+    for (int q = 0; q < c->world; ++q) c->peer_buf[q] = c->local_buf;
+    c->peers_ready = true;
+    return AKGB_OK;
+  }
+  if (bytes < (size_t)c->world * AKGB_COMM_HANDLE_BYTES) {
+    set_last_error("akgb_comm_attach_peers: one handle of AKGB_COMM_HANDLE_BYTES bytes per rank required");
+    return AKGB_INVALID_ARG;
+  }
+  for (int q = 0; q < c->world; ++q) {
+    if (q == c->rank) {
+      c->peer_buf[q] = c->local_buf;
+      continue;
+    }
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, static_cast<const char*>(handles) + (size_t)q * AKGB_COMM_HANDLE_BYTES, sizeof(h));
+    const cudaError_t e = cudaIpcOpenMemHandle(&c->peer_buf[q], h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      c->peer_buf[q] = nullptr;
+      return cuda_fail_comm(e, "cudaIpcOpenMemHandle");  // peers_ready stays false: NCCL carries the exchange
+    }
+  }
+  c->peers_ready = true;
+  return AKGB_OK;
+}
+
+akgb_status akgb_comm_create_local(int32_t rank, int32_t world, int32_t device, akgb_comm** out) {
+  if (!out || world < 1 || world > kExchangeMaxRanks || rank < 0 || rank >= world) {
+    set_last_error("akgb_comm_create_local: bad arguments (1..8 ranks)");
+    return AKGB_INVALID_ARG;
+  }
+  if (device < 0) cudaGetDevice(&device);
+  akgb_comm* k = new akgb_comm;
+  k->rank = rank;
+  k->world = world;
+  k->device = device;
+  *out = k;
+  return AKGB_OK;
+}
+
+akgb_status akgb_comm_set_peer_exchange(akgb_comm* c, int32_t enabled) {
+  if (!c) {
+    set_last_error("akgb_comm_set_peer_exchange: null communicator");
+    return AKGB_INVALID_ARG;
+  }
+  if (enabled) {
+    for (int q = 0; q < c->world; ++q)
+      if (c->world > kExchangeMaxRanks || !c->peer_buf[q]) {
+        set_last_error("akgb_comm_set_peer_exchange: the peers' buffers are not attached");
+        return AKGB_INVALID_ARG;
+      }
+  }
+  c->peers_ready = enabled != 0;
+  return AKGB_OK;
+}
+
+akgb_status akgb_comm_set_timeout_ms(akgb_comm* c, double ms) {
+  if (!c || !(ms > 0.0)) {
+    set_last_error("akgb_comm_set_timeout_ms: bad arguments");
+    return AKGB_INVALID_ARG;
+  }
+  c->timeout_ms = ms;
+  return AKGB_OK;
 }
 
 akgb_status akgb_allreduce_partials(const akgb_kernel* k, akgb_comm* c, void* const* tensors, void* stream) {
@@ -181,6 +305,8 @@ akgb_status akgb_allreduce_partials(const akgb_kernel* k, akgb_comm* c, void* co
   const int n = akgb_num_tensors(k);
   Nccl& lib = nccl();
   int pending = 0;
+  ExchangeArgs xa;
+  size_t xtotal = 0;
   for (int i = 0; i < n; ++i) {
     akgb_tensor_desc d;
     if (akgb_tensor_info(k, i, &d) != AKGB_OK) return AKGB_INVALID_ARG;
@@ -193,13 +319,28 @@ akgb_status akgb_allreduce_partials(const akgb_kernel* k, akgb_comm* c, void* co
       case AKGB_PARTIAL_PROD: op = kNcclProd; break;
       default: set_last_error("unknown shard kind"); return AKGB_INVALID_ARG;
     }
+    size_t count = 1;
+    for (int r = 0; r < d.rank; ++r) count *= (size_t)d.shape[r];
+    if (c->peers_ready && d.dtype == AKGB_FLOAT32 && xa.n_seg < kExchangeMaxSegs &&
+        xtotal + count <= (size_t)kExchangeSlotElems) {
+      // small float32 partials: they all travel in one kernel over the ranks' mapped buffers (after this loop)
+      xa.seg_count[xa.n_seg] = (int)count;
+      xa.seg_op[xa.n_seg] = (int)(op == kNcclSum ? RedOp::Sum : op == kNcclMax ? RedOp::Max : op == kNcclMin ? RedOp::Min : RedOp::Prod);
+      xa.seg_ptr[xa.n_seg] = static_cast<float*>(tensors[i]);
+      ++xa.n_seg;
+      xtotal += count;
+      continue;
+    }
+    if (!c->comm) {
+      set_last_error("akgb_allreduce_partials: this communicator has no NCCL handle and the tensor does not fit the "
+                     "peer-memory exchange (float32, at most 16384 elements, peers attached)");
+      return AKGB_UNSUPPORTED;
+    }
     const int ty = nccl_type(d.dtype);
     if (ty < 0) {
       set_last_error("akgb_allreduce_partials: element type has no NCCL counterpart");
       return AKGB_UNSUPPORTED;
     }
-    size_t count = 1;
-    for (int r = 0; r < d.rank; ++r) count *= (size_t)d.shape[r];
     if (pending++ == 0) lib.GroupStart();
     const int rc = lib.AllReduce(tensors[i], tensors[i], count, ty, op, c->comm, static_cast<cudaStream_t>(stream));
     if (rc != kNcclSuccess) {
@@ -210,6 +351,21 @@ akgb_status akgb_allreduce_partials(const akgb_kernel* k, akgb_comm* c, void* co
   if (pending) {
     const int rc = lib.GroupEnd();
     if (rc != kNcclSuccess) return nccl_fail(rc, "ncclGroupEnd");
+  }
+  if (xa.n_seg) {
+    for (int q = 0; q < c->world; ++q) xa.peer[q] = c->peer_buf[q];
+    xa.rank = c->rank;
+    xa.world = c->world;
+    if (c->clock_khz == 0) {  // queried once: this attribute is slow to read
+      int khz = 0;
+      cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, c->device);
+      c->clock_khz = khz > 0 ? khz : 1500000;
+    }
+    xa.limit_cycles = (long long)(c->timeout_ms * c->clock_khz);
+    xa.err = kernel_error_word(const_cast<akgb_kernel*>(k));
+    if (!xa.err) return AKGB_CUDA_ERROR;
+    const cudaError_t e = exchange_allreduce(xa, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail_comm(e, "exchange_allreduce");
   }
   return AKGB_OK;
 }

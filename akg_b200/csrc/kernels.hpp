@@ -93,6 +93,43 @@ void jit_set_cache_dir(const char* dir);  // nullptr: environment's choice; "": 
 void jit_cache_stats(uint64_t* compiled, uint64_t* from_disk);
 cudaError_t ew_jit_launch(const EwProgram& p, const void* const* in, void* const* out, cudaStream_t s, LaunchDims* dims);
 
+// ---- exchange over peer memory -----------------------------------------------------------------
+// Layout of one rank's exchange buffer: [2 parities][kExchangeMaxRanks slots][kExchangeSlotElems floats], then the flags
+// [2][kExchangeMaxRanks][kExchangeMaxCtas] uint32.
+constexpr int kExchangeMaxRanks = 8, kExchangeSlotElems = 16384, kExchangeMaxCtas = 16;
+constexpr size_t kExchangeDataBytes = (size_t)2 * kExchangeMaxRanks * kExchangeSlotElems * sizeof(float);
+constexpr size_t kExchangeFlagBytes = (size_t)2 * kExchangeMaxRanks * kExchangeMaxCtas * sizeof(uint32_t);
+// after the flags: the call counter (epoch) and the ticket that lets the last CTA of a call advance it
+constexpr size_t kExchangeBytes = kExchangeDataBytes + kExchangeFlagBytes + 2 * sizeof(uint32_t);
+__host__ __device__ inline float* exchange_slot(void* base, int parity, int rank) {
+  return reinterpret_cast<float*>(base) + ((size_t)parity * kExchangeMaxRanks + rank) * kExchangeSlotElems;
+}
+__host__ __device__ inline uint32_t* exchange_flag(void* base, int parity, int rank, int cta) {
+  return reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(base) + kExchangeDataBytes) +
+         ((size_t)parity * kExchangeMaxRanks + rank) * kExchangeMaxCtas + cta;
+}
+__host__ __device__ inline uint32_t* exchange_counter(void* base) {
+  return reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(base) + kExchangeDataBytes + kExchangeFlagBytes);
+}
+struct ExchangeArgs {
+  void* peer[kExchangeMaxRanks];  // every rank's exchange buffer as mapped here; peer[rank] is this rank's own
+  int rank = 0, world = 1;
+  long long limit_cycles = 0;     // bound of the wait for the peers' flags
+  // up to kExchangeMaxSegs tensors travel in one call, one after the other in the slot
+  int n_seg = 0;
+  int seg_count[4] = {0, 0, 0, 0};
+  int seg_op[4] = {0, 0, 0, 0};   // RedOp
+  float* seg_ptr[4] = {nullptr, nullptr, nullptr, nullptr};
+  uint32_t* err = nullptr;
+};
+constexpr int kExchangeMaxSegs = 4;
+cudaError_t exchange_allreduce(const ExchangeArgs& a, cudaStream_t s);
+}  // namespace akgb
+struct akgb_kernel;
+namespace akgb {
+// the device error word of the kernel's device (allocated on first use); nullptr on failure
+uint32_t* kernel_error_word(akgb_kernel* k);
+
 // ---- index ops ---------------------------------------------------------------------
 // out[o, i, r] = data[o, idx[i], r]; data is [outer, dim, inner] elements of `esize` bytes; idx int32 or int64
 cudaError_t gather_rows(const void* data, const void* idx, void* out, int64_t outer, int64_t dim, int64_t nidx,

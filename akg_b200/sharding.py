@@ -66,13 +66,50 @@ class Communicator:
     creates the id, a broadcast carries its 128 bytes); after that the data path does not go through torch:
     `launch_sharded` enqueues the kernel and the all-reduce of its partial outputs on one stream."""
 
-    def __init__(self, id_bytes: bytes, rank: int, world: int, device: int = -1):
+    def __init__(self, id_bytes: bytes | None, rank: int, world: int, device: int = -1):
+        """`id_bytes` None: a communicator without NCCL (``akgb_comm_create_local``), peer-memory exchange only."""
         import ctypes
         self._lib = _capi.load()
         self._handle = ctypes.c_void_p()
-        buf = ctypes.create_string_buffer(bytes(id_bytes), _capi.COMM_ID_BYTES)
-        _capi.check(self._lib.akgb_comm_create(buf, rank, world, device, ctypes.byref(self._handle)))
+        if id_bytes is None:
+            _capi.check(self._lib.akgb_comm_create_local(rank, world, device, ctypes.byref(self._handle)))
+        else:
+            buf = ctypes.create_string_buffer(bytes(id_bytes), _capi.COMM_ID_BYTES)
+            _capi.check(self._lib.akgb_comm_create(buf, rank, world, device, ctypes.byref(self._handle)))
         self.rank, self.world = rank, world
+        self.peer_exchange = False
+
+    def attach_loopback(self):
+        """Peer-memory exchange with every slot owner mapped to this rank's own buffer (single-rank use, tests)."""
+        _capi.check(self._lib.akgb_comm_attach_peers(self._handle, None, 0))
+        self.peer_exchange = True
+
+    def set_timeout_ms(self, ms: float):
+        _capi.check(self._lib.akgb_comm_set_timeout_ms(self._handle, float(ms)))
+
+    def enable_peer_exchange(self, group=None) -> bool:
+        """Maps the exchange buffers of all ranks of the (initialised) process group into one another; small float32
+        partials then go through one kernel over NVLink instead of NCCL.  All ranks end up on the same path: if the
+        mapping fails anywhere it is turned off everywhere.  Returns whether it is on."""
+        import ctypes
+        import torch
+        import torch.distributed as dist
+        on_gpu = dist.get_backend(group) == "nccl"
+        dev = torch.device("cuda", torch.cuda.current_device()) if on_gpu else torch.device("cpu")
+        h = ctypes.create_string_buffer(_capi.COMM_HANDLE_BYTES)
+        ok = self._lib.akgb_comm_exchange_handle(self._handle, h, _capi.COMM_HANDLE_BYTES) == _capi.AKGB_OK
+        mine = torch.frombuffer(bytearray(h.raw), dtype=torch.uint8).to(dev)
+        parts = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(parts, mine, group=group)
+        blob = b"".join(p.cpu().numpy().tobytes() for p in parts)
+        if ok:
+            ok = self._lib.akgb_comm_attach_peers(self._handle, blob, len(blob)) == _capi.AKGB_OK
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        self.peer_exchange = bool(flag.item())
+        if ok and not self.peer_exchange:
+            self._lib.akgb_comm_set_peer_exchange(self._handle, 0)
+        return self.peer_exchange
 
     @staticmethod
     def unique_id() -> bytes:

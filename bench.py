@@ -245,7 +245,9 @@ def run_classes(rank, world, device, steps, warmup, hbm_peak, tf_peak, barrier, 
 
         class _K:  # adapter so that time_launches includes the exchange step
             launch = staticmethod(step_launch)
-        ms = time_launches(_K, sets, steps, warmup, barrier, use_graph=not (partial and world > 1))
+        # NCCL calls are not captured; the library's own exchange kernel is an ordinary kernel and is
+        graphable = not (partial and world > 1) or (comm is not None and comm.peer_exchange)
+        ms = time_launches(_K, sets, steps, warmup, barrier, use_graph=graphable)
         ms_max = allreduce_max_scalar(ms, world)
         row = {"class": k.op_class, "ms": round(ms_max, 5), "launches_per_step": k.launch_count}
         if k.flops:
@@ -298,6 +300,8 @@ def gpu_arm(args):
             # the library's own communicator carries the exchange step of the sharded reductions
             from akg_b200.sharding import Communicator
             comm = Communicator.from_process_group(device=local)
+            if os.environ.get("AKGB_BENCH_NCCL_ONLY", "") != "1":
+                comm.enable_peer_exchange()  # small partials: one kernel over the ranks' mapped buffers
         finally:
             sys.stdout.flush()
             os.dup2(saved_stdout, 1)

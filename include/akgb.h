@@ -174,6 +174,24 @@ akgb_status akgb_comm_create(const void* id, int32_t rank, int32_t world, int32_
 /* Uses a communicator the caller already has (an ncclComm_t); it is not destroyed by akgb_comm_destroy. */
 akgb_status akgb_comm_wrap(void* nccl_comm, int32_t rank, int32_t world, akgb_comm** out);
 void akgb_comm_destroy(akgb_comm* c);
+/* Optional faster exchange for small float32 partials (up to 16 384 elements, up to 8 ranks on one box): every rank
+ * exports a handle of its exchange buffer, the caller gathers the handles of all ranks (rank order) and hands them to
+ * every rank; from then on akgb_allreduce_partials uses one kernel over the mapped buffers (peer stores over NVLink, a
+ * flag per rank, a fold in rank order) instead of NCCL for such tensors.  The wait for the other ranks is bounded
+ * (akgb_comm_set_timeout_ms, default 1000): on expiry bit 8 of the device error word is set (akgb_check_device_error),
+ * the output is left as it was and the context stays usable.  `handles` == NULL attaches the rank's own buffer for every
+ * rank (single-rank use).  If a peer's buffer cannot be mapped the call fails and NCCL keeps carrying the exchange. */
+#define AKGB_COMM_HANDLE_BYTES 64
+/* A communicator without NCCL (1..8 ranks of one box): only the peer-memory exchange below is available; a partial it
+ * cannot carry makes akgb_allreduce_partials return AKGB_UNSUPPORTED. */
+akgb_status akgb_comm_create_local(int32_t rank, int32_t world, int32_t device, akgb_comm** out);
+/* Turns the peer-memory exchange off (or on again once all buffers are attached): every rank must use the same path, so
+ * a caller whose attach failed on some rank turns it off on all of them. */
+akgb_status akgb_comm_set_peer_exchange(akgb_comm* c, int32_t enabled);
+akgb_status akgb_comm_exchange_handle(akgb_comm* c, void* handle, size_t cap);
+akgb_status akgb_comm_attach_peers(akgb_comm* c, const void* handles, size_t bytes);
+akgb_status akgb_comm_set_timeout_ms(akgb_comm* c, double ms);
+
 /* All-reduces, in place and on `stream`, every tensor of `tensors` (inputs then outputs, device pointers) whose
  * shard_kind is a partial; one NCCL group for all of them.  No-op for kernels without partial outputs. */
 akgb_status akgb_allreduce_partials(const akgb_kernel* k, akgb_comm* c, void* const* tensors, void* stream);

@@ -34,6 +34,28 @@ def main():
         want = ref(x)
         got = out.cpu().double().reshape(want.shape)
         ok = ok and bool(torch.allclose(got, want.double(), rtol=1e-5, atol=1e-5 * float(x.abs().sum(0).max())))
+    # the same reductions with the exchange over the ranks' mapped buffers instead of NCCL
+    peer = comm.enable_peer_exchange()
+    if peer:
+        for build, ref in ((descs.reduce_sum_axis0, lambda t: t.double().sum(0)),
+                           (descs.reduce_max_all, lambda t: t.max().reshape(1)),
+                           (descs.reduce_sum_and_max, None)):
+            k = FusedKernel(build(rows, cols), device=local, shard_rank=rank, shard_world=world)
+            outs = [torch.empty(t.shape, dtype=torch.float32, device="cuda") for t in k.outputs]
+            for _ in range(5):  # several epochs, both parities
+                comm.launch_sharded(k, [mine] + outs)
+            torch.cuda.synchronize()
+            ok = ok and k.check_device_error() == 0
+            wants = [ref(x)] if ref else [x.double().sum(0), x.max().reshape(1)]
+            for o, w in zip(outs, wants):
+                ok = ok and bool(torch.allclose(o.cpu().double().reshape(w.shape), w.double(), rtol=1e-5,
+                                                atol=1e-5 * float(x.abs().sum(0).max())))
+        # every rank holds the same bits
+        gathered = [torch.empty_like(outs[0]) for _ in range(world)]
+        dist.all_gather(gathered, outs[0])
+        ok = ok and all(bool(torch.equal(g, gathered[0])) for g in gathered)
+    if rank == 0:
+        print("PEER_EXCHANGE", "on" if peer else "off", flush=True)
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     comm.close()

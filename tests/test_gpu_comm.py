@@ -49,6 +49,54 @@ def test_partials_all_reduce_on_a_one_rank_communicator():
 
 
 @pytest.mark.gpu
+def test_peer_memory_exchange_on_one_rank_and_its_bounded_wait():
+    """The one-kernel exchange with every slot mapped to this rank's own buffer, then a two-rank communicator whose
+    second rank never arrives: the wait runs out, the error word reports it, the output is untouched and the device
+    keeps working."""
+    import ctypes
+    import torch
+    from akg_b200 import FusedKernel, descs
+    from akg_b200.sharding import Communicator
+    lib = _capi.load()
+    k = FusedKernel(descs.reduce_sum_axis0(512, 300), device=0, shard_rank=0, shard_world=2)
+    x = torch.randn(256, 300, device="cuda")
+    want = x.double().sum(0).cpu()
+    # one rank: the fold over a single slot returns the partial itself
+    solo = Communicator(None, 0, 1, 0)
+    solo.attach_loopback()
+    out = torch.empty(300, device="cuda")
+    for _ in range(3):  # both parities of the exchange buffer
+        solo.launch_sharded(k, [x, out])
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out.double().cpu(), want, rtol=1e-5, atol=1e-4)
+    assert k.check_device_error() == 0
+    # two ranks, nobody plays rank 1: its flag is never raised
+    lonely = Communicator(None, 0, 2, 0)
+    lonely.attach_loopback()
+    lonely.set_timeout_ms(50.0)
+    out2 = torch.full((300,), float("nan"), device="cuda")
+    lonely.launch_sharded(k, [x, out2])
+    torch.cuda.synchronize()
+    word = ctypes.c_uint32(0)
+    status = lib.akgb_check_device_error(k._handle, ctypes.byref(word))
+    assert status == _capi.AKGB_DEVICE_TIMEOUT and word.value & 256
+    torch.testing.assert_close(out2.double().cpu(), want, rtol=1e-5, atol=1e-4)  # the partial, not folded
+    # the device and the library keep working
+    solo.launch_sharded(k, [x, out])
+    torch.cuda.synchronize()
+    assert k.check_device_error() == 0
+    torch.testing.assert_close(out.double().cpu(), want, rtol=1e-5, atol=1e-4)
+    # a communicator without NCCL refuses what the exchange cannot carry
+    big = FusedKernel(descs.reduce_sum_axis0(512, 32768), device=0, shard_rank=0, shard_world=2)
+    xb = torch.randn(256, 32768, device="cuda")
+    ob = torch.empty(32768, device="cuda")
+    with pytest.raises(_capi.UnsupportedError):
+        solo.launch_sharded(big, [xb, ob])
+    solo.close()
+    lonely.close()
+
+
+@pytest.mark.gpu
 def test_two_ranks_reduce_through_the_communicator():
     import torch
     if torch.cuda.device_count() < 2:
