@@ -84,6 +84,11 @@ class Communicator:
         _capi.check(self._lib.akgb_comm_attach_peers(self._handle, None, 0))
         self.peer_exchange = True
 
+    def disable_peer_exchange(self):
+        """Back to NCCL for every partial (all ranks must do the same)."""
+        _capi.check(self._lib.akgb_comm_set_peer_exchange(self._handle, 0))
+        self.peer_exchange = False
+
     def set_timeout_ms(self, ms: float):
         _capi.check(self._lib.akgb_comm_set_timeout_ms(self._handle, float(ms)))
 

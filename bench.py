@@ -248,6 +248,15 @@ def run_classes(rank, world, device, steps, warmup, hbm_peak, tf_peak, barrier, 
         # NCCL calls are not captured; the library's own exchange kernel is an ordinary kernel and is
         graphable = not (partial and world > 1) or (comm is not None and comm.peer_exchange)
         ms = time_launches(_K, sets, steps, warmup, barrier, use_graph=graphable)
+        if partial and comm is not None and comm.peer_exchange:
+            # a bounded wait of the exchange kernel that ran out on any rank: NCCL carries the exchange from here on
+            try:
+                bad = 1 if k.check_device_error() else 0
+            except Exception:
+                bad = 1
+            if allreduce_max_scalar(float(bad), world) > 0:
+                comm.disable_peer_exchange()
+                ms = time_launches(_K, sets, steps, warmup, barrier, use_graph=False)
         ms_max = allreduce_max_scalar(ms, world)
         row = {"class": k.op_class, "ms": round(ms_max, 5), "launches_per_step": k.launch_count}
         if k.flops:
