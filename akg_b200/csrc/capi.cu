@@ -174,7 +174,9 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
       case StepK::ColJit: {
         const void* ins[16];
         for (size_t i = 0; i < st.ew_in.size(); ++i) ins[i] = resolve(st.ew_in[i], tensors, ws);
-        e = col_jit_launch(*st.row, ins, (float*)o, st.red_len, s, &st.dims);
+        float* parts[4] = {nullptr, nullptr, nullptr, nullptr};
+        for (size_t i = 0; i < st.ew_out.size() && i < 4; ++i) parts[i] = (float*)resolve(st.ew_out[i], tensors, ws);
+        e = col_jit_launch(*st.row, ins, parts, st.red_len, s, &st.dims);
         if (e == cudaErrorNotSupported && plan.fallback) {
           plan.use_fallback = true;
           return run_plan(k, *plan.fallback, tensors, ws, s);

@@ -640,7 +640,7 @@ struct ColShape {
 };
 
 bool col_generate(const RowProgram& P, bool vec, std::string* out, ColShape* shape) {
-  if (!P.col_reduce || P.out.size() != 1) return false;
+  if (!P.col_reduce || P.out.empty() || P.out.size() > 4) return false;
   ColShape cs;
   cs.vw = vec ? 8 : 1;
   const int64_t granules = (P.cols + cs.vw - 1) / cs.vw;
@@ -656,10 +656,11 @@ template <int OP> __device__ __forceinline__ float comb(float a, float b) {
   return OP == 0 ? __fadd_rn(a, b) : OP == 1 ? fmaxf(a, b) : OP == 2 ? fminf(a, b) : __fmul_rn(a, b);
 }
 )SRC";
-  const char* ident = P.col_red_op == 0 ? "0.f" : P.col_red_op == 1 ? "-3.402823466e+38f" : P.col_red_op == 2 ? "3.402823466e+38f" : "1.f";
+  auto ident_of = [](int op) { return op == 0 ? "0.f" : op == 1 ? "-3.402823466e+38f" : op == 2 ? "3.402823466e+38f" : "1.f"; };
   s << "extern \"C\" __global__ void __launch_bounds__(256) akgb_col_jit(";
   for (size_t i = 0; i < P.in.size(); ++i) s << "const void* __restrict__ in" << i << ", ";
-  s << "float* __restrict__ partial, i64 rows, i64 rows_per_split) {\n";
+  for (size_t i = 0; i < P.out.size(); ++i) s << "float* __restrict__ partial" << i << ", ";
+  s << "i64 rows, i64 rows_per_split) {\n";
   s << "  __shared__ float sm[TY][TX * VW + 1];\n";
   s << "  const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;\n";
   s << "  const i64 c = ((i64)blockIdx.x * TX + tx) * VW;\n";
@@ -696,7 +697,9 @@ template <int OP> __device__ __forceinline__ float comb(float a, float b) {
       s << "  }\n";
     }
   }
-  s << "  float acc[VW];\n#pragma unroll\n  for (int j = 0; j < VW; ++j) acc[j] = " << ident << ";\n";
+  for (size_t i = 0; i < P.out.size(); ++i)
+    s << "  float acc" << i << "[VW];\n#pragma unroll\n  for (int j = 0; j < VW; ++j) acc" << i << "[j] = "
+      << ident_of(P.out[i].red_op) << ";\n";
   s << "  if (valid) {\n#pragma unroll 4\n    for (i64 r = r0 + ty; r < r1; r += TY) {\n";
   for (size_t i = 0; i < P.in.size(); ++i) {
     const RowOperand& op = P.in[i];
@@ -727,13 +730,20 @@ template <int OP> __device__ __forceinline__ float comb(float a, float b) {
       s << "      const " << (fl ? "float " : "int ") << v << " = " << expr << ";\n";
     }
   }
-  s << "#pragma unroll\n      for (int j = 0; j < VW; ++j) acc[j] = comb<" << P.col_red_op << ">(acc[j], " << name[P.out[0].val]
-    << "[j]);\n";
+  for (size_t i = 0; i < P.out.size(); ++i)
+    s << "#pragma unroll\n      for (int j = 0; j < VW; ++j) acc" << i << "[j] = comb<" << P.out[i].red_op << ">(acc" << i
+      << "[j], " << name[P.out[i].val] << "[j]);\n";
   s << "    }\n  }\n";
-  s << "#pragma unroll\n  for (int j = 0; j < VW; ++j) sm[ty][tx * VW + j] = acc[j];\n  __syncthreads();\n";
-  s << "#pragma unroll\n  for (int h = TY / 2; h > 0; h >>= 1) {\n    if (ty < h) {\n#pragma unroll\n      for (int j = 0; j < VW; ++j) "
-       "sm[ty][tx * VW + j] = comb<" << P.col_red_op << ">(sm[ty][tx * VW + j], sm[ty + h][tx * VW + j]);\n    }\n    __syncthreads();\n  }\n";
-  s << "  if (ty == 0 && valid) {\n#pragma unroll\n    for (int j = 0; j < VW; ++j)\n      if (c + j < C) partial[(i64)blockIdx.y * C + c + j] = sm[0][tx * VW + j];\n  }\n}\n";
+  for (size_t i = 0; i < P.out.size(); ++i) {
+    const int op = P.out[i].red_op;
+    if (i) s << "  __syncthreads();\n";
+    s << "#pragma unroll\n  for (int j = 0; j < VW; ++j) sm[ty][tx * VW + j] = acc" << i << "[j];\n  __syncthreads();\n";
+    s << "#pragma unroll\n  for (int h = TY / 2; h > 0; h >>= 1) {\n    if (ty < h) {\n#pragma unroll\n      for (int j = 0; j < VW; ++j) "
+         "sm[ty][tx * VW + j] = comb<" << op << ">(sm[ty][tx * VW + j], sm[ty + h][tx * VW + j]);\n    }\n    __syncthreads();\n  }\n";
+    s << "  if (ty == 0 && valid) {\n#pragma unroll\n    for (int j = 0; j < VW; ++j)\n      if (c + j < C) partial" << i
+      << "[(i64)blockIdx.y * C + c + j] = sm[0][tx * VW + j];\n  }\n";
+  }
+  s << "}\n";
   *out = s.str();
   return true;
 }
@@ -876,8 +886,8 @@ int64_t col_jit_splits(const RowProgram& P, int sm_count) {
   return std::max<int64_t>(1, std::min<int64_t>(std::min(want, max_splits), 1024));
 }
 
-cudaError_t col_jit_launch(const RowProgram& P, const void* const* in, float* partial, int64_t splits, cudaStream_t s,
-                           LaunchDims* dims) {
+cudaError_t col_jit_launch(const RowProgram& P, const void* const* in, float* const* partials, int64_t splits,
+                           cudaStream_t s, LaunchDims* dims) {
   if (P.rows == 0 || P.cols == 0) return cudaSuccess;
   bool vec = P.cols % 8 == 0;
   for (size_t i = 0; i < P.in.size() && vec; ++i)
@@ -898,7 +908,11 @@ cudaError_t col_jit_launch(const RowProgram& P, const void* const* in, float* pa
     inp[i] = in[i];
     args[a++] = &inp[i];
   }
-  args[a++] = &partial;
+  float* parts[4];
+  for (size_t i = 0; i < P.out.size(); ++i) {
+    parts[i] = partials[i];
+    args[a++] = &parts[i];
+  }
   args[a++] = &rows;
   args[a++] = &rps;
   if (dims) {

@@ -80,6 +80,7 @@ struct RowOperand {
   int32_t kind = RK_FULL;
   int32_t val = 0;  // value loaded into / stored from
   int64_t mod_rows = 0;
+  int32_t red_op = 0;  // column mode results: 0 sum, 1 max, 2 min, 3 prod over the rows of `val`
 };
 
 struct RowInstr {
@@ -99,10 +100,9 @@ struct RowProgram {
   std::vector<int32_t> const_val;
   std::vector<uint32_t> const_bits;
   std::vector<uint8_t> val_full;  // per value: per element (1) or per row (0)
-  // column mode: the program's only reduction is its last op and folds the ROWS (axis 0 of [rows, cols]); the one
-  // result is [cols].  Generated as a kernel that walks rows and keeps 8 column accumulators per thread.
+  // column mode: the program ends in one or more reductions that fold the ROWS (axis 0 of [rows, cols]); every result
+  // is [cols].  Generated as a kernel that walks rows and keeps 8 column accumulators per thread and result.
   bool col_reduce = false;
-  int32_t col_red_op = 0;
 };
 
 }  // namespace akgb

@@ -85,8 +85,8 @@ cudaError_t row_jit_launch(const RowProgram& p, const void* const* in, void* con
                            LaunchDims* dims);
 std::string row_jit_source(const RowProgram& p, bool vec);
 int64_t col_jit_splits(const RowProgram& p, int sm_count);
-cudaError_t col_jit_launch(const RowProgram& p, const void* const* in, float* partial, int64_t splits, cudaStream_t s,
-                           LaunchDims* dims);
+cudaError_t col_jit_launch(const RowProgram& p, const void* const* in, float* const* partials, int64_t splits,
+                           cudaStream_t s, LaunchDims* dims);
 void ew_jit_prepare(const EwProgram& p);
 void row_jit_prepare(const RowProgram& p);
 void jit_set_cache_dir(const char* dir);  // nullptr: environment's choice; "": no disk cache

@@ -777,35 +777,49 @@ bool fused_reduce_all_plan(const Graph& g, int sm_count, Plan* out) {
 // generated kernel walks the rows, runs the chain in registers and keeps column accumulators; partial results of the
 // row splits are folded by the hand-written column reduction.  Returns false when the region is not of that form.
 bool fused_reduce_col_plan(const Graph& g, int sm_count, Plan* out) {
-  if (g.dynamic || g.outputs.size() != 1 || g.nodes.size() < 2) return false;
-  const Node& red = g.nodes.back();
-  if (!opk_is_reduce(red.kind) || red.out != g.outputs[0]) return false;
-  RedOp op;
-  switch (red.kind) {
-    case OpK::ReduceSum: op = RedOp::Sum; break;
-    case OpK::ReduceMax: op = RedOp::Max; break;
-    case OpK::ReduceMin: op = RedOp::Min; break;
-    case OpK::ReduceProd: op = RedOp::Prod; break;
-    default: return false;
-  }
-  const Value& x = g.v(red.in[0]);
-  const size_t rank = x.shape.size(), k = red.axes.size();
-  if (k == 0 || k >= rank || x.dt != DT::F32 || g.v(red.out).dt != DT::F32) return false;
+  if (g.dynamic || g.outputs.empty() || g.outputs.size() > 4 || g.nodes.size() < 2) return false;
+  // the tail of the op list: one reduction per result, all over the same leading axes of equally shaped tensors
+  const size_t n_red = g.outputs.size();
+  if (g.nodes.size() <= n_red) return false;
+  const size_t first_red = g.nodes.size() - n_red;
+  const Node& red0 = g.nodes[first_red];
+  if (!opk_is_reduce(red0.kind)) return false;
+  const Value& x = g.v(red0.in[0]);
+  const size_t rank = x.shape.size(), k = red0.axes.size();
+  if (k == 0 || k >= rank) return false;
   for (size_t i = 0; i < k; ++i)
-    if (red.axes[i] != (int64_t)i) return false;
+    if (red0.axes[i] != (int64_t)i) return false;
   int64_t R = 1, C = 1;
   for (size_t i = 0; i < rank; ++i) (i < k ? R : C) *= x.shape[i];
-  if (R < 2 || C < 2 || R * C < (1 << 16) || g.v(red.out).numel() != C) return false;
+  if (R < 2 || C < 2 || R * C < (1 << 16)) return false;
+  std::vector<RedOp> ops;
+  for (size_t i = first_red; i < g.nodes.size(); ++i) {
+    const Node& red = g.nodes[i];
+    const Value& xi = g.v(red.in[0]);
+    if (!opk_is_reduce(red.kind) || red.axes != red0.axes || xi.shape != x.shape || xi.dt != DT::F32 ||
+        g.v(red.out).dt != DT::F32 || g.v(red.out).numel() != C || g.v(red.out).output_index < 0)
+      return false;
+    switch (red.kind) {
+      case OpK::ReduceSum: ops.push_back(RedOp::Sum); break;
+      case OpK::ReduceMax: ops.push_back(RedOp::Max); break;
+      case OpK::ReduceMin: ops.push_back(RedOp::Min); break;
+      case OpK::ReduceProd: ops.push_back(RedOp::Prod); break;
+      default: return false;
+    }
+  }
   const std::vector<int64_t> lead(x.shape.begin(), x.shape.begin() + k), trail(x.shape.begin() + k, x.shape.end());
   auto strip = [](std::vector<int64_t> s) {
     while (s.size() > 1 && s.front() == 1) s.erase(s.begin());
     return s;
   };
   Graph g2 = g;
-  for (auto& v : g2.values) {
+  for (size_t vi = 0; vi < g2.values.size(); ++vi) {
+    Value& v = g2.values[vi];
     if (v.is_const) continue;
     const int64_t n = v.numel();
-    if (&v == &g2.v(red.out)) {
+    bool is_result = false;
+    for (size_t i = first_red; i < g.nodes.size(); ++i) is_result |= g.nodes[i].out == (int)vi;
+    if (is_result) {
       v.shape = {C};
     } else if (n == R * C && v.shape.size() == rank) {
       v.shape = {R, C};
@@ -819,16 +833,17 @@ bool fused_reduce_col_plan(const Graph& g, int sm_count, Plan* out) {
       return false;
     }
   }
-  for (size_t i = 0; i + 1 < g.nodes.size(); ++i) {
+  for (size_t i = 0; i < first_red; ++i) {
     const Node& nd = g.nodes[i];
     if (!opk_is_elementwise(nd.kind) || nd.kind == OpK::AddN || g.v(nd.out).output_index >= 0) return false;
   }
-  Node& red2 = g2.nodes.back();
-  red2.axes = {0};
-  red2.keep_dims = false;
+  for (size_t i = first_red; i < g2.nodes.size(); ++i) {
+    g2.nodes[i].axes = {0};
+    g2.nodes[i].keep_dims = false;
+  }
   auto rp = std::make_shared<RowProgram>();
   std::vector<int> in_values, out_values;
-  if (!build_row_program(g2, rp.get(), &in_values, &out_values, true)) return false;
+  if (!build_row_program(g2, rp.get(), &in_values, &out_values, true) || out_values.size() != n_red) return false;
   const int64_t splits = col_jit_splits(*rp, sm_count);
   Plan p;
   p.klass = "reduce_y";
@@ -842,27 +857,32 @@ bool fused_reduce_col_plan(const Graph& g, int sm_count, Plan* out) {
     ref.arg = g.v(vid).input_index;
     st.ew_in.push_back(ref);
   }
-  Ref result;
-  result.arg = (int)g.inputs.size();
   size_t ws = 0;
-  if (splits == 1) {
-    st.out = result;
-    p.steps.push_back(std::move(st));
-  } else {
+  std::vector<Step> finishes;
+  for (size_t i = 0; i < n_red; ++i) {
+    Ref result;
+    result.arg = (int)g.inputs.size() + g.v(out_values[i]).output_index;
+    if (splits == 1) {
+      st.ew_out.push_back(result);
+      continue;
+    }
     Ref partial;
-    partial.ws_off = 0;
-    st.out = partial;
-    p.steps.push_back(std::move(st));
-    ws = ((size_t)(splits * C) * sizeof(float) + 255) / 256 * 256;
+    partial.ws_off = (int64_t)ws;
+    ws += ((size_t)(splits * C) * sizeof(float) + 255) / 256 * 256;
+    st.ew_out.push_back(partial);
     Step fin;
     fin.kind = StepK::ReduceCol;
     fin.kernel_name = "reduce_col_f32";
-    fin.red_op = op;
+    fin.red_op = ops[i];
     fin.red_outer = 1;
     fin.red_len = splits;
     fin.red_inner = C;
     fin.a = partial;
     fin.out = result;
+    finishes.push_back(std::move(fin));
+  }
+  p.steps.push_back(std::move(st));
+  for (Step& fin : finishes) {
     fin.scratch.ws_off = (int64_t)ws;
     ws += (reduce_col_workspace(splits, C, sm_count) + 255) / 256 * 256;
     p.steps.push_back(std::move(fin));

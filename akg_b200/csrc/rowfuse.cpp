@@ -44,9 +44,19 @@ bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_val
   if (!first_red) return false;
   const std::vector<int64_t>& S = g.v(first_red->in[0]).shape;
   if (S.empty()) return false;
-  if (col_mode && (S.size() != 2 || first_red != &g.nodes.back() || g.outputs.size() != 1 ||
-                   g.outputs[0] != first_red->out))
-    return false;  // column mode works on the caller's 2-D view: [rows, cols], one reduction over rows at the end
+  if (col_mode) {
+    // column mode works on the caller's 2-D view [rows, cols]: from the first reduction on every op is a reduction over
+    // the rows, and those are exactly the region's results
+    if (S.size() != 2) return false;
+    size_t n_red = 0;
+    bool seen = false;
+    for (auto& n : g.nodes) {
+      seen = seen || &n == first_red;
+      if (seen && !opk_is_reduce(n.kind)) return false;
+      n_red += seen;
+    }
+    if (n_red != g.outputs.size() || n_red > 4) return false;
+  }
   const int64_t C = S.back();
   int64_t R = 1;
   for (size_t i = 0; i + 1 < S.size(); ++i) R *= S[i];
@@ -131,21 +141,22 @@ bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_val
         return false;
       int src = 0;
       if (!operand(n.in[0], &src) || !P.val_full[src]) return false;
+      RowOperand o;
       switch (n.kind) {
-        case OpK::ReduceSum: P.col_red_op = 0; break;
-        case OpK::ReduceMax: P.col_red_op = 1; break;
-        case OpK::ReduceMin: P.col_red_op = 2; break;
-        case OpK::ReduceProd: P.col_red_op = 3; break;
+        case OpK::ReduceSum: o.red_op = 0; break;
+        case OpK::ReduceMax: o.red_op = 1; break;
+        case OpK::ReduceMin: o.red_op = 2; break;
+        case OpK::ReduceProd: o.red_op = 3; break;
         default: return false;
       }
+      if (ov.output_index < 0) return false;
       P.col_reduce = true;
-      RowOperand o;
       o.dt = (int)DT::F32;
       o.kind = RK_COL;
       o.val = src;
       P.out.push_back(o);
       out_values->push_back(n.out);
-      break;  // the last node
+      continue;
     } else if (opk_is_reduce(n.kind)) {
       const Value& x = g.v(n.in[0]);
       if (n.axes.size() != 1 || n.axes[0] != (int64_t)x.shape.size() - 1 || x.shape.back() != C || x.numel() != R * C)

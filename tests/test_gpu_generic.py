@@ -777,3 +777,26 @@ def test_prepare_allows_capturing_the_first_launch(lib):
     torch.cuda.synchronize()
     want = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-6) * g_
     torch.testing.assert_close(out, want, rtol=1e-5, atol=1e-5)
+
+
+def test_two_column_reductions_share_one_pass(lib):
+    """dgamma = sum_rows(dy * xhat) and dbeta = sum_rows(dy) of one region: one generated kernel reads dy and xhat once."""
+    rng = np.random.default_rng(98)
+    f = "float32"
+    shape = [4, 1500, 512]
+    b = _Builder("Fused_Mul_ReduceSum_ReduceSum_98")
+    dy = b.input("dy", shape, f)
+    xhat = b.input("xhat", shape, f)
+    t = b.emit("Mul", [dy, xhat], shape, f)
+    b.output(b.emit("ReduceSum", [t], [512], f, _reduce_attr([0, 1], False)))
+    b.output(b.emit("ReduceSum", [dy], [512], f, _reduce_attr([0, 1], False)))
+    d = b.build()
+    ins = [rng.standard_normal(shape).astype(np.float32) for _ in range(2)]
+    got, kern = run(d, ins)
+    a64, b64 = ins[0].astype(np.float64), ins[1].astype(np.float64)
+    want = [(a64 * b64).sum(axis=(0, 1)), a64.sum(axis=(0, 1))]
+    bound = [1e-5 * np.abs(a64 * b64).sum(axis=(0, 1)), 1e-5 * np.abs(a64).sum(axis=(0, 1))]
+    for g_, w_, bd in zip(got, want, bound):
+        assert np.all(np.abs(g_.astype(np.float64) - w_) <= bd + 1e-6)
+    if FLAGS[0] == 0:
+        assert kern.meta()["template"] == "akgb_col_jit"
