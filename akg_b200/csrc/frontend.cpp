@@ -173,8 +173,10 @@ Graph parse_info(const char* text, size_t len) {
     const Json& outs = od.at("output_desc");
     if (!ins.is_array() || ins.size() == 0) throw JsonError("op '" + n.name + "' has no input_desc");
     if (!outs.is_array() || outs.size() == 0) throw JsonError("op '" + n.name + "' has no output_desc");
-    if (const Json* fo = find_attr(attrs, "fake_output"))
-      if (fo->is_bool() && fo->b) throw Unsupported("fake_output aliasing is not supported");
+    // fake_output: the result takes shape and type of the first operand and only the name of the declared output
+    // (TranslateToMindsporeDialect.cpp:348-365)
+    bool fake_output = false;
+    if (const Json* fo = find_attr(attrs, "fake_output")) fake_output = fo->is_bool() && fo->b;
 
     // Concat and AddN list all their tensors inside the first input entry
     // (TranslateToMindsporeDialect.cpp:719-727, :766-783); StridedSlice may carry begin/end/strides as inputs 1..3
@@ -215,9 +217,11 @@ Graph parse_info(const char* text, size_t len) {
     }
 
     const Json& o0 = outs[0];
-    DT odt = dt_from_name(o0.at("data_type").as_string());
-    if (odt == DT::Invalid) throw Unsupported("data type '" + o0.at("data_type").str + "' is not supported");
-    int out_id = new_value(o0.at("tensor_name").as_string(), shape_of(o0), odt);
+    const Json& first_in = ins[0].is_array() ? ins[0][0] : ins[0];
+    const Json& otype = fake_output ? first_in : o0;
+    DT odt = dt_from_name(otype.at("data_type").as_string());
+    if (odt == DT::Invalid) throw Unsupported("data type '" + otype.at("data_type").str + "' is not supported");
+    int out_id = new_value(o0.at("tensor_name").as_string(), shape_of(otype), odt);
     g.values[out_id].producer = (int)g.nodes.size();
     n.out = out_id;
 

@@ -202,3 +202,18 @@ def test_dynamic_shape_region_plans_per_extent_set(lib):
     ks = FusedKernel(s)
     assert ks.is_dynamic
     ks.bind_shapes([[4, 8, 256], [8, 256], [4, 8, 256]])
+
+
+def test_fake_output_takes_shape_and_type_of_the_first_operand(lib):
+    """An op marked fake_output declares a placeholder result; its real shape and type are those of its first operand
+    (the reference's parser substitutes them)."""
+    from akg_b200 import FusedKernel
+    from akg_b200.descs import _Builder, _attr
+    b = _Builder("Fused_Assign_fake_1")
+    dst = b.input("dst", [6, 10], "float32")
+    val = b.input("val", [6, 10], "float32")
+    t = b.emit("Add", [val, b.const(1.0, "float32")], [6, 10], "float32")
+    a = b.emit("Assign", [dst, t], [1], "float16", [_attr("fake_output", "bool", True)])  # placeholder shape / type
+    b.output(b.emit("Mul", [a, b.const(2.0, "float32")], [6, 10], "float32"))
+    k = FusedKernel(b.build())
+    assert k.inputs[0].written_in_place and k.outputs[0].shape == (6, 10) and k.outputs[0].dtype == "float32"
