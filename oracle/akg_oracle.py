@@ -204,6 +204,18 @@ def evaluate(desc: dict | str, inputs: Sequence[np.ndarray], accum: str = "numpy
                 r = np.multiply(x, x)
             elif name == "Pow":
                 r = np.power(operand(ins[0]), operand(ins[1])).astype(odt)
+            elif name == "Atan2":  # op_dsl.py:1052-1055
+                a, b = operand(ins[0]), operand(ins[1])
+                r = _round_to(np.arctan2(a.astype(np.float64), b.astype(np.float64)), odt)
+            elif name in ("IsNan", "IsInf", "IsFinite"):  # op_dsl.py:717-744
+                x = operand(ins[0])
+                x = x.astype(np.float32) if _is_low_float(x.dtype) else x
+                r = {"IsNan": np.isnan, "IsInf": np.isinf, "IsFinite": np.isfinite}[name](x)
+            elif name == "LogicalNot":
+                r = np.logical_not(operand(ins[0]))
+            elif name in ("LogicalAnd", "LogicalOr"):
+                fn = np.logical_and if name == "LogicalAnd" else np.logical_or
+                r = fn(operand(ins[0]), operand(ins[1]))
             elif name == "Cast":
                 x = operand(ins[0])
                 if x.dtype.kind == "f" or (BF16 is not None and x.dtype == BF16):

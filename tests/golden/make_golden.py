@@ -6,6 +6,7 @@ Run in a container where the reference checkout is mounted (default
 
     python tests/golden/make_golden.py          # the benchmark classes
     python tests/golden/make_golden.py corpus   # the reference's own system-test descriptions -> corpus/
+    python tests/golden/make_golden.py ops      # small regions over the whole op surface -> ops/
 
 For every case it builds a fused-op description, draws seeded inputs, feeds
 both through ``gen_json_data`` of
@@ -120,6 +121,181 @@ def main():
         os.chdir(cwd)
 
 
+def _op_cases():
+    """Small regions that together touch the op surface of the JSON factory, for fixtures under ops/."""
+    from akg_b200.descs import _Builder, _attr, _reduce_attr
+    f, h = "float32", "float16"
+    cases = {}
+
+    def unary_chain(name, ops, shape=(6, 40), dtype=f):
+        b = _Builder(f"Fused_{name}_1")
+        t = b.input("x", list(shape), dtype)
+        for op in ops:
+            t = b.emit(op, [t], list(shape), dtype)
+        b.output(t)
+        cases[name] = b.build()
+
+    unary_chain("abs_neg_floor", ["Abs", "Neg", "Floor"])
+    unary_chain("exp_log_sqrt", ["Abs", "Exp", "Log", "Sqrt"])
+    unary_chain("rsqrt_reciprocal", ["Abs", "Rsqrt", "Reciprocal"])
+    unary_chain("sin_cos", ["Sin", "Cos"])
+    unary_chain("asinh", ["Asinh"])
+    unary_chain("tanh_f32", ["Tanh"])
+
+    b = _Builder("Fused_binary_2")
+    x, y = b.input("x", [5, 33], f), b.input("y", [33], f)
+    t = b.emit("Add", [x, y], [5, 33], f)
+    t = b.emit("Sub", [t, b.const(0.5, f)], [5, 33], f)
+    t = b.emit("Mul", [t, y], [5, 33], f)
+    t = b.emit("RealDiv", [t, b.const(3.0, f)], [5, 33], f)
+    t = b.emit("Maximum", [t, x], [5, 33], f)
+    t = b.emit("Minimum", [t, b.const(1.25, f)], [5, 33], f)
+    b.output(t)
+    cases["binary_broadcast"] = b.build()
+
+    b = _Builder("Fused_pow_atan2_3")
+    x, y = b.input("x", [4, 16], f), b.input("y", [4, 16], f)
+    p = b.emit("Pow", [b.emit("Abs", [x], [4, 16], f), b.const(1.5, f)], [4, 16], f)
+    b.output(b.emit("Atan2", [p, y], [4, 16], f))
+    cases["pow_atan2"] = b.build()
+
+    b = _Builder("Fused_compare_select_4")
+    x, y = b.input("x", [7, 24], f), b.input("y", [7, 24], f)
+    gt = b.emit("Greater", [x, y], [7, 24], "bool")
+    le = b.emit("LessEqual", [x, b.const(0.0, f)], [7, 24], "bool")
+    both = b.emit("LogicalOr", [b.emit("LogicalAnd", [gt, le], [7, 24], "bool"),
+                                b.emit("LogicalNot", [gt], [7, 24], "bool")], [7, 24], "bool")
+    b.output(b.emit("Select", [both, x, y], [7, 24], f))
+    b.output(b.emit("Equal", [x, y], [7, 24], "bool"))
+    b.output(b.emit("NotEqual", [x, b.const(0.0, f)], [7, 24], "bool"))
+    b.output(b.emit("GreaterEqual", [x, y], [7, 24], "bool"))
+    b.output(b.emit("Less", [x, y], [7, 24], "bool"))
+    cases["compare_select"] = b.build()
+
+    b = _Builder("Fused_isnan_5")
+    x = b.input("x", [64], f)
+    b.output(b.emit("IsNan", [x], [64], "bool"))
+    b.output(b.emit("IsInf", [x], [64], "bool"))
+    b.output(b.emit("IsFinite", [x], [64], "bool"))
+    cases["isnan_isinf"] = b.build()
+
+    b = _Builder("Fused_casts_6")
+    i32, hx, bl = b.input("i", [3, 20], "int32"), b.input("hx", [3, 20], h), b.input("bl", [3, 20], "bool")
+    a = b.emit("Cast", [i32], [3, 20], f, [_attr("dst_type", "str", f)])
+    c = b.emit("Cast", [hx], [3, 20], f, [_attr("dst_type", "str", f)])
+    d = b.emit("Cast", [bl], [3, 20], f, [_attr("dst_type", "str", f)])
+    t = b.emit("Add", [b.emit("Mul", [a, c], [3, 20], f), d], [3, 20], f)
+    b.output(b.emit("Cast", [t], [3, 20], h, [_attr("dst_type", "str", h)]))
+    cases["casts"] = b.build()
+
+    for name, op, axes, keep, oshape in (("reduce_min_x", "ReduceMin", [1], True, [9, 1]),
+                                         ("reduce_prod_y", "ReduceProd", [0], False, [50]),
+                                         ("reduce_max_all", "ReduceMax", [0, 1], False, [1])):
+        b = _Builder(f"Fused_{name}_7")
+        x = b.input("x", [9, 50], f)
+        b.output(b.emit(op, [x], oshape, f, _reduce_attr(axes, keep)))
+        cases[name] = b.build()
+
+    b = _Builder("Fused_reduce_all_8")
+    x = b.input("x", [12, 30], "bool")
+    b.output(b.emit("ReduceAll", [x], [30], "bool", _reduce_attr([0], False)))
+    cases["reduce_all_bool"] = b.build()
+
+    b = _Builder("Fused_shapes_9")
+    x, r = b.input("x", [4, 6, 10], f), b.input("r", [4, 1, 1], f)
+    t = b.emit("Reshape", [x], [24, 10], f, [_attr("shape", "listInt", [24, 10])])
+    t = b.emit("Transpose", [t], [10, 24], f, [_attr("perm", "listInt", [1, 0])])
+    bc = b.emit("BroadcastTo", [r], [4, 6, 10], f, [_attr("shape", "listInt", [4, 6, 10])])
+    b.output(t)
+    b.output(b.emit("Add", [x, bc], [4, 6, 10], f))
+    cases["reshape_transpose_broadcast"] = b.build()
+
+    b = _Builder("Fused_tile_slice_10")
+    x = b.input("x", [3, 8], f)
+    t = b.emit("Tile", [x], [6, 16], f, [_attr("multiples", "listInt", [2, 2])])
+    s1 = b.emit("Slice", [t], [4, 8], f, [_attr("begin", "listInt", [1, 4]), _attr("size", "listInt", [4, 8])])
+    s2 = b.emit("StridedSlice", [t], [3, 8], f, [_attr("begin", "listInt", [0, 0]), _attr("end", "listInt", [6, 16]),
+                                                 _attr("strides", "listInt", [2, 2])])
+    b.output(s1)
+    b.output(s2)
+    cases["tile_slice_strided"] = b.build()
+
+    b = _Builder("Fused_concat_addn_11")
+    x, y, z = b.input("x", [4, 5], f), b.input("y", [4, 7], f), b.input("z", [4, 5], f)
+    b._n += 1
+    cat = {"tensor_name": "cat", "shape": [4, 12], "data_type": f, "format": "DefaultFormat"}
+    b.ops.append({"name": "Concat", "attr": [_attr("axis", "int", 1)], "impl_path": "",
+                  "input_desc": [[dict(x), dict(y)]], "output_desc": [dict(cat)]})
+    add = {"tensor_name": "addn", "shape": [4, 5], "data_type": f, "format": "DefaultFormat"}
+    b.ops.append({"name": "AddN", "attr": None, "impl_path": "",
+                  "input_desc": [[dict(x), dict(z), dict(x)]], "output_desc": [dict(add)]})
+    b.output(cat)
+    b.output(add)
+    cases["concat_addn"] = b.build()
+
+    b = _Builder("Fused_gather_12")
+    table, idx = b.input("table", [50, 16], f), b.input("idx", [3, 7], "int32")
+    b.output(b.emit("Gather", [table, idx], [3, 7, 16], f, [_attr("axis", "int", 0), _attr("batch_dims", "int", 0)]))
+    cases["gather_rows"] = b.build()
+
+    b = _Builder("Fused_segsum_13")
+    data, ids = b.input("data", [40, 8], f), b.input("ids", [40], "int32")
+    b.output(b.emit("UnsortedSegmentSum", [data, ids], [6, 8], f, [_attr("num_segments", "int", 6)]))
+    cases["unsorted_segment_sum"] = b.build()
+
+    b = _Builder("Fused_batchmatmul_14")
+    a, w = b.input("a", [3, 16, 24], h), b.input("w", [3, 24, 8], h)
+    b.output(b.emit("BatchMatMul", [a, w], [3, 16, 8], f,
+                    [_attr("transpose_a", "bool", False), _attr("transpose_b", "bool", False)]))
+    cases["batch_matmul_f16"] = b.build()
+
+    b = _Builder("Fused_assign_15")
+    dst, val = b.input("dst", [5, 12], f), b.input("val", [5, 12], f)
+    t = b.emit("Mul", [val, b.const(2.0, f)], [5, 12], f)
+    a = b.emit("Assign", [dst, t], [5, 12], f)
+    b.output(b.emit("Add", [a, b.const(1.0, f)], [5, 12], f))
+    cases["assign"] = b.build()
+    return cases
+
+
+def ops():
+    """Golden vectors for `_op_cases()`, from the reference's expected-value generator, under ops/."""
+    helper = _import_reference()
+    outdir = HERE / "ops"
+    outdir.mkdir(exist_ok=True)
+    cwd = os.getcwd()
+    os.chdir("/tmp")
+    made = 0
+    try:
+        for k, (name, desc) in enumerate(sorted(_op_cases().items())):
+            seed = 500 + k
+            inputs = corpus_inputs(desc, seed)
+            if name == "isnan_isinf":
+                inputs[0][::7] = np.nan
+                inputs[0][3::11] = np.inf
+            text = json.dumps(desc)
+            try:
+                _, expect, _ = helper.gen_json_data(text, True, input_for_mod=[a.copy() for a in inputs])
+            except Exception as e:
+                print(f"skip {name}: expected-value generator raised {type(e).__name__}: {str(e)[:100]}")
+                continue
+            expect = expect if isinstance(expect, (list, tuple)) else [expect]
+            blob = {"desc": np.frombuffer(text.encode(), dtype=np.uint8), "seed": np.asarray(seed)}
+            try:
+                for i, e in enumerate(expect):
+                    shape = desc["output_desc"][i].get("shape") or [1]
+                    _store(blob, f"out{i}", np.ascontiguousarray(np.asarray(e)).reshape(shape))
+            except (ValueError, IndexError) as e:
+                print(f"skip {name}: expected values do not fit the declared outputs ({e})")
+                continue
+            np.savez_compressed(outdir / f"{name}.npz", **blob)
+            made += 1
+            print(f"{name}: {len(inputs)} inputs, {len(expect)} outputs")
+    finally:
+        os.chdir(cwd)
+    print(made, "op fixtures")
+
+
 def _bind_by_position(desc: dict) -> dict:
     by_pos = {1: 24, 2: 10, 3: 12, 4: 32}
 
@@ -209,5 +385,7 @@ def _store(blob, key, a):
 if __name__ == "__main__":
     if len(sys.argv) > 1 and sys.argv[1] == "corpus":
         corpus()
+    elif len(sys.argv) > 1 and sys.argv[1] == "ops":
+        ops()
     else:
         main()

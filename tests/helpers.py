@@ -85,6 +85,22 @@ def corpus_inputs(desc: dict, seed: int) -> list[np.ndarray]:
     return out
 
 
+def ops_cases():
+    return sorted(p.stem for p in (GOLDEN / "ops").glob("*.npz"))
+
+
+def load_ops(name):
+    """(description, inputs, expected outputs) of one op-surface fixture (tests/golden/make_golden.py ops)."""
+    z = np.load(GOLDEN / "ops" / f"{name}.npz")
+    desc = json.loads(bytes(z["desc"]).decode())
+    ins = corpus_inputs(desc, int(z["seed"]))
+    if name == "isnan_isinf":
+        ins[0][::7] = np.nan
+        ins[0][3::11] = np.inf
+    outs = [z[f"out{i}"] if f"out{i}" in z else z[f"out{i}__bf16"].view(BF16) for i in range(len(desc["output_desc"]))]
+    return desc, ins, outs
+
+
 def corpus_cases():
     return sorted(p.stem for p in (GOLDEN / "corpus").glob("*.npz"))
 
