@@ -255,6 +255,19 @@ def _op_cases():
     a = b.emit("Assign", [dst, t], [5, 12], f)
     b.output(b.emit("Add", [a, b.const(1.0, f)], [5, 12], f))
     cases["assign"] = b.build()
+
+    # reduce-X / reduce-Y regions that run as generated row and column kernels
+    cases["rmsnorm_33x200"] = descs.rmsnorm(33, 200)
+    cases["rmsnorm_f16_16x512"] = descs.rmsnorm(16, 512, "float16")
+    cases["mul_reduce_rows_300x264"] = descs.mul_reduce_sum(300, 264, [0])
+    cases["mul_reduce_all_300x264"] = descs.mul_reduce_sum(300, 264, [0, 1])
+    b = _Builder("Fused_LogSoftmax_16")
+    x = b.input("x", [5, 12, 96], f)
+    m = b.emit("ReduceMax", [x], [5, 12, 1], f, _reduce_attr([2], True))
+    d = b.emit("Sub", [x, m], [5, 12, 96], f)
+    e = b.emit("ReduceSum", [b.emit("Exp", [d], [5, 12, 96], f)], [5, 12, 1], f, _reduce_attr([2], True))
+    b.output(b.emit("Sub", [d, b.emit("Log", [e], [5, 12, 1], f)], [5, 12, 96], f))
+    cases["log_softmax_5x12x96"] = b.build()
     return cases
 
 
