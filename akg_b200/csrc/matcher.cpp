@@ -724,8 +724,9 @@ bool fused_reduce_all_plan(const Graph& g, int sm_count, Plan* out) {
       if (!v.is_const && v.numel() != n) return false;  // broadcast operands would not survive the re-view
     }
   }
+  // the widest row of at most 4096 elements, a multiple of 8, that divides n
   int64_t c = 0;
-  for (int64_t cand : {4096, 2048, 1024, 512, 256, 128, 64})
+  for (int64_t cand = 4096; cand >= 32; cand -= 8)
     if (n % cand == 0) {
       c = cand;
       break;

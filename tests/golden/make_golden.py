@@ -1,10 +1,9 @@
 """Generates the golden fixtures in this directory from the reference's own
 expected-value generator.
 
-Run in a container where the reference checkout is mounted (default
-``/root/reference``, override with ``AKG_REFERENCE``)::
+Run where a checkout of the reference is available; point ``AKG_REFERENCE`` at its root::
 
-    python tests/golden/make_golden.py          # the benchmark classes
+    AKG_REFERENCE=<checkout> python tests/golden/make_golden.py          # the benchmark classes
     python tests/golden/make_golden.py corpus   # the reference's own system-test descriptions -> corpus/
     python tests/golden/make_golden.py ops      # small regions over the whole op surface -> ops/
 
@@ -37,8 +36,15 @@ sys.path.insert(0, str(HERE.parent))
 from helpers import corpus_inputs  # noqa: E402
 
 
+def _reference_root() -> Path:
+    root = os.environ.get("AKG_REFERENCE")
+    if not root:
+        raise SystemExit("set AKG_REFERENCE to the root of a checkout of the reference")
+    return Path(root)
+
+
 def _import_reference():
-    ref = Path(os.environ.get("AKG_REFERENCE", "/root/reference")) / "akg-mlir" / "python" / "akg_mlir"
+    ref = _reference_root() / "akg-mlir" / "python" / "akg_mlir"
     if not ref.exists():
         raise SystemExit(f"reference checkout not found at {ref}")
     import ml_dtypes
@@ -333,7 +339,7 @@ def corpus(max_bytes: int = 2 << 20):
     (akg-mlir/tests/st/**/*.info*): static shapes, at most `max_bytes` of tensors, evaluated by the reference's
     expected-value generator on seeded inputs.  Stored under corpus/ as description + input seed + expected outputs."""
     helper = _import_reference()
-    ref = Path(os.environ.get("AKG_REFERENCE", "/root/reference")) / "akg-mlir" / "tests" / "st"
+    ref = _reference_root() / "akg-mlir" / "tests" / "st"
     outdir = HERE / "corpus"
     outdir.mkdir(exist_ok=True)
     cwd = os.getcwd()
