@@ -217,3 +217,63 @@ def test_fake_output_takes_shape_and_type_of_the_first_operand(lib):
     b.output(b.emit("Mul", [a, b.const(2.0, "float32")], [6, 10], "float32"))
     k = FusedKernel(b.build())
     assert k.inputs[0].written_in_place and k.outputs[0].shape == (6, 10) and k.outputs[0].dtype == "float32"
+
+
+def test_planning_of_generated_kernels_needs_no_device(lib):
+    """Which plan a region gets is decided at compile time on the host: reduce-X regions become one row program,
+    elementwise chains ending in a reduction over leading / all axes a column / row program plus the fold of the
+    partials, and with run-time compilation off the same regions are planned as separate launches."""
+    from akg_b200 import FusedKernel, descs
+    from akg_b200.descs import _Builder, _attr, _reduce_attr
+    k = FusedKernel(descs.rmsnorm(300, 1024))
+    assert k.meta()["template"] == "akgb_row_jit" and k.launch_count == 1
+    src = k.jit_source()
+    assert "akgb_row_jit" in src and "constexpr int C = 1024, T = 32" in src and "row_reduce<0>" in src
+    assert FusedKernel(descs.rmsnorm(300, 1024), flags=1).launch_count > 1
+    # threads per row follow the row length: several warps for long rows, a few lanes for short ones
+    assert "T = 128" in FusedKernel(descs.rmsnorm(64, 4096)).jit_source()
+    assert "T = 8," in FusedKernel(descs.rmsnorm(64, 64)).jit_source()
+    assert "VW = 1" in FusedKernel(descs.rmsnorm(64, 100)).jit_source(False)
+    kc = FusedKernel(descs.mul_reduce_sum(4096, 512, [0]))
+    assert kc.meta()["template"] == "akgb_col_jit" and "akgb_col_jit" in kc.jit_source()
+    ka = FusedKernel(descs.mul_reduce_sum(4096, 512, [0, 1]))
+    assert ka.meta()["template"] == "akgb_row_jit" and "C = 4096" in ka.jit_source() and ka.launch_count == 3
+    # small tensors are not worth a generated reduction kernel
+    assert FusedKernel(descs.mul_reduce_sum(64, 64, [0])).meta()["template"] != "akgb_col_jit"
+
+
+def test_planning_of_the_wider_op_surface(lib):
+    from akg_b200 import FusedKernel, descs
+    from akg_b200.descs import _Builder, _attr, _reduce_attr
+    f = "float32"
+    # matmul epilogue inside a larger region: bias, ReLU and the narrowing cast ride in the matmul launch
+    b = _Builder("Fused_MatMul_Add_Max_Cast_Neg_1")
+    a, w, bias = b.input("a", [256, 128], "bfloat16"), b.input("w", [128, 192], "bfloat16"), b.input("bias", [192], f)
+    c = b.emit("MatMul", [a, w], [256, 192], f, [_attr("transpose_a", "bool", False), _attr("transpose_b", "bool", False)])
+    c = b.emit("Maximum", [b.emit("Add", [c, bias], [256, 192], f), b.const(0.0, f)], [256, 192], f)
+    c = b.emit("Cast", [c], [256, 192], "bfloat16", [_attr("dst_type", "str", "bfloat16")])
+    b.output(b.emit("Neg", [c], [256, 192], "bfloat16"))
+    assert FusedKernel(b.build()).launch_count == 2
+    # float32 and float16 operands, batches in one launch
+    assert FusedKernel(descs.matmul_bias_relu(256, 64, 128, dtype="float32")).meta()["template"] == "sgemm_f32"
+    assert FusedKernel(descs.matmul_bias_relu(256, 64, 128, dtype="float16")).launch_count == 1
+    b = _Builder("Fused_BatchMatMul_2")
+    a, w = b.input("a", [12, 128, 64], "float16"), b.input("w", [12, 64, 128], "float16")
+    b.output(b.emit("BatchMatMul", [a, w], [12, 128, 128], f,
+                    [_attr("transpose_a", "bool", False), _attr("transpose_b", "bool", False)]))
+    assert FusedKernel(b.build()).launch_count == 1
+    # Pad, Split, ArgMax, Gather, UnsortedSegmentSum are accepted
+    b = _Builder("Fused_Pad_Split_ArgMax_3")
+    x = b.input("x", [6, 10], f)
+    p = b.emit("Pad", [x], [8, 12], f, [_attr("head", "listInt", [1, 0]), _attr("tail", "listInt", [1, 2]),
+                                        _attr("pad_val", "float", 0.0)])
+    halves = b.emit_multi("Split", [p], [([8, 6], f), ([8, 6], f)], [_attr("axis", "int", 1)])
+    b.output(b.emit("ArgMax", [halves[0]], [8], "int32", _reduce_attr([1], False)))
+    b.output(halves[1])
+    k = FusedKernel(b.build())
+    assert [o.dtype for o in k.outputs] == ["int32", "float32"] and k.launch_count >= 3
+    b = _Builder("Fused_Gather_SegSum_4")
+    table, idx = b.input("table", [100, 16], f), b.input("idx", [40], "int32")
+    g = b.emit("Gather", [table, idx], [40, 16], f, [_attr("axis", "int", 0), _attr("batch_dims", "int", 0)])
+    b.output(b.emit("UnsortedSegmentSum", [g, idx], [7, 16], f, [_attr("num_segments", "int", 7)]))
+    assert FusedKernel(b.build()).launch_count == 2
