@@ -478,42 +478,73 @@ struct Builder {
     }
     std::vector<bool> red(x.shape.size(), false);
     for (auto a : n.axes) red[a] = true;
-    int64_t outer = 1, len = 1, inner = 1;
-    int phase = 0;
-    for (size_t i = 0; i < x.shape.size(); ++i) {
-      if (x.shape[i] == 1) continue;
-      if (red[i]) {
-        if (phase == 2) throw Unsupported("reduction over non-adjacent axes");
-        phase = 1;
-        len *= x.shape[i];
-      } else {
-        if (phase == 1) phase = 2;
-        (phase == 0 ? outer : inner) *= x.shape[i];
+    // runs of adjacent reduced axes (extent-1 axes neither break nor make a run); several runs are folded one after
+    // the other, the last run first, through float32 temporaries
+    std::vector<int64_t> shape = x.shape;
+    std::vector<std::vector<size_t>> runs;
+    {
+      bool open = false;
+      for (size_t i = 0; i < shape.size(); ++i) {
+        if (shape[i] == 1) continue;
+        if (red[i]) {
+          if (!open) runs.emplace_back();
+          runs.back().push_back(i);
+          open = true;
+        } else {
+          open = false;
+        }
       }
     }
+    if (runs.empty()) runs.emplace_back();  // nothing but extent-1 axes: a copy through the reduction kernel
     Step st;
-    st.red_op = op;
-    st.red_outer = outer;
-    st.red_len = len;
-    st.red_inner = inner;
-    st.a = src;
-    st.out = dst;
-    if (inner == 1 && outer == 1) {
-      st.kind = StepK::ReduceAll;
-      st.kernel_name = "reduce_all_f32";
-      st.scratch.ws_off = (int64_t)ws;
-      ws += (reduce_all_workspace(sm_count) + 255) / 256 * 256;
-    } else if (inner == 1) {
-      st.kind = StepK::ReduceRow;
-      st.kernel_name = "reduce_row_f32";
-    } else {
-      st.kind = StepK::ReduceCol;
-      st.kernel_name = "reduce_col_f32";
-      if (outer > 4096) throw Unsupported("batched column reduction with more than 4096 batches");
-      st.red_batch_in = len * inner;
-      st.red_batch_out = inner;
-      st.scratch.ws_off = (int64_t)ws;
-      ws += (reduce_col_workspace(len, inner, sm_count) + 255) / 256 * 256;
+    for (size_t ri = runs.size(); ri-- > 0;) {
+      std::vector<bool> in_run(shape.size(), false);
+      for (size_t d : runs[ri]) in_run[d] = true;
+      int64_t outer = 1, len = 1, inner = 1;
+      int phase = 0;
+      for (size_t i = 0; i < shape.size(); ++i) {
+        if (shape[i] == 1) continue;
+        if (in_run[i]) {
+          phase = 1;
+          len *= shape[i];
+        } else {
+          if (phase == 1) phase = 2;
+          (phase == 0 ? outer : inner) *= shape[i];
+        }
+      }
+      Ref to = dst;
+      if (ri > 0) {  // more runs to go: this pass writes a temporary
+        to = Ref();
+        to.ws_off = (int64_t)ws;
+        ws += ((size_t)(outer * inner) * 4 + 255) / 256 * 256;
+      }
+      st = Step();
+      st.red_op = op;
+      st.red_outer = outer;
+      st.red_len = len;
+      st.red_inner = inner;
+      st.a = src;
+      st.out = to;
+      if (inner == 1 && outer == 1) {
+        st.kind = StepK::ReduceAll;
+        st.kernel_name = "reduce_all_f32";
+        st.scratch.ws_off = (int64_t)ws;
+        ws += (reduce_all_workspace(sm_count) + 255) / 256 * 256;
+      } else if (inner == 1) {
+        st.kind = StepK::ReduceRow;
+        st.kernel_name = "reduce_row_f32";
+      } else {
+        st.kind = StepK::ReduceCol;
+        st.kernel_name = "reduce_col_f32";
+        if (outer > 4096) throw Unsupported("batched column reduction with more than 4096 batches");
+        st.red_batch_in = len * inner;
+        st.red_batch_out = inner;
+        st.scratch.ws_off = (int64_t)ws;
+        ws += (reduce_col_workspace(len, inner, sm_count) + 255) / 256 * 256;
+      }
+      for (size_t d : runs[ri]) shape[d] = 1;
+      src = to;
+      if (ri > 0) plan.steps.push_back(std::move(st));
     }
     plan.steps.push_back(std::move(st));
     if (pending_narrow) {

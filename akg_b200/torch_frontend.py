@@ -350,9 +350,45 @@ _MATMULS = (aten.mm.default, aten.bmm.default, aten.addmm.default)
 _REDUCTIONS = (aten.sum.dim_IntList, aten.sum.default, aten.amax.default, aten.amin.default, aten.mean.dim)
 
 
+def _dims_of(x, dim):
+    if dim is None or (isinstance(dim, (list, tuple)) and len(dim) == 0):
+        return list(range(x.dim()))
+    return [dim] if isinstance(dim, int) else list(dim)
+
+
+def _var_correction(x, dim=None, *, correction=None, keepdim=False):
+    dims = _dims_of(x, dim)
+    n = math.prod(x.shape[d] for d in dims)
+    c = 1 if correction is None else correction
+    xf = x.float() if x.dtype in (torch.float16, torch.bfloat16) else x
+    d = xf - xf.mean(dims, keepdim=True)
+    return ((d * d).sum(dims, keepdim=keepdim) / max(n - c, 0)).to(x.dtype)
+
+
+def _std_correction(x, dim=None, *, correction=None, keepdim=False):
+    return torch.sqrt(_var_correction(x, dim, correction=correction, keepdim=keepdim))
+
+
+def _logsumexp(x, dim, keepdim=False):
+    dims = _dims_of(x, dim)
+    m = x.amax(dims, keepdim=True)
+    out = torch.log(torch.exp(x - m).sum(dims, keepdim=True)) + m
+    return out if keepdim else out.squeeze(dims)
+
+
+def _vector_norm(x, ord=2, dim=None, keepdim=False, *, dtype=None):
+    if ord != 2 or dtype is not None:
+        return NotImplemented
+    return torch.sqrt((x * x).sum(_dims_of(x, dim), keepdim=keepdim))
+
+
 def _decompositions():
     from torch._decomp import get_decompositions
     table = _stock_decompositions()
+    table[aten.var.correction] = _var_correction
+    table[aten.std.correction] = _std_correction
+    table[aten.logsumexp.default] = _logsumexp
+    table[aten.linalg_vector_norm.default] = _vector_norm
     table[aten.native_layer_norm.default] = _native_layer_norm
     table[aten.split.Tensor] = _split                       # pieces become slices the library takes
     table[aten.split_with_sizes.default] = _split_with_sizes

@@ -800,3 +800,22 @@ def test_two_column_reductions_share_one_pass(lib):
         assert np.all(np.abs(g_.astype(np.float64) - w_) <= bd + 1e-6)
     if FLAGS[0] == 0:
         assert kern.meta()["template"] == "akgb_col_jit"
+
+
+def test_reduction_over_non_adjacent_axes(lib):
+    rng = np.random.default_rng(99)
+    f = "float32"
+    for shape, axes, keep in (([6, 40, 50], [0, 2], True), ([3, 4, 5, 64], [1, 3], False), ([5, 7, 1, 9], [0, 3], False)):
+        oshape = [1 if i in axes else e for i, e in enumerate(shape)] if keep else [e for i, e in enumerate(shape) if i not in axes]
+        for op in ("ReduceSum", "ReduceMax"):
+            b = _Builder("Fused_Reduce_non_adjacent_99")
+            x = b.input("x", shape, f)
+            b.output(b.emit(op, [x], oshape, f, _reduce_attr(axes, keep)))
+            d = b.build()
+            xv = rng.standard_normal(shape).astype(np.float32)
+            got, _ = run(d, [xv])
+            want = O.evaluate(d, [xv], accum="float64")[0]
+            if op == "ReduceMax":
+                assert bits_equal(got[0], want)
+            else:
+                assert np.all(np.abs(got[0].astype(np.float64) - want) <= 1e-5 * np.abs(xv).sum(axis=tuple(axes), keepdims=keep))

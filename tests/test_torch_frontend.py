@@ -78,6 +78,28 @@ def transformer_inputs(dtype, gen, bsz=2, seq=128, dim=256):
     return ins
 
 
+def _g(seed=0):
+    return torch.Generator().manual_seed(seed)
+
+
+MORE = {
+    "softmax_dim1": (lambda x: torch.softmax(x, dim=1), lambda g: [torch.randn(4, 16, 32, generator=g)]),
+    "center_over_axes_0_2": (lambda x: (x - x.mean(dim=(0, 2), keepdim=True)) * 2,
+                             lambda g: [torch.randn(4, 16, 32, generator=g)]),
+    "var_unbiased": (lambda x: x.var(dim=-1), lambda g: [torch.randn(8, 64, generator=g)]),
+    "std_keepdim": (lambda x: x / (x.std(dim=-1, keepdim=True) + 1e-3), lambda g: [torch.randn(8, 64, generator=g)]),
+    "silu_mul": (lambda x, y: torch.nn.functional.silu(x) * y,
+                 lambda g: [torch.randn(8, 64, generator=g), torch.randn(8, 64, generator=g)]),
+    "logsumexp": (lambda x: torch.logsumexp(x, dim=-1), lambda g: [torch.randn(8, 64, generator=g)]),
+    "cat_slice": (lambda x, y: torch.cat([x, y], dim=1)[:, 3:50:2] + 1,
+                  lambda g: [torch.randn(8, 30, generator=g), torch.randn(8, 40, generator=g)]),
+    "int_ops": (lambda i: (i * 3 + 1).float() / 2, lambda g: [torch.randint(-5, 5, (8, 16), generator=g, dtype=torch.int32)]),
+    "bmm_transposed": (lambda a, b: torch.relu(a @ b.transpose(1, 2)),
+                       lambda g: [torch.randn(3, 16, 24, generator=g), torch.randn(3, 8, 24, generator=g)]),
+    "l2_normalise": (lambda x: x / x.norm(dim=-1, keepdim=True), lambda g: [torch.randn(8, 64, generator=g)]),
+}
+
+
 CASES = {
     "gelu_bias": (gelu_bias, lambda g: [torch.randn(4, 64, 128, generator=g), torch.randn(128, generator=g) * 0.02,
                                        torch.randn(4, 64, 128, generator=g)], 1e-5),
@@ -226,3 +248,24 @@ def test_transformer_block_on_the_device(dtype, tol):
     from akg_b200.driver import FusedKernel
     launches = sum(FusedKernel(s.desc_json).launch_count for s in fused.subgraphs)
     assert launches <= 22
+
+
+@pytest.mark.parametrize("name", list(MORE))
+def test_more_programs_on_the_checker(name):
+    fn, make = MORE[name]
+    ins = make(_g(0))
+    fused = TF.fuse_and_optimize(fn, ins, executor=oracle_executor)
+    assert fused.subgraphs
+    _close(fused(*ins), fn(*ins), 2e-6)
+    from akg_b200.driver import FusedKernel
+    for sub in fused.subgraphs:  # every cluster is something the library plans
+        assert FusedKernel(sub.desc_json).launch_count >= 1
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", list(MORE))
+def test_more_programs_on_the_device(name):
+    fn, make = MORE[name]
+    ins = [t.cuda() for t in make(_g(1))]
+    fused = TF.fuse_and_optimize(fn, ins)
+    _close(fused(*ins), fn(*ins), 2e-5)
