@@ -731,6 +731,9 @@ bool fused_reduce_all_plan(const Graph& g, int sm_count, Plan* out) {
       c = cand;
       break;
     }
+  // no such divisor: any divisor will do (element-wise accesses instead of 16-byte ones, still one pass)
+  for (int64_t cand = 4096; c == 0 && cand >= 64; --cand)
+    if (n % cand == 0) c = cand;
   if (c == 0) return false;
   const int64_t r = n / c;
   Graph g2 = g;
