@@ -277,3 +277,14 @@ def test_planning_of_the_wider_op_surface(lib):
     g = b.emit("Gather", [table, idx], [40, 16], f, [_attr("axis", "int", 0), _attr("batch_dims", "int", 0)])
     b.output(b.emit("UnsortedSegmentSum", [g, idx], [7, 16], f, [_attr("num_segments", "int", 7)]))
     assert FusedKernel(b.build()).launch_count == 2
+
+
+def test_generated_kernels_shard_like_the_templates(lib):
+    from akg_b200 import FusedKernel, _capi, descs
+    k = FusedKernel(descs.rmsnorm(4096, 1024), shard_rank=1, shard_world=4)
+    assert k.meta()["template"] == "akgb_row_jit"
+    assert k.inputs[0].shape == (1024, 1024) and k.inputs[0].shard_kind == _capi.SHARD_SPLIT_AXIS0
+    assert k.inputs[1].shard_kind == _capi.SHARD_REPLICATED and k.outputs[0].shard_kind == _capi.SHARD_SPLIT_AXIS0
+    kc = FusedKernel(descs.mul_reduce_sum(8192, 512, [0]), shard_rank=0, shard_world=2)
+    assert kc.meta()["template"] == "akgb_col_jit" and kc.inputs[0].shape == (4096, 512)
+    assert kc.outputs[0].shard_kind == _capi.SHARD_PARTIAL_SUM
