@@ -333,6 +333,13 @@ bool strided_vec8_ok(const EwProgram& P, const EwOperand& o) {
   return true;
 }
 
+// 8 consecutive elements of the iteration space read ONE element of the operand: the operand does not move along the
+// innermost dimension and rows of that dimension hold whole granules
+bool strided_run8_const(const EwProgram& P, const EwOperand& o) {
+  const int last = P.rank - 1;
+  return last >= 0 && P.shape[last] % 8 == 0 && o.stride[last] == 0;
+}
+
 bool generate(const EwProgram& P, bool vec, std::string* out) {
   for (int i = 0; i < P.n_out; ++i)
     if (P.out[i].kind != EWI_FULL && P.out[i].kind != EWI_STRIDED) return false;
@@ -377,6 +384,10 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
       else if (o.kind == EWI_MOD)
         s << "      #pragma unroll\n      for (int j = 0; j < 8; ++j) a" << i << "[u][j] = ld1_" << tag << "(in" << i
           << ", (v * 8 + j) % " << o.mod << "LL);\n";
+      else if (o.kind == EWI_STRIDED && strided_run8_const(P, o))  // one value for the whole granule (a per-channel operand)
+        s << "      { const " << (is_float_dt(o.dt) ? "float" : "int") << " t = ld1_" << tag << "(in" << i << ", "
+          << strided_index(P, o, "(v * 8)") << ");\n        #pragma unroll\n        for (int j = 0; j < 8; ++j) a" << i
+          << "[u][j] = t; }\n";
       else if (o.kind == EWI_STRIDED && strided_vec8_ok(P, o))
         s << "      ld8_" << tag << "(in" << i << ", " << strided_index(P, o, "(v * 8)") << ", a" << i << "[u], false);\n";
       else if (o.kind == EWI_STRIDED)

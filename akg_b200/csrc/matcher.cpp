@@ -896,6 +896,184 @@ bool fused_reduce_col_plan(const Graph& g, int sm_count, Plan* out) {
   return true;
 }
 
+// producer / users links of every value, recomputed from the op list (after ops were removed or rewired)
+void relink(Graph& g) {
+  for (auto& v : g.values) {
+    v.producer = -1;
+    v.users.clear();
+  }
+  for (size_t i = 0; i < g.nodes.size(); ++i) {
+    g.values[g.nodes[i].out].producer = (int)i;
+    for (int vid : g.nodes[i].in) g.values[vid].users.push_back((int)i);
+  }
+}
+
+void shift_ref(Ref& r, const std::vector<Ref>& args, int64_t ws_base) {
+  if (r.arg >= 0) r = args[r.arg];
+  else if (r.ws_off >= 0) r.ws_off += ws_base;
+}
+
+// An elementwise chain over equally shaped tensors, ONE reduction whose axes include the trailing axes, then anything on
+// the reduced values (BatchNorm statistics on NCHW: Mul(x, x) -> ReduceSum over (0, 2, 3) -> Mul(1/n)).  The chain and
+// the fold over the trailing axes run as one generated row kernel on the [rows, cols] view; what remains (a reduction
+// over the other axes, the ops behind it) is planned on its own with the row results as its input.
+bool fused_reduce_tail_plan(const Graph& g, int sm_count, bool allow_jit, Plan* out) {
+  if (g.dynamic || g.nodes.size() < 2) return false;
+  int ri = -1;
+  for (size_t i = 0; i < g.nodes.size(); ++i)
+    if (opk_is_reduce(g.nodes[i].kind)) {
+      ri = (int)i;
+      break;
+    }
+  if (ri < 1) return false;  // no chain in front of the reduction: the hand-written reductions do it
+  const Node& red = g.nodes[ri];
+  if (red.kind != OpK::ReduceSum && red.kind != OpK::ReduceMax && red.kind != OpK::ReduceMin && red.kind != OpK::ReduceProd)
+    return false;
+  const Value& x = g.v(red.in[0]);
+  const size_t rank = x.shape.size();
+  if (x.dt != DT::F32 || g.v(red.out).dt != DT::F32 || rank == 0) return false;
+  std::vector<bool> is_red(rank, false);
+  for (auto a : red.axes) is_red[a] = true;
+  // the trailing run: from the last axis backwards while the axis is reduced (extent-1 axes ride along)
+  size_t first = rank;
+  while (first > 0 && (is_red[first - 1] || x.shape[first - 1] == 1)) --first;
+  int64_t C = 1, n = x.numel();
+  for (size_t i = first; i < rank; ++i) C *= x.shape[i];
+  if (first == 0 || C < 8 || C > 16384 || n < (1 << 16)) return false;  // all axes: the re-viewed plan above
+  const int64_t R = n / C;
+  // the chain: elementwise ops over tensors of exactly x's element count, none of them a result of the region
+  for (int i = 0; i < ri; ++i) {
+    const Node& nd = g.nodes[i];
+    if (!opk_is_elementwise(nd.kind) || nd.kind == OpK::AddN) return false;
+    const Value& ov = g.v(nd.out);
+    if (ov.numel() != n || ov.shape != x.shape || ov.output_index >= 0) return false;
+    for (int vid : nd.in)
+      if (!g.v(vid).is_const && g.v(vid).shape != x.shape) return false;
+    for (int u : ov.users)
+      if (u > ri) return false;  // the chain's values are not kept for the ops behind the reduction
+  }
+  // 1. the row program: chain + reduction over the trailing run on the [R, C] view
+  Graph g2 = g;
+  g2.nodes.resize(ri + 1);
+  for (auto& v : g2.values) {
+    v.output_index = -1;
+    if (!v.is_const && v.shape == x.shape) v.shape = {R, C};
+  }
+  Node& red2 = g2.nodes.back();
+  red2.axes = {1};
+  red2.keep_dims = false;
+  g2.v(red2.out).shape = {R};
+  g2.v(red2.out).output_index = 0;
+  g2.outputs = {red2.out};
+  relink(g2);
+  auto rp = std::make_shared<RowProgram>();
+  std::vector<int> in_values, out_values;
+  if (!build_row_program(g2, rp.get(), &in_values, &out_values) || out_values.size() != 1) return false;
+  bool only_trailing = true;
+  for (auto a : red.axes) only_trailing = only_trailing && ((size_t)a >= first || x.shape[a] == 1);
+  if (only_trailing && (size_t)ri + 1 == g.nodes.size() && g.outputs.size() == 1 && g.outputs[0] == red.out) {
+    // nothing behind the fold over the trailing axes: the row results are the region's result
+    Plan p;
+    p.klass = "reduce_x";
+    Step st;
+    st.kind = StepK::RowJit;
+    st.kernel_name = "akgb_row_jit";
+    st.row = rp;
+    for (int vid : in_values) {
+      Ref ref;
+      ref.arg = g.v(vid).input_index;
+      st.ew_in.push_back(ref);
+    }
+    Ref result;
+    result.arg = (int)g.inputs.size();
+    st.ew_out.push_back(result);
+    p.steps.push_back(std::move(st));
+    *out = std::move(p);
+    return true;
+  }
+  // 2. the rest: the row results stand in for the reduction's operand, with the trailing run folded to extent 1
+  Graph g3 = g;
+  g3.nodes.erase(g3.nodes.begin(), g3.nodes.begin() + ri);
+  Value part;
+  part.name = "akgb_row_results";
+  part.shape = x.shape;
+  for (size_t i = first; i < rank; ++i) part.shape[i] = 1;
+  part.dt = DT::F32;
+  const int pid = (int)g3.values.size();
+  g3.values.push_back(part);
+  Node& red3 = g3.nodes.front();
+  red3.in[0] = pid;
+  std::vector<int64_t> rest_axes;
+  for (auto a : red.axes)
+    if ((size_t)a < first && x.shape[a] != 1) rest_axes.push_back(a);
+  if (rest_axes.empty()) {
+    red3.kind = OpK::Reshape;  // nothing left to fold: the row results are the reduction's result
+    red3.name = "Reshape";
+    red3.axes.clear();
+  } else {
+    red3.axes = rest_axes;
+  }
+  relink(g3);
+  // inputs of the rest: the row results first, then the region's inputs it still reads
+  std::vector<Ref> arg_map;
+  Ref partial;
+  partial.ws_off = 0;
+  arg_map.push_back(partial);
+  std::vector<int> new_inputs = {pid};
+  for (int vid : g.inputs) {
+    if (g3.values[vid].users.empty()) {
+      g3.values[vid].input_index = -1;
+      continue;
+    }
+    Ref r;
+    r.arg = g.v(vid).input_index;
+    arg_map.push_back(r);
+    g3.values[vid].input_index = (int)new_inputs.size();
+    new_inputs.push_back(vid);
+  }
+  g3.values[pid].input_index = 0;
+  g3.inputs = new_inputs;
+  for (int vid : g3.outputs)
+    if (g3.values[vid].producer < 0) return false;  // a result that is not produced behind the reduction
+  for (size_t i = 0; i < g.outputs.size(); ++i) {
+    Ref r;
+    r.arg = (int)g.inputs.size() + (int)i;
+    arg_map.push_back(r);
+  }
+  classify(g3);
+  Plan rest;
+  try {
+    rest = build_plan(g3, sm_count, allow_jit);
+  } catch (const Unsupported&) {
+    return false;
+  }
+  if (rest.fallback) return false;  // keep it to plans with one way of running
+  const int64_t ws_base = (int64_t)(((size_t)R * sizeof(float) + 255) / 256 * 256);
+  Plan p;
+  p.klass = g.reduce_dir == ReduceDir::All ? "reduce_all" : g.reduce_dir == ReduceDir::Y ? "reduce_y" : "reduce_x";
+  Step st;
+  st.kind = StepK::RowJit;
+  st.kernel_name = "akgb_row_jit";
+  st.row = rp;
+  for (int vid : in_values) {
+    Ref ref;
+    ref.arg = g.v(vid).input_index;
+    st.ew_in.push_back(ref);
+  }
+  st.ew_out.push_back(partial);
+  p.steps.push_back(std::move(st));
+  for (Step& s2 : rest.steps) {
+    for (Ref* r : {&s2.a, &s2.b, &s2.c, &s2.out, &s2.out2, &s2.out3, &s2.scratch}) shift_ref(*r, arg_map, ws_base);
+    for (Ref& r : s2.ew_in) shift_ref(r, arg_map, ws_base);
+    for (Ref& r : s2.ew_out) shift_ref(r, arg_map, ws_base);
+    p.steps.push_back(std::move(s2));
+  }
+  p.workspace_bytes = (size_t)ws_base + rest.workspace_bytes;
+  p.needs_gelu_lut = rest.needs_gelu_lut;
+  *out = std::move(p);
+  return true;
+}
+
 Plan build_plan(const Graph& g, int sm_count, bool allow_jit) {
   for (auto& n : g.nodes)
     if (n.kind == OpK::Unknown)
@@ -945,7 +1123,8 @@ Plan build_plan(const Graph& g, int sm_count, bool allow_jit) {
       fused.fallback = std::make_shared<Plan>(std::move(plan));
       plan = std::move(fused);
     } else if (Plan fused; allow_jit && plan.steps.size() >= 2 &&
-               (fused_reduce_all_plan(g, sm_count, &fused) || fused_reduce_col_plan(g, sm_count, &fused))) {
+               (fused_reduce_all_plan(g, sm_count, &fused) || fused_reduce_col_plan(g, sm_count, &fused) ||
+                fused_reduce_tail_plan(g, sm_count, allow_jit, &fused))) {
       fused.workspace_bytes = std::max(fused.workspace_bytes, plan.workspace_bytes);
       fused.flops = plan.flops;
       fused.fallback = std::make_shared<Plan>(std::move(plan));

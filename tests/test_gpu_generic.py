@@ -819,3 +819,42 @@ def test_reduction_over_non_adjacent_axes(lib):
                 assert bits_equal(got[0], want)
             else:
                 assert np.all(np.abs(got[0].astype(np.float64) - want) <= 1e-5 * np.abs(xv).sum(axis=tuple(axes), keepdims=keep))
+
+
+def test_chain_then_reduction_over_trailing_and_leading_axes(lib):
+    """BatchNorm statistics on NCHW: Mul(x, x) -> ReduceSum over (0, 2, 3) -> Mul(1/n).  The square and the fold over
+    (H, W) run as one generated row kernel, the fold over N and the scaling on the row results."""
+    rng = np.random.default_rng(101)
+    f = "float32"
+    n_, c_, h_, w_ = 8, 32, 28, 28
+    shape = [n_, c_, h_, w_]
+    for keep in (True, False):
+        oshape = [1, c_, 1, 1] if keep else [c_]
+        b = _Builder("Fused_Mul_ReduceSum_Mul_101")
+        x = b.input("x", shape, f)
+        y = b.input("y", shape, f)
+        t = b.emit("Mul", [b.emit("Sub", [x, y], shape, f), x], shape, f)
+        s_ = b.emit("ReduceSum", [t], oshape, f, _reduce_attr([0, 2, 3], keep))
+        b.output(b.emit("Mul", [s_, b.const(1.0 / (n_ * h_ * w_), f)], oshape, f))
+        b.output(s_)
+        d = b.build()
+        ins = [rng.standard_normal(shape).astype(np.float32) for _ in range(2)]
+        got, kern = run(d, ins)
+        want = O.evaluate(d, ins, accum="float64")
+        full = (ins[0].astype(np.float64) - ins[1]) * ins[0]
+        bound = 1e-5 * np.abs(full).sum(axis=(0, 2, 3), keepdims=keep)
+        assert np.all(np.abs(got[1].astype(np.float64) - want[1]) <= bound)
+        assert np.all(np.abs(got[0].astype(np.float64) - want[0]) <= bound / (n_ * h_ * w_) + 1e-7)
+        if FLAGS[0] == 0:
+            assert kern.meta()["template"] == "akgb_row_jit"
+    # trailing axes only, over a multi-dimensional run: max over (H, W) of a difference
+    b = _Builder("Fused_Sub_ReduceMax_102")
+    x = b.input("x", shape, f)
+    y = b.input("y", shape, f)
+    b.output(b.emit("ReduceMax", [b.emit("Sub", [x, y], shape, f)], [n_, c_], f, _reduce_attr([2, 3], False)))
+    d = b.build()
+    ins = [rng.standard_normal(shape).astype(np.float32) for _ in range(2)]
+    got, kern = run(d, ins)
+    assert bits_equal(got[0], O.evaluate(d, ins)[0])
+    if FLAGS[0] == 0:
+        assert kern.meta()["template"] == "akgb_row_jit" and kern.launch_count == 1
