@@ -585,7 +585,10 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
     name[o.val] = v;
     is_float[o.val] = fl;
     if (o.kind == RK_ROW || o.kind == RK_SCALAR) {
-      s << "  const " << ty << " " << v << " = ld1_" << tag << "(in" << i << ", " << (o.kind == RK_ROW ? "r" : "0") << ");\n";
+      std::string idx = o.kind == RK_ROW ? "r" : "0";
+      if (o.kind == RK_ROW && o.row_mod != 0)
+        idx = "(r / " + std::to_string(o.row_div) + "LL) % " + std::to_string(o.row_mod) + "LL";
+      s << "  const " << ty << " " << v << " = ld1_" << tag << "(in" << i << ", " << idx << ");\n";
       continue;
     }
     std::string base = o.kind == RK_FULL ? "r * C" : o.kind == RK_COL ? "(i64)0" : "(r % " + std::to_string(o.mod_rows) + "LL) * C";

@@ -80,6 +80,7 @@ struct RowOperand {
   int32_t kind = RK_FULL;
   int32_t val = 0;  // value loaded into / stored from
   int64_t mod_rows = 0;
+  int64_t row_div = 1, row_mod = 0;  // RK_ROW read through (row / row_div) % row_mod when row_mod != 0 (a per-channel value)
   int32_t red_op = 0;  // column mode results: 0 sum, 1 max, 2 min, 3 prod over the rows of `val`
 };
 

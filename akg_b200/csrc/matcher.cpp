@@ -942,13 +942,34 @@ bool fused_reduce_tail_plan(const Graph& g, int sm_count, bool allow_jit, Plan* 
   if (first == 0 || C < 8 || C > 16384 || n < (1 << 16)) return false;  // all axes: the re-viewed plan above
   const int64_t R = n / C;
   // the chain: elementwise ops over tensors of exactly x's element count, none of them a result of the region
+  std::map<int, std::pair<int64_t, int64_t>> row_index;
   for (int i = 0; i < ri; ++i) {
     const Node& nd = g.nodes[i];
     if (!opk_is_elementwise(nd.kind) || nd.kind == OpK::AddN) return false;
     const Value& ov = g.v(nd.out);
     if (ov.numel() != n || ov.shape != x.shape || ov.output_index >= 0) return false;
-    for (int vid : nd.in)
-      if (!g.v(vid).is_const && g.v(vid).shape != x.shape) return false;
+    for (int vid : nd.in) {
+      const Value& v = g.v(vid);
+      if (v.is_const || v.shape == x.shape) continue;
+      // a region input that varies along one block of the row axes only (a per-channel [1, C, 1, 1] value): read through
+      // (row / div) % mod
+      if (v.input_index < 0 || v.shape.size() != rank) return false;
+      size_t lo = rank, hi = 0;
+      for (size_t d = 0; d < rank; ++d) {
+        if (v.shape[d] == 1) continue;
+        if (d >= first || v.shape[d] != x.shape[d]) return false;
+        lo = std::min(lo, d);
+        hi = std::max(hi, d + 1);
+      }
+      if (lo >= hi) continue;  // one element: a scalar operand
+      int64_t div = 1, mod = 1;
+      for (size_t d = lo; d < hi; ++d) {
+        if (v.shape[d] != x.shape[d]) return false;  // the block has no gaps
+        mod *= x.shape[d];
+      }
+      for (size_t d = hi; d < first; ++d) div *= x.shape[d];
+      row_index[vid] = {div, mod};
+    }
     for (int u : ov.users)
       if (u > ri) return false;  // the chain's values are not kept for the ops behind the reduction
   }
@@ -968,7 +989,7 @@ bool fused_reduce_tail_plan(const Graph& g, int sm_count, bool allow_jit, Plan* 
   relink(g2);
   auto rp = std::make_shared<RowProgram>();
   std::vector<int> in_values, out_values;
-  if (!build_row_program(g2, rp.get(), &in_values, &out_values) || out_values.size() != 1) return false;
+  if (!build_row_program(g2, rp.get(), &in_values, &out_values, false, &row_index) || out_values.size() != 1) return false;
   bool only_trailing = true;
   for (auto a : red.axes) only_trailing = only_trailing && ((size_t)a >= first || x.shape[a] == 1);
   if (only_trailing && (size_t)ri + 1 == g.nodes.size() && g.outputs.size() == 1 && g.outputs[0] == red.out) {

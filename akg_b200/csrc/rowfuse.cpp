@@ -32,7 +32,7 @@ std::vector<int64_t> strip_leading_ones(std::vector<int64_t> s) {
 }  // namespace
 
 bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_values, std::vector<int>* out_values,
-                       bool col_mode) {
+                       bool col_mode, const std::map<int, std::pair<int64_t, int64_t>>* row_index) {
   if (g.dynamic || g.nodes.empty()) return false;
   // the row shape comes from the first reduction
   const Node* first_red = nullptr;
@@ -114,9 +114,14 @@ bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_val
     }
     if (v.input_index < 0) return false;  // produced by an op this builder did not take
     int64_t mod_rows = 0;
-    const int kind = shape_kind(v.shape, &mod_rows);
-    if (kind < 0) return false;
+    int kind = shape_kind(v.shape, &mod_rows);
     RowOperand o;
+    if (row_index && row_index->count(vid)) {  // the caller knows how the rows index this operand
+      kind = RK_ROW;
+      o.row_div = row_index->at(vid).first;
+      o.row_mod = row_index->at(vid).second;
+    }
+    if (kind < 0) return false;
     o.dt = (int)v.dt;
     o.kind = kind;
     o.mod_rows = mod_rows;

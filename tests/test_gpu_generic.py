@@ -858,3 +858,28 @@ def test_chain_then_reduction_over_trailing_and_leading_axes(lib):
     assert bits_equal(got[0], O.evaluate(d, ins)[0])
     if FLAGS[0] == 0:
         assert kern.meta()["template"] == "akgb_row_jit" and kern.launch_count == 1
+
+
+def test_per_channel_operands_in_front_of_a_batchnorm_style_reduction(lib):
+    """dgamma = sum over (N, H, W) of dy * (x - mean) * rstd with mean, rstd of shape [1, C, 1, 1], and dbeta = sum of dy."""
+    rng = np.random.default_rng(103)
+    f = "float32"
+    shape, stat = [6, 24, 20, 24], [1, 24, 1, 1]
+    b = _Builder("Fused_Sub_Mul_Mul_ReduceSum_ReduceSum_103")
+    dy, x = b.input("dy", shape, f), b.input("x", shape, f)
+    mean, rstd = b.input("mean", stat, f), b.input("rstd", stat, f)
+    xhat = b.emit("Mul", [b.emit("Sub", [x, mean], shape, f), rstd], shape, f)
+    b.output(b.emit("ReduceSum", [b.emit("Mul", [dy, xhat], shape, f)], stat, f, _reduce_attr([0, 2, 3], True)))
+    b.output(b.emit("ReduceSum", [dy], stat, f, _reduce_attr([0, 2, 3], True)))
+    d = b.build()
+    ins = [rng.standard_normal(shape).astype(np.float32), rng.standard_normal(shape).astype(np.float32),
+           rng.standard_normal(stat).astype(np.float32), rng.uniform(0.5, 2.0, stat).astype(np.float32)]
+    got, kern = run(d, ins)
+    want = O.evaluate(d, ins, accum="float64")
+    dy64, x64 = ins[0].astype(np.float64), ins[1].astype(np.float64)
+    terms = np.abs(dy64 * (x64 - ins[2]) * ins[3])
+    assert np.all(np.abs(got[0] - want[0]) <= 1e-5 * terms.sum(axis=(0, 2, 3), keepdims=True))
+    assert np.all(np.abs(got[1] - want[1]) <= 1e-5 * np.abs(dy64).sum(axis=(0, 2, 3), keepdims=True))
+    if FLAGS[0] == 0:
+        assert kern.meta()["template"] == "akgb_row_jit"
+        assert "(r / 1LL) % 24LL" in kern.jit_source()
