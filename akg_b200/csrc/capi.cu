@@ -73,6 +73,7 @@ struct akgb_kernel {
   // host-pointer entry points: staging buffers kept between calls
   std::vector<void*> d_tensors;
   void* d_workspace = nullptr;
+  size_t d_workspace_bytes = 0;
   cudaStream_t stream = nullptr;
   bool staged = false;
   // chunked pipeline of akgb_run_host: the same region planned on 1/nchunks of axis 0, so that the
@@ -120,8 +121,20 @@ void* resolve(const Ref& r, void* const* tensors, void* ws) {
   return nullptr;
 }
 
-akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws, cudaStream_t s) {
-  if (plan.fallback && plan.use_fallback) return run_plan(k, *plan.fallback, tensors, ws, s);
+// switches a plan whose generated kernel cannot be built on this host to its separate launches, if the caller's
+// workspace is large enough for them (akgb_workspace_size reports what the generated kernel needs)
+akgb_status enter_fallback(Plan& plan, size_t ws_bytes) {
+  if (ws_bytes < plan.fallback->workspace_bytes)
+    return fail(AKGB_UNSUPPORTED,
+                "the kernel generated for this region could not be compiled on this host and the workspace is too small "
+                "for the separate launches (" + std::to_string(plan.fallback->workspace_bytes) +
+                " bytes): compile the region with AKGB_FLAG_NO_JIT");
+  plan.use_fallback = true;
+  return AKGB_OK;
+}
+
+akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws, size_t ws_bytes, cudaStream_t s) {
+  if (plan.fallback && plan.use_fallback) return run_plan(k, *plan.fallback, tensors, ws, ws_bytes, s);
   DeviceState& ds = g_dev[k->device];
   for (Step& st : plan.steps) {
     cudaError_t e = cudaSuccess;
@@ -166,8 +179,9 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
         e = row_jit_launch(*st.row, ins, outs, s, &st.dims);
         if (e == cudaErrorNotSupported && plan.fallback) {  // no run-time compiler here: the separate launches
           // (the generated kernel is always the plan's first step, so nothing has been enqueued yet)
-          plan.use_fallback = true;
-          return run_plan(k, *plan.fallback, tensors, ws, s);
+          const akgb_status fs = enter_fallback(plan, ws_bytes);
+          if (fs != AKGB_OK) return fs;
+          return run_plan(k, *plan.fallback, tensors, ws, ws_bytes, s);
         }
         break;
       }
@@ -178,8 +192,9 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
         for (size_t i = 0; i < st.ew_out.size() && i < 4; ++i) parts[i] = (float*)resolve(st.ew_out[i], tensors, ws);
         e = col_jit_launch(*st.row, ins, parts, st.red_len, s, &st.dims);
         if (e == cudaErrorNotSupported && plan.fallback) {
-          plan.use_fallback = true;
-          return run_plan(k, *plan.fallback, tensors, ws, s);
+          const akgb_status fs = enter_fallback(plan, ws_bytes);
+          if (fs != AKGB_OK) return fs;
+          return run_plan(k, *plan.fallback, tensors, ws, ws_bytes, s);
         }
         break;
       }
@@ -329,7 +344,7 @@ akgb_status run_host_chunked(akgb_kernel* k, void* const* host) {
     cudaStreamWaitEvent(k->stream, k->ev_in[c], 0);
     for (size_t i = 0; i < nt; ++i)
       ptrs[i] = k->chunk_split[i] ? (void*)((char*)k->d_tensors[i] + (size_t)c * k->chunk_bytes[i]) : k->d_tensors[i];
-    akgb_status st = run_plan(k, k->chunk_plan, ptrs.data(), k->d_workspace, k->stream);
+    akgb_status st = run_plan(k, k->chunk_plan, ptrs.data(), k->d_workspace, k->d_workspace_bytes, k->stream);
     if (st != AKGB_OK) return st;
     cudaEventRecord(k->ev_done[c], k->stream);
     cudaStreamWaitEvent(k->s_out, k->ev_done[c], 0);
@@ -357,8 +372,10 @@ akgb_status stage(akgb_kernel* k) {
     e = cudaMalloc(&k->d_tensors[i], bytes);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(staging tensor)");
   }
-  if (k->plan.workspace_bytes) {
-    e = cudaMalloc(&k->d_workspace, k->plan.workspace_bytes);
+  // the host-pointer path owns its workspace: large enough for the separate launches too
+  k->d_workspace_bytes = std::max(k->plan.workspace_bytes, k->plan.fallback ? k->plan.fallback->workspace_bytes : (size_t)0);
+  if (k->d_workspace_bytes) {
+    e = cudaMalloc(&k->d_workspace, k->d_workspace_bytes);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(workspace)");
   }
   e = cudaStreamCreateWithFlags(&k->stream, cudaStreamNonBlocking);
@@ -542,7 +559,7 @@ extern "C" akgb_status akgb_launch_dynamic(akgb_kernel* k, void* const* tensors,
     return fail(AKGB_MISALIGNED, "workspace must be 256-byte aligned");
   st = ensure_device_state(k, b->plan.needs_gelu_lut);
   if (st != AKGB_OK) return st;
-  return run_plan(k, b->plan, tensors, workspace, reinterpret_cast<cudaStream_t>(stream));
+  return run_plan(k, b->plan, tensors, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
 }
 
 akgb_status akgb_launch(akgb_kernel* k, void* const* tensors, void* workspace, size_t workspace_bytes, void* stream) {
@@ -557,7 +574,7 @@ akgb_status akgb_launch(akgb_kernel* k, void* const* tensors, void* workspace, s
     return fail(AKGB_MISALIGNED, "workspace must be 256-byte aligned");
   akgb_status st = ensure_device_state(k, k->plan.needs_gelu_lut);
   if (st != AKGB_OK) return st;
-  return run_plan(k, k->plan, tensors, workspace, reinterpret_cast<cudaStream_t>(stream));
+  return run_plan(k, k->plan, tensors, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
 }
 
 akgb_status akgb_run_host(akgb_kernel* k, void* const* host) {
@@ -574,7 +591,7 @@ akgb_status akgb_run_host(akgb_kernel* k, void* const* host) {
     e = cudaMemcpyAsync(k->d_tensors[i], host[i], (size_t)k->descs[i].nbytes, cudaMemcpyHostToDevice, k->stream);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(H2D)");
   }
-  st = run_plan(k, k->plan, k->d_tensors.data(), k->d_workspace, k->stream);
+  st = run_plan(k, k->plan, k->d_tensors.data(), k->d_workspace, k->d_workspace_bytes, k->stream);
   if (st != AKGB_OK) return st;
   for (size_t i = 0; i < k->descs.size(); ++i) {
     if (!k->descs[i].nbytes) continue;
@@ -596,7 +613,7 @@ akgb_status akgb_profile_host(akgb_kernel* k, void* const* host, int32_t number,
   cudaEventCreate(&t1);
   cudaEventRecord(t0, k->stream);
   for (int i = 0; i < number * repeat; ++i) {
-    st = run_plan(k, k->plan, k->d_tensors.data(), k->d_workspace, k->stream);
+    st = run_plan(k, k->plan, k->d_tensors.data(), k->d_workspace, k->d_workspace_bytes, k->stream);
     if (st != AKGB_OK) break;
   }
   cudaEventRecord(t1, k->stream);

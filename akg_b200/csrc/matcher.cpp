@@ -1124,7 +1124,7 @@ Plan build_plan(const Graph& g, int sm_count, bool allow_jit) {
         build_row_program(g, rp.get(), &in_values, &out_values)) {
       Plan fused;
       fused.klass = plan.klass;
-      fused.workspace_bytes = plan.workspace_bytes;
+      fused.workspace_bytes = 0;  // one kernel, nothing crosses launches
       fused.flops = plan.flops;
       Step st;
       st.kind = StepK::RowJit;
@@ -1146,7 +1146,6 @@ Plan build_plan(const Graph& g, int sm_count, bool allow_jit) {
     } else if (Plan fused; allow_jit && plan.steps.size() >= 2 &&
                (fused_reduce_all_plan(g, sm_count, &fused) || fused_reduce_col_plan(g, sm_count, &fused) ||
                 fused_reduce_tail_plan(g, sm_count, allow_jit, &fused))) {
-      fused.workspace_bytes = std::max(fused.workspace_bytes, plan.workspace_bytes);
       fused.flops = plan.flops;
       fused.fallback = std::make_shared<Plan>(std::move(plan));
       plan = std::move(fused);

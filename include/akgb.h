@@ -101,7 +101,10 @@ int32_t akgb_num_tensors(const akgb_kernel* k);
 int32_t akgb_num_inputs(const akgb_kernel* k);
 akgb_status akgb_tensor_info(const akgb_kernel* k, int32_t index, akgb_tensor_desc* out);
 
-/* Bytes of device scratch a launch needs (partials of split reductions, ...). */
+/* Bytes of device scratch a launch needs (partials of split reductions, values that cross launches).  For a region that
+ * runs as a kernel generated at run time this is what that kernel needs; should the kernel fail to compile on the
+ * host, akgb_launch returns AKGB_UNSUPPORTED with the larger size the separate launches would need, and the region can
+ * be compiled with AKGB_FLAG_NO_JIT instead. */
 size_t akgb_workspace_size(const akgb_kernel* k);
 
 /* Number of device kernels one akgb_launch enqueues. */
