@@ -896,6 +896,81 @@ bool fused_reduce_col_plan(const Graph& g, int sm_count, Plan* out) {
   return true;
 }
 
+// Re-views a region whose reductions all fold the same run of TRAILING axes (InstanceNorm on NCHW: mean / variance over
+// (H, W)) as [rows, cols]: full tensors become [R, C], per-(row) values [R, 1] or [R], tensors that span only the
+// trailing axes [C], and region inputs that vary along one block of the row axes only (a per-channel [1, C, 1, 1] scale)
+// are recorded in `row_index` as (div, mod) of the row number.  Returns false when the region is not of that form.
+bool view_trailing_run(const Graph& g, Graph* gv, std::map<int, std::pair<int64_t, int64_t>>* row_index) {
+  const Node* red0 = nullptr;
+  for (auto& n : g.nodes)
+    if (opk_is_reduce(n.kind)) {
+      red0 = &n;
+      break;
+    }
+  if (!red0 || g.dynamic) return false;
+  const std::vector<int64_t> S = g.v(red0->in[0]).shape;
+  const size_t rank = S.size();
+  if (rank < 2) return false;
+  std::vector<bool> is_red(rank, false);
+  for (auto a : red0->axes) is_red[a] = true;
+  size_t first = rank;
+  while (first > 0 && (is_red[first - 1] || S[first - 1] == 1)) --first;
+  if (first == 0 || first == rank) return false;
+  for (size_t d = 0; d < first; ++d)
+    if (is_red[d] && S[d] != 1) return false;  // folds leading axes too: not a pure row region
+  int64_t R = 1, C = 1;
+  for (size_t d = 0; d < rank; ++d) (d < first ? R : C) *= S[d];
+  *gv = g;
+  for (auto& n : gv->nodes) {
+    if (!opk_is_reduce(n.kind)) continue;
+    if (g.v(n.in[0]).shape != S || n.axes != red0->axes) return false;
+    n.axes = {1};
+  }
+  const std::vector<int64_t> lead(S.begin(), S.begin() + first), trail(S.begin() + first, S.end());
+  auto strip = [](std::vector<int64_t> s) {
+    while (s.size() > 1 && s.front() == 1) s.erase(s.begin());
+    return s;
+  };
+  for (size_t vi = 0; vi < gv->values.size(); ++vi) {
+    Value& v = gv->values[vi];
+    if (v.is_const) continue;
+    const std::vector<int64_t> shp = v.shape;
+    int64_t n = 1;
+    for (auto e : shp) n *= e;
+    bool trailing_ones = shp.size() == rank;
+    for (size_t d = first; trailing_ones && d < rank; ++d) trailing_ones = shp[d] == 1;
+    if (shp == S) {
+      v.shape = {R, C};
+    } else if (n == 1) {
+      v.shape = {1};
+    } else if (trailing_ones && std::equal(lead.begin(), lead.end(), shp.begin())) {
+      v.shape = {R, 1};
+    } else if (shp == lead) {
+      v.shape = {R};
+    } else if (n == C && strip(shp) == strip(trail)) {
+      v.shape = {C};
+    } else if (trailing_ones && v.input_index >= 0) {
+      size_t lo = rank, hi = 0;
+      for (size_t d = 0; d < first; ++d) {
+        if (shp[d] == 1) continue;
+        if (shp[d] != S[d]) return false;
+        lo = std::min(lo, d);
+        hi = std::max(hi, d + 1);
+      }
+      int64_t div = 1, mod = 1;
+      for (size_t d = lo; d < hi; ++d) {
+        if (shp[d] != S[d]) return false;
+        mod *= S[d];
+      }
+      for (size_t d = hi; d < first; ++d) div *= S[d];
+      (*row_index)[(int)vi] = {div, mod};
+    } else {
+      return false;
+    }
+  }
+  return true;
+}
+
 // producer / users links of every value, recomputed from the op list (after ops were removed or rewired)
 void relink(Graph& g) {
   for (auto& v : g.values) {
@@ -1120,8 +1195,14 @@ Plan build_plan(const Graph& g, int sm_count, bool allow_jit) {
     // a reduce-X region that would take several launches: one generated row kernel, the launches as its fallback
     auto rp = std::make_shared<RowProgram>();
     std::vector<int> in_values, out_values;
-    if (allow_jit && plan.steps.size() > 1 && g.op_class == OpClass::Reduction &&
-        build_row_program(g, rp.get(), &in_values, &out_values)) {
+    Graph gv;
+    std::map<int, std::pair<int64_t, int64_t>> row_index;
+    const bool row_region =
+        allow_jit && plan.steps.size() > 1 && g.op_class == OpClass::Reduction &&
+        (build_row_program(g, rp.get(), &in_values, &out_values) ||
+         (in_values.clear(), out_values.clear(), *rp = RowProgram(), view_trailing_run(g, &gv, &row_index) &&
+          build_row_program(gv, rp.get(), &in_values, &out_values, false, &row_index)));
+    if (row_region) {
       Plan fused;
       fused.klass = plan.klass;
       fused.workspace_bytes = 0;  // one kernel, nothing crosses launches

@@ -883,3 +883,31 @@ def test_per_channel_operands_in_front_of_a_batchnorm_style_reduction(lib):
     if FLAGS[0] == 0:
         assert kern.meta()["template"] == "akgb_row_jit"
         assert "(r / 1LL) % 24LL" in kern.jit_source()
+
+
+def test_instance_norm_on_nchw_is_one_row_kernel(lib):
+    """Mean / variance over (H, W) with keep_dims, per-channel scale and shift of shape [1, C, 1, 1]."""
+    rng = np.random.default_rng(104)
+    f = "float32"
+    n_, c_, h_, w_ = 3, 20, 24, 16
+    shape, red, stat = [n_, c_, h_, w_], [n_, c_, 1, 1], [1, c_, 1, 1]
+    b = _Builder("Fused_InstanceNorm_104")
+    x, gamma, beta = b.input("x", shape, f), b.input("gamma", stat, f), b.input("beta", stat, f)
+    inv = b.const(1.0 / (h_ * w_), f)
+    mean = b.emit("Mul", [b.emit("ReduceSum", [x], red, f, _reduce_attr([2, 3], True)), inv], red, f)
+    d_ = b.emit("Sub", [x, mean], shape, f)
+    var = b.emit("Mul", [b.emit("ReduceSum", [b.emit("Mul", [d_, d_], shape, f)], red, f, _reduce_attr([2, 3], True)), inv], red, f)
+    rstd = b.emit("Rsqrt", [b.emit("Add", [var, b.const(1e-5, f)], red, f)], red, f)
+    y = b.emit("Add", [b.emit("Mul", [b.emit("Mul", [d_, rstd], shape, f), gamma], shape, f), beta], shape, f)
+    b.output(y)
+    b.output(mean)
+    d = b.build()
+    ins = [rng.standard_normal(shape).astype(np.float32), rng.uniform(0.5, 1.5, stat).astype(np.float32),
+           rng.standard_normal(stat).astype(np.float32)]
+    got, kern = run(d, ins)
+    want = O.evaluate(d, ins, accum="float64")
+    np.testing.assert_allclose(got[0], want[0], rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(got[1], want[1], rtol=1e-5, atol=1e-6)
+    if FLAGS[0] == 0:
+        assert kern.launch_count == 1 and kern.meta()["template"] == "akgb_row_jit"
+        assert f"constexpr int C = {h_ * w_}" in kern.jit_source()
