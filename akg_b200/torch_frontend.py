@@ -382,9 +382,27 @@ def _vector_norm(x, ord=2, dim=None, keepdim=False, *, dtype=None):
     return torch.sqrt((x * x).sum(_dims_of(x, dim), keepdim=keepdim))
 
 
+def _var_mean_correction(x, dim=None, *, correction=None, keepdim=False):
+    dims = _dims_of(x, dim)
+    return _var_correction(x, dim, correction=correction, keepdim=keepdim), x.mean(dims, keepdim=keepdim)
+
+
+def _rms_norm(x, normalized_shape, weight=None, eps=None):
+    dims = list(range(x.dim() - len(normalized_shape), x.dim()))
+    xf = x.float() if x.dtype in (torch.float16, torch.bfloat16) else x
+    eps = torch.finfo(x.dtype).eps if eps is None else eps
+    y = xf * torch.rsqrt((xf * xf).mean(dims, keepdim=True) + eps)
+    if weight is not None:
+        y = y * weight
+    return y.to(x.dtype)
+
+
 def _decompositions():
     from torch._decomp import get_decompositions
     table = _stock_decompositions()
+    table[aten.var_mean.correction] = _var_mean_correction
+    if hasattr(aten, "rms_norm"):
+        table[aten.rms_norm.default] = _rms_norm
     table[aten.var.correction] = _var_correction
     table[aten.std.correction] = _std_correction
     table[aten.logsumexp.default] = _logsumexp
@@ -404,6 +422,8 @@ def _stock_decompositions():
         aten.clamp, aten.clamp_min, aten.clamp_max, aten.sigmoid_backward, aten.tanh_backward,
         aten.threshold_backward, aten.gelu_backward, aten.linear, aten.matmul, aten.expand_as, aten.ones_like,
         aten.zeros_like, aten.full_like, aten.log_sigmoid_forward, aten.hardswish, aten.hardsigmoid,
+        aten.native_batch_norm, aten._native_batch_norm_legit, aten._native_batch_norm_legit_no_training,
+        aten._native_batch_norm_legit_functional, aten.native_group_norm, aten.repeat,
     ])
 
 
@@ -640,7 +660,40 @@ class FusedModule(torch.nn.Module):
 def trace(fn: Callable, example_inputs: Sequence[torch.Tensor]) -> fx.GraphModule:
     """aten-level graph of `fn` with shapes and types recorded on every node (no kernels run: fake tensors)."""
     from torch.fx.experimental.proxy_tensor import make_fx
-    return make_fx(fn, decomposition_table=_decompositions(), tracing_mode="fake")(*example_inputs)
+    # in-place ops (x.add_(1)) become their out-of-place forms first, so that they can sit inside a cluster
+    gm = make_fx(torch.func.functionalize(fn), decomposition_table=_decompositions(),
+                 tracing_mode="fake")(*example_inputs)
+    _functionalize_leftovers(gm.graph)
+    gm.recompile()
+    return gm
+
+
+_INPLACE = {}
+
+
+def _functionalize_leftovers(graph: fx.Graph) -> None:
+    """Decompositions run after functionalization and may leave in-place ops on their own temporaries
+    (``t.add_(eps)``): each becomes its out-of-place form, and later readers of the temporary read the result."""
+    if not _INPLACE:
+        for name in ("add", "sub", "mul", "div", "clamp_min", "clamp_max", "clamp", "relu", "neg", "exp", "sqrt",
+                     "rsqrt", "tanh", "sigmoid", "pow", "abs"):
+            packet, inplace = getattr(aten, name, None), getattr(aten, name + "_", None)
+            if packet is None or inplace is None:
+                continue
+            for overload in inplace.overloads():
+                if hasattr(packet, overload):
+                    _INPLACE[getattr(inplace, overload)] = getattr(packet, overload)
+    order = {n: i for i, n in enumerate(graph.nodes)}
+    for node in list(graph.nodes):
+        if node.op != "call_function" or node.target not in _INPLACE:
+            continue
+        target = node.args[0]
+        if not isinstance(target, fx.Node) or target.op != "call_function":
+            continue  # a mutation of an argument of the program is visible to the caller: left alone
+        node.target = _INPLACE[node.target]
+        for user in list(target.users):
+            if user is not node and order[user] > order[node]:
+                user.replace_input_with(target, node)
 
 
 def fuse_and_optimize(fn: Callable, example_inputs: Sequence[torch.Tensor],

@@ -97,6 +97,16 @@ MORE = {
     "bmm_transposed": (lambda a, b: torch.relu(a @ b.transpose(1, 2)),
                        lambda g: [torch.randn(3, 16, 24, generator=g), torch.randn(3, 8, 24, generator=g)]),
     "l2_normalise": (lambda x: x / x.norm(dim=-1, keepdim=True), lambda g: [torch.randn(8, 64, generator=g)]),
+    "rms_norm": (lambda x, w: torch.nn.functional.rms_norm(x, (64,), w, 1e-6),
+                 lambda g: [torch.randn(8, 64, generator=g), torch.rand(64, generator=g) + 0.5]),
+    "log_softmax": (lambda x: torch.nn.functional.log_softmax(x, dim=-1), lambda g: [torch.randn(8, 64, generator=g)]),
+    "instance_norm": (lambda x, w, b: torch.nn.functional.instance_norm(x, weight=w, bias=b),
+                      lambda g: [torch.randn(2, 8, 12, 16, generator=g), torch.rand(8, generator=g) + 0.5,
+                                 torch.randn(8, generator=g)]),
+    "batch_norm_training": (lambda x, w, b: torch.nn.functional.batch_norm(x, None, None, w, b, training=True),
+                            lambda g: [torch.randn(4, 8, 12, 16, generator=g), torch.rand(8, generator=g) + 0.5,
+                                       torch.randn(8, generator=g)]),
+    "gelu_erf_stays_with_torch": (lambda x: torch.nn.functional.gelu(x) * 2, lambda g: [torch.randn(8, 64, generator=g)]),
 }
 
 
@@ -256,7 +266,7 @@ def test_more_programs_on_the_checker(name):
     ins = make(_g(0))
     fused = TF.fuse_and_optimize(fn, ins, executor=oracle_executor)
     assert fused.subgraphs
-    _close(fused(*ins), fn(*ins), 2e-6)
+    _close(fused(*ins), fn(*ins), 5e-6)
     from akg_b200.driver import FusedKernel
     for sub in fused.subgraphs:  # every cluster is something the library plans
         assert FusedKernel(sub.desc_json).launch_count >= 1
