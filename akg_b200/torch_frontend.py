@@ -397,9 +397,25 @@ def _rms_norm(x, normalized_shape, weight=None, eps=None):
     return y.to(x.dtype)
 
 
+def _native_group_norm(x, weight, bias, n, c, hxw, group, eps):
+    """Statistics per (sample, group) on the [n, group, rest] view, then the per-channel scale and shift."""
+    xf = x.float() if x.dtype in (torch.float16, torch.bfloat16) else x
+    g = xf.reshape(n, group, (c // group) * hxw)
+    mean = g.mean(-1, keepdim=True)
+    d = g - mean
+    rstd = torch.rsqrt((d * d).mean(-1, keepdim=True) + eps)
+    y = (d * rstd).reshape(n, c, hxw)
+    if weight is not None:
+        y = y * weight.reshape(1, c, 1)
+    if bias is not None:
+        y = y + bias.reshape(1, c, 1)
+    return y.reshape(x.shape).to(x.dtype), mean.reshape(n, group).to(x.dtype), rstd.reshape(n, group).to(x.dtype)
+
+
 def _decompositions():
     from torch._decomp import get_decompositions
     table = _stock_decompositions()
+    table[aten.native_group_norm.default] = _native_group_norm
     table[aten.var_mean.correction] = _var_mean_correction
     if hasattr(aten, "rms_norm"):
         table[aten.rms_norm.default] = _rms_norm

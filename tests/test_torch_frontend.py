@@ -106,6 +106,9 @@ MORE = {
     "batch_norm_training": (lambda x, w, b: torch.nn.functional.batch_norm(x, None, None, w, b, training=True),
                             lambda g: [torch.randn(4, 8, 12, 16, generator=g), torch.rand(8, generator=g) + 0.5,
                                        torch.randn(8, generator=g)]),
+    "group_norm": (lambda x, w, b: torch.nn.functional.group_norm(x, 4, w, b),
+                   lambda g: [torch.randn(2, 8, 12, 16, generator=g), torch.rand(8, generator=g) + 0.5,
+                              torch.randn(8, generator=g)]),
     "gelu_erf_stays_with_torch": (lambda x: torch.nn.functional.gelu(x) * 2, lambda g: [torch.randn(8, 64, generator=g)]),
 }
 
