@@ -1170,6 +1170,212 @@ bool fused_reduce_tail_plan(const Graph& g, int sm_count, bool allow_jit, Plan* 
   return true;
 }
 
+// ---- regions that are a row region only in part -----------------------------------------------------------------------
+// Nodes [a, b) of the region as a region of its own: what it reads from outside becomes its inputs (first use order),
+// what is read outside of it or is a result of the whole region becomes its outputs.
+Graph subregion(const Graph& g, int a, int b, std::vector<int>* in_vals, std::vector<int>* out_vals) {
+  Graph gs = g;
+  gs.nodes.assign(g.nodes.begin() + a, g.nodes.begin() + b);
+  relink(gs);
+  for (auto& v : gs.values) v.input_index = v.output_index = -1;
+  in_vals->clear();
+  out_vals->clear();
+  for (const Node& n : gs.nodes)
+    for (int vid : n.in) {
+      const Value& v = gs.values[vid];
+      if (v.is_const || v.producer >= 0 || v.input_index >= 0) continue;
+      gs.values[vid].input_index = (int)in_vals->size();
+      in_vals->push_back(vid);
+    }
+  for (const Node& n : gs.nodes) {
+    const Value& ov = g.v(n.out);
+    bool outside = ov.output_index >= 0;
+    for (int u : ov.users) outside = outside || u >= b;
+    if (!outside) continue;
+    gs.values[n.out].output_index = (int)out_vals->size();
+    out_vals->push_back(n.out);
+  }
+  gs.inputs = *in_vals;
+  gs.outputs = *out_vals;
+  classify(gs);
+  return gs;
+}
+
+bool try_row_program(const Graph& gs, std::shared_ptr<RowProgram>* rp, std::vector<int>* in_values,
+                     std::vector<int>* out_values) {
+  *rp = std::make_shared<RowProgram>();
+  in_values->clear();
+  out_values->clear();
+  if (build_row_program(gs, rp->get(), in_values, out_values)) return true;
+  Graph gv;
+  std::map<int, std::pair<int64_t, int64_t>> row_index;
+  *rp = std::make_shared<RowProgram>();
+  in_values->clear();
+  out_values->clear();
+  return view_trailing_run(gs, &gv, &row_index) && build_row_program(gv, rp->get(), in_values, out_values, false, &row_index);
+}
+
+// Cuts the op list into pieces: the longest runs of ops that form a row region of their own (at least one reduction
+// inside) become one generated row kernel each, the ops in between are planned as separate launches; values that cross
+// pieces live in the workspace.  GroupNorm (statistics on the [n, groups, rest] view, scale and shift per channel on
+// another view) or a LayerNorm followed by a transpose run as two launches this way.  Returns false when no piece is
+// a row region.
+bool segmented_plan(const Graph& g, int sm_count, Plan* out) {
+  const int n = (int)g.nodes.size();
+  if (g.dynamic || n < 3 || n > 200) return false;
+  for (auto& nd : g.nodes)
+    if (nd.kind == OpK::Assign) return false;  // stores into inputs: keep the whole-region planner
+  struct Piece {
+    int a, b;
+    bool row;
+    std::shared_ptr<RowProgram> rp;
+    std::vector<int> in_vals, out_vals;  // graph values, in the order the piece's kernel(s) take them
+  };
+  std::vector<Piece> pieces;
+  bool any_row = false;
+  int a = 0;
+  while (a < n) {
+    // the longest [a, b) with a reduction inside that is a row region
+    int best = -1;
+    Piece cand;
+    for (int b = n; b > a + 1; --b) {
+      bool has_red = false;
+      for (int i = a; i < b; ++i) has_red = has_red || opk_is_reduce(g.nodes[i].kind);
+      if (!has_red) break;
+      std::vector<int> iv, ov, riv, rov;
+      Graph gs = subregion(g, a, b, &iv, &ov);
+      std::shared_ptr<RowProgram> rp;
+      if (ov.empty() || !try_row_program(gs, &rp, &riv, &rov)) continue;
+      best = b;
+      cand.a = a;
+      cand.b = b;
+      cand.row = true;
+      cand.rp = rp;
+      cand.in_vals = riv;
+      cand.out_vals = rov;
+      break;
+    }
+    if (best > 0) {
+      pieces.push_back(std::move(cand));
+      any_row = true;
+      a = best;
+    } else {
+      if (!pieces.empty() && !pieces.back().row) pieces.back().b = a + 1;  // extend the open run of other ops
+      else pieces.push_back(Piece{a, a + 1, false, nullptr, {}, {}});
+      ++a;
+    }
+  }
+  if (!any_row || pieces.size() < 2) return false;
+  // A piece made of Reshape ops only is a change of view: its result shares the buffer of its operand (the producer
+  // writes into the region's output directly when the view is one).
+  std::map<int, int> same_buffer;  // value -> value whose buffer it uses
+  for (Piece& pc : pieces) {
+    if (pc.row) continue;
+    bool views = true;
+    for (int i = pc.a; i < pc.b; ++i) {
+      const Node& nd = g.nodes[i];
+      const Value& src = g.v(nd.in[0]);
+      // (two buffers of the caller cannot be one: a view of an input or output that is itself a result needs a copy)
+      views = views && nd.kind == OpK::Reshape && src.numel() == g.v(nd.out).numel() &&
+              !((src.input_index >= 0 || src.output_index >= 0) && g.v(nd.out).output_index >= 0);
+    }
+    if (!views) continue;
+    for (int i = pc.a; i < pc.b; ++i) {
+      const Node& nd = g.nodes[i];
+      if (g.v(nd.out).output_index >= 0) same_buffer[nd.in[0]] = nd.out;  // the output's buffer holds both
+      else same_buffer[nd.out] = nd.in[0];
+    }
+    pc.a = pc.b;  // nothing left to launch
+  }
+  auto root_of = [&](int vid) {
+    for (int hops = 0; hops < 64; ++hops) {
+      auto it = same_buffer.find(vid);
+      if (it == same_buffer.end()) break;
+      vid = it->second;
+    }
+    return vid;
+  };
+  // buffers of the values that cross pieces
+  std::map<int, Ref> where;
+  size_t ws = 0;
+  auto ref_of = [&](int vid) {
+    vid = root_of(vid);
+    auto it = where.find(vid);
+    if (it != where.end()) return it->second;
+    const Value& v = g.v(vid);
+    Ref r;
+    if (v.input_index >= 0) r.arg = v.input_index;
+    else if (v.output_index >= 0) r.arg = (int)g.inputs.size() + v.output_index;
+    else {
+      r.ws_off = (int64_t)ws;
+      ws += ((size_t)v.numel() * dt_size(v.dt) + 255) / 256 * 256;
+    }
+    where[vid] = r;
+    return r;
+  };
+  Plan p;
+  p.klass = g.reduce_dir == ReduceDir::All ? "reduce_all" : g.reduce_dir == ReduceDir::Y ? "reduce_y" : "reduce_x";
+  struct Pending {
+    size_t first_step, n_steps;
+  };
+  std::vector<Pending> generic_runs;
+  size_t sub_ws = 0;
+  for (Piece& pc : pieces) {
+    if (pc.row) {
+      Step st;
+      st.kind = StepK::RowJit;
+      st.kernel_name = "akgb_row_jit";
+      st.row = pc.rp;
+      for (int vid : pc.in_vals) st.ew_in.push_back(ref_of(vid));
+      for (int vid : pc.out_vals) st.ew_out.push_back(ref_of(vid));
+      p.steps.push_back(std::move(st));
+      continue;
+    }
+    if (pc.a >= pc.b) continue;  // a change of view
+    std::vector<int> iv, ov;
+    Graph gs = subregion(g, pc.a, pc.b, &iv, &ov);
+    if (ov.empty()) continue;  // nothing of it is used
+    Plan sub;
+    try {
+      sub = build_generic_plan(gs, sm_count);
+    } catch (const Unsupported&) {
+      return false;
+    }
+    std::vector<Ref> arg_map;
+    for (int vid : iv) arg_map.push_back(ref_of(vid));
+    for (int vid : ov) arg_map.push_back(ref_of(vid));
+    generic_runs.push_back({p.steps.size(), sub.steps.size()});
+    for (Step& s2 : sub.steps) {
+      // workspace offsets of the piece are made absolute once all crossing buffers are known (marked by +1 below)
+      for (Ref* r : {&s2.a, &s2.b, &s2.c, &s2.out, &s2.out2, &s2.out3, &s2.scratch}) {
+        if (r->arg >= 0) *r = arg_map[r->arg];
+        else if (r->ws_off >= 0) r->ws_off = -2 - r->ws_off;
+      }
+      for (auto* vec : {&s2.ew_in, &s2.ew_out})
+        for (Ref& r : *vec) {
+          if (r.arg >= 0) r = arg_map[r.arg];
+          else if (r.ws_off >= 0) r.ws_off = -2 - r.ws_off;
+        }
+      p.steps.push_back(std::move(s2));
+    }
+    sub_ws = std::max(sub_ws, sub.workspace_bytes);
+    p.flops += sub.flops;
+    p.needs_gelu_lut = p.needs_gelu_lut || sub.needs_gelu_lut;
+  }
+  // the pieces' own scratch shares one area behind the crossing buffers (pieces run one after the other)
+  const int64_t base = (int64_t)ws;
+  for (Step& st : p.steps) {
+    for (Ref* r : {&st.a, &st.b, &st.c, &st.out, &st.out2, &st.out3, &st.scratch})
+      if (r->arg < 0 && r->ws_off <= -2) r->ws_off = base + (-2 - r->ws_off);
+    for (auto* vec : {&st.ew_in, &st.ew_out})
+      for (Ref& r : *vec)
+        if (r.arg < 0 && r.ws_off <= -2) r.ws_off = base + (-2 - r.ws_off);
+  }
+  p.workspace_bytes = ws + sub_ws;
+  *out = std::move(p);
+  return true;
+}
+
 Plan build_plan(const Graph& g, int sm_count, bool allow_jit) {
   for (auto& n : g.nodes)
     if (n.kind == OpK::Unknown)
@@ -1230,6 +1436,11 @@ Plan build_plan(const Graph& g, int sm_count, bool allow_jit) {
       fused.flops = plan.flops;
       fused.fallback = std::make_shared<Plan>(std::move(plan));
       plan = std::move(fused);
+    } else if (Plan cut; allow_jit && plan.steps.size() > 2 && segmented_plan(g, sm_count, &cut) &&
+               cut.steps.size() < plan.steps.size()) {
+      cut.flops = plan.flops;
+      cut.fallback = std::make_shared<Plan>(std::move(plan));
+      plan = std::move(cut);
     }
   }
   plan.bytes = io_bytes(g);

@@ -163,9 +163,12 @@ def test_generic_plan_splits_at_shape_changes(lib):
     u = b.emit("Sub", [x, r], [32, 64], f)
     v = b.emit("Reshape", [u], [2048], f, [_attr("shape", "listInt", [2048])])
     b.output(v)
-    k = FusedKernel(b.build())
+    k = FusedKernel(b.build(), flags=1)  # run-time compilation off: the separate launches
     assert k.launch_count == 3 and k.workspace_size > 0 and k.op_class == "reduce_x"
     assert k.meta()["template"] == "ew_generic"
+    # with it on, the ops in front of the Reshape are a row region of their own and write through the view
+    k = FusedKernel(b.build())
+    assert k.launch_count == 1 and k.workspace_size == 0 and k.meta()["template"] == "akgb_row_jit"
 
 
 def _dynamic_sub_mul_cast():

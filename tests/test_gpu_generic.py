@@ -911,3 +911,55 @@ def test_instance_norm_on_nchw_is_one_row_kernel(lib):
     if FLAGS[0] == 0:
         assert kern.launch_count == 1 and kern.meta()["template"] == "akgb_row_jit"
         assert f"constexpr int C = {h_ * w_}" in kern.jit_source()
+
+
+def test_regions_that_are_row_regions_only_in_part(lib):
+    rng = np.random.default_rng(105)
+    f = "float32"
+    # centred rows, flattened: the row kernel writes through the view
+    b = _Builder("Fused_Mul_ReduceSum_Sub_Reshape_105")
+    x = b.input("x", [96, 200], f)
+    r = b.emit("ReduceSum", [b.emit("Mul", [x, x], [96, 200], f)], [96, 1], f, _reduce_attr([1], True))
+    u = b.emit("Sub", [x, r], [96, 200], f)
+    b.output(b.emit("Reshape", [u], [19200], f, [_attr("shape", "listInt", [19200])]))
+    d = b.build()
+    ins = [rng.standard_normal((96, 200)).astype(np.float32)]
+    got, kern = run(d, ins)
+    np.testing.assert_allclose(got[0], O.evaluate(d, ins, accum="float64")[0], rtol=1e-5, atol=1e-4)
+    if FLAGS[0] == 0:
+        assert kern.launch_count == 1
+    # softmax over the last axis, then a transpose of the leading axes and a scale: row kernel + the rest
+    b = _Builder("Fused_Softmax_Transpose_Mul_106")
+    x = b.input("x", [6, 10, 128], f)
+    m = b.emit("ReduceMax", [x], [6, 10, 1], f, _reduce_attr([2], True))
+    e = b.emit("Exp", [b.emit("Sub", [x, m], [6, 10, 128], f)], [6, 10, 128], f)
+    p = b.emit("RealDiv", [e, b.emit("ReduceSum", [e], [6, 10, 1], f, _reduce_attr([2], True))], [6, 10, 128], f)
+    t = b.emit("Transpose", [p], [10, 6, 128], f, [_attr("perm", "listInt", [1, 0, 2])])
+    b.output(b.emit("Mul", [t, b.const(0.5, f)], [10, 6, 128], f))
+    b.output(m)
+    d = b.build()
+    ins = [rng.standard_normal((6, 10, 128)).astype(np.float32)]
+    got, kern = run(d, ins)
+    want = O.evaluate(d, ins, accum="float64")
+    np.testing.assert_allclose(got[0], want[0], rtol=1e-5, atol=1e-7)
+    assert bits_equal(got[1], want[1])
+    if FLAGS[0] == 0:
+        assert kern.launch_count == 3  # row kernel, transpose, scale
+    # two row regions over different views with elementwise ops in between (GroupNorm-like)
+    b = _Builder("Fused_GroupStats_Affine_107")
+    x = b.input("x", [4, 8, 6, 10], f)       # [n, c, h, w]
+    w = b.input("w", [1, 8, 1, 1], f)
+    g_ = b.emit("Reshape", [x], [4, 2, 240], f, [_attr("shape", "listInt", [4, 2, 240])])
+    mean = b.emit("Mul", [b.emit("ReduceSum", [g_], [4, 2, 1], f, _reduce_attr([2], True)), b.const(1 / 240, f)], [4, 2, 1], f)
+    dd = b.emit("Sub", [g_, mean], [4, 2, 240], f)
+    var = b.emit("Mul", [b.emit("ReduceSum", [b.emit("Mul", [dd, dd], [4, 2, 240], f)], [4, 2, 1], f, _reduce_attr([2], True)),
+                         b.const(1 / 240, f)], [4, 2, 1], f)
+    y = b.emit("Mul", [dd, b.emit("Rsqrt", [b.emit("Add", [var, b.const(1e-5, f)], [4, 2, 1], f)], [4, 2, 1], f)], [4, 2, 240], f)
+    y4 = b.emit("Reshape", [y], [4, 8, 6, 10], f, [_attr("shape", "listInt", [4, 8, 6, 10])])
+    b.output(b.emit("Mul", [y4, w], [4, 8, 6, 10], f))
+    d = b.build()
+    ins = [rng.standard_normal((4, 8, 6, 10)).astype(np.float32), rng.uniform(0.5, 1.5, (1, 8, 1, 1)).astype(np.float32)]
+    got, kern = run(d, ins)
+    np.testing.assert_allclose(got[0], O.evaluate(d, ins, accum="float64")[0], rtol=1e-5, atol=1e-5)
+    if FLAGS[0] == 0:
+        assert kern.launch_count == 2  # statistics + normalisation as a row kernel, then the per-channel scale
