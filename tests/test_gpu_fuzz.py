@@ -153,3 +153,64 @@ def test_random_reduction_tail(seed, flags):
         assert np.all(np.abs(g.astype(np.float64) - w.astype(np.float64)) <= bound + 1e-5 * np.abs(w))
     if flags == 0:
         assert k.meta()["template"] in ("akgb_col_jit", "akgb_row_jit")
+
+
+def random_cut_region(seed):
+    """Two row regions with a change of layout between them: a transpose of the leading axes, or a re-view of the rows."""
+    rng = np.random.default_rng(5000 + seed)
+    lead = [int(v) for v in rng.choice([2, 3, 5, 12], size=2)]
+    cols = int(rng.choice([8, 40, 128, 264]))
+    shape, red = lead + [cols], lead + [1]
+    b = _Builder(f"Fused_FuzzCut_{seed}")
+    x = b.input("x", shape, F)
+    g_ = b.input("g", [cols], F)
+
+    def row_block(cur, shp, rd):
+        kind = int(rng.integers(3))
+        ax = [len(shp) - 1]
+        if kind == 0:  # centre
+            m = b.emit("Mul", [b.emit("ReduceSum", [cur], rd, F, _reduce_attr(ax, True)), b.const(1.0 / shp[-1], F)], rd, F)
+            return b.emit("Sub", [cur, m], shp, F)
+        if kind == 1:  # softmax-like
+            m = b.emit("ReduceMax", [cur], rd, F, _reduce_attr(ax, True))
+            e = b.emit("Exp", [b.emit("Sub", [cur, m], shp, F)], shp, F)
+            return b.emit("RealDiv", [e, b.emit("ReduceSum", [e], rd, F, _reduce_attr(ax, True))], shp, F)
+        s_ = b.emit("ReduceSum", [b.emit("Mul", [cur, cur], shp, F)], rd, F, _reduce_attr(ax, True))
+        return b.emit("Mul", [cur, b.emit("Rsqrt", [b.emit("Add", [s_, b.const(1.0, F)], rd, F)], rd, F)], shp, F)
+
+    cur = b.emit("Mul", [row_block(x, shape, red), g_], shape, F)
+    outs = []
+    if rng.random() < 0.5:
+        outs.append(cur)
+    if rng.random() < 0.5:
+        shape2 = [lead[1], lead[0], cols]
+        cur = b.emit("Transpose", [cur], shape2, F, [_attr("perm", "listInt", [1, 0, 2])])
+    else:
+        shape2 = [lead[0] * lead[1], cols]
+        cur = b.emit("Reshape", [cur], shape2, F, [_attr("shape", "listInt", shape2)])
+    red2 = shape2[:-1] + [1]
+    cur = b.emit("Add", [cur, g_], shape2, F)
+    if rng.random() < 0.7:
+        cur = row_block(cur, shape2, red2)
+    outs.append(b.emit("Tanh", [cur], shape2, F))
+    for o in outs:
+        b.output(o)
+    desc = b.build()
+    ins = [rng.standard_normal(shape).astype(np.float32), rng.uniform(0.5, 1.5, [cols]).astype(np.float32)]
+    return desc, ins
+
+
+@pytest.mark.parametrize("seed", range(24))
+@pytest.mark.parametrize("flags", [0, 1], ids=["generated", "separate"])
+def test_random_cut_region(seed, flags):
+    desc, ins = random_cut_region(seed)
+    k = FusedKernel(desc, flags=flags)
+    outs = k.empty_outputs()
+    for o in outs:
+        o.view(np.uint8)[...] = 0xCD
+    k.run_host([a.copy() for a in ins] + outs)
+    assert k.check_device_error() == 0
+    want = O.evaluate(desc, ins, accum="float64")
+    for g, w in zip(outs, want):
+        assert g.shape == w.shape and g.dtype == w.dtype
+        np.testing.assert_allclose(g.astype(np.float64), w.astype(np.float64), rtol=2e-5, atol=2e-5)
