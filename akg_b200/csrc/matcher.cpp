@@ -1335,12 +1335,15 @@ bool segmented_plan(const Graph& g, int sm_count, Plan* out) {
     std::vector<int> iv, ov;
     Graph gs = subregion(g, pc.a, pc.b, &iv, &ov);
     if (ov.empty()) continue;  // nothing of it is used
+    // the piece is a region of its own: templates and generated reductions apply to it like to any region (should a
+    // generated kernel fail to compile at launch, the whole region falls back, so the piece's own fallback is dropped)
     Plan sub;
     try {
-      sub = build_generic_plan(gs, sm_count);
+      sub = build_plan(gs, sm_count, true);
     } catch (const Unsupported&) {
       return false;
     }
+    sub.fallback.reset();
     std::vector<Ref> arg_map;
     for (int vid : iv) arg_map.push_back(ref_of(vid));
     for (int vid : ov) arg_map.push_back(ref_of(vid));
