@@ -274,6 +274,43 @@ def _op_cases():
     e = b.emit("ReduceSum", [b.emit("Exp", [d], [5, 12, 96], f)], [5, 12, 1], f, _reduce_attr([2], True))
     b.output(b.emit("Sub", [d, b.emit("Log", [e], [5, 12, 1], f)], [5, 12, 96], f))
     cases["log_softmax_5x12x96"] = b.build()
+
+    # NCHW regions: BatchNorm statistics (chain + reduction over (0, 2, 3) + scaling), InstanceNorm with per-channel
+    # scale and shift, a reduction over non-adjacent axes, a region that is a row region only in part
+    nchw, stat = [8, 32, 16, 16], [1, 32, 1, 1]
+    b = _Builder("Fused_BNStats_17")
+    x = b.input("x", nchw, f)
+    mean_in = b.input("mean", stat, f)
+    dlt = b.emit("Sub", [x, mean_in], nchw, f)
+    s2 = b.emit("ReduceSum", [b.emit("Mul", [dlt, dlt], nchw, f)], stat, f, _reduce_attr([0, 2, 3], True))
+    b.output(b.emit("Mul", [s2, b.const(1.0 / (8 * 16 * 16), f)], stat, f))
+    cases["bn_variance_nchw"] = b.build()
+
+    b = _Builder("Fused_InstanceNorm_18")
+    x, gamma, beta = b.input("x", nchw, f), b.input("gamma", stat, f), b.input("beta", stat, f)
+    red = [8, 32, 1, 1]
+    inv = b.const(1.0 / 256, f)
+    mean = b.emit("Mul", [b.emit("ReduceSum", [x], red, f, _reduce_attr([2, 3], True)), inv], red, f)
+    dlt = b.emit("Sub", [x, mean], nchw, f)
+    var = b.emit("Mul", [b.emit("ReduceSum", [b.emit("Mul", [dlt, dlt], nchw, f)], red, f, _reduce_attr([2, 3], True)), inv], red, f)
+    rstd = b.emit("Rsqrt", [b.emit("Add", [var, b.const(1e-5, f)], red, f)], red, f)
+    b.output(b.emit("Add", [b.emit("Mul", [b.emit("Mul", [dlt, rstd], nchw, f), gamma], nchw, f), beta], nchw, f))
+    cases["instance_norm_nchw"] = b.build()
+
+    b = _Builder("Fused_ReduceNonAdjacent_19")
+    x = b.input("x", [6, 40, 50], f)
+    b.output(b.emit("ReduceSum", [x], [1, 40, 1], f, _reduce_attr([0, 2], True)))
+    b.output(b.emit("ReduceMax", [x], [40], f, _reduce_attr([0, 2], False)))
+    cases["reduce_non_adjacent"] = b.build()
+
+    b = _Builder("Fused_Softmax_Transpose_20")
+    x = b.input("x", [6, 10, 128], f)
+    m = b.emit("ReduceMax", [x], [6, 10, 1], f, _reduce_attr([2], True))
+    e = b.emit("Exp", [b.emit("Sub", [x, m], [6, 10, 128], f)], [6, 10, 128], f)
+    p = b.emit("RealDiv", [e, b.emit("ReduceSum", [e], [6, 10, 1], f, _reduce_attr([2], True))], [6, 10, 128], f)
+    t = b.emit("Transpose", [p], [10, 6, 128], f, [_attr("perm", "listInt", [1, 0, 2])])
+    b.output(b.emit("Mul", [t, b.const(0.5, f)], [10, 6, 128], f))
+    cases["softmax_transpose_scale"] = b.build()
     return cases
 
 

@@ -30,7 +30,7 @@ def _check(got, want, name, loose):
 
 
 def test_fixtures_present():
-    assert len(CASES) >= 24
+    assert len(CASES) >= 28
 
 
 @pytest.mark.parametrize("name", CASES)
