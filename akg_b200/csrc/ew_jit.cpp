@@ -523,16 +523,157 @@ bool row_shape(const RowProgram& P, bool vec, RowShape* rs) {
   int64_t coalesce = 1;
   while (coalesce < granules && coalesce < 32) coalesce <<= 1;
   t = std::max(t, coalesce);
-  if (t > 1024) return false;
+  if (t > 512) return false;  // 1024-thread groups leave 64 registers per thread: the multi-pass schedule takes over
   rs->t = (int)t;
   rs->nv = (int)((granules + t - 1) / t);
   rs->tpb = std::max(128, rs->t);
   return true;
 }
 
+
+// Rows too long for registers: one CTA of 512 threads walks its row once per reduction and once more for the results,
+// recomputing the per-element values each pass needs from the inputs (the later passes find the row in L2).  The same
+// row program, the same per-op rounding; only the schedule differs from row_generate.
+bool row_generate_multipass(const RowProgram& P, bool vec, std::string* out, RowShape* shape) {
+  RowShape rs;
+  rs.vw = vec ? 8 : 1;
+  rs.t = 512;
+  rs.tpb = 512;
+  rs.nv = 0;  // marks the multi-pass schedule
+  *shape = rs;
+  const int ni = (int)P.instr.size();
+  std::ostringstream s;
+  s << kPreamble;
+  s << "constexpr int C = " << P.cols << ", T = 512, TPB = 512, VW = " << rs.vw << ";\n";
+  s << R"SRC(
+template <int OP> __device__ __forceinline__ float comb(float a, float b) {
+  return OP == 0 ? __fadd_rn(a, b) : OP == 1 ? fmaxf(a, b) : OP == 2 ? fminf(a, b) : __fmul_rn(a, b);
+}
+template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = comb<OP>(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = v;
+  __syncthreads();
+  v = sm[0];
+#pragma unroll
+  for (int w = 1; w < T / 32; ++w) v = comb<OP>(v, sm[w]);
+  return v;
+}
+)SRC";
+  s << "extern \"C\" __global__ void __launch_bounds__(TPB) akgb_row_jit(";
+  for (size_t i = 0; i < P.in.size(); ++i) s << "const void* __restrict__ in" << i << ", ";
+  for (size_t i = 0; i < P.out.size(); ++i) s << "void* __restrict__ out" << i << ", ";
+  s << "i64 rows) {\n";
+  s << "  __shared__ float sm[TPB / 32];\n  const int tr = threadIdx.x;\n  const i64 r = blockIdx.x;\n";
+  std::vector<std::string> name(P.n_val);
+  std::vector<char> is_const(P.n_val, 0);
+  std::vector<int> def_instr(P.n_val, -1), def_input(P.n_val, -1);
+  for (size_t c = 0; c < P.const_val.size(); ++c) {
+    char buf[32];
+    std::snprintf(buf, sizeof(buf), "0x%08xu", P.const_bits[c]);
+    name[P.const_val[c]] = buf;
+    is_const[P.const_val[c]] = 1;
+  }
+  for (size_t i = 0; i < P.in.size(); ++i) {
+    const RowOperand& o = P.in[i];
+    name[o.val] = "x" + std::to_string(i);
+    def_input[o.val] = (int)i;
+    if (o.kind == RK_ROW || o.kind == RK_SCALAR) {
+      std::string idx = o.kind == RK_ROW ? "r" : "0";
+      if (o.kind == RK_ROW && o.row_mod != 0)
+        idx = "(r / " + std::to_string(o.row_div) + "LL) % " + std::to_string(o.row_mod) + "LL";
+      s << "  const " << (is_float_dt(o.dt) ? "float " : "int ") << name[o.val] << " = ld1_" << dt_tag(o.dt) << "(in" << i
+        << ", " << idx << ");\n";
+    }
+  }
+  for (int k = 0; k < ni; ++k) {
+    def_instr[P.instr[k].dst] = k;
+    name[P.instr[k].dst] = "t" + std::to_string(k);
+  }
+  auto ref = [&](int val, bool want_float) -> std::string {
+    if (is_const[val]) return want_float ? "__uint_as_float(" + name[val] + ")" : "(int)" + name[val];
+    return P.val_full[val] ? name[val] + "[j]" : name[val];
+  };
+  // one pass over the row: everything per-element that `roots` need, recomputed from the inputs, then `tail`
+  auto emit_pass = [&](const std::vector<int>& roots, const std::string& tail) {
+    std::vector<char> need_instr(ni, 0), need_input(P.in.size(), 0);
+    std::vector<int> stack(roots.begin(), roots.end());
+    while (!stack.empty()) {
+      const int v = stack.back();
+      stack.pop_back();
+      if (!P.val_full[v] || is_const[v]) continue;
+      if (def_input[v] >= 0) {
+        need_input[def_input[v]] = 1;
+        continue;
+      }
+      const int k = def_instr[v];
+      if (k < 0 || need_instr[k]) continue;
+      need_instr[k] = 1;
+      const RowInstr& x = P.instr[k];
+      stack.push_back(x.a);
+      if (!x.reduce) {
+        stack.push_back(x.b);
+        stack.push_back(x.c);
+      }
+    }
+    s << "#pragma unroll 2\n  for (i64 c = (i64)tr * VW; c < C; c += (i64)T * VW) {\n";
+    for (size_t i = 0; i < P.in.size(); ++i) {
+      if (!need_input[i]) continue;
+      const RowOperand& o = P.in[i];
+      const std::string base = o.kind == RK_FULL ? "r * C" : o.kind == RK_COL ? "(i64)0" : "(r % " + std::to_string(o.mod_rows) + "LL) * C";
+      s << "    " << (is_float_dt(o.dt) ? "float " : "int ") << name[o.val] << "[VW];\n";
+      if (vec) s << "    ld8_" << dt_tag(o.dt) << "(in" << i << ", " << base << " + c, " << name[o.val] << ", false);\n";
+      else s << "    " << name[o.val] << "[0] = ld1_" << dt_tag(o.dt) << "(in" << i << ", " << base << " + c);\n";
+    }
+    for (int k = 0; k < ni; ++k) {
+      if (!need_instr[k]) continue;
+      const RowInstr& x = P.instr[k];
+      const std::string expr = instr_expr(x.op, x.dt, x.cls, x.src_cls, x.a, x.b, x.c, ref);
+      s << "    " << (x.cls == EWC_FLOAT ? "float " : "int ") << name[x.dst] << "[VW];\n#pragma unroll\n    for (int j = 0; j < VW; ++j) "
+        << name[x.dst] << "[j] = " << expr << ";\n";
+    }
+    s << tail << "  }\n";
+  };
+  for (int k = 0; k < ni; ++k) {
+    const RowInstr& x = P.instr[k];
+    if (x.full) continue;  // per-element values are computed inside the passes that need them
+    if (x.reduce) {
+      const char* ident = x.red_op == 0 ? "0.f" : x.red_op == 1 ? "-3.402823466e+38f" : x.red_op == 2 ? "3.402823466e+38f" : "1.f";
+      s << "  float acc" << k << " = " << ident << ";\n";
+      std::ostringstream tail;
+      tail << "#pragma unroll\n    for (int j = 0; j < VW; ++j) acc" << k << " = comb<" << x.red_op << ">(acc" << k << ", "
+           << name[x.a] << "[j]);\n";
+      emit_pass({x.a}, tail.str());
+      s << "  const float " << name[x.dst] << " = " << round_fn(x.dt) << "(row_reduce<" << x.red_op << ">(acc" << k << ", sm));\n";
+    } else {
+      const std::string expr = instr_expr(x.op, x.dt, x.cls, x.src_cls, x.a, x.b, x.c, ref);
+      s << "  const " << (x.cls == EWC_FLOAT ? "float " : "int ") << name[x.dst] << " = " << expr << ";\n";
+    }
+  }
+  std::vector<int> roots;
+  std::ostringstream tail;
+  for (size_t i = 0; i < P.out.size(); ++i) {
+    const RowOperand& o = P.out[i];
+    if (o.kind != RK_FULL) continue;
+    roots.push_back(o.val);
+    if (vec) tail << "    st8_" << dt_tag(o.dt) << "(out" << i << ", r * C + c, " << name[o.val] << ");\n";
+    else tail << "    st1_" << dt_tag(o.dt) << "(out" << i << ", r * C + c, " << name[o.val] << "[0]);\n";
+  }
+  if (!roots.empty()) emit_pass(roots, tail.str());
+  for (size_t i = 0; i < P.out.size(); ++i) {
+    const RowOperand& o = P.out[i];
+    if (o.kind == RK_ROW)
+      s << "  if (tr == 0) st1_" << dt_tag(o.dt) << "(out" << i << ", r, " << ref(o.val, is_float_dt(o.dt)) << ");\n";
+  }
+  s << "}\n";
+  *out = s.str();
+  return true;
+}
+
 bool row_generate(const RowProgram& P, bool vec, std::string* out, RowShape* shape) {
   RowShape rs;
-  if (!row_shape(P, vec, &rs)) return false;
+  if (!row_shape(P, vec, &rs)) return row_generate_multipass(P, vec, out, shape);
   *shape = rs;
   std::ostringstream s;
   s << kPreamble;
@@ -966,7 +1107,7 @@ cudaError_t row_jit_launch(const RowProgram& P, const void* const* in, void* con
   if (!row_generate(P, vec, &src, &rs)) return cudaErrorNotSupported;
   JitKernel* k = compile(src, "akgb_row_jit");
   if (!k || k->failed) return cudaErrorNotSupported;
-  const int rpb = rs.tpb / rs.t;
+  const int rpb = rs.tpb / rs.t;  // 1 for the multi-pass schedule
   const int64_t grid = (P.rows + rpb - 1) / rpb;
   if (grid > 0x7fffffff) return cudaErrorNotSupported;
   long long rows = P.rows;

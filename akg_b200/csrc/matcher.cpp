@@ -1014,7 +1014,7 @@ bool fused_reduce_tail_plan(const Graph& g, int sm_count, bool allow_jit, Plan* 
   while (first > 0 && (is_red[first - 1] || x.shape[first - 1] == 1)) --first;
   int64_t C = 1, n = x.numel();
   for (size_t i = first; i < rank; ++i) C *= x.shape[i];
-  if (first == 0 || C < 8 || C > 16384 || n < (1 << 16)) return false;  // all axes: the re-viewed plan above
+  if (first == 0 || C < 8 || C > (1 << 20) || n < (1 << 16)) return false;  // all axes: the re-viewed plan above
   const int64_t R = n / C;
   // the chain: elementwise ops over tensors of exactly x's element count, none of them a result of the region
   std::map<int, std::pair<int64_t, int64_t>> row_index;

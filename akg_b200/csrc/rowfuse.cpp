@@ -60,7 +60,7 @@ bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_val
   const int64_t C = S.back();
   int64_t R = 1;
   for (size_t i = 0; i + 1 < S.size(); ++i) R *= S[i];
-  if (C < 2 || R < 1 || C > 16384) return false;
+  if (C < 2 || R < 1 || C > (1 << 20)) return false;
   const std::vector<int64_t> S_lead(S.begin(), S.end() - 1);
 
   RowProgram P;

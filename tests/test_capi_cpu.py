@@ -237,6 +237,9 @@ def test_planning_of_generated_kernels_needs_no_device(lib):
     assert "T = 128" in FusedKernel(descs.rmsnorm(64, 4096)).jit_source()
     assert "T = 8," in FusedKernel(descs.rmsnorm(64, 64)).jit_source()
     assert "VW = 1" in FusedKernel(descs.rmsnorm(64, 100)).jit_source(False)
+    # rows too long for registers: still one launch, a 512-thread block per row that walks the row once per reduction
+    kl = FusedKernel(descs.rmsnorm(64, 40000))
+    assert kl.launch_count == 1 and "T = 512" in kl.jit_source() and "c += (i64)T * VW" in kl.jit_source()
     kc = FusedKernel(descs.mul_reduce_sum(4096, 512, [0]))
     assert kc.meta()["template"] == "akgb_col_jit" and "akgb_col_jit" in kc.jit_source()
     ka = FusedKernel(descs.mul_reduce_sum(4096, 512, [0, 1]))

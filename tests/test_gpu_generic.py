@@ -694,6 +694,10 @@ def _rows_region(kind, rows_shape, cols, dtype="float32"):
     ("select_softmax", [3, 64], 256, "float16"),
     ("l2norm_stats", [257], 768, "float32"),
     ("l2norm_stats", [2, 3, 5], 8192, "float32"),
+    ("log_softmax", [70], 32000, "float32"),      # rows too long for registers: one pass per reduction, one for the result
+    ("rmsnorm", [33], 20000, "float16"),
+    ("select_softmax", [2, 9], 24576, "bfloat16"),
+    ("l2norm_stats", [5], 50001, "float32"),      # and not a multiple of 8
 ])
 def test_reduce_x_regions_as_one_generated_kernel(lib, kind, rows_shape, cols, dtype):
     rng = np.random.default_rng(hash((kind, cols)) % 1000)
