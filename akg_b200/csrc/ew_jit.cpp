@@ -546,6 +546,20 @@ bool row_generate_multipass(const RowProgram& P, bool vec, std::string* out, Row
   s << kPreamble;
   s << "constexpr int C = " << P.cols << ", T = 512, TPB = 512, VW = " << rs.vw << ";\n";
   s << R"SRC(
+__device__ __forceinline__ U4 ld16p(const void* p, unsigned long long pol) { U4 v;
+  asm volatile("ld.global.nc.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(pol)); return v; }
+__device__ __forceinline__ void ld8p_f32(const void* p, i64 e0, float* r, unsigned long long pol) {
+  const U4 a = ld16p((const float*)p + e0, pol), b = ld16p((const float*)p + e0 + 4, pol);
+  r[0] = __uint_as_float(a.x); r[1] = __uint_as_float(a.y); r[2] = __uint_as_float(a.z); r[3] = __uint_as_float(a.w);
+  r[4] = __uint_as_float(b.x); r[5] = __uint_as_float(b.y); r[6] = __uint_as_float(b.z); r[7] = __uint_as_float(b.w); }
+__device__ __forceinline__ void ld8p_f16(const void* p, i64 e0, float* r, unsigned long long pol) {
+  const U4 v = ld16p((const u16*)p + e0, pol); const u32 w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { r[2*i] = h2f((u16)(w[i] & 0xffffu)); r[2*i+1] = h2f((u16)(w[i] >> 16)); } }
+__device__ __forceinline__ void ld8p_bf16(const void* p, i64 e0, float* r, unsigned long long pol) {
+  const U4 v = ld16p((const u16*)p + e0, pol); const u32 w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { r[2*i] = b2f((u16)(w[i] & 0xffffu)); r[2*i+1] = b2f((u16)(w[i] >> 16)); } }
 template <int OP> __device__ __forceinline__ float comb(float a, float b) {
   return OP == 0 ? __fadd_rn(a, b) : OP == 1 ? fmaxf(a, b) : OP == 2 ? fminf(a, b) : __fmul_rn(a, b);
 }
@@ -566,6 +580,10 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
   for (size_t i = 0; i < P.out.size(); ++i) s << "void* __restrict__ out" << i << ", ";
   s << "i64 rows) {\n";
   s << "  __shared__ float sm[TPB / 32];\n  const int tr = threadIdx.x;\n  const i64 r = blockIdx.x;\n";
+  // L2 policies: a row stays resident while later passes still need it and leaves first once the last pass has read it
+  s << "  unsigned long long pol_last, pol_first;\n"
+         "  asm volatile(\"createpolicy.fractional.L2::evict_last.b64 %0, 1.0;\" : \"=l\"(pol_last));\n"
+         "  asm volatile(\"createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\" : \"=l\"(pol_first));\n";
   std::vector<std::string> name(P.n_val);
   std::vector<char> is_const(P.n_val, 0);
   std::vector<int> def_instr(P.n_val, -1), def_input(P.n_val, -1);
@@ -596,7 +614,8 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
     return P.val_full[val] ? name[val] + "[j]" : name[val];
   };
   // one pass over the row: everything per-element that `roots` need, recomputed from the inputs, then `tail`
-  auto emit_pass = [&](const std::vector<int>& roots, const std::string& tail) {
+  int pass_no = 0;
+  auto emit_pass = [&](const std::vector<int>& roots, const std::string& tail, bool last = false) {
     std::vector<char> need_instr(ni, 0), need_input(P.in.size(), 0);
     std::vector<int> stack(roots.begin(), roots.end());
     while (!stack.empty()) {
@@ -617,13 +636,18 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
         stack.push_back(x.c);
       }
     }
-    s << "#pragma unroll 2\n  for (i64 c = (i64)tr * VW; c < C; c += (i64)T * VW) {\n";
+    const bool rev = pass_no & 1;  // every other pass walks backwards: it starts with what the pass before left in L2
+    if (rev) s << "#pragma unroll 2\n  for (i64 c = (i64)tr * VW + (i64)((C - 1) / (T * VW)) * (T * VW); c >= 0; c -= (i64)T * VW) {\n    if (c >= C) continue;\n";
+    else s << "#pragma unroll 2\n  for (i64 c = (i64)tr * VW; c < C; c += (i64)T * VW) {\n";
+    ++pass_no;
     for (size_t i = 0; i < P.in.size(); ++i) {
       if (!need_input[i]) continue;
       const RowOperand& o = P.in[i];
       const std::string base = o.kind == RK_FULL ? "r * C" : o.kind == RK_COL ? "(i64)0" : "(r % " + std::to_string(o.mod_rows) + "LL) * C";
       s << "    " << (is_float_dt(o.dt) ? "float " : "int ") << name[o.val] << "[VW];\n";
-      if (vec) s << "    ld8_" << dt_tag(o.dt) << "(in" << i << ", " << base << " + c, " << name[o.val] << ", false);\n";
+      const bool pol = vec && o.kind == RK_FULL && is_float_dt(o.dt);
+      if (pol) s << "    ld8p_" << dt_tag(o.dt) << "(in" << i << ", " << base << " + c, " << name[o.val] << ", " << (last ? "pol_first" : "pol_last") << ");\n";
+      else if (vec) s << "    ld8_" << dt_tag(o.dt) << "(in" << i << ", " << base << " + c, " << name[o.val] << ", false);\n";
       else s << "    " << name[o.val] << "[0] = ld1_" << dt_tag(o.dt) << "(in" << i << ", " << base << " + c);\n";
     }
     for (int k = 0; k < ni; ++k) {
@@ -660,7 +684,7 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
     if (vec) tail << "    st8_" << dt_tag(o.dt) << "(out" << i << ", r * C + c, " << name[o.val] << ");\n";
     else tail << "    st1_" << dt_tag(o.dt) << "(out" << i << ", r * C + c, " << name[o.val] << "[0]);\n";
   }
-  if (!roots.empty()) emit_pass(roots, tail.str());
+  if (!roots.empty()) emit_pass(roots, tail.str(), true);
   for (size_t i = 0; i < P.out.size(); ++i) {
     const RowOperand& o = P.out[i];
     if (o.kind == RK_ROW)
