@@ -12,10 +12,13 @@ pytestmark = pytest.mark.gpu
 F = "float32"
 
 
-def random_region(seed):
+def random_region(seed, long_rows=False):
     rng = np.random.default_rng(seed)
     lead = [int(v) for v in rng.choice([1, 2, 3, 5, 16, 33], size=int(rng.integers(1, 4)))]
     cols = int(rng.choice([8, 24, 40, 96, 257, 1024]))
+    if long_rows:  # rows that do not fit a thread group's registers
+        lead = [int(v) for v in rng.choice([1, 2, 3, 7], size=int(rng.integers(1, 3)))]
+        cols = int(rng.choice([16392, 20000, 33000, 40001, 65536]))
     shape, red = lead + [cols], lead + [1]
     io_dtype = str(rng.choice([F, F, "float16"]))
     b = _Builder(f"Fused_Fuzz_{seed}")
@@ -96,6 +99,29 @@ def test_random_region(seed, flags):
         scale = float(np.abs(w64[fin]).max()) if fin.any() else 1.0
         tol = 5e-3 if w.dtype == np.float16 else 2e-5
         # Floor / Greater / Select are discontinuous: a last-bit difference upstream may flip a few elements
+        bad = np.abs(g64 - w64)[fin] > tol * max(scale, 1.0) + tol * np.abs(w64[fin])
+        assert bad.mean() <= 2e-3, (seed, float(bad.mean()))
+
+
+@pytest.mark.parametrize("seed", range(100, 130))
+def test_random_long_row_region(seed):
+    """The same random regions on rows of 16K-64K elements: the generated kernel walks the row once per reduction."""
+    desc, ins, io_dtype = random_region(seed, long_rows=True)
+    k = FusedKernel(desc)
+    has_reduce = any(op["name"].startswith("Reduce") for op in desc["op_desc"])
+    if has_reduce and k.meta()["template"] == "akgb_row_jit":
+        assert k.launch_count == 1 and "c += (i64)T * VW" in k.jit_source(desc["input_desc"][0][0]["shape"][-1] % 8 == 0)
+    outs = k.empty_outputs()
+    k.run_host([a.copy() for a in ins] + outs)
+    assert k.check_device_error() == 0
+    want = O.evaluate(desc, ins, accum="float64")
+    for g, w in zip(outs, want):
+        assert g.shape == w.shape and g.dtype == w.dtype
+        g64, w64 = g.astype(np.float64), w.astype(np.float64)
+        fin = np.isfinite(w64)
+        assert np.array_equal(np.isfinite(g64), fin)
+        scale = float(np.abs(w64[fin]).max()) if fin.any() else 1.0
+        tol = 5e-3 if w.dtype == np.float16 else 2e-5
         bad = np.abs(g64 - w64)[fin] > tol * max(scale, 1.0) + tol * np.abs(w64[fin])
         assert bad.mean() <= 2e-3, (seed, float(bad.mean()))
 
