@@ -696,7 +696,9 @@ akgb_status akgb_kernel_meta(const akgb_kernel* k, char* buf, size_t cap, size_t
     << ", \"threadIdx.z\": " << d.block[2] << ", \"is_dynamic\": " << (k->graph.dynamic ? "true" : "false") << ", \"sha256\": \"" << k->graph.sha256_hex
     << "\", \"class\": \"" << k->plan.klass << "\", \"template\": \"" << st.kernel_name
     << "\", \"bytes\": " << k->plan.bytes << ", \"flops\": " << k->plan.flops << ", \"smem\": " << d.smem
-    << ", \"workspace\": " << k->plan.workspace_bytes << ", \"launches\": " << launches_of(k) << "}";
+    << ", \"workspace\": " << k->plan.workspace_bytes << ", \"launches\": " << launches_of(k) << ", \"steps\": [";
+  for (size_t i = 0; i < ap.steps.size(); ++i) o << (i ? ", " : "") << "\"" << ap.steps[i].kernel_name << "\"";  // in launch order
+  o << "]}";
   std::string s = o.str();
   if (needed) *needed = s.size() + 1;
   if (!buf || cap < s.size() + 1) return buf ? fail(AKGB_INVALID_ARG, "buffer too small") : AKGB_OK;

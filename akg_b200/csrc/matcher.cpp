@@ -12,6 +12,7 @@
 // because every op rounds to its declared element type.
 #include <algorithm>
 #include <cmath>
+#include <functional>
 #include <set>
 
 #include "hostconv.hpp"
@@ -934,15 +935,31 @@ bool view_trailing_run(const Graph& g, Graph* gv, std::map<int, std::pair<int64_
   for (size_t vi = 0; vi < gv->values.size(); ++vi) {
     Value& v = gv->values[vi];
     if (v.is_const) continue;
-    const std::vector<int64_t> shp = v.shape;
+    if (v.producer < 0 && v.users.empty() && v.input_index < 0 && v.output_index < 0) continue;  // not of this region
+    std::vector<int64_t> shp = v.shape;
     int64_t n = 1;
     for (auto e : shp) n *= e;
+    // a per-row vector on its way to the broadcastable shape (weight [R] -> [R, 1] -> [R, 1, 1]): only re-viewed here
+    bool only_reshaped = n == R && n > 1 && v.output_index < 0 && !v.users.empty() && shp.size() < rank;
+    for (int u : v.users) only_reshaped = only_reshaped && g.nodes[u].kind == OpK::Reshape;
+    if (shp.size() < rank && n != C) shp.insert(shp.begin(), rank - shp.size(), 1);  // broadcasting aligns trailing axes
     bool trailing_ones = shp.size() == rank;
     for (size_t d = first; trailing_ones && d < rank; ++d) trailing_ones = shp[d] == 1;
-    if (shp == S) {
+    auto squeeze = [](const std::vector<int64_t>& s) {
+      std::vector<int64_t> r;
+      for (auto e : s)
+        if (e != 1) r.push_back(e);
+      return r;
+    };
+    // the same elements under another split of the row axes ([n, c, h, w] against [1, n * c, h, w])
+    const bool regrouped = n == R * C && shp.size() >= trail.size() &&
+                           std::equal(trail.begin(), trail.end(), shp.end() - (std::ptrdiff_t)trail.size());
+    if (shp == S || regrouped) {
       v.shape = {R, C};
     } else if (n == 1) {
       v.shape = {1};
+    } else if (only_reshaped && squeeze(shp) == squeeze(lead)) {
+      v.shape = {R};
     } else if (trailing_ones && std::equal(lead.begin(), lead.end(), shp.begin())) {
       v.shape = {R, 1};
     } else if (shp == lead) {
@@ -1220,17 +1237,19 @@ bool try_row_program(const Graph& gs, std::shared_ptr<RowProgram>* rp, std::vect
 // pieces live in the workspace.  GroupNorm (statistics on the [n, groups, rest] view, scale and shift per channel on
 // another view) or a LayerNorm followed by a transpose run as two launches this way.  Returns false when no piece is
 // a row region.
+struct Piece {
+  int a, b;
+  bool row;
+  std::shared_ptr<RowProgram> rp;
+  std::vector<int> in_vals, out_vals;  // graph values, in the order the piece's kernel(s) take them
+};
+bool assemble_pieces(const Graph& g, std::vector<Piece>& pieces, int sm_count, Plan* out);
+
 bool segmented_plan(const Graph& g, int sm_count, Plan* out) {
   const int n = (int)g.nodes.size();
   if (g.dynamic || n < 3 || n > 200) return false;
   for (auto& nd : g.nodes)
     if (nd.kind == OpK::Assign) return false;  // stores into inputs: keep the whole-region planner
-  struct Piece {
-    int a, b;
-    bool row;
-    std::shared_ptr<RowProgram> rp;
-    std::vector<int> in_vals, out_vals;  // graph values, in the order the piece's kernel(s) take them
-  };
   std::vector<Piece> pieces;
   bool any_row = false;
   int a = 0;
@@ -1266,6 +1285,82 @@ bool segmented_plan(const Graph& g, int sm_count, Plan* out) {
     }
   }
   if (!any_row || pieces.size() < 2) return false;
+  return assemble_pieces(g, pieces, sm_count, out);
+}
+
+// Cuts the op list behind every reduction and the per-result ops that follow it: a piece is an elementwise chain, the
+// reduction it feeds and the small ops on the reduced values, so each piece is planned as a region of its own (chain
+// folded into the reduction pass) and only reduced values cross pieces.  Batch normalisation in training mode (mean
+// over n, h, w; variance of the centred values; scale and shift) becomes three such pieces instead of materialising
+// the centred squares.  Returns false when nothing is cut.
+bool reduction_cut_plan(const Graph& g, int sm_count, Plan* out) {
+  const int n = (int)g.nodes.size();
+  if (g.dynamic || n < 3 || n > 200) return false;
+  for (auto& nd : g.nodes)
+    if (nd.kind == OpK::Assign) return false;
+  std::vector<std::pair<int, int>> ranges;
+  int a = 0;
+  bool seen_reduce = false;
+  int64_t reduced_numel = 0, large = 0;
+  for (int i = 0; i < n; ++i) {
+    const Node& nd = g.nodes[i];
+    const bool red = opk_is_reduce(nd.kind);
+    large = std::max(large, g.v(nd.out).numel());
+    if (seen_reduce && (red || g.v(nd.out).numel() > reduced_numel)) {
+      ranges.push_back({a, i});
+      a = i;
+      seen_reduce = false;
+    }
+    if (red) {
+      seen_reduce = true;
+      reduced_numel = g.v(nd.out).numel();
+    }
+  }
+  ranges.push_back({a, n});
+  if (ranges.size() < 2) return false;
+  // A full-size elementwise value of an earlier piece (the centred values x - mean, read again by the scale and
+  // shift) is computed again in the piece that reads it instead of crossing through memory: its operands are read
+  // there anyway or are small.
+  Graph g2 = g;
+  std::vector<Node> order;
+  std::vector<Piece> pieces;
+  for (size_t k = 0; k < ranges.size(); ++k) {
+    const int pa = ranges[k].first, pb = ranges[k].second;
+    const int start = (int)order.size();
+    std::map<int, int> again;  // value of an earlier piece -> its copy in this piece
+    int budget = 16;
+    std::function<int(int)> here = [&](int vid) -> int {
+      const Value& v = g.v(vid);
+      if (v.is_const || v.producer < 0 || v.producer >= pa || v.output_index >= 0 || v.numel() < large) return vid;
+      const Node& pn = g.nodes[v.producer];
+      if (!opk_is_elementwise(pn.kind)) return vid;
+      auto it = again.find(vid);
+      if (it != again.end()) return it->second;
+      if (--budget < 0) return vid;
+      Node c = pn;
+      for (int& u : c.in) u = here(u);
+      Value nv = v;
+      nv.name += "_again" + std::to_string(k);
+      nv.users.clear();
+      g2.values.push_back(nv);
+      c.out = (int)g2.values.size() - 1;
+      order.push_back(c);
+      again[vid] = c.out;
+      return c.out;
+    };
+    for (int i = pa; i < pb; ++i) {
+      Node nd = g.nodes[i];
+      for (int& u : nd.in) u = here(u);
+      order.push_back(std::move(nd));
+    }
+    pieces.push_back(Piece{start, (int)order.size(), false, nullptr, {}, {}});
+  }
+  g2.nodes = std::move(order);
+  relink(g2);
+  return assemble_pieces(g2, pieces, sm_count, out);
+}
+
+bool assemble_pieces(const Graph& g, std::vector<Piece>& pieces, int sm_count, Plan* out) {
   // A piece made of Reshape ops only is a change of view: its result shares the buffer of its operand (the producer
   // writes into the region's output directly when the view is one).
   std::map<int, int> same_buffer;  // value -> value whose buffer it uses
@@ -1444,6 +1539,14 @@ Plan build_plan(const Graph& g, int sm_count, bool allow_jit) {
       cut.flops = plan.flops;
       cut.fallback = std::make_shared<Plan>(std::move(plan));
       plan = std::move(cut);
+    } else if (Plan cut2; allow_jit && plan.steps.size() > 2 && g.op_class == OpClass::Reduction &&
+               reduction_cut_plan(g, sm_count, &cut2) &&
+               // fewer launches, or far less crossing launches in the workspace (no full-size intermediate is written)
+               (cut2.steps.size() < plan.steps.size() ||
+                (cut2.steps.size() <= plan.steps.size() + 2 && cut2.workspace_bytes * 2 < plan.workspace_bytes))) {
+      cut2.flops = plan.flops;
+      cut2.fallback = std::make_shared<Plan>(std::move(plan));
+      plan = std::move(cut2);
     }
   }
   plan.bytes = io_bytes(g);

@@ -440,6 +440,9 @@ def _stock_decompositions():
         aten.zeros_like, aten.full_like, aten.log_sigmoid_forward, aten.hardswish, aten.hardsigmoid,
         aten.native_batch_norm, aten._native_batch_norm_legit, aten._native_batch_norm_legit_no_training,
         aten._native_batch_norm_legit_functional, aten.native_group_norm, aten.repeat,
+        # what batch_norm / instance_norm dispatch to when traced on device tensors
+        aten.cudnn_batch_norm, aten.miopen_batch_norm, aten._batch_norm_with_update, aten._batch_norm_no_update,
+        aten._batch_norm_with_update_functional,
     ])
 
 
@@ -680,8 +683,35 @@ def trace(fn: Callable, example_inputs: Sequence[torch.Tensor]) -> fx.GraphModul
     gm = make_fx(torch.func.functionalize(fn), decomposition_table=_decompositions(),
                  tracing_mode="fake")(*example_inputs)
     _functionalize_leftovers(gm.graph)
+    _merge_repeated_ops(gm.graph)
     gm.recompile()
     return gm
+
+
+def _merge_repeated_ops(graph: fx.Graph) -> None:
+    """Common subexpressions: decompositions often compute the same value twice (the mean of batch normalisation, once
+    for the variance and once for the result); the later op is replaced by the earlier one.  Only ops with a lowering
+    are merged: all of them are pure functions of their arguments."""
+    def freeze(a):
+        if isinstance(a, (list, tuple)):
+            return tuple(freeze(v) for v in a)
+        if isinstance(a, dict):
+            return tuple(sorted((k, freeze(v)) for k, v in a.items()))
+        if isinstance(a, fx.Node):
+            return ("node", id(a))
+        return (type(a).__name__, a) if a.__hash__ is not None else ("obj", id(a))
+
+    seen = {}
+    for node in list(graph.nodes):
+        if node.op != "call_function" or node.target not in _LOWERINGS:
+            continue
+        if any(isinstance(u, fx.Node) and u.op == "call_function" and u.target in _INPLACE for u in node.users):
+            continue  # mutated later by an op that stayed in place
+        key = (node.target, freeze(node.args), freeze(node.kwargs))
+        first = seen.setdefault(key, node)
+        if first is not node:
+            node.replace_all_uses_with(first)
+            graph.erase_node(node)
 
 
 _INPLACE = {}

@@ -248,6 +248,20 @@ def test_planning_of_generated_kernels_needs_no_device(lib):
     assert FusedKernel(descs.mul_reduce_sum(64, 64, [0])).meta()["template"] != "akgb_col_jit"
 
 
+def test_batch_norm_training_is_planned_without_full_size_intermediates(lib):
+    """Cut at the reductions: the centred squares are folded into the variance pass, the centred values are computed
+    again by the scale-and-shift launch, so only per-channel values live in the workspace."""
+    import sys, os
+    sys.path.insert(0, os.path.dirname(__file__))
+    from test_gpu_generic import _batch_norm_training
+    from akg_b200 import FusedKernel
+    k = FusedKernel(_batch_norm_training([64, 256, 56, 56]))
+    meta = k.meta()
+    assert meta["steps"].count("akgb_row_jit") == 1 and meta["steps"][-1] == "ew_generic"
+    assert meta["workspace"] < (1 << 20) and len(meta["steps"]) == 7
+    assert FusedKernel(_batch_norm_training([64, 256, 56, 56]), flags=1).meta()["workspace"] > (100 << 20)
+
+
 def test_planning_of_the_wider_op_surface(lib):
     from akg_b200 import FusedKernel, descs
     from akg_b200.descs import _Builder, _attr, _reduce_attr

@@ -240,3 +240,68 @@ def test_random_cut_region(seed, flags):
     for g, w in zip(outs, want):
         assert g.shape == w.shape and g.dtype == w.dtype
         np.testing.assert_allclose(g.astype(np.float64), w.astype(np.float64), rtol=2e-5, atol=2e-5)
+
+
+def random_statistics_region(seed):
+    """Normalisation-like regions on [n, c, h, w]: one to three stages of (elementwise chain -> reduction over a random
+    axis set -> ops on the reduced values), then a full-size result that uses the statistics and earlier full-size
+    values. Statistics over (n, h, w), (h, w), (c, h, w), n or w."""
+    rng = np.random.default_rng(9000 + seed)
+    shape = [int(rng.choice([4, 8, 16])), int(rng.choice([16, 24, 32])), int(rng.choice([12, 20, 28])), int(rng.choice([24, 40, 56]))]
+    axes = [[0, 2, 3], [2, 3], [1, 2, 3], [0], [3]][int(rng.integers(5))]
+    stat = [1 if i in axes else s for i, s in enumerate(shape)]
+    count = int(np.prod([shape[i] for i in axes]))
+    b = _Builder(f"Fused_FuzzStat_{seed}")
+    x = b.input("x", shape, F)
+    per = b.input("p", stat, F)
+    full, stats = [x], [per]
+    if rng.random() < 0.5:
+        full.append(b.emit("Mul", [x, b.input("y", shape, F)], shape, F))
+    else:
+        full.append(b.emit("Add", [x, per], shape, F))
+    for _ in range(int(rng.integers(1, 4))):
+        cur = full[int(rng.integers(len(full)))]
+        for _ in range(int(rng.integers(0, 3))):
+            kind = int(rng.integers(4))
+            if kind == 0:
+                cur = b.emit(str(rng.choice(["Sub", "Mul", "Add"])), [cur, stats[int(rng.integers(len(stats)))]], shape, F)
+            elif kind == 1:
+                cur = b.emit("Mul", [cur, cur], shape, F)
+            elif kind == 2:
+                cur = b.emit(str(rng.choice(["Abs", "Tanh", "Neg"])), [cur], shape, F)
+            else:
+                cur = b.emit(str(rng.choice(["Sub", "Maximum"])), [cur, full[int(rng.integers(len(full)))]], shape, F)
+            full.append(cur)
+        op = str(rng.choice(["ReduceSum", "ReduceSum", "ReduceMax", "ReduceMin"]))
+        r = b.emit(op, [cur], stat, F, _reduce_attr(axes, True))
+        if op == "ReduceSum":
+            r = b.emit("Mul", [r, b.const(1.0 / count, F)], stat, F)
+        if rng.random() < 0.5:
+            r = b.emit("Rsqrt", [b.emit("Add", [b.emit("Abs", [r], stat, F), b.const(0.5, F)], stat, F)], stat, F)
+        stats.append(r)
+    y = full[int(rng.integers(len(full)))]
+    y = b.emit(str(rng.choice(["Sub", "Mul"])), [y, stats[-1]], shape, F)
+    y = b.emit("Add", [b.emit("Mul", [y, stats[int(rng.integers(1, len(stats)))]], shape, F), per], shape, F)
+    b.output(y)
+    if rng.random() < 0.6:
+        b.output(stats[-1])
+    desc = b.build()
+    ins = [rng.standard_normal(t[0]["shape"]).astype(np.float32) for t in desc["input_desc"]]
+    return desc, ins
+
+
+@pytest.mark.parametrize("seed", range(40))
+@pytest.mark.parametrize("flags", [0, 1], ids=["generated", "separate"])
+def test_random_statistics_region(seed, flags):
+    desc, ins = random_statistics_region(seed)
+    k = FusedKernel(desc, flags=flags)
+    outs = k.empty_outputs()
+    for o in outs:
+        o.view(np.uint8)[...] = 0xCD
+    k.run_host([a.copy() for a in ins] + outs)
+    assert k.check_device_error() == 0
+    want = O.evaluate(desc, ins, accum="float64")
+    for g, w in zip(outs, want):
+        assert g.shape == w.shape and g.dtype == w.dtype
+        scale = max(1.0, float(np.abs(w).max()))
+        np.testing.assert_allclose(g.astype(np.float64), w.astype(np.float64), rtol=5e-5, atol=5e-5 * scale)

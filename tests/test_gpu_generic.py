@@ -889,6 +889,46 @@ def test_per_channel_operands_in_front_of_a_batchnorm_style_reduction(lib):
         assert "(r / 1LL) % 24LL" in kern.jit_source()
 
 
+def _batch_norm_training(shape, io="float32", seed=0):
+    """Mean over (N, H, W), variance of the centred values, scale and shift; the centred values are used twice."""
+    f = "float32"
+    n_, c_, h_, w_ = shape
+    stat = [1, c_, 1, 1]
+    b = _Builder(f"Fused_BatchNormTraining_{seed}")
+    x0, gamma, beta = b.input("x", shape, io), b.input("gamma", stat, f), b.input("beta", stat, f)
+    x = x0 if io == f else b.emit("Cast", [x0], shape, f, [_attr("dst_type", "str", f)])
+    inv = b.const(1.0 / (n_ * h_ * w_), f)
+    mean = b.emit("Mul", [b.emit("ReduceSum", [x], stat, f, _reduce_attr([0, 2, 3], True)), inv], stat, f)
+    d_ = b.emit("Sub", [x, mean], shape, f)
+    var = b.emit("Mul", [b.emit("ReduceSum", [b.emit("Mul", [d_, d_], shape, f)], stat, f, _reduce_attr([0, 2, 3], True)), inv], stat, f)
+    rstd = b.emit("Rsqrt", [b.emit("Add", [var, b.const(1e-5, f)], stat, f)], stat, f)
+    y = b.emit("Add", [b.emit("Mul", [b.emit("Mul", [d_, rstd], shape, f), gamma], shape, f), beta], shape, f)
+    b.output(y if io == f else b.emit("Cast", [y], shape, io, [_attr("dst_type", "str", io)]))
+    b.output(mean)
+    b.output(rstd)
+    return b.build()
+
+
+@pytest.mark.parametrize("io", ["float32", "float16"])
+def test_batch_norm_training_region_is_cut_at_its_reductions(lib, io):
+    """Three pieces (mean; centred squares folded into the variance pass; scale and shift with the centred values
+    computed again): only per-channel values cross launches."""
+    rng = np.random.default_rng(106)
+    shape = [6, 40, 24, 24]
+    d = _batch_norm_training(shape, io, 106)
+    ins = [(rng.standard_normal(shape) * 2 + 0.5).astype(np.dtype(io)), rng.uniform(0.5, 1.5, [1, 40, 1, 1]).astype(np.float32),
+           rng.standard_normal([1, 40, 1, 1]).astype(np.float32)]
+    got, kern = run(d, ins)
+    want = O.evaluate(d, ins, accum="float64")
+    np.testing.assert_allclose(got[0].astype(np.float32), want[0].astype(np.float32), rtol=2e-3 if io == "float16" else 1e-5,
+                               atol=2e-3 if io == "float16" else 1e-5)
+    np.testing.assert_allclose(got[1], want[1], rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(got[2], want[2], rtol=1e-5, atol=1e-6)
+    if FLAGS[0] == 0:
+        meta = kern.meta()
+        assert "akgb_row_jit" in meta["steps"] and meta["workspace"] < 4 * shape[0] * shape[1] * 64
+
+
 def test_instance_norm_on_nchw_is_one_row_kernel(lib):
     """Mean / variance over (H, W) with keep_dims, per-channel scale and shift of shape [1, C, 1, 1]."""
     rng = np.random.default_rng(104)

@@ -282,3 +282,15 @@ def test_more_programs_on_the_device(name):
     ins = [t.cuda() for t in make(_g(1))]
     fused = TF.fuse_and_optimize(fn, ins)
     _close(fused(*ins), fn(*ins), 2e-5)
+
+
+def test_batch_norm_as_traced_on_device_tensors():
+    """On device tensors batch_norm / instance_norm trace to the vendor-library op; it is decomposed like the native one."""
+    g = torch.Generator().manual_seed(0)
+    x, w, b = torch.randn(4, 8, 12, 16, generator=g), torch.rand(8, generator=g) + 0.5, torch.randn(8, generator=g)
+    fn = lambda x, w, b: torch.ops.aten.cudnn_batch_norm(x, w, b, None, None, True, 0.1, 1e-5)[0]
+    fused = TF.fuse_and_optimize(fn, [x, w, b], executor=oracle_executor)
+    assert len(fused.subgraphs) == 1
+    kept = [n.target for n in fused.gm.graph.nodes if n.op == "call_function" and n.target is torch.ops.aten.cudnn_batch_norm.default]
+    assert not kept
+    _close(fused(x, w, b), torch.nn.functional.batch_norm(x, None, None, w, b, training=True), 1e-5)
