@@ -152,8 +152,9 @@ akgb_status akgb_profile_host(akgb_kernel* k, void* const* host_tensors, int32_t
 /* The launch metadata the reference writes to <kernel>.json
  * (lib/Dialect/GPU/Transforms/GPUMapping.cpp:645-703,
  * python/akg_mlir/mlir_driver.py:776-815): blockIdx.{x,y,z}, threadIdx.{x,y,z},
- * kernelName, is_dynamic, sha256 — plus class, bytes, flops.  Writes a
- * NUL-terminated JSON text; `*needed` receives the size including the NUL. */
+ * kernelName, is_dynamic, sha256 — plus class, template, bytes, flops, smem,
+ * workspace, launches and "steps" (the kernel family of every step of the
+ * plan, in launch order).  Writes a NUL-terminated JSON text; `*needed` receives the size including the NUL. */
 akgb_status akgb_kernel_meta(const akgb_kernel* k, char* buf, size_t cap, size_t* needed);
 
 /* The CUDA C++ text that is compiled at run time for the first generic elementwise group of the region
