@@ -311,6 +311,38 @@ def _op_cases():
     t = b.emit("Transpose", [p], [10, 6, 128], f, [_attr("perm", "listInt", [1, 0, 2])])
     b.output(b.emit("Mul", [t, b.const(0.5, f)], [10, 6, 128], f))
     cases["softmax_transpose_scale"] = b.build()
+
+    # batch normalisation in training mode: three reductions' worth of pieces, the centred values used twice
+    b = _Builder("Fused_BatchNormTraining_21")
+    x, gamma, beta = b.input("x", nchw, f), b.input("gamma", stat, f), b.input("beta", stat, f)
+    inv = b.const(1.0 / (8 * 16 * 16), f)
+    mean = b.emit("Mul", [b.emit("ReduceSum", [x], stat, f, _reduce_attr([0, 2, 3], True)), inv], stat, f)
+    dlt = b.emit("Sub", [x, mean], nchw, f)
+    var = b.emit("Mul", [b.emit("ReduceSum", [b.emit("Mul", [dlt, dlt], nchw, f)], stat, f, _reduce_attr([0, 2, 3], True)), inv], stat, f)
+    rstd = b.emit("Rsqrt", [b.emit("Add", [var, b.const(1e-5, f)], stat, f)], stat, f)
+    b.output(b.emit("Add", [b.emit("Mul", [b.emit("Mul", [dlt, rstd], nchw, f), gamma], nchw, f), beta], nchw, f))
+    b.output(mean)
+    b.output(rstd)
+    cases["batch_norm_training_nchw"] = b.build()
+
+    # rows too long for a thread group's registers
+    b = _Builder("Fused_LogSoftmax_22")
+    x = b.input("x", [3, 20000], f)
+    m = b.emit("ReduceMax", [x], [3, 1], f, _reduce_attr([1], True))
+    d = b.emit("Sub", [x, m], [3, 20000], f)
+    e = b.emit("ReduceSum", [b.emit("Exp", [d], [3, 20000], f)], [3, 1], f, _reduce_attr([1], True))
+    b.output(b.emit("Sub", [d, b.emit("Log", [e], [3, 1], f)], [3, 20000], f))
+    cases["log_softmax_long_rows"] = b.build()
+
+    b = _Builder("Fused_RMSNorm_23")
+    x, g_ = b.input("x", [2, 16392], h), b.input("g", [16392], h)
+    xf = b.emit("Cast", [x], [2, 16392], f, [_attr("dst_type", "str", f)])
+    ms = b.emit("Mul", [b.emit("ReduceSum", [b.emit("Mul", [xf, xf], [2, 16392], f)], [2, 1], f, _reduce_attr([1], True)),
+                        b.const(1.0 / 16392, f)], [2, 1], f)
+    y = b.emit("Mul", [xf, b.emit("Rsqrt", [b.emit("Add", [ms, b.const(1e-6, f)], [2, 1], f)], [2, 1], f)], [2, 16392], f)
+    y = b.emit("Mul", [y, b.emit("Cast", [g_], [16392], f, [_attr("dst_type", "str", f)])], [2, 16392], f)
+    b.output(b.emit("Cast", [y], [2, 16392], h, [_attr("dst_type", "str", h)]))
+    cases["rmsnorm_long_rows_f16"] = b.build()
     return cases
 
 
