@@ -1005,25 +1005,24 @@ void shift_ref(Ref& r, const std::vector<Ref>& args, int64_t ws_base) {
   else if (r.ws_off >= 0) r.ws_off += ws_base;
 }
 
-// An elementwise chain over equally shaped tensors, ONE reduction whose axes include the trailing axes, then anything on
-// the reduced values (BatchNorm statistics on NCHW: Mul(x, x) -> ReduceSum over (0, 2, 3) -> Mul(1/n)).  The chain and
+// Elementwise chains over equally shaped tensors, the reductions they feed (one to four, same axes, which include the
+// trailing axes, none needing another's result), then anything on the reduced values (BatchNorm statistics on NCHW: Mul(x, x) -> ReduceSum over (0, 2, 3) -> Mul(1/n)).  The chain and
 // the fold over the trailing axes run as one generated row kernel on the [rows, cols] view; what remains (a reduction
 // over the other axes, the ops behind it) is planned on its own with the row results as its input.
 bool fused_reduce_tail_plan(const Graph& g, int sm_count, bool allow_jit, Plan* out) {
   if (g.dynamic || g.nodes.size() < 2) return false;
+  const int nn = (int)g.nodes.size();
   int ri = -1;
-  for (size_t i = 0; i < g.nodes.size(); ++i)
+  for (int i = 0; i < nn; ++i)
     if (opk_is_reduce(g.nodes[i].kind)) {
-      ri = (int)i;
+      ri = i;
       break;
     }
-  if (ri < 1) return false;  // no chain in front of the reduction: the hand-written reductions do it
+  if (ri < 0) return false;
   const Node& red = g.nodes[ri];
-  if (red.kind != OpK::ReduceSum && red.kind != OpK::ReduceMax && red.kind != OpK::ReduceMin && red.kind != OpK::ReduceProd)
-    return false;
   const Value& x = g.v(red.in[0]);
   const size_t rank = x.shape.size();
-  if (x.dt != DT::F32 || g.v(red.out).dt != DT::F32 || rank == 0) return false;
+  if (rank == 0) return false;
   std::vector<bool> is_red(rank, false);
   for (auto a : red.axes) is_red[a] = true;
   // the trailing run: from the last axis backwards while the axis is reduced (extent-1 axes ride along)
@@ -1033,13 +1032,45 @@ bool fused_reduce_tail_plan(const Graph& g, int sm_count, bool allow_jit, Plan* 
   for (size_t i = first; i < rank; ++i) C *= x.shape[i];
   if (first == 0 || C < 8 || C > (1 << 20) || n < (1 << 16)) return false;  // all axes: the re-viewed plan above
   const int64_t R = n / C;
-  // the chain: elementwise ops over tensors of exactly x's element count, none of them a result of the region
-  std::map<int, std::pair<int64_t, int64_t>> row_index;
-  for (int i = 0; i < ri; ++i) {
+  // Front: the ops that need no reduction result — elementwise ops over x's shape (the chains) and the reductions of
+  // such values over the same axes (up to four share the pass).  Everything else is the rest.
+  enum { REST = 0, CHAIN = 1, FOLD = 2 };
+  std::vector<int> role(nn, REST);
+  std::vector<char> dep(nn, 0);
+  std::vector<int> folds;
+  for (int i = 0; i < nn; ++i) {
     const Node& nd = g.nodes[i];
-    if (!opk_is_elementwise(nd.kind) || nd.kind == OpK::AddN) return false;
+    for (int vid : nd.in) {
+      const int p = g.v(vid).producer;
+      if (p >= 0 && (dep[p] || opk_is_reduce(g.nodes[p].kind))) dep[i] = 1;
+    }
+    if (dep[i]) continue;
     const Value& ov = g.v(nd.out);
-    if (ov.numel() != n || ov.shape != x.shape || ov.output_index >= 0) return false;
+    if (opk_is_reduce(nd.kind)) {
+      if (nd.kind != OpK::ReduceSum && nd.kind != OpK::ReduceMax && nd.kind != OpK::ReduceMin && nd.kind != OpK::ReduceProd)
+        return false;
+      if (g.v(nd.in[0]).shape != x.shape || nd.axes != red.axes || g.v(nd.in[0]).dt != DT::F32 || ov.dt != DT::F32) return false;
+      role[i] = FOLD;
+      folds.push_back(i);
+    } else if (opk_is_elementwise(nd.kind) && nd.kind != OpK::AddN && ov.shape == x.shape) {
+      role[i] = CHAIN;
+    }
+  }
+  bool any_chain = false;
+  for (int i = 0; i < nn; ++i) any_chain = any_chain || role[i] == CHAIN;
+  // (a single reduction with no chain in front: the hand-written reductions do it)
+  if (folds.empty() || folds.size() > 4 || !any_chain) return false;
+  std::map<int, std::pair<int64_t, int64_t>> row_index;
+  for (int i = 0; i < nn; ++i) {
+    const Node& nd = g.nodes[i];
+    if (role[i] == REST) {
+      // the rest works on reduced values: nothing of x's size is read or made there
+      if (opk_is_reduce(nd.kind) && g.v(nd.in[0]).numel() == n) return false;
+      continue;
+    }
+    if (role[i] != CHAIN) continue;
+    const Value& ov = g.v(nd.out);
+    if (ov.output_index >= 0) return false;
     for (int vid : nd.in) {
       const Value& v = g.v(vid);
       if (v.is_const || v.shape == x.shape) continue;
@@ -1063,28 +1094,36 @@ bool fused_reduce_tail_plan(const Graph& g, int sm_count, bool allow_jit, Plan* 
       row_index[vid] = {div, mod};
     }
     for (int u : ov.users)
-      if (u > ri) return false;  // the chain's values are not kept for the ops behind the reduction
+      if (role[u] == REST) return false;  // the chain's values are not kept for the ops behind the reductions
   }
-  // 1. the row program: chain + reduction over the trailing run on the [R, C] view
+  // 1. the row program: chains + folds over the trailing run on the [R, C] view
   Graph g2 = g;
-  g2.nodes.resize(ri + 1);
+  g2.nodes.clear();
+  for (int i = 0; i < nn; ++i)
+    if (role[i] != REST) g2.nodes.push_back(g.nodes[i]);
   for (auto& v : g2.values) {
     v.output_index = -1;
     if (!v.is_const && v.shape == x.shape) v.shape = {R, C};
   }
-  Node& red2 = g2.nodes.back();
-  red2.axes = {1};
-  red2.keep_dims = false;
-  g2.v(red2.out).shape = {R};
-  g2.v(red2.out).output_index = 0;
-  g2.outputs = {red2.out};
+  g2.outputs.clear();
+  for (Node& nd : g2.nodes) {
+    if (!opk_is_reduce(nd.kind)) continue;
+    nd.axes = {1};
+    nd.keep_dims = false;
+    g2.v(nd.out).shape = {R};
+    g2.v(nd.out).output_index = (int)g2.outputs.size();
+    g2.outputs.push_back(nd.out);
+  }
   relink(g2);
   auto rp = std::make_shared<RowProgram>();
   std::vector<int> in_values, out_values;
-  if (!build_row_program(g2, rp.get(), &in_values, &out_values, false, &row_index) || out_values.size() != 1) return false;
+  if (!build_row_program(g2, rp.get(), &in_values, &out_values, false, &row_index) || out_values.size() != folds.size())
+    return false;
+  for (size_t j = 0; j < folds.size(); ++j)
+    if (out_values[j] != g.nodes[folds[j]].out) return false;
   bool only_trailing = true;
   for (auto a : red.axes) only_trailing = only_trailing && ((size_t)a >= first || x.shape[a] == 1);
-  if (only_trailing && (size_t)ri + 1 == g.nodes.size() && g.outputs.size() == 1 && g.outputs[0] == red.out) {
+  if (only_trailing && folds.size() == 1 && (size_t)ri + 1 == g.nodes.size() && g.outputs.size() == 1 && g.outputs[0] == red.out) {
     // nothing behind the fold over the trailing axes: the row results are the region's result
     Plan p;
     p.klass = "reduce_x";
@@ -1104,35 +1143,43 @@ bool fused_reduce_tail_plan(const Graph& g, int sm_count, bool allow_jit, Plan* 
     *out = std::move(p);
     return true;
   }
-  // 2. the rest: the row results stand in for the reduction's operand, with the trailing run folded to extent 1
+  // 2. the rest: the row results stand in for the reductions' operands, with the trailing run folded to extent 1
+  const int64_t each = (int64_t)(((size_t)R * sizeof(float) + 255) / 256 * 256);
   Graph g3 = g;
-  g3.nodes.erase(g3.nodes.begin(), g3.nodes.begin() + ri);
-  Value part;
-  part.name = "akgb_row_results";
-  part.shape = x.shape;
-  for (size_t i = first; i < rank; ++i) part.shape[i] = 1;
-  part.dt = DT::F32;
-  const int pid = (int)g3.values.size();
-  g3.values.push_back(part);
-  Node& red3 = g3.nodes.front();
-  red3.in[0] = pid;
+  g3.nodes.clear();
+  std::vector<Ref> arg_map;
+  std::vector<int> new_inputs;
   std::vector<int64_t> rest_axes;
   for (auto a : red.axes)
     if ((size_t)a < first && x.shape[a] != 1) rest_axes.push_back(a);
-  if (rest_axes.empty()) {
-    red3.kind = OpK::Reshape;  // nothing left to fold: the row results are the reduction's result
-    red3.name = "Reshape";
-    red3.axes.clear();
-  } else {
-    red3.axes = rest_axes;
+  for (int i = 0; i < nn; ++i) {
+    if (role[i] == CHAIN) continue;
+    g3.nodes.push_back(g.nodes[i]);
+    if (role[i] != FOLD) continue;
+    Value part;
+    part.name = "akgb_row_results" + std::to_string(new_inputs.size());
+    part.shape = x.shape;
+    for (size_t d = first; d < rank; ++d) part.shape[d] = 1;
+    part.dt = DT::F32;
+    part.input_index = (int)new_inputs.size();
+    const int pid = (int)g3.values.size();
+    g3.values.push_back(part);
+    Ref partial;
+    partial.ws_off = each * (int64_t)new_inputs.size();
+    arg_map.push_back(partial);
+    new_inputs.push_back(pid);
+    Node& red3 = g3.nodes.back();
+    red3.in[0] = pid;
+    if (rest_axes.empty()) {
+      red3.kind = OpK::Reshape;  // nothing left to fold: the row results are the reduction's result
+      red3.name = "Reshape";
+      red3.axes.clear();
+    } else {
+      red3.axes = rest_axes;
+    }
   }
   relink(g3);
   // inputs of the rest: the row results first, then the region's inputs it still reads
-  std::vector<Ref> arg_map;
-  Ref partial;
-  partial.ws_off = 0;
-  arg_map.push_back(partial);
-  std::vector<int> new_inputs = {pid};
   for (int vid : g.inputs) {
     if (g3.values[vid].users.empty()) {
       g3.values[vid].input_index = -1;
@@ -1144,10 +1191,9 @@ bool fused_reduce_tail_plan(const Graph& g, int sm_count, bool allow_jit, Plan* 
     g3.values[vid].input_index = (int)new_inputs.size();
     new_inputs.push_back(vid);
   }
-  g3.values[pid].input_index = 0;
   g3.inputs = new_inputs;
   for (int vid : g3.outputs)
-    if (g3.values[vid].producer < 0) return false;  // a result that is not produced behind the reduction
+    if (g3.values[vid].producer < 0) return false;  // a result that is not produced behind the reductions
   for (size_t i = 0; i < g.outputs.size(); ++i) {
     Ref r;
     r.arg = (int)g.inputs.size() + (int)i;
@@ -1161,7 +1207,7 @@ bool fused_reduce_tail_plan(const Graph& g, int sm_count, bool allow_jit, Plan* 
     return false;
   }
   if (rest.fallback) return false;  // keep it to plans with one way of running
-  const int64_t ws_base = (int64_t)(((size_t)R * sizeof(float) + 255) / 256 * 256);
+  const int64_t ws_base = each * (int64_t)folds.size();
   Plan p;
   p.klass = g.reduce_dir == ReduceDir::All ? "reduce_all" : g.reduce_dir == ReduceDir::Y ? "reduce_y" : "reduce_x";
   Step st;
@@ -1173,7 +1219,7 @@ bool fused_reduce_tail_plan(const Graph& g, int sm_count, bool allow_jit, Plan* 
     ref.arg = g.v(vid).input_index;
     st.ew_in.push_back(ref);
   }
-  st.ew_out.push_back(partial);
+  for (size_t j = 0; j < folds.size(); ++j) st.ew_out.push_back(arg_map[j]);
   p.steps.push_back(std::move(st));
   for (Step& s2 : rest.steps) {
     for (Ref* r : {&s2.a, &s2.b, &s2.c, &s2.out, &s2.out2, &s2.out3, &s2.scratch}) shift_ref(*r, arg_map, ws_base);
@@ -1293,30 +1339,85 @@ bool segmented_plan(const Graph& g, int sm_count, Plan* out) {
 // folded into the reduction pass) and only reduced values cross pieces.  Batch normalisation in training mode (mean
 // over n, h, w; variance of the centred values; scale and shift) becomes three such pieces instead of materialising
 // the centred squares.  Returns false when nothing is cut.
-bool reduction_cut_plan(const Graph& g, int sm_count, Plan* out) {
+// Op order by stage: a value's stage counts the reductions whose results it needs.  Independent reductions (the two
+// sums of a batch-norm backward pass) share a stage and therefore a pass over their operands; the small ops on reduced
+// values stay with the reduction that feeds them.  Returns the end of each stage in the new op list.
+std::vector<int> order_by_stage(Graph& g) {
   const int n = (int)g.nodes.size();
-  if (g.dynamic || n < 3 || n > 200) return false;
-  for (auto& nd : g.nodes)
-    if (nd.kind == OpK::Assign) return false;
-  std::vector<std::pair<int, int>> ranges;
-  int a = 0;
-  bool seen_reduce = false;
-  int64_t reduced_numel = 0, large = 0;
+  int64_t large = 0;
+  for (auto& nd : g.nodes) large = std::max(large, g.v(nd.out).numel());
+  std::vector<int> stage(n, 0);
+  std::vector<char> reduced(n, 0);  // the op works on reduced values only
   for (int i = 0; i < n; ++i) {
     const Node& nd = g.nodes[i];
     const bool red = opk_is_reduce(nd.kind);
-    large = std::max(large, g.v(nd.out).numel());
-    if (seen_reduce && (red || g.v(nd.out).numel() > reduced_numel)) {
-      ranges.push_back({a, i});
-      a = i;
-      seen_reduce = false;
+    bool all_small = !red && g.v(nd.out).numel() < large;
+    int st = 0;
+    for (int vid : nd.in) {
+      const Value& v = g.v(vid);
+      if (v.is_const || v.producer < 0) {
+        all_small = all_small && v.numel() < large;
+        continue;
+      }
+      all_small = all_small && reduced[v.producer];
     }
-    if (red) {
-      seen_reduce = true;
-      reduced_numel = g.v(nd.out).numel();
+    for (int vid : nd.in) {
+      const int p = g.v(vid).producer;
+      if (p < 0) continue;
+      st = std::max(st, stage[p] + ((reduced[p] && !all_small) ? 1 : 0));
+    }
+    stage[i] = st;
+    reduced[i] = red || all_small;
+  }
+  std::vector<int> idx(n);
+  for (int i = 0; i < n; ++i) idx[i] = i;
+  std::stable_sort(idx.begin(), idx.end(), [&](int x, int y) { return stage[x] < stage[y]; });
+  std::vector<Node> sorted;
+  std::vector<int> ends;
+  for (int k = 0; k < n; ++k) {
+    if (k && stage[idx[k]] != stage[idx[k - 1]]) ends.push_back(k);
+    sorted.push_back(g.nodes[idx[k]]);
+  }
+  ends.push_back(n);
+  g.nodes = std::move(sorted);
+  relink(g);
+  return ends;
+}
+
+bool reduction_cut_plan(const Graph& g0, int sm_count, bool by_stage, Plan* out) {
+  const int n = (int)g0.nodes.size();
+  if (g0.dynamic || n < 3 || n > 200) return false;
+  for (auto& nd : g0.nodes)
+    if (nd.kind == OpK::Assign) return false;
+  Graph g = g0;
+  std::vector<std::pair<int, int>> ranges;
+  int a = 0;
+  int64_t large = 0;
+  for (auto& nd : g.nodes) large = std::max(large, g.v(nd.out).numel());
+  if (by_stage) {
+    for (int e : order_by_stage(g)) {
+      ranges.push_back({a, e});
+      a = e;
+    }
+    a = n;
+  } else {
+    bool seen_reduce = false;
+    int64_t reduced_numel = 0;
+    for (int i = 0; i < n; ++i) {
+      const Node& nd = g.nodes[i];
+      const bool red = opk_is_reduce(nd.kind);
+      if (seen_reduce && (red || g.v(nd.out).numel() > reduced_numel)) {
+        ranges.push_back({a, i});
+        a = i;
+        seen_reduce = false;
+      }
+      if (red) {
+        seen_reduce = true;
+        reduced_numel = g.v(nd.out).numel();
+      }
     }
   }
-  ranges.push_back({a, n});
+  if (a < n) ranges.push_back({a, n});
   if (ranges.size() < 2) return false;
   // A full-size elementwise value of an earlier piece (the centred values x - mean, read again by the scale and
   // shift) is computed again in the piece that reads it instead of crossing through memory: its operands are read
@@ -1539,14 +1640,23 @@ Plan build_plan(const Graph& g, int sm_count, bool allow_jit) {
       cut.flops = plan.flops;
       cut.fallback = std::make_shared<Plan>(std::move(plan));
       plan = std::move(cut);
-    } else if (Plan cut2; allow_jit && plan.steps.size() > 2 && g.op_class == OpClass::Reduction &&
-               reduction_cut_plan(g, sm_count, &cut2) &&
-               // fewer launches, or far less crossing launches in the workspace (no full-size intermediate is written)
-               (cut2.steps.size() < plan.steps.size() ||
-                (cut2.steps.size() <= plan.steps.size() + 2 && cut2.workspace_bytes * 2 < plan.workspace_bytes))) {
-      cut2.flops = plan.flops;
-      cut2.fallback = std::make_shared<Plan>(std::move(plan));
-      plan = std::move(cut2);
+    } else if (allow_jit && plan.steps.size() > 2 && g.op_class == OpClass::Reduction) {
+      // cut at the reductions, in the given op order or stage by stage: the variant with the smaller workspace (fewer
+      // full-size values crossing launches), then the one with fewer launches
+      Plan c1, c2;
+      const bool ok1 = reduction_cut_plan(g, sm_count, false, &c1), ok2 = reduction_cut_plan(g, sm_count, true, &c2);
+      auto better = [](const Plan& x, const Plan& y) {
+        const size_t wx = x.workspace_bytes >> 20, wy = y.workspace_bytes >> 20;
+        return wx != wy ? wx < wy : x.steps.size() < y.steps.size();
+      };
+      Plan* cut2 = ok1 && ok2 ? (better(c2, c1) ? &c2 : &c1) : ok1 ? &c1 : ok2 ? &c2 : nullptr;
+      // taken with fewer launches, or far less workspace (no full-size intermediate is written)
+      if (cut2 && (cut2->steps.size() < plan.steps.size() ||
+                   (cut2->steps.size() <= plan.steps.size() + 2 && cut2->workspace_bytes * 2 < plan.workspace_bytes))) {
+        cut2->flops = plan.flops;
+        cut2->fallback = std::make_shared<Plan>(std::move(plan));
+        plan = std::move(*cut2);
+      }
     }
   }
   plan.bytes = io_bytes(g);

@@ -443,6 +443,10 @@ def _stock_decompositions():
         # what batch_norm / instance_norm dispatch to when traced on device tensors
         aten.cudnn_batch_norm, aten.miopen_batch_norm, aten._batch_norm_with_update, aten._batch_norm_no_update,
         aten._batch_norm_with_update_functional,
+        # backward passes of the normalisations and softmaxes
+        aten.native_batch_norm_backward, aten.cudnn_batch_norm_backward, aten.batch_norm_backward,
+        aten.native_layer_norm_backward, aten.native_group_norm_backward, aten._softmax_backward_data,
+        aten._log_softmax_backward_data,
     ])
 
 

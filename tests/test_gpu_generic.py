@@ -929,6 +929,45 @@ def test_batch_norm_training_region_is_cut_at_its_reductions(lib, io):
         assert "akgb_row_jit" in meta["steps"] and meta["workspace"] < 4 * shape[0] * shape[1] * 64
 
 
+def _batch_norm_backward(shape, seed=0):
+    """dbeta = sum dy, dgamma = sum dy * xhat over (N, H, W), dx = gamma * rstd * (dy - dbeta / m - xhat * dgamma / m)."""
+    f = "float32"
+    n_, c_, h_, w_ = shape
+    stat = [1, c_, 1, 1]
+    m_ = n_ * h_ * w_
+    b = _Builder(f"Fused_BatchNormGrad_{seed}")
+    dy, x = b.input("dy", shape, f), b.input("x", shape, f)
+    mean, rstd, gamma = b.input("mean", stat, f), b.input("rstd", stat, f), b.input("gamma", stat, f)
+    xhat = b.emit("Mul", [b.emit("Sub", [x, mean], shape, f), rstd], shape, f)
+    dbeta = b.emit("ReduceSum", [dy], stat, f, _reduce_attr([0, 2, 3], True))
+    dgamma = b.emit("ReduceSum", [b.emit("Mul", [dy, xhat], shape, f)], stat, f, _reduce_attr([0, 2, 3], True))
+    inv = b.const(1.0 / m_, f)
+    t = b.emit("Sub", [dy, b.emit("Mul", [dbeta, inv], stat, f)], shape, f)
+    t = b.emit("Sub", [t, b.emit("Mul", [xhat, b.emit("Mul", [dgamma, inv], stat, f)], shape, f)], shape, f)
+    b.output(b.emit("Mul", [t, b.emit("Mul", [gamma, rstd], stat, f)], shape, f))
+    b.output(dgamma)
+    b.output(dbeta)
+    return b.build()
+
+
+def test_batch_norm_backward_folds_both_sums_in_one_pass(lib):
+    rng = np.random.default_rng(107)
+    shape, stat = [6, 40, 24, 24], [1, 40, 1, 1]
+    d = _batch_norm_backward(shape, 107)
+    ins = [rng.standard_normal(shape).astype(np.float32), (rng.standard_normal(shape) * 2 + 0.5).astype(np.float32),
+           rng.standard_normal(stat).astype(np.float32) * 0.1 + 0.5, rng.uniform(0.4, 0.6, stat).astype(np.float32),
+           rng.uniform(0.5, 1.5, stat).astype(np.float32)]
+    got, kern = run(d, ins)
+    want = O.evaluate(d, ins, accum="float64")
+    np.testing.assert_allclose(got[0], want[0], rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(got[1], want[1], rtol=1e-4, atol=1e-3)
+    np.testing.assert_allclose(got[2], want[2], rtol=1e-4, atol=1e-3)
+    if FLAGS[0] == 0:
+        meta = kern.meta()
+        assert meta["steps"].count("akgb_row_jit") == 1 and meta["workspace"] < (1 << 20)
+        assert "out1" in kern.jit_source()  # one generated kernel with both row results
+
+
 def test_instance_norm_on_nchw_is_one_row_kernel(lib):
     """Mean / variance over (H, W) with keep_dims, per-channel scale and shift of shape [1, C, 1, 1]."""
     rng = np.random.default_rng(104)
