@@ -82,6 +82,11 @@ def _g(seed=0):
     return torch.Generator().manual_seed(seed)
 
 
+def _pull(fn, primals, dy):
+    out, pull = torch.func.vjp(fn, *primals)
+    return pull(dy)
+
+
 MORE = {
     "softmax_dim1": (lambda x: torch.softmax(x, dim=1), lambda g: [torch.randn(4, 16, 32, generator=g)]),
     "center_over_axes_0_2": (lambda x: (x - x.mean(dim=(0, 2), keepdim=True)) * 2,
@@ -109,6 +114,18 @@ MORE = {
     "group_norm": (lambda x, w, b: torch.nn.functional.group_norm(x, 4, w, b),
                    lambda g: [torch.randn(2, 8, 12, 16, generator=g), torch.rand(8, generator=g) + 0.5,
                               torch.randn(8, generator=g)]),
+    # forward and backward in one trace: the backward ops of normalisations and softmaxes are decomposed too
+    "layer_norm_backward": (lambda x, w, b, dy: _pull(lambda x, w, b: torch.nn.functional.layer_norm(x, (64,), w, b), (x, w, b), dy),
+                            lambda g: [torch.randn(24, 64, generator=g), torch.rand(64, generator=g) + 0.5,
+                                       torch.randn(64, generator=g), torch.randn(24, 64, generator=g)]),
+    "softmax_backward": (lambda x, dy: _pull(lambda x: torch.softmax(x, -1), (x,), dy),
+                         lambda g: [torch.randn(24, 64, generator=g), torch.randn(24, 64, generator=g)]),
+    "log_softmax_backward": (lambda x, dy: _pull(lambda x: torch.log_softmax(x, -1), (x,), dy),
+                             lambda g: [torch.randn(24, 64, generator=g), torch.randn(24, 64, generator=g)]),
+    "batch_norm_backward": (lambda x, w, b, dy: _pull(lambda x, w, b: torch.nn.functional.batch_norm(x, None, None, w, b, training=True),
+                                                      (x, w, b), dy),
+                            lambda g: [torch.randn(4, 8, 12, 16, generator=g), torch.rand(8, generator=g) + 0.5,
+                                       torch.randn(8, generator=g), torch.randn(4, 8, 12, 16, generator=g)]),
     "gelu_erf_stays_with_torch": (lambda x: torch.nn.functional.gelu(x) * 2, lambda g: [torch.randn(8, 64, generator=g)]),
 }
 
