@@ -259,3 +259,44 @@ def unary(op: str, shape: Sequence[int], dtype: str) -> dict:
     x = b.input("x", shape, dtype)
     b.output(b.emit(op, [x], shape, dtype, out_name="out"))
     return b.build()
+
+
+def batch_norm_training(shape: Sequence[int], io: str = "float32", seed: int = 0) -> dict:
+    """Mean over (N, H, W), variance of the centred values, scale and shift; the centred values are used twice."""
+    f = "float32"
+    n_, c_, h_, w_ = shape
+    stat = [1, c_, 1, 1]
+    b = _Builder(f"Fused_BatchNormTraining_{seed}")
+    x0, gamma, beta = b.input("x", shape, io), b.input("gamma", stat, f), b.input("beta", stat, f)
+    x = x0 if io == f else b.emit("Cast", [x0], shape, f, [_attr("dst_type", "str", f)])
+    inv = b.const(1.0 / (n_ * h_ * w_), f)
+    mean = b.emit("Mul", [b.emit("ReduceSum", [x], stat, f, _reduce_attr([0, 2, 3], True)), inv], stat, f)
+    d_ = b.emit("Sub", [x, mean], shape, f)
+    var = b.emit("Mul", [b.emit("ReduceSum", [b.emit("Mul", [d_, d_], shape, f)], stat, f, _reduce_attr([0, 2, 3], True)), inv], stat, f)
+    rstd = b.emit("Rsqrt", [b.emit("Add", [var, b.const(1e-5, f)], stat, f)], stat, f)
+    y = b.emit("Add", [b.emit("Mul", [b.emit("Mul", [d_, rstd], shape, f), gamma], shape, f), beta], shape, f)
+    b.output(y if io == f else b.emit("Cast", [y], shape, io, [_attr("dst_type", "str", io)]))
+    b.output(mean)
+    b.output(rstd)
+    return b.build()
+
+
+def batch_norm_backward(shape: Sequence[int], seed: int = 0) -> dict:
+    """dbeta = sum dy, dgamma = sum dy * xhat over (N, H, W), dx = gamma * rstd * (dy - dbeta / m - xhat * dgamma / m)."""
+    f = "float32"
+    n_, c_, h_, w_ = shape
+    stat = [1, c_, 1, 1]
+    m_ = n_ * h_ * w_
+    b = _Builder(f"Fused_BatchNormGrad_{seed}")
+    dy, x = b.input("dy", shape, f), b.input("x", shape, f)
+    mean, rstd, gamma = b.input("mean", stat, f), b.input("rstd", stat, f), b.input("gamma", stat, f)
+    xhat = b.emit("Mul", [b.emit("Sub", [x, mean], shape, f), rstd], shape, f)
+    dbeta = b.emit("ReduceSum", [dy], stat, f, _reduce_attr([0, 2, 3], True))
+    dgamma = b.emit("ReduceSum", [b.emit("Mul", [dy, xhat], shape, f)], stat, f, _reduce_attr([0, 2, 3], True))
+    inv = b.const(1.0 / m_, f)
+    t = b.emit("Sub", [dy, b.emit("Mul", [dbeta, inv], stat, f)], shape, f)
+    t = b.emit("Sub", [t, b.emit("Mul", [xhat, b.emit("Mul", [dgamma, inv], stat, f)], shape, f)], shape, f)
+    b.output(b.emit("Mul", [t, b.emit("Mul", [gamma, rstd], stat, f)], shape, f))
+    b.output(dgamma)
+    b.output(dbeta)
+    return b.build()

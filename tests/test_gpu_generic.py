@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 from akg_b200 import FusedKernel, descs
-from akg_b200.descs import _Builder, _attr, _reduce_attr
+from akg_b200.descs import _Builder, _attr, _reduce_attr, batch_norm_training as _batch_norm_training, batch_norm_backward as _batch_norm_backward
 from oracle import akg_oracle as O
 from helpers import BF16, bits_equal, make_inputs
 
@@ -889,26 +889,6 @@ def test_per_channel_operands_in_front_of_a_batchnorm_style_reduction(lib):
         assert "(r / 1LL) % 24LL" in kern.jit_source()
 
 
-def _batch_norm_training(shape, io="float32", seed=0):
-    """Mean over (N, H, W), variance of the centred values, scale and shift; the centred values are used twice."""
-    f = "float32"
-    n_, c_, h_, w_ = shape
-    stat = [1, c_, 1, 1]
-    b = _Builder(f"Fused_BatchNormTraining_{seed}")
-    x0, gamma, beta = b.input("x", shape, io), b.input("gamma", stat, f), b.input("beta", stat, f)
-    x = x0 if io == f else b.emit("Cast", [x0], shape, f, [_attr("dst_type", "str", f)])
-    inv = b.const(1.0 / (n_ * h_ * w_), f)
-    mean = b.emit("Mul", [b.emit("ReduceSum", [x], stat, f, _reduce_attr([0, 2, 3], True)), inv], stat, f)
-    d_ = b.emit("Sub", [x, mean], shape, f)
-    var = b.emit("Mul", [b.emit("ReduceSum", [b.emit("Mul", [d_, d_], shape, f)], stat, f, _reduce_attr([0, 2, 3], True)), inv], stat, f)
-    rstd = b.emit("Rsqrt", [b.emit("Add", [var, b.const(1e-5, f)], stat, f)], stat, f)
-    y = b.emit("Add", [b.emit("Mul", [b.emit("Mul", [d_, rstd], shape, f), gamma], shape, f), beta], shape, f)
-    b.output(y if io == f else b.emit("Cast", [y], shape, io, [_attr("dst_type", "str", io)]))
-    b.output(mean)
-    b.output(rstd)
-    return b.build()
-
-
 @pytest.mark.parametrize("io", ["float32", "float16"])
 def test_batch_norm_training_region_is_cut_at_its_reductions(lib, io):
     """Three pieces (mean; centred squares folded into the variance pass; scale and shift with the centred values
@@ -927,27 +907,6 @@ def test_batch_norm_training_region_is_cut_at_its_reductions(lib, io):
     if FLAGS[0] == 0:
         meta = kern.meta()
         assert "akgb_row_jit" in meta["steps"] and meta["workspace"] < 4 * shape[0] * shape[1] * 64
-
-
-def _batch_norm_backward(shape, seed=0):
-    """dbeta = sum dy, dgamma = sum dy * xhat over (N, H, W), dx = gamma * rstd * (dy - dbeta / m - xhat * dgamma / m)."""
-    f = "float32"
-    n_, c_, h_, w_ = shape
-    stat = [1, c_, 1, 1]
-    m_ = n_ * h_ * w_
-    b = _Builder(f"Fused_BatchNormGrad_{seed}")
-    dy, x = b.input("dy", shape, f), b.input("x", shape, f)
-    mean, rstd, gamma = b.input("mean", stat, f), b.input("rstd", stat, f), b.input("gamma", stat, f)
-    xhat = b.emit("Mul", [b.emit("Sub", [x, mean], shape, f), rstd], shape, f)
-    dbeta = b.emit("ReduceSum", [dy], stat, f, _reduce_attr([0, 2, 3], True))
-    dgamma = b.emit("ReduceSum", [b.emit("Mul", [dy, xhat], shape, f)], stat, f, _reduce_attr([0, 2, 3], True))
-    inv = b.const(1.0 / m_, f)
-    t = b.emit("Sub", [dy, b.emit("Mul", [dbeta, inv], stat, f)], shape, f)
-    t = b.emit("Sub", [t, b.emit("Mul", [xhat, b.emit("Mul", [dgamma, inv], stat, f)], shape, f)], shape, f)
-    b.output(b.emit("Mul", [t, b.emit("Mul", [gamma, rstd], stat, f)], shape, f))
-    b.output(dgamma)
-    b.output(dbeta)
-    return b.build()
 
 
 def test_batch_norm_backward_folds_both_sums_in_one_pass(lib):
