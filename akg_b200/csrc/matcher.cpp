@@ -952,8 +952,21 @@ bool view_trailing_run(const Graph& g, Graph* gv, std::map<int, std::pair<int64_
       return r;
     };
     // the same elements under another split of the row axes ([n, c, h, w] against [1, n * c, h, w])
-    const bool regrouped = n == R * C && shp.size() >= trail.size() &&
-                           std::equal(trail.begin(), trail.end(), shp.end() - (std::ptrdiff_t)trail.size());
+    bool regrouped = n == R * C && shp.size() >= trail.size() &&
+                     std::equal(trail.begin(), trail.end(), shp.end() - (std::ptrdiff_t)trail.size());
+    if (!regrouped && n == R * C && v.shape != S) {
+      // any other shape of the same elements (the [n, c, h, w] tensor in front of GroupNorm's [n, groups, rest] view):
+      // fine as long as only re-views and elementwise ops between equally shaped tensors touch it
+      auto plain = [&](const Node& nd) {
+        if (nd.kind == OpK::Reshape) return true;
+        if (!opk_is_elementwise(nd.kind) || nd.kind == OpK::AddN || g.v(nd.out).shape != v.shape) return false;
+        for (int o : nd.in)
+          if (!g.v(o).is_const && g.v(o).numel() != 1 && g.v(o).shape != v.shape) return false;
+        return true;
+      };
+      regrouped = v.producer < 0 || plain(g.nodes[v.producer]);
+      for (int u : v.users) regrouped = regrouped && plain(g.nodes[u]);
+    }
     if (shp == S || regrouped) {
       v.shape = {R, C};
     } else if (n == 1) {

@@ -397,6 +397,18 @@ def _rms_norm(x, normalized_shape, weight=None, eps=None):
     return y.to(x.dtype)
 
 
+def _fused_rms_norm(x, normalized_shape, weight=None, eps=None):
+    """The (result, reciprocal rms) pair rms_norm traces to on device tensors."""
+    dims = list(range(x.dim() - len(normalized_shape), x.dim()))
+    xf = x.float() if x.dtype in (torch.float16, torch.bfloat16) else x
+    eps = torch.finfo(x.dtype).eps if eps is None else eps
+    rstd = torch.rsqrt((xf * xf).mean(dims, keepdim=True) + eps)
+    y = xf * rstd
+    if weight is not None:
+        y = y * weight
+    return y.to(x.dtype), rstd
+
+
 def _native_group_norm(x, weight, bias, n, c, hxw, group, eps):
     """Statistics per (sample, group) on the [n, group, rest] view, then the per-channel scale and shift."""
     xf = x.float() if x.dtype in (torch.float16, torch.bfloat16) else x
@@ -404,12 +416,14 @@ def _native_group_norm(x, weight, bias, n, c, hxw, group, eps):
     mean = g.mean(-1, keepdim=True)
     d = g - mean
     rstd = torch.rsqrt((d * d).mean(-1, keepdim=True) + eps)
-    y = (d * rstd).reshape(n, c, hxw)
+    # scale and shift on x's own shape: what follows the normalisation (an activation) is then one elementwise group
+    per_channel = [1, c] + [1] * (x.dim() - 2)
+    y = (d * rstd).reshape(x.shape)
     if weight is not None:
-        y = y * weight.reshape(1, c, 1)
+        y = y * weight.reshape(per_channel)
     if bias is not None:
-        y = y + bias.reshape(1, c, 1)
-    return y.reshape(x.shape).to(x.dtype), mean.reshape(n, group).to(x.dtype), rstd.reshape(n, group).to(x.dtype)
+        y = y + bias.reshape(per_channel)
+    return y.to(x.dtype), mean.reshape(n, group).to(x.dtype), rstd.reshape(n, group).to(x.dtype)
 
 
 def _decompositions():
@@ -419,6 +433,8 @@ def _decompositions():
     table[aten.var_mean.correction] = _var_mean_correction
     if hasattr(aten, "rms_norm"):
         table[aten.rms_norm.default] = _rms_norm
+    if hasattr(aten, "_fused_rms_norm"):
+        table[aten._fused_rms_norm.default] = _fused_rms_norm
     table[aten.var.correction] = _var_correction
     table[aten.std.correction] = _std_correction
     table[aten.logsumexp.default] = _logsumexp

@@ -311,3 +311,14 @@ def test_batch_norm_as_traced_on_device_tensors():
     kept = [n.target for n in fused.gm.graph.nodes if n.op == "call_function" and n.target is torch.ops.aten.cudnn_batch_norm.default]
     assert not kept
     _close(fused(x, w, b), torch.nn.functional.batch_norm(x, None, None, w, b, training=True), 1e-5)
+
+
+@pytest.mark.skipif(not hasattr(torch.ops.aten, "_fused_rms_norm"), reason="this torch has no fused rms norm op")
+def test_rms_norm_as_traced_on_device_tensors():
+    g = torch.Generator().manual_seed(0)
+    x, w = torch.randn(8, 64, generator=g), torch.rand(64, generator=g) + 0.5
+    fn = lambda x, w: torch.ops.aten._fused_rms_norm(x, [64], w, 1e-6)[0] * 2
+    fused = TF.fuse_and_optimize(fn, [x, w], executor=oracle_executor)
+    assert len(fused.subgraphs) == 1
+    assert not [n for n in fused.gm.graph.nodes if n.op == "call_function" and n.target is torch.ops.aten._fused_rms_norm.default]
+    _close(fused(x, w), torch.nn.functional.rms_norm(x, (64,), w, 1e-6) * 2, 1e-5)
