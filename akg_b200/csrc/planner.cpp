@@ -1002,7 +1002,7 @@ struct Builder {
       for (size_t i = 0; i < g.nodes.size(); ++i) {
         const Node& n = g.nodes[i];
         bool early = opk_is_elementwise(n.kind) && n.kind != OpK::AddN && g.v(n.out).numel() * 4 <= largest;
-        for (int vid : n.in) early = early && (g.v(vid).is_const || g.v(vid).input_index >= 0);
+        for (int vid : n.in) early = early && (g.v(vid).is_const || g.v(root(vid)).input_index >= 0);  // also through views
         (early ? order : later).push_back(i);
       }
       order.insert(order.end(), later.begin(), later.end());
