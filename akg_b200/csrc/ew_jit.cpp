@@ -513,7 +513,8 @@ int max_live_full(const RowProgram& P) {
 bool row_shape(const RowProgram& P, bool vec, RowShape* rs) {
   rs->vw = vec ? 8 : 1;
   const int64_t granules = (P.cols + rs->vw - 1) / rs->vw;
-  const int live = max_live_full(P);
+  int live = max_live_full(P);
+  for (auto& o : P.out) live += o.kind == RK_COL && !P.col_reduce;  // column sums are kept in registers too
   // about 96 registers per thread for the per-element values that are live at once (measured: 160 costs occupancy
   // on 16-bit rows, 32 makes the thread groups too wide)
   int nv_max = std::max(1, 96 / (rs->vw * live));
@@ -535,6 +536,7 @@ bool row_shape(const RowProgram& P, bool vec, RowShape* rs) {
 // recomputing the per-element values each pass needs from the inputs (the later passes find the row in L2).  The same
 // row program, the same per-op rounding; only the schedule differs from row_generate.
 bool row_generate_multipass(const RowProgram& P, bool vec, std::string* out, RowShape* shape) {
+  if (P.col_sums) return false;
   RowShape rs;
   rs.vw = vec ? 8 : 1;
   rs.t = 512;
@@ -729,7 +731,19 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
   s << "i64 rows) {\n";
   s << "  __shared__ float sm[TPB / 32];\n";
   s << "  const int tr = threadIdx.x % T;\n";
-  s << "  const i64 row0 = (i64)blockIdx.x * RPB + threadIdx.x / T;\n";
+  if (P.col_sums) {
+    // a fixed number of CTAs walk the row blocks; every thread keeps the sums of its own columns
+    s << "  __shared__ float smc[TPB][VW];\n";
+    for (size_t i = 0; i < P.out.size(); ++i)
+      if (P.out[i].kind == RK_COL)
+        s << "  float cs" << i << "[NV][VW];\n#pragma unroll\n  for (int k = 0; k < NV; ++k) {\n#pragma unroll\n"
+             "    for (int j = 0; j < VW; ++j) cs" << i << "[k][j] = 0.f;\n  }\n";
+    s << "  const i64 nblk = (rows + RPB - 1) / RPB;\n";
+    s << "  for (i64 rb = blockIdx.x; rb < nblk; rb += gridDim.x) {\n";
+    s << "  const i64 row0 = rb * RPB + threadIdx.x / T;\n";
+  } else {
+    s << "  const i64 row0 = (i64)blockIdx.x * RPB + threadIdx.x / T;\n";
+  }
   s << "  const bool active = row0 < rows;\n";
   s << "  const i64 r = active ? row0 : rows - 1;\n";
   std::vector<std::string> name(P.n_val);
@@ -804,10 +818,27 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
       s << "  if (active && tr == 0) st1_" << tag << "(out" << i << ", r, " << ref_full(o.val, fl) << ");\n";
       continue;
     }
+    if (o.kind == RK_COL) {
+      s << "  if (active) {\n#pragma unroll\n    for (int k = 0; k < NV; ++k) {\n#pragma unroll\n      for (int j = 0; j < VW; ++j) cs"
+        << i << "[k][j] = __fadd_rn(cs" << i << "[k][j], " << name[o.val] << "[k][j]);\n    }\n  }\n";
+      continue;
+    }
     s << "  if (active) {\n#pragma unroll\n    for (int k = 0; k < NV; ++k) {\n      const int c = (tr + T * k) * VW;\n";
     if (vec) s << "      if (c < C) st8_" << tag << "(out" << i << ", r * C + c, " << name[o.val] << "[k]);\n";
     else s << "      if (c < C) st1_" << tag << "(out" << i << ", r * C + c, " << name[o.val] << "[k][0]);\n";
     s << "    }\n  }\n";
+  }
+  if (P.col_sums) {
+    s << "  }\n";  // the walk over the row blocks
+    // the row groups of the CTA hold sums of the same columns: folded in group order, one partial vector per CTA
+    for (size_t i = 0; i < P.out.size(); ++i) {
+      if (P.out[i].kind != RK_COL) continue;
+      s << "#pragma unroll\n  for (int k = 0; k < NV; ++k) {\n    __syncthreads();\n#pragma unroll\n"
+           "    for (int j = 0; j < VW; ++j) smc[threadIdx.x][j] = cs" << i << "[k][j];\n    __syncthreads();\n"
+           "    if (threadIdx.x < T) {\n      const int c = (tr + T * k) * VW;\n#pragma unroll\n      for (int j = 0; j < VW; ++j) {\n"
+           "        float a = smc[tr][j];\n        for (int g2 = 1; g2 < RPB; ++g2) a = __fadd_rn(a, smc[g2 * T + tr][j]);\n"
+           "        if (c + j < C) ((float*)out" << i << ")[(i64)blockIdx.x * C + c + j] = a;\n      }\n    }\n  }\n";
+    }
   }
   s << "}\n";
   *out = s.str();
@@ -1105,6 +1136,15 @@ cudaError_t col_jit_launch(const RowProgram& P, const void* const* in, float* co
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorLaunchFailure;
 }
 
+bool row_jit_fits_registers(const RowProgram& P) {
+  RowShape rs;
+  return row_shape(P, true, &rs) && row_shape(P, false, &rs);
+}
+
+// The same for both access widths, so that the planner can size the partial vectors: at most four CTAs per SM of a
+// 148-SM part, never more than there are rows (a CTA without rows writes zeros).
+int64_t row_jit_col_sum_ctas(const RowProgram& P) { return std::min<int64_t>(592, std::max<int64_t>(1, P.rows)); }
+
 std::string row_jit_source(const RowProgram& P, bool vec) {
   std::string src;
   if (P.col_reduce) {
@@ -1132,7 +1172,7 @@ cudaError_t row_jit_launch(const RowProgram& P, const void* const* in, void* con
   JitKernel* k = compile(src, "akgb_row_jit");
   if (!k || k->failed) return cudaErrorNotSupported;
   const int rpb = rs.tpb / rs.t;  // 1 for the multi-pass schedule
-  const int64_t grid = (P.rows + rpb - 1) / rpb;
+  const int64_t grid = P.col_sums ? row_jit_col_sum_ctas(P) : (P.rows + rpb - 1) / rpb;
   if (grid > 0x7fffffff) return cudaErrorNotSupported;
   long long rows = P.rows;
   void* args[32];

@@ -104,6 +104,10 @@ struct RowProgram {
   // column mode: the program ends in one or more reductions that fold the ROWS (axis 0 of [rows, cols]); every result
   // is [cols].  Generated as a kernel that walks rows and keeps 8 column accumulators per thread and result.
   bool col_reduce = false;
+  // A row program may also sum some of its per-element values over ALL rows (LayerNorm backward: the weight and bias
+  // gradients next to the row-wise input gradient).  Those results are outputs of kind RK_COL; the kernel is then
+  // launched with a fixed number of CTAs that walk the rows and writes one partial [cols] vector per CTA and result.
+  bool col_sums = false;
 };
 
 }  // namespace akgb

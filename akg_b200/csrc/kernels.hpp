@@ -85,6 +85,8 @@ cudaError_t row_jit_launch(const RowProgram& p, const void* const* in, void* con
                            LaunchDims* dims);
 std::string row_jit_source(const RowProgram& p, bool vec);
 int64_t col_jit_splits(const RowProgram& p, int sm_count);
+bool row_jit_fits_registers(const RowProgram& p);  // the register schedule applies (in both access widths)
+int64_t row_jit_col_sum_ctas(const RowProgram& p);  // CTAs (= partial vectors per result) of a program with column sums
 cudaError_t col_jit_launch(const RowProgram& p, const void* const* in, float* const* partials, int64_t splits,
                            cudaStream_t s, LaunchDims* dims);
 void ew_jit_prepare(const EwProgram& p);

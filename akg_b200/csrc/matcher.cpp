@@ -1617,7 +1617,7 @@ Plan build_plan(const Graph& g, int sm_count, bool allow_jit) {
     std::map<int, std::pair<int64_t, int64_t>> row_index;
     const bool row_region =
         allow_jit && plan.steps.size() > 1 && g.op_class == OpClass::Reduction &&
-        (build_row_program(g, rp.get(), &in_values, &out_values) ||
+        (build_row_program(g, rp.get(), &in_values, &out_values, false, nullptr, true) ||
          (in_values.clear(), out_values.clear(), *rp = RowProgram(), view_trailing_run(g, &gv, &row_index) &&
           build_row_program(gv, rp.get(), &in_values, &out_values, false, &row_index)));
     if (row_region) {
@@ -1634,12 +1634,39 @@ Plan build_plan(const Graph& g, int sm_count, bool allow_jit) {
         r.arg = g.v(vid).input_index;
         st.ew_in.push_back(r);
       }
-      for (int vid : out_values) {
+      // sums over all rows: the kernel writes one partial vector per CTA, a column reduction folds them
+      std::vector<Step> finishes;
+      size_t fws = 0;
+      const int64_t parts = rp->col_sums ? row_jit_col_sum_ctas(*rp) : 0;
+      for (size_t i = 0; i < out_values.size(); ++i) {
         Ref r;
-        r.arg = (int)g.inputs.size() + g.v(vid).output_index;
-        st.ew_out.push_back(r);
+        r.arg = (int)g.inputs.size() + g.v(out_values[i]).output_index;
+        if (rp->out[i].kind != RK_COL) {
+          st.ew_out.push_back(r);
+          continue;
+        }
+        Ref partial;
+        partial.ws_off = (int64_t)fws;
+        fws += ((size_t)(parts * rp->cols) * sizeof(float) + 255) / 256 * 256;
+        st.ew_out.push_back(partial);
+        Step fin;
+        fin.kind = StepK::ReduceCol;
+        fin.kernel_name = "reduce_col_f32";
+        fin.red_op = RedOp::Sum;
+        fin.red_outer = 1;
+        fin.red_len = parts;
+        fin.red_inner = rp->cols;
+        fin.a = partial;
+        fin.out = r;
+        finishes.push_back(std::move(fin));
       }
       fused.steps.push_back(std::move(st));
+      for (Step& fin : finishes) {
+        fin.scratch.ws_off = (int64_t)fws;
+        fws += (reduce_col_workspace(parts, rp->cols, sm_count) + 255) / 256 * 256;
+        fused.steps.push_back(std::move(fin));
+      }
+      fused.workspace_bytes = fws;
       fused.fallback = std::make_shared<Plan>(std::move(plan));
       plan = std::move(fused);
     } else if (Plan fused; allow_jit && plan.steps.size() >= 2 &&

@@ -61,7 +61,8 @@ struct Plan {
 Plan build_plan(const Graph& g, int sm_count, bool allow_jit = true);
 // Reduce-X regions as one row program (rowfuse.cpp); `in_values` / `out_values` receive the graph values of the operands.
 bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_values, std::vector<int>* out_values,
-                       bool col_mode = false, const std::map<int, std::pair<int64_t, int64_t>>* row_index = nullptr);
+                       bool col_mode = false, const std::map<int, std::pair<int64_t, int64_t>>* row_index = nullptr,
+                       bool allow_col_sums = false);
 // Fallback of build_plan: splits the region into elementwise groups (generic kernel), reductions, transposes and
 // matmuls that run one after the other with intermediates in the workspace.
 Plan build_generic_plan(const Graph& g, int sm_count);

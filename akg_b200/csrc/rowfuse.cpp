@@ -32,7 +32,7 @@ std::vector<int64_t> strip_leading_ones(std::vector<int64_t> s) {
 }  // namespace
 
 bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_values, std::vector<int>* out_values,
-                       bool col_mode, const std::map<int, std::pair<int64_t, int64_t>>* row_index) {
+                       bool col_mode, const std::map<int, std::pair<int64_t, int64_t>>* row_index, bool allow_col_sums) {
   if (g.dynamic || g.nodes.empty()) return false;
   // the row shape comes from the first reduction
   const Node* first_red = nullptr;
@@ -67,6 +67,7 @@ bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_val
   P.rows = R;
   P.cols = C;
   std::map<int, int> val_of;  // graph value -> program value
+  std::map<int, int> col_sum_of;  // region result -> the per-element value it sums over all rows
   auto new_val = [&](bool full) {
     P.val_full.push_back(full ? 1 : 0);
     return P.n_val++;
@@ -162,6 +163,17 @@ bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_val
       P.out.push_back(o);
       out_values->push_back(n.out);
       continue;
+    } else if (allow_col_sums && n.kind == OpK::ReduceSum && S.size() >= 2 && n.axes.size() + 1 == S.size() &&
+               n.axes.front() == 0 && n.axes.back() == (int64_t)S.size() - 2 && g.v(n.in[0]).numel() == R * C &&
+               g.v(n.in[0]).shape.back() == C) {
+      // a sum over all rows of a per-element value: a result of its own, written per CTA and folded afterwards
+      const Value& x = g.v(n.in[0]);
+      int src = 0;
+      if (x.dt != DT::F32 || ov.dt != DT::F32 || ov.numel() != C || ov.output_index < 0 || !ov.users.empty()) return false;
+      if (!operand(n.in[0], &src) || !P.val_full[src] || col_sum_of.size() >= 4) return false;
+      col_sum_of[n.out] = src;
+      P.col_sums = true;
+      continue;
     } else if (opk_is_reduce(n.kind)) {
       const Value& x = g.v(n.in[0]);
       if (n.axes.size() != 1 || n.axes[0] != (int64_t)x.shape.size() - 1 || x.shape.back() != C || x.numel() != R * C)
@@ -226,8 +238,18 @@ bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_val
   }
   for (int vid : g.outputs) {
     if (col_mode) break;
-    auto it = val_of.find(vid);
     const Value& v = g.v(vid);
+    if (col_sum_of.count(vid)) {
+      RowOperand o;
+      o.dt = (int)DT::F32;
+      o.kind = RK_COL;
+      o.val = col_sum_of[vid];
+      o.red_op = 0;
+      P.out.push_back(o);
+      out_values->push_back(vid);
+      continue;
+    }
+    auto it = val_of.find(vid);
     if (it == val_of.end() || v.producer < 0) return false;  // an input or constant passed through
     RowOperand o;
     o.dt = (int)v.dt;
@@ -246,6 +268,13 @@ bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_val
   bool any_full_in = false;
   for (auto& o : P.in) any_full_in |= o.kind == RK_FULL;
   if (!any_full_in) return false;
+  if (P.col_sums) {
+    // only next to row-wise work (sums over rows alone are the column kernels' job), and only in registers (the
+    // multi-pass schedule has no column sums)
+    bool any_row_reduction = false;
+    for (auto& x : P.instr) any_row_reduction |= x.reduce;
+    if (!any_row_reduction || !row_jit_fits_registers(P)) return false;
+  }
   *out = std::move(P);
   return true;
 }

@@ -300,3 +300,25 @@ def batch_norm_backward(shape: Sequence[int], seed: int = 0) -> dict:
     b.output(dgamma)
     b.output(dbeta)
     return b.build()
+
+
+def layer_norm_backward(rows: int, cols: int, eps: float = 1e-5) -> dict:
+    """Statistics recomputed from x, then dx (row-wise) with dgamma = sum over rows of dy * xhat and dbeta = sum of dy."""
+    f = "float32"
+    full, red = [rows, cols], [rows, 1]
+    b = _Builder(f"Fused_LayerNormGrad_{rows}x{cols}")
+    dy, x, gamma = b.input("dy", full, f), b.input("x", full, f), b.input("gamma", [cols], f)
+    inv = b.const(1.0 / cols, f)
+    mean = b.emit("Mul", [b.emit("ReduceSum", [x], red, f, _reduce_attr([1], True)), inv], red, f)
+    d = b.emit("Sub", [x, mean], full, f)
+    var = b.emit("Mul", [b.emit("ReduceSum", [b.emit("Mul", [d, d], full, f)], red, f, _reduce_attr([1], True)), inv], red, f)
+    rstd = b.emit("Rsqrt", [b.emit("Add", [var, b.const(eps, f)], red, f)], red, f)
+    xhat = b.emit("Mul", [d, rstd], full, f)
+    g_ = b.emit("Mul", [dy, gamma], full, f)
+    m1 = b.emit("Mul", [b.emit("ReduceSum", [g_], red, f, _reduce_attr([1], True)), inv], red, f)
+    m2 = b.emit("Mul", [b.emit("ReduceSum", [b.emit("Mul", [g_, xhat], full, f)], red, f, _reduce_attr([1], True)), inv], red, f)
+    t = b.emit("Sub", [b.emit("Sub", [g_, m1], full, f), b.emit("Mul", [xhat, m2], full, f)], full, f)
+    b.output(b.emit("Mul", [t, rstd], full, f))
+    b.output(b.emit("ReduceSum", [b.emit("Mul", [dy, xhat], full, f)], [cols], f, _reduce_attr([0], False)))
+    b.output(b.emit("ReduceSum", [dy], [cols], f, _reduce_attr([0], False)))
+    return b.build()

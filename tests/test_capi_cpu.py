@@ -262,6 +262,17 @@ def test_batch_norm_training_is_planned_without_full_size_intermediates(lib):
     assert FusedKernel(_batch_norm_training([64, 256, 56, 56]), flags=1).meta()["workspace"] > (100 << 20)
 
 
+def test_layer_norm_backward_is_one_row_kernel_with_column_sums(lib):
+    from akg_b200 import FusedKernel, descs
+    k = FusedKernel(descs.layer_norm_backward(16384, 4096))
+    assert k.meta()["steps"] == ["akgb_row_jit", "reduce_col_f32", "reduce_col_f32"]
+    src = k.jit_source()
+    assert "rb += gridDim.x" in src and "cs1[k][j] = __fadd_rn" in src
+    # rows too long for registers keep the separate column reductions
+    assert "akgb_row_jit" in FusedKernel(descs.layer_norm_backward(64, 40000)).meta()["steps"]
+    assert "rb += gridDim.x" not in FusedKernel(descs.layer_norm_backward(64, 40000)).jit_source()
+
+
 def test_planning_of_the_wider_op_surface(lib):
     from akg_b200 import FusedKernel, descs
     from akg_b200.descs import _Builder, _attr, _reduce_attr

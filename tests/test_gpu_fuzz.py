@@ -72,6 +72,9 @@ def random_region(seed, long_rows=False):
     extra = [v for v in rowvals if v not in rows_in]
     if extra and rng.random() < 0.5:
         b.output(extra[-1])
+    if rng.random() < 0.3:  # a sum over all rows beside the row-wise work (a weight gradient)
+        src = full[int(rng.integers(len(full)))]
+        b.output(b.emit("ReduceSum", [src], [cols], F, _reduce_attr(list(range(len(shape) - 1)), False)))
     desc = b.build()
     ins = []
     for (t,) in desc["input_desc"]:
@@ -109,7 +112,8 @@ def test_random_long_row_region(seed):
     desc, ins, io_dtype = random_region(seed, long_rows=True)
     k = FusedKernel(desc)
     has_reduce = any(op["name"].startswith("Reduce") for op in desc["op_desc"])
-    if has_reduce and k.meta()["template"] == "akgb_row_jit":
+    sums_rows = any(op["name"] == "ReduceSum" and len(op["output_desc"][0]["shape"]) == 1 for op in desc["op_desc"])
+    if has_reduce and not sums_rows and k.meta()["template"] == "akgb_row_jit":
         assert k.launch_count == 1 and "c += (i64)T * VW" in k.jit_source(desc["input_desc"][0][0]["shape"][-1] % 8 == 0)
     outs = k.empty_outputs()
     k.run_host([a.copy() for a in ins] + outs)

@@ -927,6 +927,27 @@ def test_batch_norm_backward_folds_both_sums_in_one_pass(lib):
         assert "out1" in kern.jit_source()  # one generated kernel with both row results
 
 
+@pytest.mark.parametrize("rows,cols", [(300, 1024), (77, 200), (2048, 4096), (5, 8192)])
+def test_layer_norm_backward_sums_over_rows_inside_the_row_kernel(lib, rows, cols):
+    """dx row by row, and in the same pass the weight and bias gradients as per-CTA column sums that a column
+    reduction folds afterwards."""
+    rng = np.random.default_rng(108)
+    d = descs.layer_norm_backward(rows, cols)
+    ins = [rng.standard_normal((rows, cols)).astype(np.float32), (rng.standard_normal((rows, cols)) * 2 + 0.5).astype(np.float32),
+           rng.uniform(0.5, 1.5, cols).astype(np.float32)]
+    got, kern = run(d, ins)
+    want = O.evaluate(d, ins, accum="float64")
+    np.testing.assert_allclose(got[0], want[0], rtol=1e-4, atol=1e-4)
+    scale = np.sqrt(rows)
+    np.testing.assert_allclose(got[1], want[1], rtol=1e-4, atol=1e-4 * scale)
+    np.testing.assert_allclose(got[2], want[2], rtol=1e-4, atol=1e-4 * scale)
+    if FLAGS[0] == 0:
+        meta = kern.meta()
+        assert meta["steps"] == ["akgb_row_jit", "reduce_col_f32", "reduce_col_f32"]
+        # (with 8192 columns the sums no longer fit the registers beside the row: two separate column reductions)
+        assert ("rb += gridDim.x" in kern.jit_source(cols % 8 == 0)) == (cols <= 4096)
+
+
 def test_instance_norm_on_nchw_is_one_row_kernel(lib):
     """Mean / variance over (H, W) with keep_dims, per-channel scale and shift of shape [1, C, 1, 1]."""
     rng = np.random.default_rng(104)
