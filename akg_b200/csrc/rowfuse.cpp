@@ -10,6 +10,7 @@
 #include <cmath>
 #include <cstring>
 #include <map>
+#include <set>
 
 #include "hostconv.hpp"
 #include "plan.hpp"
@@ -68,6 +69,7 @@ bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_val
   P.cols = C;
   std::map<int, int> val_of;  // graph value -> program value
   std::map<int, int> col_sum_of;  // region result -> the per-element value it sums over all rows
+  std::set<int> view_of_col_sum;  // re-views of such sums: no instruction of their own
   auto new_val = [&](bool full) {
     P.val_full.push_back(full ? 1 : 0);
     return P.n_val++;
@@ -136,6 +138,7 @@ bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_val
 
   for (const Node& n : g.nodes) {
     const Value& ov = g.v(n.out);
+    if (view_of_col_sum.count(n.out)) continue;
     if (!ew_type_ok(ov.dt)) return false;
     RowInstr ins;
     ins.dt = (uint8_t)ov.dt;
@@ -169,9 +172,18 @@ bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_val
       // a sum over all rows of a per-element value: a result of its own, written per CTA and folded afterwards
       const Value& x = g.v(n.in[0]);
       int src = 0;
-      if (x.dt != DT::F32 || ov.dt != DT::F32 || ov.numel() != C || ov.output_index < 0 || !ov.users.empty()) return false;
+      if (x.dt != DT::F32 || ov.dt != DT::F32 || ov.numel() != C) return false;
+      // the result itself, or what a chain of re-views ([1, cols] -> [cols]) makes of it, is a result of the region
+      int result = n.out;
+      for (int hops = 0; hops < 4 && g.v(result).output_index < 0; ++hops) {
+        const Value& rv = g.v(result);
+        if (rv.users.size() != 1 || g.nodes[rv.users[0]].kind != OpK::Reshape) return false;
+        result = g.nodes[rv.users[0]].out;
+        view_of_col_sum.insert(result);
+      }
+      if (g.v(result).output_index < 0 || !g.v(result).users.empty()) return false;
       if (!operand(n.in[0], &src) || !P.val_full[src] || col_sum_of.size() >= 4) return false;
-      col_sum_of[n.out] = src;
+      col_sum_of[result] = src;
       P.col_sums = true;
       continue;
     } else if (opk_is_reduce(n.kind)) {

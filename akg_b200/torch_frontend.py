@@ -257,8 +257,16 @@ def _slice(L, node, x, dim=0, start=None, end=None, step=1):
 
 
 def _pow_scalar(L, node, x, e):
+    """Small whole exponents as products, like torch's own kernels (x * x is also the correctly rounded square)."""
     dt = L.dtype(node)
-    return L.emit("Pow", [L.cast_to(x, dt), L.b.const(float(e), dt)], node)
+    x = L.cast_to(x, dt)
+    if float(e) == 2.0:
+        return L.emit("Mul", [x, x], node)
+    if float(e) == 3.0:
+        return L.emit("Mul", [L.emit("Mul", [x, x], node), x], node)
+    if float(e) == 1.0:
+        return L.emit("Mul", [x, L.b.const(1.0, dt)], node)
+    return L.emit("Pow", [x, L.b.const(float(e), dt)], node)
 
 
 _LOWERINGS: dict = {}

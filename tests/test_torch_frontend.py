@@ -118,6 +118,9 @@ MORE = {
     "layer_norm_backward": (lambda x, w, b, dy: _pull(lambda x, w, b: torch.nn.functional.layer_norm(x, (64,), w, b), (x, w, b), dy),
                             lambda g: [torch.randn(24, 64, generator=g), torch.rand(64, generator=g) + 0.5,
                                        torch.randn(64, generator=g), torch.randn(24, 64, generator=g)]),
+    "rms_norm_backward": (lambda x, w, dy: _pull(lambda x, w: torch.nn.functional.rms_norm(x, (64,), w, 1e-6), (x, w), dy),
+                          lambda g: [torch.randn(24, 64, generator=g), torch.rand(64, generator=g) + 0.5,
+                                     torch.randn(24, 64, generator=g)]),
     "softmax_backward": (lambda x, dy: _pull(lambda x: torch.softmax(x, -1), (x,), dy),
                          lambda g: [torch.randn(24, 64, generator=g), torch.randn(24, 64, generator=g)]),
     "log_softmax_backward": (lambda x, dy: _pull(lambda x: torch.log_softmax(x, -1), (x,), dy),
