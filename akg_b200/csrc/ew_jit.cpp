@@ -1141,9 +1141,14 @@ bool row_jit_fits_registers(const RowProgram& P) {
   return row_shape(P, true, &rs) && row_shape(P, false, &rs);
 }
 
-// The same for both access widths, so that the planner can size the partial vectors: at most four CTAs per SM of a
-// 148-SM part, never more than there are rows (a CTA without rows writes zeros).
-int64_t row_jit_col_sum_ctas(const RowProgram& P) { return std::min<int64_t>(592, std::max<int64_t>(1, P.rows)); }
+// The same for both access widths, so that the planner can size the partial vectors: about 1024 threads per SM of a
+// 148-SM part with the CTA size of the 16-byte variant (measured on LayerNorm backward: 2 CTAs of 512 threads per SM
+// for 4096 columns, 8 of 128 for 1024 columns), never more than there are rows (a CTA without rows writes zeros).
+int64_t row_jit_col_sum_ctas(const RowProgram& P) {
+  RowShape rs;
+  const int tpb = row_shape(P, true, &rs) ? rs.tpb : 512;
+  return std::min<int64_t>(148 * std::max(1, 1024 / tpb), std::max<int64_t>(1, P.rows));
+}
 
 std::string row_jit_source(const RowProgram& P, bool vec) {
   std::string src;
