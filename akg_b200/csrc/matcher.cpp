@@ -1588,6 +1588,52 @@ bool assemble_pieces(const Graph& g, std::vector<Piece>& pieces, int sm_count, P
   return true;
 }
 
+// Ops behind a sum over all rows (the cast of a weight gradient to the parameter type) are split off: the region in
+// front of them is planned on its own, so that its sums can stay inside a row kernel, and the few small ops run after
+// the partial sums have been folded.
+bool tail_split_plan(const Graph& g0, int sm_count, Plan* out) {
+  const int n = (int)g0.nodes.size();
+  if (g0.dynamic || n < 3 || n > 200) return false;
+  int64_t large = 0;
+  for (auto& nd : g0.nodes) {
+    if (nd.kind == OpK::Assign) return false;
+    large = std::max(large, g0.v(nd.out).numel());
+  }
+  std::vector<char> tail(n, 0), view_of_sum(n, 0);
+  bool any = false;
+  for (int i = 0; i < n; ++i) {
+    const Node& nd = g0.nodes[i];
+    for (int vid : nd.in) {
+      const int p = g0.v(vid).producer;
+      if (p < 0) continue;
+      const Node& pn = g0.nodes[p];
+      const bool sum_over_rows = pn.kind == OpK::ReduceSum && !pn.axes.empty() && pn.axes.front() == 0 &&
+                                 g0.v(pn.in[0]).shape.size() >= 2 && pn.axes.size() + 1 == g0.v(pn.in[0]).shape.size() &&
+                                 pn.axes.back() == (int64_t)g0.v(pn.in[0]).shape.size() - 2;
+      const bool of_sum = sum_over_rows || view_of_sum[p];
+      if (of_sum && nd.kind == OpK::Reshape) view_of_sum[i] = 1;  // still the sum itself
+      else if (tail[p] || of_sum) tail[i] = 1;
+    }
+    if (tail[i]) {
+      if (g0.v(nd.out).numel() >= large) return false;  // the tail works on column vectors only
+      any = true;
+    }
+  }
+  if (!any) return false;
+  Graph g = g0;
+  std::vector<Node> order;
+  for (int i = 0; i < n; ++i)
+    if (!tail[i]) order.push_back(g0.nodes[i]);
+  const int n_main = (int)order.size();
+  for (int i = 0; i < n; ++i)
+    if (tail[i]) order.push_back(g0.nodes[i]);
+  if (n_main < 2 || n_main == n) return false;
+  g.nodes = std::move(order);
+  relink(g);
+  std::vector<Piece> pieces = {Piece{0, n_main, false, nullptr, {}, {}}, Piece{n_main, n, false, nullptr, {}, {}}};
+  return assemble_pieces(g, pieces, sm_count, out);
+}
+
 Plan build_plan(const Graph& g, int sm_count, bool allow_jit) {
   for (auto& n : g.nodes)
     if (n.kind == OpK::Unknown)
@@ -1675,27 +1721,34 @@ Plan build_plan(const Graph& g, int sm_count, bool allow_jit) {
       fused.flops = plan.flops;
       fused.fallback = std::make_shared<Plan>(std::move(plan));
       plan = std::move(fused);
-    } else if (Plan cut; allow_jit && plan.steps.size() > 2 && segmented_plan(g, sm_count, &cut) &&
-               cut.steps.size() < plan.steps.size()) {
-      cut.flops = plan.flops;
-      cut.fallback = std::make_shared<Plan>(std::move(plan));
-      plan = std::move(cut);
-    } else if (allow_jit && plan.steps.size() > 2 && g.op_class == OpClass::Reduction) {
-      // cut at the reductions, in the given op order or stage by stage: the variant with the smaller workspace (fewer
-      // full-size values crossing launches), then the one with fewer launches
-      Plan c1, c2;
-      const bool ok1 = reduction_cut_plan(g, sm_count, false, &c1), ok2 = reduction_cut_plan(g, sm_count, true, &c2);
-      auto better = [](const Plan& x, const Plan& y) {
-        const size_t wx = x.workspace_bytes >> 20, wy = y.workspace_bytes >> 20;
-        return wx != wy ? wx < wy : x.steps.size() < y.steps.size();
-      };
-      Plan* cut2 = ok1 && ok2 ? (better(c2, c1) ? &c2 : &c1) : ok1 ? &c1 : ok2 ? &c2 : nullptr;
-      // taken with fewer launches, or far less workspace (no full-size intermediate is written)
-      if (cut2 && (cut2->steps.size() < plan.steps.size() ||
-                   (cut2->steps.size() <= plan.steps.size() + 2 && cut2->workspace_bytes * 2 < plan.workspace_bytes))) {
-        cut2->flops = plan.flops;
-        cut2->fallback = std::make_shared<Plan>(std::move(plan));
-        plan = std::move(*cut2);
+    } else if (allow_jit && plan.steps.size() > 2) {
+      // Other ways to run the region in fewer passes over its tensors: cut into row-kernel pieces and other ops; cut at
+      // the reductions, in the given op order or stage by stage; the small ops behind sums over all rows split off.
+      // The candidate with the smallest workspace (fewest full-size values crossing launches) wins, then the one with
+      // the fewest launches.
+      std::vector<Plan> cands;
+      Plan c;
+      if (segmented_plan(g, sm_count, &c)) cands.push_back(std::move(c));
+      if (g.op_class == OpClass::Reduction) {
+        if (c = Plan(); reduction_cut_plan(g, sm_count, false, &c)) cands.push_back(std::move(c));
+        if (c = Plan(); reduction_cut_plan(g, sm_count, true, &c)) cands.push_back(std::move(c));
+        if (c = Plan(); tail_split_plan(g, sm_count, &c)) cands.push_back(std::move(c));
+      }
+      Plan* best = nullptr;
+      for (Plan& x : cands) {
+        // taken with fewer launches, or far less workspace (no full-size intermediate is written)
+        if (!(x.steps.size() < plan.steps.size() ||
+              (x.steps.size() <= plan.steps.size() + 2 && x.workspace_bytes * 2 < plan.workspace_bytes)))
+          continue;
+        // (workspace counted in eighths of the region's own tensors: partial sums and per-channel values do not matter)
+        const size_t quantum = std::max<size_t>((size_t)8 << 20, (size_t)io_bytes(g) / 8);
+        const size_t wx = x.workspace_bytes / quantum, wb = best ? best->workspace_bytes / quantum : 0;
+        if (!best || (wx != wb ? wx < wb : x.steps.size() < best->steps.size())) best = &x;
+      }
+      if (best) {
+        best->flops = plan.flops;
+        best->fallback = std::make_shared<Plan>(std::move(plan));
+        plan = std::move(*best);
       }
     }
   }

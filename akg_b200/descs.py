@@ -302,8 +302,9 @@ def batch_norm_backward(shape: Sequence[int], seed: int = 0) -> dict:
     return b.build()
 
 
-def layer_norm_backward(rows: int, cols: int, eps: float = 1e-5) -> dict:
-    """Statistics recomputed from x, then dx (row-wise) with dgamma = sum over rows of dy * xhat and dbeta = sum of dy."""
+def layer_norm_backward(rows: int, cols: int, eps: float = 1e-5, grads_dtype: str = "float32") -> dict:
+    """Statistics recomputed from x, then dx (row-wise) with dgamma = sum over rows of dy * xhat and dbeta = sum of dy
+    (cast to `grads_dtype`, the parameters' type, when that is not float32)."""
     f = "float32"
     full, red = [rows, cols], [rows, 1]
     b = _Builder(f"Fused_LayerNormGrad_{rows}x{cols}")
@@ -319,6 +320,8 @@ def layer_norm_backward(rows: int, cols: int, eps: float = 1e-5) -> dict:
     m2 = b.emit("Mul", [b.emit("ReduceSum", [b.emit("Mul", [g_, xhat], full, f)], red, f, _reduce_attr([1], True)), inv], red, f)
     t = b.emit("Sub", [b.emit("Sub", [g_, m1], full, f), b.emit("Mul", [xhat, m2], full, f)], full, f)
     b.output(b.emit("Mul", [t, rstd], full, f))
-    b.output(b.emit("ReduceSum", [b.emit("Mul", [dy, xhat], full, f)], [cols], f, _reduce_attr([0], False)))
-    b.output(b.emit("ReduceSum", [dy], [cols], f, _reduce_attr([0], False)))
+    dgamma = b.emit("ReduceSum", [b.emit("Mul", [dy, xhat], full, f)], [cols], f, _reduce_attr([0], False))
+    dbeta = b.emit("ReduceSum", [dy], [cols], f, _reduce_attr([0], False))
+    for grad in (dgamma, dbeta):
+        b.output(grad if grads_dtype == f else b.emit("Cast", [grad], [cols], grads_dtype, [_attr("dst_type", "str", grads_dtype)]))
     return b.build()

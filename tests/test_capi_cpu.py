@@ -268,6 +268,9 @@ def test_layer_norm_backward_is_one_row_kernel_with_column_sums(lib):
     assert k.meta()["steps"] == ["akgb_row_jit", "reduce_col_f32", "reduce_col_f32"]
     src = k.jit_source()
     assert "rb += gridDim.x" in src and "cs1[k][j] = __fadd_rn" in src
+    # ops behind the sums (a cast to the parameters' type) are split off and run after the partial sums are folded
+    kb = FusedKernel(descs.layer_norm_backward(16384, 4096, grads_dtype="bfloat16"))
+    assert kb.meta()["steps"] == ["akgb_row_jit", "reduce_col_f32", "reduce_col_f32", "ew_generic"]
     # rows too long for registers keep the separate column reductions
     assert "akgb_row_jit" in FusedKernel(descs.layer_norm_backward(64, 40000)).meta()["steps"]
     assert "rb += gridDim.x" not in FusedKernel(descs.layer_norm_backward(64, 40000)).jit_source()

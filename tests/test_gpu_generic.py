@@ -948,6 +948,22 @@ def test_layer_norm_backward_sums_over_rows_inside_the_row_kernel(lib, rows, col
         assert ("rb += gridDim.x" in kern.jit_source(cols % 8 == 0)) == (cols <= 4096)
 
 
+def test_ops_behind_sums_over_rows_run_after_the_fold(lib):
+    rng = np.random.default_rng(109)
+    rows, cols = 600, 512
+    d = descs.layer_norm_backward(rows, cols, grads_dtype="float16")
+    ins = [rng.standard_normal((rows, cols)).astype(np.float32), (rng.standard_normal((rows, cols)) + 0.5).astype(np.float32),
+           rng.uniform(0.5, 1.5, cols).astype(np.float32)]
+    got, kern = run(d, ins)
+    want = O.evaluate(d, ins, accum="float64")
+    np.testing.assert_allclose(got[0], want[0], rtol=1e-4, atol=1e-4)
+    for i in (1, 2):
+        assert got[i].dtype == np.float16
+        np.testing.assert_allclose(got[i].astype(np.float32), want[i].astype(np.float32), rtol=2e-3, atol=5e-2)
+    if FLAGS[0] == 0:
+        assert kern.meta()["steps"] == ["akgb_row_jit", "reduce_col_f32", "reduce_col_f32", "ew_generic"]
+
+
 def test_instance_norm_on_nchw_is_one_row_kernel(lib):
     """Mean / variance over (H, W) with keep_dims, per-channel scale and shift of shape [1, C, 1, 1]."""
     rng = np.random.default_rng(104)
