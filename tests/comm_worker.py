@@ -34,6 +34,22 @@ def main():
         want = ref(x)
         got = out.cpu().double().reshape(want.shape)
         ok = ok and bool(torch.allclose(got, want.double(), rtol=1e-5, atol=1e-5 * float(x.abs().sum(0).max())))
+    # data-parallel LayerNorm backward: dx stays with the rank's rows, the weight and bias gradients are partial sums
+    rows_ln, cols_ln = 256 * world, 512
+    dy_all, x_all = torch.randn(rows_ln, cols_ln, generator=g), torch.randn(rows_ln, cols_ln, generator=g) * 2 + 0.5
+    gamma = torch.rand(cols_ln, generator=g) + 0.5
+    k = FusedKernel(descs.layer_norm_backward(rows_ln, cols_ln), device=local, shard_rank=rank, shard_world=world)
+    lo, hi = rank * (rows_ln // world), (rank + 1) * (rows_ln // world)
+    outs = [torch.empty(t.shape, dtype=torch.float32, device="cuda") for t in k.outputs]
+    comm.launch_sharded(k, [dy_all[lo:hi].contiguous().cuda(), x_all[lo:hi].contiguous().cuda(), gamma.cuda()] + outs)
+    torch.cuda.synchronize()
+    xd, dyd = x_all.double(), dy_all.double()
+    xhat = (xd - xd.mean(1, keepdim=True)) / torch.sqrt(xd.var(1, unbiased=False, keepdim=True) + 1e-5)
+    gd = dyd * gamma.double()
+    dx = (gd - gd.mean(1, keepdim=True) - xhat * (gd * xhat).mean(1, keepdim=True)) / torch.sqrt(xd.var(1, unbiased=False, keepdim=True) + 1e-5)
+    ok = ok and bool(torch.allclose(outs[0].cpu().double(), dx[lo:hi], rtol=1e-4, atol=1e-4))
+    ok = ok and bool(torch.allclose(outs[1].cpu().double(), (dyd * xhat).sum(0), rtol=1e-4, atol=1e-3))
+    ok = ok and bool(torch.allclose(outs[2].cpu().double(), dyd.sum(0), rtol=1e-4, atol=1e-3))
     # the same reductions with the exchange over the ranks' mapped buffers instead of NCCL
     peer = comm.enable_peer_exchange()
     if peer:

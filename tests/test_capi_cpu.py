@@ -322,3 +322,7 @@ def test_generated_kernels_shard_like_the_templates(lib):
     kc = FusedKernel(descs.mul_reduce_sum(8192, 512, [0]), shard_rank=0, shard_world=2)
     assert kc.meta()["template"] == "akgb_col_jit" and kc.inputs[0].shape == (4096, 512)
     assert kc.outputs[0].shard_kind == _capi.SHARD_PARTIAL_SUM
+    # LayerNorm backward over a slice of the rows: dx stays split, the weight and bias gradients are partial sums
+    kl = FusedKernel(descs.layer_norm_backward(16384, 4096), shard_rank=1, shard_world=4)
+    assert kl.meta()["steps"] == ["akgb_row_jit", "reduce_col_f32", "reduce_col_f32"] and kl.inputs[0].shape == (4096, 4096)
+    assert [t.shard_kind for t in kl.outputs] == [_capi.SHARD_SPLIT_AXIS0, _capi.SHARD_PARTIAL_SUM, _capi.SHARD_PARTIAL_SUM]
