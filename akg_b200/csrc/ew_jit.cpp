@@ -536,7 +536,9 @@ bool row_shape(const RowProgram& P, bool vec, RowShape* rs) {
 // recomputing the per-element values each pass needs from the inputs (the later passes find the row in L2).  The same
 // row program, the same per-op rounding; only the schedule differs from row_generate.
 bool row_generate_multipass(const RowProgram& P, bool vec, std::string* out, RowShape* shape) {
-  if (P.col_sums) return false;
+  // sums over all rows: every thread keeps the sums of its own columns, NIT granules per result (registers)
+  const int64_t nit = (P.cols + 512 * (vec ? 8 : 1) - 1) / (512 * (vec ? 8 : 1));
+  if (P.col_sums && nit * (vec ? 8 : 1) > 32) return false;
   RowShape rs;
   rs.vw = vec ? 8 : 1;
   rs.t = 512;
@@ -581,7 +583,17 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
   for (size_t i = 0; i < P.in.size(); ++i) s << "const void* __restrict__ in" << i << ", ";
   for (size_t i = 0; i < P.out.size(); ++i) s << "void* __restrict__ out" << i << ", ";
   s << "i64 rows) {\n";
-  s << "  __shared__ float sm[TPB / 32];\n  const int tr = threadIdx.x;\n  const i64 r = blockIdx.x;\n";
+  s << "  __shared__ float sm[TPB / 32];\n  const int tr = threadIdx.x;\n";
+  if (P.col_sums) {
+    s << "  constexpr int NIT = " << nit << ";\n";
+    for (size_t i = 0; i < P.out.size(); ++i)
+      if (P.out[i].kind == RK_COL)
+        s << "  float cs" << i << "[NIT][VW];\n#pragma unroll\n  for (int q = 0; q < NIT; ++q) {\n#pragma unroll\n"
+             "    for (int j = 0; j < VW; ++j) cs" << i << "[q][j] = 0.f;\n  }\n";
+    s << "  for (i64 r = blockIdx.x; r < rows; r += gridDim.x) {\n";  // a fixed number of CTAs walk the rows
+  } else {
+    s << "  const i64 r = blockIdx.x;\n";
+  }
   // L2 policies: a row stays resident while later passes still need it and leaves first once the last pass has read it
   s << "  unsigned long long pol_last, pol_first;\n"
          "  asm volatile(\"createpolicy.fractional.L2::evict_last.b64 %0, 1.0;\" : \"=l\"(pol_last));\n"
@@ -639,7 +651,10 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
       }
     }
     const bool rev = pass_no & 1;  // every other pass walks backwards: it starts with what the pass before left in L2
-    if (rev) s << "#pragma unroll 2\n  for (i64 c = (i64)tr * VW + (i64)((C - 1) / (T * VW)) * (T * VW); c >= 0; c -= (i64)T * VW) {\n    if (c >= C) continue;\n";
+    if (P.col_sums && last)  // fully unrolled, so that the column sums are indexed statically
+      s << "#pragma unroll\n  for (int q = 0; q < NIT; ++q) {\n    const int it = " << (rev ? "NIT - 1 - q" : "q")
+        << ";\n    const i64 c = (i64)tr * VW + (i64)it * (T * VW);\n    if (c >= C) continue;\n";
+    else if (rev) s << "#pragma unroll 2\n  for (i64 c = (i64)tr * VW + (i64)((C - 1) / (T * VW)) * (T * VW); c >= 0; c -= (i64)T * VW) {\n    if (c >= C) continue;\n";
     else s << "#pragma unroll 2\n  for (i64 c = (i64)tr * VW; c < C; c += (i64)T * VW) {\n";
     ++pass_no;
     for (size_t i = 0; i < P.in.size(); ++i) {
@@ -686,11 +701,27 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
     if (vec) tail << "    st8_" << dt_tag(o.dt) << "(out" << i << ", r * C + c, " << name[o.val] << ");\n";
     else tail << "    st1_" << dt_tag(o.dt) << "(out" << i << ", r * C + c, " << name[o.val] << "[0]);\n";
   }
+  for (size_t i = 0; i < P.out.size(); ++i) {
+    const RowOperand& o = P.out[i];
+    if (o.kind != RK_COL) continue;
+    roots.push_back(o.val);
+    tail << "#pragma unroll\n    for (int j = 0; j < VW; ++j) cs" << i << "[it][j] = __fadd_rn(cs" << i << "[it][j], "
+         << name[o.val] << "[j]);\n";
+  }
   if (!roots.empty()) emit_pass(roots, tail.str(), true);
   for (size_t i = 0; i < P.out.size(); ++i) {
     const RowOperand& o = P.out[i];
     if (o.kind == RK_ROW)
       s << "  if (tr == 0) st1_" << dt_tag(o.dt) << "(out" << i << ", r, " << ref(o.val, is_float_dt(o.dt)) << ");\n";
+  }
+  if (P.col_sums) {
+    s << "  }\n";  // the walk over the rows
+    for (size_t i = 0; i < P.out.size(); ++i) {
+      if (P.out[i].kind != RK_COL) continue;
+      s << "#pragma unroll\n  for (int q = 0; q < NIT; ++q) {\n    const i64 c = (i64)tr * VW + (i64)q * (T * VW);\n#pragma unroll\n"
+           "    for (int j = 0; j < VW; ++j)\n      if (c + j < C) ((float*)out" << i << ")[(i64)blockIdx.x * C + c + j] = cs" << i
+        << "[q][j];\n  }\n";
+    }
   }
   s << "}\n";
   *out = s.str();

@@ -281,11 +281,11 @@ bool build_row_program(const Graph& g, RowProgram* out, std::vector<int>* in_val
   for (auto& o : P.in) any_full_in |= o.kind == RK_FULL;
   if (!any_full_in) return false;
   if (P.col_sums) {
-    // only next to row-wise work (sums over rows alone are the column kernels' job), and only in registers (the
-    // multi-pass schedule has no column sums)
+    // only next to row-wise work (sums over rows alone are the column kernels' job); the multi-pass schedule keeps the
+    // sums of up to 16 384 columns
     bool any_row_reduction = false;
     for (auto& x : P.instr) any_row_reduction |= x.reduce;
-    if (!any_row_reduction || !row_jit_fits_registers(P)) return false;
+    if (!any_row_reduction || (!row_jit_fits_registers(P) && P.cols > 16384)) return false;
   }
   *out = std::move(P);
   return true;

@@ -18,7 +18,7 @@ def random_region(seed, long_rows=False):
     cols = int(rng.choice([8, 24, 40, 96, 257, 1024]))
     if long_rows:  # rows that do not fit a thread group's registers
         lead = [int(v) for v in rng.choice([1, 2, 3, 7], size=int(rng.integers(1, 3)))]
-        cols = int(rng.choice([16392, 20000, 33000, 40001, 65536]))
+        cols = int(rng.choice([9000, 12288, 16392, 20000, 33000, 40001, 65536]))
     shape, red = lead + [cols], lead + [1]
     io_dtype = str(rng.choice([F, F, "float16"]))
     b = _Builder(f"Fused_Fuzz_{seed}")
@@ -113,8 +113,10 @@ def test_random_long_row_region(seed):
     k = FusedKernel(desc)
     has_reduce = any(op["name"].startswith("Reduce") for op in desc["op_desc"])
     sums_rows = any(op["name"] == "ReduceSum" and len(op["output_desc"][0]["shape"]) == 1 for op in desc["op_desc"])
+    cols = desc["input_desc"][0][0]["shape"][-1]
     if has_reduce and not sums_rows and k.meta()["template"] == "akgb_row_jit":
-        assert k.launch_count == 1 and "c += (i64)T * VW" in k.jit_source(desc["input_desc"][0][0]["shape"][-1] % 8 == 0)
+        # (9000 or 12288 columns still fit the registers when few values are live at once)
+        assert k.launch_count == 1 and (cols < 16392 or "c += (i64)T * VW" in k.jit_source(cols % 8 == 0))
     outs = k.empty_outputs()
     k.run_host([a.copy() for a in ins] + outs)
     assert k.check_device_error() == 0

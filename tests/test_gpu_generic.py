@@ -927,7 +927,7 @@ def test_batch_norm_backward_folds_both_sums_in_one_pass(lib):
         assert "out1" in kern.jit_source()  # one generated kernel with both row results
 
 
-@pytest.mark.parametrize("rows,cols", [(300, 1024), (77, 200), (2048, 4096), (5, 8192)])
+@pytest.mark.parametrize("rows,cols", [(300, 1024), (77, 200), (2048, 4096), (5, 8192), (700, 8192), (33, 8190), (40, 16384)])
 def test_layer_norm_backward_sums_over_rows_inside_the_row_kernel(lib, rows, cols):
     """dx row by row, and in the same pass the weight and bias gradients as per-CTA column sums that a column
     reduction folds afterwards."""
@@ -944,8 +944,9 @@ def test_layer_norm_backward_sums_over_rows_inside_the_row_kernel(lib, rows, col
     if FLAGS[0] == 0:
         meta = kern.meta()
         assert meta["steps"] == ["akgb_row_jit", "reduce_col_f32", "reduce_col_f32"]
-        # (with 8192 columns the sums no longer fit the registers beside the row: two separate column reductions)
-        assert ("rb += gridDim.x" in kern.jit_source(cols % 8 == 0)) == (cols <= 4096)
+        # the register schedule walks row blocks, the multi-pass schedule (rows too long for registers) rows
+        src = kern.jit_source(cols % 8 == 0)
+        assert ("rb += gridDim.x" in src) == (cols <= 4096) and ("r += gridDim.x" in src) == (cols > 4096)
 
 
 def test_ops_behind_sums_over_rows_run_after_the_fold(lib):
