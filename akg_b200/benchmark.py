@@ -31,6 +31,7 @@ CASES = {
     "rmsnorm": (lambda s: descs.rmsnorm(s[0], s[1]), {"g": "gamma"}),
     "mulsum_rows": (lambda s: descs.mul_reduce_sum(s[0], s[1], [0]), {}),
     "mulsum_all": (lambda s: descs.mul_reduce_sum(s[0], s[1], [0, 1]), {}),
+    "layernorm_backward": (lambda s: descs.layer_norm_backward(s[0], s[1]), {"gamma": "gamma"}),
     "batchnorm_training": (lambda s: descs.batch_norm_training(s), {"gamma": "gamma", "beta": "beta"}),
     "batchnorm_backward": (lambda s: descs.batch_norm_backward(s), {"gamma": "gamma", "rstd": "gamma"}),
     "matmul": (lambda s, dtype="bfloat16": descs.matmul_bias_relu(s[0], s[1], s[2], dtype=dtype),
