@@ -31,6 +31,8 @@ DTYPE_NAMES = {0: "bool", 1: "int8", 2: "int16", 3: "int32", 4: "int64",
 
 SHARD_REPLICATED, SHARD_SPLIT_AXIS0, SHARD_PARTIAL_SUM, SHARD_PARTIAL_MAX, SHARD_PARTIAL_MIN, SHARD_PARTIAL_PROD = range(6)
 
+EXCHANGE_NAMES = {0: "none", 1: "nccl", 2: "peer-kernel", 3: "in-reduction"}
+
 AKGB_MAX_RANK = 8
 AKGB_FLAG_NO_JIT = 1
 
@@ -110,6 +112,7 @@ _SIGNATURES = [
     ("akgb_allreduce_partials", ctypes.c_int, [_vp, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]),
     ("akgb_launch_sharded", ctypes.c_int, [_vp, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p,
                                            ctypes.c_size_t, ctypes.c_void_p]),
+    ("akgb_sharded_exchange_kind", ctypes.c_int32, [_vp, ctypes.c_void_p]),
     ("akgb_set_cache_dir", ctypes.c_int, [ctypes.c_char_p]),
     ("akgb_jit_cache_stats", ctypes.c_int, [ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]),
     ("akgb_dump_jit_source", ctypes.c_int, [_vp, ctypes.c_int32, ctypes.c_char_p, ctypes.c_size_t,

@@ -41,6 +41,7 @@ struct DeviceState {
   void* gelu_lut = nullptr;   // device copy of the f16 tanh table
   uint32_t* err_word = nullptr;
   int sm_count = 0;
+  bool exchange_failed = false;  // sticky: see device_exchange_failed()
 };
 DeviceState g_dev[kMaxDevices];
 
@@ -85,15 +86,48 @@ struct akgb_kernel {
   std::vector<size_t> chunk_bytes;   // per argument: bytes of one chunk
   cudaStream_t s_in = nullptr, s_out = nullptr;
   std::vector<cudaEvent_t> ev_in, ev_done;
+  // arrival counters of the reductions that fold their partials in the launch that produced them (k_reduce.cu);
+  // allocated zeroed on the first launch of a plan with such a step, left at zero by every launch
+  uint32_t* d_tickets = nullptr;
 };
 
 namespace {
 
-akgb_status ensure_device_state(akgb_kernel* k, bool need_lut) {
+bool plan_has_reduction(const Plan& p) {
+  for (const Step& st : p.steps)
+    if (st.kind == StepK::ReduceCol || st.kind == StepK::ReduceAll || st.kind == StepK::ReduceColDual) return true;
+  return p.fallback && plan_has_reduction(*p.fallback);
+}
+
+// The calling thread's current device must be the kernel's: device state is cached per ordinal and generated kernels are
+// loaded into the current context, so a launch issued with another device current would mix the two.
+akgb_status check_current_device(const akgb_kernel* k, const char* who) {
+  int cur = -1;
+  if (cudaGetDevice(&cur) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(AKGB_CUDA_ERROR, std::string(who) + ": no current CUDA device");
+  }
+  if (cur != k->device)
+    return fail(AKGB_INVALID_ARG, std::string(who) + ": the kernel was compiled for device " + std::to_string(k->device) +
+                                      " but device " + std::to_string(cur) + " is current on this thread");
+  return AKGB_OK;
+}
+
+akgb_status ensure_device_state(akgb_kernel* k, bool need_lut, const Plan* plan = nullptr) {
   int dev = k->device;
   if (dev < 0 || dev >= kMaxDevices) return fail(AKGB_INVALID_ARG, "device ordinal out of range");
+  akgb_status cs = check_current_device(k, "akgb");
+  if (cs != AKGB_OK) return cs;
   DeviceState& ds = g_dev[dev];
   std::lock_guard<std::mutex> lock(ds.mu);
+  if (!k->d_tickets && plan_has_reduction(plan ? *plan : k->plan)) {
+    void* d = nullptr;
+    cudaError_t e = cudaMalloc(&d, kReduceTicketWords * sizeof(uint32_t));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(arrival counters)");
+    e = cudaMemset(d, 0, kReduceTicketWords * sizeof(uint32_t));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemset(arrival counters)");
+    k->d_tickets = reinterpret_cast<uint32_t*>(d);
+  }
   if (need_lut && !ds.gelu_lut) {
     std::vector<uint16_t> h(gelu_lut_entries());
     gelu_lut_build(h.data());
@@ -133,10 +167,14 @@ akgb_status enter_fallback(Plan& plan, size_t ws_bytes) {
   return AKGB_OK;
 }
 
-akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws, size_t ws_bytes, cudaStream_t s) {
+// `fx` / `fx_step`: the exchange that step `fx_step` of the plan completes inside its own launch (sharded reductions)
+akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws, size_t ws_bytes, cudaStream_t s,
+                     const FinishExchange* fx = nullptr, int fx_step = -1) {
   if (plan.fallback && plan.use_fallback) return run_plan(k, *plan.fallback, tensors, ws, ws_bytes, s);
   DeviceState& ds = g_dev[k->device];
-  for (Step& st : plan.steps) {
+  for (size_t si = 0; si < plan.steps.size(); ++si) {
+    Step& st = plan.steps[si];
+    const FinishExchange* sfx = ((int)si == fx_step) ? fx : nullptr;
     cudaError_t e = cudaSuccess;
     void* a = resolve(st.a, tensors, ws);
     void* b = resolve(st.b, tensors, ws);
@@ -159,7 +197,7 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
       case StepK::ReduceCol:
         for (int64_t bi = 0; bi < st.red_outer && e == cudaSuccess; ++bi)
           e = reduce_col_f32(st.red_op, (const float*)a + bi * st.red_batch_in, (float*)o + bi * st.red_batch_out,
-                             st.red_len, st.red_inner, scratch, k->sm_count, s, &st.dims);
+                             st.red_len, st.red_inner, scratch, k->sm_count, s, &st.dims, k->d_tickets, sfx);
         break;
       case StepK::Gather:
         e = gather_rows(a, b, o, st.ix_outer, st.ix_dim, st.ix_n, st.ix_inner, st.ix_esize, st.ix_idx64, s, &st.dims);
@@ -209,17 +247,20 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
       case StepK::ReduceColDual:
         if (reduce_col_dual_supported(st.red_inner, a)) {
           e = reduce_col_dual_f32(st.red_op, st.red_op2, (const float*)a, (float*)o, (float*)o2, st.red_len, st.red_inner,
-                                  scratch, k->sm_count, s, &st.dims);
+                                  scratch, k->sm_count, s, &st.dims, k->d_tickets, sfx);
+        } else if (sfx) {
+          e = cudaErrorNotSupported;  // fused_exchange_step() only picks aligned inputs
         } else {  // unaligned input: the two single reductions, one after the other
           e = reduce_col_f32(st.red_op, (const float*)a, (float*)o, st.red_len, st.red_inner, scratch, k->sm_count, s,
-                             &st.dims);
+                             &st.dims, k->d_tickets);
           if (e == cudaSuccess)
             e = reduce_all_f32(st.red_op2, (const float*)a, (float*)o2, st.red_len * st.red_inner, scratch, k->sm_count, s,
-                               nullptr);
+                               nullptr, k->d_tickets);
         }
         break;
       case StepK::ReduceAll:
-        e = reduce_all_f32(st.red_op, (const float*)a, (float*)o, st.red_len, scratch, k->sm_count, s, &st.dims);
+        e = reduce_all_f32(st.red_op, (const float*)a, (float*)o, st.red_len, scratch, k->sm_count, s, &st.dims,
+                           k->d_tickets, sfx);
         break;
       case StepK::ReduceRow:
         e = reduce_row_f32(st.red_op, (const float*)a, (float*)o, st.red_outer, st.red_len, s, &st.dims);
@@ -250,14 +291,14 @@ int launches_of(const akgb_kernel* k) {
   int n = 0;
   for (const Step& st : active_plan(k).steps) {
     switch (st.kind) {
-      case StepK::ReduceCol:
-        n += (int)st.red_outer * (reduce_col_workspace(st.red_len, st.red_inner, k->sm_count) ? 2 : 1);
+      case StepK::ReduceCol:  // the fold of the row splits happens in the launch that produced them
+        n += (int)st.red_outer * reduce_col_launches(st.red_len, st.red_inner, k->sm_count, true);
         break;
       case StepK::ReduceAll:
-        n += 2;
+        n += 1;
         break;
       case StepK::ReduceColDual:
-        n += 3;
+        n += (st.red_inner + 127) / 128 <= kReduceMaxTicketTiles ? 1 : 3;
         break;
       case StepK::GeluChain:
         n += (st.gelu.n % 8) ? 2 : 1;
@@ -387,6 +428,91 @@ akgb_status stage(akgb_kernel* k) {
 
 }  // namespace
 
+bool akgb::device_exchange_failed(int device) {
+  return device >= 0 && device < kMaxDevices && g_dev[device].exchange_failed;
+}
+void akgb::device_exchange_set_failed(int device, bool failed) {
+  if (device >= 0 && device < kMaxDevices) g_dev[device].exchange_failed = failed;
+}
+
+// The step of the plan that produces ALL partial outputs of a sharded kernel, if there is exactly one and it is a
+// reduction that can complete the exchange in its own launch; -1 otherwise.  Fills the slot positions.
+namespace {
+int fused_exchange_step(const akgb_kernel* k, const Plan& plan, FinishExchange* fx) {
+  std::vector<int> partial;
+  for (size_t i = 0; i < k->descs.size(); ++i)
+    if (k->descs[i].shard_kind >= AKGB_PARTIAL_SUM) {
+      if (k->descs[i].dtype != AKGB_FLOAT32) return -1;
+      partial.push_back((int)i);
+    }
+  if (partial.empty() || partial.size() > 2) return -1;
+  auto op_of = [](int kind) {
+    return kind == AKGB_PARTIAL_SUM ? RedOp::Sum : kind == AKGB_PARTIAL_MAX ? RedOp::Max
+         : kind == AKGB_PARTIAL_MIN ? RedOp::Min : RedOp::Prod;
+  };
+  for (size_t si = 0; si < plan.steps.size(); ++si) {
+    const Step& st = plan.steps[si];
+    if (st.out.arg != partial[0]) continue;
+    // nothing after this step may touch the result (it is final once the finisher has written it)
+    if (si + 1 != plan.steps.size()) return -1;
+    if (st.kind == StepK::ReduceCol && partial.size() == 1) {
+      if (st.red_outer != 1 || st.red_inner > kExchangeSlotElems || st.red_op != op_of(k->descs[partial[0]].shard_kind) ||
+          !reduce_col_fusable(st.red_len, st.red_inner, k->sm_count))
+        return -1;
+      fx->slot_off = 0;
+      fx->finishers = (int)((st.red_inner + 127) / 128);
+      return (int)si;
+    }
+    if (st.kind == StepK::ReduceAll && partial.size() == 1) {
+      if (st.red_op != op_of(k->descs[partial[0]].shard_kind)) return -1;
+      fx->slot_off = 0;
+      fx->finishers = 1;
+      return (int)si;
+    }
+    if (st.kind == StepK::ReduceColDual && partial.size() == 2 && st.out2.arg == partial[1]) {
+      if (st.red_inner + 1 > kExchangeSlotElems || st.red_inner % 4 != 0 ||
+          st.red_op != op_of(k->descs[partial[0]].shard_kind) || st.red_op2 != op_of(k->descs[partial[1]].shard_kind))
+        return -1;
+      fx->slot_off = 0;
+      fx->slot_off2 = (int)st.red_inner;
+      fx->finishers = (int)((st.red_inner + 127) / 128) + 1;
+      return (int)si;
+    }
+    return -1;
+  }
+  return -1;
+}
+}  // namespace
+
+bool akgb::kernel_exchange_fusable(const akgb_kernel* k) {
+  if (!k || k->graph.dynamic) return false;
+  FinishExchange fx;
+  return fused_exchange_step(k, active_plan(k), &fx) >= 0;
+}
+
+akgb_status akgb::launch_with_exchange(akgb_kernel* k, const FinishExchange& base, void* const* tensors, void* workspace,
+                                       size_t workspace_bytes, void* stream, bool* fused) {
+  *fused = false;
+  if (!k || !tensors) return fail(AKGB_INVALID_ARG, "null argument");
+  if (k->graph.dynamic) return AKGB_OK;
+  FinishExchange fx = base;
+  Plan& plan = (k->plan.fallback && k->plan.use_fallback) ? *k->plan.fallback : k->plan;
+  const int step = fused_exchange_step(k, plan, &fx);
+  if (step < 0) return AKGB_OK;  // nothing launched: the caller runs the kernel and the exchange one after the other
+  if (workspace_bytes < k->plan.workspace_bytes || (k->plan.workspace_bytes && !workspace))
+    return fail(AKGB_INVALID_ARG, "workspace smaller than akgb_workspace_size()");
+  if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return fail(AKGB_MISALIGNED, "workspace must be 256-byte aligned");
+  const Step& st = plan.steps[step];
+  if (st.kind == StepK::ReduceColDual && (reinterpret_cast<uintptr_t>(resolve(st.a, tensors, workspace)) & 15))
+    return AKGB_OK;  // unaligned input: the two-kernel form of this step cannot carry the exchange
+  akgb_status s = ensure_device_state(k, plan.needs_gelu_lut);
+  if (s != AKGB_OK) return s;
+  fx.err = g_dev[k->device].err_word;
+  *fused = true;
+  return run_plan(k, plan, tensors, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream), &fx, step);
+}
+
 uint32_t* akgb::kernel_error_word(akgb_kernel* k) {
   if (!k || ensure_device_state(k, false) != AKGB_OK) return nullptr;
   return g_dev[k->device].err_word;
@@ -471,6 +597,13 @@ akgb_status akgb_compile(const char* info_json, size_t len, const akgb_options* 
 
 void akgb_release(akgb_kernel* k) {
   if (!k) return;
+  if (k->d_tickets) {
+    int cur = -1;
+    cudaGetDevice(&cur);
+    cudaSetDevice(k->device);
+    cudaFree(k->d_tickets);
+    if (cur >= 0) cudaSetDevice(cur);
+  }
   if (k->staged) {
     cudaSetDevice(k->device);
     for (void* p : k->d_tensors)
@@ -557,7 +690,7 @@ extern "C" akgb_status akgb_launch_dynamic(akgb_kernel* k, void* const* tensors,
     return fail(AKGB_INVALID_ARG, "workspace smaller than akgb_bind_shapes() reported");
   if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255))
     return fail(AKGB_MISALIGNED, "workspace must be 256-byte aligned");
-  st = ensure_device_state(k, b->plan.needs_gelu_lut);
+  st = ensure_device_state(k, b->plan.needs_gelu_lut, &b->plan);
   if (st != AKGB_OK) return st;
   return run_plan(k, b->plan, tensors, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
 }
@@ -580,6 +713,9 @@ akgb_status akgb_launch(akgb_kernel* k, void* const* tensors, void* workspace, s
 akgb_status akgb_run_host(akgb_kernel* k, void* const* host) {
   if (!k || !host) return fail(AKGB_INVALID_ARG, "null argument");
   if (k->graph.dynamic) return fail(AKGB_INVALID_ARG, "this kernel has dynamic shapes: use akgb_launch_dynamic");
+  // like the reference's launcher this entry point picks its device itself (and leaves it current)
+  const cudaError_t se = cudaSetDevice(k->device);
+  if (se != cudaSuccess) return cuda_fail(se, "cudaSetDevice");
   akgb_status st = stage(k);
   if (st != AKGB_OK) return st;
   st = ensure_device_state(k, k->plan.needs_gelu_lut);
@@ -637,6 +773,7 @@ akgb_status akgb_check_device_error(akgb_kernel* k, uint32_t* word) {
   if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(error word)");
   if (*word) {
     cudaMemset(ds.err_word, 0, sizeof(uint32_t));
+    if (*word & 256u) ds.exchange_failed = true;  // the ranks' exchange counters may disagree now
     return fail(AKGB_DEVICE_TIMEOUT, "a bounded device-side wait gave up");
   }
   return AKGB_OK;

@@ -284,6 +284,15 @@ akgb_status akgb_comm_set_peer_exchange(akgb_comm* c, int32_t enabled) {
         return AKGB_INVALID_ARG;
       }
   }
+  if (c->local_buf && device_exchange_failed(c->device)) {
+    // after a wait that ran out the ranks' call counters may differ: start again from call 0 (every rank does this,
+    // then the ranks synchronise before their next sharded launch)
+    cudaSetDevice(c->device);
+    cudaDeviceSynchronize();
+    const cudaError_t e = cudaMemset(c->local_buf, 0, kExchangeBytes);
+    if (e != cudaSuccess) return cuda_fail_comm(e, "cudaMemset (exchange buffer)");
+  }
+  device_exchange_set_failed(c->device, false);
   c->peers_ready = enabled != 0;
   return AKGB_OK;
 }
@@ -297,10 +306,58 @@ akgb_status akgb_comm_set_timeout_ms(akgb_comm* c, double ms) {
   return AKGB_OK;
 }
 
+namespace {
+akgb_status refuse_after_timeout(const akgb_comm* c) {
+  if (!c->peers_ready || c->world <= 1 || !device_exchange_failed(c->device)) return AKGB_OK;
+  set_last_error("a peer-memory exchange on this device gave up earlier, the ranks' call counters may disagree: call "
+                 "akgb_comm_set_peer_exchange on ALL ranks (1 to restart the path, 0 to continue over NCCL) and "
+                 "synchronise the ranks before the next sharded launch");
+  return AKGB_DEVICE_TIMEOUT;
+}
+void fill_exchange_base(akgb_comm* c, FinishExchange* fx) {
+  for (int q = 0; q < c->world; ++q) fx->peer[q] = c->peer_buf[q];
+  fx->rank = c->rank;
+  fx->world = c->world;
+  if (c->clock_khz == 0) {  // queried once: this attribute is slow to read
+    int khz = 0;
+    cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, c->device);
+    c->clock_khz = khz > 0 ? khz : 1500000;
+  }
+  fx->limit_cycles = (long long)(c->timeout_ms * c->clock_khz);
+}
+}  // namespace
+
+int32_t akgb_sharded_exchange_kind(const akgb_kernel* k, const akgb_comm* c) {
+  if (!k || !c || c->world <= 1) return AKGB_EXCHANGE_NONE;
+  const int n = akgb_num_tensors(k);
+  bool any = false, all_small_f32 = true;
+  size_t total = 0;
+  int segs = 0;
+  for (int i = 0; i < n; ++i) {
+    akgb_tensor_desc d;
+    if (akgb_tensor_info(k, i, &d) != AKGB_OK || d.shard_kind < AKGB_PARTIAL_SUM) continue;
+    any = true;
+    size_t count = 1;
+    for (int r = 0; r < d.rank; ++r) count *= (size_t)d.shape[r];
+    total += count;
+    ++segs;
+    if (d.dtype != AKGB_FLOAT32) all_small_f32 = false;
+  }
+  if (!any) return AKGB_EXCHANGE_NONE;
+  if (!c->peers_ready) return AKGB_EXCHANGE_NCCL;
+  if (kernel_exchange_fusable(k)) return AKGB_EXCHANGE_IN_REDUCTION;
+  return all_small_f32 && total <= (size_t)kExchangeSlotElems && segs <= kExchangeMaxSegs ? AKGB_EXCHANGE_PEER_KERNEL
+                                                                                         : AKGB_EXCHANGE_NCCL;
+}
+
 akgb_status akgb_allreduce_partials(const akgb_kernel* k, akgb_comm* c, void* const* tensors, void* stream) {
   if (!k || !c || !tensors) {
     set_last_error("akgb_allreduce_partials: null argument");
     return AKGB_INVALID_ARG;
+  }
+  {
+    const akgb_status rs = refuse_after_timeout(c);
+    if (rs != AKGB_OK) return rs;
   }
   const int n = akgb_num_tensors(k);
   Nccl& lib = nccl();
@@ -353,15 +410,12 @@ akgb_status akgb_allreduce_partials(const akgb_kernel* k, akgb_comm* c, void* co
     if (rc != kNcclSuccess) return nccl_fail(rc, "ncclGroupEnd");
   }
   if (xa.n_seg) {
-    for (int q = 0; q < c->world; ++q) xa.peer[q] = c->peer_buf[q];
+    FinishExchange base;
+    fill_exchange_base(c, &base);
+    for (int q = 0; q < c->world; ++q) xa.peer[q] = base.peer[q];
     xa.rank = c->rank;
     xa.world = c->world;
-    if (c->clock_khz == 0) {  // queried once: this attribute is slow to read
-      int khz = 0;
-      cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, c->device);
-      c->clock_khz = khz > 0 ? khz : 1500000;
-    }
-    xa.limit_cycles = (long long)(c->timeout_ms * c->clock_khz);
+    xa.limit_cycles = base.limit_cycles;
     xa.err = kernel_error_word(const_cast<akgb_kernel*>(k));
     if (!xa.err) return AKGB_CUDA_ERROR;
     const cudaError_t e = exchange_allreduce(xa, static_cast<cudaStream_t>(stream));
@@ -372,6 +426,20 @@ akgb_status akgb_allreduce_partials(const akgb_kernel* k, akgb_comm* c, void* co
 
 akgb_status akgb_launch_sharded(akgb_kernel* k, akgb_comm* c, void* const* tensors, void* workspace,
                                 size_t workspace_bytes, void* stream) {
+  if (!k || !c || !tensors) {
+    set_last_error("akgb_launch_sharded: null argument");
+    return AKGB_INVALID_ARG;
+  }
+  if (c->world > 1 && c->peers_ready) {
+    const akgb_status rs = refuse_after_timeout(c);
+    if (rs != AKGB_OK) return rs;
+    // a reduction that produces all the partial outputs completes their exchange in its own launch
+    FinishExchange base;
+    fill_exchange_base(c, &base);
+    bool fused = false;
+    const akgb_status fs = launch_with_exchange(k, base, tensors, workspace, workspace_bytes, stream, &fused);
+    if (fs != AKGB_OK || fused) return fs;
+  }
   const akgb_status st = akgb_launch(k, tensors, workspace, workspace_bytes, stream);
   if (st != AKGB_OK) return st;
   return akgb_allreduce_partials(k, c, tensors, stream);

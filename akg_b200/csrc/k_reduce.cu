@@ -249,11 +249,290 @@ __global__ void __launch_bounds__(256) reduce_row_f32_kernel(const float* __rest
   }
 }
 
+// ---- fold by the finishing CTA, optionally with the exchange over peer memory ------------------------------------
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Called by ALL threads of a finishing CTA (any block shape).  Thread `tid` of `nthreads` holds value `v` for slot position `pos` when
+// `active`.  Stores the values into this rank's slot of every rank's buffer, raises flag `flag` there, waits (bounded)
+// for the same flag of every rank in the own buffer and folds the slots in rank order, so that every rank gets the same
+// bits.  Returns false when the wait ran out (bit 8 of the error word is set, `v` is unchanged).  The finisher that
+// closes the call (the last of fx.finishers) advances the call counter.
+template <class Op>
+__device__ __forceinline__ bool finish_exchange(const FinishExchange& fx, float& v, bool active, int pos, int flag,
+                                                int tid) {
+  void* own = fx.peer[fx.rank];
+  uint32_t* counter = exchange_counter(own);
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(counter) + 1u;
+  const int par = (int)(epoch & 1u);
+  if (active)
+    for (int q = 0; q < fx.world; ++q) exchange_slot(fx.peer[q], par, fx.rank)[pos] = v;
+  __threadfence_system();
+  __syncthreads();
+  int timed_out = 0;
+  if (tid < fx.world) {
+    st_release_sys_u32(exchange_flag(fx.peer[tid], par, fx.rank, flag), epoch);
+    const uint32_t* f = exchange_flag(own, par, tid, flag);
+    const long long t0 = clock64();
+    while (ld_acquire_sys_u32(f) != epoch) {
+      if (clock64() - t0 > fx.limit_cycles) {
+        timed_out = 1;
+        break;
+      }
+      __nanosleep(32);
+    }
+  }
+  const bool failed = __syncthreads_or(timed_out) != 0;
+  if (failed) {
+    if (tid == 0) atomicOr(fx.err, 256u);
+  } else if (active) {
+    float r = *reinterpret_cast<volatile float*>(exchange_slot(own, par, 0) + pos);
+    for (int q = 1; q < fx.world; ++q)
+      r = Op::apply(r, *reinterpret_cast<volatile float*>(exchange_slot(own, par, q) + pos));
+    v = r;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    uint32_t* ticket = counter + 1;
+    if (atomicAdd(ticket, 1u) == (uint32_t)fx.finishers - 1u) {
+      *ticket = 0;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(counter) = epoch;
+    }
+  }
+  return !failed;
+}
+
+// true in every thread of exactly one CTA among the `expected` that call this with the same ticket word: the one that
+// arrives last.  The caller has written its partials before the call; the last CTA may read everybody's afterwards.
+__device__ __forceinline__ bool arrive_last(uint32_t* ticket, unsigned expected, int tid) {
+  __shared__ int last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned t = atomicAdd(ticket, 1u);
+    last = t == expected - 1u;
+    if (last) *ticket = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  const bool r = last != 0;
+  if (r) __threadfence();
+  return r;
+}
+
+// fold of partial[splits, inner] over the splits for the 128 columns of tile `tile`, in split order (the order of
+// reduce_col_finish_kernel: same bits), then the exchange, then the store
+template <class Op>
+__device__ __forceinline__ void finish_col_tile(const float* partial, float* out, int64_t splits, int64_t inner,
+                                                int tile, int tid, const FinishExchange& fx) {
+  const int64_t c = (int64_t)tile * kColTile + tid;
+  const bool active = tid < kColTile && c < inner;
+  float a = Op::identity();
+  if (active)
+    for (int64_t s = 0; s < splits; ++s) a = Op::apply(a, __ldcg(partial + s * inner + c));
+  // when the wait runs out the value stays this rank's own partial (and the error word says so)
+  if (fx.world > 1) finish_exchange<Op>(fx, a, active, fx.slot_off + (int)c, tile, tid);
+  if (active) out[c] = a;
+}
+
+// fold of partial[n] by a 256-thread CTA in a fixed order, then the exchange of the one value, then the store
+template <class Op>
+__device__ __forceinline__ void finish_all(const float* partial, float* out, int n, int tid, float* red,
+                                           const FinishExchange& fx, int slot_pos, int flag) {
+  float a = Op::identity();
+  for (int i = tid; i < n; i += 256) a = Op::apply(a, __ldcg(partial + i));
+  // block_reduce by linear thread id (the CTA may be 32x8)
+  a = warp_reduce<Op>(a);
+  __syncthreads();
+  if ((tid & 31) == 0) red[tid >> 5] = a;
+  __syncthreads();
+  float r = (tid & 31) < 8 ? red[tid & 31] : Op::identity();
+  r = warp_reduce<Op>(r);
+  if (fx.world > 1) finish_exchange<Op>(fx, r, tid == 0, slot_pos, flag, tid);
+  if (tid == 0) out[0] = r;
+}
+
+// reduce_col_f32_kernel + fold by the last CTA of every column tile (+ exchange)
+template <class Op, bool VEC>
+__global__ void __launch_bounds__(kColTx* kColTy) reduce_col_fused_f32_kernel(const float* __restrict__ x,
+                                                                              float* __restrict__ partial,
+                                                                              float* __restrict__ out, int64_t red,
+                                                                              int64_t inner, int64_t rows_per_split,
+                                                                              uint32_t* tickets, FinishExchange fx) {
+  __shared__ float4 sm[kColTy][kColTx];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int64_t col = ((int64_t)blockIdx.x * kColTx + tx) * 4;
+  const int64_t r0 = (int64_t)blockIdx.y * rows_per_split;
+  const int64_t r1 = min(red, r0 + rows_per_split);
+  const float id = Op::identity();
+  float4 acc0 = make_float4(id, id, id, id), acc1 = acc0, acc2 = acc0, acc3 = acc0;
+  if (VEC) {
+    if (col < inner) {
+      const float* base = x + col;
+      int64_t r = r0 + ty;
+      for (; r + 3 * kColTy < r1; r += 4 * kColTy) {
+        const float4 a = ld_stream_f4(base + r * inner);
+        const float4 b = ld_stream_f4(base + (r + kColTy) * inner);
+        const float4 c = ld_stream_f4(base + (r + 2 * kColTy) * inner);
+        const float4 d = ld_stream_f4(base + (r + 3 * kColTy) * inner);
+        acc0 = apply4<Op>(acc0, a);
+        acc1 = apply4<Op>(acc1, b);
+        acc2 = apply4<Op>(acc2, c);
+        acc3 = apply4<Op>(acc3, d);
+      }
+      for (; r < r1; r += kColTy) acc0 = apply4<Op>(acc0, ld_stream_f4(base + r * inner));
+    }
+  } else {
+    for (int64_t r = r0 + ty; r < r1; r += kColTy) {
+      const float* row = x + r * inner;
+      float4 a = make_float4(id, id, id, id);
+      if (col + 0 < inner) a.x = row[col + 0];
+      if (col + 1 < inner) a.y = row[col + 1];
+      if (col + 2 < inner) a.z = row[col + 2];
+      if (col + 3 < inner) a.w = row[col + 3];
+      acc0 = apply4<Op>(acc0, a);
+    }
+  }
+  acc0 = apply4<Op>(apply4<Op>(acc0, acc1), apply4<Op>(acc2, acc3));
+  sm[ty][tx] = acc0;
+  __syncthreads();
+#pragma unroll
+  for (int h = kColTy / 2; h > 0; h >>= 1) {
+    if (ty < h) sm[ty][tx] = apply4<Op>(sm[ty][tx], sm[ty + h][tx]);
+    __syncthreads();
+  }
+  if (ty == 0) {
+    const float4 r = sm[0][tx];
+    float* o = partial + (int64_t)blockIdx.y * inner + col;
+    if (col + 0 < inner) o[0] = r.x;
+    if (col + 1 < inner) o[1] = r.y;
+    if (col + 2 < inner) o[2] = r.z;
+    if (col + 3 < inner) o[3] = r.w;
+  }
+  const int tid = ty * kColTx + tx;
+  if (!arrive_last(tickets + blockIdx.x, gridDim.y, tid)) return;
+  finish_col_tile<Op>(partial, out, gridDim.y, inner, blockIdx.x, tid, fx);
+}
+
+// reduce_col_dual_f32_kernel + both folds in the same launch (+ exchange of both results)
+template <class Op1, class Op2>
+__global__ void __launch_bounds__(kColTx* kColTy) reduce_col_dual_fused_f32_kernel(
+    const float* __restrict__ x, float* __restrict__ partial, float* __restrict__ partial2, float* __restrict__ out1,
+    float* __restrict__ out2, int64_t red, int64_t inner, int64_t rows_per_split, uint32_t* tickets, FinishExchange fx) {
+  __shared__ float4 sm[kColTy][kColTx];
+  __shared__ float red2[32];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int64_t col = ((int64_t)blockIdx.x * kColTx + tx) * 4;
+  const int64_t r0 = (int64_t)blockIdx.y * rows_per_split;
+  const int64_t r1 = min(red, r0 + rows_per_split);
+  const float id = Op1::identity(), id2 = Op2::identity();
+  float4 acc0 = make_float4(id, id, id, id), acc1 = acc0, acc2 = acc0, acc3 = acc0;
+  float4 b0 = make_float4(id2, id2, id2, id2), b1 = b0;
+  if (col < inner) {
+    const float* base = x + col;
+    int64_t r = r0 + ty;
+    for (; r + 3 * kColTy < r1; r += 4 * kColTy) {
+      const float4 a = ld_stream_f4(base + r * inner);
+      const float4 b = ld_stream_f4(base + (r + kColTy) * inner);
+      const float4 c = ld_stream_f4(base + (r + 2 * kColTy) * inner);
+      const float4 d = ld_stream_f4(base + (r + 3 * kColTy) * inner);
+      acc0 = apply4<Op1>(acc0, a);
+      acc1 = apply4<Op1>(acc1, b);
+      acc2 = apply4<Op1>(acc2, c);
+      acc3 = apply4<Op1>(acc3, d);
+      b0 = apply4<Op2>(b0, apply4<Op2>(a, b));
+      b1 = apply4<Op2>(b1, apply4<Op2>(c, d));
+    }
+    for (; r < r1; r += kColTy) {
+      const float4 a = ld_stream_f4(base + r * inner);
+      acc0 = apply4<Op1>(acc0, a);
+      b0 = apply4<Op2>(b0, a);
+    }
+  }
+  acc0 = apply4<Op1>(apply4<Op1>(acc0, acc1), apply4<Op1>(acc2, acc3));
+  sm[ty][tx] = acc0;
+  __syncthreads();
+#pragma unroll
+  for (int h = kColTy / 2; h > 0; h >>= 1) {
+    if (ty < h) sm[ty][tx] = apply4<Op1>(sm[ty][tx], sm[ty + h][tx]);
+    __syncthreads();
+  }
+  if (ty == 0) {
+    const float4 r = sm[0][tx];
+    float* o = partial + (int64_t)blockIdx.y * inner + col;
+    if (col + 0 < inner) o[0] = r.x;
+    if (col + 1 < inner) o[1] = r.y;
+    if (col + 2 < inner) o[2] = r.z;
+    if (col + 3 < inner) o[3] = r.w;
+  }
+  b0 = apply4<Op2>(b0, b1);
+  float s2 = Op2::apply(Op2::apply(b0.x, b0.y), Op2::apply(b0.z, b0.w));
+  s2 = warp_reduce<Op2>(s2);
+  const int tid = ty * kColTx + tx, lane = tid & 31, warp = tid >> 5;
+  if (lane == 0) red2[warp] = s2;
+  __syncthreads();
+  if (warp == 0) {
+    float v = lane < (kColTx * kColTy) / 32 ? red2[lane] : id2;
+    v = warp_reduce<Op2>(v);
+    if (lane == 0) partial2[(int64_t)blockIdx.y * gridDim.x + blockIdx.x] = v;
+  }
+  // one arrival covers both partials of this CTA: first the column tile's counter, then the counter of the whole grid
+  const bool last_of_tile = arrive_last(tickets + blockIdx.x, gridDim.y, tid);
+  if (last_of_tile) finish_col_tile<Op1>(partial, out1, gridDim.y, inner, blockIdx.x, tid, fx);
+  const bool last_of_grid = arrive_last(tickets + gridDim.x, gridDim.x * gridDim.y, tid);
+  if (last_of_grid)
+    finish_all<Op2>(partial2, out2, (int)(gridDim.x * gridDim.y), tid, red2, fx, fx.slot_off2, (int)gridDim.x);
+}
+
+// reduce_all_f32_kernel + fold by the last CTA (+ exchange)
+template <class Op, bool VEC>
+__global__ void __launch_bounds__(256) reduce_all_fused_f32_kernel(const float* __restrict__ x,
+                                                                   float* __restrict__ partial,
+                                                                   float* __restrict__ out, int64_t n,
+                                                                   uint32_t* tickets, FinishExchange fx) {
+  __shared__ float red[32];
+  const float id = Op::identity();
+  float a0 = id, a1 = id, a2 = id, a3 = id;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  if (VEC) {
+    const int64_t n4 = n >> 2;
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    int64_t i = tid;
+    for (; i + 3 * stride < n4; i += 4 * stride) {
+      const float4 p = ld_stream_f4(x4 + i), q = ld_stream_f4(x4 + i + stride);
+      const float4 r = ld_stream_f4(x4 + i + 2 * stride), t = ld_stream_f4(x4 + i + 3 * stride);
+      a0 = Op::apply(a0, Op::apply(Op::apply(p.x, p.y), Op::apply(p.z, p.w)));
+      a1 = Op::apply(a1, Op::apply(Op::apply(q.x, q.y), Op::apply(q.z, q.w)));
+      a2 = Op::apply(a2, Op::apply(Op::apply(r.x, r.y), Op::apply(r.z, r.w)));
+      a3 = Op::apply(a3, Op::apply(Op::apply(t.x, t.y), Op::apply(t.z, t.w)));
+    }
+    for (; i < n4; i += stride) {
+      const float4 p = ld_stream_f4(x4 + i);
+      a0 = Op::apply(a0, Op::apply(Op::apply(p.x, p.y), Op::apply(p.z, p.w)));
+    }
+    for (int64_t j = (n4 << 2) + tid; j < n; j += stride) a1 = Op::apply(a1, x[j]);
+  } else {
+    for (int64_t j = tid; j < n; j += stride) a0 = Op::apply(a0, x[j]);
+  }
+  float a = Op::apply(Op::apply(a0, a1), Op::apply(a2, a3));
+  a = block_reduce<Op>(a, red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = a;
+  if (!arrive_last(tickets, gridDim.x, threadIdx.x)) return;
+  finish_all<Op>(partial, out, (int)gridDim.x, threadIdx.x, red, fx, fx.slot_off, 0);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 template <class Op>
 cudaError_t col_impl(const float* x, float* out, int64_t red, int64_t inner, void* ws, int sm_count, cudaStream_t s,
-                     LaunchDims* dims) {
+                     LaunchDims* dims, uint32_t* tickets, const FinishExchange* fx) {
   const int64_t splits = col_row_splits(red, inner, sm_count);
   const int64_t rows_per_split = (red + splits - 1) / splits;
   dim3 grid((unsigned)((inner + kColTile - 1) / kColTile), (unsigned)splits), block(kColTx, kColTy);
@@ -265,7 +544,19 @@ cudaError_t col_impl(const float* x, float* out, int64_t red, int64_t inner, voi
     dims->smem = sizeof(float4) * kColTx * kColTy;
   }
   float* partial = splits == 1 ? out : reinterpret_cast<float*>(ws);
-  if (inner % 4 == 0 && aligned16(x))
+  const bool vec = inner % 4 == 0 && aligned16(x);
+  const bool fused = tickets && splits > 1 && grid.x <= (unsigned)kReduceMaxTicketTiles;
+  if (fx && fx->world > 1 && !fused) return cudaErrorNotSupported;  // the caller asks reduce_col_fusable() first
+  if (fused) {
+    FinishExchange none;
+    const FinishExchange& f = fx ? *fx : none;
+    if (vec)
+      reduce_col_fused_f32_kernel<Op, true><<<grid, block, 0, s>>>(x, partial, out, red, inner, rows_per_split, tickets, f);
+    else
+      reduce_col_fused_f32_kernel<Op, false><<<grid, block, 0, s>>>(x, partial, out, red, inner, rows_per_split, tickets, f);
+    return cudaGetLastError();
+  }
+  if (vec)
     reduce_col_f32_kernel<Op, true><<<grid, block, 0, s>>>(x, partial, red, inner, rows_per_split);
   else
     reduce_col_f32_kernel<Op, false><<<grid, block, 0, s>>>(x, partial, red, inner, rows_per_split);
@@ -276,7 +567,8 @@ cudaError_t col_impl(const float* x, float* out, int64_t red, int64_t inner, voi
 }
 
 template <class Op>
-cudaError_t all_impl(const float* x, float* out, int64_t n, void* ws, int sm_count, cudaStream_t s, LaunchDims* dims) {
+cudaError_t all_impl(const float* x, float* out, int64_t n, void* ws, int sm_count, cudaStream_t s, LaunchDims* dims,
+                     uint32_t* tickets, const FinishExchange* fx) {
   const int64_t want = (n / 4 + 255) / 256;
   static const int per_sm = std::min(8, resident_ctas_per_sm(reduce_all_f32_kernel<Op, true>, 256));
   const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)sm_count * per_sm));
@@ -285,6 +577,14 @@ cudaError_t all_impl(const float* x, float* out, int64_t n, void* ws, int sm_cou
     dims->block[0] = 256;
   }
   float* partial = reinterpret_cast<float*>(ws);
+  if (fx && fx->world > 1 && !tickets) return cudaErrorNotSupported;
+  if (tickets) {
+    FinishExchange none;
+    const FinishExchange& f = fx ? *fx : none;
+    if (aligned16(x)) reduce_all_fused_f32_kernel<Op, true><<<grid, 256, 0, s>>>(x, partial, out, n, tickets, f);
+    else reduce_all_fused_f32_kernel<Op, false><<<grid, 256, 0, s>>>(x, partial, out, n, tickets, f);
+    return cudaGetLastError();
+  }
   if (aligned16(x)) reduce_all_f32_kernel<Op, true><<<grid, 256, 0, s>>>(x, partial, n);
   else reduce_all_f32_kernel<Op, false><<<grid, 256, 0, s>>>(x, partial, n);
   cudaError_t e = cudaGetLastError();
@@ -315,11 +615,18 @@ size_t reduce_col_workspace(int64_t red, int64_t inner, int sm_count) {
   return splits == 1 ? 0 : (size_t)(splits * inner) * sizeof(float);
 }
 size_t reduce_all_workspace(int sm_count) { return (size_t)sm_count * 8 * sizeof(float); }
+bool reduce_col_fusable(int64_t red, int64_t inner, int sm_count) {
+  return col_row_splits(red, inner, sm_count) > 1 && (inner + kColTile - 1) / kColTile <= kReduceMaxTicketTiles;
+}
+int reduce_col_launches(int64_t red, int64_t inner, int sm_count, bool tickets) {
+  if (col_row_splits(red, inner, sm_count) == 1) return 1;
+  return tickets && reduce_col_fusable(red, inner, sm_count) ? 1 : 2;
+}
 
 namespace {
 template <class Op1, class Op2>
 cudaError_t dual_impl(const float* x, float* out1, float* out2, int64_t red, int64_t inner, void* ws, int sm_count,
-                      cudaStream_t s, LaunchDims* dims) {
+                      cudaStream_t s, LaunchDims* dims, uint32_t* tickets, const FinishExchange* fx) {
   const int64_t splits = col_row_splits(red, inner, sm_count);
   const int64_t rows_per_split = (red + splits - 1) / splits;
   dim3 grid((unsigned)((inner + kColTile - 1) / kColTile), (unsigned)splits), block(kColTx, kColTy);
@@ -332,6 +639,14 @@ cudaError_t dual_impl(const float* x, float* out1, float* out2, int64_t red, int
   }
   float* partial = reinterpret_cast<float*>(ws);
   float* partial2 = partial + splits * inner;
+  const bool fused = tickets && grid.x <= (unsigned)kReduceMaxTicketTiles;
+  if (fx && fx->world > 1 && !fused) return cudaErrorNotSupported;
+  if (fused) {
+    FinishExchange none;
+    reduce_col_dual_fused_f32_kernel<Op1, Op2><<<grid, block, 0, s>>>(x, partial, partial2, out1, out2, red, inner,
+                                                                      rows_per_split, tickets, fx ? *fx : none);
+    return cudaGetLastError();
+  }
   reduce_col_dual_f32_kernel<Op1, Op2><<<grid, block, 0, s>>>(x, partial, partial2, red, inner, rows_per_split);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
@@ -343,12 +658,12 @@ cudaError_t dual_impl(const float* x, float* out1, float* out2, int64_t red, int
 }
 template <class Op1>
 cudaError_t dual_pick(RedOp op2, const float* x, float* o1, float* o2, int64_t red, int64_t inner, void* ws, int sms,
-                      cudaStream_t s, LaunchDims* dims) {
+                      cudaStream_t s, LaunchDims* dims, uint32_t* tk, const FinishExchange* fx) {
   switch (op2) {
-    case RedOp::Sum: return dual_impl<Op1, SumOp>(x, o1, o2, red, inner, ws, sms, s, dims);
-    case RedOp::Max: return dual_impl<Op1, MaxOp>(x, o1, o2, red, inner, ws, sms, s, dims);
-    case RedOp::Min: return dual_impl<Op1, MinOp>(x, o1, o2, red, inner, ws, sms, s, dims);
-    case RedOp::Prod: return dual_impl<Op1, ProdOp>(x, o1, o2, red, inner, ws, sms, s, dims);
+    case RedOp::Sum: return dual_impl<Op1, SumOp>(x, o1, o2, red, inner, ws, sms, s, dims, tk, fx);
+    case RedOp::Max: return dual_impl<Op1, MaxOp>(x, o1, o2, red, inner, ws, sms, s, dims, tk, fx);
+    case RedOp::Min: return dual_impl<Op1, MinOp>(x, o1, o2, red, inner, ws, sms, s, dims, tk, fx);
+    case RedOp::Prod: return dual_impl<Op1, ProdOp>(x, o1, o2, red, inner, ws, sms, s, dims, tk, fx);
   }
   return cudaErrorInvalidValue;
 }
@@ -363,12 +678,13 @@ size_t reduce_col_dual_workspace(int64_t red, int64_t inner, int sm_count) {
   return (size_t)(splits * inner + ctas) * sizeof(float);
 }
 cudaError_t reduce_col_dual_f32(RedOp op1, RedOp op2, const float* x, float* out1, float* out2, int64_t red,
-                                int64_t inner, void* ws, int sm_count, cudaStream_t s, LaunchDims* dims) {
+                                int64_t inner, void* ws, int sm_count, cudaStream_t s, LaunchDims* dims,
+                                uint32_t* tickets, const FinishExchange* fx) {
   switch (op1) {
-    case RedOp::Sum: return dual_pick<SumOp>(op2, x, out1, out2, red, inner, ws, sm_count, s, dims);
-    case RedOp::Max: return dual_pick<MaxOp>(op2, x, out1, out2, red, inner, ws, sm_count, s, dims);
-    case RedOp::Min: return dual_pick<MinOp>(op2, x, out1, out2, red, inner, ws, sm_count, s, dims);
-    case RedOp::Prod: return dual_pick<ProdOp>(op2, x, out1, out2, red, inner, ws, sm_count, s, dims);
+    case RedOp::Sum: return dual_pick<SumOp>(op2, x, out1, out2, red, inner, ws, sm_count, s, dims, tickets, fx);
+    case RedOp::Max: return dual_pick<MaxOp>(op2, x, out1, out2, red, inner, ws, sm_count, s, dims, tickets, fx);
+    case RedOp::Min: return dual_pick<MinOp>(op2, x, out1, out2, red, inner, ws, sm_count, s, dims, tickets, fx);
+    case RedOp::Prod: return dual_pick<ProdOp>(op2, x, out1, out2, red, inner, ws, sm_count, s, dims, tickets, fx);
   }
   return cudaErrorInvalidValue;
 }
@@ -383,12 +699,12 @@ cudaError_t reduce_col_dual_f32(RedOp op1, RedOp op2, const float* x, float* out
   return cudaErrorInvalidValue;
 
 cudaError_t reduce_col_f32(RedOp op, const float* x, float* out, int64_t red, int64_t inner, void* ws, int sm_count,
-                           cudaStream_t s, LaunchDims* dims) {
-  AKGB_DISPATCH(col_impl, x, out, red, inner, ws, sm_count, s, dims)
+                           cudaStream_t s, LaunchDims* dims, uint32_t* tickets, const FinishExchange* fx) {
+  AKGB_DISPATCH(col_impl, x, out, red, inner, ws, sm_count, s, dims, tickets, fx)
 }
 cudaError_t reduce_all_f32(RedOp op, const float* x, float* out, int64_t n, void* ws, int sm_count, cudaStream_t s,
-                           LaunchDims* dims) {
-  AKGB_DISPATCH(all_impl, x, out, n, ws, sm_count, s, dims)
+                           LaunchDims* dims, uint32_t* tickets, const FinishExchange* fx) {
+  AKGB_DISPATCH(all_impl, x, out, n, ws, sm_count, s, dims, tickets, fx)
 }
 cudaError_t reduce_row_f32(RedOp op, const float* x, float* out, int64_t rows, int64_t cols, cudaStream_t s,
                            LaunchDims* dims) {

@@ -57,19 +57,41 @@ cudaError_t softmax_rows(const SoftmaxParams& p, const void* x, const void* mask
                          cudaStream_t s, LaunchDims* dims);
 
 // ---- reductions ----------------------------------------------------------------
-// x[outer, red, inner] -> out[outer, inner]; f32 only.
+// A reduction whose per-CTA partials are folded by the CTA that finishes last ("finisher": one per column tile, one for
+// a reduction of all elements) needs no second launch.  The finishers are found with arrival counters (`tickets`,
+// kReduceTicketWords zero-initialised words that every launch leaves at zero again; launches that share them must be
+// ordered on the device).  With an exchange attached, each finisher also completes the all-reduce of its values over
+// the ranks' mapped exchange buffers (layout below): peer stores, a flag per finisher, a bounded wait, a fold in rank
+// order.  The result is written by the finisher, so a sharded reduction is ONE launch on every rank.
+constexpr int kReduceMaxTicketTiles = 4096;
+constexpr int kReduceTicketWords = kReduceMaxTicketTiles + 8;
+struct FinishExchange {
+  void* peer[8] = {};           // every rank's exchange buffer as mapped here; peer[rank] is this rank's own
+  int rank = 0, world = 1;      // world == 1: no exchange
+  long long limit_cycles = 0;   // bound of the wait for the peers' flags
+  uint32_t* err = nullptr;      // device error word (bit 8: the wait ran out)
+  int slot_off = 0;             // slot position of the first output's first element
+  int slot_off2 = 0;            // slot position of the second output (column + all-elements kernel)
+  int finishers = 0;            // finishers of the launch: the last one closes the call
+};
+// x[outer, red, inner] -> out[outer, inner]; f32 only.  With `tickets` the fold of the row splits happens in the same
+// launch (see above); `fx` (needs `tickets`, several row splits and reduce_col_fusable()) adds the exchange.
 size_t reduce_col_workspace(int64_t red, int64_t inner, int sm_count);
+bool reduce_col_fusable(int64_t red, int64_t inner, int sm_count);
+int reduce_col_launches(int64_t red, int64_t inner, int sm_count, bool tickets);
 cudaError_t reduce_col_f32(RedOp op, const float* x, float* out, int64_t red, int64_t inner, void* ws, int sm_count,
-                           cudaStream_t s, LaunchDims* dims);
+                           cudaStream_t s, LaunchDims* dims, uint32_t* tickets = nullptr,
+                           const FinishExchange* fx = nullptr);
 // one pass over x: column reduction with op1 into out1[inner] and reduction of all elements with op2 into out2[1]
 // (inner % 4 == 0, x 16-byte aligned)
 bool reduce_col_dual_supported(int64_t inner, const void* x);
 size_t reduce_col_dual_workspace(int64_t red, int64_t inner, int sm_count);
 cudaError_t reduce_col_dual_f32(RedOp op1, RedOp op2, const float* x, float* out1, float* out2, int64_t red,
-                                int64_t inner, void* ws, int sm_count, cudaStream_t s, LaunchDims* dims);
+                                int64_t inner, void* ws, int sm_count, cudaStream_t s, LaunchDims* dims,
+                                uint32_t* tickets = nullptr, const FinishExchange* fx = nullptr);
 size_t reduce_all_workspace(int sm_count);
 cudaError_t reduce_all_f32(RedOp op, const float* x, float* out, int64_t n, void* ws, int sm_count, cudaStream_t s,
-                           LaunchDims* dims);
+                           LaunchDims* dims, uint32_t* tickets = nullptr, const FinishExchange* fx = nullptr);
 cudaError_t reduce_row_f32(RedOp op, const float* x, float* out, int64_t rows, int64_t cols, cudaStream_t s,
                            LaunchDims* dims);
 
@@ -97,10 +119,13 @@ cudaError_t ew_jit_launch(const EwProgram& p, const void* const* in, void* const
 
 // ---- exchange over peer memory -----------------------------------------------------------------
 // Layout of one rank's exchange buffer: [2 parities][kExchangeMaxRanks slots][kExchangeSlotElems floats], then the flags
-// [2][kExchangeMaxRanks][kExchangeMaxCtas] uint32.
-constexpr int kExchangeMaxRanks = 8, kExchangeSlotElems = 16384, kExchangeMaxCtas = 16;
+// [2][kExchangeMaxRanks][kExchangeMaxFlags] uint32.
+// kExchangeMaxFlags flags per (parity, rank): the stand-alone exchange kernel raises one per CTA (at most
+// kExchangeMaxCtas), a reduction that carries its own exchange one per finisher (a column tile of 128 values, or the
+// single result of a reduction of all elements).
+constexpr int kExchangeMaxRanks = 8, kExchangeSlotElems = 16384, kExchangeMaxCtas = 16, kExchangeMaxFlags = 136;
 constexpr size_t kExchangeDataBytes = (size_t)2 * kExchangeMaxRanks * kExchangeSlotElems * sizeof(float);
-constexpr size_t kExchangeFlagBytes = (size_t)2 * kExchangeMaxRanks * kExchangeMaxCtas * sizeof(uint32_t);
+constexpr size_t kExchangeFlagBytes = (size_t)2 * kExchangeMaxRanks * kExchangeMaxFlags * sizeof(uint32_t);
 // after the flags: the call counter (epoch) and the ticket that lets the last CTA of a call advance it
 constexpr size_t kExchangeBytes = kExchangeDataBytes + kExchangeFlagBytes + 2 * sizeof(uint32_t);
 __host__ __device__ inline float* exchange_slot(void* base, int parity, int rank) {
@@ -108,7 +133,7 @@ __host__ __device__ inline float* exchange_slot(void* base, int parity, int rank
 }
 __host__ __device__ inline uint32_t* exchange_flag(void* base, int parity, int rank, int cta) {
   return reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(base) + kExchangeDataBytes) +
-         ((size_t)parity * kExchangeMaxRanks + rank) * kExchangeMaxCtas + cta;
+         ((size_t)parity * kExchangeMaxRanks + rank) * kExchangeMaxFlags + cta;
 }
 __host__ __device__ inline uint32_t* exchange_counter(void* base) {
   return reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(base) + kExchangeDataBytes + kExchangeFlagBytes);
@@ -127,10 +152,21 @@ struct ExchangeArgs {
 constexpr int kExchangeMaxSegs = 4;
 cudaError_t exchange_allreduce(const ExchangeArgs& a, cudaStream_t s);
 }  // namespace akgb
-struct akgb_kernel;
+#include "../../include/akgb.h"
 namespace akgb {
+// A bounded wait of a peer-memory exchange ran out on this device (seen by akgb_check_device_error): the ranks' call
+// counters may disagree from here on, so further peer-memory exchanges are refused until the caller turns the path on
+// again on all ranks (akgb_comm_set_peer_exchange), which also restarts the counters.
+bool device_exchange_failed(int device);
+void device_exchange_set_failed(int device, bool failed);
 // the device error word of the kernel's device (allocated on first use); nullptr on failure
 uint32_t* kernel_error_word(akgb_kernel* k);
+// Sharded launch whose reduction completes the exchange itself: if the kernel's partial outputs all come from one
+// reduction step that can do so, launches the plan with `base` (peers, rank, world, wait limit) attached and sets
+// *fused; otherwise launches nothing and leaves *fused false.
+bool kernel_exchange_fusable(const akgb_kernel* k);
+akgb_status launch_with_exchange(akgb_kernel* k, const FinishExchange& base, void* const* tensors, void* workspace,
+                                 size_t workspace_bytes, void* stream, bool* fused);
 
 // ---- index ops ---------------------------------------------------------------------
 // out[o, i, r] = data[o, idx[i], r]; data is [outer, dim, inner] elements of `esize` bytes; idx int32 or int64

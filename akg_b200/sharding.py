@@ -89,6 +89,18 @@ class Communicator:
         _capi.check(self._lib.akgb_comm_set_peer_exchange(self._handle, 0))
         self.peer_exchange = False
 
+    def restart_peer_exchange(self):
+        """After a bounded wait ran out (AKGB_DEVICE_TIMEOUT): clears the refusal and restarts the call counters.
+        Every rank must call it, and the ranks must synchronise before their next sharded launch."""
+        _capi.check(self._lib.akgb_comm_set_peer_exchange(self._handle, 1))
+        self.peer_exchange = True
+
+    def exchange_kind(self, kernel) -> str:
+        """How the partial outputs of `kernel` travel with this communicator as it is set up now:
+        'none', 'nccl', 'peer-kernel' (one exchange kernel after the launch) or 'in-reduction' (the reduction's own
+        launch completes the exchange)."""
+        return _capi.EXCHANGE_NAMES[int(self._lib.akgb_sharded_exchange_kind(kernel._handle, self._handle))]
+
     def set_timeout_ms(self, ms: float):
         _capi.check(self._lib.akgb_comm_set_timeout_ms(self._handle, float(ms)))
 

@@ -114,7 +114,12 @@ int32_t akgb_launch_count(const akgb_kernel* k);
  * are DEVICE pointers, inputs then outputs.  `workspace` must hold at least
  * akgb_workspace_size() bytes (may be NULL when that is 0).  Asynchronous.
  * Replaces cuLaunchKernel of the generated kernel
- * (python/akg_mlir/utils/code_template.py:204). */
+ * (python/akg_mlir/utils/code_template.py:204).
+ * The calling thread's current CUDA device must be the one the kernel was compiled for (akgb_options.device):
+ * otherwise AKGB_INVALID_ARG, nothing is launched.  The same holds for akgb_launch_dynamic, akgb_launch_sharded and
+ * akgb_allreduce_partials; akgb_run_host, akgb_profile_host and akgb_prepare select the kernel's device themselves
+ * and leave it current.  Launches of ONE kernel object must be ordered on the device (one stream, or events between
+ * streams): the object owns small device-side arrival counters that its reductions share. */
 akgb_status akgb_launch(akgb_kernel* k, void* const* tensors, void* workspace,
                         size_t workspace_bytes, void* stream);
 
@@ -199,9 +204,22 @@ akgb_status akgb_comm_set_timeout_ms(akgb_comm* c, double ms);
 /* All-reduces, in place and on `stream`, every tensor of `tensors` (inputs then outputs, device pointers) whose
  * shard_kind is a partial; one NCCL group for all of them.  No-op for kernels without partial outputs. */
 akgb_status akgb_allreduce_partials(const akgb_kernel* k, akgb_comm* c, void* const* tensors, void* stream);
-/* akgb_launch followed by akgb_allreduce_partials on the same stream. */
+/* The kernel and the exchange of its partial outputs on one stream.  Where ONE reduction (column, all-elements, or both
+ * in one pass) produces all partial outputs and the peers' buffers are attached, the reduction completes the exchange in
+ * its own launch: the CTA that folds a tile of the result stores it into every rank's buffer, waits (bounded) for the
+ * other ranks' tiles and folds them in rank order -- one kernel per rank and step.  Otherwise: akgb_launch followed by
+ * akgb_allreduce_partials.  After a sharded step every rank should read akgb_check_device_error: once a bounded wait has
+ * run out on a device (AKGB_DEVICE_TIMEOUT, bit 8), further peer-memory exchanges there are refused with
+ * AKGB_DEVICE_TIMEOUT until akgb_comm_set_peer_exchange has been called on ALL ranks (1: restart the path, 0: continue
+ * over NCCL) and the ranks have synchronised. */
 akgb_status akgb_launch_sharded(akgb_kernel* k, akgb_comm* c, void* const* tensors, void* workspace,
                                 size_t workspace_bytes, void* stream);
+/* Which way the partial outputs of `k` travel with communicator `c` as it is set up now. */
+#define AKGB_EXCHANGE_NONE 0          /* no partial outputs, or a single rank */
+#define AKGB_EXCHANGE_NCCL 1          /* ncclAllReduce after the kernel */
+#define AKGB_EXCHANGE_PEER_KERNEL 2   /* one exchange kernel over the ranks' mapped buffers after the kernel */
+#define AKGB_EXCHANGE_IN_REDUCTION 3  /* inside the reduction's own launch (see akgb_launch_sharded) */
+int32_t akgb_sharded_exchange_kind(const akgb_kernel* k, const akgb_comm* c);
 
 /* Directory of the on-disk cache of run-time compiled kernels.  The reference keeps its compiled kernels
  * (<kernel>.ptx / .json) under KERNEL_META_DIR and reuses them by name (python/akg_mlir/mlir_driver.py:47-53,
@@ -240,6 +258,8 @@ akgb_status akgb_check_device_error(akgb_kernel* k, uint32_t* word);
  *     that first call outside any stream capture.  The current device must be the one holding x/out.
  *   - All calls on a device share the array: issue them so that their kernels do not overlap on the
  *     GPU (same stream, or ordered by events).  No clearing is needed between calls.
+ *   - The address found by the first call is kept per device ordinal for the life of the process; it
+ *     does not survive cudaDeviceReset (do not call this entry point again after one).
  * Results are bit-identical to akgb_launch of the same ReduceSum(axis 0) description. */
 akgb_status akgb_reduce_sum_axis0_f32_noalloc(const float* x, float* out, int64_t rows, int64_t cols, void* stream);
 

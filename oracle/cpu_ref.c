@@ -54,6 +54,16 @@ int akg_ref_num_threads(void) {
 #endif
 }
 
+/* Thread count of the parallel variants; a launcher may have exported OMP_NUM_THREADS=1 for its workers, which the
+ * timed baseline must not inherit.  Returns the count now in effect. */
+int akg_ref_set_num_threads(int n) {
+#ifdef _OPENMP
+  extern void omp_set_num_threads(int);
+  if (n > 0) omp_set_num_threads(n);
+#endif
+  return akg_ref_num_threads();
+}
+
 /* ---- LayerNorm: tensors = {x, gamma, beta, y, mean, var}; dims = {rows, cols}; scal = {1/N, eps} */
 static void layernorm_row(const float* x, const float* g, const float* b, float* y, float* mean, float* var, int64_t r,
                           int64_t cols, float inv_n, float eps) {

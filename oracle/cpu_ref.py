@@ -32,6 +32,16 @@ def num_threads() -> int:
     return int(load().akg_ref_num_threads())
 
 
+def use_all_host_threads() -> int:
+    """Sets the OpenMP thread count to the cores this process may run on (not to an inherited OMP_NUM_THREADS)."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    fn = load().akg_ref_set_num_threads
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_int]
+    return int(fn(n))
+
+
 def call(name: str, tensors, dims, scal=(), variant: str = "r1"):
     """Runs ``akg_ref_<name>_<variant>(void** tensors, const int64_t* dims, const double* scal)``."""
     fn = getattr(load(), f"akg_ref_{name}_{variant}")

@@ -243,7 +243,7 @@ def test_planning_of_generated_kernels_needs_no_device(lib):
     kc = FusedKernel(descs.mul_reduce_sum(4096, 512, [0]))
     assert kc.meta()["template"] == "akgb_col_jit" and "akgb_col_jit" in kc.jit_source()
     ka = FusedKernel(descs.mul_reduce_sum(4096, 512, [0, 1]))
-    assert ka.meta()["template"] == "akgb_row_jit" and "C = 4096" in ka.jit_source() and ka.launch_count == 3
+    assert ka.meta()["template"] == "akgb_row_jit" and "C = 4096" in ka.jit_source() and ka.launch_count == 2
     # small tensors are not worth a generated reduction kernel
     assert FusedKernel(descs.mul_reduce_sum(64, 64, [0])).meta()["template"] != "akgb_col_jit"
 

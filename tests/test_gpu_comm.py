@@ -81,6 +81,29 @@ def test_peer_memory_exchange_on_one_rank_and_its_bounded_wait():
     status = lib.akgb_check_device_error(k._handle, ctypes.byref(word))
     assert status == _capi.AKGB_DEVICE_TIMEOUT and word.value & 256
     torch.testing.assert_close(out2.double().cpu(), want, rtol=1e-5, atol=1e-4)  # the partial, not folded
+    assert lonely.exchange_kind(k) == "in-reduction"  # the reduction's own launch carried (and bounded) the exchange
+    # once a wait has run out the ranks' call counters may disagree: further exchanges of a multi-rank communicator on
+    # this device are refused until the path is restarted (on all ranks)
+    with pytest.raises(_capi.AkgbError) as refused:
+        lonely.launch_sharded(k, [x, out2])
+    assert refused.value.status == _capi.AKGB_DEVICE_TIMEOUT
+    lonely.restart_peer_exchange()
+    lonely.launch_sharded(k, [x, out2])  # accepted again (and, with nobody playing rank 1, runs out again)
+    torch.cuda.synchronize()
+    status = lib.akgb_check_device_error(k._handle, ctypes.byref(word))
+    assert status == _capi.AKGB_DEVICE_TIMEOUT and word.value & 256
+    lonely.disable_peer_exchange()  # clears the refusal as well
+    # the same bound inside the exchange kernel that runs after a launch (two reductions produce the partials)
+    lonely.restart_peer_exchange()
+    kb = FusedKernel(descs.layer_norm_backward(512, 256), device=0, shard_rank=0, shard_world=2)
+    assert lonely.exchange_kind(kb) == "peer-kernel"
+    ins_b = [torch.randn(t.shape, device="cuda") for t in kb.inputs]
+    outs_b = [torch.empty(t.shape, device="cuda") for t in kb.outputs]
+    lonely.launch_sharded(kb, ins_b + outs_b)
+    torch.cuda.synchronize()
+    status = lib.akgb_check_device_error(kb._handle, ctypes.byref(word))
+    assert status == _capi.AKGB_DEVICE_TIMEOUT and word.value & 256
+    lonely.disable_peer_exchange()
     # the device and the library keep working
     solo.launch_sharded(k, [x, out])
     torch.cuda.synchronize()
