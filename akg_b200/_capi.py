@@ -35,6 +35,7 @@ EXCHANGE_NAMES = {0: "none", 1: "nccl", 2: "peer-kernel", 3: "in-reduction"}
 
 AKGB_MAX_RANK = 8
 AKGB_FLAG_NO_JIT = 1
+AKGB_FLAG_FOLD_IN_LAUNCH = 2
 
 
 class TensorDesc(ctypes.Structure):
@@ -109,6 +110,7 @@ _SIGNATURES = [
     ("akgb_comm_exchange_handle", ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]),
     ("akgb_comm_attach_peers", ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]),
     ("akgb_comm_set_timeout_ms", ctypes.c_int, [ctypes.c_void_p, ctypes.c_double]),
+    ("akgb_comm_set_exchange_in_reduction", ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32]),
     ("akgb_allreduce_partials", ctypes.c_int, [_vp, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]),
     ("akgb_launch_sharded", ctypes.c_int, [_vp, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p,
                                            ctypes.c_size_t, ctypes.c_void_p]),

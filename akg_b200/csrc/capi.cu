@@ -62,6 +62,7 @@ struct akgb_kernel {
   int sm_count = 148;
   int shard_rank = 0, shard_world = 1;
   bool no_jit = false;  // AKGB_FLAG_NO_JIT
+  bool fold_in_launch = false;  // AKGB_FLAG_FOLD_IN_LAUNCH
   // dynamic-shape regions: one plan per set of launch-time extents
   struct Bound {
     Graph graph;
@@ -175,6 +176,8 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
   for (size_t si = 0; si < plan.steps.size(); ++si) {
     Step& st = plan.steps[si];
     const FinishExchange* sfx = ((int)si == fx_step) ? fx : nullptr;
+    // arrival counters: the reduction folds its partials itself (always when it carries an exchange)
+    uint32_t* tickets = (k->fold_in_launch || sfx) ? k->d_tickets : nullptr;
     cudaError_t e = cudaSuccess;
     void* a = resolve(st.a, tensors, ws);
     void* b = resolve(st.b, tensors, ws);
@@ -197,7 +200,7 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
       case StepK::ReduceCol:
         for (int64_t bi = 0; bi < st.red_outer && e == cudaSuccess; ++bi)
           e = reduce_col_f32(st.red_op, (const float*)a + bi * st.red_batch_in, (float*)o + bi * st.red_batch_out,
-                             st.red_len, st.red_inner, scratch, k->sm_count, s, &st.dims, k->d_tickets, sfx);
+                             st.red_len, st.red_inner, scratch, k->sm_count, s, &st.dims, tickets, sfx);
         break;
       case StepK::Gather:
         e = gather_rows(a, b, o, st.ix_outer, st.ix_dim, st.ix_n, st.ix_inner, st.ix_esize, st.ix_idx64, s, &st.dims);
@@ -247,20 +250,20 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
       case StepK::ReduceColDual:
         if (reduce_col_dual_supported(st.red_inner, a)) {
           e = reduce_col_dual_f32(st.red_op, st.red_op2, (const float*)a, (float*)o, (float*)o2, st.red_len, st.red_inner,
-                                  scratch, k->sm_count, s, &st.dims, k->d_tickets, sfx);
+                                  scratch, k->sm_count, s, &st.dims, tickets, sfx);
         } else if (sfx) {
           e = cudaErrorNotSupported;  // fused_exchange_step() only picks aligned inputs
         } else {  // unaligned input: the two single reductions, one after the other
           e = reduce_col_f32(st.red_op, (const float*)a, (float*)o, st.red_len, st.red_inner, scratch, k->sm_count, s,
-                             &st.dims, k->d_tickets);
+                             &st.dims, tickets);
           if (e == cudaSuccess)
             e = reduce_all_f32(st.red_op2, (const float*)a, (float*)o2, st.red_len * st.red_inner, scratch, k->sm_count, s,
-                               nullptr, k->d_tickets);
+                               nullptr, tickets);
         }
         break;
       case StepK::ReduceAll:
         e = reduce_all_f32(st.red_op, (const float*)a, (float*)o, st.red_len, scratch, k->sm_count, s, &st.dims,
-                           k->d_tickets, sfx);
+                           tickets, sfx);
         break;
       case StepK::ReduceRow:
         e = reduce_row_f32(st.red_op, (const float*)a, (float*)o, st.red_outer, st.red_len, s, &st.dims);
@@ -292,13 +295,13 @@ int launches_of(const akgb_kernel* k) {
   for (const Step& st : active_plan(k).steps) {
     switch (st.kind) {
       case StepK::ReduceCol:  // the fold of the row splits happens in the launch that produced them
-        n += (int)st.red_outer * reduce_col_launches(st.red_len, st.red_inner, k->sm_count, true);
+        n += (int)st.red_outer * reduce_col_launches(st.red_len, st.red_inner, k->sm_count, k->fold_in_launch);
         break;
       case StepK::ReduceAll:
-        n += 1;
+        n += k->fold_in_launch ? 1 : 2;
         break;
       case StepK::ReduceColDual:
-        n += (st.red_inner + 127) / 128 <= kReduceMaxTicketTiles ? 1 : 3;
+        n += (k->fold_in_launch && (st.red_inner + 127) / 128 <= kReduceMaxTicketTiles) ? 1 : 3;
         break;
       case StepK::GeluChain:
         n += (st.gelu.n % 8) ? 2 : 1;
@@ -548,6 +551,7 @@ akgb_status akgb_compile(const char* info_json, size_t len, const akgb_options* 
     k->shard_rank = rank;
     k->shard_world = world;
     k->no_jit = (flags & AKGB_FLAG_NO_JIT) != 0;
+    k->fold_in_launch = (flags & AKGB_FLAG_FOLD_IN_LAUNCH) != 0;
     k->json_text.assign(info_json, len);
     k->graph = parse_info(info_json, len);
     if (k->graph.dynamic) {

@@ -97,6 +97,7 @@ struct akgb_comm {
   void* local_buf = nullptr;               // this rank's exchange buffer (cudaMalloc)
   void* peer_buf[kExchangeMaxRanks] = {};  // every rank's buffer as mapped into this process
   bool peers_ready = false;
+  bool in_reduction = true;                // reductions complete the exchange in their own launch where they can
   double timeout_ms = 1000.0;
   int clock_khz = 0;
 };
@@ -297,6 +298,15 @@ akgb_status akgb_comm_set_peer_exchange(akgb_comm* c, int32_t enabled) {
   return AKGB_OK;
 }
 
+akgb_status akgb_comm_set_exchange_in_reduction(akgb_comm* c, int32_t enabled) {
+  if (!c) {
+    set_last_error("akgb_comm_set_exchange_in_reduction: null communicator");
+    return AKGB_INVALID_ARG;
+  }
+  c->in_reduction = enabled != 0;
+  return AKGB_OK;
+}
+
 akgb_status akgb_comm_set_timeout_ms(akgb_comm* c, double ms) {
   if (!c || !(ms > 0.0)) {
     set_last_error("akgb_comm_set_timeout_ms: bad arguments");
@@ -345,7 +355,7 @@ int32_t akgb_sharded_exchange_kind(const akgb_kernel* k, const akgb_comm* c) {
   }
   if (!any) return AKGB_EXCHANGE_NONE;
   if (!c->peers_ready) return AKGB_EXCHANGE_NCCL;
-  if (kernel_exchange_fusable(k)) return AKGB_EXCHANGE_IN_REDUCTION;
+  if (c->in_reduction && kernel_exchange_fusable(k)) return AKGB_EXCHANGE_IN_REDUCTION;
   return all_small_f32 && total <= (size_t)kExchangeSlotElems && segs <= kExchangeMaxSegs ? AKGB_EXCHANGE_PEER_KERNEL
                                                                                          : AKGB_EXCHANGE_NCCL;
 }
@@ -430,7 +440,7 @@ akgb_status akgb_launch_sharded(akgb_kernel* k, akgb_comm* c, void* const* tenso
     set_last_error("akgb_launch_sharded: null argument");
     return AKGB_INVALID_ARG;
   }
-  if (c->world > 1 && c->peers_ready) {
+  if (c->world > 1 && c->peers_ready && c->in_reduction) {
     const akgb_status rs = refuse_after_timeout(c);
     if (rs != AKGB_OK) return rs;
     // a reduction that produces all the partial outputs completes their exchange in its own launch

@@ -527,28 +527,40 @@ void infer_sharding(Graph& g, int rank, int world) {
       lead = vid;
   }
   if (lead < 0) throw Unsupported("sharding needs at least one tensor input");
-  const int64_t S = g.v(lead).shape[0];
-  const size_t R = g.v(lead).shape.size();
+  int64_t S = g.v(lead).shape[0];
+  size_t R = g.v(lead).shape.size();
+
+  // With a (Batch)MatMul in the region the split axis is axis 0 of its LEFT operand: the rows of a MatMul, the batch
+  // of a BatchMatMul.  Values that reach a right operand which does not carry that batch (the 2-D weight of a MatMul,
+  // a BatchMatMul's shared right operand) stay whole on every rank, whatever their extents happen to be.
+  bool has_matmul = false;
+  std::vector<char> shared_rhs(g.values.size(), 0);
+  for (auto& n : g.nodes) {
+    if (n.kind != OpK::MatMul && n.kind != OpK::BatchMatMul) continue;
+    if (!has_matmul) {
+      S = g.v(n.in[0]).shape[0];
+      R = g.v(n.in[0]).shape.size();
+      has_matmul = true;
+    }
+    const Value& b = g.v(n.in[1]);
+    const bool batched_rhs = n.kind == OpK::BatchMatMul && b.shape.size() >= 3 && b.shape.size() == R && b.shape[0] == S;
+    if (!batched_rhs) shared_rhs[n.in[1]] = 1;
+  }
+  if (has_matmul)
+    for (size_t i = g.nodes.size(); i-- > 0;)
+      if (shared_rhs[g.nodes[i].out])
+        for (int vid : g.nodes[i].in) shared_rhs[vid] = 1;
   if (S % world != 0) throw Unsupported("leading extent is not divisible by shard_world");
   const int64_t Sl = S / world;
-
-  bool has_matmul = false;
-  for (auto& n : g.nodes)
-    if (n.kind == OpK::MatMul || n.kind == OpK::BatchMatMul) has_matmul = true;
 
   auto mark = [&](Value& v) {
     v.split0 = true;
     v.shape[0] = Sl;
   };
-  if (has_matmul) {
-    // only the left operand's rows (M) are split; everything the matmul result
-    // meets afterwards is split iff it has full rank and S leading rows
-    mark(g.v(lead));
-  } else {
-    for (int vid : g.inputs) {
-      Value& v = g.v(vid);
-      if (v.shape.size() == R && v.shape[0] == S) mark(v);
-    }
+  for (int vid : g.inputs) {
+    Value& v = g.v(vid);
+    if (has_matmul && shared_rhs[vid]) continue;
+    if (v.shape.size() == R && v.shape[0] == S) mark(v);
   }
   for (auto& n : g.nodes) {
     Value& out = g.v(n.out);
@@ -597,7 +609,15 @@ void infer_sharding(Graph& g, int rank, int world) {
       }
     } else if (n.kind == OpK::MatMul || n.kind == OpK::BatchMatMul) {
       if (n.transpose_a) throw Unsupported("transpose_a matmul cannot be split on rows");
-      if (g.v(n.in[1]).split0 && n.kind == OpK::MatMul) throw Unsupported("right matmul operand is split");
+      const Value& lhs = g.v(n.in[0]);
+      const Value& rhs = g.v(n.in[1]);
+      if (!lhs.split0) throw Unsupported("the left matmul operand is not split over the ranks");
+      if (rhs.split0 && n.kind == OpK::MatMul) throw Unsupported("right matmul operand is split");
+      if (n.kind == OpK::BatchMatMul && rhs.shape.size() >= 3) {
+        // a batched right operand must carry this rank's batch entries, like the left one
+        if (!rhs.split0 || rhs.shape[0] != lhs.shape[0])
+          throw Unsupported("the batched right operand of a BatchMatMul is not split like the left one");
+      }
       mark(out);
     } else if (n.kind == OpK::BroadcastTo) {
       mark(out);

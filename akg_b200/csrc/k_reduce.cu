@@ -313,17 +313,16 @@ __device__ __forceinline__ bool finish_exchange(const FinishExchange& fx, float&
 // arrives last.  The caller has written its partials before the call; the last CTA may read everybody's afterwards.
 __device__ __forceinline__ bool arrive_last(uint32_t* ticket, unsigned expected, int tid) {
   __shared__ int last;
-  __threadfence();
-  __syncthreads();
+  __syncthreads();  // every thread's partials are ordered before thread 0's fence (the fence is cumulative)
   if (tid == 0) {
+    __threadfence();
     const unsigned t = atomicAdd(ticket, 1u);
     last = t == expected - 1u;
     if (last) *ticket = 0;  // ready for the next launch
+    __threadfence();        // the others' partials are read after their arrivals were seen
   }
   __syncthreads();
-  const bool r = last != 0;
-  if (r) __threadfence();
-  return r;
+  return last != 0;
 }
 
 // fold of partial[splits, inner] over the splits for the 128 columns of tile `tile`, in split order (the order of

@@ -966,6 +966,9 @@ struct Builder {
     p.K = a.shape[ra - 1];
     p.transpose_b = n.transpose_b;
     p.N = n.transpose_b ? b.shape[rb - 2] : b.shape[rb - 1];
+    // the launch writes batch * M * N elements: the declared result must be exactly that (a result whose batch
+    // differs from the left operand's, e.g. after an inconsistent split over ranks, would be overrun)
+    if (o.numel() != batch * p.M * p.N) throw Unsupported("BatchMatMul result does not hold batch x M x N elements");
     p.out_dt = (int)o.dt;
     p.in_dt = (int)a.dt;
     p.bias_dt = (int)DT::F32;

@@ -214,6 +214,18 @@ def matmul_bias_relu(m: int, k: int, n: int, transpose_b: bool = False, with_bia
     return b.build()
 
 
+def batch_matmul(batch: int, m: int, k: int, n: int, shared_b: bool = False, transpose_b: bool = False,
+                 dtype: str = "bfloat16", out_dtype: str = "float32") -> dict:
+    """a[batch,m,k] x b[batch,k,n] (or one shared b[k,n]; [.., n, k] with transpose_b) -> [batch,m,n]."""
+    b = _Builder(f"Fused_BatchMatMul_{batch}x{m}x{k}x{n}_9")
+    a = b.input("a", [batch, m, k], dtype)
+    inner = [n, k] if transpose_b else [k, n]
+    w = b.input("b", inner if shared_b else [batch] + inner, dtype)
+    attr = [_attr("transpose_a", "bool", False), _attr("transpose_b", "bool", bool(transpose_b))]
+    b.output(b.emit("BatchMatMul", [a, w], [batch, m, n], out_dtype, attr))
+    return b.build()
+
+
 def rmsnorm(rows: int, cols: int, dtype: str = "float32", eps: float = 1e-6) -> dict:
     """x[rows, cols] * rsqrt(mean(x^2) + eps) * g[cols]; float32 math, `dtype` in and out."""
     f = "float32"
@@ -249,6 +261,14 @@ def transpose(shape: Sequence[int], perm: Sequence[int], dtype: str = "float16")
     x = b.input("x", shape, dtype)
     oshape = [shape[p] for p in perm]
     b.output(b.emit("Transpose", [x], oshape, dtype, [_attr("perm", "listInt", perm)], out_name="xt"))
+    return b.build()
+
+
+def scale_copy(shape: Sequence[int], dtype: str = "float32") -> dict:
+    """`Mul(x, 1)`: the smallest elementwise region -- every element read once and written once (a copy)."""
+    b = _Builder("Fused_Mul_" + "x".join(map(str, shape)) + "_3")
+    x = b.input("x", list(shape), dtype)
+    b.output(b.emit("Mul", [x, b.const(1.0, dtype)], list(shape), dtype))
     return b.build()
 
 

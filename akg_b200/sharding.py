@@ -101,6 +101,10 @@ class Communicator:
         launch completes the exchange)."""
         return _capi.EXCHANGE_NAMES[int(self._lib.akgb_sharded_exchange_kind(kernel._handle, self._handle))]
 
+    def set_exchange_in_reduction(self, enabled: bool):
+        """Whether reductions complete the exchange in their own launch (all ranks must choose the same)."""
+        _capi.check(self._lib.akgb_comm_set_exchange_in_reduction(self._handle, 1 if enabled else 0))
+
     def set_timeout_ms(self, ms: float):
         _capi.check(self._lib.akgb_comm_set_timeout_ms(self._handle, float(ms)))
 

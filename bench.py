@@ -1,24 +1,29 @@
 #!/usr/bin/env python
 """Benchmark of the fused-op hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-classes]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-classes] [--scaling strong|weak]
 
 A step is one launch of the headline fused op over one batch of synthetic input: the float16
-bias + tanh-GELU * y -> float32 chain on [64,512,4096] (1.07 GB of algorithmic traffic, larger
-than L2, so no flush is needed between steps).  Rank 0 prints ONE JSON line:
+bias + tanh-GELU * y -> float32 chain on [64,512,4096] (1.07 GB of algorithmic traffic).  Rank 0 prints ONE
+JSON line:
 
-  value      algorithmic GB/s over all GPUs with inputs resident in HBM (CUDA events, max over ranks)
-  e2e        the same metric through the host-pointer entry point akgb_run_host with pinned host
-             buffers: H2D of the inputs and D2H of the output inside the timed region
+  value      algorithmic GB/s of the whole job with inputs resident in HBM (CUDA events, max over ranks)
+  e2e        the same metric through the host-pointer entry point akgb_run_host with pinned host buffers
+             (H2D of the inputs and D2H of the output inside the timed region), next to `copy_only`: the bare
+             pinned copies of the same bytes on all ranks at once, no kernel
   roofline   achieved GB/s of the dominant kernel against the measured copy bandwidth
   cpu_baseline  the C restatement of the reference CPU pipeline on a bounded slice of the workload
-  classes    one row per fused-op class of the benchmark definition (same timing rules)
+  classes    one row per fused-op class of the benchmark definition (same timing rules); every row carries
+             "checked": a sample of its outputs compared with the CPU oracle after (outside) the timed region
+  ceilings   plain copies of LayerNorm's 67 MB with the same buffer rotation and graph timing
 
-With N > 1 (under torchrun) every rank runs the same per-GPU workload on its own shard of a
-leading axis that is N times longer (weak scaling); only the column-sum / global-max row of
-`classes` has an exchange step (an NCCL all-reduce of the partials).
+With N > 1 (under torchrun) the FIXED benchmark shapes are split along their leading axis over the N ranks
+(strong scaling: per-GPU work shrinks with N); `value` is the full configuration's bytes over the slowest rank's
+step time.  Only the reductions over the split axis have an exchange step; their rows say which way it went
+("exchange").  The key "weak" repeats the headline and the reduction rows with every rank running the full
+single-GPU shape (`--scaling weak` makes that the main mode).
 
-`--impl reference` times the reference arm instead: the CPU restatement with all host threads.
+`--impl reference` times the reference arm instead: the CPU restatement of the path with all host threads.
 """
 from __future__ import annotations
 
@@ -40,6 +45,7 @@ METRIC = "achieved HBM GB/s (algorithmic bytes / device time), fused elementwise
 UNIT = "GB/s"
 WORKLOAD = "bias+tanh-GELU*y->f32, f16 [64,512,4096] (configs[1])"
 FALLBACK_HBM_GBS = 6650.0
+ROTATE_BELOW_BYTES = 512 * 2**20  # working sets smaller than this rotate through several buffer sets (L2 is 126 MB)
 
 
 def measured_peaks():
@@ -114,6 +120,8 @@ class ClockSampler:
         return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
 
 
+
+
 def dist_env():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -128,13 +136,14 @@ def torch_dtype(name):
             "int32": torch.int32, "int64": torch.int64, "bool": torch.bool}[name]
 
 
-def device_inputs(kernel, kinds, seed, device):
-    """Synthetic inputs created on the device with the benchmark's distributions."""
+def device_inputs(kernel, kinds, seed, device, rank=0):
+    """Synthetic inputs created on the device with the benchmark's distributions.  Tensors every rank holds whole
+    (bias, gamma, mask, the right matmul operand) get the same values on every rank, slices of the split axis differ."""
     import torch
-    g = torch.Generator(device=device)
-    g.manual_seed(seed)
     out = []
-    for t in kernel.inputs:
+    for j, t in enumerate(kernel.inputs):
+        g = torch.Generator(device=device)
+        g.manual_seed(seed * 131 + j * 17 + (7919 * rank if t.shard_kind == 1 else 0))
         kind = kinds.get(t.name, "normal")
         dt = torch_dtype(t.dtype)
         if kind == "normal":
@@ -159,11 +168,18 @@ def device_outputs(kernel, device):
     return [torch.empty(t.shape, dtype=torch_dtype(t.dtype), device=device) for t in kernel.outputs]
 
 
+def buffer_sets_for(kernel, kinds, device, rank, seed0=100):
+    """Enough (inputs + outputs) sets that consecutive steps do not find their data in L2."""
+    per_set = sum(t.nbytes for t in kernel.tensors)
+    nsets = 1 if per_set >= ROTATE_BELOW_BYTES else max(2, int(np.ceil(ROTATE_BELOW_BYTES / per_set)))
+    return [device_inputs(kernel, kinds, seed0 + s, device, rank) + device_outputs(kernel, device) for s in range(nsets)]
+
+
 def time_launches(kernel, buffer_sets, steps, warmup, barrier=None, use_graph=True):
     """Average device time of one step in ms: CUDA events on the launch stream, sync on both sides.
 
     The `steps` launches are captured once into a CUDA graph and the graph is what gets timed, so that short
-    kernels are not paced by the Python/ctypes call path; if capture is not possible (a collective in the step)
+    kernels are not paced by the Python/ctypes call path; if capture is not possible (an NCCL call in the step)
     the launches are issued directly.
     """
     import torch
@@ -199,90 +215,258 @@ def time_launches(kernel, buffer_sets, steps, warmup, barrier=None, use_graph=Tr
     return t0.elapsed_time(t1) / steps
 
 
-def class_configs(world):
-    """(key, description, input kinds) for every fused-op class; leading axes scale with the rank count."""
+def allreduce_scalar(x, world, op="max"):
+    if world == 1:
+        return x
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op={"max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN, "sum": dist.ReduceOp.SUM}[op])
+    return float(t.item())
+
+
+# ----------------------------------------------------------------------------------------- classes and their checks
+def class_table():
+    """(key, make(lead) -> description, leading extent of the benchmark shape, input kinds, check, sample extent).
+
+    `make(lead)` builds the class's description with `lead` as its leading extent, so the same table serves the
+    benchmark shape, its split over ranks, the weak-scaling shape and the small slices the oracle evaluates."""
     from akg_b200 import descs
-    w = world
-    cfgs = [
-        ("layernorm_f32_8192x1024", descs.layernorm(8192 * w, 1024), {"gamma": "gamma", "beta": "beta"}),
-        ("gelu_chain_f16_64x512x4096", descs.gelu_chain([64 * w, 512, 4096]), {"bias": "normal_small"}),
-        ("gelu_chain_f32math_64x512x4096", descs.gelu_chain([64 * w, 512, 4096], f32_math=True),
-         {"bias": "normal_small"}),
-        ("masked_softmax_f16_256x2048x2048", descs.masked_softmax(256 * w, 2048, 2048), {"mask": "causal"}),
-        ("reduce_sum_axis0_f32_65536x4096", descs.reduce_sum_axis0(65536 * w, 4096), {}),
-        ("reduce_max_all_f32_65536x4096", descs.reduce_max_all(65536 * w, 4096), {}),
-        ("reduce_sum_and_max_f32_65536x4096", descs.reduce_sum_and_max(65536 * w, 4096), {}),
-        ("transpose_f16_32x2048x32x128", descs.transpose([32 * w, 2048, 32, 128], [0, 2, 1, 3]), {}),
-        ("matmul_bias_relu_bf16_8192x4096x8192", descs.matmul_bias_relu(8192 * w, 4096, 8192),
-         {"a": "normal_small", "b": "normal_small", "bias": "normal_small"}),
+    ln = {"gamma": "gamma", "beta": "beta"}
+    ge = {"bias": "normal_small"}
+    mm = {"a": "normal_small", "b": "normal_small", "bias": "normal_small"}
+    return [
+        ("layernorm_f32_8192x1024", lambda r: descs.layernorm(r, 1024), 8192, ln, "f32", 64),
+        ("gelu_chain_f16_64x512x4096", lambda b: descs.gelu_chain([b, 512, 4096]), 64, ge, "exact", 1),
+        ("gelu_chain_f32math_64x512x4096", lambda b: descs.gelu_chain([b, 512, 4096], f32_math=True), 64, ge,
+         "f32_rms", 1),
+        ("masked_softmax_f16_256x2048x2048", lambda b: descs.masked_softmax(b, 2048, 2048), 256, {"mask": "causal"},
+         "half", 1),
+        ("reduce_sum_axis0_f32_65536x4096", lambda r: descs.reduce_sum_axis0(r, 4096), 65536, {}, "reduce", 0),
+        ("reduce_max_all_f32_65536x4096", lambda r: descs.reduce_max_all(r, 4096), 65536, {}, "reduce", 0),
+        ("reduce_sum_and_max_f32_65536x4096", lambda r: descs.reduce_sum_and_max(r, 4096), 65536, {}, "reduce", 0),
+        ("transpose_f16_32x2048x32x128", lambda b: descs.transpose([b, 2048, 32, 128], [0, 2, 1, 3]), 32, {}, "exact", 1),
+        ("matmul_bias_relu_bf16_8192x4096x8192", lambda m: descs.matmul_bias_relu(m, 4096, 8192), 8192, mm, "matmul", 16),
     ]
-    return cfgs
 
 
-def run_classes(rank, world, device, steps, warmup, hbm_peak, tf_peak, barrier, comm):
-    """One row per class: GB/s (or TFLOP/s) per GPU and aggregate, fraction of the measured peak."""
+def to_numpy(t):
+    """Device tensor -> numpy array of the same element type (bfloat16 through ml_dtypes)."""
+    import torch
+    if t.dtype == torch.bfloat16:
+        import ml_dtypes
+        return t.view(torch.int16).cpu().numpy().view(ml_dtypes.bfloat16)
+    return t.cpu().numpy()
+
+
+def check_sliced(make, kernel, bufs, how, sample):
+    """Classes whose leading-axis slices are independent: the oracle evaluates the first and the last `sample`
+    slices of this rank's tensors (a description of 2*sample slices), compared with the same slices of the output."""
+    import torch
+    from oracle import akg_oracle as O
+    ins, outs = bufs[:kernel.num_inputs], bufs[kernel.num_inputs:]
+
+    def ends(t):
+        return torch.cat([t[:sample], t[-sample:]], dim=0)
+
+    # at one rank nothing is marked as split: an input spans the leading axis when it has the first input's rank and
+    # leading extent (bias, gamma, mask and the right matmul operand do not)
+    lead = kernel.inputs[0]
+    def spans(d):
+        return d.shard_kind == 1 or (len(d.shape) == len(lead.shape) and d.shape[0] == lead.shape[0] and d.name != "b")
+    host_in = [to_numpy(ends(t) if spans(d) else t) for t, d in zip(ins, kernel.inputs)]
+    want = O.evaluate(make(2 * sample), host_in)
+    for o, w, d in zip(outs, want, kernel.outputs):
+        got = to_numpy(ends(o))
+        w = np.ascontiguousarray(w)
+        if how == "exact":
+            if not np.array_equal(got.view(np.uint8), w.view(np.uint8)):
+                return False
+            continue
+        g64, w64 = got.astype(np.float64), w.astype(np.float64)
+        if how == "f32":  # 1e-5 relative (+1e-6 absolute, as the parity tests)
+            ok = np.all(np.abs(g64 - w64) <= 1e-5 * np.abs(w64) + 1e-6)
+        elif how == "f32_rms":  # the reference's comparison, np.allclose(rtol=atol), with atol scaled by the rms
+            ok = np.all(np.abs(g64 - w64) <= 1e-5 * np.abs(w64) + 1e-5 * np.sqrt(np.mean(w64 * w64)))
+        elif how == "half":  # 2e-3 for float16 / bfloat16 results; masked entries exactly zero
+            ok = np.all(np.abs(g64 - w64) <= 2e-3 * np.abs(w64) + 1e-7) and np.array_equal(g64 == 0, w64 == 0)
+        elif how == "matmul":  # the bfloat16 rounding of a value within 2e-3 of the oracle's float32 accumulate
+            atol = 1e-3 * float(np.abs(w64).max() + 1e-30)
+            ok = np.all(np.abs(g64 - w64) <= (2e-3 + 2.0 ** -8) * np.abs(w64) + atol)
+        else:
+            raise ValueError(how)
+        if not ok:
+            return False
+    return True
+
+
+def check_reduction(make, kernel, bufs, rank, world):
+    """Reductions over the split axis: every rank evaluates the oracle on ITS rows (float32, the oracle's own order) and
+    a float64 sum; the per-rank results are combined over the ranks in float64 / by max and compared with what the
+    library returned on every rank: column sums within 1e-5 * sum|x| of the float64 truth, the maximum bit for bit."""
+    import torch
+    import torch.distributed as dist
+    from oracle import akg_oracle as O
+    x = bufs[0]
+    outs = bufs[kernel.num_inputs:]
+    xh = x.cpu().numpy()
+    want = O.evaluate(make(xh.shape[0]), [xh])
+    dev = x.device
+    ok = True
+    for o, w, d in zip(outs, want, kernel.outputs):
+        got = o.cpu().numpy().astype(np.float64).reshape(-1)
+        if d.shard_kind == 3 or (world == 1 and got.size == 1):  # maximum of all elements
+            m = torch.tensor([float(np.asarray(w).reshape(-1)[0])], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(m, op=dist.ReduceOp.MAX)
+            ok = ok and got[0] == float(m.item())
+            continue
+        truth = np.zeros(xh.shape[1], np.float64)
+        mag = np.zeros(xh.shape[1], np.float64)
+        for r in range(0, xh.shape[0], 8192):
+            blk = xh[r:r + 8192].astype(np.float64)
+            truth += blk.sum(axis=0)
+            mag += np.abs(blk).sum(axis=0)
+        packed = torch.from_numpy(np.stack([truth, mag, np.asarray(w, np.float64).reshape(-1)])).to(dev)
+        if world > 1:
+            dist.all_reduce(packed, op=dist.ReduceOp.SUM)
+        truth, mag, oracle_sum = packed.cpu().numpy()
+        ok = ok and bool(np.all(np.abs(got - truth) <= 1e-5 * mag)) and bool(np.all(np.abs(oracle_sum - truth) <= 1e-5 * mag))
+    if world > 1:  # the same bits on every rank
+        for o in outs:
+            parts = [torch.empty_like(o) for _ in range(world)]
+            dist.all_gather(parts, o.contiguous())
+            ok = ok and all(bool(torch.equal(p.view(torch.int32), parts[0].view(torch.int32))) for p in parts)
+    return bool(ok)
+
+
+def run_classes(rank, world, device, steps, warmup, hbm_peak, tf_peak, barrier, comm, scaling, only=None):
+    """One row per class: GB/s (or TFLOP/s) of the whole job, fraction of the measured peak per GPU, oracle check."""
     import torch
     from akg_b200 import FusedKernel, UnsupportedError
     rows = {}
-    for key, desc, kinds in class_configs(world):
+    for key, make, lead, kinds, how, sample in class_table():
+        if only is not None and key not in only:
+            continue
+        global_lead = lead if scaling == "strong" else lead * world
         try:
-            k = FusedKernel(desc, device=device.index, shard_rank=rank, shard_world=world)
+            k = FusedKernel(make(global_lead), device=device.index, shard_rank=rank, shard_world=world)
         except UnsupportedError as e:
             rows[key] = {"unsupported": str(e)[:120]}
             continue
-        per_set = sum(t.nbytes for t in k.tensors)
-        nsets = 1 if per_set > 512 * 2**20 else max(2, int(np.ceil(512 * 2**20 / per_set)))
-        sets = []
-        for s in range(nsets):
-            sets.append(device_inputs(k, kinds, 100 + s, device) + device_outputs(k, device))
+        sets = buffer_sets_for(k, kinds, device, rank)
         partial = [i for i, t in enumerate(k.tensors) if t.shard_kind >= 2]
+        exchange = comm.exchange_kind(k) if (partial and comm is not None) else "none"
 
         def step_launch(bufs, stream=None, k=k, partial=partial):
             if partial and comm is not None:
-                comm.launch_sharded(k, bufs, stream)  # kernel + NCCL all-reduce of the partials, one stream
+                comm.launch_sharded(k, bufs, stream)  # the kernel and the exchange of its partials, one stream
             else:
                 k.launch(bufs, stream)
 
         class _K:  # adapter so that time_launches includes the exchange step
             launch = staticmethod(step_launch)
-        # NCCL calls are not captured; the library's own exchange kernel is an ordinary kernel and is
-        graphable = not (partial and world > 1) or (comm is not None and comm.peer_exchange)
+        # NCCL calls are not captured into the graph; the library's own exchange runs inside ordinary kernels and is
+        graphable = exchange in ("none", "peer-kernel", "in-reduction")
         ms = time_launches(_K, sets, steps, warmup, barrier, use_graph=graphable)
-        if partial and comm is not None and comm.peer_exchange:
-            # a bounded wait of the exchange kernel that ran out on any rank: NCCL carries the exchange from here on
+        if exchange in ("peer-kernel", "in-reduction"):
+            # a bounded wait that ran out on any rank: NCCL carries the exchange from here on (on every rank)
             try:
                 bad = 1 if k.check_device_error() else 0
             except Exception:
                 bad = 1
-            if allreduce_max_scalar(float(bad), world) > 0:
+            if allreduce_scalar(float(bad), world) > 0:
                 comm.disable_peer_exchange()
+                exchange = "nccl (after a peer-memory wait ran out)"
                 ms = time_launches(_K, sets, steps, warmup, barrier, use_graph=False)
-        ms_max = allreduce_max_scalar(ms, world)
-        row = {"class": k.op_class, "ms": round(ms_max, 5), "launches_per_step": k.launch_count}
+        ms_max = allreduce_scalar(ms, world)
+        bytes_job = k.bytes * world   # the ranks' shares add up to the global shape
+        flops_job = k.flops * world
+        row = {"class": k.op_class, "ms": round(ms_max, 5), "launches_per_step": k.launch_count,
+               "per_gpu_lead": k.inputs[0].shape[0], "buffer_sets": len(sets)}
+        if partial:
+            row["exchange"] = exchange
         if k.flops:
-            tf = k.flops * world / (ms_max * 1e-3) / 1e12
+            tf = flops_job / (ms_max * 1e-3) / 1e12
             row.update({"tflops": round(tf, 2), "frac_of_peak": round(tf / world / tf_peak, 4), "bound": "tensor"})
         else:
-            gbs = k.bytes * world / (ms_max * 1e-3) / 1e9
+            gbs = bytes_job / (ms_max * 1e-3) / 1e9
             row.update({"gbs": round(gbs, 1), "frac_of_peak": round(gbs / world / hbm_peak, 4), "bound": "hbm",
-                        "frac_of_8TBs": round(gbs / world / 8000.0, 4), "buffer_sets": nsets})
+                        "frac_of_8TBs": round(gbs / world / 8000.0, 4)})
+        # ---- outside the timed region: a sample of the outputs against the CPU oracle
+        try:
+            step_launch(sets[0])
+            torch.cuda.synchronize()
+            if how == "reduce":
+                good = check_reduction(make, k, sets[0], rank, world)
+            else:
+                good = check_sliced(make, k, sets[0], how, sample)
+        except Exception as e:  # a check that cannot run is a failed check, not a crashed benchmark
+            sys.stderr.write(f"[bench] check of {key} raised: {e!r}\n")
+            good = False
+        row["checked"] = bool(allreduce_scalar(1.0 if good else 0.0, world, "min") > 0)
         rows[key] = row
         del sets, k
         torch.cuda.empty_cache()
     return rows
 
 
-_dist = {"on": False}
-
-
-def allreduce_max_scalar(x, world):
-    if world == 1:
-        return x
+def copy_ceilings(device, steps, warmup, hbm_peak):
+    """What a plain copy of LayerNorm's bytes (33.5 MB in, 33.5 MB out) reaches with the same buffer rotation and graph
+    timing: torch's copy kernel (the kernel the measured peak was taken with, at 2 GB) and this library's generated
+    elementwise kernel on `Mul(x, 1)`.  A size-matched ceiling for the 67 MB row-wise classes."""
     import torch
-    import torch.distributed as dist
-    t = torch.tensor([x], dtype=torch.float64, device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
+    from akg_b200 import FusedKernel, descs
+    n_sets = 8
+    xs = [torch.randn(8192, 1024, device=device) for _ in range(n_sets)]
+    ys = [torch.empty_like(x) for x in xs]
+    nbytes = 2 * xs[0].numel() * 4
+
+    class TorchCopy:
+        @staticmethod
+        def launch(b, stream=None):
+            b[1].copy_(b[0])
+
+    out = {}
+    ms = time_launches(TorchCopy, [[x, y] for x, y in zip(xs, ys)], steps, warmup)
+    out["torch_copy_67MB"] = {"ms": round(ms, 5), "gbs": round(nbytes / ms / 1e6, 1), "frac_of_peak": round(nbytes / ms / 1e6 / hbm_peak, 4)}
+    try:
+        k = FusedKernel(descs.scale_copy([8192, 1024]), device=device.index)
+        ms = time_launches(k, [[x, y] for x, y in zip(xs, ys)], steps, warmup)
+        out["library_copy_67MB"] = {"ms": round(ms, 5), "gbs": round(nbytes / ms / 1e6, 1),
+                                    "frac_of_peak": round(nbytes / ms / 1e6 / hbm_peak, 4)}
+    except Exception as e:
+        out["library_copy_67MB"] = {"error": str(e)[:100]}
+    return out
+
+
+def host_copy_only(bufs, kernel, device, steps, barrier, world):
+    """Bare pinned copies of one step's bytes, no kernel: all inputs host->device on one stream while all outputs go
+    device->host on another, on every rank at once.  Seconds per step (max over ranks)."""
+    import torch
+    ins = bufs[:kernel.num_inputs]
+    outs = bufs[kernel.num_inputs:]
+    h_in = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in ins]
+    h_out = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in outs]
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def once():
+        with torch.cuda.stream(s1):
+            for d, h in zip(ins, h_in):
+                d.copy_(h, non_blocking=True)
+        with torch.cuda.stream(s2):
+            for d, h in zip(outs, h_out):
+                h.copy_(d, non_blocking=True)
+    once()
+    torch.cuda.synchronize()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        once()
+    torch.cuda.synchronize()
+    barrier()
+    sec = (time.perf_counter() - t0) / steps
+    return allreduce_scalar(sec, world)
 
 
 def gpu_arm(args):
@@ -310,7 +494,7 @@ def gpu_arm(args):
             from akg_b200.sharding import Communicator
             comm = Communicator.from_process_group(device=local)
             if os.environ.get("AKGB_BENCH_NCCL_ONLY", "") != "1":
-                comm.enable_peer_exchange()  # small partials: one kernel over the ranks' mapped buffers
+                comm.enable_peer_exchange()  # small partials travel inside the library's own kernels
         finally:
             sys.stdout.flush()
             os.dup2(saved_stdout, 1)
@@ -322,19 +506,25 @@ def gpu_arm(args):
         torch.cuda.synchronize()
 
     hbm_peak, tf_peak, peak_src = measured_peaks()
-    desc = descs.gelu_chain([64 * world, 512, 4096])
-    k = FusedKernel(desc, device=local, shard_rank=rank, shard_world=world)
+    scaling = args.scaling
+    lead = 64 if scaling == "strong" else 64 * world
+    if lead % world:
+        raise SystemExit(f"the leading extent {lead} does not split over {world} ranks")
+    k = FusedKernel(descs.gelu_chain([lead, 512, 4096]), device=local, shard_rank=rank, shard_world=world)
     kinds = {"bias": "normal_small"}
-    bufs = device_inputs(k, kinds, 1 + rank, device) + device_outputs(k, device)
+    sets = buffer_sets_for(k, kinds, device, rank, seed0=1)
+    bufs = sets[0]
 
     # ---- device-resident throughput (value) + roofline of the dominant kernel
     with ClockSampler(local) as clk:
-        ms = time_launches(k, [bufs], args.steps, args.warmup, barrier)
-    ms = allreduce_max_scalar(ms, world)
+        ms = time_launches(k, sets, args.steps, args.warmup, barrier)
+    ms = allreduce_scalar(ms, world)
     clocks = clk.summary()
     total_bytes = k.bytes * world
     value = total_bytes / (ms * 1e-3) / 1e9
     achieved = k.bytes / (ms * 1e-3) / 1e9
+    checked = check_sliced(lambda b: descs.gelu_chain([b, 512, 4096]), k, bufs, "exact", 1)
+    checked = allreduce_scalar(1.0 if checked else 0.0, world, "min") > 0
 
     # ---- end to end through the host-pointer entry point, pinned host buffers
     host = []
@@ -352,37 +542,69 @@ def gpu_arm(args):
         k.run_host(host_np)
     barrier()
     e2e_s = (time.perf_counter() - t0) / e2e_steps
-    e2e_s = allreduce_max_scalar(e2e_s, world)
+    e2e_s = allreduce_scalar(e2e_s, world)
     h2d = sum(d.nbytes for d in k.inputs)
     d2h = sum(d.nbytes for d in k.outputs)
-    # the e2e result must be the device result
-    assert np.array_equal(host_np[-1][:4096], bufs[-1].view(torch.uint8).reshape(-1)[:4096].cpu().numpy())
+    # the end-to-end result must be the device result, bit for bit, on the whole output
+    k.launch(bufs)
+    torch.cuda.synchronize()
+    e2e_same = bool(torch.equal(host[-1].view(torch.int32), bufs[-1].cpu().view(torch.int32)))
+    e2e_same = allreduce_scalar(1.0 if e2e_same else 0.0, world, "min") > 0
+    copy_s = host_copy_only(bufs, k, device, e2e_steps, barrier, world)
 
+    per_gpu_shape = list(k.inputs[0].shape)
+    nsets = len(sets)
     line = {
         "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": round(ms, 5), "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": round(ms, 5), "higher_is_better": True, "scaling": scaling,
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "per_gpu_shape": [64, 512, 4096], "shard": "axis 0 split over ranks",
-                   "l2": "inputs larger than L2 (1.07 GB per step), no flush"},
+        "config": {"workload": WORKLOAD, "global_shape": [lead, 512, 4096], "per_gpu_shape": per_gpu_shape,
+                   "shard": "axis 0 split over ranks, no collective on this path",
+                   "l2": ("inputs larger than L2 (1.07 GB per step), no flush" if nsets == 1 else
+                          f"{nsets} buffer sets in rotation ({sum(t.nbytes for t in k.tensors) * nsets >> 20} MB), "
+                          "every step reads and writes data last touched a full rotation ago")},
+        "checked": bool(checked),
         "clocks": clocks,
         "e2e": {"value": round(total_bytes / e2e_s / 1e9, 2), "unit": UNIT, "h2d_bytes_per_step": h2d * world,
-                "d2h_bytes_per_step": d2h * world, "steps": e2e_steps, "ms_per_step": round(e2e_s * 1e3, 3)},
+                "d2h_bytes_per_step": d2h * world, "steps": e2e_steps, "ms_per_step": round(e2e_s * 1e3, 3),
+                "same_bits_as_device_launch": bool(e2e_same),
+                "copy_only": {"value": round(total_bytes / copy_s / 1e9, 2), "unit": UNIT,
+                              "ms_per_step": round(copy_s * 1e3, 3),
+                              "what": "the same pinned H2D and D2H bytes on all ranks at once, no kernel"}},
         "gpu_launches": k.launch_count * args.steps,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
-                     "frac": round(achieved / hbm_peak, 4), "traffic": NCU_TRAFFIC_BYTES["gelu"],
-                     "peak_source": peak_src, "kernel": "gelu_chain_f16_oneshot_kernel",
-                     "frac_of_8TBs": round(achieved / 8000.0, 4)},
+                     "frac": round(achieved / hbm_peak, 4),
+                     "traffic": NCU_TRAFFIC_BYTES["gelu"] // world, "peak_source": peak_src,
+                     "kernel": "gelu_chain_f16_oneshot_kernel", "frac_of_8TBs": round(achieved / 8000.0, 4)},
     }
-    del bufs, host, host_np
+    del bufs, sets, host, host_np
     torch.cuda.empty_cache()
     if rank == 0 and world == 1:
         line["cpu_baseline"] = cpu_baseline_sample()
+    csteps, cwarm = max(3, min(args.steps, 10)), max(3, min(args.warmup, 3))
     if not args.no_classes:
-        line["classes"] = run_classes(rank, world, device, max(3, min(args.steps, 10)), max(3, min(args.warmup, 3)),
-                                      hbm_peak, tf_peak, barrier, comm)
+        line["classes"] = run_classes(rank, world, device, csteps, cwarm, hbm_peak, tf_peak, barrier, comm, scaling)
+        if world == 1:
+            line["ceilings"] = copy_ceilings(device, csteps, cwarm, hbm_peak)
+    if world > 1 and not args.no_classes:
+        # the other scaling mode, for the headline and for the rows that have an exchange step
+        other = "weak" if scaling == "strong" else "strong"
+        ko = FusedKernel(descs.gelu_chain([64 * world if other == "weak" else 64, 512, 4096]), device=local,
+                         shard_rank=rank, shard_world=world)
+        so = buffer_sets_for(ko, kinds, device, rank, seed0=1)
+        mo = allreduce_scalar(time_launches(ko, so, csteps, cwarm, barrier), world)
+        del so
+        torch.cuda.empty_cache()
+        line[other] = {"value": round(ko.bytes * world / (mo * 1e-3) / 1e9, 1), "unit": UNIT,
+                       "ms_per_step": round(mo, 5), "per_gpu_shape": list(ko.inputs[0].shape),
+                       "classes": run_classes(rank, world, device, csteps, cwarm, hbm_peak, tf_peak, barrier, comm, other,
+                                              only={"reduce_sum_axis0_f32_65536x4096", "reduce_max_all_f32_65536x4096",
+                                                    "reduce_sum_and_max_f32_65536x4096"})}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
+        if comm is not None:
+            comm.close()
         dist.destroy_process_group()
 
 
@@ -412,38 +634,52 @@ def cpu_time(batches, variant, reps):
 
 def cpu_baseline_sample():
     from oracle import cpu_ref
-    cores = cpu_ref.num_threads()
+    cores = cpu_ref.use_all_host_threads()  # not an OMP_NUM_THREADS inherited from a launcher
     batches = 8
     gbs, sec = cpu_time(batches, "rp", 3)
     return {"value": round(gbs, 3), "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": f"{batches} of the 64 leading slices ([{batches},512,4096]), OpenMP over all host threads, "
+            "sample": f"{batches} of the 64 leading slices ([{batches},512,4096]), OpenMP over {cores} host threads, "
                       f"median of 3, {sec:.2f} s each"}
 
 
 def reference_arm(args):
-    """The reference's CPU implementation of the path (C restatement: the MLIR toolchain cannot be built here)."""
+    """The reference's CPU implementation of the path (C restatement: the MLIR toolchain cannot be built here), on all
+    the host threads this process may use.  A step is the WHOLE workload ([64,512,4096]) when the run then ends within
+    a few minutes, else a leading-axis slice of it (stated in the line); throughput is per algorithmic byte."""
     rank, world, _ = dist_env()
     if rank != 0:
         return
     from oracle import cpu_ref
-    cores = cpu_ref.num_threads()
-    batches = 8
+    cores = cpu_ref.use_all_host_threads()
+    steps, warmup = max(1, args.steps), max(1, min(args.warmup, 3))
+    # size the step from a probe on 4 slices
+    px, pb, py = cpu_workload(4)
+    cpu_ref.gelu_chain(px, pb, py, variant="rp")
+    t0 = time.perf_counter()
+    cpu_ref.gelu_chain(px, pb, py, variant="rp")
+    per_slice = (time.perf_counter() - t0) / 4
+    del px, py
+    batches = 64
+    while batches > 1 and per_slice * batches * (steps + warmup) > 150.0:
+        batches //= 2
     x, bias, y = cpu_workload(batches)
     nbytes = x.nbytes + y.nbytes + bias.nbytes + x.size * 4
-    for _ in range(max(1, min(args.warmup, 3))):
+    for _ in range(warmup):
         cpu_ref.gelu_chain(x, bias, y, variant="rp")
-    steps = max(1, min(args.steps, 10))
     t0 = time.perf_counter()
     for _ in range(steps):
         cpu_ref.gelu_chain(x, bias, y, variant="rp")
     sec = (time.perf_counter() - t0) / steps
     gbs = nbytes / sec / 1e9
-    sample = f"each step = {batches} of the 64 leading slices ([{batches},512,4096]); OpenMP over all host threads"
+    whole = batches == 64
+    sample = (f"each step = {'the whole workload' if whole else f'{batches} of the 64 leading slices'} "
+              f"([{batches},512,4096]); OpenMP over {cores} host threads")
     line = {
         "impl": "reference", "metric": METRIC, "value": round(gbs, 3), "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": sample},
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD + ("" if whole else f" -- CPU arm: {batches} of its 64 leading slices per step"),
+                   "global_shape": [64, 512, 4096], "sample": sample},
         "cpu_baseline": {"value": round(gbs, 3), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": round(gbs, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -457,7 +693,7 @@ def cpu_classes_table():
     import ml_dtypes
     from oracle import cpu_ref as C
     rng = np.random.default_rng(0)
-    cores = C.num_threads()
+    cores = C.use_all_host_threads()
 
     def med(fn, reps=3):
         fn()
@@ -527,6 +763,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="N > 1: split the fixed benchmark shapes over the ranks (strong) or give every rank the full "
+                         "single-GPU shape (weak)")
     ap.add_argument("--no-classes", action="store_true", help="skip the per-class table")
     ap.add_argument("--cpu-classes", action="store_true",
                     help="time the CPU restatement on a slice of every class (no GPU work) and exit")

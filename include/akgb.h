@@ -84,6 +84,13 @@ typedef struct akgb_options {
  * (NVRTC-compiled) variant of the same template.  Results are identical; this is for hosts without NVRTC
  * and for tests. */
 #define AKGB_FLAG_NO_JIT 1
+/* Fold the per-CTA partials of column / all-element reductions by the last CTA of the launch that produced them
+ * instead of in a second, small launch.  Results are identical bit for bit.  Measured on B200 the second launch is the
+ * faster of the two (the in-launch fold ends the kernel with a chain of dependent global-memory round trips: store
+ * acknowledged, arrival counter, partials read back -- about 6 us, against about 2 us for a dependent launch inside a
+ * CUDA graph), so this is off by default; a sharded reduction that completes its exchange in its own launch
+ * (akgb_launch_sharded) folds in-launch regardless. */
+#define AKGB_FLAG_FOLD_IN_LAUNCH 2
 
 typedef struct akgb_kernel akgb_kernel;
 
@@ -200,6 +207,10 @@ akgb_status akgb_comm_set_peer_exchange(akgb_comm* c, int32_t enabled);
 akgb_status akgb_comm_exchange_handle(akgb_comm* c, void* handle, size_t cap);
 akgb_status akgb_comm_attach_peers(akgb_comm* c, const void* handles, size_t bytes);
 akgb_status akgb_comm_set_timeout_ms(akgb_comm* c, double ms);
+/* Whether a reduction that produces all partial outputs of a kernel completes the exchange inside its own launch
+ * (see akgb_launch_sharded) or leaves it to the exchange kernel / NCCL after the launch.  Every rank must choose the
+ * same. */
+akgb_status akgb_comm_set_exchange_in_reduction(akgb_comm* c, int32_t enabled);
 
 /* All-reduces, in place and on `stream`, every tensor of `tensors` (inputs then outputs, device pointers) whose
  * shard_kind is a partial; one NCCL group for all of them.  No-op for kernels without partial outputs. */

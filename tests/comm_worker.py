@@ -50,28 +50,82 @@ def main():
     ok = ok and bool(torch.allclose(outs[0].cpu().double(), dx[lo:hi], rtol=1e-4, atol=1e-4))
     ok = ok and bool(torch.allclose(outs[1].cpu().double(), (dyd * xhat).sum(0), rtol=1e-4, atol=1e-3))
     ok = ok and bool(torch.allclose(outs[2].cpu().double(), dyd.sum(0), rtol=1e-4, atol=1e-3))
-    # the same reductions with the exchange over the ranks' mapped buffers instead of NCCL
+    # the same reductions with the exchange over the ranks' mapped buffers instead of NCCL: inside the reduction's own
+    # launch (the CTA that folds a tile exchanges it), and as one exchange kernel after the launch
     peer = comm.enable_peer_exchange()
+    timings = {}
     if peer:
-        for build, ref in ((descs.reduce_sum_axis0, lambda t: t.double().sum(0)),
-                           (descs.reduce_max_all, lambda t: t.max().reshape(1)),
-                           (descs.reduce_sum_and_max, None)):
-            k = FusedKernel(build(rows, cols), device=local, shard_rank=rank, shard_world=world)
-            outs = [torch.empty(t.shape, dtype=torch.float32, device="cuda") for t in k.outputs]
-            for _ in range(5):  # several epochs, both parities
-                comm.launch_sharded(k, [mine] + outs)
-            torch.cuda.synchronize()
-            ok = ok and k.check_device_error() == 0
-            wants = [ref(x)] if ref else [x.double().sum(0), x.max().reshape(1)]
-            for o, w in zip(outs, wants):
-                ok = ok and bool(torch.allclose(o.cpu().double().reshape(w.shape), w.double(), rtol=1e-5,
-                                                atol=1e-5 * float(x.abs().sum(0).max())))
-        # every rank holds the same bits
-        gathered = [torch.empty_like(outs[0]) for _ in range(world)]
-        dist.all_gather(gathered, outs[0])
-        ok = ok and all(bool(torch.equal(g, gathered[0])) for g in gathered)
+        big = torch.randn(65536 // world, 4096, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3 + rank))
+        for in_reduction in (True, False):
+            comm.set_exchange_in_reduction(in_reduction)
+            for build, ref in ((descs.reduce_sum_axis0, lambda t: t.double().sum(0)),
+                               (descs.reduce_max_all, lambda t: t.max().reshape(1)),
+                               (descs.reduce_sum_and_max, None)):
+                k = FusedKernel(build(rows, cols), device=local, shard_rank=rank, shard_world=world)
+                ok = ok and comm.exchange_kind(k) == ("in-reduction" if in_reduction else "peer-kernel")
+                outs = [torch.empty(t.shape, dtype=torch.float32, device="cuda") for t in k.outputs]
+                for _ in range(5):  # several calls, both parities of the exchange buffer
+                    comm.launch_sharded(k, [mine] + outs)
+                torch.cuda.synchronize()
+                ok = ok and k.check_device_error() == 0
+                wants = [ref(x)] if ref else [x.double().sum(0), x.max().reshape(1)]
+                for o, w in zip(outs, wants):
+                    ok = ok and bool(torch.allclose(o.cpu().double().reshape(w.shape), w.double(), rtol=1e-5,
+                                                    atol=1e-5 * float(x.abs().sum(0).max())))
+                # every rank holds the same bits
+                for o in outs:
+                    gathered = [torch.empty_like(o) for _ in range(world)]
+                    dist.all_gather(gathered, o)
+                    ok = ok and all(bool(torch.equal(g_, gathered[0])) for g_ in gathered)
+                # the benchmark's split: [65536 / world, 4096] per rank, replayed from a CUDA graph
+                kb = FusedKernel(build(65536, 4096), device=local, shard_rank=rank, shard_world=world)
+                ob = [torch.empty(t.shape, dtype=torch.float32, device="cuda") for t in kb.outputs]
+                s = torch.cuda.Stream()
+                with torch.cuda.stream(s):
+                    for _ in range(3):
+                        comm.launch_sharded(kb, [big] + ob, s)
+                    s.synchronize()
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=s):
+                        for _ in range(10):
+                            comm.launch_sharded(kb, [big] + ob, torch.cuda.current_stream())
+                    graph.replay()
+                    torch.cuda.synchronize()
+                    dist.barrier()
+                    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    t0.record(s)
+                    graph.replay()
+                    t1.record(s)
+                    torch.cuda.synchronize()
+                ok = ok and kb.check_device_error() == 0
+                timings[(build.__name__, in_reduction)] = t0.elapsed_time(t1) / 10 * 1e3
+                for o, d in zip(ob, kb.outputs):
+                    if d.shard_kind == 2:  # column sums
+                        part = big.double().sum(0)
+                        dist.all_reduce(part)
+                        ok = ok and bool(torch.allclose(o.double(), part, rtol=1e-5, atol=1e-2))
+                    else:  # the maximum of all elements, bit for bit
+                        mx = big.max().reshape(1).clone()
+                        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+                        ok = ok and bool(torch.equal(o.reshape(1), mx))
+        comm.set_exchange_in_reduction(True)
+    # a BatchMatMul whose operands both carry the batch: every rank multiplies its own batch entries
+    bsz = 2 * world
+    a_all = (torch.randn(bsz, 128, 64, generator=g) * 0.1).bfloat16()
+    b_all = (torch.randn(bsz, 64, 256, generator=g) * 0.1).bfloat16()
+    kbm = FusedKernel(descs.batch_matmul(bsz, 128, 64, 256), device=local, shard_rank=rank, shard_world=world)
+    ok = ok and all(t.shard_kind == 1 for t in kbm.tensors) and kbm.inputs[1].shape == (2, 64, 256)
+    obm = torch.empty(kbm.outputs[0].shape, dtype=torch.float32, device="cuda")
+    comm.launch_sharded(kbm, [a_all[2 * rank:2 * rank + 2].contiguous().cuda(),
+                              b_all[2 * rank:2 * rank + 2].contiguous().cuda(), obm])
+    torch.cuda.synchronize()
+    want_bm = torch.matmul(a_all.double(), b_all.double())[2 * rank:2 * rank + 2]
+    ok = ok and bool(torch.allclose(obm.cpu().double(), want_bm, rtol=2e-3, atol=2e-3 * float(want_bm.abs().max())))
     if rank == 0:
         print("PEER_EXCHANGE", "on" if peer else "off", flush=True)
+        for (name, in_red), us in sorted(timings.items()):
+            print(f"TIMING {name} [65536/{world},4096] per rank, exchange {'in-reduction' if in_red else 'peer-kernel'}: "
+                  f"{us:.1f} us per step", flush=True)
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     comm.close()

@@ -243,7 +243,7 @@ def test_planning_of_generated_kernels_needs_no_device(lib):
     kc = FusedKernel(descs.mul_reduce_sum(4096, 512, [0]))
     assert kc.meta()["template"] == "akgb_col_jit" and "akgb_col_jit" in kc.jit_source()
     ka = FusedKernel(descs.mul_reduce_sum(4096, 512, [0, 1]))
-    assert ka.meta()["template"] == "akgb_row_jit" and "C = 4096" in ka.jit_source() and ka.launch_count == 2
+    assert ka.meta()["template"] == "akgb_row_jit" and "C = 4096" in ka.jit_source() and ka.launch_count == 3
     # small tensors are not worth a generated reduction kernel
     assert FusedKernel(descs.mul_reduce_sum(64, 64, [0])).meta()["template"] != "akgb_col_jit"
 
@@ -311,6 +311,33 @@ def test_planning_of_the_wider_op_surface(lib):
     g = b.emit("Gather", [table, idx], [40, 16], f, [_attr("axis", "int", 0), _attr("batch_dims", "int", 0)])
     b.output(b.emit("UnsortedSegmentSum", [g, idx], [7, 16], f, [_attr("num_segments", "int", 7)]))
     assert FusedKernel(b.build()).launch_count == 2
+
+
+def test_batch_matmul_shards_on_the_batch_of_both_operands(lib):
+    """The split axis of a BatchMatMul is the batch of its LEFT operand; a right operand that carries the same batch is
+    split with it, a 2-D shared one stays whole -- whichever of the two inputs is larger."""
+    # batch == world, right operand larger than the left one
+    k = FusedKernel(descs.batch_matmul(2, 64, 64, 256), shard_rank=1, shard_world=2)
+    by = {t.name: t for t in k.tensors}
+    assert by["a"].shape == (1, 64, 64) and by["a"].shard_kind == _capi.SHARD_SPLIT_AXIS0
+    assert by["b"].shape == (1, 64, 256) and by["b"].shard_kind == _capi.SHARD_SPLIT_AXIS0
+    assert k.outputs[0].shape == (1, 64, 256) and k.outputs[0].shard_kind == _capi.SHARD_SPLIT_AXIS0
+    assert k.flops == 2 * 64 * 64 * 256  # one batch entry per rank
+    # batch > world
+    k = FusedKernel(descs.batch_matmul(8, 128, 64, 256, transpose_b=True), shard_rank=0, shard_world=4)
+    assert [t.shape for t in k.tensors] == [(2, 128, 64), (2, 256, 64), (2, 128, 256)]
+    assert all(t.shard_kind == _capi.SHARD_SPLIT_AXIS0 for t in k.tensors) and k.flops == 2 * 2 * 128 * 64 * 256
+    # one shared 2-D right operand, even when its leading extent equals the batch
+    k = FusedKernel(descs.batch_matmul(64, 128, 64, 256, shared_b=True), shard_rank=0, shard_world=4)
+    by = {t.name: t for t in k.tensors}
+    assert by["a"].shape == (16, 128, 64) and by["b"].shape == (64, 256) and by["b"].shard_kind == _capi.SHARD_REPLICATED
+    # a square MatMul: the weight has as many rows as the left operand and must not be cut
+    k = FusedKernel(descs.matmul_bias_relu(256, 256, 256), shard_rank=1, shard_world=2)
+    by = {t.name: t for t in k.tensors}
+    assert by["a"].shape == (128, 256) and by["b"].shape == (256, 256) and by["b"].shard_kind == _capi.SHARD_REPLICATED
+    assert k.outputs[0].shape == (128, 256)
+    with pytest.raises(UnsupportedError):  # the batch does not divide
+        FusedKernel(descs.batch_matmul(3, 64, 64, 256), shard_rank=0, shard_world=2)
 
 
 def test_generated_kernels_shard_like_the_templates(lib):

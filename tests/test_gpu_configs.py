@@ -167,7 +167,13 @@ def test_config_transpose_full_size_bit_exact(lib):
 
 # ------------------------------------------------------------------ C5a matmul + bias + ReLU, multi-tile and full size
 def check_matmul(d, ins, got_bf16, rows=None):
-    """`got_bf16`: the library's output rows `rows` (all if None).  Bound as in test_gpu_parity.py::test_matmul_epilogue."""
+    """`got_bf16`: the library's output rows `rows` (all if None).  Bound as in test_gpu_parity.py::test_matmul_epilogue:
+    every output is the bfloat16 rounding of a value within 2e-3 of the oracle's float32 result, and where it differs
+    from the oracle's own rounded output it does so by one bfloat16 step.  How often that happens follows from the
+    arithmetic: two float32 accumulations of K products in different orders differ by about sqrt(K) * 2^-24 relative,
+    a bfloat16 rounding boundary is hit when that difference straddles it, i.e. with probability of the order of
+    sqrt(K) * 2^-24 / 2^-9 -- 0.2 % at K = 4096 (measured: 0.25 % without ReLU, which zeroes half the outputs)."""
+    K = ins[0].shape[1]
     d32 = copy.deepcopy(d)
     last_is_cast = d32["op_desc"][-1]["name"] == "Cast"
     if last_is_cast:
@@ -187,7 +193,7 @@ def check_matmul(d, ins, got_bf16, rows=None):
     wi = want.view(np.uint16).astype(np.int32)
     diff = np.abs(gi - wi)
     assert diff.max() <= 1 or np.all(np.abs(g - want.astype(np.float64))[diff > 1] <= atol)
-    assert (diff > 0).mean() < 2e-3
+    assert (diff > 0).mean() < max(2e-3, 3.0 * np.sqrt(K) * 2.0 ** -15)
 
 
 @pytest.mark.parametrize("m,k,n,tb,bias,relu,f32_out", [

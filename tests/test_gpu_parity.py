@@ -117,6 +117,25 @@ def test_column_sum_and_global_max(lib, rows, cols):
     assert got[1][0] == x.max()
 
 
+@pytest.mark.parametrize("rows,cols", [(4096, 4096), (1000, 52), (70000, 16), (513, 1030), (20000, 3000)])
+def test_fold_by_the_last_cta_gives_the_bits_of_the_fold_in_a_second_launch(lib, rows, cols):
+    """AKGB_FLAG_FOLD_IN_LAUNCH: the CTA that arrives last folds the row splits (arrival counters that every launch
+    leaves at zero, so launches repeat); same order of operations, same bits, one launch less per fold."""
+    from akg_b200 import _capi
+    x = make_inputs(descs.reduce_sum_axis0(rows, cols), 19)[0]
+    for build in (descs.reduce_sum_axis0, descs.reduce_max_all, descs.reduce_sum_and_max):
+        want, k0 = run_host(build(rows, cols), [x])
+        k1 = FusedKernel(build(rows, cols), flags=_capi.AKGB_FLAG_FOLD_IN_LAUNCH)
+        assert k1.launch_count < k0.launch_count or k0.launch_count == 1
+        for _ in range(3):  # the counters are back at zero after every launch
+            got = k1.empty_outputs()
+            for o in got:
+                o.view(np.uint8)[...] = 0xCD
+            k1.run_host([x] + got)
+            for g, w in zip(got, want):
+                assert bits_equal(g, w)
+
+
 def test_row_reductions_and_other_combiners(lib):
     import json
     x = make_inputs(descs.reduce_sum_axis0(300, 260), 15)[0]
