@@ -176,8 +176,8 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
   for (size_t si = 0; si < plan.steps.size(); ++si) {
     Step& st = plan.steps[si];
     const FinishExchange* sfx = ((int)si == fx_step) ? fx : nullptr;
-    // arrival counters: the reduction folds its partials itself (always when it carries an exchange)
-    uint32_t* tickets = (k->fold_in_launch || sfx) ? k->d_tickets : nullptr;
+    // arrival counters: the last CTA of a reduction folds its partials (AKGB_FLAG_FOLD_IN_LAUNCH); else a fold launch
+    uint32_t* tickets = k->fold_in_launch ? k->d_tickets : nullptr;
     cudaError_t e = cudaSuccess;
     void* a = resolve(st.a, tensors, ws);
     void* b = resolve(st.b, tensors, ws);
@@ -459,8 +459,7 @@ int fused_exchange_step(const akgb_kernel* k, const Plan& plan, FinishExchange* 
     // nothing after this step may touch the result (it is final once the finisher has written it)
     if (si + 1 != plan.steps.size()) return -1;
     if (st.kind == StepK::ReduceCol && partial.size() == 1) {
-      if (st.red_outer != 1 || st.red_inner > kExchangeSlotElems || st.red_op != op_of(k->descs[partial[0]].shard_kind) ||
-          !reduce_col_fusable(st.red_len, st.red_inner, k->sm_count))
+      if (st.red_outer != 1 || st.red_inner > kExchangeTaggedElems || st.red_op != op_of(k->descs[partial[0]].shard_kind))
         return -1;
       fx->slot_off = 0;
       fx->finishers = (int)((st.red_inner + 127) / 128);
@@ -473,7 +472,7 @@ int fused_exchange_step(const akgb_kernel* k, const Plan& plan, FinishExchange* 
       return (int)si;
     }
     if (st.kind == StepK::ReduceColDual && partial.size() == 2 && st.out2.arg == partial[1]) {
-      if (st.red_inner + 1 > kExchangeSlotElems || st.red_inner % 4 != 0 ||
+      if (st.red_inner + 1 > kExchangeTaggedElems || st.red_inner % 4 != 0 ||
           st.red_op != op_of(k->descs[partial[0]].shard_kind) || st.red_op2 != op_of(k->descs[partial[1]].shard_kind))
         return -1;
       fx->slot_off = 0;

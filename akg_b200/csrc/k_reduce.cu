@@ -250,58 +250,59 @@ __global__ void __launch_bounds__(256) reduce_row_f32_kernel(const float* __rest
 }
 
 // ---- fold by the finishing CTA, optionally with the exchange over peer memory ------------------------------------
-__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
+// the number of the exchange call in progress on this rank (read early: the load overlaps the fold of the partials)
+__device__ __forceinline__ uint32_t exchange_epoch(const FinishExchange& fx) {
+  return *reinterpret_cast<volatile uint32_t*>(exchange_counter(fx.peer[fx.rank])) + 1u;
+}
 
-// Called by ALL threads of a finishing CTA (any block shape).  Thread `tid` of `nthreads` holds value `v` for slot position `pos` when
-// `active`.  Stores the values into this rank's slot of every rank's buffer, raises flag `flag` there, waits (bounded)
-// for the same flag of every rank in the own buffer and folds the slots in rank order, so that every rank gets the same
-// bits.  Returns false when the wait ran out (bit 8 of the error word is set, `v` is unchanged).  The finisher that
-// closes the call (the last of fx.finishers) advances the call counter.
+// Called by ALL threads of a finishing CTA (any block shape).  Thread `tid` holds value `v` for position `pos` of the
+// call's values when `active`.  Stores (value, call number) as one 64-bit word into this rank's slot of every rank's
+// buffer, then polls (bounded) the same position of every rank's slot in its own buffer until the word carries this
+// call's number, and folds the values in rank order, so that every rank gets the same bits.  No flag and no fence: the
+// 8-byte store is single-copy atomic, a word with the right number holds the right value.  Returns false when a wait
+// ran out (bit 8 of the error word is set, `v` is unchanged).  The finisher that closes the call (the last of
+// fx.finishers) advances the call counter.
 template <class Op>
-__device__ __forceinline__ bool finish_exchange(const FinishExchange& fx, float& v, bool active, int pos, int flag,
+__device__ __forceinline__ bool finish_exchange(const FinishExchange& fx, uint32_t epoch, float& v, bool active, int pos,
                                                 int tid) {
   void* own = fx.peer[fx.rank];
-  uint32_t* counter = exchange_counter(own);
-  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(counter) + 1u;
   const int par = (int)(epoch & 1u);
-  if (active)
-    for (int q = 0; q < fx.world; ++q) exchange_slot(fx.peer[q], par, fx.rank)[pos] = v;
-  __threadfence_system();
-  __syncthreads();
   int timed_out = 0;
-  if (tid < fx.world) {
-    st_release_sys_u32(exchange_flag(fx.peer[tid], par, fx.rank, flag), epoch);
-    const uint32_t* f = exchange_flag(own, par, tid, flag);
+  if (active) {
+    const unsigned long long word = ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(v);
+    for (int q = 0; q < fx.world; ++q) st_relaxed_sys_u64(exchange_tagged(fx.peer[q], par, fx.rank) + pos, word);
+    float r = 0.f;
     const long long t0 = clock64();
-    while (ld_acquire_sys_u32(f) != epoch) {
-      if (clock64() - t0 > fx.limit_cycles) {
-        timed_out = 1;
-        break;
+    for (int q = 0; q < fx.world && !timed_out; ++q) {
+      const unsigned long long* src = exchange_tagged(own, par, q) + pos;
+      unsigned long long w = ld_relaxed_sys_u64(src);
+      while ((uint32_t)(w >> 32) != epoch) {
+        if (clock64() - t0 > fx.limit_cycles) {
+          timed_out = 1;
+          break;
+        }
+        __nanosleep(20);
+        w = ld_relaxed_sys_u64(src);
       }
-      __nanosleep(32);
+      const float x = __uint_as_float((uint32_t)w);
+      r = q == 0 ? x : Op::apply(r, x);
     }
+    if (!timed_out) v = r;
   }
   const bool failed = __syncthreads_or(timed_out) != 0;
-  if (failed) {
-    if (tid == 0) atomicOr(fx.err, 256u);
-  } else if (active) {
-    float r = *reinterpret_cast<volatile float*>(exchange_slot(own, par, 0) + pos);
-    for (int q = 1; q < fx.world; ++q)
-      r = Op::apply(r, *reinterpret_cast<volatile float*>(exchange_slot(own, par, q) + pos));
-    v = r;
-  }
-  __syncthreads();
   if (tid == 0) {
+    if (failed) atomicOr(fx.err, 256u);
+    uint32_t* counter = exchange_counter(own);
     uint32_t* ticket = counter + 1;
-    if (atomicAdd(ticket, 1u) == (uint32_t)fx.finishers - 1u) {
-      *ticket = 0;
+    if (atomicInc(ticket, (uint32_t)fx.finishers - 1u) == (uint32_t)fx.finishers - 1u) {  // wraps to 0 by itself
       __threadfence();
       *reinterpret_cast<volatile uint32_t*>(counter) = epoch;
     }
@@ -332,18 +333,20 @@ __device__ __forceinline__ void finish_col_tile(const float* partial, float* out
                                                 int tile, int tid, const FinishExchange& fx) {
   const int64_t c = (int64_t)tile * kColTile + tid;
   const bool active = tid < kColTile && c < inner;
+  const uint32_t epoch = fx.world > 1 ? exchange_epoch(fx) : 0u;
   float a = Op::identity();
   if (active)
     for (int64_t s = 0; s < splits; ++s) a = Op::apply(a, __ldcg(partial + s * inner + c));
   // when the wait runs out the value stays this rank's own partial (and the error word says so)
-  if (fx.world > 1) finish_exchange<Op>(fx, a, active, fx.slot_off + (int)c, tile, tid);
+  if (fx.world > 1) finish_exchange<Op>(fx, epoch, a, active, fx.slot_off + (int)c, tid);
   if (active) out[c] = a;
 }
 
 // fold of partial[n] by a 256-thread CTA in a fixed order, then the exchange of the one value, then the store
 template <class Op>
 __device__ __forceinline__ void finish_all(const float* partial, float* out, int n, int tid, float* red,
-                                           const FinishExchange& fx, int slot_pos, int flag) {
+                                           const FinishExchange& fx, int slot_pos) {
+  const uint32_t epoch = fx.world > 1 ? exchange_epoch(fx) : 0u;
   float a = Op::identity();
   for (int i = tid; i < n; i += 256) a = Op::apply(a, __ldcg(partial + i));
   // block_reduce by linear thread id (the CTA may be 32x8)
@@ -353,7 +356,7 @@ __device__ __forceinline__ void finish_all(const float* partial, float* out, int
   __syncthreads();
   float r = (tid & 31) < 8 ? red[tid & 31] : Op::identity();
   r = warp_reduce<Op>(r);
-  if (fx.world > 1) finish_exchange<Op>(fx, r, tid == 0, slot_pos, flag, tid);
+  if (fx.world > 1) finish_exchange<Op>(fx, epoch, r, tid == 0, slot_pos, tid);
   if (tid == 0) out[0] = r;
 }
 
@@ -486,7 +489,7 @@ __global__ void __launch_bounds__(kColTx* kColTy) reduce_col_dual_fused_f32_kern
   if (last_of_tile) finish_col_tile<Op1>(partial, out1, gridDim.y, inner, blockIdx.x, tid, fx);
   const bool last_of_grid = arrive_last(tickets + gridDim.x, gridDim.x * gridDim.y, tid);
   if (last_of_grid)
-    finish_all<Op2>(partial2, out2, (int)(gridDim.x * gridDim.y), tid, red2, fx, fx.slot_off2, (int)gridDim.x);
+    finish_all<Op2>(partial2, out2, (int)(gridDim.x * gridDim.y), tid, red2, fx, fx.slot_off2);
 }
 
 // reduce_all_f32_kernel + fold by the last CTA (+ exchange)
@@ -524,7 +527,22 @@ __global__ void __launch_bounds__(256) reduce_all_fused_f32_kernel(const float* 
   a = block_reduce<Op>(a, red);
   if (threadIdx.x == 0) partial[blockIdx.x] = a;
   if (!arrive_last(tickets, gridDim.x, threadIdx.x)) return;
-  finish_all<Op>(partial, out, (int)gridDim.x, threadIdx.x, red, fx, fx.slot_off, 0);
+  finish_all<Op>(partial, out, (int)gridDim.x, threadIdx.x, red, fx, fx.slot_off);
+}
+
+// The fold of the partials as a launch of its own that also completes the exchange: one CTA per finisher.
+// grid = column tiles (+ 1 CTA for the all-elements result when `partial2` is given), 256 threads.
+template <class Op1, class Op2>
+__global__ void __launch_bounds__(256) reduce_finish_exchange_kernel(const float* __restrict__ partial,
+                                                                     float* __restrict__ out, int64_t splits,
+                                                                     int64_t inner, int col_tiles,
+                                                                     const float* __restrict__ partial2,
+                                                                     float* __restrict__ out2, int n2,
+                                                                     FinishExchange fx) {
+  __shared__ float red[32];
+  const int tid = threadIdx.x;
+  if ((int)blockIdx.x < col_tiles) finish_col_tile<Op1>(partial, out, splits, inner, blockIdx.x, tid, fx);
+  else finish_all<Op2>(partial2, out2, n2, tid, red, fx, fx.slot_off2);
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -545,7 +563,7 @@ cudaError_t col_impl(const float* x, float* out, int64_t red, int64_t inner, voi
   float* partial = splits == 1 ? out : reinterpret_cast<float*>(ws);
   const bool vec = inner % 4 == 0 && aligned16(x);
   const bool fused = tickets && splits > 1 && grid.x <= (unsigned)kReduceMaxTicketTiles;
-  if (fx && fx->world > 1 && !fused) return cudaErrorNotSupported;  // the caller asks reduce_col_fusable() first
+  const bool exchange = fx && fx->world > 1;
   if (fused) {
     FinishExchange none;
     const FinishExchange& f = fx ? *fx : none;
@@ -560,7 +578,13 @@ cudaError_t col_impl(const float* x, float* out, int64_t red, int64_t inner, voi
   else
     reduce_col_f32_kernel<Op, false><<<grid, block, 0, s>>>(x, partial, red, inner, rows_per_split);
   cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess || splits == 1) return e;
+  if (e != cudaSuccess) return e;
+  if (exchange) {  // the fold of the splits (a single split: the result itself) and the exchange in one launch
+    reduce_finish_exchange_kernel<Op, Op><<<grid.x, 256, 0, s>>>(partial, out, splits, inner, (int)grid.x, nullptr,
+                                                                 nullptr, 0, *fx);
+    return cudaGetLastError();
+  }
+  if (splits == 1) return e;
   reduce_col_finish_kernel<Op><<<(unsigned)((inner + 255) / 256), 256, 0, s>>>(partial, out, splits, inner);
   return cudaGetLastError();
 }
@@ -576,7 +600,6 @@ cudaError_t all_impl(const float* x, float* out, int64_t n, void* ws, int sm_cou
     dims->block[0] = 256;
   }
   float* partial = reinterpret_cast<float*>(ws);
-  if (fx && fx->world > 1 && !tickets) return cudaErrorNotSupported;
   if (tickets) {
     FinishExchange none;
     const FinishExchange& f = fx ? *fx : none;
@@ -588,6 +611,12 @@ cudaError_t all_impl(const float* x, float* out, int64_t n, void* ws, int sm_cou
   else reduce_all_f32_kernel<Op, false><<<grid, 256, 0, s>>>(x, partial, n);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
+  if (fx && fx->world > 1) {
+    FinishExchange f = *fx;
+    f.slot_off2 = f.slot_off;  // the one result sits at the first output's slot position, flag 0
+    reduce_finish_exchange_kernel<Op, Op><<<1, 256, 0, s>>>(nullptr, nullptr, 0, 0, 0, partial, out, grid, f);
+    return cudaGetLastError();
+  }
   reduce_all_finish_kernel<Op><<<1, 1024, 0, s>>>(partial, out, grid);
   return cudaGetLastError();
 }
@@ -617,6 +646,7 @@ size_t reduce_all_workspace(int sm_count) { return (size_t)sm_count * 8 * sizeof
 bool reduce_col_fusable(int64_t red, int64_t inner, int sm_count) {
   return col_row_splits(red, inner, sm_count) > 1 && (inner + kColTile - 1) / kColTile <= kReduceMaxTicketTiles;
 }
+
 int reduce_col_launches(int64_t red, int64_t inner, int sm_count, bool tickets) {
   if (col_row_splits(red, inner, sm_count) == 1) return 1;
   return tickets && reduce_col_fusable(red, inner, sm_count) ? 1 : 2;
@@ -639,7 +669,6 @@ cudaError_t dual_impl(const float* x, float* out1, float* out2, int64_t red, int
   float* partial = reinterpret_cast<float*>(ws);
   float* partial2 = partial + splits * inner;
   const bool fused = tickets && grid.x <= (unsigned)kReduceMaxTicketTiles;
-  if (fx && fx->world > 1 && !fused) return cudaErrorNotSupported;
   if (fused) {
     FinishExchange none;
     reduce_col_dual_fused_f32_kernel<Op1, Op2><<<grid, block, 0, s>>>(x, partial, partial2, out1, out2, red, inner,
@@ -649,6 +678,11 @@ cudaError_t dual_impl(const float* x, float* out1, float* out2, int64_t red, int
   reduce_col_dual_f32_kernel<Op1, Op2><<<grid, block, 0, s>>>(x, partial, partial2, red, inner, rows_per_split);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
+  if (fx && fx->world > 1) {  // both folds and both exchanges in one launch
+    reduce_finish_exchange_kernel<Op1, Op2><<<grid.x + 1, 256, 0, s>>>(partial, out1, splits, inner, (int)grid.x, partial2,
+                                                                       out2, (int)(grid.x * grid.y), *fx);
+    return cudaGetLastError();
+  }
   reduce_col_finish_kernel<Op1><<<(unsigned)((inner + 255) / 256), 256, 0, s>>>(partial, out1, splits, inner);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;

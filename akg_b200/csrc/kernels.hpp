@@ -60,9 +60,10 @@ cudaError_t softmax_rows(const SoftmaxParams& p, const void* x, const void* mask
 // A reduction whose per-CTA partials are folded by the CTA that finishes last ("finisher": one per column tile, one for
 // a reduction of all elements) needs no second launch.  The finishers are found with arrival counters (`tickets`,
 // kReduceTicketWords zero-initialised words that every launch leaves at zero again; launches that share them must be
-// ordered on the device).  With an exchange attached, each finisher also completes the all-reduce of its values over
-// the ranks' mapped exchange buffers (layout below): peer stores, a flag per finisher, a bounded wait, a fold in rank
-// order.  The result is written by the finisher, so a sharded reduction is ONE launch on every rank.
+// ordered on the device).  Without `tickets` the fold is a second, small launch with one CTA per finisher.  With an
+// exchange attached, each finisher (in either form) also completes the all-reduce of its values over the ranks' mapped
+// exchange buffers (layout below): every value goes to every rank as one 64-bit word tagged with the call number, the
+// finisher polls (bounded) the words of the other ranks and folds them in rank order, then writes the final result.
 constexpr int kReduceMaxTicketTiles = 4096;
 constexpr int kReduceTicketWords = kReduceMaxTicketTiles + 8;
 struct FinishExchange {
@@ -75,7 +76,7 @@ struct FinishExchange {
   int finishers = 0;            // finishers of the launch: the last one closes the call
 };
 // x[outer, red, inner] -> out[outer, inner]; f32 only.  With `tickets` the fold of the row splits happens in the same
-// launch (see above); `fx` (needs `tickets`, several row splits and reduce_col_fusable()) adds the exchange.
+// launch (see above) when reduce_col_fusable(); `fx` adds the exchange to the fold, wherever it happens.
 size_t reduce_col_workspace(int64_t red, int64_t inner, int sm_count);
 bool reduce_col_fusable(int64_t red, int64_t inner, int sm_count);
 int reduce_col_launches(int64_t red, int64_t inner, int sm_count, bool tickets);
@@ -119,15 +120,23 @@ cudaError_t ew_jit_launch(const EwProgram& p, const void* const* in, void* const
 
 // ---- exchange over peer memory -----------------------------------------------------------------
 // Layout of one rank's exchange buffer: [2 parities][kExchangeMaxRanks slots][kExchangeSlotElems floats], then the flags
-// [2][kExchangeMaxRanks][kExchangeMaxFlags] uint32.
-// kExchangeMaxFlags flags per (parity, rank): the stand-alone exchange kernel raises one per CTA (at most
-// kExchangeMaxCtas), a reduction that carries its own exchange one per finisher (a column tile of 128 values, or the
-// single result of a reduction of all elements).
-constexpr int kExchangeMaxRanks = 8, kExchangeSlotElems = 16384, kExchangeMaxCtas = 16, kExchangeMaxFlags = 136;
+// [2][kExchangeMaxRanks][kExchangeMaxFlags] uint32 (the exchange kernel raises one flag per CTA).
+constexpr int kExchangeMaxRanks = 8, kExchangeSlotElems = 16384, kExchangeMaxCtas = 16, kExchangeMaxFlags = 16;
 constexpr size_t kExchangeDataBytes = (size_t)2 * kExchangeMaxRanks * kExchangeSlotElems * sizeof(float);
 constexpr size_t kExchangeFlagBytes = (size_t)2 * kExchangeMaxRanks * kExchangeMaxFlags * sizeof(uint32_t);
-// after the flags: the call counter (epoch) and the ticket that lets the last CTA of a call advance it
-constexpr size_t kExchangeBytes = kExchangeDataBytes + kExchangeFlagBytes + 2 * sizeof(uint32_t);
+// after the flags: the call counter (epoch) and the ticket that lets the last CTA of a call advance it; then, 256-byte
+// aligned, the region of the exchanges that reductions complete themselves: [2 parities][kExchangeMaxRanks]
+// [kExchangeTaggedElems] 64-bit words, each a float32 value with the call number it belongs to in the upper half.  Value
+// and tag travel in ONE 8-byte store, so a receiver that sees the tag has the value: no flag, no fence, one NVLink
+// crossing on the critical path.
+constexpr int kExchangeTaggedElems = 8192;
+constexpr size_t kExchangeTaggedOffset = (kExchangeDataBytes + kExchangeFlagBytes + 2 * sizeof(uint32_t) + 255) / 256 * 256;
+constexpr size_t kExchangeTaggedBytes = (size_t)2 * kExchangeMaxRanks * kExchangeTaggedElems * sizeof(unsigned long long);
+constexpr size_t kExchangeBytes = kExchangeTaggedOffset + kExchangeTaggedBytes;
+__host__ __device__ inline unsigned long long* exchange_tagged(void* base, int parity, int rank) {
+  return reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(base) + kExchangeTaggedOffset) +
+         ((size_t)parity * kExchangeMaxRanks + rank) * kExchangeTaggedElems;
+}
 __host__ __device__ inline float* exchange_slot(void* base, int parity, int rank) {
   return reinterpret_cast<float*>(base) + ((size_t)parity * kExchangeMaxRanks + rank) * kExchangeSlotElems;
 }

@@ -184,6 +184,8 @@ def time_launches(kernel, buffer_sets, steps, warmup, barrier=None, use_graph=Tr
     """
     import torch
     stream = torch.cuda.Stream()
+    if barrier:
+        barrier()  # ranks start their warm-up together: a step with an exchange waits (bounded) for its peers
     with torch.cuda.stream(stream):
         for i in range(warmup):
             kernel.launch(buffer_sets[i % len(buffer_sets)], stream)
@@ -213,6 +215,14 @@ def time_launches(kernel, buffer_sets, steps, warmup, barrier=None, use_graph=Tr
         if barrier:
             barrier()
     return t0.elapsed_time(t1) / steps
+
+
+def device_error_word(kernel):
+    """Reads and clears the device error word through the C ABI without turning a non-zero word into an exception."""
+    import ctypes
+    word = ctypes.c_uint32(0)
+    kernel._lib.akgb_check_device_error(kernel._handle, ctypes.byref(word))
+    return int(word.value)
 
 
 def allreduce_scalar(x, world, op="max"):
@@ -369,23 +379,29 @@ def run_classes(rank, world, device, steps, warmup, hbm_peak, tf_peak, barrier, 
         # NCCL calls are not captured into the graph; the library's own exchange runs inside ordinary kernels and is
         graphable = exchange in ("none", "peer-kernel", "in-reduction")
         ms = time_launches(_K, sets, steps, warmup, barrier, use_graph=graphable)
+        word = device_error_word(k)  # bounded device-side waits that gave up (0 = none); bit 8: a peer-memory exchange
         if exchange in ("peer-kernel", "in-reduction"):
-            # a bounded wait that ran out on any rank: NCCL carries the exchange from here on (on every rank)
-            try:
-                bad = 1 if k.check_device_error() else 0
-            except Exception:
-                bad = 1
-            if allreduce_scalar(float(bad), world) > 0:
+            # a wait that ran out on any rank: NCCL carries the exchange from here on (on every rank)
+            if allreduce_scalar(float(word != 0), world) > 0:
                 comm.disable_peer_exchange()
                 exchange = "nccl (after a peer-memory wait ran out)"
                 ms = time_launches(_K, sets, steps, warmup, barrier, use_graph=False)
         ms_max = allreduce_scalar(ms, world)
+        alone = None
+        if partial and comm is not None:
+            # the same shard on the same rank without the exchange step: what the exchange costs on top
+            alone = allreduce_scalar(time_launches(k, sets, steps, warmup, barrier), world)
         bytes_job = k.bytes * world   # the ranks' shares add up to the global shape
         flops_job = k.flops * world
         row = {"class": k.op_class, "ms": round(ms_max, 5), "launches_per_step": k.launch_count,
                "per_gpu_lead": k.inputs[0].shape[0], "buffer_sets": len(sets)}
         if partial:
             row["exchange"] = exchange
+        if alone is not None:
+            row["ms_without_exchange"] = round(alone, 5)
+            row["exchange_us"] = round((ms_max - alone) * 1e3, 2)
+        if word:
+            row["device_error_word"] = word
         if k.flops:
             tf = flops_job / (ms_max * 1e-3) / 1e12
             row.update({"tflops": round(tf, 2), "frac_of_peak": round(tf / world / tf_peak, 4), "bound": "tensor"})

@@ -207,8 +207,8 @@ akgb_status akgb_comm_set_peer_exchange(akgb_comm* c, int32_t enabled);
 akgb_status akgb_comm_exchange_handle(akgb_comm* c, void* handle, size_t cap);
 akgb_status akgb_comm_attach_peers(akgb_comm* c, const void* handles, size_t bytes);
 akgb_status akgb_comm_set_timeout_ms(akgb_comm* c, double ms);
-/* Whether a reduction that produces all partial outputs of a kernel completes the exchange inside its own launch
- * (see akgb_launch_sharded) or leaves it to the exchange kernel / NCCL after the launch.  Every rank must choose the
+/* Whether a reduction that produces all partial outputs of a kernel completes the exchange inside its fold step
+ * (see akgb_launch_sharded; the default) or leaves it to the exchange kernel / NCCL after the launch.  Every rank must choose the
  * same. */
 akgb_status akgb_comm_set_exchange_in_reduction(akgb_comm* c, int32_t enabled);
 
@@ -216,10 +216,12 @@ akgb_status akgb_comm_set_exchange_in_reduction(akgb_comm* c, int32_t enabled);
  * shard_kind is a partial; one NCCL group for all of them.  No-op for kernels without partial outputs. */
 akgb_status akgb_allreduce_partials(const akgb_kernel* k, akgb_comm* c, void* const* tensors, void* stream);
 /* The kernel and the exchange of its partial outputs on one stream.  Where ONE reduction (column, all-elements, or both
- * in one pass) produces all partial outputs and the peers' buffers are attached, the reduction completes the exchange in
- * its own launch: the CTA that folds a tile of the result stores it into every rank's buffer, waits (bounded) for the
- * other ranks' tiles and folds them in rank order -- one kernel per rank and step.  Otherwise: akgb_launch followed by
- * akgb_allreduce_partials.  After a sharded step every rank should read akgb_check_device_error: once a bounded wait has
+ * in one pass) produces all partial outputs and the peers' buffers are attached, the reduction's fold step completes
+ * the exchange (results of up to 8192 float32 elements): the CTA that folds a tile of the per-CTA partials stores each
+ * value, tagged with the call number, into every rank's buffer as one 8-byte word, polls (bounded) the other ranks'
+ * words and folds them in rank order -- two launches per rank and step (the reduction and its fold; one with
+ * AKGB_FLAG_FOLD_IN_LAUNCH) instead of reduction, fold and exchange kernel.  Otherwise:
+ * akgb_launch followed by akgb_allreduce_partials.  After a sharded step every rank should read akgb_check_device_error: once a bounded wait has
  * run out on a device (AKGB_DEVICE_TIMEOUT, bit 8), further peer-memory exchanges there are refused with
  * AKGB_DEVICE_TIMEOUT until akgb_comm_set_peer_exchange has been called on ALL ranks (1: restart the path, 0: continue
  * over NCCL) and the ranks have synchronised. */
@@ -229,7 +231,7 @@ akgb_status akgb_launch_sharded(akgb_kernel* k, akgb_comm* c, void* const* tenso
 #define AKGB_EXCHANGE_NONE 0          /* no partial outputs, or a single rank */
 #define AKGB_EXCHANGE_NCCL 1          /* ncclAllReduce after the kernel */
 #define AKGB_EXCHANGE_PEER_KERNEL 2   /* one exchange kernel over the ranks' mapped buffers after the kernel */
-#define AKGB_EXCHANGE_IN_REDUCTION 3  /* inside the reduction's own launch (see akgb_launch_sharded) */
+#define AKGB_EXCHANGE_IN_REDUCTION 3  /* inside the reduction's fold step (see akgb_launch_sharded) */
 int32_t akgb_sharded_exchange_kind(const akgb_kernel* k, const akgb_comm* c);
 
 /* Directory of the on-disk cache of run-time compiled kernels.  The reference keeps its compiled kernels

@@ -56,12 +56,14 @@ def main():
     timings = {}
     if peer:
         big = torch.randn(65536 // world, 4096, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3 + rank))
-        for in_reduction in (True, False):
+        # three ways: the reduction's fold launch carries the exchange (default), the last CTA of the reduction itself
+        # does (AKGB_FLAG_FOLD_IN_LAUNCH), one exchange kernel after the kernel's own launches
+        for label, in_reduction, flags in (("fold launch", True, 0), ("last CTA", True, 2), ("exchange kernel", False, 0)):
             comm.set_exchange_in_reduction(in_reduction)
             for build, ref in ((descs.reduce_sum_axis0, lambda t: t.double().sum(0)),
                                (descs.reduce_max_all, lambda t: t.max().reshape(1)),
                                (descs.reduce_sum_and_max, None)):
-                k = FusedKernel(build(rows, cols), device=local, shard_rank=rank, shard_world=world)
+                k = FusedKernel(build(rows, cols), device=local, shard_rank=rank, shard_world=world, flags=flags)
                 ok = ok and comm.exchange_kind(k) == ("in-reduction" if in_reduction else "peer-kernel")
                 outs = [torch.empty(t.shape, dtype=torch.float32, device="cuda") for t in k.outputs]
                 for _ in range(5):  # several calls, both parities of the exchange buffer
@@ -78,7 +80,7 @@ def main():
                     dist.all_gather(gathered, o)
                     ok = ok and all(bool(torch.equal(g_, gathered[0])) for g_ in gathered)
                 # the benchmark's split: [65536 / world, 4096] per rank, replayed from a CUDA graph
-                kb = FusedKernel(build(65536, 4096), device=local, shard_rank=rank, shard_world=world)
+                kb = FusedKernel(build(65536, 4096), device=local, shard_rank=rank, shard_world=world, flags=flags)
                 ob = [torch.empty(t.shape, dtype=torch.float32, device="cuda") for t in kb.outputs]
                 s = torch.cuda.Stream()
                 with torch.cuda.stream(s):
@@ -98,7 +100,7 @@ def main():
                     t1.record(s)
                     torch.cuda.synchronize()
                 ok = ok and kb.check_device_error() == 0
-                timings[(build.__name__, in_reduction)] = t0.elapsed_time(t1) / 10 * 1e3
+                timings[(build.__name__, label)] = t0.elapsed_time(t1) / 10 * 1e3
                 for o, d in zip(ob, kb.outputs):
                     if d.shard_kind == 2:  # column sums
                         part = big.double().sum(0)
@@ -123,9 +125,8 @@ def main():
     ok = ok and bool(torch.allclose(obm.cpu().double(), want_bm, rtol=2e-3, atol=2e-3 * float(want_bm.abs().max())))
     if rank == 0:
         print("PEER_EXCHANGE", "on" if peer else "off", flush=True)
-        for (name, in_red), us in sorted(timings.items()):
-            print(f"TIMING {name} [65536/{world},4096] per rank, exchange {'in-reduction' if in_red else 'peer-kernel'}: "
-                  f"{us:.1f} us per step", flush=True)
+        for (name, label), us in sorted(timings.items()):
+            print(f"TIMING {name} [65536/{world},4096] per rank, exchange by {label}: {us:.1f} us per step", flush=True)
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     comm.close()
