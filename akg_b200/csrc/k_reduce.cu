@@ -162,6 +162,24 @@ __global__ void __launch_bounds__(kColTx* kColTy) reduce_col_dual_f32_kernel(con
   }
 }
 
+// Fold of column c over the row splits, in split order.  The loads of eight splits are issued together (they do not
+// depend on one another), the combines stay one after the other, so the result has the bits of the plain loop.
+template <class Op>
+__device__ __forceinline__ float fold_splits(const float* __restrict__ partial, int64_t splits, int64_t inner, int64_t c) {
+  float a = Op::identity();
+  const float* p = partial + c;
+  int64_t s = 0;
+  for (; s + 8 <= splits; s += 8) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = __ldcg(p + (s + u) * inner);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) a = Op::apply(a, v[u]);
+  }
+  for (; s < splits; ++s) a = Op::apply(a, __ldcg(p + s * inner));
+  return a;
+}
+
 // partial[splits, inner] -> out[inner], fixed order
 template <class Op>
 __global__ void __launch_bounds__(256) reduce_col_finish_kernel(const float* __restrict__ partial,
@@ -169,9 +187,7 @@ __global__ void __launch_bounds__(256) reduce_col_finish_kernel(const float* __r
                                                                 int64_t inner) {
   const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= inner) return;
-  float a = Op::identity();
-  for (int64_t s = 0; s < splits; ++s) a = Op::apply(a, partial[s * inner + c]);
-  out[c] = a;
+  out[c] = fold_splits<Op>(partial, splits, inner, c);
 }
 
 // x[n] -> partial[grid]
@@ -335,8 +351,7 @@ __device__ __forceinline__ void finish_col_tile(const float* partial, float* out
   const bool active = tid < kColTile && c < inner;
   const uint32_t epoch = fx.world > 1 ? exchange_epoch(fx) : 0u;
   float a = Op::identity();
-  if (active)
-    for (int64_t s = 0; s < splits; ++s) a = Op::apply(a, __ldcg(partial + s * inner + c));
+  if (active) a = fold_splits<Op>(partial, splits, inner, c);
   // when the wait runs out the value stays this rank's own partial (and the error word says so)
   if (fx.world > 1) finish_exchange<Op>(fx, epoch, a, active, fx.slot_off + (int)c, tid);
   if (active) out[c] = a;
