@@ -162,6 +162,10 @@ def test_row_reductions_and_other_combiners(lib):
     ([2, 64, 4, 128], [0, 2, 1, 3], "float16"), ([6, 10], [1, 0], "float32"), ([3, 5, 7], [2, 0, 1], "float16"),
     ([2, 3, 4, 5, 6], [4, 2, 0, 3, 1], "int8"), ([1, 9, 1, 8], [3, 1, 2, 0], "float32"), ([130, 70], [1, 0], "float16"),
     ([4, 8, 16], [0, 1, 2], "float32"), ([2, 33, 65], [0, 2, 1], "int64"),
+    # tile mode with 16-byte loads and 128-byte stores (2- and 4-byte elements), whole and ragged tiles, batches
+    ([256, 192], [1, 0], "float16"), ([100, 64], [1, 0], "float32"), ([3, 72, 40], [0, 2, 1], "float16"),
+    ([2, 3, 64, 48], [0, 1, 3, 2], "float32"), ([5, 128, 8], [2, 0, 1], "int16"), ([1000, 1016], [1, 0], "float16"),
+    ([7, 36, 260], [0, 2, 1], "int32"), ([4, 6, 8, 24], [2, 0, 3, 1], "float16"), ([2, 130, 72], [0, 2, 1], "float16"),
 ])
 def test_transpose_bit_exact(lib, shape, perm, dt):
     d = descs.transpose(shape, perm, dt)
