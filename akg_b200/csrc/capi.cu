@@ -90,6 +90,20 @@ struct akgb_kernel {
   // arrival counters of the reductions that fold their partials in the launch that produced them (k_reduce.cu);
   // allocated zeroed on the first launch of a plan with such a step, left at zero by every launch
   uint32_t* d_tickets = nullptr;
+  // a sharded region cut into stages at the reductions over the split axis that feed later ops (stages.cpp): every
+  // stage is a kernel of its own; a stage argument is one of this kernel's arguments (`arg` >= 0) or a carried value
+  // (a completed partial of an earlier stage) at `ws_off` of the workspace
+  struct StageArg {
+    int arg = -1;
+    int64_t ws_off = -1;
+  };
+  struct Stage {
+    akgb_kernel* k = nullptr;
+    std::vector<StageArg> args;  // the stage kernel's inputs then outputs
+  };
+  std::vector<Stage> stages;
+  size_t stage_ws_off = 0;  // the stages' own workspace starts here (after the carried values)
+  ~akgb_kernel();
 };
 
 namespace {
@@ -292,6 +306,7 @@ const Plan& active_plan(const akgb_kernel* k) {
 
 int launches_of(const akgb_kernel* k) {
   int n = 0;
+  for (auto& st : k->stages) n += launches_of(st.k);
   for (const Step& st : active_plan(k).steps) {
     switch (st.kind) {
       case StepK::ReduceCol:  // the fold of the row splits happens in the launch that produced them
@@ -520,6 +535,184 @@ uint32_t* akgb::kernel_error_word(akgb_kernel* k) {
   return g_dev[k->device].err_word;
 }
 
+namespace {
+// plan + argument descriptions of k->graph (already parsed) for k's shard
+void plan_and_describe(akgb_kernel* k) {
+  if (k->graph.dynamic) {
+    if (k->shard_world > 1) throw Unsupported("dynamic-shape regions cannot be sharded at compile time");
+    for (auto& n : k->graph.nodes)
+      if (n.kind == OpK::Unknown) throw Unsupported("operator '" + n.name + "' is not supported");
+    k->plan.klass = "dynamic";
+  } else {
+    infer_sharding(k->graph, k->shard_rank, k->shard_world);
+    k->plan = build_plan(k->graph, k->sm_count, !k->no_jit);
+  }
+  const Graph& g = k->graph;
+  k->n_inputs = (int)g.inputs.size();
+  k->descs.clear();
+  auto add = [&](int vid, bool is_out) {
+    const Value& v = g.v(vid);
+    akgb_tensor_desc d;
+    std::memset(&d, 0, sizeof(d));
+    std::snprintf(d.name, sizeof(d.name), "%s", v.name.c_str());
+    d.dtype = (int32_t)v.dt;
+    d.rank = (int32_t)std::min<size_t>(v.shape.size(), AKGB_MAX_RANK);
+    if (v.shape.size() > AKGB_MAX_RANK) throw Unsupported("tensor rank above 8");
+    for (int i = 0; i < d.rank; ++i) d.shape[i] = v.shape[i];
+    d.nbytes = v.numel() * (int64_t)dt_size(v.dt);
+    for (auto e : v.shape)
+      if (e < 0) d.nbytes = -1;  // bound at launch
+    d.is_output = is_out;
+    d.shard_kind = v.partial ? v.partial : (v.split0 ? AKGB_SPLIT_AXIS0 : AKGB_REPLICATED);
+    k->descs.push_back(d);
+  };
+  for (int vid : g.inputs) add(vid, false);
+  for (int vid : g.outputs) add(vid, true);
+  for (auto& n : g.nodes)
+    if (n.kind == OpK::Assign && g.v(n.in[0]).input_index >= 0) k->descs[g.v(n.in[0]).input_index].written_in_place = 1;
+}
+
+// The region as stages (stages.cpp): every stage planned as a sharded kernel of its own.  On success k describes the
+// whole region (its arguments as the caller passes them) and holds the stage kernels.
+bool build_stages(akgb_kernel* k, const char* text, size_t len) {
+  Graph whole = parse_info(text, len);  // global shapes (k->graph may be half rewritten by the failed attempt)
+  StagePlan sp;
+  if (!split_at_sharded_reductions(whole, &sp)) return false;
+  std::vector<akgb_kernel::Stage> stages;
+  auto drop = [&] {
+    for (auto& st : stages) delete st.k;
+  };
+  try {
+    // carried values: in the caller's output when they are results of the region, else in the workspace
+    std::vector<akgb_kernel::StageArg> where(sp.carried.size());
+    size_t ws = 0;
+    const int n_in = (int)whole.inputs.size();
+    for (size_t c = 0; c < sp.carried.size(); ++c) {
+      const Value& v = whole.v(sp.carried[c]);
+      if (v.output_index >= 0) {
+        where[c].arg = n_in + v.output_index;
+      } else {
+        where[c].ws_off = (int64_t)ws;
+        ws += ((size_t)v.numel() * dt_size(v.dt) + 255) / 256 * 256;
+      }
+    }
+    k->stage_ws_off = ws;
+    size_t stage_ws = 0;
+    std::vector<akgb_tensor_desc> descs(whole.inputs.size() + whole.outputs.size());
+    std::vector<char> have(descs.size(), 0);
+    Plan summary;
+    summary.klass = "sharded_stages";
+    for (StageGraph& sg : sp.stages) {
+      akgb_kernel::Stage st;
+      st.k = new akgb_kernel();
+      stages.push_back(st);
+      akgb_kernel* sk = stages.back().k;
+      sk->device = k->device;
+      sk->sm_count = k->sm_count;
+      sk->shard_rank = k->shard_rank;
+      sk->shard_world = k->shard_world;
+      sk->no_jit = k->no_jit;
+      sk->fold_in_launch = k->fold_in_launch;
+      sk->graph = std::move(sg.g);
+      plan_and_describe(sk);
+      stage_ws = std::max(stage_ws, sk->plan.workspace_bytes);
+      summary.bytes += sk->plan.bytes;
+      summary.flops += sk->plan.flops;
+      summary.needs_gelu_lut = summary.needs_gelu_lut || sk->plan.needs_gelu_lut;
+      auto& args = stages.back().args;
+      for (size_t i = 0; i < sg.in_parent.size(); ++i) {
+        akgb_kernel::StageArg a;
+        if (sg.in_parent[i] >= 0) {
+          a.arg = sg.in_parent[i];
+          if (!have[a.arg]) {
+            descs[a.arg] = sk->descs[i];
+            have[a.arg] = 1;
+          }
+        } else {
+          a = where[sg.in_carried[i]];
+        }
+        args.push_back(a);
+      }
+      for (size_t i = 0; i < sg.out_parent.size(); ++i) {
+        akgb_kernel::StageArg a;
+        const akgb_tensor_desc& sd = sk->descs[sg.in_parent.size() + i];
+        if (sg.out_parent[i] >= 0) {
+          a.arg = n_in + sg.out_parent[i];
+          descs[a.arg] = sd;
+          // the exchange runs inside akgb_launch_sharded of this kernel: the caller gets the completed value
+          if (descs[a.arg].shard_kind >= AKGB_PARTIAL_SUM) descs[a.arg].shard_kind = AKGB_REPLICATED;
+          have[a.arg] = 1;
+        } else if (sg.out_carried[i] >= 0) {
+          a = where[sg.out_carried[i]];
+        } else {
+          throw Unsupported("a stage result is neither a result of the region nor read by a later stage");
+        }
+        if (sd.shard_kind >= AKGB_PARTIAL_SUM && sd.dtype != AKGB_FLOAT32 && sd.dtype != AKGB_FLOAT16 &&
+            sd.dtype != AKGB_BFLOAT16 && sd.dtype != AKGB_INT32)
+          throw Unsupported("partial result of a type the exchange step does not carry");
+        args.push_back(a);
+      }
+    }
+    // arguments no stage reads (dead inputs) are described whole
+    for (size_t i = 0; i < descs.size(); ++i) {
+      if (have[i]) continue;
+      const bool is_out = (int)i >= n_in;
+      const Value& v = whole.v(is_out ? whole.outputs[i - n_in] : whole.inputs[i]);
+      if (is_out) throw Unsupported("a result of the region is produced by no stage");
+      akgb_tensor_desc d;
+      std::memset(&d, 0, sizeof(d));
+      std::snprintf(d.name, sizeof(d.name), "%s", v.name.c_str());
+      d.dtype = (int32_t)v.dt;
+      d.rank = (int32_t)v.shape.size();
+      for (int r = 0; r < d.rank; ++r) d.shape[r] = v.shape[r];
+      d.nbytes = v.numel() * (int64_t)dt_size(v.dt);
+      descs[i] = d;
+    }
+    summary.workspace_bytes = ws + stage_ws;
+    k->graph = std::move(whole);
+    k->plan = std::move(summary);
+    k->descs = std::move(descs);
+    k->n_inputs = n_in;
+    k->stages = std::move(stages);
+    return true;
+  } catch (const Unsupported&) {
+    drop();
+    return false;
+  } catch (...) {
+    drop();
+    throw;
+  }
+}
+}  // namespace
+
+akgb_kernel::~akgb_kernel() {
+  for (auto& st : stages) akgb_release(st.k);
+}
+
+bool akgb::kernel_is_staged(const akgb_kernel* k) { return k && !k->stages.empty(); }
+const akgb_kernel* akgb::kernel_stage(const akgb_kernel* k, int i) {
+  return (k && i >= 0 && i < (int)k->stages.size()) ? k->stages[i].k : nullptr;
+}
+
+akgb_status akgb::launch_staged(akgb_kernel* k, akgb_comm* c, void* const* tensors, void* workspace,
+                                size_t workspace_bytes, void* stream) {
+  if (workspace_bytes < k->plan.workspace_bytes || (k->plan.workspace_bytes && !workspace))
+    return fail(AKGB_INVALID_ARG, "workspace smaller than akgb_workspace_size()");
+  if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return fail(AKGB_MISALIGNED, "workspace must be 256-byte aligned");
+  std::vector<void*> args;
+  char* ws = static_cast<char*>(workspace);
+  for (auto& st : k->stages) {
+    args.clear();
+    for (auto& a : st.args) args.push_back(a.arg >= 0 ? tensors[a.arg] : (void*)(ws + a.ws_off));
+    // the stage, then the exchange that completes its partial results, on the same stream
+    const akgb_status s = akgb_launch_sharded(st.k, c, args.data(), ws ? ws + k->stage_ws_off : nullptr,
+                                              workspace_bytes - k->stage_ws_off, stream);
+    if (s != AKGB_OK) return s;
+  }
+  return AKGB_OK;
+}
+
 extern "C" {
 
 const char* akgb_last_error(void) { return g_err.c_str(); }
@@ -553,37 +746,12 @@ akgb_status akgb_compile(const char* info_json, size_t len, const akgb_options* 
     k->fold_in_launch = (flags & AKGB_FLAG_FOLD_IN_LAUNCH) != 0;
     k->json_text.assign(info_json, len);
     k->graph = parse_info(info_json, len);
-    if (k->graph.dynamic) {
-      if (world > 1) throw Unsupported("dynamic-shape regions cannot be sharded at compile time");
-      for (auto& n : k->graph.nodes)
-        if (n.kind == OpK::Unknown) throw Unsupported("operator '" + n.name + "' is not supported");
-      k->plan.klass = "dynamic";
-    } else {
-      infer_sharding(k->graph, rank, world);
-      k->plan = build_plan(k->graph, k->sm_count, !k->no_jit);
+    try {
+      plan_and_describe(k);
+    } catch (const Unsupported&) {
+      // a reduction over the split axis that feeds later ops: stages with the exchange step between them
+      if (world <= 1 || k->graph.dynamic || !build_stages(k, info_json, len)) throw;
     }
-    const Graph& g = k->graph;
-    k->n_inputs = (int)g.inputs.size();
-    auto add = [&](int vid, bool is_out) {
-      const Value& v = g.v(vid);
-      akgb_tensor_desc d;
-      std::memset(&d, 0, sizeof(d));
-      std::snprintf(d.name, sizeof(d.name), "%s", v.name.c_str());
-      d.dtype = (int32_t)v.dt;
-      d.rank = (int32_t)std::min<size_t>(v.shape.size(), AKGB_MAX_RANK);
-      if (v.shape.size() > AKGB_MAX_RANK) throw Unsupported("tensor rank above 8");
-      for (int i = 0; i < d.rank; ++i) d.shape[i] = v.shape[i];
-      d.nbytes = v.numel() * (int64_t)dt_size(v.dt);
-      for (auto e : v.shape)
-        if (e < 0) d.nbytes = -1;  // bound at launch
-      d.is_output = is_out;
-      d.shard_kind = v.partial ? v.partial : (v.split0 ? AKGB_SPLIT_AXIS0 : AKGB_REPLICATED);
-      k->descs.push_back(d);
-    };
-    for (int vid : g.inputs) add(vid, false);
-    for (int vid : g.outputs) add(vid, true);
-    for (auto& n : g.nodes)
-      if (n.kind == OpK::Assign && g.v(n.in[0]).input_index >= 0) k->descs[g.v(n.in[0]).input_index].written_in_place = 1;
   } catch (const JsonError& e) {
     delete k;
     return fail(AKGB_INVALID_JSON, e.what());
@@ -700,6 +868,8 @@ extern "C" akgb_status akgb_launch_dynamic(akgb_kernel* k, void* const* tensors,
 
 akgb_status akgb_launch(akgb_kernel* k, void* const* tensors, void* workspace, size_t workspace_bytes, void* stream) {
   if (!k || !tensors) return fail(AKGB_INVALID_ARG, "null argument");
+  if (!k->stages.empty())
+    return fail(AKGB_INVALID_ARG, "this sharded region has an exchange step between its stages: use akgb_launch_sharded");
   if (k->graph.dynamic) return fail(AKGB_INVALID_ARG, "this kernel has dynamic shapes: use akgb_launch_dynamic");
   if (workspace_bytes < k->plan.workspace_bytes || (k->plan.workspace_bytes && !workspace))
     return fail(AKGB_INVALID_ARG, "workspace smaller than akgb_workspace_size()");
@@ -715,6 +885,8 @@ akgb_status akgb_launch(akgb_kernel* k, void* const* tensors, void* workspace, s
 
 akgb_status akgb_run_host(akgb_kernel* k, void* const* host) {
   if (!k || !host) return fail(AKGB_INVALID_ARG, "null argument");
+  if (!k->stages.empty())
+    return fail(AKGB_INVALID_ARG, "this sharded region has an exchange step between its stages: use akgb_launch_sharded");
   if (k->graph.dynamic) return fail(AKGB_INVALID_ARG, "this kernel has dynamic shapes: use akgb_launch_dynamic");
   // like the reference's launcher this entry point picks its device itself (and leaves it current)
   const cudaError_t se = cudaSetDevice(k->device);

@@ -339,6 +339,14 @@ void fill_exchange_base(akgb_comm* c, FinishExchange* fx) {
 
 int32_t akgb_sharded_exchange_kind(const akgb_kernel* k, const akgb_comm* c) {
   if (!k || !c || c->world <= 1) return AKGB_EXCHANGE_NONE;
+  if (kernel_is_staged(k)) {  // the least direct way any of the stages' exchanges goes
+    int32_t kind = AKGB_EXCHANGE_NONE;
+    for (int i = 0; const akgb_kernel* sk = kernel_stage(k, i); ++i) {
+      const int32_t sk_kind = akgb_sharded_exchange_kind(sk, c);
+      if (sk_kind != AKGB_EXCHANGE_NONE && (kind == AKGB_EXCHANGE_NONE || sk_kind < kind)) kind = sk_kind;
+    }
+    return kind;
+  }
   const int n = akgb_num_tensors(k);
   bool any = false, all_small_f32 = true;
   size_t total = 0;
@@ -440,6 +448,7 @@ akgb_status akgb_launch_sharded(akgb_kernel* k, akgb_comm* c, void* const* tenso
     set_last_error("akgb_launch_sharded: null argument");
     return AKGB_INVALID_ARG;
   }
+  if (kernel_is_staged(k)) return launch_staged(k, c, tensors, workspace, workspace_bytes, stream);
   if (c->world > 1 && c->peers_ready && c->in_reduction) {
     const akgb_status rs = refuse_after_timeout(c);
     if (rs != AKGB_OK) return rs;

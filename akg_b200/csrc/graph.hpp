@@ -147,6 +147,25 @@ void infer_sharding(Graph& g, int rank, int world);
 // Returns a static copy of the graph; throws JsonError when the extents contradict the description.
 Graph bind_shapes(const Graph& g, const std::vector<std::vector<int64_t>>& shapes);
 
+// Sharded regions in which a reduction over the split axis feeds later ops, cut into stages at those reductions
+// (stages.cpp).  Every stage is a region of its own with GLOBAL shapes (infer_sharding is applied to it afterwards);
+// its arguments are the parent's arguments or "carried" values: partial results an earlier stage produced and the
+// exchange step completed.
+struct StageGraph {
+  Graph g;
+  std::vector<int> in_parent;    // per stage input: index among the parent's inputs, or -1
+  std::vector<int> in_carried;   // per stage input: index of the carried value it reads, or -1
+  std::vector<int> out_parent;   // per stage output: index among the parent's outputs, or -1
+  std::vector<int> out_carried;  // per stage output: index of the carried value it defines, or -1
+};
+struct StagePlan {
+  std::vector<StageGraph> stages;
+  std::vector<int> carried;      // value ids (in the parent graph) of the carried values
+};
+// false when the region has no reduction over the split axis that feeds another op (or holds ops the cut does not
+// handle: matmuls, in-place stores)
+bool split_at_sharded_reductions(const Graph& g, StagePlan* out);
+
 std::string sha256_hex(const char* data, size_t len);
 
 }  // namespace akgb

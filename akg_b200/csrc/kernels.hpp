@@ -174,6 +174,12 @@ uint32_t* kernel_error_word(akgb_kernel* k);
 // reduction step that can do so, launches the plan with `base` (peers, rank, world, wait limit) attached and sets
 // *fused; otherwise launches nothing and leaves *fused false.
 bool kernel_exchange_fusable(const akgb_kernel* k);
+// a sharded region that runs as stages with the exchange step between them: launches every stage through
+// akgb_launch_sharded (kernel, then the exchange of its partial results)
+bool kernel_is_staged(const akgb_kernel* k);
+const akgb_kernel* kernel_stage(const akgb_kernel* k, int i);  // nullptr past the last stage
+akgb_status launch_staged(akgb_kernel* k, akgb_comm* c, void* const* tensors, void* workspace, size_t workspace_bytes,
+                          void* stream);
 akgb_status launch_with_exchange(akgb_kernel* k, const FinishExchange& base, void* const* tensors, void* workspace,
                                  size_t workspace_bytes, void* stream, bool* fused);
 

@@ -261,6 +261,9 @@ def class_table():
         ("transpose_tile_f16_8192x8192", lambda r: descs.transpose([r, 8192], [1, 0]), 8192, {}, "exact_full", 0),
         ("transpose_tile_f32_64x1024x1024", lambda b: descs.transpose([b, 1024, 1024], [0, 2, 1], "float32"), 64, {},
          "exact", 1),
+        # statistics over the split axis feed the normalisation: stages with the exchange between them at N > 1
+        ("batchnorm_training_f32_64x256x56x56", lambda n: descs.batch_norm_training([n, 256, 56, 56]), 64,
+         {"gamma": "gamma", "beta": "beta"}, "gathered", 0),
     ]
 
 
@@ -312,6 +315,34 @@ def check_sliced(make, kernel, bufs, how, sample):
         if not ok:
             return False
     return True
+
+
+def check_gathered(make, global_lead, kernel, bufs, rank, world):
+    """Results that depend on the whole split axis (batch statistics): every rank gathers the split inputs, evaluates
+    the oracle on the whole tensors and compares its own slice of the split results and the replicated results whole
+    (1e-4 relative with an absolute term scaled by the largest expected value: float32 sums of 200 000 terms)."""
+    import torch
+    import torch.distributed as dist
+    from oracle import akg_oracle as O
+    ins, outs = bufs[:kernel.num_inputs], bufs[kernel.num_inputs:]
+    full = []
+    for t, d in zip(ins, kernel.inputs):
+        if world > 1 and d.shard_kind == 1:
+            parts = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(parts, t.contiguous())
+            full.append(torch.cat(parts, dim=0).cpu().numpy())
+        else:
+            full.append(t.cpu().numpy())
+    want = O.evaluate(make(global_lead), full)
+    ok = True
+    for o, w, d in zip(outs, want, kernel.outputs):
+        if world > 1 and d.shard_kind == 1:
+            n = d.shape[0]
+            w = w[rank * n:(rank + 1) * n]
+        got = o.cpu().numpy().reshape(w.shape).astype(np.float64)
+        w = w.astype(np.float64)
+        ok = ok and bool(np.all(np.abs(got - w) <= 1e-4 * np.abs(w) + 1e-4 * float(np.abs(w).max())))
+    return ok
 
 
 def check_reduction(make, kernel, bufs, rank, world):
@@ -369,7 +400,7 @@ def run_classes(rank, world, device, steps, warmup, hbm_peak, tf_peak, barrier, 
             rows[key] = {"unsupported": str(e)[:120]}
             continue
         sets = buffer_sets_for(k, kinds, device, rank)
-        partial = [i for i, t in enumerate(k.tensors) if t.shard_kind >= 2]
+        partial = [i for i, t in enumerate(k.tensors) if t.shard_kind >= 2] or (k.op_class == "sharded_stages")
         exchange = comm.exchange_kind(k) if (partial and comm is not None) else "none"
 
         def step_launch(bufs, stream=None, k=k, partial=partial):
@@ -392,7 +423,7 @@ def run_classes(rank, world, device, steps, warmup, hbm_peak, tf_peak, barrier, 
                 ms = time_launches(_K, sets, steps, warmup, barrier, use_graph=False)
         ms_max = allreduce_scalar(ms, world)
         alone = None
-        if partial and comm is not None:
+        if partial and comm is not None and k.op_class != "sharded_stages":
             # the same shard on the same rank without the exchange step: what the exchange costs on top
             alone = allreduce_scalar(time_launches(k, sets, steps, warmup, barrier), world)
         bytes_job = k.bytes * world   # the ranks' shares add up to the global shape
@@ -419,6 +450,8 @@ def run_classes(rank, world, device, steps, warmup, hbm_peak, tf_peak, barrier, 
             torch.cuda.synchronize()
             if how == "reduce":
                 good = check_reduction(make, k, sets[0], rank, world)
+            elif how == "gathered":
+                good = check_gathered(make, global_lead, k, sets[0], rank, world)
             elif how == "exact_full":  # the oracle on the whole tensors (no independent slices to sample)
                 from oracle import akg_oracle as O
                 want = O.evaluate(make(global_lead), [to_numpy(t) for t in sets[0][:k.num_inputs]])

@@ -227,7 +227,14 @@ akgb_status akgb_allreduce_partials(const akgb_kernel* k, akgb_comm* c, void* co
  * over NCCL) and the ranks have synchronised. */
 akgb_status akgb_launch_sharded(akgb_kernel* k, akgb_comm* c, void* const* tensors, void* workspace,
                                 size_t workspace_bytes, void* stream);
-/* Which way the partial outputs of `k` travel with communicator `c` as it is set up now. */
+/* A region in which a reduction over the split axis feeds later ops (batch-norm statistics over a batch that is split
+ * across the ranks) compiles, with shard_world > 1, into STAGES cut at those reductions (class "sharded_stages"):
+ * akgb_launch_sharded runs stage, exchange, stage, ... on the one stream; results of such reductions are reported as
+ * AKGB_REPLICATED because the caller receives them completed.  akgb_launch and akgb_run_host refuse such a kernel
+ * (AKGB_INVALID_ARG): its stages cannot run without the exchange between them.
+ *
+ * Which way the partial outputs of `k` travel with communicator `c` as it is set up now (for a kernel made of stages:
+ * the least direct way among its stages). */
 #define AKGB_EXCHANGE_NONE 0          /* no partial outputs, or a single rank */
 #define AKGB_EXCHANGE_NCCL 1          /* ncclAllReduce after the kernel */
 #define AKGB_EXCHANGE_PEER_KERNEL 2   /* one exchange kernel over the ranks' mapped buffers after the kernel */

@@ -123,6 +123,37 @@ def main():
     torch.cuda.synchronize()
     want_bm = torch.matmul(a_all.double(), b_all.double())[2 * rank:2 * rank + 2]
     ok = ok and bool(torch.allclose(obm.cpu().double(), want_bm, rtol=2e-3, atol=2e-3 * float(want_bm.abs().max())))
+    # reductions over the split axis that feed later ops: the region runs as stages with the exchange between them.
+    # Batch normalisation in training mode and its gradient over a batch split across the ranks, against the CPU oracle
+    # on the whole batch (every rank evaluates it and checks its own slice and the per-channel results)
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "tests"))
+    from oracle import akg_oracle as O
+    shape = [4 * world, 32, 14, 14]
+    for build in (descs.batch_norm_training, descs.batch_norm_backward):
+        d = build(shape)
+        rng = np.random.default_rng(11)
+        full = [rng.standard_normal(t[0]["shape"], dtype=np.float32) for t in d["input_desc"]]
+        if build is descs.batch_norm_backward:
+            full[3] = np.abs(full[3]) + 0.5  # rstd
+        want = O.evaluate(d, full)
+        ks = FusedKernel(d, device=local, shard_rank=rank, shard_world=world)
+        ok = ok and ks.op_class == "sharded_stages"
+        lo, hi = 4 * rank, 4 * rank + 4
+        ins = [torch.from_numpy(np.ascontiguousarray(a[lo:hi] if t.shard_kind == 1 else a)).cuda()
+               for a, t in zip(full, ks.inputs)]
+        outs = [torch.empty(t.shape, dtype=torch.float32, device="cuda") for t in ks.outputs]
+        for _ in range(2):
+            comm.launch_sharded(ks, ins + outs)
+        torch.cuda.synchronize()
+        ok = ok and ks.check_device_error() == 0
+        for o, w, t in zip(outs, want, ks.outputs):
+            w = w[lo:hi] if t.shard_kind == 1 else w
+            ok = ok and bool(np.allclose(o.cpu().numpy(), w, rtol=1e-4, atol=1e-4 * float(np.abs(w).max())))
+        try:  # without a communicator the stages cannot exchange: refused, not run half-way
+            ks.launch(ins + outs)
+            ok = False
+        except Exception:
+            pass
     if rank == 0:
         print("PEER_EXCHANGE", "on" if peer else "off", flush=True)
         for (name, label), us in sorted(timings.items()):

@@ -340,6 +340,25 @@ def test_batch_matmul_shards_on_the_batch_of_both_operands(lib):
         FusedKernel(descs.batch_matmul(3, 64, 64, 256), shard_rank=0, shard_world=2)
 
 
+def test_reductions_over_the_split_axis_that_feed_later_ops_run_as_stages(lib):
+    """Batch-norm statistics over a batch that is split across ranks: the region is cut at the reductions over the
+    split axis; the caller sees one kernel whose per-channel results arrive completed (the exchange runs between the
+    stages inside akgb_launch_sharded)."""
+    k = FusedKernel(descs.batch_norm_training([8, 16, 4, 4]), shard_rank=1, shard_world=2)
+    assert k.op_class == "sharded_stages" and k.workspace_size > 0
+    by = {t.name: t for t in k.tensors}
+    assert by["x"].shape == (4, 16, 4, 4) and by["x"].shard_kind == _capi.SHARD_SPLIT_AXIS0
+    assert by["gamma"].shard_kind == _capi.SHARD_REPLICATED
+    assert k.outputs[0].shape == (4, 16, 4, 4) and k.outputs[0].shard_kind == _capi.SHARD_SPLIT_AXIS0
+    assert all(o.shape == (1, 16, 1, 1) and o.shard_kind == _capi.SHARD_REPLICATED for o in k.outputs[1:])
+    # three stages (sum; centred squares; normalisation), each at least one launch
+    assert k.launch_count >= 3
+    kb = FusedKernel(descs.batch_norm_backward([8, 16, 4, 4]), shard_rank=0, shard_world=4)
+    assert kb.op_class == "sharded_stages" and kb.inputs[0].shape == (2, 16, 4, 4)
+    # the same descriptions unsplit are ordinary kernels
+    assert FusedKernel(descs.batch_norm_training([8, 16, 4, 4])).op_class != "sharded_stages"
+
+
 def test_generated_kernels_shard_like_the_templates(lib):
     from akg_b200 import FusedKernel, _capi, descs
     k = FusedKernel(descs.rmsnorm(4096, 1024), shard_rank=1, shard_world=4)
