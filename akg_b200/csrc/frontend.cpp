@@ -1,5 +1,6 @@
 // JSON front end, class tagging and leading-axis shard inference.
 #include <algorithm>
+#include <cctype>
 #include <cstring>
 #include <set>
 
@@ -92,6 +93,104 @@ std::vector<int64_t> shape_of(const Json& d) {
   return s;
 }
 
+// "symbolic_shape": a list with one entry per dim, symbols ("s0") or numbers, as strings or integers
+// (TranslateToMindsporeDialect.cpp:64, :322-335)
+std::vector<std::string> symbols_of(const Json& d) {
+  std::vector<std::string> out;
+  const Json* s = d.find("symbolic_shape");
+  if (!s || !s->is_array()) return out;
+  for (auto& e : s->arr) {
+    if (e.is_string()) out.push_back(e.str);
+    else if (e.is_number()) out.push_back(std::to_string(e.as_int()));
+    else out.push_back("");
+  }
+  return out;
+}
+
+// Integer expression over symbols: + - * / (floor division of non-negative values), parentheses, integer literals.
+// `lookup` returns false for a symbol without a value yet, which makes the whole evaluation fail (return false).
+struct SymExpr {
+  const std::string& t;
+  size_t i = 0;
+  const std::map<std::string, int64_t>& env;
+  bool ok = true;
+  void ws() {
+    while (i < t.size() && (t[i] == ' ' || t[i] == '\t')) ++i;
+  }
+  int64_t atom() {
+    ws();
+    if (i < t.size() && t[i] == '(') {
+      ++i;
+      const int64_t v = sum();
+      ws();
+      if (i < t.size() && t[i] == ')') ++i;
+      else ok = false;
+      return v;
+    }
+    if (i < t.size() && t[i] == '-') {
+      ++i;
+      return -atom();
+    }
+    if (i < t.size() && t[i] >= '0' && t[i] <= '9') {
+      int64_t v = 0;
+      while (i < t.size() && t[i] >= '0' && t[i] <= '9') v = v * 10 + (t[i++] - '0');
+      return v;
+    }
+    std::string name;
+    while (i < t.size() && (std::isalnum((unsigned char)t[i]) || t[i] == '_')) name += t[i++];
+    auto it = env.find(name);
+    if (name.empty() || it == env.end()) {
+      ok = false;
+      return 0;
+    }
+    return it->second;
+  }
+  int64_t product() {
+    int64_t v = atom();
+    for (;;) {
+      ws();
+      if (i < t.size() && t[i] == '*') {
+        ++i;
+        v *= atom();
+      } else if (i < t.size() && t[i] == '/') {
+        ++i;
+        if (i < t.size() && t[i] == '/') ++i;  // "//"
+        const int64_t d = atom();
+        if (d == 0) {
+          ok = false;
+          return 0;
+        }
+        v = v / d;
+      } else {
+        return v;
+      }
+    }
+  }
+  int64_t sum() {
+    int64_t v = product();
+    for (;;) {
+      ws();
+      if (i < t.size() && t[i] == '+') {
+        ++i;
+        v += product();
+      } else if (i < t.size() && t[i] == '-') {
+        ++i;
+        v -= product();
+      } else {
+        return v;
+      }
+    }
+  }
+};
+bool eval_symbol_expr(const std::string& text, const std::map<std::string, int64_t>& env, int64_t* out) {
+  SymExpr e{text, 0, env};
+  const int64_t v = e.sum();
+  e.ws();
+  if (!e.ok || e.i != text.size()) return false;
+  *out = v;
+  return true;
+}
+
 const Json* find_attr(const Json& attrs, const char* name) {
   if (!attrs.is_array()) return nullptr;
   for (auto& a : attrs.arr) {
@@ -125,7 +224,16 @@ Graph parse_info(const char* text, size_t len) {
     if (ti->is_object() && ti->contains("compute_capability") && ti->at("compute_capability").is_string())
       g.compute_capability = ti->at("compute_capability").str;
   }
-  // symbol_calc_expr / symbolic_shape only name the unknown extents; they are bound from the launch-time shapes
+  // symbol_calc_expr (TranslateToMindsporeDialect.cpp:59, :575-580): symbol -> expression, kept for bind_shapes
+  if (const Json* sc = root.find("symbol_calc_expr")) {
+    if (sc->is_object())
+      for (auto& kv : sc->obj) {
+        if (kv.second.is_string()) g.symbol_expr.emplace_back(kv.first, kv.second.str);
+        else if (kv.second.is_number()) g.symbol_expr.emplace_back(kv.first, std::to_string(kv.second.as_int()));
+        else if (kv.second.is_array() && kv.second.size() == 1 && kv.second[0].is_string())
+          g.symbol_expr.emplace_back(kv.first, kv.second[0].str);
+      }
+  }
 
   std::map<std::string, int> by_name;
   auto new_value = [&](const std::string& name, std::vector<int64_t> shape, DT dt) {
@@ -148,6 +256,7 @@ Graph parse_info(const char* text, size_t len) {
       const std::string& name = d.at("tensor_name").as_string();
       int id = new_value(name, shape_of(d), dt);
       g.values[id].input_index = (int)i;
+      g.values[id].sym = symbols_of(d);
       if (d.contains("value") && d.at("value").is_number()) {
         // a graph input with a literal value stays a runtime argument (the
         // harness materialises it with np.full) — keep the value for matching
@@ -459,6 +568,7 @@ Graph parse_info(const char* text, size_t len) {
     }
     Value& v = g.values[it->second];
     v.output_index = (int)i;
+    v.sym = symbols_of(d);
     // the declared output shape may differ from the op's by a trailing view
     // change only; keep the op's shape when the element counts agree
     std::vector<int64_t> s = shape_of(d);
@@ -659,6 +769,58 @@ Graph bind_shapes(const Graph& src, const std::vector<std::vector<int64_t>>& sha
   };
   for (size_t i = 0; i < g.inputs.size(); ++i) bind_arg(g.inputs[i], shapes[i]);
   for (size_t i = 0; i < g.outputs.size(); ++i) bind_arg(g.outputs[i], shapes[g.inputs.size() + i]);
+  // Symbols: a symbol names ONE extent.  The inputs define them, symbol_calc_expr derives further ones (an output
+  // extent as an expression of input extents), and every argument dim that carries a symbol must agree.
+  {
+    std::map<std::string, int64_t> env;
+    auto is_number = [](const std::string& t) {
+      if (t.empty()) return false;
+      for (char ch : t)
+        if (ch < '0' || ch > '9') return false;
+      return true;
+    };
+    auto visit = [&](int vid, bool define) {
+      const Value& v = g.v(vid);
+      if (v.sym.size() != v.shape.size()) return;  // no (or a malformed) symbolic_shape: nothing to check
+      for (size_t d = 0; d < v.sym.size(); ++d) {
+        const std::string& t = v.sym[d];
+        if (t.empty()) continue;
+        if (is_number(t)) {
+          if (std::stoll(t) != v.shape[d])
+            throw JsonError("argument '" + v.name + "': dim " + std::to_string(d) + " is declared as " + t);
+          continue;
+        }
+        auto it = env.find(t);
+        if (it == env.end()) {
+          if (define) env[t] = v.shape[d];
+        } else if (it->second != v.shape[d]) {
+          throw JsonError("argument '" + v.name + "': symbol '" + t + "' is bound to " + std::to_string(it->second) +
+                          " by another dim but this dim has " + std::to_string(v.shape[d]));
+        }
+      }
+    };
+    for (int vid : g.inputs) visit(vid, true);
+    bool progress = true;
+    while (progress) {  // expressions may build on one another, in any order
+      progress = false;
+      for (auto& kv : g.symbol_expr) {
+        if (env.count(kv.first)) continue;
+        int64_t val = 0;
+        if (eval_symbol_expr(kv.second, env, &val)) {
+          env[kv.first] = val;
+          progress = true;
+        }
+      }
+    }
+    for (auto& kv : g.symbol_expr) {  // a symbol that an input also carries must agree with its expression
+      int64_t val = 0;
+      auto it = env.find(kv.first);
+      if (it != env.end() && eval_symbol_expr(kv.second, env, &val) && val != it->second)
+        throw JsonError("symbol '" + kv.first + "' = " + kv.second + " evaluates to " + std::to_string(val) +
+                        " but is bound to " + std::to_string(it->second));
+    }
+    for (int vid : g.outputs) visit(vid, true);
+  }
   for (auto& n : g.nodes) {
     Value& out = g.v(n.out);
     std::vector<int64_t> inf;

@@ -77,6 +77,7 @@ struct Value {
   int input_index = -1;      // position in input_desc, -1 otherwise
   int output_index = -1;     // position in output_desc, -1 otherwise
   std::vector<int> users;    // op indices
+  std::vector<std::string> sym;  // "symbolic_shape" of a region argument: one symbol or number per dim ("" = none)
   // sharding (filled by infer_sharding)
   bool split0 = false;       // axis 0 holds only this rank's slice
   int partial = 0;           // akgb_shard_kind of a partial result, 0 = none
@@ -119,6 +120,9 @@ struct Graph {
   ReduceDir reduce_dir = ReduceDir::None;
   std::string sha256_hex;    // of the JSON text
   bool dynamic = false;      // some extent is -1: shapes are bound at launch (bind_shapes)
+  // "symbol_calc_expr": symbol -> expression over other symbols (integers, + - * /, parentheses); bind_shapes
+  // evaluates them from the extents the caller binds and checks every argument dim that names a symbol against it
+  std::vector<std::pair<std::string, std::string>> symbol_expr;
 
   const Value& v(int id) const { return values[id]; }
   Value& v(int id) { return values[id]; }

@@ -134,3 +134,61 @@ def ulp_diff_f16(a, b):
         i = x.view(np.int16).astype(np.int32)
         return np.where(i < 0, -(i & 0x7FFF), i)
     return np.abs(key(a) - key(b))
+
+
+GUARD_BYTES = 4096
+GUARD_PATTERN = 0xA5
+
+
+def guarded_launch(desc, ins, flags=0):
+    """One device launch with every tensor (inputs, outputs, workspace) placed between two guard zones.
+
+    The sanitizer tools are not available on every machine these tests run on, so the tests carry their own evidence
+    that kernels stay inside their buffers: each tensor sits at `GUARD_BYTES` inside a larger device allocation whose
+    first and last `GUARD_BYTES` hold a known pattern (the zone behind a tensor starts at its last byte + 1, not at
+    an aligned boundary, so a vector store that overshoots a ragged tail is caught too).  After the launch every guard
+    zone must be intact and every input that the region does not store into unchanged.  Returns (outputs as numpy
+    arrays, kernel)."""
+    import torch
+    from akg_b200 import FusedKernel
+    k = FusedKernel(desc, flags=flags)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    bufs, ptrs = [], []
+
+    def alloc(nbytes, fill):
+        b = torch.full((GUARD_BYTES + nbytes + GUARD_BYTES,), GUARD_PATTERN, dtype=torch.uint8, device=dev)
+        if nbytes:
+            b[GUARD_BYTES:GUARD_BYTES + nbytes] = fill
+        assert b.data_ptr() % 256 == 0
+        return b
+
+    host_in = []
+    for a, t in zip(ins, k.inputs):
+        raw = np.ascontiguousarray(a).view(np.uint8).reshape(-1)
+        assert raw.size == t.nbytes, (t.name, raw.size, t.nbytes)
+        b = alloc(t.nbytes, 0)
+        if t.nbytes:
+            b[GUARD_BYTES:GUARD_BYTES + t.nbytes] = torch.from_numpy(raw.copy()).to(dev)
+        bufs.append(b)
+        host_in.append(raw)
+    for t in k.outputs:
+        bufs.append(alloc(t.nbytes, 0xCD))
+    ws = alloc(k.workspace_size, 0xCD)
+    k.launch_ptrs([b.data_ptr() + GUARD_BYTES for b in bufs], ws.data_ptr() + GUARD_BYTES if k.workspace_size else 0,
+                  k.workspace_size, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert k.check_device_error() == 0
+    for b, t in zip(bufs + [ws], list(k.tensors) + [None]):
+        name = t.name if t is not None else "workspace"
+        n = t.nbytes if t is not None else k.workspace_size
+        front, back = b[:GUARD_BYTES], b[GUARD_BYTES + n:]
+        assert bool((front == GUARD_PATTERN).all()), f"bytes in front of '{name}' were overwritten"
+        assert bool((back == GUARD_PATTERN).all()), f"bytes behind '{name}' were overwritten"
+    for b, raw, t in zip(bufs, host_in, k.inputs):
+        if not t.written_in_place and t.nbytes:
+            assert np.array_equal(b[GUARD_BYTES:GUARD_BYTES + t.nbytes].cpu().numpy(), raw), f"input '{t.name}' was modified"
+    outs = []
+    for b, t in zip(bufs[k.num_inputs:], k.outputs):
+        dt = BF16 if t.dtype == "bfloat16" else np.dtype(t.dtype)
+        outs.append(b[GUARD_BYTES:GUARD_BYTES + t.nbytes].cpu().numpy().view(dt).reshape(t.shape))
+    return outs, k

@@ -359,6 +359,53 @@ def test_reductions_over_the_split_axis_that_feed_later_ops_run_as_stages(lib):
     assert FusedKernel(descs.batch_norm_training([8, 16, 4, 4])).op_class != "sharded_stages"
 
 
+def test_symbolic_shapes_bind_consistently(lib):
+    """symbolic_shape / symbol_calc_expr (TranslateToMindsporeDialect.cpp:55-75): a symbol names one extent; the
+    inputs define the symbols, the expressions derive further ones, every argument dim that carries a symbol must
+    agree when the launch-time extents are bound."""
+    from akg_b200.descs import _Builder, _attr
+    b = _Builder("Fused_Concat_Mul_sym_5")
+    f = "float32"
+    x, y = b.input("x", [-1, 8], f), b.input("y", [-1, 8], f)
+    x["symbolic_shape"], y["symbolic_shape"] = ["s0", "8"], ["s1", 8]
+    node = {"name": "Concat", "attr": [_attr("axis", "int", 0)], "impl_path": "",
+            "input_desc": [[dict(x), dict(y)]],
+            "output_desc": [{"data_type": f, "format": "DefaultFormat", "shape": [-1, 8], "tensor_name": "cat"}]}
+    b.ops.append(node)
+    out = b.emit("Mul", [dict(node["output_desc"][0]), b.const(2.0, f)], [-1, 8], f)
+    out["symbolic_shape"] = ["s2", "8"]
+    b.output(out)
+    d = b.build()
+    d["symbol_calc_expr"] = {"s2": "s0 + s1"}
+    k = FusedKernel(d)
+    assert k.is_dynamic
+    k.bind_shapes([[5, 8], [7, 8], [12, 8]])
+    with pytest.raises(AkgbError, match="symbol 's2'"):
+        k.bind_shapes([[5, 8], [7, 8], [13, 8]])  # the result must have s0 + s1 rows
+    # one symbol on two inputs: both must be bound to the same extent
+    b = _Builder("Fused_Add_sym_6")
+    p_, q_ = b.input("p", [-1, 16], f), b.input("q", [-1, 16], f)
+    p_["symbolic_shape"], q_["symbolic_shape"] = ["n", "16"], ["n", "16"]
+    b.output(b.emit("Add", [p_, q_], [-1, 16], f))
+    k = FusedKernel(b.build())
+    k.bind_shapes([[9, 16], [9, 16], [9, 16]])
+    with pytest.raises(AkgbError, match="symbol 'n'"):
+        k.bind_shapes([[9, 16], [1, 16], [9, 16]])  # would broadcast, but the description says the extents are equal
+    # products, quotients and parentheses; a numeric entry must match the extent
+    b = _Builder("Fused_Reshape_sym_7")
+    r_ = b.input("r", [-1, -1, 4], f)
+    r_["symbolic_shape"] = ["a", "b", "4"]
+    o_ = b.emit("Reshape", [r_], [-1, 2], f, [_attr("shape", "listInt", [-1, 2])])
+    o_["symbolic_shape"] = ["m", "2"]
+    b.output(o_)
+    d = b.build()
+    d["symbol_calc_expr"] = {"m": "(a * b * 4) / 2"}
+    k = FusedKernel(d)
+    k.bind_shapes([[3, 5, 4], [30, 2]])
+    with pytest.raises(AkgbError):
+        k.bind_shapes([[3, 5, 4], [15, 4]])
+
+
 def test_generated_kernels_shard_like_the_templates(lib):
     from akg_b200 import FusedKernel, _capi, descs
     k = FusedKernel(descs.rmsnorm(4096, 1024), shard_rank=1, shard_world=4)

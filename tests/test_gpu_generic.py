@@ -10,7 +10,7 @@ import pytest
 from akg_b200 import FusedKernel, descs
 from akg_b200.descs import _Builder, _attr, _reduce_attr, batch_norm_training as _batch_norm_training, batch_norm_backward as _batch_norm_backward
 from oracle import akg_oracle as O
-from helpers import BF16, bits_equal, make_inputs
+from helpers import BF16, bits_equal, guarded_launch, make_inputs
 
 pytestmark = pytest.mark.gpu
 
@@ -31,6 +31,11 @@ def run(desc, ins):
         o.view(np.uint8)[...] = 0xCD
     k.run_host(list(ins) + outs)
     assert k.check_device_error() == 0
+    # the same region as a device launch between guard zones: same bits, nothing written outside the tensors
+    guarded, _ = guarded_launch(desc, ins, flags=FLAGS[0])
+    atomics = any(op["name"] == "UnsortedSegmentSum" for op in desc["op_desc"])  # float atomics: order varies
+    for a, b in zip(outs, guarded):
+        assert atomics or np.array_equal(np.ascontiguousarray(a).view(np.uint8).reshape(-1), b.view(np.uint8).reshape(-1))
     return outs, k
 
 

@@ -9,17 +9,23 @@ import pytest
 
 from akg_b200 import FusedKernel, descs
 from oracle import akg_oracle as O
-from helpers import BF16, KINDS, bits_equal, golden_cases, load_golden, make_inputs, ulp_diff_f16
+from helpers import BF16, KINDS, bits_equal, golden_cases, guarded_launch, load_golden, make_inputs, ulp_diff_f16
 
 pytestmark = pytest.mark.gpu
 
 
 def run_host(desc, ins, **kw):
+    """The host-pointer entry point (what the reference's launcher does), and the same region once more as a device
+    launch between guard zones: same bits, nothing written outside the tensors."""
     k = FusedKernel(desc, **kw)
     outs = k.empty_outputs()
     for o in outs:
         o.view(np.uint8)[...] = 0xCD  # poison
     k.run_host(list(ins) + outs)
+    if not kw:
+        guarded, _ = guarded_launch(desc, ins)
+        for a, b in zip(outs, guarded):
+            assert np.array_equal(np.ascontiguousarray(a).view(np.uint8).reshape(-1), b.view(np.uint8).reshape(-1))
     return outs, k
 
 
