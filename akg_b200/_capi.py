@@ -99,6 +99,7 @@ _SIGNATURES = [
                                           ctypes.POINTER(ctypes.c_double)]),
     ("akgb_kernel_meta", ctypes.c_int, [_vp, ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t)]),
     ("akgb_prepare", ctypes.c_int, [_vp]),
+    ("akgb_export_kernel", ctypes.c_int, [_vp, ctypes.c_char_p]),
     ("akgb_comm_unique_id", ctypes.c_int, [ctypes.c_void_p, ctypes.c_size_t]),
     ("akgb_comm_create", ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
                                         ctypes.POINTER(ctypes.c_void_p)]),

@@ -5,6 +5,7 @@
 // staging buffers, and launches are asynchronous on the caller's stream.
 #include <cuda_runtime.h>
 
+#include <cctype>
 #include <cstdio>
 #include <cstring>
 #include <map>
@@ -990,6 +991,60 @@ akgb_status akgb_dump_jit_source(const akgb_kernel* k, int32_t vectorised, char*
   if (!buf) return AKGB_OK;
   if (cap < src.size() + 1) return fail(AKGB_INVALID_ARG, "buffer too small");
   std::memcpy(buf, src.c_str(), src.size() + 1);
+  return AKGB_OK;
+}
+
+akgb_status akgb_export_kernel(const akgb_kernel* k, const char* dir) {
+  if (!k || !dir || !*dir) return fail(AKGB_INVALID_ARG, "null argument");
+  if (k->graph.dynamic || !k->stages.empty())
+    return fail(AKGB_UNSUPPORTED, "only static, single-kernel regions have a stand-alone binary");
+  const Plan& ap = active_plan(k);
+  if (ap.steps.size() != 1 || (ap.steps[0].kind != StepK::Ew && ap.steps[0].kind != StepK::RowJit))
+    return fail(AKGB_UNSUPPORTED,
+                "this region runs on kernel templates built into the library or in several launches: there is no "
+                "stand-alone binary for it (launch it through akgb_launch)");
+  const Step& st = ap.steps[0];
+  // the kernel takes the caller's tensors directly only when every operand is one of them, in argument order
+  const std::vector<Ref>& in = st.ew_in;
+  const std::vector<Ref>& out = st.ew_out;
+  if ((int)in.size() != k->n_inputs || in.size() + out.size() != k->descs.size())
+    return fail(AKGB_UNSUPPORTED, "the generated kernel does not take exactly the region's arguments");
+  for (size_t i = 0; i < in.size(); ++i)
+    if (in[i].arg != (int)i) return fail(AKGB_UNSUPPORTED, "the generated kernel reorders the region's arguments");
+  for (size_t i = 0; i < out.size(); ++i)
+    if (out[i].arg != k->n_inputs + (int)i)
+      return fail(AKGB_UNSUPPORTED, "the generated kernel reorders the region's arguments");
+  const std::string entry = k->graph.kernel_name + "_kernel";
+  for (char ch : entry)
+    if (!(std::isalnum((unsigned char)ch) || ch == '_'))
+      return fail(AKGB_UNSUPPORTED, "the kernel name is not usable as a symbol");
+  std::vector<char> cubin;
+  LaunchDims d;
+  bool align16 = false;
+  const bool ok = st.kind == StepK::Ew ? ew_jit_export(st.ew, entry, &cubin, &d, &align16)
+                                       : row_jit_export(*st.row, entry, &cubin, &d, &align16);
+  if (!ok) return fail(AKGB_UNSUPPORTED, "the kernel of this region could not be generated or compiled on this host: " + g_err);
+  const std::string base = std::string(dir) + "/" + k->graph.kernel_name;
+  {
+    FILE* f = std::fopen((base + ".cubin").c_str(), "wb");
+    if (!f) return fail(AKGB_INVALID_ARG, "cannot write " + base + ".cubin");
+    const bool w = std::fwrite(cubin.data(), 1, cubin.size(), f) == cubin.size();
+    std::fclose(f);
+    if (!w) return fail(AKGB_INVALID_ARG, "short write to " + base + ".cubin");
+  }
+  std::ostringstream o;
+  o << "{\"kernelName\": \"" << entry << "\", \"blockIdx.x\": " << d.grid[0] << ", \"blockIdx.y\": " << d.grid[1]
+    << ", \"blockIdx.z\": " << d.grid[2] << ", \"threadIdx.x\": " << d.block[0] << ", \"threadIdx.y\": " << d.block[1]
+    << ", \"threadIdx.z\": " << d.block[2] << ", \"is_dynamic\": false, \"sha256\": \""
+    << sha256_hex(cubin.data(), cubin.size()) << "\", \"binary\": \"" << k->graph.kernel_name
+    << ".cubin\", \"arch\": \"sm_100a\", \"shared_mem_bytes\": " << d.smem
+    << ", \"args\": \"device pointers of the inputs, then of the outputs\", \"pointer_alignment\": "
+    << (align16 ? 16 : 1) << ", \"class\": \"" << k->plan.klass << "\"}";
+  const std::string text = o.str();
+  FILE* f = std::fopen((base + ".json").c_str(), "wb");
+  if (!f) return fail(AKGB_INVALID_ARG, "cannot write " + base + ".json");
+  std::fwrite(text.data(), 1, text.size(), f);
+  std::fclose(f);
   return AKGB_OK;
 }
 

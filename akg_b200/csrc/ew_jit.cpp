@@ -11,9 +11,11 @@
 // (akg-mlir/lib/Target/PTX/GPUKernelToPTX.cpp:108-172) with a far smaller surface: only the op chain is
 // generated, never the loop structure or the memory access pattern.
 #include <cuda.h>
+#include <fcntl.h>
+#include <sys/stat.h>
+#include <unistd.h>
 #include <cuda_runtime.h>
 #include <dlfcn.h>
-#include <unistd.h>
 
 #include <algorithm>
 #include <cstdio>
@@ -43,6 +45,7 @@ struct Nvrtc {
   nvrtcResult (*GetProgramLogSize)(nvrtcProgram, size_t*);
   nvrtcResult (*GetProgramLog)(nvrtcProgram, char*);
   nvrtcResult (*DestroyProgram)(nvrtcProgram*);
+  nvrtcResult (*Version)(int*, int*) = nullptr;
   bool ok = false;
 };
 struct Driver {
@@ -73,6 +76,7 @@ Nvrtc& nvrtc() {
     AKGB_SYM(GetProgramLogSize, "nvrtcGetProgramLogSize")
     AKGB_SYM(GetProgramLog, "nvrtcGetProgramLog")
     AKGB_SYM(DestroyProgram, "nvrtcDestroyProgram")
+    AKGB_SYM(Version, "nvrtcVersion")
 #undef AKGB_SYM
     n.ok = true;
   });
@@ -1032,11 +1036,74 @@ bool read_file(const std::string& path, std::vector<char>* out) {
 
 void write_file_atomically(const std::string& path, const std::vector<char>& data) {
   const std::string tmp = path + ".tmp." + std::to_string((long long)getpid());
-  FILE* f = std::fopen(tmp.c_str(), "wb");
-  if (!f) return;
+  const int fd = ::open(tmp.c_str(), O_WRONLY | O_CREAT | O_TRUNC, 0600);  // readable by its owner only
+  if (fd < 0) return;
+  FILE* f = ::fdopen(fd, "wb");
+  if (!f) {
+    ::close(fd);
+    return;
+  }
   const bool ok = std::fwrite(data.data(), 1, data.size(), f) == data.size();
   std::fclose(f);
   if (!ok || std::rename(tmp.c_str(), path.c_str()) != 0) std::remove(tmp.c_str());
+}
+
+// A cached image is launched on the device, so it is only accepted when (1) the file belongs to this user and
+// (2) the digest recorded beside it (<file>.sha256, written together with the image) is the digest of its bytes: a
+// truncated, stale or foreign file at the expected path is ignored and the kernel is compiled again.
+bool owned_by_this_user(const std::string& path) {
+  struct stat st;
+  return ::stat(path.c_str(), &st) == 0 && st.st_uid == ::geteuid() && S_ISREG(st.st_mode);
+}
+bool read_verified_image(const std::string& path, std::vector<char>* image) {
+  if (!owned_by_this_user(path) || !owned_by_this_user(path + ".sha256")) return false;
+  std::vector<char> digest;
+  {
+    FILE* f = std::fopen((path + ".sha256").c_str(), "rb");
+    if (!f) return false;
+    digest.resize(64);
+    const bool ok = std::fread(digest.data(), 1, 64, f) == 64;
+    std::fclose(f);
+    if (!ok) return false;
+  }
+  if (!read_file(path, image)) return false;
+  return sha256_hex(image->data(), image->size()) == std::string(digest.data(), 64);
+}
+void write_image_with_digest(const std::string& path, const std::vector<char>& image) {
+  const std::string hex = sha256_hex(image.data(), image.size());
+  write_file_atomically(path + ".sha256", std::vector<char>(hex.begin(), hex.end()));
+  write_file_atomically(path, image);
+}
+
+// the compile options and the version of the compiler that produced an image are part of its cache key
+std::string jit_options_tag();
+
+// source text -> cubin image for sm_100a (no device needed); empty on failure (the log goes to akgb_last_error)
+std::vector<char> compile_to_cubin(const std::string& src) {
+  std::vector<char> cubin;
+  Nvrtc& n = nvrtc();
+  if (!n.ok) return cubin;
+  nvrtcProgram prog = nullptr;
+  if (n.CreateProgram(&prog, src.c_str(), "akgb_ew_jit.cu", 0, nullptr, nullptr) != 0) return cubin;
+  const char* opts[] = {"--gpu-architecture=sm_100a", "-std=c++17", "--fmad=false", "-default-device"};
+  const nvrtcResult r = n.CompileProgram(prog, 4, opts);
+  if (r != 0) {
+    size_t ls = 0;
+    if (n.GetProgramLogSize(prog, &ls) == 0 && ls > 1) {
+      std::string log(ls, '\0');
+      n.GetProgramLog(prog, &log[0]);
+      set_last_error(("elementwise JIT: " + log.substr(0, 400)).c_str());
+    }
+    n.DestroyProgram(&prog);
+    return cubin;
+  }
+  size_t sz = 0;
+  if (n.GetCUBINSize(prog, &sz) == 0 && sz > 0) {
+    cubin.resize(sz);
+    if (n.GetCUBIN(prog, cubin.data()) != 0) cubin.clear();
+  }
+  n.DestroyProgram(&prog);
+  return cubin;
 }
 
 JitKernel* compile(const std::string& src, const char* entry = "akgb_ew_jit") {
@@ -1055,10 +1122,10 @@ JitKernel* compile(const std::string& src, const char* entry = "akgb_ew_jit") {
   const std::string dir = cache_dir();
   std::string path;
   if (!dir.empty()) {
-    const std::string tagged = std::string(kJitOptionsTag) + "\n" + src;
+    const std::string tagged = jit_options_tag() + "\n" + src;
     path = dir + "/akgb_ew_" + sha256_hex(tagged.data(), tagged.size()) + ".sm_100a.cubin";
     std::vector<char> image;
-    if (read_file(path, &image)) {
+    if (read_verified_image(path, &image)) {
       CUmodule mod = nullptr;
       if (d.ModuleLoadData(&mod, image.data()) == CUDA_SUCCESS &&
           d.ModuleGetFunction(&k.fn, mod, entry) == CUDA_SUCCESS) {
@@ -1068,36 +1135,39 @@ JitKernel* compile(const std::string& src, const char* entry = "akgb_ew_jit") {
       }
     }
   }
-  if (!n.ok) return &k;
-  nvrtcProgram prog = nullptr;
-  if (n.CreateProgram(&prog, src.c_str(), "akgb_ew_jit.cu", 0, nullptr, nullptr) != 0) return &k;
-  const char* opts[] = {"--gpu-architecture=sm_100a", "-std=c++17", "--fmad=false", "-default-device"};
-  const nvrtcResult r = n.CompileProgram(prog, 4, opts);
-  if (r != 0) {
-    size_t ls = 0;
-    if (n.GetProgramLogSize(prog, &ls) == 0 && ls > 1) {
-      std::string log(ls, '\0');
-      n.GetProgramLog(prog, &log[0]);
-      set_last_error(("elementwise JIT: " + log.substr(0, 400)).c_str());
-    }
-    n.DestroyProgram(&prog);
-    return &k;
-  }
-  size_t sz = 0;
-  std::vector<char> cubin;
-  if (n.GetCUBINSize(prog, &sz) == 0 && sz > 0) {
-    cubin.resize(sz);
-    if (n.GetCUBIN(prog, cubin.data()) != 0) cubin.clear();
-  }
-  n.DestroyProgram(&prog);
+  const std::vector<char> cubin = compile_to_cubin(src);
   if (cubin.empty()) return &k;
   CUmodule mod = nullptr;
   if (d.ModuleLoadData(&mod, cubin.data()) != CUDA_SUCCESS) return &k;
   if (d.ModuleGetFunction(&k.fn, mod, entry) != CUDA_SUCCESS) return &k;
   k.failed = false;
   ++g_n_compiled;
-  if (!path.empty()) write_file_atomically(path, cubin);
+  if (!path.empty()) write_image_with_digest(path, cubin);
   return &k;
+}
+
+std::string jit_options_tag() {
+  int major = 0, minor = 0;
+  Nvrtc& n = nvrtc();
+  if (n.ok && n.Version) n.Version(&major, &minor);
+  return std::string(kJitOptionsTag) + " nvrtc " + std::to_string(major) + "." + std::to_string(minor);
+}
+
+// The generated text with its entry point renamed to `entry` and the trailing element / row count turned into a
+// constant, so that the kernel takes the tensors' bare pointers and nothing else -- the signature a runtime that loads
+// <kernel>.cubin + <kernel>.json from the kernel meta directory launches.
+std::string standalone_source(std::string src, const char* generated_entry, const std::string& entry,
+                              const char* count_name, long long count) {
+  const std::string from = std::string(generated_entry) + "(";
+  const size_t at = src.find(from);
+  if (at == std::string::npos) return "";
+  src.replace(at, from.size(), entry + "(");
+  const std::string tail = std::string(", i64 ") + count_name + ") {\n";
+  const size_t tp = src.find(tail, at);
+  if (tp == std::string::npos) return "";
+  // the last pointer parameter ends in ", " before the count: drop the count, keep the pointers
+  src.replace(tp, tail.size(), std::string(") {\n  constexpr i64 ") + count_name + " = " + std::to_string(count) + "LL;\n");
+  return src;
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -1248,6 +1318,51 @@ void row_jit_prepare(const RowProgram& P) {
     RowShape rs;
     if (row_generate(P, vec, &src, &rs)) compile(src, "akgb_row_jit");
   }
+}
+
+// Stand-alone binaries of generated kernels (the reference leaves <kernel>.ptx + <kernel>.json for the framework's
+// runtime, akg-mlir/python/akg_mlir/mlir_driver.py:776-815): the image of the kernel with entry point `entry` taking
+// only the tensors' pointers (inputs then outputs), and the launch dimensions.  The 16-byte-vector variant is exported
+// when the extents allow it; it then requires 16-byte aligned tensors, which `*needs_align16` reports.
+bool ew_jit_export(const EwProgram& P, const std::string& entry, std::vector<char>* cubin, LaunchDims* dims,
+                   bool* needs_align16) {
+  if (P.n <= 0) return false;
+  const bool vec = P.n % 8 == 0;
+  std::string src;
+  if (!generate(P, vec, &src)) return false;
+  src = standalone_source(src, "akgb_ew_jit", entry, "n", (long long)P.n);
+  if (src.empty()) return false;
+  *cubin = compile_to_cubin(src);
+  if (cubin->empty()) return false;
+  const int U = vec ? 2 : 4, E = vec ? 8 : 1;
+  const int64_t nv = P.n / E;
+  const int64_t grid = (nv + 256 * U - 1) / (256 * U);
+  if (grid > 0x7fffffff) return false;
+  *dims = LaunchDims();
+  dims->grid[0] = (unsigned)grid;
+  dims->block[0] = 256;
+  *needs_align16 = vec;
+  return true;
+}
+bool row_jit_export(const RowProgram& P, const std::string& entry, std::vector<char>* cubin, LaunchDims* dims,
+                    bool* needs_align16) {
+  if (P.rows <= 0 || P.col_reduce || P.col_sums) return false;  // those write partials another launch folds
+  const bool vec = P.cols % 8 == 0;
+  std::string src;
+  RowShape rs;
+  if (!row_generate(P, vec, &src, &rs)) return false;
+  src = standalone_source(src, "akgb_row_jit", entry, "rows", (long long)P.rows);
+  if (src.empty()) return false;
+  *cubin = compile_to_cubin(src);
+  if (cubin->empty()) return false;
+  const int rpb = rs.tpb / rs.t;
+  const int64_t grid = (P.rows + rpb - 1) / rpb;
+  if (grid > 0x7fffffff) return false;
+  *dims = LaunchDims();
+  dims->grid[0] = (unsigned)grid;
+  dims->block[0] = (unsigned)rs.tpb;
+  *needs_align16 = vec;
+  return true;
 }
 
 // The CUDA C++ text that would be compiled for this program (empty when the program needs the interpreter).

@@ -112,6 +112,14 @@ bool row_jit_fits_registers(const RowProgram& p);  // the register schedule appl
 int64_t row_jit_col_sum_ctas(const RowProgram& p);  // CTAs (= partial vectors per result) of a program with column sums
 cudaError_t col_jit_launch(const RowProgram& p, const void* const* in, float* const* partials, int64_t splits,
                            cudaStream_t s, LaunchDims* dims);
+}  // namespace akgb
+#include <vector>
+namespace akgb {
+// stand-alone image of a generated kernel whose entry point `entry` takes only the tensors' pointers (ew_jit.cpp)
+bool ew_jit_export(const EwProgram& p, const std::string& entry, std::vector<char>* cubin, LaunchDims* dims,
+                   bool* needs_align16);
+bool row_jit_export(const RowProgram& p, const std::string& entry, std::vector<char>* cubin, LaunchDims* dims,
+                    bool* needs_align16);
 void ew_jit_prepare(const EwProgram& p);
 void row_jit_prepare(const RowProgram& p);
 void jit_set_cache_dir(const char* dir);  // nullptr: environment's choice; "": no disk cache

@@ -116,6 +116,11 @@ class FusedKernel:
         _capi.check(self._lib.akgb_check_device_error(self._handle, ctypes.byref(word)))
         return int(word.value)
 
+    def export(self, directory: str) -> None:
+        """``akgb_export_kernel``: ``<kernel>.cubin`` + ``<kernel>.json`` for a region that runs as one generated
+        kernel (raises ``UnsupportedError`` for the others)."""
+        _capi.check(self._lib.akgb_export_kernel(self._handle, str(directory).encode()))
+
     def prepare(self):
         """``akgb_prepare``: device tables and generated kernels ahead of the first launch (needed before the launches
         are captured into a CUDA graph)."""
@@ -256,8 +261,18 @@ class MlirDriver:
         # kernels generated at the first launch are cached there too, as the reference's <kernel>.ptx is
         os.makedirs(self.output_dir, exist_ok=True)
         set_cache_dir(self.output_dir)
+        meta = self.kernel.meta()
+        # a region that runs as one generated kernel also leaves <kernel>.cubin there: the pair a runtime that loads
+        # kernels from the meta directory needs (entry point, launch dims and sha256 then describe that image)
+        own_name = json.loads(text).get("op", self.kernel_name)
+        try:
+            self.kernel.export(self.output_dir)
+            with open(os.path.join(self.output_dir, own_name + ".json"), "r", encoding="utf-8") as f:
+                meta.update(json.load(f))
+        except (_capi.UnsupportedError, OSError):
+            pass
         with open(os.path.join(self.output_dir, self.kernel_name + ".json"), "w", encoding="utf-8") as f:
-            json.dump(self.kernel.meta(), f)
+            json.dump(meta, f)
 
     def run(self, input_for_mod, output_indexes=None):
         if self.kernel is None:

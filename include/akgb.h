@@ -169,6 +169,16 @@ akgb_status akgb_profile_host(akgb_kernel* k, void* const* host_tensors, int32_t
  * plan, in launch order).  Writes a NUL-terminated JSON text; `*needed` receives the size including the NUL. */
 akgb_status akgb_kernel_meta(const akgb_kernel* k, char* buf, size_t cap, size_t* needed);
 
+/* Writes <dir>/<kernel>.cubin and <dir>/<kernel>.json for a region that runs as ONE kernel generated at run time
+ * (elementwise / broadcast chains, reduce-X regions without sums over all rows): the artefact pair the reference
+ * leaves under KERNEL_META_DIR for the framework's own runtime (<kernel>.ptx + <kernel>.json,
+ * python/akg_mlir/mlir_driver.py:47-53, 776-815).  The image's entry point "<kernel>_kernel" takes the device pointers
+ * of the inputs, then of the outputs, and nothing else (extents are compiled in); the JSON carries kernelName,
+ * blockIdx.{x,y,z}, threadIdx.{x,y,z}, is_dynamic, the sha256 of the image, and the pointer alignment the image
+ * assumes.  Needs the run-time compiler but no device.  Regions that run on the templates built into the library, in
+ * several launches, or with dynamic shapes have no such binary: AKGB_UNSUPPORTED. */
+akgb_status akgb_export_kernel(const akgb_kernel* k, const char* dir);
+
 /* The CUDA C++ text that is compiled at run time for the first generic elementwise group of the region
  * (`vectorised` != 0: the 16-byte-vector variant, else the scalar one); an empty text means the region has
  * no such group or it runs on the interpreting kernel.  The counterpart of the reference's IR/PTX dumps

@@ -152,6 +152,37 @@ def test_mlir_driver_writes_kernel_meta_like_the_reference(lib, tmp_path, monkey
         MlirDriver(d["op"], str(info), backend="ascend")
 
 
+def test_generated_kernels_export_a_loadable_binary(lib, tmp_path):
+    """<kernel>.cubin + <kernel>.json for regions that run as one generated kernel (the pair the reference leaves in
+    the kernel meta directory, mlir_driver.py:776-815); template regions have no stand-alone binary.  Compiling needs
+    the run-time compiler but no device."""
+    import hashlib
+    from akg_b200.descs import _Builder
+    b = _Builder("Fused_Add_Mul_export_1")
+    f = "float32"
+    x, y = b.input("x", [64, 256], f), b.input("y", [256], f)
+    b.output(b.emit("Mul", [b.emit("Add", [x, y], [64, 256], f), b.const(0.5, f)], [64, 256], f))
+    d = b.build()
+    for desc in (d, descs.rmsnorm(128, 512)):
+        k = FusedKernel(desc)
+        try:
+            k.export(tmp_path)
+        except UnsupportedError as e:
+            if "could not be generated or compiled" in str(e):
+                pytest.skip("no run-time compiler on this host")
+            raise
+        image = (tmp_path / (desc["op"] + ".cubin")).read_bytes()
+        meta = json.loads((tmp_path / (desc["op"] + ".json")).read_text())
+        assert image[:4] == b"\x7fELF" and meta["sha256"] == hashlib.sha256(image).hexdigest()
+        assert meta["kernelName"] == desc["op"] + "_kernel" and meta["kernelName"].encode() in image
+        assert meta["blockIdx.x"] >= 1 and meta["threadIdx.x"] >= 32 and meta["is_dynamic"] is False
+        assert meta["binary"] == desc["op"] + ".cubin" and meta["pointer_alignment"] in (1, 16)
+    with pytest.raises(UnsupportedError, match="no stand-alone binary"):
+        FusedKernel(descs.layernorm(64, 1024)).export(tmp_path)
+    with pytest.raises(UnsupportedError):
+        FusedKernel(descs.reduce_sum_axis0(4096, 512)).export(tmp_path)
+
+
 def test_generic_plan_splits_at_shape_changes(lib):
     """Elementwise groups, reductions and data-movement ops become separate launches; Reshape is a view."""
     from akg_b200.descs import _Builder, _attr, _reduce_attr

@@ -1048,3 +1048,42 @@ def test_regions_that_are_row_regions_only_in_part(lib):
     np.testing.assert_allclose(got[0], O.evaluate(d, ins, accum="float64")[0], rtol=1e-5, atol=1e-5)
     if FLAGS[0] == 0:
         assert kern.launch_count == 2  # statistics + normalisation as a row kernel, then the per-channel scale
+
+
+def test_exported_binary_runs_through_the_driver_api_alone(lib, tmp_path):
+    """The exported <kernel>.cubin is launched the way a foreign runtime would: cuModuleLoadData, the entry point and
+    launch dimensions from <kernel>.json, the tensors' bare device pointers as the only arguments -- and gives the
+    bits akgb_launch gives."""
+    import ctypes
+    import json
+    import torch
+    b = _Builder("Fused_Add_Tanh_Mul_export_2")
+    f = "float32"
+    x, y = b.input("x", [384, 1000], f), b.input("y", [1000], f)
+    t = b.emit("Tanh", [b.emit("Add", [x, y], [384, 1000], f)], [384, 1000], f)
+    b.output(b.emit("Mul", [t, x], [384, 1000], f))
+    for d in (b.build(), descs.rmsnorm(300, 1024)):
+        k = FusedKernel(d)
+        k.export(tmp_path)
+        meta = json.loads((tmp_path / (d["op"] + ".json")).read_text())
+        image = (tmp_path / meta["binary"]).read_bytes()
+        ins = [torch.from_numpy(a).cuda() for a in make_inputs(d, 41)]
+        want = [torch.empty(t_.shape, dtype=torch.float32, device="cuda") for t_ in k.outputs]
+        k.launch(ins + want)
+        got = [torch.full(t_.shape, float("nan"), dtype=torch.float32, device="cuda") for t_ in k.outputs]
+        torch.cuda.synchronize()
+        cu = ctypes.CDLL("libcuda.so.1")
+        mod, fn = ctypes.c_void_p(), ctypes.c_void_p()
+        assert cu.cuModuleLoadData(ctypes.byref(mod), image) == 0
+        assert cu.cuModuleGetFunction(ctypes.byref(fn), mod, meta["kernelName"].encode()) == 0
+        ptrs = [ctypes.c_void_p(t_.data_ptr()) for t_ in ins + got]
+        assert all(p.value % meta["pointer_alignment"] == 0 for p in ptrs)
+        args = (ctypes.c_void_p * len(ptrs))(*[ctypes.cast(ctypes.pointer(p), ctypes.c_void_p) for p in ptrs])
+        rc = cu.cuLaunchKernel(fn, meta["blockIdx.x"], meta["blockIdx.y"], meta["blockIdx.z"], meta["threadIdx.x"],
+                               meta["threadIdx.y"], meta["threadIdx.z"], meta["shared_mem_bytes"],
+                               ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), args, None)
+        assert rc == 0
+        torch.cuda.synchronize()
+        for g, w in zip(got, want):
+            assert torch.equal(g.view(torch.int32), w.view(torch.int32))
+        assert cu.cuModuleUnload(mod) == 0
