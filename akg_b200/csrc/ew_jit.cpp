@@ -125,6 +125,10 @@ __device__ __forceinline__ float rn_f32(float x) { return x; }
 __device__ __forceinline__ int wr_i8(int x) { return (int)(signed char)x; }
 __device__ __forceinline__ int wr_i16(int x) { return (int)(short)x; }
 __device__ __forceinline__ int wr_i32(int x) { return x; }
+// float -> integer as tosa.cast: round to nearest even, clamp to the type's range (cvt.rni saturates; NaN gives 0)
+__device__ __forceinline__ int f2i_i32(float x) { return __float2int_rn(x); }
+__device__ __forceinline__ int f2i_i16(float x) { return max(-32768, min(32767, __float2int_rn(x))); }
+__device__ __forceinline__ int f2i_i8(float x) { return max(-128, min(127, __float2int_rn(x))); }
 __device__ __forceinline__ float mx_f(float a, float b) { return (a != a || b != b) ? __int_as_float(0x7fc00000) : fmaxf(a, b); }
 __device__ __forceinline__ float mn_f(float a, float b) { return (a != a || b != b) ? __int_as_float(0x7fc00000) : fminf(a, b); }
 // 8 consecutive elements starting at element e0 (e0 % 8 == 0, base 16-byte aligned)
@@ -274,6 +278,7 @@ std::string instr_expr(int op, int dt, int cls, int src_cls, int a, int b, int c
   } else if (op == EW_CAST) {
     if (fl) expr = std::string(round_fn(dt)) + "(" + (sfl ? ref(a, true) : "(float)" + ref(a, false)) + ")";
     else if (cls == EWC_BOOL) expr = sfl ? "(" + ref(a, true) + " != 0.f ? 1 : 0)" : "(" + ref(a, false) + " != 0 ? 1 : 0)";
+    else if (sfl) expr = std::string((DT)dt == DT::I8 ? "f2i_i8" : (DT)dt == DT::I16 ? "f2i_i16" : "f2i_i32") + "(" + ref(a, true) + ")";
     else expr = std::string(wrap_fn(dt)) + "(" + ref(a, false) + ")";
   } else if (op <= EW_ACOS) {
     if (fl) expr = std::string(round_fn(dt)) + "(" + float_unary(op, ref(a, true)) + ")";
@@ -995,7 +1000,7 @@ template <int OP> __device__ __forceinline__ float comb(float a, float b) {
   return true;
 }
 
-constexpr const char* kJitOptionsTag = "akgb-ew-jit-1 sm_100a c++17 fmad=false";
+constexpr const char* kJitOptionsTag = "akgb-ew-jit-2 sm_100a c++17 fmad=false";
 
 struct JitKernel {
   CUfunction fn = nullptr;

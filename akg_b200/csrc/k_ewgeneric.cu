@@ -168,8 +168,12 @@ __global__ void __launch_bounds__(kEwThreads) ew_generic_kernel(const __grid_con
           r = __float_as_uint(round_to(f, ins.dt));
         } else if (ins.cls == EWC_BOOL) {
           r = ins.src_cls == EWC_FLOAT ? (__uint_as_float(a) != 0.f ? 1u : 0u) : (a != 0u ? 1u : 0u);
+        } else if (ins.src_cls == EWC_FLOAT) {
+          // as tosa.cast: round to nearest even, clamp to the type's range (cvt.rni saturates; NaN gives 0)
+          const int q = __float2int_rn(__uint_as_float(a));
+          r = (uint32_t)(ins.dt == kI8 ? max(-128, min(127, q)) : ins.dt == kI16 ? max(-32768, min(32767, q)) : q);
         } else {
-          r = (uint32_t)wrap_int((int)a, ins.dt);  // int/bool -> int (float -> int is rejected at planning)
+          r = (uint32_t)wrap_int((int)a, ins.dt);  // int/bool -> int
         }
       } else if (op <= EW_ACOS) {  // EW_COPY and the value-producing unary ops
         if (ins.cls == EWC_FLOAT) r = __float_as_uint(round_to(unary_f(op, __uint_as_float(a)), ins.dt));

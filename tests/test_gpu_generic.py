@@ -253,13 +253,35 @@ def test_transpose_then_elementwise(lib):
     check(d, make_inputs(d, 13), exact=True)
 
 
-def test_float_to_int_cast_is_refused(lib):
+def test_float_to_int_cast_rounds_to_nearest_even_and_clamps(lib):
+    """The reference's compiled route (tosa.cast) rounds to nearest even and clamps to the result type; its NumPy
+    generator would truncate.  The library and the restatement follow the compiled route; NaN gives 0."""
+    x = np.array([0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 0.49999997, 126.5, 127.5, 300.0, -129.0, 32767.5, 40000.0, -40000.0,
+                  3e10, -3e10, np.inf, -np.inf, np.nan, 1e-30, -7.75, 8388607.5] + [0.0] * 10, dtype=np.float32)
+    rng = np.random.default_rng(15)
+    x = np.concatenate([x, (rng.standard_normal(4096 - x.size) * 100).astype(np.float32)])
+    for dst, src in (("int32", "float32"), ("int16", "float32"), ("int8", "float32"), ("int32", "float16"),
+                     ("int8", "bfloat16")):
+        b = _Builder(f"Fused_CastToInt_{dst}_{src}_14")
+        xin = b.input("x", [4096], src)
+        b.output(b.emit("Cast", [xin], [4096], dst, [_attr("dst_type", "str", dst)]))
+        d = b.build()
+        xv = x.astype(BF16 if src == "bfloat16" else np.dtype(src))
+        k = check(d, [xv], exact=True)
+        assert k.launch_count == 1
+    got, _ = run(_cast_desc("int32"), [x])
+    assert got[0][:6].tolist() == [0, 2, 2, 0, -2, -2] and got[0][14] == 2**31 - 1 and got[0][15] == -2**31
+    assert got[0][18] == 0  # NaN
     from akg_b200 import UnsupportedError
-    b = _Builder("Fused_CastToInt_14")
-    x = b.input("x", [16], "float32")
-    b.output(b.emit("Cast", [x], [16], "int32", [_attr("dst_type", "str", "int32")]))
     with pytest.raises(UnsupportedError):
-        FusedKernel(b.build())
+        FusedKernel(_cast_desc("int64"))
+
+
+def _cast_desc(dst):
+    b = _Builder(f"Fused_CastTo_{dst}_14")
+    x = b.input("x", [4096], "float32")
+    b.output(b.emit("Cast", [x], [4096], dst, [_attr("dst_type", "str", dst)]))
+    return b.build()
 
 
 def test_tile_slice_strided_slice_concat_addn(lib):
