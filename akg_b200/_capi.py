@@ -36,6 +36,7 @@ EXCHANGE_NAMES = {0: "none", 1: "nccl", 2: "peer-kernel", 3: "in-reduction"}
 AKGB_MAX_RANK = 8
 AKGB_FLAG_NO_JIT = 1
 AKGB_FLAG_FOLD_IN_LAUNCH = 2
+AKGB_FLAG_STAGE_LONG_ROWS = 4
 
 
 class TensorDesc(ctypes.Structure):

@@ -64,6 +64,7 @@ struct akgb_kernel {
   int shard_rank = 0, shard_world = 1;
   bool no_jit = false;  // AKGB_FLAG_NO_JIT
   bool fold_in_launch = false;  // AKGB_FLAG_FOLD_IN_LAUNCH
+  bool stage_long_rows = false;  // AKGB_FLAG_STAGE_LONG_ROWS
   // dynamic-shape regions: one plan per set of launch-time extents
   struct Bound {
     Graph graph;
@@ -547,6 +548,9 @@ void plan_and_describe(akgb_kernel* k) {
   } else {
     infer_sharding(k->graph, k->shard_rank, k->shard_world);
     k->plan = build_plan(k->graph, k->sm_count, !k->no_jit);
+    if (k->stage_long_rows)
+      for (Step& st : k->plan.steps)
+        if (st.kind == StepK::RowJit && st.row) st.row->stage_long_rows = true;
   }
   const Graph& g = k->graph;
   k->n_inputs = (int)g.inputs.size();
@@ -614,6 +618,7 @@ bool build_stages(akgb_kernel* k, const char* text, size_t len) {
       sk->shard_world = k->shard_world;
       sk->no_jit = k->no_jit;
       sk->fold_in_launch = k->fold_in_launch;
+      sk->stage_long_rows = k->stage_long_rows;
       sk->graph = std::move(sg.g);
       plan_and_describe(sk);
       stage_ws = std::max(stage_ws, sk->plan.workspace_bytes);
@@ -745,6 +750,7 @@ akgb_status akgb_compile(const char* info_json, size_t len, const akgb_options* 
     k->shard_world = world;
     k->no_jit = (flags & AKGB_FLAG_NO_JIT) != 0;
     k->fold_in_launch = (flags & AKGB_FLAG_FOLD_IN_LAUNCH) != 0;
+    k->stage_long_rows = (flags & AKGB_FLAG_STAGE_LONG_ROWS) != 0;
     k->json_text.assign(info_json, len);
     k->graph = parse_info(info_json, len);
     try {

@@ -19,6 +19,7 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -53,6 +54,7 @@ struct Driver {
   CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*);
   CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
                            void**, void**);
+  CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
   bool ok = false;
 };
 
@@ -95,6 +97,7 @@ Driver& driver() {
     if (!get("cuModuleLoadData", reinterpret_cast<void**>(&d.ModuleLoadData))) return;
     if (!get("cuModuleGetFunction", reinterpret_cast<void**>(&d.ModuleGetFunction))) return;
     if (!get("cuLaunchKernel", reinterpret_cast<void**>(&d.LaunchKernel))) return;
+    if (!get("cuFuncSetAttribute", reinterpret_cast<void**>(&d.FuncSetAttribute))) return;
     d.ok = true;
   });
   return d;
@@ -494,6 +497,8 @@ struct RowShape {
   int nv = 1;    // granules per thread
   int t = 32;    // threads that own one row (a power of two)
   int tpb = 128; // threads per CTA
+  int cluster = 1;        // CTAs that share one row (multi-pass schedule with the row staged in shared memory)
+  unsigned dyn_smem = 0;  // dynamic shared memory of the kernel, bytes
 };
 
 int max_live_full(const RowProgram& P) {
@@ -553,11 +558,80 @@ bool row_generate_multipass(const RowProgram& P, bool vec, std::string* out, Row
   rs.t = 512;
   rs.tpb = 512;
   rs.nv = 0;  // marks the multi-pass schedule
-  *shape = rs;
   const int ni = (int)P.instr.size();
+  // Which per-element inputs are read by more than one pass?  Those are staged: the first pass that reads them leaves
+  // their bytes in shared memory and the later passes read them there, so the row crosses HBM/L2 once.  A row that
+  // does not fit one CTA's shared memory is shared by a cluster of K CTAs (K = 2, 4 or 8): each keeps one K-th of the
+  // columns, and the per-row reductions are completed through distributed shared memory (every CTA reads the K
+  // partial results, in CTA order).
+  std::vector<int> pass_uses(P.in.size(), 0);
+  {
+    std::vector<int> def_i(P.n_val, -1), def_in(P.n_val, -1);
+    for (size_t i = 0; i < P.in.size(); ++i) def_in[P.in[i].val] = (int)i;
+    for (int k = 0; k < ni; ++k) def_i[P.instr[k].dst] = k;
+    auto count = [&](std::vector<int> stack) {
+      std::vector<char> seen_i(ni, 0), seen_in(P.in.size(), 0);
+      while (!stack.empty()) {
+        const int v = stack.back();
+        stack.pop_back();
+        if (v < 0 || v >= P.n_val || !P.val_full[v]) continue;
+        if (def_in[v] >= 0) {
+          if (!seen_in[def_in[v]]) ++pass_uses[def_in[v]];
+          seen_in[def_in[v]] = 1;
+          continue;
+        }
+        const int k = def_i[v];
+        if (k < 0 || seen_i[k]) continue;
+        seen_i[k] = 1;
+        stack.push_back(P.instr[k].a);
+        if (!P.instr[k].reduce) {
+          stack.push_back(P.instr[k].b);
+          stack.push_back(P.instr[k].c);
+        }
+      }
+    };
+    std::vector<int> final_roots;
+    for (int k = 0; k < ni; ++k)
+      if (!P.instr[k].full && P.instr[k].reduce) count({P.instr[k].a});
+    for (auto& o : P.out)
+      if (o.kind == RK_FULL || o.kind == RK_COL) final_roots.push_back(o.val);
+    if (!final_roots.empty()) count(final_roots);
+  }
+  std::vector<int64_t> stage_off(P.in.size(), -1);  // byte offset of a staged input in the CTA's dynamic shared memory
+  int K = 1;
+  int64_t CH = P.cols;  // columns per CTA
+  if (vec && !P.col_sums && P.stage_long_rows) {
+    int64_t row_bytes = 0;
+    for (size_t i = 0; i < P.in.size(); ++i)
+      if (P.in[i].kind == RK_FULL && is_float_dt(P.in[i].dt) && pass_uses[i] >= 2)
+        row_bytes += P.cols * (int64_t)((DT)P.in[i].dt == DT::F32 ? 4 : 2);
+    if (row_bytes > 0) {
+      // at most 72 KB per CTA, so that three CTAs of 512 threads stay resident per SM
+      while (K < 8 && (row_bytes + K - 1) / K > 72 * 1024) K *= 2;
+      const int64_t granules = (P.cols + 7) / 8;
+      CH = ((granules + K - 1) / K) * 8;
+      int64_t off = 0;
+      for (size_t i = 0; i < P.in.size(); ++i)
+        if (P.in[i].kind == RK_FULL && is_float_dt(P.in[i].dt) && pass_uses[i] >= 2) {
+          stage_off[i] = off;
+          off += CH * (int64_t)((DT)P.in[i].dt == DT::F32 ? 4 : 2);
+        }
+      if (off > 200 * 1024) {  // does not fit even as a cluster of 8: the passes re-read the row through L2
+        K = 1;
+        CH = P.cols;
+        std::fill(stage_off.begin(), stage_off.end(), -1);
+      } else {
+        rs.cluster = K;
+        rs.dyn_smem = (unsigned)off;
+      }
+    }
+  }
+  const bool staged = rs.dyn_smem > 0;
+  *shape = rs;
   std::ostringstream s;
   s << kPreamble;
-  s << "constexpr int C = " << P.cols << ", T = 512, TPB = 512, VW = " << rs.vw << ";\n";
+  s << "constexpr int C = " << P.cols << ", T = 512, TPB = 512, VW = " << rs.vw << ", K = " << K << ";\n";
+  s << "constexpr i64 CH = " << CH << ";\n";
   s << R"SRC(
 __device__ __forceinline__ U4 ld16p(const void* p, unsigned long long pol) { U4 v;
   asm volatile("ld.global.nc.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(pol)); return v; }
@@ -587,12 +661,70 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
   for (int w = 1; w < T / 32; ++w) v = comb<OP>(v, sm[w]);
   return v;
 }
+// staged rows: the first pass keeps the bytes it loads in shared memory (sp, element s0), later passes read them there
+__device__ __forceinline__ void ld8ps_f32(const void* p, i64 e0, float* r, unsigned long long pol, void* sp, i64 s0) {
+  const U4 a = ld16p((const float*)p + e0, pol), b = ld16p((const float*)p + e0 + 4, pol);
+  U4* d = (U4*)((float*)sp + s0); d[0] = a; d[1] = b;
+  r[0] = __uint_as_float(a.x); r[1] = __uint_as_float(a.y); r[2] = __uint_as_float(a.z); r[3] = __uint_as_float(a.w);
+  r[4] = __uint_as_float(b.x); r[5] = __uint_as_float(b.y); r[6] = __uint_as_float(b.z); r[7] = __uint_as_float(b.w); }
+__device__ __forceinline__ void ld8s_f32(const void* sp, i64 s0, float* r) {
+  const U4* d = (const U4*)((const float*)sp + s0); const U4 a = d[0], b = d[1];
+  r[0] = __uint_as_float(a.x); r[1] = __uint_as_float(a.y); r[2] = __uint_as_float(a.z); r[3] = __uint_as_float(a.w);
+  r[4] = __uint_as_float(b.x); r[5] = __uint_as_float(b.y); r[6] = __uint_as_float(b.z); r[7] = __uint_as_float(b.w); }
+__device__ __forceinline__ void ld8ps_f16(const void* p, i64 e0, float* r, unsigned long long pol, void* sp, i64 s0) {
+  const U4 v = ld16p((const u16*)p + e0, pol); *(U4*)((u16*)sp + s0) = v; const u32 w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { r[2*i] = h2f((u16)(w[i] & 0xffffu)); r[2*i+1] = h2f((u16)(w[i] >> 16)); } }
+__device__ __forceinline__ void ld8s_f16(const void* sp, i64 s0, float* r) {
+  const U4 v = *(const U4*)((const u16*)sp + s0); const u32 w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { r[2*i] = h2f((u16)(w[i] & 0xffffu)); r[2*i+1] = h2f((u16)(w[i] >> 16)); } }
+__device__ __forceinline__ void ld8ps_bf16(const void* p, i64 e0, float* r, unsigned long long pol, void* sp, i64 s0) {
+  const U4 v = ld16p((const u16*)p + e0, pol); *(U4*)((u16*)sp + s0) = v; const u32 w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { r[2*i] = b2f((u16)(w[i] & 0xffffu)); r[2*i+1] = b2f((u16)(w[i] >> 16)); } }
+__device__ __forceinline__ void ld8s_bf16(const void* sp, i64 s0, float* r) {
+  const U4 v = *(const U4*)((const u16*)sp + s0); const u32 w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { r[2*i] = b2f((u16)(w[i] & 0xffffu)); r[2*i+1] = b2f((u16)(w[i] >> 16)); } }
+// every thread of every CTA of the cluster arrives; nobody passes before all have (a hardware barrier, like
+// __syncthreads for the cluster), with release / acquire ordering of shared-memory accesses across the CTAs
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the row's reduction over all K CTAs: each CTA publishes its own result, then reads everybody's through distributed
+// shared memory and folds them in CTA order, so all CTAs hold the same bits
+template <int OP> __device__ __forceinline__ float row_reduce_cl(float v, float* sm, float* slot) {
+  v = row_reduce<OP>(v, sm);
+  if (K == 1) return v;
+  if (threadIdx.x == 0) *slot = v;
+  cluster_sync();
+  const u32 a = (u32)__cvta_generic_to_shared(slot);
+  float r = 0.f;
+#pragma unroll
+  for (int q = 0; q < K; ++q) {
+    u32 ra; float x;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a), "r"(q));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(x) : "r"(ra) : "memory");
+    r = q == 0 ? x : comb<OP>(r, x);
+  }
+  return r;
+}
 )SRC";
-  s << "extern \"C\" __global__ void __launch_bounds__(TPB) akgb_row_jit(";
+  s << "extern \"C\" __global__ void ";
+  if (K > 1) s << "__cluster_dims__(" << K << ", 1, 1) ";
+  s << "__launch_bounds__(TPB) akgb_row_jit(";
   for (size_t i = 0; i < P.in.size(); ++i) s << "const void* __restrict__ in" << i << ", ";
   for (size_t i = 0; i < P.out.size(); ++i) s << "void* __restrict__ out" << i << ", ";
   s << "i64 rows) {\n";
   s << "  __shared__ float sm[TPB / 32];\n  const int tr = threadIdx.x;\n";
+  if (staged) {
+    s << "  extern __shared__ __align__(16) unsigned char stage_mem[];\n";
+    s << "  __shared__ float cl_slot[" << std::max(1, ni) << "];\n";
+    s << "  const i64 c_lo = (i64)(blockIdx.x % K) * CH, c_hi = c_lo + CH < C ? c_lo + CH : (i64)C;\n";
+  } else {
+    s << "  constexpr i64 c_lo = 0, c_hi = C;\n";
+  }
   if (P.col_sums) {
     s << "  constexpr int NIT = " << nit << ";\n";
     for (size_t i = 0; i < P.out.size(); ++i)
@@ -601,7 +733,7 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
              "    for (int j = 0; j < VW; ++j) cs" << i << "[q][j] = 0.f;\n  }\n";
     s << "  for (i64 r = blockIdx.x; r < rows; r += gridDim.x) {\n";  // a fixed number of CTAs walk the rows
   } else {
-    s << "  const i64 r = blockIdx.x;\n";
+    s << "  const i64 r = blockIdx.x / K;\n";
   }
   // L2 policies: a row stays resident while later passes still need it and leaves first once the last pass has read it
   s << "  unsigned long long pol_last, pol_first;\n"
@@ -638,7 +770,9 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
   };
   // one pass over the row: everything per-element that `roots` need, recomputed from the inputs, then `tail`
   int pass_no = 0;
+  std::vector<char> stage_filled(P.in.size(), 0);
   auto emit_pass = [&](const std::vector<int>& roots, const std::string& tail, bool last = false) {
+    std::vector<int> filled_now;
     std::vector<char> need_instr(ni, 0), need_input(P.in.size(), 0);
     std::vector<int> stack(roots.begin(), roots.end());
     while (!stack.empty()) {
@@ -659,12 +793,12 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
         stack.push_back(x.c);
       }
     }
-    const bool rev = pass_no & 1;  // every other pass walks backwards: it starts with what the pass before left in L2
+    const bool rev = !staged && (pass_no & 1);  // every other pass walks backwards: it starts with what the pass before left in L2
     if (P.col_sums && last)  // fully unrolled, so that the column sums are indexed statically
       s << "#pragma unroll\n  for (int q = 0; q < NIT; ++q) {\n    const int it = " << (rev ? "NIT - 1 - q" : "q")
         << ";\n    const i64 c = (i64)tr * VW + (i64)it * (T * VW);\n    if (c >= C) continue;\n";
     else if (rev) s << "#pragma unroll 2\n  for (i64 c = (i64)tr * VW + (i64)((C - 1) / (T * VW)) * (T * VW); c >= 0; c -= (i64)T * VW) {\n    if (c >= C) continue;\n";
-    else s << "#pragma unroll 2\n  for (i64 c = (i64)tr * VW; c < C; c += (i64)T * VW) {\n";
+    else s << "#pragma unroll 2\n  for (i64 c = c_lo + (i64)tr * VW; c < c_hi; c += (i64)T * VW) {\n";
     ++pass_no;
     for (size_t i = 0; i < P.in.size(); ++i) {
       if (!need_input[i]) continue;
@@ -672,7 +806,13 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
       const std::string base = o.kind == RK_FULL ? "r * C" : o.kind == RK_COL ? "(i64)0" : "(r % " + std::to_string(o.mod_rows) + "LL) * C";
       s << "    " << (is_float_dt(o.dt) ? "float " : "int ") << name[o.val] << "[VW];\n";
       const bool pol = vec && o.kind == RK_FULL && is_float_dt(o.dt);
-      if (pol) s << "    ld8p_" << dt_tag(o.dt) << "(in" << i << ", " << base << " + c, " << name[o.val] << ", " << (last ? "pol_first" : "pol_last") << ");\n";
+      if (stage_off[i] >= 0 && !stage_filled[i]) {  // first pass over this input: from memory, kept in shared memory
+        s << "    ld8ps_" << dt_tag(o.dt) << "(in" << i << ", " << base << " + c, " << name[o.val] << ", pol_first, stage_mem + "
+          << stage_off[i] << ", c - c_lo);\n";
+        filled_now.push_back((int)i);
+      } else if (stage_off[i] >= 0) {
+        s << "    ld8s_" << dt_tag(o.dt) << "(stage_mem + " << stage_off[i] << ", c - c_lo, " << name[o.val] << ");\n";
+      } else if (pol) s << "    ld8p_" << dt_tag(o.dt) << "(in" << i << ", " << base << " + c, " << name[o.val] << ", " << (last ? "pol_first" : "pol_last") << ");\n";
       else if (vec) s << "    ld8_" << dt_tag(o.dt) << "(in" << i << ", " << base << " + c, " << name[o.val] << ", false);\n";
       else s << "    " << name[o.val] << "[0] = ld1_" << dt_tag(o.dt) << "(in" << i << ", " << base << " + c);\n";
     }
@@ -684,6 +824,8 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
         << name[x.dst] << "[j] = " << expr << ";\n";
     }
     s << tail << "  }\n";
+    // (every pass gives a thread the same columns, so a thread reads back only what it staged itself: no barrier)
+    for (int i : filled_now) stage_filled[i] = 1;
   };
   for (int k = 0; k < ni; ++k) {
     const RowInstr& x = P.instr[k];
@@ -695,7 +837,11 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
       tail << "#pragma unroll\n    for (int j = 0; j < VW; ++j) acc" << k << " = comb<" << x.red_op << ">(acc" << k << ", "
            << name[x.a] << "[j]);\n";
       emit_pass({x.a}, tail.str());
-      s << "  const float " << name[x.dst] << " = " << round_fn(x.dt) << "(row_reduce<" << x.red_op << ">(acc" << k << ", sm));\n";
+      if (staged)
+        s << "  const float " << name[x.dst] << " = " << round_fn(x.dt) << "(row_reduce_cl<" << x.red_op << ">(acc" << k
+          << ", sm, cl_slot + " << k << "));\n";
+      else
+        s << "  const float " << name[x.dst] << " = " << round_fn(x.dt) << "(row_reduce<" << x.red_op << ">(acc" << k << ", sm));\n";
     } else {
       const std::string expr = instr_expr(x.op, x.dt, x.cls, x.src_cls, x.a, x.b, x.c, ref);
       s << "  const " << (x.cls == EWC_FLOAT ? "float " : "int ") << name[x.dst] << " = " << expr << ";\n";
@@ -723,6 +869,7 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
     if (o.kind == RK_ROW)
       s << "  if (tr == 0) st1_" << dt_tag(o.dt) << "(out" << i << ", r, " << ref(o.val, is_float_dt(o.dt)) << ");\n";
   }
+  if (staged && K > 1) s << "  cluster_sync();\n";  // no CTA leaves while another may still read its partial results
   if (P.col_sums) {
     s << "  }\n";  // the walk over the rows
     for (size_t i = 0; i < P.out.size(); ++i) {
@@ -1005,6 +1152,7 @@ constexpr const char* kJitOptionsTag = "akgb-ew-jit-2 sm_100a c++17 fmad=false";
 struct JitKernel {
   CUfunction fn = nullptr;
   bool failed = false;
+  unsigned dyn_smem_allowed = 0;  // what cuFuncSetAttribute(MAX_DYNAMIC_SHARED_SIZE_BYTES) was last set to
 };
 std::mutex g_mu;
 std::map<std::string, JitKernel> g_cache;  // device + source text -> kernel (per process; modules live until exit)
@@ -1283,8 +1431,13 @@ cudaError_t row_jit_launch(const RowProgram& P, const void* const* in, void* con
   JitKernel* k = compile(src, "akgb_row_jit");
   if (!k || k->failed) return cudaErrorNotSupported;
   const int rpb = rs.tpb / rs.t;  // 1 for the multi-pass schedule
-  const int64_t grid = P.col_sums ? row_jit_col_sum_ctas(P) : (P.rows + rpb - 1) / rpb;
+  const int64_t grid = P.col_sums ? row_jit_col_sum_ctas(P) : ((P.rows + rpb - 1) / rpb) * rs.cluster;
   if (grid > 0x7fffffff) return cudaErrorNotSupported;
+  if (rs.dyn_smem > 32 * 1024 && k->dyn_smem_allowed < rs.dyn_smem) {  // static + dynamic above the 48 KB default
+    if (driver().FuncSetAttribute(k->fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)rs.dyn_smem) != CUDA_SUCCESS)
+      return cudaErrorNotSupported;
+    k->dyn_smem_allowed = rs.dyn_smem;
+  }
   long long rows = P.rows;
   void* args[32];
   const void* inp[16];
@@ -1302,8 +1455,9 @@ cudaError_t row_jit_launch(const RowProgram& P, const void* const* in, void* con
   if (dims) {
     dims->grid[0] = (unsigned)grid;
     dims->block[0] = (unsigned)rs.tpb;
+    dims->smem = rs.dyn_smem;
   }
-  const CUresult r = driver().LaunchKernel(k->fn, (unsigned)grid, 1, 1, (unsigned)rs.tpb, 1, 1, 0, (CUstream)s, args, nullptr);
+  const CUresult r = driver().LaunchKernel(k->fn, (unsigned)grid, 1, 1, (unsigned)rs.tpb, 1, 1, rs.dyn_smem, (CUstream)s, args, nullptr);
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorLaunchFailure;
 }
 
@@ -1361,11 +1515,12 @@ bool row_jit_export(const RowProgram& P, const std::string& entry, std::vector<c
   *cubin = compile_to_cubin(src);
   if (cubin->empty()) return false;
   const int rpb = rs.tpb / rs.t;
-  const int64_t grid = (P.rows + rpb - 1) / rpb;
+  const int64_t grid = ((P.rows + rpb - 1) / rpb) * rs.cluster;
   if (grid > 0x7fffffff) return false;
   *dims = LaunchDims();
   dims->grid[0] = (unsigned)grid;
   dims->block[0] = (unsigned)rs.tpb;
+  dims->smem = rs.dyn_smem;  // above 48 KB the loader must raise the function's dynamic shared memory limit first
   *needs_align16 = vec;
   return true;
 }

@@ -108,6 +108,10 @@ struct RowProgram {
   // gradients next to the row-wise input gradient).  Those results are outputs of kind RK_COL; the kernel is then
   // launched with a fixed number of CTAs that walk the rows and writes one partial [cols] vector per CTA and result.
   bool col_sums = false;
+  // Rows too long for registers: keep the inputs that several passes read in shared memory (a cluster of CTAs per row
+  // when one CTA's shared memory is too small, reductions completed through distributed shared memory) instead of
+  // re-reading them through L2.  Off by default: measured slower than the L2 schedule on B200 (AKGB_FLAG_STAGE_LONG_ROWS).
+  bool stage_long_rows = false;
 };
 
 }  // namespace akgb

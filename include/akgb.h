@@ -91,6 +91,13 @@ typedef struct akgb_options {
  * CUDA graph), so this is off by default; a sharded reduction that completes its exchange in its own launch
  * (akgb_launch_sharded) folds in-launch regardless. */
 #define AKGB_FLAG_FOLD_IN_LAUNCH 2
+/* Reduce-X regions whose rows do not fit the register file (above about 16 384 elements) walk the row once per
+ * reduction.  By default the passes after the first re-read the row through L2 (evict-last hints, alternating walk
+ * direction).  With this flag the first pass keeps the row in shared memory instead -- across a thread-block cluster
+ * of 2, 4 or 8 CTAs when it exceeds one CTA's share, the per-row reductions then completed through distributed shared
+ * memory -- so the row crosses HBM/L2 once.  Identical results.  Measured on B200 the L2 schedule is the faster one
+ * (log-softmax float32 [8192,32000]: 415 us against 523 us staged), which is why this is opt-in. */
+#define AKGB_FLAG_STAGE_LONG_ROWS 4
 
 typedef struct akgb_kernel akgb_kernel;
 

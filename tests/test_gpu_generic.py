@@ -754,6 +754,47 @@ def test_reduce_x_regions_as_one_generated_kernel(lib, kind, rows_shape, cols, d
         assert k.launch_count > 1
 
 
+@pytest.mark.parametrize("kind,rows_shape,cols,dtype,cluster", [
+    ("log_softmax", [70], 32000, "float32", 2),       # 125 KB per row: two CTAs share a row
+    ("rmsnorm", [33], 20000, "float16", 1),           # 39 KB: one CTA keeps its row
+    ("select_softmax", [2, 9], 24576, "bfloat16", 1),  # exactly 48 KB of dynamic shared memory
+    ("log_softmax", [9], 131072, "float32", 8),       # 512 KB per row: a cluster of eight
+    ("log_softmax", [5], 100008, "bfloat16", 4),      # chunks of different length (the last CTA's is shorter)
+])
+def test_long_rows_staged_in_shared_memory_across_a_cluster(lib, kind, rows_shape, cols, dtype, cluster):
+    """AKGB_FLAG_STAGE_LONG_ROWS: the first pass keeps the row in shared memory, a thread-block cluster shares rows that
+    exceed one CTA's part, per-row reductions are completed through distributed shared memory.  Same bits as the
+    default schedule (which re-reads the row through L2) when one CTA holds the row; within the tolerance of the
+    region otherwise (the fold over the CTAs of a cluster changes the order of the sums)."""
+    from akg_b200 import _capi
+    if FLAGS[0] != 0:
+        pytest.skip("generated kernels only")
+    rng = np.random.default_rng(cols % 1000)
+    d = _rows_region(kind, rows_shape, cols, dtype)
+    ins = []
+    for (t,) in d["input_desc"]:
+        if t["data_type"] == "bool":
+            a = rng.random(t["shape"]) < 0.7
+            a[:, 0] = True
+            ins.append(a)
+        elif t["tensor_name"] == "g":
+            ins.append(rng.uniform(0.5, 1.5, t["shape"]).astype(np.float32))
+        else:
+            npdt = BF16 if t["data_type"] == "bfloat16" else np.dtype(t["data_type"])
+            ins.append(rng.standard_normal(t["shape"]).astype(np.float32).astype(npdt))
+    base, _ = guarded_launch(d, ins)
+    got, k = guarded_launch(d, ins, flags=_capi.AKGB_FLAG_STAGE_LONG_ROWS)
+    src = k.jit_source()
+    assert "stage_mem" in src and f"K = {cluster}" in src and (cluster == 1 or f"__cluster_dims__({cluster}, 1, 1)" in src)
+    want = O.evaluate(d, ins, accum="float64")
+    tol = 1e-5 if dtype == "float32" else 4e-3
+    for g_, b_, w_ in zip(got, base, want):
+        if cluster == 1:
+            assert bits_equal(g_, b_)
+        scale = float(np.abs(w_.astype(np.float64)).max())
+        np.testing.assert_allclose(g_.astype(np.float64), w_.astype(np.float64), rtol=tol, atol=tol * max(scale, 1e-6))
+
+
 @pytest.mark.parametrize("shape,k,cols_kind", [
     ([4096, 1024], 1, "plain"),       # dgamma-like: sum over rows of dy * xhat
     ([8, 600, 768], 2, "with_col"),   # two leading axes folded, a [cols] operand in the chain
