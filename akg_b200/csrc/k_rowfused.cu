@@ -12,6 +12,7 @@
 // order differs from a sequential loop
 // (akg-mlir/lib/Conversion/MindSporeToLinalg/MindSporeToLinalg.cpp:1401-1426).
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 #include "async.cuh"
@@ -455,12 +456,25 @@ cudaError_t layernorm_f32(const LayerNormParams& p, const float* x, const float*
     // one row per warp, 4 warps per CTA: measured equal or better than 1, 2 or 8 warps per CTA and than
     // register caps that raise occupancy (13.4 us for [8192,1024], 42.2 us for [32768,1024])
     constexpr int WPC = 4;
-    const int64_t grid = (p.rows + WPC - 1) / WPC;
+    int64_t grid = (p.rows + WPC - 1) / WPC;
+    const int64_t v = (p.cols + 127) / 128;
+    // experiment hook (probing only): AKGB_LN_VARIANT=1 one wave of 7 CTAs per SM, rows in a grid-stride loop
+    static const int variant = [] { const char* e = std::getenv("AKGB_LN_VARIANT"); return e ? std::atoi(e) : 0; }();
+    if (variant >= 1 && v == 8) {
+      const int per_sm = variant == 1 ? 7 : variant == 2 ? 6 : 5;
+      grid = std::min<int64_t>(grid, (int64_t)sms * per_sm);
+      if (dims) {
+        dims->grid[0] = (unsigned)grid;
+        dims->block[0] = WPC * 32;
+      }
+      if (variant == 1) layernorm_rows_f32_kernel<8, WPC, 7><<<(unsigned)grid, WPC * 32, 0, s>>>(p, x, gamma, beta, y, mean, var);
+      else layernorm_rows_f32_kernel<8, WPC, 1><<<(unsigned)grid, WPC * 32, 0, s>>>(p, x, gamma, beta, y, mean, var);
+      return cudaGetLastError();
+    }
     if (dims) {
       dims->grid[0] = (unsigned)grid;
       dims->block[0] = WPC * 32;
     }
-    const int64_t v = (p.cols + 127) / 128;
 #define AKGB_LN(V) layernorm_rows_f32_kernel<V, WPC, 1><<<(unsigned)grid, WPC * 32, 0, s>>>(p, x, gamma, beta, y, mean, var)
     if (v <= 1) AKGB_LN(1);
     else if (v <= 2) AKGB_LN(2);
