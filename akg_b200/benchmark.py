@@ -28,6 +28,9 @@ CASES = {
     "colsum": (lambda s: descs.reduce_sum_axis0(s[0], s[1]), {}),
     "gmax": (lambda s: descs.reduce_max_all(s[0], s[1]), {}),
     "transpose": (lambda s: descs.transpose(s, [0, 2, 1, 3]), {}),
+    # the last two axes swapped (the innermost output axis is strided in the input); --dtype picks the element type
+    "transpose_tile": (lambda s, dtype="float16": descs.transpose(s, list(range(len(s) - 2)) + [len(s) - 1, len(s) - 2],
+                                                                  dtype), {}),
     "rmsnorm": (lambda s: descs.rmsnorm(s[0], s[1]), {"g": "gamma"}),
     "mulsum_rows": (lambda s: descs.mul_reduce_sum(s[0], s[1], [0]), {}),
     "mulsum_all": (lambda s: descs.mul_reduce_sum(s[0], s[1], [0, 1]), {}),
@@ -82,7 +85,7 @@ def main(argv=None):
     ap.add_argument("-f", "--file", help="fused-op description (.info JSON)")
     ap.add_argument("--case", choices=sorted(CASES), help="build a benchmarked description instead")
     ap.add_argument("--shape", default="", help="comma-separated extents for --case")
-    ap.add_argument("--dtype", default="", help="operand type for --case matmul (bfloat16, float16, float32)")
+    ap.add_argument("--dtype", default="", help="element type for --case matmul / transpose_tile")
     ap.add_argument("--repeat", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--device", type=int, default=0)
@@ -96,7 +99,7 @@ def main(argv=None):
     else:
         shape = [int(x) for x in args.shape.split(",") if x]
         build, kinds = CASES[args.case]
-        desc = build(shape, args.dtype) if args.dtype and args.case == "matmul" else build(shape)
+        desc = build(shape, args.dtype) if args.dtype and args.case in ("matmul", "transpose_tile") else build(shape)
     torch.cuda.set_device(args.device)
     device = torch.device("cuda", args.device)
     k = FusedKernel(desc, device=args.device)

@@ -12,7 +12,6 @@
 // order differs from a sequential loop
 // (akg-mlir/lib/Conversion/MindSporeToLinalg/MindSporeToLinalg.cpp:1401-1426).
 #include <algorithm>
-#include <cstdlib>
 #include <mutex>
 
 #include "async.cuh"
@@ -458,17 +457,17 @@ cudaError_t layernorm_f32(const LayerNormParams& p, const float* x, const float*
     constexpr int WPC = 4;
     int64_t grid = (p.rows + WPC - 1) / WPC;
     const int64_t v = (p.cols + 127) / 128;
-    // experiment hook (probing only): AKGB_LN_VARIANT=1 one wave of 7 CTAs per SM, rows in a grid-stride loop
-    static const int variant = [] { const char* e = std::getenv("AKGB_LN_VARIANT"); return e ? std::atoi(e) : 0; }();
-    if (variant >= 1 && v == 8) {
-      const int per_sm = variant == 1 ? 7 : variant == 2 ? 6 : 5;
-      grid = std::min<int64_t>(grid, (int64_t)sms * per_sm);
+    // 1024-column rows: the kernel needs 82 registers (6 CTAs per SM).  When the grid is just above six CTAs per SM
+    // but within seven, the variant capped at 72 registers keeps every CTA resident at once instead of leaving a
+    // small second wave: [4096,1024] 9.1 -> 8.0 us.  With several waves the uncapped kernel is the faster one
+    // ([8192,1024]: 13.4 against 14.2 us), and fewer, longer-lived CTAs (one wave, rows in a grid-stride loop) are
+    // slower still (14.2 us).
+    if (v == 8 && grid > (int64_t)sms * 6 && grid <= (int64_t)sms * 7) {
       if (dims) {
         dims->grid[0] = (unsigned)grid;
         dims->block[0] = WPC * 32;
       }
-      if (variant == 1) layernorm_rows_f32_kernel<8, WPC, 7><<<(unsigned)grid, WPC * 32, 0, s>>>(p, x, gamma, beta, y, mean, var);
-      else layernorm_rows_f32_kernel<8, WPC, 1><<<(unsigned)grid, WPC * 32, 0, s>>>(p, x, gamma, beta, y, mean, var);
+      layernorm_rows_f32_kernel<8, WPC, 7><<<(unsigned)grid, WPC * 32, 0, s>>>(p, x, gamma, beta, y, mean, var);
       return cudaGetLastError();
     }
     if (dims) {

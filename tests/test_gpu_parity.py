@@ -87,7 +87,7 @@ def test_gelu_chain_covers_every_float16_value(lib):
                                              (1, 4, True), (64, 129, False),
                                              # many rows (several waves of CTAs), widths on either side of the vector-per-lane steps
                                              (8192, 256, True), (5000, 1000, False), (4736, 132, True), (10001, 8, True),
-                                             (6000, 1024, True), (4800, 2048, True)])
+                                             (6000, 1024, True), (4800, 2048, True), (4096, 1024, True), (3700, 1024, False)])
 def test_layernorm(lib, rows, cols, stats):
     d = descs.layernorm(rows, cols, with_stats=stats)
     ins = make_inputs(d, 12, KINDS["layernorm"])
