@@ -225,8 +225,7 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
         e = argmax_axis(a, o, st.ix_outer, st.ix_dim, st.ix_inner, st.ix_esize, st.ix_idx64, s, &st.dims);
         break;
       case StepK::SegmentSum:
-        e = segment_sum_f32((const float*)a, b, (float*)o, st.ix_n, st.ix_inner, st.ix_segments, st.ix_idx64, s,
-                            &st.dims);
+        e = segment_sum(a, b, o, st.ix_n, st.ix_inner, st.ix_segments, st.ix_idx64, st.ix_esize, s, &st.dims);
         break;
       case StepK::RowJit: {
         const void* ins[16];
@@ -261,6 +260,9 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
         for (size_t i = 0; i < st.ew_in.size(); ++i) ins[i] = resolve(st.ew_in[i], tensors, ws);
         for (size_t i = 0; i < st.ew_out.size(); ++i) outs[i] = resolve(st.ew_out[i], tensors, ws);
         e = ew_generic(st.ew, ins, outs, !k->no_jit, s, &st.dims);
+        if (e == cudaErrorNotSupported)
+          return fail(AKGB_UNSUPPORTED, "this region holds 64-bit integer values and needs the run-time compiler, which is "
+                                        "switched off (AKGB_FLAG_NO_JIT) or not available on this host");
         break;
       }
       case StepK::ReduceColDual:

@@ -145,17 +145,17 @@ __device__ __forceinline__ void ld8_f32(const void* p, i64 e0, float* r, bool st
   const U4 b = stream ? ld16s((const float*)p + e0 + 4) : ld16c((const float*)p + e0 + 4);
   r[0] = __uint_as_float(a.x); r[1] = __uint_as_float(a.y); r[2] = __uint_as_float(a.z); r[3] = __uint_as_float(a.w);
   r[4] = __uint_as_float(b.x); r[5] = __uint_as_float(b.y); r[6] = __uint_as_float(b.z); r[7] = __uint_as_float(b.w); }
-__device__ __forceinline__ void ld8_i32(const void* p, i64 e0, int* r, bool stream) {
+template <class I> __device__ __forceinline__ void ld8_i32(const void* p, i64 e0, I* r, bool stream) {
   const U4 a = stream ? ld16s((const int*)p + e0) : ld16c((const int*)p + e0);
   const U4 b = stream ? ld16s((const int*)p + e0 + 4) : ld16c((const int*)p + e0 + 4);
   r[0] = (int)a.x; r[1] = (int)a.y; r[2] = (int)a.z; r[3] = (int)a.w; r[4] = (int)b.x; r[5] = (int)b.y; r[6] = (int)b.z; r[7] = (int)b.w; }
-__device__ __forceinline__ void ld8_i16(const void* p, i64 e0, int* r, bool stream) {
+template <class I> __device__ __forceinline__ void ld8_i16(const void* p, i64 e0, I* r, bool stream) {
   const U4 v = stream ? ld16s((const u16*)p + e0) : ld16c((const u16*)p + e0); const u32 w[4] = {v.x, v.y, v.z, v.w};
   _Pragma("unroll") for (int i = 0; i < 4; ++i) { r[2*i] = (int)(short)(w[i] & 0xffffu); r[2*i+1] = (int)(short)(w[i] >> 16); } }
-__device__ __forceinline__ void ld8_i8(const void* p, i64 e0, int* r, bool stream) {
+template <class I> __device__ __forceinline__ void ld8_i8(const void* p, i64 e0, I* r, bool stream) {
   const U2 v = ld8s((const u8*)p + e0); const u32 w[2] = {v.x, v.y};
   _Pragma("unroll") for (int i = 0; i < 8; ++i) r[i] = (int)(signed char)((w[i >> 2] >> (8 * (i & 3))) & 0xffu); }
-__device__ __forceinline__ void ld8_bool(const void* p, i64 e0, int* r, bool stream) {
+template <class I> __device__ __forceinline__ void ld8_bool(const void* p, i64 e0, I* r, bool stream) {
   const U2 v = ld8s((const u8*)p + e0); const u32 w[2] = {v.x, v.y};
   _Pragma("unroll") for (int i = 0; i < 8; ++i) r[i] = ((w[i >> 2] >> (8 * (i & 3))) & 0xffu) ? 1 : 0; }
 #define ST8_16(NAME, CVT) __device__ __forceinline__ void NAME(void* p, i64 e0, const float* r) { U4 v; \
@@ -167,15 +167,15 @@ __device__ __forceinline__ void st8_f32(void* p, i64 e0, const float* r) {
   U4 a, b; a.x = __float_as_uint(r[0]); a.y = __float_as_uint(r[1]); a.z = __float_as_uint(r[2]); a.w = __float_as_uint(r[3]);
   b.x = __float_as_uint(r[4]); b.y = __float_as_uint(r[5]); b.z = __float_as_uint(r[6]); b.w = __float_as_uint(r[7]);
   st16((float*)p + e0, a); st16((float*)p + e0 + 4, b); }
-__device__ __forceinline__ void st8_i32(void* p, i64 e0, const int* r) {
-  U4 a, b; a.x = r[0]; a.y = r[1]; a.z = r[2]; a.w = r[3]; b.x = r[4]; b.y = r[5]; b.z = r[6]; b.w = r[7];
+template <class I> __device__ __forceinline__ void st8_i32(void* p, i64 e0, const I* r) {
+  U4 a, b; a.x = (u32)r[0]; a.y = (u32)r[1]; a.z = (u32)r[2]; a.w = (u32)r[3]; b.x = (u32)r[4]; b.y = (u32)r[5]; b.z = (u32)r[6]; b.w = (u32)r[7];
   st16((int*)p + e0, a); st16((int*)p + e0 + 4, b); }
-__device__ __forceinline__ void st8_i16(void* p, i64 e0, const int* r) { U4 v;
+template <class I> __device__ __forceinline__ void st8_i16(void* p, i64 e0, const I* r) { U4 v;
   v.x = (u32)(u16)r[0] | ((u32)(u16)r[1] << 16); v.y = (u32)(u16)r[2] | ((u32)(u16)r[3] << 16);
   v.z = (u32)(u16)r[4] | ((u32)(u16)r[5] << 16); v.w = (u32)(u16)r[6] | ((u32)(u16)r[7] << 16); st16((u16*)p + e0, v); }
-__device__ __forceinline__ void st8_i8(void* p, i64 e0, const int* r) { U2 v; v.x = 0; v.y = 0;
+template <class I> __device__ __forceinline__ void st8_i8(void* p, i64 e0, const I* r) { U2 v; v.x = 0; v.y = 0;
   _Pragma("unroll") for (int i = 0; i < 4; ++i) { v.x |= ((u32)(u8)r[i]) << (8 * i); v.y |= ((u32)(u8)r[4 + i]) << (8 * i); } st8((u8*)p + e0, v); }
-__device__ __forceinline__ void st8_bool(void* p, i64 e0, const int* r) { U2 v; v.x = 0; v.y = 0;
+template <class I> __device__ __forceinline__ void st8_bool(void* p, i64 e0, const I* r) { U2 v; v.x = 0; v.y = 0;
   _Pragma("unroll") for (int i = 0; i < 4; ++i) { v.x |= (r[i] ? 1u : 0u) << (8 * i); v.y |= (r[4 + i] ? 1u : 0u) << (8 * i); } st8((u8*)p + e0, v); }
 // scalar element access (any alignment)
 __device__ __forceinline__ float ld1_f16(const void* p, i64 i) { return h2f(((const u16*)p)[i]); }
@@ -192,6 +192,18 @@ __device__ __forceinline__ void st1_i32(void* p, i64 i, int v) { ((int*)p)[i] = 
 __device__ __forceinline__ void st1_i16(void* p, i64 i, int v) { ((short*)p)[i] = (short)v; }
 __device__ __forceinline__ void st1_i8(void* p, i64 i, int v) { ((signed char*)p)[i] = (signed char)v; }
 __device__ __forceinline__ void st1_bool(void* p, i64 i, int v) { ((u8*)p)[i] = v ? 1 : 0; }
+// 64-bit integers (programs that hold any keep ALL their integer registers in 64 bits)
+__device__ __forceinline__ i64 wr_i64(i64 x) { return x; }
+__device__ __forceinline__ i64 ld1_i64(const void* p, i64 i) { return ((const i64*)p)[i]; }
+__device__ __forceinline__ void st1_i64(void* p, i64 i, i64 v) { ((i64*)p)[i] = v; }
+__device__ __forceinline__ void ld8_i64(const void* p, i64 e0, i64* r, bool stream) {
+  _Pragma("unroll") for (int q = 0; q < 4; ++q) {
+    const U4 v = stream ? ld16s((const i64*)p + e0 + 2 * q) : ld16c((const i64*)p + e0 + 2 * q);
+    r[2*q] = (i64)(((unsigned long long)v.y << 32) | v.x); r[2*q+1] = (i64)(((unsigned long long)v.w << 32) | v.z); } }
+__device__ __forceinline__ void st8_i64(void* p, i64 e0, const i64* r) {
+  _Pragma("unroll") for (int q = 0; q < 4; ++q) { U4 v;
+    v.x = (u32)r[2*q]; v.y = (u32)((unsigned long long)r[2*q] >> 32); v.z = (u32)r[2*q+1]; v.w = (u32)((unsigned long long)r[2*q+1] >> 32);
+    st16((i64*)p + e0 + 2 * q, v); } }
 )SRC";
 
 const char* dt_tag(int dt) {
@@ -202,12 +214,23 @@ const char* dt_tag(int dt) {
     case DT::I32: return "i32";
     case DT::I16: return "i16";
     case DT::I8: return "i8";
+    case DT::I64: return "i64";
     default: return "bool";
   }
 }
+// a program with a 64-bit integer operand or result keeps all its integer registers in 64 bits
+bool ew_has_i64(const EwProgram& P) {
+  for (int i = 0; i < P.n_in; ++i)
+    if ((DT)P.in[i].dt == DT::I64) return true;
+  for (int i = 0; i < P.n_out; ++i)
+    if ((DT)P.out[i].dt == DT::I64) return true;
+  for (int k = 0; k < P.n_instr; ++k)
+    if ((DT)P.instr[k].dt == DT::I64) return true;
+  return false;
+}
 bool is_float_dt(int dt) { return (DT)dt == DT::F16 || (DT)dt == DT::BF16 || (DT)dt == DT::F32; }
 const char* round_fn(int dt) { return (DT)dt == DT::F16 ? "rn_f16" : (DT)dt == DT::BF16 ? "rn_bf16" : "rn_f32"; }
-const char* wrap_fn(int dt) { return (DT)dt == DT::I8 ? "wr_i8" : (DT)dt == DT::I16 ? "wr_i16" : "wr_i32"; }
+const char* wrap_fn(int dt) { return (DT)dt == DT::I8 ? "wr_i8" : (DT)dt == DT::I16 ? "wr_i16" : (DT)dt == DT::I64 ? "wr_i64" : "wr_i32"; }
 
 struct Var {
   std::string name;
@@ -356,6 +379,8 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
   for (int i = 0; i < P.n_out; ++i)
     if (P.out[i].kind != EWI_FULL && P.out[i].kind != EWI_STRIDED) return false;
   std::ostringstream s;
+  const bool i64 = ew_has_i64(P);
+  const std::string ity = i64 ? "long long" : "int";
   s << kPreamble;
   s << "extern \"C\" __global__ void __launch_bounds__(256) akgb_ew_jit(";
   for (int i = 0; i < P.n_in; ++i) s << "const void* __restrict__ in" << i << ", ";
@@ -379,7 +404,7 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
   for (int i = 0; i < P.n_in; ++i) {
     const EwOperand& o = P.in[i];
     const bool fl = is_float_dt(o.dt);
-    s << "  " << (fl ? "float" : "int") << " a" << i << "[U][E];\n";
+    s << "  " << (fl ? "float" : ity) << " a" << i << "[U][E];\n";
     Var v;
     v.name = "a" + std::to_string(i);
     v.is_float = fl;
@@ -397,7 +422,7 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
         s << "      #pragma unroll\n      for (int j = 0; j < 8; ++j) a" << i << "[u][j] = ld1_" << tag << "(in" << i
           << ", (v * 8 + j) % " << o.mod << "LL);\n";
       else if (o.kind == EWI_STRIDED && strided_run8_const(P, o))  // one value for the whole granule (a per-channel operand)
-        s << "      { const " << (is_float_dt(o.dt) ? "float" : "int") << " t = ld1_" << tag << "(in" << i << ", "
+        s << "      { const " << (is_float_dt(o.dt) ? "float" : ity) << " t = ld1_" << tag << "(in" << i << ", "
           << strided_index(P, o, "(v * 8)") << ");\n        #pragma unroll\n        for (int j = 0; j < 8; ++j) a" << i
           << "[u][j] = t; }\n";
       else if (o.kind == EWI_STRIDED && strided_vec8_ok(P, o))
@@ -406,7 +431,7 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
         s << "      #pragma unroll\n      for (int j = 0; j < 8; ++j) a" << i << "[u][j] = ld1_" << tag << "(in" << i
           << ", " << strided_index(P, o, "(v * 8 + j)") << ");\n";
       else  // scalar
-        s << "      { const " << (is_float_dt(o.dt) ? "float" : "int") << " t = ld1_" << tag << "(in" << i
+        s << "      { const " << (is_float_dt(o.dt) ? "float" : ity) << " t = ld1_" << tag << "(in" << i
           << ", 0);\n        #pragma unroll\n        for (int j = 0; j < 8; ++j) a" << i << "[u][j] = t; }\n";
     } else {
       if (o.kind == EWI_FULL) s << "      a" << i << "[u][0] = ld1_" << tag << "(in" << i << ", v);\n";
@@ -421,7 +446,7 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
   s << "  #pragma unroll\n  for (int u = 0; u < U; ++u) {\n    const i64 v = vbase + (i64)u * 256;\n    if (v < nv) {\n";
   auto ref = [&](int reg, bool want_float) -> std::string {
     const Var& v = regs[reg];
-    if (v.is_const) return want_float ? "__uint_as_float(" + v.literal + ")" : "(int)" + v.literal;
+    if (v.is_const) return want_float ? "__uint_as_float(" + v.literal + ")" : (i64 ? "(long long)(int)" : "(int)") + v.literal;
     return v.name + "[u][j]";
   };
   int tcount = 0;
@@ -430,7 +455,7 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
     const bool fl = ins.cls == EWC_FLOAT;
     std::string name = "t" + std::to_string(tcount++);
     const std::string expr = instr_expr(ins.op, ins.dt, ins.cls, ins.src_cls, ins.a, ins.b, ins.c, ref);
-    s << "      " << (fl ? "float " : "int ") << name << "[E];\n";
+    s << "      " << (fl ? "float" : ity) << " " << name << "[E];\n";
     s << "      #pragma unroll\n      for (int j = 0; j < E; ++j) " << name << "[j] = " << expr << ";\n";
     Var nv;
     nv.name = name;
@@ -463,7 +488,7 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
     const bool fl = is_float_dt(o.dt);
     std::string src;
     if (v.is_const) {
-      t << "      " << (fl ? "float" : "int") << " oc" << i << "[E];\n      #pragma unroll\n      for (int j = 0; j < E; ++j) oc"
+      t << "      " << (fl ? "float" : ity) << " oc" << i << "[E];\n      #pragma unroll\n      for (int j = 0; j < E; ++j) oc"
         << i << "[j] = " << (fl ? "__uint_as_float(" + v.literal + ")" : "(int)" + v.literal) << ";\n";
       src = "oc" + std::to_string(i);
     } else if (!v.name.empty() && v.name.back() == '#') {
@@ -1524,6 +1549,8 @@ bool row_jit_export(const RowProgram& P, const std::string& entry, std::vector<c
   *needs_align16 = vec;
   return true;
 }
+
+bool ew_program_needs_jit(const EwProgram& P) { return ew_has_i64(P); }
 
 // The CUDA C++ text that would be compiled for this program (empty when the program needs the interpreter).
 std::string ew_jit_source(const EwProgram& P, bool vec) {

@@ -231,6 +231,7 @@ cudaError_t ew_generic(const EwProgram& p, const void* const* in, void* const* o
     const cudaError_t je = ew_jit_launch(p, in, out, s, dims);
     if (je != cudaErrorNotSupported) return je;
   }
+  if (ew_program_needs_jit(p)) return cudaErrorNotSupported;  // 64-bit integers: no interpreter behind the generated kernel
   EwPtrs ptrs;
   for (int i = 0; i < kEwMaxIn; ++i) ptrs.in[i] = i < p.n_in ? in[i] : nullptr;
   for (int i = 0; i < kEwMaxOut; ++i) ptrs.out[i] = i < p.n_out ? out[i] : nullptr;

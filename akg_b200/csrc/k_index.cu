@@ -44,10 +44,13 @@ __global__ void __launch_bounds__(256) gather_kernel(const T* __restrict__ data,
   }
 }
 
-__global__ void __launch_bounds__(256) segment_sum_f32_kernel(const float* __restrict__ data,
-                                                              const void* __restrict__ ids, float* __restrict__ out,
-                                                              int64_t nids, int64_t inner, int64_t num_segments,
-                                                              int idx64) {
+// T: float, int32, __half, __nv_bfloat16 -- the sum accumulates in the element type, as the reference's loop nest does
+// (akg-mlir/lib/Conversion/MindSporeToLinalg/MindSporeToLinalg.cpp:596-744); atomics make the order of the additions
+// (and with it the last bits of floating-point results) vary from run to run
+template <typename T>
+__global__ void __launch_bounds__(256) segment_sum_kernel(const T* __restrict__ data, const void* __restrict__ ids,
+                                                          T* __restrict__ out, int64_t nids, int64_t inner,
+                                                          int64_t num_segments, int idx64) {
   const int64_t total = nids * inner;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
@@ -208,16 +211,27 @@ cudaError_t argmax_axis(const void* data, void* out, int64_t outer, int64_t dim,
   }
 }
 
-cudaError_t segment_sum_f32(const float* data, const void* ids, float* out, int64_t nids, int64_t inner,
-                            int64_t num_segments, int idx64, cudaStream_t s, LaunchDims* dims) {
-  cudaError_t e = cudaMemsetAsync(out, 0, (size_t)(num_segments * inner) * sizeof(float), s);
+cudaError_t segment_sum(const void* data, const void* ids, void* out, int64_t nids, int64_t inner,
+                        int64_t num_segments, int idx64, int dt, cudaStream_t s, LaunchDims* dims) {
+  const size_t esize = dt == kF32 || dt == 3 /* int32 */ ? 4 : 2;
+  cudaError_t e = cudaMemsetAsync(out, 0, (size_t)(num_segments * inner) * esize, s);  // zero bits are 0 in every type
   if (e != cudaSuccess || nids * inner == 0) return e;
   const int grid = grid_for(nids * inner);
   if (dims) {
     dims->grid[0] = grid;
     dims->block[0] = 256;
   }
-  segment_sum_f32_kernel<<<grid, 256, 0, s>>>(data, ids, out, nids, inner, num_segments, idx64);
+  if (dt == kF32)
+    segment_sum_kernel<float><<<grid, 256, 0, s>>>((const float*)data, ids, (float*)out, nids, inner, num_segments, idx64);
+  else if (dt == 3)
+    segment_sum_kernel<int><<<grid, 256, 0, s>>>((const int*)data, ids, (int*)out, nids, inner, num_segments, idx64);
+  else if (dt == kF16)
+    segment_sum_kernel<__half><<<grid, 256, 0, s>>>((const __half*)data, ids, (__half*)out, nids, inner, num_segments, idx64);
+  else if (dt == kBF16)
+    segment_sum_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)data, ids, (__nv_bfloat16*)out, nids, inner,
+                                                           num_segments, idx64);
+  else
+    return cudaErrorInvalidValue;
   return cudaGetLastError();
 }
 

@@ -120,6 +120,8 @@ bool ew_jit_export(const EwProgram& p, const std::string& entry, std::vector<cha
                    bool* needs_align16);
 bool row_jit_export(const RowProgram& p, const std::string& entry, std::vector<char>* cubin, LaunchDims* dims,
                     bool* needs_align16);
+// programs the interpreting kernel cannot run (64-bit integer values): they need the run-time compiler
+bool ew_program_needs_jit(const EwProgram& p);
 void ew_jit_prepare(const EwProgram& p);
 void row_jit_prepare(const RowProgram& p);
 void jit_set_cache_dir(const char* dir);  // nullptr: environment's choice; "": no disk cache
@@ -195,9 +197,10 @@ akgb_status launch_with_exchange(akgb_kernel* k, const FinishExchange& base, voi
 // out[o, i, r] = data[o, idx[i], r]; data is [outer, dim, inner] elements of `esize` bytes; idx int32 or int64
 cudaError_t gather_rows(const void* data, const void* idx, void* out, int64_t outer, int64_t dim, int64_t nidx,
                         int64_t inner, int esize, int idx64, cudaStream_t s, LaunchDims* dims);
-// out[num_segments, inner] = 0; out[ids[i], :] += data[i, :]
-cudaError_t segment_sum_f32(const float* data, const void* ids, float* out, int64_t nids, int64_t inner,
-                            int64_t num_segments, int idx64, cudaStream_t s, LaunchDims* dims);
+// out[num_segments, inner] = 0; out[ids[i], :] += data[i, :]; dt = DT code of data and out (float32, int32, float16,
+// bfloat16), the sum accumulates in that type
+cudaError_t segment_sum(const void* data, const void* ids, void* out, int64_t nids, int64_t inner, int64_t num_segments,
+                        int idx64, int dt, cudaStream_t s, LaunchDims* dims);
 
 // index of the first maximum along `dim` of a [outer, dim, inner] tensor (NaN counts as the maximum, as np.argmax);
 // in_dt is the DT code of the data (float32, float16, bfloat16, int32), out64 selects int64 indices

@@ -68,7 +68,8 @@ bool ew_opcode(OpK k, EwOp* op) {
   }
 }
 
-bool ew_dtype_ok(DT d) { return d != DT::I64 && d != DT::F64 && d != DT::Invalid; }
+// int64 values run in generated kernels only (all integer registers widened to 64 bits); float64 is not placed
+bool ew_dtype_ok(DT d) { return d != DT::F64 && d != DT::Invalid; }
 
 uint32_t const_bits(double v, DT d) {
   float f;
@@ -77,7 +78,10 @@ uint32_t const_bits(double v, DT d) {
     case DT::BF16: f = round_f64_to_bf16(v); break;
     case DT::F32: f = (float)v; break;
     case DT::Bool: return v != 0.0 ? 1u : 0u;
-    default: return (uint32_t)(int32_t)std::llround(v);
+    default:
+      if (d == DT::I64 && (v > 2147483647.0 || v < -2147483648.0))
+        throw Unsupported("64-bit integer constant outside the 32-bit range");
+      return (uint32_t)(int32_t)std::llround(v);
   }
   uint32_t b;
   std::memcpy(&b, &f, 4);
@@ -89,7 +93,7 @@ uint32_t const_bits(double v, DT d) {
 // shared with the row-program builder (rowfuse.cpp)
 bool ew_opcode_of(OpK k, EwOp* op) { return ew_opcode(k, op); }
 uint32_t ew_const_bits(double v, DT d) { return const_bits(v, d); }
-bool ew_type_ok(DT d) { return ew_dtype_ok(d); }
+bool ew_type_ok(DT d) { return ew_dtype_ok(d) && d != DT::I64; }  // row / column programs keep 32-bit integers
 
 namespace {
 
@@ -772,11 +776,13 @@ struct Builder {
   void add_segment_sum(const Node& n) {
     const Value& data = g.v(n.in[0]);
     const Value& ids = g.v(n.in[1]);
-    if (data.dt != DT::F32 || g.v(n.out).dt != DT::F32) throw Unsupported("UnsortedSegmentSum over float32 only");
+    if (data.dt != g.v(n.out).dt || (data.dt != DT::F32 && data.dt != DT::I32 && data.dt != DT::F16 && data.dt != DT::BF16))
+      throw Unsupported("UnsortedSegmentSum over float32, float16, bfloat16 or int32 (data and result of one type)");
     if (ids.dt != DT::I32 && ids.dt != DT::I64) throw Unsupported("segment ids must be int32 or int64");
     Step st;
     st.kind = StepK::SegmentSum;
-    st.kernel_name = "segment_sum_f32";
+    st.kernel_name = "segment_sum";
+    st.ix_esize = (int)data.dt;  // the element type of data and result
     st.a = buffer(n.in[0]);
     st.b = buffer(n.in[1]);
     st.out = buffer(n.out);

@@ -277,6 +277,43 @@ def test_float_to_int_cast_rounds_to_nearest_even_and_clamps(lib):
         FusedKernel(_cast_desc("int64"))
 
 
+def test_int64_values_run_in_generated_kernels(lib):
+    """64-bit integer arithmetic, compares, selects and casts (index computations of embedding / gather regions): the
+    generated kernel keeps all its integer registers in 64 bits; the interpreting kernel has no such mode, so the same
+    region is refused when the run-time compiler is switched off."""
+    from akg_b200 import UnsupportedError
+    b = _Builder("Fused_I64_Chain_16")
+    i64, i32 = "int64", "int32"
+    x, y, z = b.input("x", [64, 40], i64), b.input("y", [40], i64), b.input("z", [64, 40], i32)
+    t = b.emit("Mul", [b.emit("Add", [x, y], [64, 40], i64), b.const(3, i64)], [64, 40], i64)
+    zc = b.emit("Cast", [z], [64, 40], i64, [_attr("dst_type", "str", i64)])
+    m = b.emit("Maximum", [t, zc], [64, 40], i64)
+    gt = b.emit("Greater", [t, zc], [64, 40], "bool")
+    sel = b.emit("Select", [gt, b.emit("Sub", [m, zc], [64, 40], i64), b.emit("Neg", [m], [64, 40], i64)], [64, 40], i64)
+    b.output(sel)
+    b.output(b.emit("Cast", [m], [64, 40], i32, [_attr("dst_type", "str", i32)]))
+    b.output(gt)
+    b.output(b.emit("Cast", [sel], [64, 40], "float32", [_attr("dst_type", "str", "float32")]))
+    d = b.build()
+    rng = np.random.default_rng(16)
+    ins = [rng.integers(-2**40, 2**40, (64, 40)).astype(np.int64), rng.integers(-2**33, 2**33, 40).astype(np.int64),
+           rng.integers(-2**31, 2**31 - 1, (64, 40)).astype(np.int32)]
+    if FLAGS[0] != 0:
+        with pytest.raises(UnsupportedError):
+            run(d, ins)
+        return
+    k = check(d, ins, exact=True)
+    assert k.launch_count == 1
+    # ragged extent (element-wise accesses) and a strided operand (Tile)
+    b = _Builder("Fused_I64_Tile_17")
+    p_ = b.input("p", [3, 7], i64)
+    tl = b.emit("Tile", [p_], [6, 21], i64, [_attr("multiples", "listInt", [2, 3])])
+    q_ = b.input("q", [6, 21], i64)
+    b.output(b.emit("Minimum", [b.emit("Abs", [tl], [6, 21], i64), q_], [6, 21], i64))
+    d = b.build()
+    check(d, [rng.integers(-2**50, 2**50, (3, 7)).astype(np.int64), rng.integers(0, 2**50, (6, 21)).astype(np.int64)], exact=True)
+
+
 def _cast_desc(dst):
     b = _Builder(f"Fused_CastTo_{dst}_14")
     x = b.input("x", [4096], "float32")
@@ -515,6 +552,26 @@ def test_gather_and_unsorted_segment_sum(lib):
     absum = np.zeros((37, 48))
     np.add.at(absum, ins[1], np.abs(ins[0]).astype(np.float64))
     assert np.all(np.abs(got[0] - want) <= 1e-5 * absum + 1e-30)  # atomics: order-dependent last bits
+    # the other element types: int32 exact; float16 / bfloat16 accumulate in their own type (as the reference's loop
+    # nest does), so the bound is one rounding per addition of a segment (about 110 rows each here)
+    for dt, npdt, tol in (("int32", np.int32, 0.0), ("float16", np.float16, 2.0 ** -10), ("bfloat16", BF16, 2.0 ** -7)):
+        b = _Builder(f"Fused_UnsortedSegmentSum_{dt}_62")
+        data = b.input("data", [4000, 48], dt)
+        ids = b.input("ids", [4000], "int64")
+        b.output(b.emit("UnsortedSegmentSum", [data, ids], [37, 48], dt, [_attr("num_segments", "int", 37)]))
+        d = b.build()
+        vals = rng.integers(-50, 50, (4000, 48)) if dt == "int32" else rng.standard_normal((4000, 48))
+        ins = [vals.astype(np.float32).astype(npdt) if dt != "int32" else vals.astype(np.int32),
+               rng.integers(0, 37, 4000).astype(np.int64)]
+        got, _ = run(d, ins)
+        want = O.evaluate(d, ins)[0]
+        if dt == "int32":
+            assert bits_equal(got[0], want)
+        else:
+            absum = np.zeros((37, 48))
+            np.add.at(absum, ins[1], np.abs(ins[0].astype(np.float64)))
+            counts = np.bincount(ins[1], minlength=37)[:, None]
+            assert np.all(np.abs(got[0].astype(np.float64) - want.astype(np.float64)) <= tol * counts * absum / 8 + tol * absum)
 
 
 def test_pad_split_argmax(lib):
