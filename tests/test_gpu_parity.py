@@ -246,7 +246,7 @@ def test_matmul_epilogue(lib, m, k, n, tb, bias, relu):
     ("layernorm", descs.layernorm(16384, 1024), KINDS["layernorm"]),
 ])
 def test_chunked_host_entry_point_matches_device_launch(lib, name, desc, kinds):
-    """Above 64 MB akgb_run_host cuts axis 0 into chunks and overlaps copies with kernels; the bytes it returns
+    """Above 64 MB akgb_run_host cuts axis 0 into (at most 16) chunks and overlaps copies with kernels; the bytes it returns
     must be those of one launch over the whole tensors."""
     import torch
     ins = make_inputs(desc, 21, kinds)
