@@ -1442,7 +1442,7 @@ bool reduction_cut_plan(const Graph& g0, int sm_count, bool by_stage, Plan* out)
     const int pa = ranges[k].first, pb = ranges[k].second;
     const int start = (int)order.size();
     std::map<int, int> again;  // value of an earlier piece -> its copy in this piece
-    int budget = 16;
+    int steps_left = 16;
     std::function<int(int)> here = [&](int vid) -> int {
       const Value& v = g.v(vid);
       if (v.is_const || v.producer < 0 || v.producer >= pa || v.output_index >= 0 || v.numel() < large) return vid;
@@ -1450,7 +1450,7 @@ bool reduction_cut_plan(const Graph& g0, int sm_count, bool by_stage, Plan* out)
       if (!opk_is_elementwise(pn.kind)) return vid;
       auto it = again.find(vid);
       if (it != again.end()) return it->second;
-      if (--budget < 0) return vid;
+      if (--steps_left < 0) return vid;
       Node c = pn;
       for (int& u : c.in) u = here(u);
       Value nv = v;
