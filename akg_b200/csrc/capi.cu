@@ -1031,6 +1031,11 @@ akgb_status akgb_check_device_error(akgb_kernel* k, uint32_t* word) {
 
 akgb_status akgb_prepare(akgb_kernel* k) {
   if (!k) return fail(AKGB_INVALID_ARG, "null argument");
+  for (auto& st : k->stages) {  // a region that runs as stages: every stage's tables, counters and generated kernels
+    const akgb_status ss = akgb_prepare(st.k);
+    if (ss != AKGB_OK) return ss;
+  }
+  if (!k->stages.empty()) return AKGB_OK;
   const cudaError_t e = cudaSetDevice(k->device);
   if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
   akgb_status st = ensure_device_state(k, k->plan.needs_gelu_lut);
