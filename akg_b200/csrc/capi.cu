@@ -1144,6 +1144,12 @@ akgb_status akgb_kernel_meta(const akgb_kernel* k, char* buf, size_t cap, size_t
     << "\", \"bytes\": " << k->plan.bytes << ", \"flops\": " << k->plan.flops << ", \"smem\": " << d.smem
     << ", \"workspace\": " << k->plan.workspace_bytes << ", \"launches\": " << launches_of(k) << ", \"steps\": [";
   for (size_t i = 0; i < ap.steps.size(); ++i) o << (i ? ", " : "") << "\"" << ap.steps[i].kernel_name << "\"";  // in launch order
+  bool first = ap.steps.empty();
+  for (auto& stg : k->stages)  // a staged region: the steps of every stage, "|" where an exchange separates two stages
+    for (size_t i = 0; i < active_plan(stg.k).steps.size(); ++i) {
+      o << (first ? "" : ", ") << "\"" << (i == 0 && &stg != &k->stages.front() ? "| " : "") << active_plan(stg.k).steps[i].kernel_name << "\"";
+      first = false;
+    }
   o << "]}";
   std::string s = o.str();
   if (needed) *needed = s.size() + 1;
