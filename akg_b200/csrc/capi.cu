@@ -690,7 +690,6 @@ bool build_stages(akgb_kernel* k, const char* text, size_t len) {
       sk->graph = std::move(sg.g);
       plan_and_describe(sk);
       stage_ws = std::max(stage_ws, sk->plan.workspace_bytes);
-      summary.bytes += sk->plan.bytes;
       summary.flops += sk->plan.flops;
       summary.needs_gelu_lut = summary.needs_gelu_lut || sk->plan.needs_gelu_lut;
       auto& args = stages.back().args;
@@ -743,6 +742,7 @@ bool build_stages(akgb_kernel* k, const char* text, size_t len) {
       descs[i] = d;
     }
     summary.workspace_bytes = ws + stage_ws;
+    for (auto& d : descs) summary.bytes += d.nbytes;  // algorithmic: every argument of the region once
     k->graph = std::move(whole);
     k->plan = std::move(summary);
     k->descs = std::move(descs);
