@@ -181,6 +181,28 @@ def test_transpose_bit_exact(lib, shape, perm, dt):
     assert bits_equal(got[0], np.ascontiguousarray(np.transpose(x, perm)))
 
 
+# ------------------------------------------------------------------ empty tensors
+def test_empty_leading_extent(lib):
+    """A region over zero rows is legal: nothing is read or written, reductions over the empty axis return the
+    reference's init values (sum 0, max -FLT_MAX: MindSporeToLinalg.cpp:791-843), launches with nothing to do are
+    skipped rather than rejected by the driver."""
+    import torch
+    flt_max = np.finfo(np.float32).max
+    for d in (descs.gelu_chain([0, 8, 64]), descs.layernorm(0, 128), descs.masked_softmax(0, 16, 64),
+              descs.transpose([0, 4, 8, 16], [0, 2, 1, 3]), descs.transpose([0, 6], [1, 0], "float32"),
+              descs.rmsnorm(0, 256)):
+        ins = make_inputs(d, 3, {"mask": "causal"})
+        got, k = guarded_launch(d, ins)
+        assert all(g.size == 0 for g in got) and k.check_device_error() == 0
+    for d, want in ((descs.reduce_sum_axis0(0, 48), [np.zeros(48, np.float32)]),
+                    (descs.reduce_max_all(0, 48), [np.full(1, -flt_max, np.float32)]),
+                    (descs.reduce_sum_and_max(0, 48), [np.zeros(48, np.float32), np.full(1, -flt_max, np.float32)])):
+        got, k = guarded_launch(d, make_inputs(d, 3))
+        for g, w in zip(got, want):
+            assert bits_equal(g.reshape(w.shape), w)
+    torch.cuda.synchronize()
+
+
 # ------------------------------------------------------------------ launch path + metadata
 def test_device_launch_matches_host_run_and_reports_dims(lib):
     import torch
