@@ -53,10 +53,15 @@ def measured_peaks():
     if p.exists():
         try:
             d = json.loads(p.read_text())
+            global tf_sustained
+            tf_sustained = float(d.get("bf16_tflops_sustained", 0.0))
             return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 0.0)), "measured"
         except Exception:
             pass
     return FALLBACK_HBM_GBS, 1590.0, "fallback"
+
+
+tf_sustained = 1400.0  # the fallback's sustained figure; replaced by MEASURED_PEAKS.json's when present
 
 
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, scaled to the full
@@ -175,7 +180,7 @@ def buffer_sets_for(kernel, kinds, device, rank, seed0=100):
     return [device_inputs(kernel, kinds, seed0 + s, device, rank) + device_outputs(kernel, device) for s in range(nsets)]
 
 
-def time_launches(kernel, buffer_sets, steps, warmup, barrier=None, use_graph=True):
+def time_launches(kernel, buffer_sets, steps, warmup, barrier=None, use_graph=True, sustain_s=0.0, sustained=None):
     """Average device time of one step in ms: CUDA events on the launch stream, sync on both sides.
 
     The `steps` launches are captured once into a CUDA graph and the graph is what gets timed, so that short
@@ -212,6 +217,18 @@ def time_launches(kernel, buffer_sets, steps, warmup, barrier=None, use_graph=Tr
                 kernel.launch(buffer_sets[i % len(buffer_sets)], stream)
         t1.record(stream)
         torch.cuda.synchronize()
+        if sustain_s > 0 and graph is not None and sustained is not None:
+            # the same graph replayed back to back for `sustain_s` seconds: what the part sustains under its power cap
+            one = t0.elapsed_time(t1)
+            reps = max(2, int(sustain_s * 1e3 / max(one, 1e-3)))
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            s1.record(stream)
+            torch.cuda.synchronize()
+            sustained["ms"] = s0.elapsed_time(s1) / (reps * steps)
+            sustained["seconds"] = s0.elapsed_time(s1) / 1e3
         if barrier:
             barrier()
     return t0.elapsed_time(t1) / steps
@@ -413,7 +430,13 @@ def run_classes(rank, world, device, steps, warmup, hbm_peak, tf_peak, barrier, 
             launch = staticmethod(step_launch)
         # NCCL calls are not captured into the graph; the library's own exchange runs inside ordinary kernels and is
         graphable = exchange in ("none", "peer-kernel", "in-reduction")
-        ms = time_launches(_K, sets, steps, warmup, barrier, use_graph=graphable)
+        sustained = {}
+        if k.flops:  # tensor-core rows: also a second-long loop with the SM clock sampled, next to the short burst
+            with ClockSampler(device.index) as clk_mm:
+                ms = time_launches(_K, sets, steps, warmup, barrier, use_graph=graphable, sustain_s=1.0, sustained=sustained)
+            sustained["clocks"] = clk_mm.summary()
+        else:
+            ms = time_launches(_K, sets, steps, warmup, barrier, use_graph=graphable)
         word = device_error_word(k)  # bounded device-side waits that gave up (0 = none); bit 8: a peer-memory exchange
         if exchange in ("peer-kernel", "in-reduction"):
             # a wait that ran out on any rank: NCCL carries the exchange from here on (on every rank)
@@ -440,6 +463,15 @@ def run_classes(rank, world, device, steps, warmup, hbm_peak, tf_peak, barrier, 
         if k.flops:
             tf = flops_job / (ms_max * 1e-3) / 1e12
             row.update({"tflops": round(tf, 2), "frac_of_peak": round(tf / world / tf_peak, 4), "bound": "tensor"})
+            if "ms" in sustained:
+                ms_s = allreduce_scalar(sustained["ms"], world)
+                tf_s = flops_job / (ms_s * 1e-3) / 1e12
+                mhz = sustained["clocks"].get("sm_mhz")
+                row["sustained"] = {"tflops": round(tf_s, 2), "seconds": round(sustained["seconds"], 2), "sm_mhz": mhz,
+                                    "reasons": sustained["clocks"].get("reasons"),
+                                    "frac_of_sustained_peak": round(tf_s / world / tf_sustained, 4) if tf_sustained else None,
+                                    # dense bf16 nominal 2 250 TFLOP/s at 1 965 MHz, scaled to the clock seen under load
+                                    "frac_of_nominal_at_clock": round(tf_s / world / (2250.0 * mhz / 1965.0), 4) if mhz else None}
         else:
             gbs = bytes_job / (ms_max * 1e-3) / 1e9
             row.update({"gbs": round(gbs, 1), "frac_of_peak": round(gbs / world / hbm_peak, 4), "bound": "hbm",
