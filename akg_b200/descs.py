@@ -322,6 +322,45 @@ def batch_norm_backward(shape: Sequence[int], seed: int = 0) -> dict:
     return b.build()
 
 
+def normalise_over_axis0(rows: int, cols: int, eps: float = 1e-5) -> dict:
+    """(x - mean) * rsqrt(var + eps) with the statistics over axis 0 (per column): the reductions fold the leading axis
+    and feed the ops behind them."""
+    f = "float32"
+    b = _Builder(f"Fused_NormaliseAxis0_{rows}x{cols}_4")
+    x = b.input("x", [rows, cols], f)
+    stat = [1, cols]
+    mean = b.emit("Mul", [b.emit("ReduceSum", [x], stat, f, _reduce_attr([0], True)), b.const(1.0 / rows, f)], stat, f)
+    d = b.emit("Sub", [x, mean], [rows, cols], f)
+    var = b.emit("Mul", [b.emit("ReduceSum", [b.emit("Mul", [d, d], [rows, cols], f)], stat, f, _reduce_attr([0], True)),
+                         b.const(1.0 / rows, f)], stat, f)
+    r = b.emit("Rsqrt", [b.emit("Add", [var, b.const(eps, f)], stat, f)], stat, f)
+    b.output(b.emit("Mul", [d, r], [rows, cols], f))
+    return b.build()
+
+
+def softmax_over_axis0(rows: int, cols: int) -> dict:
+    """exp(x - max) / sum exp(x - max) with the maximum and the sum over axis 0 (per column)."""
+    f = "float32"
+    b = _Builder(f"Fused_SoftmaxAxis0_{rows}x{cols}_5")
+    x = b.input("x", [rows, cols], f)
+    stat = [1, cols]
+    m = b.emit("ReduceMax", [x], stat, f, _reduce_attr([0], True))
+    e = b.emit("Exp", [b.emit("Sub", [x, m], [rows, cols], f)], [rows, cols], f)
+    b.output(b.emit("RealDiv", [e, b.emit("ReduceSum", [e], stat, f, _reduce_attr([0], True))], [rows, cols], f))
+    return b.build()
+
+
+def scale_by_global_max(rows: int, cols: int) -> dict:
+    """x / max|x| over the whole tensor, and the maximum itself."""
+    f = "float32"
+    b = _Builder(f"Fused_ScaleByGlobalMax_{rows}x{cols}_6")
+    x = b.input("x", [rows, cols], f)
+    m = b.emit("ReduceMax", [b.emit("Abs", [x], [rows, cols], f)], [1], f, _reduce_attr([0, 1], False))
+    b.output(b.emit("RealDiv", [x, m], [rows, cols], f))
+    b.output(m)
+    return b.build()
+
+
 def layer_norm_backward(rows: int, cols: int, eps: float = 1e-5, grads_dtype: str = "float32") -> dict:
     """Statistics recomputed from x, then dx (row-wise) with dgamma = sum over rows of dy * xhat and dbeta = sum of dy
     (cast to `grads_dtype`, the parameters' type, when that is not float32)."""

@@ -129,7 +129,10 @@ def main():
     sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "tests"))
     from oracle import akg_oracle as O
     shape = [4 * world, 32, 14, 14]
-    for build in (descs.batch_norm_training, descs.batch_norm_backward):
+    rows0 = 4 * world
+    for build in (descs.batch_norm_training, descs.batch_norm_backward,
+                  lambda _: descs.normalise_over_axis0(rows0, 1000), lambda _: descs.softmax_over_axis0(rows0, 520),
+                  lambda _: descs.scale_by_global_max(rows0, 3000)):
         d = build(shape)
         rng = np.random.default_rng(11)
         full = [rng.standard_normal(t[0]["shape"], dtype=np.float32) for t in d["input_desc"]]

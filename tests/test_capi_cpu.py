@@ -388,6 +388,15 @@ def test_reductions_over_the_split_axis_that_feed_later_ops_run_as_stages(lib):
     assert kb.op_class == "sharded_stages" and kb.inputs[0].shape == (2, 16, 4, 4)
     # the same descriptions unsplit are ordinary kernels
     assert FusedKernel(descs.batch_norm_training([8, 16, 4, 4])).op_class != "sharded_stages"
+    # statistics per column over the split rows; a softmax over the split axis (max, then sum: two exchanges); a scale
+    # taken from the whole tensor, which is also a result (it lives in the caller's output, not in the workspace)
+    for d, stages in ((descs.normalise_over_axis0(4096, 512), 3), (descs.softmax_over_axis0(4096, 512), 3),
+                      (descs.scale_by_global_max(4096, 512), 2)):
+        ks = FusedKernel(d, shard_rank=1, shard_world=4)
+        assert ks.op_class == "sharded_stages" and ks.inputs[0].shape == (1024, 512)
+        assert sum(1 for s_ in ks.meta()["steps"] if s_.startswith("| ")) == stages - 1
+        assert ks.outputs[0].shard_kind == _capi.SHARD_SPLIT_AXIS0
+    assert FusedKernel(descs.scale_by_global_max(4096, 512), shard_rank=0, shard_world=4).outputs[1].shard_kind == _capi.SHARD_REPLICATED
 
 
 def test_symbolic_shapes_bind_consistently(lib):
