@@ -23,6 +23,7 @@ from .driver import FusedKernel
 
 CASES = {
     "gelu": (lambda s: descs.gelu_chain(s), {"bias": "normal_small"}),
+    "gelu_f32math": (lambda s: descs.gelu_chain(s, f32_math=True), {"bias": "normal_small"}),
     "layernorm": (lambda s: descs.layernorm(s[0], s[1]), {"gamma": "gamma", "beta": "beta"}),
     "softmax": (lambda s: descs.masked_softmax(s[0], s[1], s[2]), {"mask": "causal"}),
     "colsum": (lambda s: descs.reduce_sum_axis0(s[0], s[1]), {}),

@@ -16,13 +16,14 @@
 // Maximum and Cast follow in that order, one rounding each.
 //
 // Two variants share the epilogue: a single-CTA kernel (128x256 tiles, used when M <= 128) and a CTA-pair
-// kernel (tcgen05 cta_group::2, 256x256 tiles over two SMs, 6-stage ring), which is the default.
+// kernel (tcgen05 cta_group::2, 256x256 tiles over two SMs, 5-stage ring, 16-bit results stored through shared memory by tensor-map stores), which is the default.
 //
 // Every wait on an mbarrier is bounded: when a limit is hit the kernel writes
 // an error word, drains its copies and MMAs, frees its TMEM and returns.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstring>
 #include <mutex>
 
 #include "async.cuh"
@@ -120,6 +121,52 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int*
   *n_tile = in_group / rows;
 }
 
+// Bias, then ReLU, on the 32 accumulator columns starting at col0 (this lane's row); columns at or beyond N keep
+// whatever the accumulator held and are never stored.
+__device__ __forceinline__ void epilogue_values(const MatmulDev& p, const uint32_t* r, int col0, float* v) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  if (p.has_bias) {
+    if (col0 + 32 <= p.N) {
+      if (p.bias_dt != kF32) {
+        const uint4* bp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float b8[8];
+          unpack8(__ldg(bp + q), p.bias_dt, b8);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[q * 8 + j] = __fadd_rn(v[q * 8 + j], b8[j]);
+        }
+      } else {
+        const float4* bp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + col0);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float4 b = __ldg(bp + q);
+          v[q * 4 + 0] = __fadd_rn(v[q * 4 + 0], b.x);
+          v[q * 4 + 1] = __fadd_rn(v[q * 4 + 1], b.y);
+          v[q * 4 + 2] = __fadd_rn(v[q * 4 + 2], b.z);
+          v[q * 4 + 3] = __fadd_rn(v[q * 4 + 3], b.w);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (col0 + j < p.N) {
+          const float b = p.bias_dt == kBF16
+                              ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(p.bias)[col0 + j])
+                              : p.bias_dt == kF16 ? __half2float(reinterpret_cast<const __half*>(p.bias)[col0 + j])
+                                                  : reinterpret_cast<const float*>(p.bias)[col0 + j];
+          v[j] = __fadd_rn(v[j], b);
+        }
+      }
+    }
+  }
+  if (p.relu) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = v[j] != v[j] ? v[j] : fmaxf(v[j], 0.f);  // NaN stays NaN
+  }
+}
+
 // Reads one 128x256 accumulator (this warp's 32 lanes) in chunks of 32 columns, applies bias / ReLU / cast in
 // that order and stores the row segment.
 __device__ __forceinline__ void epilogue_tile(const MatmulDev& p, uint32_t taddr, int row, int n0, size_t out_off) {
@@ -131,47 +178,7 @@ __device__ __forceinline__ void epilogue_tile(const MatmulDev& p, uint32_t taddr
     const int col0 = n0 + c * 32;
     if (col0 >= p.N) continue;
     float v[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-    if (p.has_bias) {
-      if (col0 + 32 <= p.N) {
-        if (p.bias_dt != kF32) {
-          const uint4* bp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + col0);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            float b8[8];
-            unpack8(__ldg(bp + q), p.bias_dt, b8);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[q * 8 + j] = __fadd_rn(v[q * 8 + j], b8[j]);
-          }
-        } else {
-          const float4* bp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + col0);
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const float4 b = __ldg(bp + q);
-            v[q * 4 + 0] = __fadd_rn(v[q * 4 + 0], b.x);
-            v[q * 4 + 1] = __fadd_rn(v[q * 4 + 1], b.y);
-            v[q * 4 + 2] = __fadd_rn(v[q * 4 + 2], b.z);
-            v[q * 4 + 3] = __fadd_rn(v[q * 4 + 3], b.w);
-          }
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          if (col0 + j < p.N) {
-            const float b = p.bias_dt == kBF16
-                                ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(p.bias)[col0 + j])
-                                : p.bias_dt == kF16 ? __half2float(reinterpret_cast<const __half*>(p.bias)[col0 + j])
-                                                    : reinterpret_cast<const float*>(p.bias)[col0 + j];
-            v[j] = __fadd_rn(v[j], b);
-          }
-        }
-      }
-    }
-    if (p.relu) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = v[j] != v[j] ? v[j] : fmaxf(v[j], 0.f);  // NaN stays NaN
-    }
+    epilogue_values(p, r, col0, v);
     if (row < p.M) {
       if (p.out_dt != kF32) {
         uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + out_off + (size_t)row * p.N + col0;
@@ -199,6 +206,55 @@ __device__ __forceinline__ void epilogue_tile(const MatmulDev& p, uint32_t taddr
     }
   }
 }
+
+// The same for a 16-bit result, through shared memory: the warp's 32 rows x 256 columns are laid out as four boxes of
+// 32 rows x 64 columns (128-byte rows in the 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r & 7), so
+// the 32 lanes' 16-byte stores of one instruction touch every bank once), which four tensor-map stores then write as
+// whole 128-byte lines; rows at or beyond M and columns at or beyond N are clipped by the tensor map.
+__device__ __forceinline__ void epilogue_tile_staged(const MatmulDev& p, uint32_t taddr, uint32_t stage_smem, int lane,
+                                                     int n0) {
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld32(taddr + c * 32, r);
+    tmem_ld_wait();
+    const int col0 = n0 + c * 32;
+    if (col0 >= p.N) continue;
+    float v[32];
+    epilogue_values(p, r, col0, v);
+    const uint32_t row_smem = stage_smem + (uint32_t)(c >> 1) * 4096u + (uint32_t)lane * 128u;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint4 w = pack8(v + q * 8, p.out_dt);
+      const uint32_t chunk = (uint32_t)(((c & 1) * 4 + q) ^ (lane & 7));
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_smem + chunk * 16u), "r"(w.x), "r"(w.y), "r"(w.z),
+                   "r"(w.w)
+                   : "memory");
+    }
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the stores above become visible to the bulk copies
+}
+// `policy`: the result is written once and not read again by this kernel, so its lines are the first to leave L2 and
+// the operands, which every CTA pair of a wave re-reads, stay
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3, %4}], [%1], %5;" ::"l"(map),
+               "r"(src), "r"(x), "r"(y), "r"(z), "l"(policy)
+               : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the bulk stores issued by this thread have finished reading shared memory
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 __global__ void __launch_bounds__(THREADS, 1)
 matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -384,10 +440,11 @@ matmul_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
 // shared memory, and each CTA's TMEM receives its 128 rows of the accumulator.  Per CTA a stage is 32 KiB
 // instead of 48, so the ring is 6 deep, and B is fetched from L2 once per pair.  Every CTA issues its own plain
 // tensor-map copies; only the MMA-completion signal (tcgen05.commit) is delivered to both CTAs' barriers.
-constexpr int STAGES2 = 6;
+constexpr int STAGES2 = 5;
 constexpr int B2_BYTES = (BN / 2) * BK * 2;             // this CTA's half of B: 16 KiB
 constexpr int STAGE2_BYTES = A_BYTES + B2_BYTES;        // 32 KiB
-constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + 512;
+constexpr int OUT_STAGE_BYTES = 32 * BN * 2;                  // one epilogue warp's 32 rows x 256 columns of a 16-bit result
+constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 4 * OUT_STAGE_BYTES + 1024 + 512;
 constexpr uint32_t kPeerMask = 0xFEFFFFFFu;             // shared::cluster address of the same offset in the pair's leader
 
 struct Bars2 {
@@ -410,10 +467,10 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y,
-                                                 int z) {
+                                                 int z, uint64_t policy) {
   asm volatile(
-      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"(map), "r"(leader_bar), "r"(x), "r"(y), "r"(z)
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(dst), "l"(map), "r"(leader_bar), "r"(x), "r"(y), "r"(z), "l"(policy)
       : "memory");
 }
 __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
@@ -445,12 +502,12 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t local_addr, uint32_t
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 matmul_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                                const MatmulDev p) {
+                                const __grid_constant__ CUtensorMap tmC, const MatmulDev p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw);
-  Bars2* bars = reinterpret_cast<Bars2*>(smem + STAGES2 * STAGE2_BYTES);
+  Bars2* bars = reinterpret_cast<Bars2*>(smem + STAGES2 * STAGE2_BYTES + 4 * OUT_STAGE_BYTES);
   volatile uint32_t* abort_flag = &bars->abort;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
@@ -490,6 +547,7 @@ matmul_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const _
   if (warp == 0) {
     if (lane == 0) {
       // ------------------------------------------------------------ TMA producer (both CTAs)
+      const uint64_t load_policy = l2_policy_evict_last();
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -506,13 +564,13 @@ matmul_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const _
           const uint32_t full_leader = smem_u32(&bars->full[stage]) & kPeerMask;
           const uint32_t sa = base + stage * STAGE2_BYTES, sb = sa + A_BYTES;
           if (leader) mbar_expect_tx(smem_u32(&bars->full[stage]), 2 * STAGE2_BYTES);
-          tma_load_3d_pair(sa, &tmA, full_leader, kb * BK, m0, bt);
+          tma_load_3d_pair(sa, &tmA, full_leader, kb * BK, m0, bt, load_policy);
           if (p.transpose_b) {
-            tma_load_3d_pair(sb, &tmB, full_leader, kb * BK, n0, bz);
+            tma_load_3d_pair(sb, &tmB, full_leader, kb * BK, n0, bz, load_policy);
           } else {
 #pragma unroll
             for (int j = 0; j < (BN / 2) / B_BOX_N; ++j)
-              tma_load_3d_pair(sb + j * B_BOX_BYTES, &tmB, full_leader, n0 + j * B_BOX_N, kb * BK, bz);
+              tma_load_3d_pair(sb + j * B_BOX_BYTES, &tmB, full_leader, n0 + j * B_BOX_N, kb * BK, bz, load_policy);
           }
           if (++stage == STAGES2) {
             stage = 0;
@@ -576,6 +634,9 @@ matmul_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const _
   } else {
     // -------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
     const int quarter = warp & 3;
+    const bool staged = p.out_dt != kF32;  // 16-bit results leave through shared memory and tensor-map stores
+    const uint64_t store_policy = l2_policy_evict_first();
+    const uint32_t out_smem = base + STAGES2 * STAGE2_BYTES + (uint32_t)quarter * OUT_STAGE_BYTES;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -591,12 +652,30 @@ matmul_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const _
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * BN;
-      epilogue_tile(p, taddr, row, n0, (size_t)bt * (size_t)p.out_stride);
+      if (staged) {
+        if (lane == 0) bulk_wait_read();  // the previous tile's stores have read this warp's staging area
+        __syncwarp();
+        epilogue_tile_staged(p, taddr, out_smem, lane, n0);
+      } else {
+        epilogue_tile(p, taddr, row, n0, (size_t)bt * (size_t)p.out_stride);
+      }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_remote(smem_u32(&bars->tmem_empty[acc]), 0);
+      if (lane == 0) {
+        mbar_arrive_remote(smem_u32(&bars->tmem_empty[acc]), 0);  // the accumulator is read: the next tile may use it
+        if (staged) {
+          const int row0 = row - lane;
+          if (row0 < p.M) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              if (n0 + j * 64 < p.N) tma_store_3d(&tmC, out_smem + (uint32_t)j * 4096u, n0 + j * 64, row0, bt, store_policy);
+          }
+          bulk_commit();
+        }
+      }
       if ((acc ^= 1) == 0) acc_phase ^= 1u;
     }
+    if (staged && lane == 0) bulk_wait_all();
     if (!ok && lane == 0) {
       *abort_flag = 1;
       atomicOr(p.err, 4u);
@@ -717,7 +796,13 @@ cudaError_t matmul_bf16(const MatmulParams& p, const void* A, const void* B, con
       dims->block[0] = THREADS;
       dims->smem = SMEM2_BYTES;
     }
-    matmul_bf16_tcgen05_pair_kernel<<<grid2, THREADS, SMEM2_BYTES, s>>>(tmA, tmB2, d);
+    // 16-bit results: the output as boxes of 64 columns x 32 rows (one epilogue warp's share of a 128-byte-swizzled box)
+    CUtensorMap tmC;
+    std::memset(&tmC, 0, sizeof(tmC));
+    if (p.out_dt != kF32 &&
+        !encode_3d(&tmC, out, (uint64_t)p.N, (uint64_t)p.M, (uint64_t)batch, 64, 32, p.out_dt == kF16))
+      return cudaErrorInvalidValue;
+    matmul_bf16_tcgen05_pair_kernel<<<grid2, THREADS, SMEM2_BYTES, s>>>(tmA, tmB2, tmC, d);
     return cudaGetLastError();
   }
   const int64_t tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * batch;

@@ -530,6 +530,26 @@ def copy_ceilings(device, steps, warmup, hbm_peak):
     return out
 
 
+def matmul_ceiling(device, steps, warmup, tf_peak):
+    """cuBLAS (torch.matmul) on the matmul class's own operands, 8192x4096 by 4096x8192 in bfloat16 without bias or
+    ReLU, timed like the class row.  The measured tensor peak was taken on 8192^3, whose tiles run twice as many MMAs per
+    result tile; this is the library's figure at the benchmark's shape.  A measuring stick only: no class row uses it."""
+    import torch
+    g = torch.Generator(device=device).manual_seed(5)
+    a = (torch.randn(8192, 4096, device=device, generator=g) * 0.02).bfloat16()
+    bs = [(torch.randn(4096, 8192, device=device, generator=g) * 0.02).bfloat16() for _ in range(2)]
+    outs = [torch.empty(8192, 8192, dtype=torch.bfloat16, device=device) for _ in range(2)]
+
+    class TorchMatmul:
+        @staticmethod
+        def launch(b, stream=None):
+            torch.matmul(b[0], b[1], out=b[2])
+
+    ms = time_launches(TorchMatmul, [[a, b, o] for b, o in zip(bs, outs)], steps, warmup)
+    tf = 2.0 * 8192 * 4096 * 8192 / (ms * 1e-3) / 1e12
+    return {"ms": round(ms, 5), "tflops": round(tf, 1), "frac_of_peak": round(tf / tf_peak, 4)}
+
+
 def host_copy_only(bufs, kernel, device, steps, barrier, world):
     """Bare pinned copies of one step's bytes, no kernel: all inputs host->device on one stream while all outputs go
     device->host on another, on every rank at once.  Seconds per step (max over ranks)."""
@@ -677,6 +697,11 @@ def gpu_arm(args):
         line["classes"] = run_classes(rank, world, device, csteps, cwarm, hbm_peak, tf_peak, barrier, comm, scaling, only)
         if world == 1:
             line["ceilings"] = copy_ceilings(device, csteps, cwarm, hbm_peak)
+            if only is None or "matmul_bias_relu_bf16_8192x4096x8192" in only:
+                try:
+                    line["ceilings"]["cublas_bf16_8192x4096x8192"] = matmul_ceiling(device, csteps, cwarm, tf_peak)
+                except Exception as e:
+                    line["ceilings"]["cublas_bf16_8192x4096x8192"] = {"error": str(e)[:100]}
     if world > 1 and not args.no_classes:
         # the other scaling mode, for the headline and for the rows that have an exchange step
         other = "weak" if scaling == "strong" else "strong"
