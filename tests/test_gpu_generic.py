@@ -112,6 +112,39 @@ def test_mul_realdiv_exp_f16(lib):
     check(d, ins, rtol=2e-3, atol=1e-6)
 
 
+@pytest.mark.parametrize("dt", ["float16", "bfloat16"])
+def test_every_16_bit_pattern_through_add_mul_cast_with_shared_operands(lib, dt):
+    """x runs over all 65 536 bit patterns of the type (NaNs, infinities, subnormals, both zeros), y is shared along
+    the rows and z along the columns: the generated kernel keeps 16-bit granules packed until their turn and rounds
+    results two per instruction, and every result bit must still be the oracle's (NaNs compared as NaNs)."""
+    b = _Builder("Fused_Add_Mul_Cast_patterns_" + dt + "_3")
+    npdt = BF16 if dt == "bfloat16" else np.dtype(dt)
+    x = b.input("x", [256, 256], dt)
+    y = b.input("y", [256], dt)
+    z = b.input("z", [256, 1], dt)
+    t = b.emit("Add", [x, y], [256, 256], dt)
+    m = b.emit("Mul", [t, z], [256, 256], dt)
+    w = b.emit("Cast", [m], [256, 256], "float32", [_attr("dst_type", "str", "float32")])
+    n = b.emit("Cast", [b.emit("Mul", [w, b.const(0.333251953125, "float32")], [256, 256], "float32")], [256, 256], dt,
+               [_attr("dst_type", "str", dt)])
+    b.output(t)
+    b.output(m)
+    b.output(n)
+    d = b.build()
+    rng = np.random.default_rng(11)
+    xs = np.arange(65536, dtype=np.uint16).reshape(256, 256).view(npdt)
+    ys = rng.standard_normal(256).astype(np.float32).astype(npdt)
+    zs = (rng.standard_normal((256, 1)) * 3).astype(np.float32).astype(npdt)
+    got, k = run(d, [xs, ys, zs])
+    want = O.evaluate(d, [xs, ys, zs])
+    for g, w_ in zip(got, want):
+        g32, w32 = g.astype(np.float32), w_.astype(np.float32)
+        nan = np.isnan(w32)
+        assert np.array_equal(np.isnan(g32), nan)
+        assert np.array_equal(g.view(np.uint16)[~nan], w_.view(np.uint16)[~nan])
+    assert k.meta()["template"] == "ew_generic"
+
+
 def test_compare_select_maximum_bool_outputs(lib):
     b = _Builder("Fused_LessEqual_Select_5")
     f = "float32"
