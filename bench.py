@@ -471,7 +471,9 @@ def run_classes(rank, world, device, steps, warmup, hbm_peak, tf_peak, barrier, 
                                     "reasons": sustained["clocks"].get("reasons"),
                                     "frac_of_sustained_peak": round(tf_s / world / tf_sustained, 4) if tf_sustained else None,
                                     # dense bf16 nominal 2 250 TFLOP/s at 1 965 MHz, scaled to the clock seen under load
-                                    "frac_of_nominal_at_clock": round(tf_s / world / (2250.0 * mhz / 1965.0), 4) if mhz else None}
+                                    "frac_of_nominal_at_clock": round(tf_s / world / (2250.0 * mhz / 1965.0), 4) if mhz else None,
+                                    # step time x median SM clock: runs at different clocks compare by this
+                                    "sm_mcycles_per_step": round(ms_s * 1e-3 * mhz, 3) if mhz else None}
         else:
             gbs = bytes_job / (ms_max * 1e-3) / 1e9
             row.update({"gbs": round(gbs, 1), "frac_of_peak": round(gbs / world / hbm_peak, 4), "bound": "hbm",
