@@ -219,8 +219,48 @@ __device__ __forceinline__ void st8_i64(void* p, i64 e0, const i64* r) {
     st16((i64*)p + e0 + 2 * q, v); } }
 )SRC";
 
+// Appended for programs that hold a float64 value: ALL their floating-point registers are doubles.  Values of a
+// narrower type are the doubles that type can represent; an op computes in double and rounds once to its own type,
+// which for + - * / sqrt is the correctly rounded result of that type (53 bits >= 2 * 24 + 2).  double -> 16-bit goes
+// through a float32 rounded to odd, so that the second rounding sees what the first one dropped.
+const char* kPreambleF64 = R"SRC(
+__device__ __forceinline__ float odd_f32(double x) { float f = __double2float_rz(x);
+  if (x == x && (double)f != x) f = __uint_as_float(__float_as_uint(f) | 1u); return f; }
+__device__ __forceinline__ double rn_f64(double x) { return x; }
+__device__ __forceinline__ double rn_f32_d(double x) { return (double)__double2float_rn(x); }
+__device__ __forceinline__ double rn_f16_d(double x) { return (double)rn_f16(odd_f32(x)); }
+__device__ __forceinline__ double rn_bf16_d(double x) { return (double)rn_bf16(odd_f32(x)); }
+// (the conversion from a double NaN gives INT_MIN, not the 0 it gives from a float NaN)
+__device__ __forceinline__ int f2i_i32_d(double x) { return x != x ? 0 : __double2int_rn(x); }
+__device__ __forceinline__ int f2i_i16_d(double x) { return max(-32768, min(32767, f2i_i32_d(x))); }
+__device__ __forceinline__ int f2i_i8_d(double x) { return max(-128, min(127, f2i_i32_d(x))); }
+__device__ __forceinline__ double mx_d(double a, double b) { return (a != a || b != b) ? __longlong_as_double(0x7ff8000000000000LL) : fmax(a, b); }
+__device__ __forceinline__ double mn_d(double a, double b) { return (a != a || b != b) ? __longlong_as_double(0x7ff8000000000000LL) : fmin(a, b); }
+#define LD8_D(NAME, BASE) __device__ __forceinline__ void NAME(const void* p, i64 e0, double* r, bool stream) { \
+  float t[8]; BASE(p, e0, t, stream); _Pragma("unroll") for (int i = 0; i < 8; ++i) r[i] = (double)t[i]; }
+LD8_D(ld8_f32_d, ld8_f32)
+LD8_D(ld8_f16_d, ld8_f16)
+LD8_D(ld8_bf16_d, ld8_bf16)
+#define ST8_D(NAME, BASE) __device__ __forceinline__ void NAME(void* p, i64 e0, const double* r) { \
+  float t[8]; _Pragma("unroll") for (int i = 0; i < 8; ++i) t[i] = (float)r[i]; BASE(p, e0, t); }
+ST8_D(st8_f32_d, st8_f32)
+ST8_D(st8_f16_d, st8_f16)
+ST8_D(st8_bf16_d, st8_bf16)
+__device__ __forceinline__ void ld8_f64(const void* p, i64 e0, double* r, bool stream) {
+  _Pragma("unroll") for (int q = 0; q < 4; ++q) {
+    const U4 v = stream ? ld16s((const double*)p + e0 + 2 * q) : ld16c((const double*)p + e0 + 2 * q);
+    r[2*q] = __hiloint2double((int)v.y, (int)v.x); r[2*q+1] = __hiloint2double((int)v.w, (int)v.z); } }
+__device__ __forceinline__ void st8_f64(void* p, i64 e0, const double* r) {
+  _Pragma("unroll") for (int q = 0; q < 4; ++q) { U4 v;
+    v.x = (u32)__double2loint(r[2*q]); v.y = (u32)__double2hiint(r[2*q]); v.z = (u32)__double2loint(r[2*q+1]); v.w = (u32)__double2hiint(r[2*q+1]);
+    st16((double*)p + e0 + 2 * q, v); } }
+__device__ __forceinline__ double ld1_f64(const void* p, i64 i) { return ((const double*)p)[i]; }
+__device__ __forceinline__ void st1_f64(void* p, i64 i, double v) { ((double*)p)[i] = v; }
+)SRC";
+
 const char* dt_tag(int dt) {
   switch ((DT)dt) {
+    case DT::F64: return "f64";
     case DT::F16: return "f16";
     case DT::BF16: return "bf16";
     case DT::F32: return "f32";
@@ -241,8 +281,22 @@ bool ew_has_i64(const EwProgram& P) {
     if ((DT)P.instr[k].dt == DT::I64) return true;
   return false;
 }
-bool is_float_dt(int dt) { return (DT)dt == DT::F16 || (DT)dt == DT::BF16 || (DT)dt == DT::F32; }
+// a program with a float64 operand or result keeps all its floating-point registers as doubles
+bool ew_has_f64(const EwProgram& P) {
+  for (int i = 0; i < P.n_in; ++i)
+    if ((DT)P.in[i].dt == DT::F64) return true;
+  for (int i = 0; i < P.n_out; ++i)
+    if ((DT)P.out[i].dt == DT::F64) return true;
+  for (int k = 0; k < P.n_instr; ++k)
+    if ((DT)P.instr[k].dt == DT::F64) return true;
+  return false;
+}
+bool is_float_dt(int dt) { return (DT)dt == DT::F16 || (DT)dt == DT::BF16 || (DT)dt == DT::F32 || (DT)dt == DT::F64; }
 const char* round_fn(int dt) { return (DT)dt == DT::F16 ? "rn_f16" : (DT)dt == DT::BF16 ? "rn_bf16" : "rn_f32"; }
+// the same in a program whose registers are doubles
+const char* round_fn_d(int dt) {
+  return (DT)dt == DT::F16 ? "rn_f16_d" : (DT)dt == DT::BF16 ? "rn_bf16_d" : (DT)dt == DT::F64 ? "rn_f64" : "rn_f32_d";
+}
 const char* wrap_fn(int dt) { return (DT)dt == DT::I8 ? "wr_i8" : (DT)dt == DT::I16 ? "wr_i16" : (DT)dt == DT::I64 ? "wr_i64" : "wr_i32"; }
 
 struct Var {
@@ -250,6 +304,7 @@ struct Var {
   bool is_float = true;
   bool is_const = false;
   std::string literal;
+  std::string literal64;  // the expression of a float64 constant
 };
 
 std::string float_unary(int op, const std::string& a) {
@@ -272,6 +327,40 @@ std::string float_unary(int op, const std::string& a) {
     case EW_ASIN: return "asinf(" + a + ")";
     case EW_ACOS: return "acosf(" + a + ")";
     default: return a;
+  }
+}
+std::string double_unary(int op, const std::string& a) {
+  switch (op) {
+    case EW_ABS: return "fabs(" + a + ")";
+    case EW_NEG: return "(-" + a + ")";
+    case EW_EXP: return "exp(" + a + ")";
+    case EW_LOG: return "log(" + a + ")";
+    case EW_TANH: return "tanh(" + a + ")";
+    case EW_RSQRT: return "__ddiv_rn(1.0, __dsqrt_rn(" + a + "))";
+    case EW_SQRT: return "__dsqrt_rn(" + a + ")";
+    case EW_RECIP: return "__ddiv_rn(1.0, " + a + ")";
+    case EW_FLOOR: return "floor(" + a + ")";
+    case EW_SQUARE: return "__dmul_rn(" + a + ", " + a + ")";
+    case EW_SIN: return "sin(" + a + ")";
+    case EW_COS: return "cos(" + a + ")";
+    case EW_ASINH: return "asinh(" + a + ")";
+    case EW_ACOSH: return "acosh(" + a + ")";
+    case EW_ATAN: return "atan(" + a + ")";
+    case EW_ASIN: return "asin(" + a + ")";
+    case EW_ACOS: return "acos(" + a + ")";
+    default: return a;
+  }
+}
+std::string double_binary(int op, const std::string& a, const std::string& b) {
+  switch (op) {
+    case EW_ADD: return "__dadd_rn(" + a + ", " + b + ")";
+    case EW_SUB: return "__dsub_rn(" + a + ", " + b + ")";
+    case EW_MUL: return "__dmul_rn(" + a + ", " + b + ")";
+    case EW_DIV: return "__ddiv_rn(" + a + ", " + b + ")";
+    case EW_MAX: return "mx_d(" + a + ", " + b + ")";
+    case EW_MIN: return "mn_d(" + a + ", " + b + ")";
+    case EW_POW: return "pow(" + a + ", " + b + ")";
+    default: return "atan2(" + a + ", " + b + ")";
   }
 }
 std::string float_binary(int op, const std::string& a, const std::string& b) {
@@ -308,19 +397,20 @@ const char* cmp_op(int op) {
 
 // The expression of one elementwise op in generated code; `ref(value, want_float)` yields an operand's expression.
 template <class Ref>
-std::string instr_expr(int op, int dt, int cls, int src_cls, int a, int b, int c, Ref&& ref) {
+std::string instr_expr(int op, int dt, int cls, int src_cls, int a, int b, int c, Ref&& ref, bool f64 = false) {
   const bool fl = cls == EWC_FLOAT;
   const bool sfl = src_cls == EWC_FLOAT;
+  const std::string rnd = f64 ? round_fn_d(dt) : round_fn(dt);
   std::string expr;
   if (op == EW_COPY) {
     expr = ref(a, fl);
   } else if (op == EW_CAST) {
-    if (fl) expr = std::string(round_fn(dt)) + "(" + (sfl ? ref(a, true) : "(float)" + ref(a, false)) + ")";
+    if (fl) expr = rnd + "(" + (sfl ? ref(a, true) : (f64 ? "(double)" : "(float)") + ref(a, false)) + ")";
     else if (cls == EWC_BOOL) expr = sfl ? "(" + ref(a, true) + " != 0.f ? 1 : 0)" : "(" + ref(a, false) + " != 0 ? 1 : 0)";
-    else if (sfl) expr = std::string((DT)dt == DT::I8 ? "f2i_i8" : (DT)dt == DT::I16 ? "f2i_i16" : "f2i_i32") + "(" + ref(a, true) + ")";
+    else if (sfl) expr = std::string((DT)dt == DT::I8 ? "f2i_i8" : (DT)dt == DT::I16 ? "f2i_i16" : "f2i_i32") + (f64 ? "_d(" : "(") + ref(a, true) + ")";
     else expr = std::string(wrap_fn(dt)) + "(" + ref(a, false) + ")";
   } else if (op <= EW_ACOS) {
-    if (fl) expr = std::string(round_fn(dt)) + "(" + float_unary(op, ref(a, true)) + ")";
+    if (fl) expr = rnd + "(" + (f64 ? double_unary(op, ref(a, true)) : float_unary(op, ref(a, true))) + ")";
     else if (op == EW_ABS) expr = std::string(wrap_fn(dt)) + "(abs(" + ref(a, false) + "))";
     else if (op == EW_NEG) expr = std::string(wrap_fn(dt)) + "(-" + ref(a, false) + ")";
     else if (op == EW_SQUARE) expr = std::string(wrap_fn(dt)) + "(" + ref(a, false) + " * " + ref(a, false) + ")";
@@ -332,7 +422,7 @@ std::string instr_expr(int op, int dt, int cls, int src_cls, int a, int b, int c
   } else if (op == EW_NOT) {
     expr = "(" + ref(a, false) + " ? 0 : 1)";
   } else if (op <= EW_ATAN2) {
-    if (fl) expr = std::string(round_fn(dt)) + "(" + float_binary(op, ref(a, true), ref(b, true)) + ")";
+    if (fl) expr = rnd + "(" + (f64 ? double_binary(op, ref(a, true), ref(b, true)) : float_binary(op, ref(a, true), ref(b, true))) + ")";
     else expr = std::string(wrap_fn(dt)) + "(" + int_binary(op, ref(a, false), ref(b, false)) + ")";
   } else if (op <= EW_LE) {
     const std::string x = ref(a, sfl), y = ref(b, sfl);
@@ -419,12 +509,13 @@ EwShape ew_shape(const EwProgram& P, bool vec) {
     live_max = std::max(live_max, live + 1);
   }
   regs += 8 * live_max;
+  if (ew_has_f64(P)) return sh;  // doubles: twice the registers of this estimate
   if (regs <= 40) sh.min_blocks = 6;
   else if (regs <= 48) sh.min_blocks = 5;
   return sh;
 }
 bool packed_load(const EwProgram& P, const EwOperand& o) {
-  if ((DT)o.dt != DT::F16 && (DT)o.dt != DT::BF16) return false;
+  if (((DT)o.dt != DT::F16 && (DT)o.dt != DT::BF16) || ew_has_f64(P)) return false;
   return o.kind == EWI_FULL || (o.kind == EWI_MOD && o.mod % 8 == 0) ||
          (o.kind == EWI_STRIDED && !strided_run8_const(P, o) && strided_vec8_ok(P, o));
 }
@@ -435,8 +526,14 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
   std::ostringstream s;
   const bool i64 = ew_has_i64(P);
   const std::string ity = i64 ? "long long" : "int";
+  const bool f64 = ew_has_f64(P);
+  const std::string fty = f64 ? "double" : "float";
+  // loads and stores of floating-point tensors narrower than the registers convert through float32
+  auto ld8_name = [&](int dt) { return std::string("ld8_") + dt_tag(dt) + (f64 && is_float_dt(dt) && (DT)dt != DT::F64 ? "_d" : ""); };
+  auto st8_name = [&](int dt) { return std::string("st8_") + dt_tag(dt) + (f64 && is_float_dt(dt) && (DT)dt != DT::F64 ? "_d" : ""); };
   const EwShape sh = ew_shape(P, vec);
   s << kPreamble;
+  if (f64) s << kPreambleF64;
   s << "extern \"C\" __global__ void __launch_bounds__(256";
   if (sh.min_blocks > 0) s << ", " << sh.min_blocks;
   s << ") akgb_ew_jit(";
@@ -455,6 +552,10 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
     char buf[64];
     std::snprintf(buf, sizeof(buf), "0x%08xu", P.const_bits[c]);
     v.literal = buf;
+    if (P.const_f64[c]) {
+      std::snprintf(buf, sizeof(buf), "__longlong_as_double(0x%08x%08xLL)", P.const_hi[c], P.const_bits[c]);
+      v.literal64 = buf;
+    }
     regs[P.const_reg[c]] = v;  // class decided at use (float bits or int)
   }
   // loads
@@ -467,7 +568,7 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
       s << "  U4 r" << i << "[U];\n";
       v.name = "a" + std::to_string(i) + "#";  // widened per granule in the compute loop: indexed [j] only
     } else {
-      s << "  " << (fl ? "float" : ity) << " a" << i << "[U][E];\n";
+      s << "  " << (fl ? fty : ity) << " a" << i << "[U][E];\n";
       v.name = "a" + std::to_string(i);
     }
     regs[o.reg] = v;
@@ -482,23 +583,23 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
       else if (o.kind == EWI_MOD) s << "      r" << i << "[u] = ld16c(" << at << "(v * 8) % " << o.mod << "LL);\n";
       else s << "      r" << i << "[u] = ld16c(" << at << strided_index(P, o, "(v * 8)") << ");\n";
     } else if (vec) {
-      if (o.kind == EWI_FULL) s << "      ld8_" << tag << "(in" << i << ", v * 8, a" << i << "[u], true);\n";
+      if (o.kind == EWI_FULL) s << "      " << ld8_name(o.dt) << "(in" << i << ", v * 8, a" << i << "[u], true);\n";
       else if (o.kind == EWI_MOD && o.mod % 8 == 0)
-        s << "      ld8_" << tag << "(in" << i << ", (v * 8) % " << o.mod << "LL, a" << i << "[u], false);\n";
+        s << "      " << ld8_name(o.dt) << "(in" << i << ", (v * 8) % " << o.mod << "LL, a" << i << "[u], false);\n";
       else if (o.kind == EWI_MOD)
         s << "      #pragma unroll\n      for (int j = 0; j < 8; ++j) a" << i << "[u][j] = ld1_" << tag << "(in" << i
           << ", (v * 8 + j) % " << o.mod << "LL);\n";
       else if (o.kind == EWI_STRIDED && strided_run8_const(P, o))  // one value for the whole granule (a per-channel operand)
-        s << "      { const " << (is_float_dt(o.dt) ? "float" : ity) << " t = ld1_" << tag << "(in" << i << ", "
+        s << "      { const " << (is_float_dt(o.dt) ? fty : ity) << " t = ld1_" << tag << "(in" << i << ", "
           << strided_index(P, o, "(v * 8)") << ");\n        #pragma unroll\n        for (int j = 0; j < 8; ++j) a" << i
           << "[u][j] = t; }\n";
       else if (o.kind == EWI_STRIDED && strided_vec8_ok(P, o))
-        s << "      ld8_" << tag << "(in" << i << ", " << strided_index(P, o, "(v * 8)") << ", a" << i << "[u], false);\n";
+        s << "      " << ld8_name(o.dt) << "(in" << i << ", " << strided_index(P, o, "(v * 8)") << ", a" << i << "[u], false);\n";
       else if (o.kind == EWI_STRIDED)
         s << "      #pragma unroll\n      for (int j = 0; j < 8; ++j) a" << i << "[u][j] = ld1_" << tag << "(in" << i
           << ", " << strided_index(P, o, "(v * 8 + j)") << ");\n";
       else  // scalar
-        s << "      { const " << (is_float_dt(o.dt) ? "float" : ity) << " t = ld1_" << tag << "(in" << i
+        s << "      { const " << (is_float_dt(o.dt) ? fty : ity) << " t = ld1_" << tag << "(in" << i
           << ", 0);\n        #pragma unroll\n        for (int j = 0; j < 8; ++j) a" << i << "[u][j] = t; }\n";
     } else {
       if (o.kind == EWI_FULL) s << "      a" << i << "[u][0] = ld1_" << tag << "(in" << i << ", v);\n";
@@ -516,6 +617,8 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
       s << "      float a" << i << "[E];\n      cvt8_" << dt_tag(P.in[i].dt) << "(r" << i << "[u], a" << i << ");\n";
   auto ref = [&](int reg, bool want_float) -> std::string {
     const Var& v = regs[reg];
+    if (v.is_const && want_float && f64)
+      return !v.literal64.empty() ? v.literal64 : "(double)__uint_as_float(" + v.literal + ")";
     if (v.is_const) return want_float ? "__uint_as_float(" + v.literal + ")" : (i64 ? "(long long)(int)" : "(int)") + v.literal;
     return v.name + "[u][j]";
   };
@@ -525,11 +628,11 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
     const bool fl = ins.cls == EWC_FLOAT;
     std::string name = "t" + std::to_string(tcount++);
     // results of a 16-bit type: the granule is computed unrounded, then rounded two values per instruction
-    const bool pair_round = vec && fl && ((DT)ins.dt == DT::F16 || (DT)ins.dt == DT::BF16) && ins.op != EW_COPY &&
+    const bool pair_round = vec && !f64 && fl && ((DT)ins.dt == DT::F16 || (DT)ins.dt == DT::BF16) && ins.op != EW_COPY &&
                             ins.op != EW_SELECT;
     const std::string expr =
-        instr_expr(ins.op, pair_round ? (int)DT::F32 : ins.dt, ins.cls, ins.src_cls, ins.a, ins.b, ins.c, ref);
-    s << "      " << (fl ? "float" : ity) << " " << name << "[E];\n";
+        instr_expr(ins.op, pair_round ? (int)DT::F32 : ins.dt, ins.cls, ins.src_cls, ins.a, ins.b, ins.c, ref, f64);
+    s << "      " << (fl ? fty : ity) << " " << name << "[E];\n";
     s << "      #pragma unroll\n      for (int j = 0; j < E; ++j) " << name << "[j] = " << expr << ";\n";
     if (pair_round) s << "      rn8_" << dt_tag(ins.dt) << "(" << name << ");\n";
     Var nv;
@@ -563,8 +666,11 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
     const bool fl = is_float_dt(o.dt);
     std::string src;
     if (v.is_const) {
-      t << "      " << (fl ? "float" : ity) << " oc" << i << "[E];\n      #pragma unroll\n      for (int j = 0; j < E; ++j) oc"
-        << i << "[j] = " << (fl ? "__uint_as_float(" + v.literal + ")" : "(int)" + v.literal) << ";\n";
+      const std::string cexpr = !fl ? "(int)" + v.literal
+                                : f64 && !v.literal64.empty() ? v.literal64
+                                                               : (f64 ? "(double)" : "") + ("__uint_as_float(" + v.literal + ")");
+      t << "      " << (fl ? fty : ity) << " oc" << i << "[E];\n      #pragma unroll\n      for (int j = 0; j < E; ++j) oc"
+        << i << "[j] = " << cexpr << ";\n";
       src = "oc" + std::to_string(i);
     } else if (!v.name.empty() && v.name.back() == '#') {
       src = v.name.substr(0, v.name.size() - 1);
@@ -573,14 +679,14 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
     }
     if (o.kind == EWI_STRIDED) {
       if (vec && strided_vec8_ok(P, o))
-        t << "      st8_" << tag << "(out" << i << ", " << strided_index(P, o, "(v * 8)") << ", " << src << ");\n";
+        t << "      " << st8_name(o.dt) << "(out" << i << ", " << strided_index(P, o, "(v * 8)") << ", " << src << ");\n";
       else if (vec)
         t << "      #pragma unroll\n      for (int j = 0; j < 8; ++j) st1_" << tag << "(out" << i << ", "
           << strided_index(P, o, "(v * 8 + j)") << ", " << src << "[j]);\n";
       else
         t << "      st1_" << tag << "(out" << i << ", " << strided_index(P, o, "v") << ", " << src << "[0]);\n";
     } else if (vec) {
-      t << "      st8_" << tag << "(out" << i << ", v * 8, " << src << ");\n";
+      t << "      " << st8_name(o.dt) << "(out" << i << ", v * 8, " << src << ");\n";
     } else {
       t << "      st1_" << tag << "(out" << i << ", v, " << src << "[0]);\n";
     }
@@ -1625,7 +1731,7 @@ bool row_jit_export(const RowProgram& P, const std::string& entry, std::vector<c
   return true;
 }
 
-bool ew_program_needs_jit(const EwProgram& P) { return ew_has_i64(P); }
+bool ew_program_needs_jit(const EwProgram& P) { return ew_has_i64(P) || ew_has_f64(P); }
 
 // The CUDA C++ text that would be compiled for this program (empty when the program needs the interpreter).
 std::string ew_jit_source(const EwProgram& P, bool vec) {

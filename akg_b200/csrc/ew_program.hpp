@@ -54,6 +54,9 @@ struct EwProgram {
   uint32_t const_bits[kEwMaxConst];  // already rounded to the constant's declared type
   uint8_t const_reg[kEwMaxConst];
   EwInstr instr[kEwMaxInstr];
+  // float64 constants: const_bits holds the low word of the double, const_hi the high word
+  uint32_t const_hi[kEwMaxConst];
+  uint8_t const_f64[kEwMaxConst];
 };
 
 }  // namespace akgb

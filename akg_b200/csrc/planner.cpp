@@ -68,8 +68,9 @@ bool ew_opcode(OpK k, EwOp* op) {
   }
 }
 
-// int64 values run in generated kernels only (all integer registers widened to 64 bits); float64 is not placed
-bool ew_dtype_ok(DT d) { return d != DT::F64 && d != DT::Invalid; }
+// int64 and float64 values run in generated kernels only (all integer registers widened to 64 bits, all
+// floating-point registers to double)
+bool ew_dtype_ok(DT d) { return d != DT::Invalid; }
 
 uint32_t const_bits(double v, DT d) {
   float f;
@@ -93,7 +94,7 @@ uint32_t const_bits(double v, DT d) {
 // shared with the row-program builder (rowfuse.cpp)
 bool ew_opcode_of(OpK k, EwOp* op) { return ew_opcode(k, op); }
 uint32_t ew_const_bits(double v, DT d) { return const_bits(v, d); }
-bool ew_type_ok(DT d) { return ew_dtype_ok(d) && d != DT::I64; }  // row / column programs keep 32-bit integers
+bool ew_type_ok(DT d) { return ew_dtype_ok(d) && d != DT::I64 && d != DT::F64; }  // row / column programs keep 32-bit registers
 
 namespace {
 
@@ -234,7 +235,16 @@ struct Builder {
       if (v.is_const) {
         if (v.cval.size() != 1) throw Unsupported("constant tensors with more than one element");
         if (P.n_const >= kEwMaxConst) throw Unsupported("too many constants in one elementwise group");
-        P.const_bits[P.n_const] = const_bits(v.cval[0], v.dt);
+        if (v.dt == DT::F64) {
+          uint64_t b;
+          const double dv = v.cval[0];
+          std::memcpy(&b, &dv, 8);
+          P.const_bits[P.n_const] = (uint32_t)b;
+          P.const_hi[P.n_const] = (uint32_t)(b >> 32);
+          P.const_f64[P.n_const] = 1;
+        } else {
+          P.const_bits[P.n_const] = const_bits(v.cval[0], v.dt);
+        }
         P.const_reg[P.n_const] = (uint8_t)r;
         ++P.n_const;
         return r;
@@ -739,7 +749,16 @@ struct Builder {
       P.n = out.numel();
       P.shape[0] = P.n;
       P.n_const = 1;
-      P.const_bits[0] = const_bits(n.pad_value, out.dt);
+      if (out.dt == DT::F64) {
+        uint64_t b;
+        const double dv = n.pad_value;
+        std::memcpy(&b, &dv, 8);
+        P.const_bits[0] = (uint32_t)b;
+        P.const_hi[0] = (uint32_t)(b >> 32);
+        P.const_f64[0] = 1;
+      } else {
+        P.const_bits[0] = const_bits(n.pad_value, out.dt);
+      }
       P.const_reg[0] = 0;
       P.n_out = 1;
       P.out[0].dt = (int)out.dt;

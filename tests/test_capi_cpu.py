@@ -459,3 +459,24 @@ def test_generated_kernels_shard_like_the_templates(lib):
     kl = FusedKernel(descs.layer_norm_backward(16384, 4096), shard_rank=1, shard_world=4)
     assert kl.meta()["steps"] == ["akgb_row_jit", "reduce_col_f32", "reduce_col_f32"] and kl.inputs[0].shape == (4096, 4096)
     assert [t.shard_kind for t in kl.outputs] == [_capi.SHARD_SPLIT_AXIS0, _capi.SHARD_PARTIAL_SUM, _capi.SHARD_PARTIAL_SUM]
+
+
+def test_float64_regions_plan_as_generated_kernels_only(lib):
+    """float64 elementwise chains are one generated kernel whose registers are doubles; reductions or row programs over
+    float64 are refused (no float64 reduction template)."""
+    from akg_b200 import FusedKernel, UnsupportedError
+    from akg_b200.descs import _Builder, _attr, _reduce_attr
+    f = "float64"
+    b = _Builder("Fused_F64_plan_1")
+    x, y = b.input("x", [64, 256], f), b.input("y", [256], f)
+    b.output(b.emit("Mul", [b.emit("Add", [x, y], [64, 256], f), b.const(0.1, f)], [64, 256], f))
+    d = b.build()
+    k = FusedKernel(d)
+    assert k.meta()["template"] == "ew_generic" and k.launch_count == 1
+    src = k.jit_source()
+    assert "double a0[U][E]" in src and "__dadd_rn" in src and "__longlong_as_double(0x" in src
+    b = _Builder("Fused_F64_reduce_2")
+    x = b.input("x", [64, 256], f)
+    b.output(b.emit("ReduceSum", [x], [64, 1], f, _reduce_attr([1], True)))
+    with pytest.raises(UnsupportedError):
+        FusedKernel(b.build())

@@ -347,6 +347,51 @@ def test_int64_values_run_in_generated_kernels(lib):
     check(d, [rng.integers(-2**50, 2**50, (3, 7)).astype(np.int64), rng.integers(0, 2**50, (6, 21)).astype(np.int64)], exact=True)
 
 
+def test_float64_values_run_in_generated_kernels(lib):
+    """float64 arithmetic, compares and casts: the generated kernel keeps all its floating-point registers as doubles
+    (an op of a narrower type rounds its double result once to that type); the interpreting kernel has no such mode.
+    + - * / sqrt and every cast are bit-exact against the oracle, transcendentals to 1e-14."""
+    from akg_b200 import UnsupportedError
+    b = _Builder("Fused_F64_Chain_18")
+    f64, f32 = "float64", "float32"
+    x, y, z = b.input("x", [96, 200], f64), b.input("y", [200], f64), b.input("z", [96, 200], f32)
+    t = b.emit("Mul", [b.emit("Add", [x, y], [96, 200], f64), b.const(0.3, f64)], [96, 200], f64)
+    zc = b.emit("Cast", [z], [96, 200], f64, [_attr("dst_type", "str", f64)])
+    q = b.emit("RealDiv", [t, b.emit("Sqrt", [b.emit("Abs", [zc], [96, 200], f64)], [96, 200], f64)], [96, 200], f64)
+    gt = b.emit("Greater", [t, zc], [96, 200], "bool")
+    sel = b.emit("Select", [gt, b.emit("Sub", [q, zc], [96, 200], f64), b.emit("Maximum", [q, zc], [96, 200], f64)], [96, 200], f64)
+    b.output(sel)
+    for dst in (f32, "float16", "bfloat16", "int32"):
+        b.output(b.emit("Cast", [sel], [96, 200], dst, [_attr("dst_type", "str", dst)]))
+    # a float32-typed op inside the float64 program: correctly rounded float32 arithmetic
+    b.output(b.emit("Mul", [z, b.emit("Cast", [t], [96, 200], f32, [_attr("dst_type", "str", f32)])], [96, 200], f32))
+    d = b.build()
+    rng = np.random.default_rng(18)
+    ins = [rng.standard_normal((96, 200)) * 100, rng.standard_normal(200), (rng.standard_normal((96, 200)) * 50).astype(np.float32)]
+    ins[0][0, :6] = [np.inf, -np.inf, np.nan, 1e300, -1e-310, 0.0]
+    ins[2][1, :3] = [np.inf, np.nan, 0.0]
+    if FLAGS[0] != 0:
+        with pytest.raises(UnsupportedError):
+            run(d, ins)
+        return
+    got, k = run(d, ins)
+    want = O.evaluate(d, ins)
+    assert k.launch_count == 1 and k.meta()["template"] == "ew_generic"
+    for g, w in zip(got, want):
+        assert g.dtype == w.dtype
+        nan = np.isnan(w.astype(np.float64)) if w.dtype.kind == "f" or w.dtype == BF16 else np.zeros(w.shape, bool)
+        assert np.array_equal(np.isnan(g.astype(np.float64)) if nan.any() else nan, nan)
+        gb, wb = g.view(np.uint8).reshape(g.shape + (-1,)), np.ascontiguousarray(w).view(np.uint8).reshape(w.shape + (-1,))
+        assert np.array_equal(gb[~nan], wb[~nan])
+    # transcendentals, a ragged extent (element-wise accesses) and a float64 constant that float32 cannot hold
+    b = _Builder("Fused_F64_Tanh_19")
+    p_ = b.input("p", [37, 13], f64)
+    e = b.emit("Exp", [b.emit("Mul", [b.emit("Tanh", [p_], [37, 13], f64), b.const(0.1234567890123456, f64)], [37, 13], f64)], [37, 13], f64)
+    b.output(b.emit("Log", [b.emit("Add", [e, b.const(1.0, f64)], [37, 13], f64)], [37, 13], f64))
+    d = b.build()
+    check(d, [rng.standard_normal((37, 13)) * 3], rtol=1e-14, atol=1e-15)
+
+
 def _cast_desc(dst):
     b = _Builder(f"Fused_CastTo_{dst}_14")
     x = b.input("x", [4096], "float32")
