@@ -481,7 +481,7 @@ bool strided_run8_const(const EwProgram& P, const EwOperand& o) {
 // How one thread of the generated elementwise kernel is laid out: U granules (of 8 elements with 16-byte accesses, of 1
 // otherwise), all loaded before the first is computed.  Measured on 0.5-1 GB chains: 16-bit granules that stay packed
 // until their turn (4 registers instead of 8) took a float16-in / float32-math GELU chain from 204 to 168 us and a
-// bfloat16 multiply-add from 153 to 120 us; four granules per thread, or one, were never faster than two; a register
+// bfloat16 multiply-add from 153 to 120 us; four granules per thread, or one, were never faster than two at that size; a register
 // cap for six resident CTAs gained another 1-10 % on the programs small enough to fit it.
 struct EwShape {
   int U = 2;
@@ -492,6 +492,10 @@ EwShape ew_shape(const EwProgram& P, bool vec) {
   EwShape sh;
   sh.U = vec ? 2 : 4;
   if (!vec) return sh;
+  // small launches (a shard of a split tensor, a 67 MB copy) run faster with twice the CTAs of half the work: float32
+  // copy of 2^23 elements 13.2 -> 11.8 us, the float32-math GELU chain on 2^23 elements 15.2 -> 14.6 us; from 2^24
+  // elements on the two shapes time alike (25.1 / 24.9 us) and two granules win at 2^27 (168.6 / 172.5 us)
+  if (P.n <= ((int64_t)3 << 22)) sh.U = 1;
   // registers the loaded granules hold, plus 8 per value alive at once in the op chain
   int regs = 0;
   for (int i = 0; i < P.n_in; ++i) regs += sh.U * (packed_load(P, P.in[i]) ? 4 : 8);

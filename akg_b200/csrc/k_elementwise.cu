@@ -179,10 +179,10 @@ __global__ void __launch_bounds__(256) gelu_chain_f16_scalar_kernel(const __half
   }
 }
 
-template <bool BIAS, bool MUL, bool OUTF32>
-cudaError_t launch_vec(const GeluChainParams& p, const void* x, const void* bias, const void* y, void* out,
-                       const void* lut, uint32_t* err, int64_t nvec, int sms, cudaStream_t s, LaunchDims* dims) {
-  constexpr int T = 512, U = 2, I = 2;
+template <bool BIAS, bool MUL, bool OUTF32, int U>
+cudaError_t launch_vec_shape(const GeluChainParams& p, const void* x, const void* bias, const void* y, void* out,
+                             const void* lut, uint32_t* err, int64_t nvec, cudaStream_t s, LaunchDims* dims) {
+  constexpr int T = 512, I = 2;
   const int64_t per_cta = (int64_t)T * U * I;
   const int64_t grid = (nvec + per_cta - 1) / per_cta;
   if (dims) {
@@ -194,6 +194,17 @@ cudaError_t launch_vec(const GeluChainParams& p, const void* x, const void* bias
       (const uint4*)x, (const uint4*)bias, (const uint4*)y, out, nvec, p.inner / 8, p.c0, p.c1, p.c2, p.c_one,
       (const uint16_t*)lut, err);
   return cudaGetLastError();
+}
+
+// CTA shapes measured at 4 / 8 / 16 / 32 / 64 x [512,4096] (0.07 - 1.07 GB, 20 launches in a graph): 512 threads x 2
+// vectors x 2 rounds 13.9 / 23.3 / 42.7 / 81.2 / 158.1 us; one vector per thread and round 12.9 / 22.8 / 42.4 / 81.0 /
+// 158.8 us; one round per CTA, or 256 threads, 7 - 25 % slower at every size (every CTA stages the table).  Small
+// launches, as a shard of a split tensor is, take the finer shape.
+template <bool BIAS, bool MUL, bool OUTF32>
+cudaError_t launch_vec(const GeluChainParams& p, const void* x, const void* bias, const void* y, void* out,
+                       const void* lut, uint32_t* err, int64_t nvec, int /*sms*/, cudaStream_t s, LaunchDims* dims) {
+  if (nvec <= (int64_t)3 << 20) return launch_vec_shape<BIAS, MUL, OUTF32, 1>(p, x, bias, y, out, lut, err, nvec, s, dims);
+  return launch_vec_shape<BIAS, MUL, OUTF32, 2>(p, x, bias, y, out, lut, err, nvec, s, dims);
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
