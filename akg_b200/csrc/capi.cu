@@ -321,7 +321,7 @@ int launches_of(const akgb_kernel* k) {
         n += k->fold_in_launch ? 1 : 2;
         break;
       case StepK::ReduceColDual:
-        n += (k->fold_in_launch && (st.red_inner + 127) / 128 <= kReduceMaxTicketTiles) ? 1 : 3;
+        n += (k->fold_in_launch && (st.red_inner + 127) / 128 <= kReduceMaxTicketTiles) ? 1 : 2;
         break;
       case StepK::GeluChain:
         n += (st.gelu.n % 8) ? 2 : 1;

@@ -693,15 +693,10 @@ cudaError_t dual_impl(const float* x, float* out1, float* out2, int64_t red, int
   reduce_col_dual_f32_kernel<Op1, Op2><<<grid, block, 0, s>>>(x, partial, partial2, red, inner, rows_per_split);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  if (fx && fx->world > 1) {  // both folds and both exchanges in one launch
-    reduce_finish_exchange_kernel<Op1, Op2><<<grid.x + 1, 256, 0, s>>>(partial, out1, splits, inner, (int)grid.x, partial2,
-                                                                       out2, (int)(grid.x * grid.y), *fx);
-    return cudaGetLastError();
-  }
-  reduce_col_finish_kernel<Op1><<<(unsigned)((inner + 255) / 256), 256, 0, s>>>(partial, out1, splits, inner);
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
-  reduce_all_finish_kernel<Op2><<<1, 1024, 0, s>>>(partial2, out2, (int)(grid.x * grid.y));
+  // both folds (and, between ranks, both exchanges) in one launch: a CTA per column tile and one for the all-elements result
+  FinishExchange none;
+  reduce_finish_exchange_kernel<Op1, Op2><<<grid.x + 1, 256, 0, s>>>(partial, out1, splits, inner, (int)grid.x, partial2,
+                                                                     out2, (int)(grid.x * grid.y), fx ? *fx : none);
   return cudaGetLastError();
 }
 template <class Op1>
