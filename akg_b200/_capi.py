@@ -22,7 +22,7 @@ AKGB_TOO_LARGE = 7
 
 STATUS_NAMES = {
     0: "AKGB_OK", 1: "AKGB_INVALID_JSON", 2: "AKGB_UNSUPPORTED", 3: "AKGB_INVALID_ARG",
-    4: "AKGB_CUDA_ERROR", 5: "AKGB_MISALIGNED", 6: "AKGB_DEVICE_TIMEOUT", 7: "AKGB_TOO_LARGE",
+    4: "AKGB_CUDA_ERROR", 5: "AKGB_MISALIGNED", 6: "AKGB_DEVICE_TIMEOUT", 7: "AKGB_TOO_LARGE", 8: "AKGB_OUT_OF_RANGE",
 }
 
 # akgb_dtype code -> numpy dtype name
@@ -125,6 +125,7 @@ _SIGNATURES = [
     ("akgb_kernel_bytes", ctypes.c_int64, [_vp]),
     ("akgb_kernel_flops", ctypes.c_int64, [_vp]),
     ("akgb_check_device_error", ctypes.c_int, [_vp, ctypes.POINTER(ctypes.c_uint32)]),
+    ("akgb_checked_shrink_for_test", None, [ctypes.c_int]),
     ("akgb_reduce_sum_axis0_f32_noalloc", ctypes.c_int, [_vp, _vp, ctypes.c_int64, ctypes.c_int64, _vp]),
     ("akgb_last_error", ctypes.c_char_p, []),
     ("akgb_version", ctypes.c_char_p, []),

@@ -66,6 +66,7 @@ struct akgb_kernel {
   bool no_jit = false;  // AKGB_FLAG_NO_JIT
   bool fold_in_launch = false;  // AKGB_FLAG_FOLD_IN_LAUNCH
   bool stage_long_rows = false;  // AKGB_FLAG_STAGE_LONG_ROWS
+  bool checked = false;  // AKGB_FLAG_CHECKED
   // dynamic-shape regions: one plan per set of launch-time extents
   struct Bound {
     Graph graph;
@@ -186,9 +187,47 @@ akgb_status enter_fallback(Plan& plan, size_t ws_bytes) {
 }
 
 // `fx` / `fx_step`: the exchange that step `fx_step` of the plan completes inside its own launch (sharded reductions)
+void fill_arg_bytes(Plan& p, const Graph& g) {
+  p.arg_bytes.clear();
+  for (int vid : g.inputs) p.arg_bytes.push_back((size_t)g.v(vid).numel() * dt_size(g.v(vid).dt));
+  for (int vid : g.outputs) p.arg_bytes.push_back((size_t)g.v(vid).numel() * dt_size(g.v(vid).dt));
+  if (p.fallback) p.fallback->arg_bytes = p.arg_bytes;
+}
+
+akgb_status run_plan_steps(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws, size_t ws_bytes, cudaStream_t s,
+                           const FinishExchange* fx, int fx_step);
+
+// Bytes taken off the end of every range of a checked launch: a test of the checker itself (the accesses it then
+// reports and skips are inside the real tensors).
+int g_checked_shrink = 0;
+
 akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws, size_t ws_bytes, cudaStream_t s,
                      const FinishExchange* fx = nullptr, int fx_step = -1) {
-  if (plan.fallback && plan.use_fallback) return run_plan(k, *plan.fallback, tensors, ws, ws_bytes, s);
+  if (!k->checked) return run_plan_steps(k, plan, tensors, ws, ws_bytes, s, fx, fx_step);
+  // checked launch: generated kernels test every global access against these ranges
+  CheckedRanges r;
+  for (size_t i = 0; i < plan.arg_bytes.size() && r.n < 31; ++i) {
+    if (!tensors[i] || !plan.arg_bytes[i]) continue;
+    r.lo[r.n] = reinterpret_cast<unsigned long long>(tensors[i]);
+    r.hi[r.n] = r.lo[r.n] + plan.arg_bytes[i] - std::min<size_t>(plan.arg_bytes[i], (size_t)g_checked_shrink);
+    ++r.n;
+  }
+  if (ws && ws_bytes) {
+    r.lo[r.n] = reinterpret_cast<unsigned long long>(ws);
+    r.hi[r.n] = r.lo[r.n] + ws_bytes;
+    ++r.n;
+  }
+  r.err = g_dev[k->device].err_word;
+  if (plan.arg_bytes.size() > 31) return fail(AKGB_UNSUPPORTED, "checked launches take at most 31 tensors");
+  jit_set_checked_ranges(&r);
+  const akgb_status st = run_plan_steps(k, plan, tensors, ws, ws_bytes, s, fx, fx_step);
+  jit_set_checked_ranges(nullptr);
+  return st;
+}
+
+akgb_status run_plan_steps(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws, size_t ws_bytes, cudaStream_t s,
+                           const FinishExchange* fx, int fx_step) {
+  if (plan.fallback && plan.use_fallback) return run_plan_steps(k, *plan.fallback, tensors, ws, ws_bytes, s, nullptr, -1);
   DeviceState& ds = g_dev[k->device];
   for (size_t si = 0; si < plan.steps.size(); ++si) {
     Step& st = plan.steps[si];
@@ -238,7 +277,7 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
           // (the generated kernel is always the plan's first step, so nothing has been enqueued yet)
           const akgb_status fs = enter_fallback(plan, ws_bytes);
           if (fs != AKGB_OK) return fs;
-          return run_plan(k, *plan.fallback, tensors, ws, ws_bytes, s);
+          return run_plan_steps(k, *plan.fallback, tensors, ws, ws_bytes, s, nullptr, -1);
         }
         break;
       }
@@ -251,7 +290,7 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
         if (e == cudaErrorNotSupported && plan.fallback) {
           const akgb_status fs = enter_fallback(plan, ws_bytes);
           if (fs != AKGB_OK) return fs;
-          return run_plan(k, *plan.fallback, tensors, ws, ws_bytes, s);
+          return run_plan_steps(k, *plan.fallback, tensors, ws, ws_bytes, s, nullptr, -1);
         }
         break;
       }
@@ -368,6 +407,7 @@ void plan_chunks(akgb_kernel* k) {
       }
       if (!ok) return;
       Plan p = build_plan(g, k->sm_count, !k->no_jit);
+      fill_arg_bytes(p, g);
       if (p.workspace_bytes > k->plan.workspace_bytes) return;
       if (cudaStreamCreateWithFlags(&k->s_in, cudaStreamNonBlocking) != cudaSuccess) return;
       if (cudaStreamCreateWithFlags(&k->s_out, cudaStreamNonBlocking) != cudaSuccess) return;
@@ -555,6 +595,7 @@ void plan_and_describe(akgb_kernel* k) {
   } else {
     infer_sharding(k->graph, k->shard_rank, k->shard_world);
     k->plan = build_plan(k->graph, k->sm_count, !k->no_jit);
+    fill_arg_bytes(k->plan, k->graph);
     if (k->stage_long_rows)
       for (Step& st : k->plan.steps)
         if (st.kind == StepK::RowJit && st.row) st.row->stage_long_rows = true;
@@ -687,6 +728,7 @@ bool build_stages(akgb_kernel* k, const char* text, size_t len) {
       sk->no_jit = k->no_jit;
       sk->fold_in_launch = k->fold_in_launch;
       sk->stage_long_rows = k->stage_long_rows;
+      sk->checked = k->checked;
       sk->graph = std::move(sg.g);
       plan_and_describe(sk);
       stage_ws = std::max(stage_ws, sk->plan.workspace_bytes);
@@ -819,6 +861,7 @@ akgb_status akgb_compile(const char* info_json, size_t len, const akgb_options* 
     k->no_jit = (flags & AKGB_FLAG_NO_JIT) != 0;
     k->fold_in_launch = (flags & AKGB_FLAG_FOLD_IN_LAUNCH) != 0;
     k->stage_long_rows = (flags & AKGB_FLAG_STAGE_LONG_ROWS) != 0;
+    k->checked = (flags & AKGB_FLAG_CHECKED) != 0;
     k->json_text.assign(info_json, len);
     k->graph = parse_info(info_json, len);
     try {
@@ -903,6 +946,7 @@ akgb_status bound_plan(akgb_kernel* k, const int64_t* shapes, size_t count, akgb
       std::unique_ptr<akgb_kernel::Bound> b(new akgb_kernel::Bound());
       b->graph = bind_shapes(k->graph, per);
       b->plan = build_plan(b->graph, k->sm_count, !k->no_jit);
+      fill_arg_bytes(b->plan, b->graph);
       it = k->bound.emplace(std::move(key), std::move(b)).first;
     } catch (const JsonError& e) {
       return fail(AKGB_INVALID_ARG, e.what());
@@ -1024,6 +1068,7 @@ akgb_status akgb_check_device_error(akgb_kernel* k, uint32_t* word) {
   if (*word) {
     cudaMemset(ds.err_word, 0, sizeof(uint32_t));
     if (*word & 256u) ds.exchange_failed = true;  // the ranks' exchange counters may disagree now
+    if (*word == 512u) return fail(AKGB_OUT_OF_RANGE, "a checked launch reported an access outside its tensors (skipped)");
     return fail(AKGB_DEVICE_TIMEOUT, "a bounded device-side wait gave up");
   }
   return AKGB_OK;
@@ -1159,3 +1204,5 @@ akgb_status akgb_kernel_meta(const akgb_kernel* k, char* buf, size_t cap, size_t
 }
 
 }  // extern "C"
+
+extern "C" void akgb_checked_shrink_for_test(int bytes) { g_checked_shrink = bytes < 0 ? 0 : bytes; }

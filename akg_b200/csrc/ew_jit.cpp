@@ -108,15 +108,34 @@ const char* kPreamble = R"SRC(
 typedef unsigned int u32; typedef unsigned short u16; typedef unsigned char u8; typedef long long i64;
 struct __align__(16) U4 { u32 x, y, z, w; };
 struct __align__(8) U2 { u32 x, y; };
-__device__ __forceinline__ U4 ld16s(const void* p) { U4 v;
+// Checked build (the source then starts with "#define AKGB_CHECKED 1"): every access to global memory is tested
+// against the address ranges of the launch's tensors and workspace; one that falls outside any of them sets bit 9 of
+// the device error word and is skipped (a load gives zeros) -- no assert, no trap.
+#ifdef AKGB_CHECKED
+struct AkgbRanges { unsigned long long lo[32], hi[32]; int n; u32* err; };
+__device__ AkgbRanges akgb_rng;  // the same table from every block of a launch (its last kernel argument)
+__device__ __noinline__ bool akgb_ok(const void* p, int bytes) {
+  const unsigned long long a = (unsigned long long)p;
+  for (int i = 0; i < akgb_rng.n; ++i)
+    if (a >= akgb_rng.lo[i] && a + (unsigned long long)bytes <= akgb_rng.hi[i]) return true;
+  atomicOr(akgb_rng.err, 512u);
+  return false;
+}
+#define AKGB_CHK(p, bytes, zero) if (!akgb_ok(p, bytes)) return zero;
+#define AKGB_CHKV(p, bytes) if (!akgb_ok(p, bytes)) return;
+#else
+#define AKGB_CHK(p, bytes, zero)
+#define AKGB_CHKV(p, bytes)
+#endif
+__device__ __forceinline__ U4 ld16s(const void* p) { U4 v; v.x = v.y = v.z = v.w = 0; AKGB_CHK(p, 16, v)
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p)); return v; }
-__device__ __forceinline__ U4 ld16c(const void* p) { U4 v;
+__device__ __forceinline__ U4 ld16c(const void* p) { U4 v; v.x = v.y = v.z = v.w = 0; AKGB_CHK(p, 16, v)
   asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p)); return v; }
-__device__ __forceinline__ U2 ld8s(const void* p) { U2 v;
+__device__ __forceinline__ U2 ld8s(const void* p) { U2 v; v.x = v.y = 0; AKGB_CHK(p, 8, v)
   asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p)); return v; }
-__device__ __forceinline__ void st16(void* p, U4 v) {
+__device__ __forceinline__ void st16(void* p, U4 v) { AKGB_CHKV(p, 16)
   asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory"); }
-__device__ __forceinline__ void st8(void* p, U2 v) {
+__device__ __forceinline__ void st8(void* p, U2 v) { AKGB_CHKV(p, 8)
   asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" :: "l"(p), "r"(v.x), "r"(v.y) : "memory"); }
 __device__ __forceinline__ float h2f(u16 h) { float f; asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h)); return f; }
 __device__ __forceinline__ u16 f2h(float f) { u16 h; asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(f)); return h; }
@@ -191,24 +210,24 @@ template <class I> __device__ __forceinline__ void st8_i8(void* p, i64 e0, const
 template <class I> __device__ __forceinline__ void st8_bool(void* p, i64 e0, const I* r) { U2 v; v.x = 0; v.y = 0;
   _Pragma("unroll") for (int i = 0; i < 4; ++i) { v.x |= (r[i] ? 1u : 0u) << (8 * i); v.y |= (r[4 + i] ? 1u : 0u) << (8 * i); } st8((u8*)p + e0, v); }
 // scalar element access (any alignment)
-__device__ __forceinline__ float ld1_f16(const void* p, i64 i) { return h2f(((const u16*)p)[i]); }
-__device__ __forceinline__ float ld1_bf16(const void* p, i64 i) { return b2f(((const u16*)p)[i]); }
-__device__ __forceinline__ float ld1_f32(const void* p, i64 i) { return ((const float*)p)[i]; }
-__device__ __forceinline__ int ld1_i32(const void* p, i64 i) { return ((const int*)p)[i]; }
-__device__ __forceinline__ int ld1_i16(const void* p, i64 i) { return (int)((const short*)p)[i]; }
-__device__ __forceinline__ int ld1_i8(const void* p, i64 i) { return (int)((const signed char*)p)[i]; }
-__device__ __forceinline__ int ld1_bool(const void* p, i64 i) { return ((const u8*)p)[i] ? 1 : 0; }
-__device__ __forceinline__ void st1_f16(void* p, i64 i, float v) { ((u16*)p)[i] = f2h(v); }
-__device__ __forceinline__ void st1_bf16(void* p, i64 i, float v) { ((u16*)p)[i] = f2b(v); }
-__device__ __forceinline__ void st1_f32(void* p, i64 i, float v) { ((float*)p)[i] = v; }
-__device__ __forceinline__ void st1_i32(void* p, i64 i, int v) { ((int*)p)[i] = v; }
-__device__ __forceinline__ void st1_i16(void* p, i64 i, int v) { ((short*)p)[i] = (short)v; }
-__device__ __forceinline__ void st1_i8(void* p, i64 i, int v) { ((signed char*)p)[i] = (signed char)v; }
-__device__ __forceinline__ void st1_bool(void* p, i64 i, int v) { ((u8*)p)[i] = v ? 1 : 0; }
+__device__ __forceinline__ float ld1_f16(const void* p, i64 i) { AKGB_CHK((const u16*)p + i, 2, 0.f) return h2f(((const u16*)p)[i]); }
+__device__ __forceinline__ float ld1_bf16(const void* p, i64 i) { AKGB_CHK((const u16*)p + i, 2, 0.f) return b2f(((const u16*)p)[i]); }
+__device__ __forceinline__ float ld1_f32(const void* p, i64 i) { AKGB_CHK((const float*)p + i, 4, 0.f) return ((const float*)p)[i]; }
+__device__ __forceinline__ int ld1_i32(const void* p, i64 i) { AKGB_CHK((const int*)p + i, 4, 0) return ((const int*)p)[i]; }
+__device__ __forceinline__ int ld1_i16(const void* p, i64 i) { AKGB_CHK((const short*)p + i, 2, 0) return (int)((const short*)p)[i]; }
+__device__ __forceinline__ int ld1_i8(const void* p, i64 i) { AKGB_CHK((const u8*)p + i, 1, 0) return (int)((const signed char*)p)[i]; }
+__device__ __forceinline__ int ld1_bool(const void* p, i64 i) { AKGB_CHK((const u8*)p + i, 1, 0) return ((const u8*)p)[i] ? 1 : 0; }
+__device__ __forceinline__ void st1_f16(void* p, i64 i, float v) { AKGB_CHKV((u16*)p + i, 2) ((u16*)p)[i] = f2h(v); }
+__device__ __forceinline__ void st1_bf16(void* p, i64 i, float v) { AKGB_CHKV((u16*)p + i, 2) ((u16*)p)[i] = f2b(v); }
+__device__ __forceinline__ void st1_f32(void* p, i64 i, float v) { AKGB_CHKV((float*)p + i, 4) ((float*)p)[i] = v; }
+__device__ __forceinline__ void st1_i32(void* p, i64 i, int v) { AKGB_CHKV((int*)p + i, 4) ((int*)p)[i] = v; }
+__device__ __forceinline__ void st1_i16(void* p, i64 i, int v) { AKGB_CHKV((short*)p + i, 2) ((short*)p)[i] = (short)v; }
+__device__ __forceinline__ void st1_i8(void* p, i64 i, int v) { AKGB_CHKV((u8*)p + i, 1) ((signed char*)p)[i] = (signed char)v; }
+__device__ __forceinline__ void st1_bool(void* p, i64 i, int v) { AKGB_CHKV((u8*)p + i, 1) ((u8*)p)[i] = v ? 1 : 0; }
 // 64-bit integers (programs that hold any keep ALL their integer registers in 64 bits)
 __device__ __forceinline__ i64 wr_i64(i64 x) { return x; }
-__device__ __forceinline__ i64 ld1_i64(const void* p, i64 i) { return ((const i64*)p)[i]; }
-__device__ __forceinline__ void st1_i64(void* p, i64 i, i64 v) { ((i64*)p)[i] = v; }
+__device__ __forceinline__ i64 ld1_i64(const void* p, i64 i) { AKGB_CHK((const i64*)p + i, 8, 0) return ((const i64*)p)[i]; }
+__device__ __forceinline__ void st1_i64(void* p, i64 i, i64 v) { AKGB_CHKV((i64*)p + i, 8) ((i64*)p)[i] = v; }
 __device__ __forceinline__ void ld8_i64(const void* p, i64 e0, i64* r, bool stream) {
   _Pragma("unroll") for (int q = 0; q < 4; ++q) {
     const U4 v = stream ? ld16s((const i64*)p + e0 + 2 * q) : ld16c((const i64*)p + e0 + 2 * q);
@@ -254,8 +273,8 @@ __device__ __forceinline__ void st8_f64(void* p, i64 e0, const double* r) {
   _Pragma("unroll") for (int q = 0; q < 4; ++q) { U4 v;
     v.x = (u32)__double2loint(r[2*q]); v.y = (u32)__double2hiint(r[2*q]); v.z = (u32)__double2loint(r[2*q+1]); v.w = (u32)__double2hiint(r[2*q+1]);
     st16((double*)p + e0 + 2 * q, v); } }
-__device__ __forceinline__ double ld1_f64(const void* p, i64 i) { return ((const double*)p)[i]; }
-__device__ __forceinline__ void st1_f64(void* p, i64 i, double v) { ((double*)p)[i] = v; }
+__device__ __forceinline__ double ld1_f64(const void* p, i64 i) { AKGB_CHK((const double*)p + i, 8, 0.0) return ((const double*)p)[i]; }
+__device__ __forceinline__ void st1_f64(void* p, i64 i, double v) { AKGB_CHKV((double*)p + i, 8) ((double*)p)[i] = v; }
 )SRC";
 
 const char* dt_tag(int dt) {
@@ -843,7 +862,7 @@ bool row_generate_multipass(const RowProgram& P, bool vec, std::string* out, Row
   s << "constexpr int C = " << P.cols << ", T = 512, TPB = 512, VW = " << rs.vw << ", K = " << K << ";\n";
   s << "constexpr i64 CH = " << CH << ";\n";
   s << R"SRC(
-__device__ __forceinline__ U4 ld16p(const void* p, unsigned long long pol) { U4 v;
+__device__ __forceinline__ U4 ld16p(const void* p, unsigned long long pol) { U4 v; v.x = v.y = v.z = v.w = 0; AKGB_CHK(p, 16, v)
   asm volatile("ld.global.nc.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(pol)); return v; }
 __device__ __forceinline__ void ld8p_f32(const void* p, i64 e0, float* r, unsigned long long pol) {
   const U4 a = ld16p((const float*)p + e0, pol), b = ld16p((const float*)p + e0 + 4, pol);
@@ -1085,8 +1104,8 @@ template <int OP> __device__ __forceinline__ float row_reduce_cl(float v, float*
     for (size_t i = 0; i < P.out.size(); ++i) {
       if (P.out[i].kind != RK_COL) continue;
       s << "#pragma unroll\n  for (int q = 0; q < NIT; ++q) {\n    const i64 c = (i64)tr * VW + (i64)q * (T * VW);\n#pragma unroll\n"
-           "    for (int j = 0; j < VW; ++j)\n      if (c + j < C) ((float*)out" << i << ")[(i64)blockIdx.x * C + c + j] = cs" << i
-        << "[q][j];\n  }\n";
+           "    for (int j = 0; j < VW; ++j)\n      if (c + j < C) st1_f32(out" << i << ", (i64)blockIdx.x * C + c + j, cs" << i
+        << "[q][j]);\n  }\n";
     }
   }
   s << "}\n";
@@ -1234,7 +1253,7 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
            "    for (int j = 0; j < VW; ++j) smc[threadIdx.x][j] = cs" << i << "[k][j];\n    __syncthreads();\n"
            "    if (threadIdx.x < T) {\n      const int c = (tr + T * k) * VW;\n#pragma unroll\n      for (int j = 0; j < VW; ++j) {\n"
            "        float a = smc[tr][j];\n        for (int g2 = 1; g2 < RPB; ++g2) a = __fadd_rn(a, smc[g2 * T + tr][j]);\n"
-           "        if (c + j < C) ((float*)out" << i << ")[(i64)blockIdx.x * C + c + j] = a;\n      }\n    }\n  }\n";
+           "        if (c + j < C) st1_f32(out" << i << ", (i64)blockIdx.x * C + c + j, a);\n      }\n    }\n  }\n";
     }
   }
   s << "}\n";
@@ -1349,8 +1368,8 @@ template <int OP> __device__ __forceinline__ float comb(float a, float b) {
     s << "#pragma unroll\n  for (int j = 0; j < VW; ++j) sm[ty][tx * VW + j] = acc" << i << "[j];\n  __syncthreads();\n";
     s << "#pragma unroll\n  for (int h = TY / 2; h > 0; h >>= 1) {\n    if (ty < h) {\n#pragma unroll\n      for (int j = 0; j < VW; ++j) "
          "sm[ty][tx * VW + j] = comb<" << op << ">(sm[ty][tx * VW + j], sm[ty + h][tx * VW + j]);\n    }\n    __syncthreads();\n  }\n";
-    s << "  if (ty == 0 && valid) {\n#pragma unroll\n    for (int j = 0; j < VW; ++j)\n      if (c + j < C) partial" << i
-      << "[(i64)blockIdx.y * C + c + j] = sm[0][tx * VW + j];\n  }\n";
+    s << "  if (ty == 0 && valid) {\n#pragma unroll\n    for (int j = 0; j < VW; ++j)\n      if (c + j < C) st1_f32(partial" << i
+      << ", (i64)blockIdx.y * C + c + j, sm[0][tx * VW + j]);\n  }\n";
   }
   s << "}\n";
   *out = s.str();
@@ -1535,7 +1554,25 @@ std::string standalone_source(std::string src, const char* generated_entry, cons
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// The address ranges the launches of the calling thread are checked against (null: ordinary kernels).
+thread_local const CheckedRanges* t_checked = nullptr;
+
+// The checked form of a generated source: the checker compiled in, the table as last kernel argument, stored by every
+// block before its first access.
+std::string checked_source(const std::string& src, const char* entry) {
+  const size_t at = src.find(std::string(entry) + "(");
+  if (at == std::string::npos) return "";
+  const size_t close = src.find(") {\n", at);
+  if (close == std::string::npos) return "";
+  std::string out = "#define AKGB_CHECKED 1\n" + src.substr(0, close) + ", AkgbRanges akgb_rng_arg" +
+                    ") {\n  if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) akgb_rng = akgb_rng_arg;\n  __syncthreads();\n" +
+                    src.substr(close + 4);
+  return out;
+}
+
 }  // namespace
+
+void jit_set_checked_ranges(const CheckedRanges* r) { t_checked = r; }
 
 void jit_set_cache_dir(const char* dir) {
   std::lock_guard<std::mutex> lock(g_mu);
@@ -1571,6 +1608,8 @@ cudaError_t col_jit_launch(const RowProgram& P, const void* const* in, float* co
   std::string src;
   ColShape cs;
   if (!col_generate(P, vec, &src, &cs)) return cudaErrorNotSupported;
+  const CheckedRanges* ck = t_checked;
+  if (ck && (src = checked_source(src, "akgb_col_jit")).empty()) return cudaErrorNotSupported;
   JitKernel* k = compile(src, "akgb_col_jit");
   if (!k || k->failed) return cudaErrorNotSupported;
   const int64_t granules = (P.cols + cs.vw - 1) / cs.vw;
@@ -1591,6 +1630,11 @@ cudaError_t col_jit_launch(const RowProgram& P, const void* const* in, float* co
   }
   args[a++] = &rows;
   args[a++] = &rps;
+  CheckedRanges ckv;
+  if (ck) {
+    ckv = *ck;
+    args[a++] = &ckv;
+  }
   if (dims) {
     dims->grid[0] = (unsigned)gx;
     dims->grid[1] = (unsigned)splits;
@@ -1638,6 +1682,8 @@ cudaError_t row_jit_launch(const RowProgram& P, const void* const* in, void* con
   std::string src;
   RowShape rs;
   if (!row_generate(P, vec, &src, &rs)) return cudaErrorNotSupported;
+  const CheckedRanges* ck = t_checked;
+  if (ck && (src = checked_source(src, "akgb_row_jit")).empty()) return cudaErrorNotSupported;
   JitKernel* k = compile(src, "akgb_row_jit");
   if (!k || k->failed) return cudaErrorNotSupported;
   const int rpb = rs.tpb / rs.t;  // 1 for the multi-pass schedule
@@ -1662,6 +1708,11 @@ cudaError_t row_jit_launch(const RowProgram& P, const void* const* in, void* con
     args[a++] = &outp[i];
   }
   args[a++] = &rows;
+  CheckedRanges ckv;
+  if (ck) {
+    ckv = *ck;
+    args[a++] = &ckv;
+  }
   if (dims) {
     dims->grid[0] = (unsigned)grid;
     dims->block[0] = (unsigned)rs.tpb;
@@ -1752,6 +1803,8 @@ cudaError_t ew_jit_launch(const EwProgram& P, const void* const* in, void* const
   for (int i = 0; i < P.n_out && vec; ++i) vec = aligned16(out[i]);
   std::string src;
   if (!generate(P, vec, &src)) return cudaErrorNotSupported;
+  const CheckedRanges* ck = t_checked;
+  if (ck && (src = checked_source(src, "akgb_ew_jit")).empty()) return cudaErrorNotSupported;
   JitKernel* k = compile(src);
   if (!k || k->failed) return cudaErrorNotSupported;
   const int U = ew_shape(P, vec).U, E = vec ? 8 : 1;
@@ -1759,7 +1812,7 @@ cudaError_t ew_jit_launch(const EwProgram& P, const void* const* in, void* const
   const int64_t grid = (nv + 256 * U - 1) / (256 * U);
   if (grid > 0x7fffffff) return cudaErrorNotSupported;
   long long n = P.n;
-  void* args[kEwMaxIn + kEwMaxOut + 1];
+  void* args[kEwMaxIn + kEwMaxOut + 2];
   const void* inp[kEwMaxIn];
   void* outp[kEwMaxOut];
   int a = 0;
@@ -1772,6 +1825,11 @@ cudaError_t ew_jit_launch(const EwProgram& P, const void* const* in, void* const
     args[a++] = &outp[i];
   }
   args[a++] = &n;
+  CheckedRanges ckv;
+  if (ck) {
+    ckv = *ck;
+    args[a++] = &ckv;
+  }
   if (dims) {
     dims->grid[0] = (unsigned)grid;
     dims->block[0] = 256;

@@ -120,7 +120,16 @@ bool ew_jit_export(const EwProgram& p, const std::string& entry, std::vector<cha
                    bool* needs_align16);
 bool row_jit_export(const RowProgram& p, const std::string& entry, std::vector<char>* cubin, LaunchDims* dims,
                     bool* needs_align16);
-// programs the interpreting kernel cannot run (64-bit integer values): they need the run-time compiler
+// Checked launches of generated kernels (AKGB_FLAG_CHECKED): the address ranges of the launch's tensors and workspace.
+// While a table is set for the calling thread, generated kernels are built with every global access tested against it
+// (outside all ranges: bit 9 of the error word, the access skipped).  Layout shared with the generated source.
+struct CheckedRanges {
+  unsigned long long lo[32], hi[32];
+  int n = 0;
+  uint32_t* err = nullptr;
+};
+void jit_set_checked_ranges(const CheckedRanges* r);
+// programs the interpreting kernel cannot run (64-bit integer or float64 values): they need the run-time compiler
 bool ew_program_needs_jit(const EwProgram& p);
 void ew_jit_prepare(const EwProgram& p);
 void row_jit_prepare(const RowProgram& p);

@@ -55,6 +55,8 @@ struct Plan {
   // for good if the kernel cannot be generated or compiled on this host.
   std::shared_ptr<Plan> fallback;
   bool use_fallback = false;
+  // bytes of every argument (inputs then outputs) of the graph this plan was built for: the ranges of checked launches
+  std::vector<size_t> arg_bytes;
 };
 
 // Pattern matcher: places the region on kernel templates or throws Unsupported.

@@ -36,7 +36,8 @@ typedef enum akgb_status {
   AKGB_CUDA_ERROR = 4,     /* a CUDA runtime/driver call failed; see akgb_last_error() */
   AKGB_MISALIGNED = 5,     /* a tensor pointer is not 16-byte aligned */
   AKGB_DEVICE_TIMEOUT = 6, /* a bounded device-side wait gave up (error word set) */
-  AKGB_TOO_LARGE = 7       /* size beyond a fixed-capacity entry point's limit */
+  AKGB_TOO_LARGE = 7,      /* size beyond a fixed-capacity entry point's limit */
+  AKGB_OUT_OF_RANGE = 8    /* a checked launch (AKGB_FLAG_CHECKED) reported an access outside its tensors */
 } akgb_status;
 
 /* Element types of the .info schema (TranslateToMindsporeDialect.cpp:488-502). */
@@ -98,6 +99,12 @@ typedef struct akgb_options {
  * memory -- so the row crosses HBM/L2 once.  Identical results.  Measured on B200 the L2 schedule is the faster one
  * (log-softmax float32 [8192,32000]: 415 us against 523 us staged), which is why this is opt-in. */
 #define AKGB_FLAG_STAGE_LONG_ROWS 4
+/* Checked launches (memory-safety evidence where compute-sanitizer is not available): kernels generated at run time
+ * are built with every access to global memory tested against the address ranges of the launch's tensors and
+ * workspace.  An access outside all of them sets bit 9 (512) of the device error word (akgb_check_device_error) and is
+ * skipped -- a load gives zeros; nothing asserts or traps.  The kernel templates built into the library are not
+ * instrumented (their tests run with guard zones around every buffer instead).  Slower; for tests. */
+#define AKGB_FLAG_CHECKED 8
 
 typedef struct akgb_kernel akgb_kernel;
 
@@ -278,6 +285,10 @@ const char* akgb_kernel_class(const akgb_kernel* k);
  * floating-point operations (2*M*N*K for matmul, else 0) of one launch. */
 int64_t akgb_kernel_bytes(const akgb_kernel* k);
 int64_t akgb_kernel_flops(const akgb_kernel* k);
+
+/* For tests of the checker itself: take `bytes` off the end of every tensor range of subsequent checked launches of
+ * this process (0 restores).  The accesses then reported and skipped lie inside the real tensors. */
+void akgb_checked_shrink_for_test(int bytes);
 
 /* Reads and clears the device-side error word of the last launches of `k`
  * (bounded waits that gave up).  0 = none. */

@@ -84,7 +84,7 @@ def random_region(seed, long_rows=False):
 
 
 @pytest.mark.parametrize("seed", range(40))
-@pytest.mark.parametrize("flags", [0, 1], ids=["generated", "separate"])
+@pytest.mark.parametrize("flags", [0, 1, 8], ids=["generated", "separate", "generated-checked"])
 def test_random_region(seed, flags):
     desc, ins, io_dtype = random_region(seed)
     k = FusedKernel(desc, flags=flags)
@@ -110,7 +110,8 @@ def test_random_region(seed, flags):
 def test_random_long_row_region(seed):
     """The same random regions on rows of 16K-64K elements: the generated kernel walks the row once per reduction."""
     desc, ins, io_dtype = random_region(seed, long_rows=True)
-    k = FusedKernel(desc)
+    # odd seeds run the checked build: every global access of the generated kernels range-tested, error word 0 below
+    k = FusedKernel(desc, flags=8 if seed % 2 else 0)
     has_reduce = any(op["name"].startswith("Reduce") for op in desc["op_desc"])
     sums_rows = any(op["name"] == "ReduceSum" and len(op["output_desc"][0]["shape"]) == 1 for op in desc["op_desc"])
     cols = desc["input_desc"][0][0]["shape"][-1]

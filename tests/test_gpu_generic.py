@@ -16,23 +16,32 @@ pytestmark = pytest.mark.gpu
 
 
 FLAGS = [0]  # set by the fixture below: 0 = run-time instantiated elementwise kernels, 1 = interpreter only
+CHECKED = [0]  # 8 = generated kernels built with every global access range-tested (AKGB_FLAG_CHECKED)
 
 
-@pytest.fixture(autouse=True, params=[0, 1], ids=["jit", "interp"])
+def _flags():
+    return FLAGS[0] | CHECKED[0]
+
+
+@pytest.fixture(autouse=True, params=[(0, 0), (1, 0), (0, 8)], ids=["jit", "interp", "jit-checked"])
 def _both_elementwise_paths(request):
-    FLAGS[0] = request.param
+    """Every test of this file runs three times: generated kernels, the interpreting kernel, and generated kernels in
+    the checked build -- there every load and store is tested against the ranges of the launch's tensors, and `run`
+    requires the device error word to stay 0 (bit 9 would report an access outside them)."""
+    FLAGS[0], CHECKED[0] = request.param
     yield
+    FLAGS[0], CHECKED[0] = 0, 0
 
 
 def run(desc, ins):
-    k = FusedKernel(desc, flags=FLAGS[0])
+    k = FusedKernel(desc, flags=_flags())
     outs = k.empty_outputs()
     for o in outs:
         o.view(np.uint8)[...] = 0xCD
     k.run_host(list(ins) + outs)
     assert k.check_device_error() == 0
     # the same region as a device launch between guard zones: same bits, nothing written outside the tensors
-    guarded, _ = guarded_launch(desc, ins, flags=FLAGS[0])
+    guarded, _ = guarded_launch(desc, ins, flags=_flags())
     atomics = any(op["name"] == "UnsortedSegmentSum" for op in desc["op_desc"])  # float atomics: order varies
     for a, b in zip(outs, guarded):
         assert atomics or np.array_equal(np.ascontiguousarray(a).view(np.uint8).reshape(-1), b.view(np.uint8).reshape(-1))
@@ -392,6 +401,46 @@ def test_float64_values_run_in_generated_kernels(lib):
     check(d, [rng.standard_normal((37, 13)) * 3], rtol=1e-14, atol=1e-15)
 
 
+def test_checked_build_reports_and_skips_accesses_outside_the_ranges(lib):
+    """The checker itself: with 16 bytes taken off the end of every tensor range (a test hook; the tensors themselves
+    keep their size) a checked launch sets bit 9 of the error word, leaves the last 16 bytes of the output untouched
+    (the last 16 bytes of every input read as zeros) and everything those bytes do not feed correct; with the hook off the same kernel runs clean.  No access leaves a real tensor."""
+    import ctypes
+    import torch
+    from akg_b200 import _capi
+    if FLAGS[0] != 0 or CHECKED[0] == 0:
+        pytest.skip("one mode is enough")
+    libc = _capi.load()
+    # (region, output shape, rows and columns at the end that the zeros read from the shrunk INPUT ranges may change:
+    # the copy's last 4 elements; RMSNorm's last row and, through the last 4 weights, the last 4 columns of every row)
+    for build, shape, rows_off, cols_off in ((lambda: descs.scale_copy([1, 65536]), (1, 65536), 0, 4),
+                                             (lambda: descs.rmsnorm(48, 1024), (48, 1024), 1, 4)):
+        d = build()
+        k = FusedKernel(d, flags=8)
+        ins = [torch.from_numpy(a).cuda() for a in make_inputs(d, 5)]
+        want = torch.empty(shape, dtype=torch.float32, device="cuda")
+        k.launch(ins + [want])
+        torch.cuda.synchronize()
+        assert k.check_device_error() == 0
+        got = torch.full(shape, -7.0, dtype=torch.float32, device="cuda")
+        libc.akgb_checked_shrink_for_test(16)
+        try:
+            k.launch(ins + [got])
+            torch.cuda.synchronize()
+            word = ctypes.c_uint32(0)
+            status = libc.akgb_check_device_error(k._handle, ctypes.byref(word))
+        finally:
+            libc.akgb_checked_shrink_for_test(0)
+        assert status == 8 and word.value == 512  # AKGB_OUT_OF_RANGE
+        g, w = got.flatten(), want.flatten()
+        assert torch.equal(g[-4:], torch.full((4,), -7.0, device="cuda"))
+        r_end = shape[0] - rows_off
+        assert torch.equal(got[:r_end, :-cols_off], want[:r_end, :-cols_off])
+        k.launch(ins + [got])
+        torch.cuda.synchronize()
+        assert k.check_device_error() == 0 and torch.equal(got, want)
+
+
 def _cast_desc(dst):
     b = _Builder(f"Fused_CastTo_{dst}_14")
     x = b.input("x", [4096], "float32")
@@ -512,7 +561,7 @@ def test_dynamic_shapes_match_the_static_plan(lib):
         b.output(b.emit("Cast", [t], [32, 16, s2, s3], "float16", [_attr("dst_type", "str", "float16")]))
         return b.build()
 
-    kd = FusedKernel(region(-1, -1), flags=FLAGS[0])
+    kd = FusedKernel(region(-1, -1), flags=_flags())
     assert kd.is_dynamic
     for s2, s3 in ((40, 24), (7, 129)):
         static = region(s2, s3)
@@ -527,7 +576,7 @@ def test_dynamic_shapes_match_the_static_plan(lib):
     for desc_dyn, desc_static, kinds in (
             (descs.masked_softmax(-1, -1, 256), descs.masked_softmax(6, 32, 256), {"mask": "causal"}),
             (descs.layernorm(-1, 512), descs.layernorm(96, 512), {"gamma": "gamma", "beta": "beta"})):
-        k = FusedKernel(desc_dyn, flags=FLAGS[0])
+        k = FusedKernel(desc_dyn, flags=_flags())
         ins = make_inputs(desc_static, 41, kinds)
         want = O.evaluate(desc_static, ins)
         dev = [torch.from_numpy(a).cuda() for a in ins]
@@ -547,7 +596,7 @@ def test_assign_writes_the_input_in_place(lib):
     t = b.emit("Add", [x, b.const(1, i)], [1], i)
     b.output(b.emit("Assign", [x, t], [1], i))
     d = b.build()
-    k = FusedKernel(d, flags=FLAGS[0])
+    k = FusedKernel(d, flags=_flags())
     assert k.inputs[0].written_in_place
     xin = np.array([41], dtype=np.int32)
     out = np.zeros(1, np.int32)
@@ -568,7 +617,7 @@ def test_assign_writes_the_input_in_place(lib):
     ins = [rng.standard_normal((300, 40)).astype(np.float32), rng.standard_normal((300, 40)).astype(np.float32),
            rng.integers(0, 2, (300, 40)).astype(bool)]
     want_out, want_in = O.evaluate(d, [a.copy() for a in ins], return_inputs=True)
-    k = FusedKernel(d, flags=FLAGS[0])
+    k = FusedKernel(d, flags=_flags())
     host = [a.copy() for a in ins] + k.empty_outputs()
     k.run_host(host)
     assert bits_equal(host[3], want_out[0]) and bits_equal(host[0], want_in[0])
@@ -970,7 +1019,7 @@ def test_prepare_allows_capturing_the_first_launch(lib):
     """After prepare() the first launch of a region with generated kernels can be recorded into a CUDA graph."""
     import torch
     d = _rows_region("rmsnorm", [64], 512)
-    k = FusedKernel(d, flags=FLAGS[0])
+    k = FusedKernel(d, flags=_flags())
     k.prepare()
     x = torch.randn(64, 512, device="cuda")
     g_ = torch.rand(512, device="cuda") + 0.5
