@@ -226,6 +226,7 @@ __device__ __forceinline__ void st1_i8(void* p, i64 i, int v) { AKGB_CHKV((u8*)p
 __device__ __forceinline__ void st1_bool(void* p, i64 i, int v) { AKGB_CHKV((u8*)p + i, 1) ((u8*)p)[i] = v ? 1 : 0; }
 // 64-bit integers (programs that hold any keep ALL their integer registers in 64 bits)
 __device__ __forceinline__ i64 wr_i64(i64 x) { return x; }
+__device__ __forceinline__ i64 f2i_i64(float x) { return x != x ? 0 : __float2ll_rn(x); }  // saturating; NaN gives 0
 __device__ __forceinline__ i64 ld1_i64(const void* p, i64 i) { AKGB_CHK((const i64*)p + i, 8, 0) return ((const i64*)p)[i]; }
 __device__ __forceinline__ void st1_i64(void* p, i64 i, i64 v) { AKGB_CHKV((i64*)p + i, 8) ((i64*)p)[i] = v; }
 __device__ __forceinline__ void ld8_i64(const void* p, i64 e0, i64* r, bool stream) {
@@ -251,6 +252,7 @@ __device__ __forceinline__ double rn_f16_d(double x) { return (double)rn_f16(odd
 __device__ __forceinline__ double rn_bf16_d(double x) { return (double)rn_bf16(odd_f32(x)); }
 // (the conversion from a double NaN gives INT_MIN, not the 0 it gives from a float NaN)
 __device__ __forceinline__ int f2i_i32_d(double x) { return x != x ? 0 : __double2int_rn(x); }
+__device__ __forceinline__ i64 f2i_i64_d(double x) { return x != x ? 0 : __double2ll_rn(x); }
 __device__ __forceinline__ int f2i_i16_d(double x) { return max(-32768, min(32767, f2i_i32_d(x))); }
 __device__ __forceinline__ int f2i_i8_d(double x) { return max(-128, min(127, f2i_i32_d(x))); }
 __device__ __forceinline__ double mx_d(double a, double b) { return (a != a || b != b) ? __longlong_as_double(0x7ff8000000000000LL) : fmax(a, b); }
@@ -426,7 +428,7 @@ std::string instr_expr(int op, int dt, int cls, int src_cls, int a, int b, int c
   } else if (op == EW_CAST) {
     if (fl) expr = rnd + "(" + (sfl ? ref(a, true) : (f64 ? "(double)" : "(float)") + ref(a, false)) + ")";
     else if (cls == EWC_BOOL) expr = sfl ? "(" + ref(a, true) + " != 0.f ? 1 : 0)" : "(" + ref(a, false) + " != 0 ? 1 : 0)";
-    else if (sfl) expr = std::string((DT)dt == DT::I8 ? "f2i_i8" : (DT)dt == DT::I16 ? "f2i_i16" : "f2i_i32") + (f64 ? "_d(" : "(") + ref(a, true) + ")";
+    else if (sfl) expr = std::string((DT)dt == DT::I8 ? "f2i_i8" : (DT)dt == DT::I16 ? "f2i_i16" : (DT)dt == DT::I64 ? "f2i_i64" : "f2i_i32") + (f64 ? "_d(" : "(") + ref(a, true) + ")";
     else expr = std::string(wrap_fn(dt)) + "(" + ref(a, false) + ")";
   } else if (op <= EW_ACOS) {
     if (fl) expr = rnd + "(" + (f64 ? double_unary(op, ref(a, true)) : float_unary(op, ref(a, true))) + ")";

@@ -415,8 +415,6 @@ struct Builder {
       if (op == EW_SELECT) ins.src_cls = cls_of(g.v(n.in[1]).dt);
       // float -> integer Cast follows the reference's compiled route (tosa.cast: round to nearest even, clamp to the
       // result type; the expected-value generator would truncate like NumPy).  NaN gives 0.
-      if (op == EW_CAST && ins.src_cls == EWC_FLOAT && ins.cls == EWC_INT && out.dt == DT::I64)
-        throw Unsupported("Cast to int64: 64-bit integer values are not placed");
       int regs[3] = {0, 0, 0};
       const size_t nin = std::min<size_t>(n.in.size(), 3);
       for (size_t j = 0; j < nin; ++j) regs[j] = operand_reg(n.in[j]);

@@ -223,11 +223,17 @@ def evaluate(desc: dict | str, inputs: Sequence[np.ndarray], accum: str = "numpy
                     if odt.kind in "iu":
                         # the MLIR route (upstream tosa.cast): round to nearest even, clamp to the result type; the
                         # reference's NumPy generator would truncate instead.  NaN gives 0.
-                        if odt.itemsize > 4:
-                            raise NotImplementedError("float->int64 Cast is not restated")
                         x64 = np.nan_to_num(x.astype(np.float64), nan=0.0, posinf=np.inf, neginf=-np.inf)
                         info = np.iinfo(odt)
-                        r = np.clip(np.rint(x64), info.min, info.max).astype(odt)
+                        if odt.itemsize > 4:
+                            # 2^63 - 1 is no float64: saturate by comparison, convert only what is in range
+                            rr = np.rint(x64)
+                            hi, lo = rr >= 2.0 ** 63, rr <= -(2.0 ** 63)
+                            r = np.where(hi | lo, 0.0, rr).astype(odt)
+                            r[hi] = info.max
+                            r[lo] = info.min
+                        else:
+                            r = np.clip(np.rint(x64), info.min, info.max).astype(odt)
                     # widening is exact; narrowing rounds to nearest even (arith.truncf)
                     elif _is_low_float(x.dtype):
                         r = x.astype(np.float32).astype(odt)

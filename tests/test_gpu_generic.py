@@ -314,9 +314,19 @@ def test_float_to_int_cast_rounds_to_nearest_even_and_clamps(lib):
     got, _ = run(_cast_desc("int32"), [x])
     assert got[0][:6].tolist() == [0, 2, 2, 0, -2, -2] and got[0][14] == 2**31 - 1 and got[0][15] == -2**31
     assert got[0][18] == 0  # NaN
-    from akg_b200 import UnsupportedError
-    with pytest.raises(UnsupportedError):
-        FusedKernel(_cast_desc("int64"))
+    # to int64: a generated kernel (64-bit integer registers; the interpreting kernel has no such mode); saturates at
+    # +-2^63, from float32 and from float64
+    if FLAGS[0] == 0:
+        x64 = np.concatenate([x.astype(np.float64), np.array([9.3e18, -9.3e18, 2.0 ** 63, -(2.0 ** 63), 2.0 ** 62 + 1024,
+                                                              4503599627370497.5, 1e300, -1e300] + [0.0] * 8)])
+        for src, xv in (("float32", x), ("float64", x64)):
+            b = _Builder(f"Fused_CastToInt64_{src}_14")
+            xin = b.input("x", [xv.size], src)
+            b.output(b.emit("Cast", [xin], [xv.size], "int64", [_attr("dst_type", "str", "int64")]))
+            got, _ = run(b.build(), [xv])
+            want = O.evaluate(b.build(), [xv])[0]
+            assert got[0].dtype == np.int64 and np.array_equal(got[0], want)
+            assert got[0][16] == 2**63 - 1 and got[0][17] == -2**63 and got[0][18] == 0  # +inf, -inf, NaN
 
 
 def test_int64_values_run_in_generated_kernels(lib):
