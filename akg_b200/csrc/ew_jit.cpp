@@ -325,7 +325,8 @@ struct Var {
   bool is_float = true;
   bool is_const = false;
   std::string literal;
-  std::string literal64;  // the expression of a float64 constant
+  std::string literal64;      // the expression of a float64 constant
+  std::string int64_literal;  // the expression of a 64-bit integer constant outside the 32-bit range
 };
 
 std::string float_unary(int op, const std::string& a) {
@@ -577,9 +578,12 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
     char buf[64];
     std::snprintf(buf, sizeof(buf), "0x%08xu", P.const_bits[c]);
     v.literal = buf;
-    if (P.const_f64[c]) {
+    if (P.const_f64[c] == 1) {
       std::snprintf(buf, sizeof(buf), "__longlong_as_double(0x%08x%08xLL)", P.const_hi[c], P.const_bits[c]);
       v.literal64 = buf;
+    } else if (P.const_f64[c] == 2) {
+      std::snprintf(buf, sizeof(buf), "((long long)0x%08x%08xULL)", P.const_hi[c], P.const_bits[c]);
+      v.int64_literal = buf;
     }
     regs[P.const_reg[c]] = v;  // class decided at use (float bits or int)
   }
@@ -644,6 +648,7 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
     const Var& v = regs[reg];
     if (v.is_const && want_float && f64)
       return !v.literal64.empty() ? v.literal64 : "(double)__uint_as_float(" + v.literal + ")";
+    if (v.is_const && !want_float && !v.int64_literal.empty()) return v.int64_literal;
     if (v.is_const) return want_float ? "__uint_as_float(" + v.literal + ")" : (i64 ? "(long long)(int)" : "(int)") + v.literal;
     return v.name + "[u][j]";
   };

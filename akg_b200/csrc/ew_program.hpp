@@ -54,7 +54,7 @@ struct EwProgram {
   uint32_t const_bits[kEwMaxConst];  // already rounded to the constant's declared type
   uint8_t const_reg[kEwMaxConst];
   EwInstr instr[kEwMaxInstr];
-  // float64 constants: const_bits holds the low word of the double, const_hi the high word
+  // 64-bit constants: const_bits holds the low word, const_hi the high word; const_f64 = 1 a double, 2 a 64-bit integer
   uint32_t const_hi[kEwMaxConst];
   uint8_t const_f64[kEwMaxConst];
 };

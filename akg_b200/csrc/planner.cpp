@@ -242,6 +242,13 @@ struct Builder {
           P.const_bits[P.n_const] = (uint32_t)b;
           P.const_hi[P.n_const] = (uint32_t)(b >> 32);
           P.const_f64[P.n_const] = 1;
+        } else if (v.dt == DT::I64 && (v.cval[0] > 2147483647.0 || v.cval[0] < -2147483648.0)) {
+          // a 64-bit integer constant outside the 32-bit range (the description carries it as a number: exact to 2^53)
+          if (!(std::fabs(v.cval[0]) < 9.2e18)) throw Unsupported("64-bit integer constant out of range");
+          const uint64_t b = (uint64_t)(int64_t)std::llround(v.cval[0]);
+          P.const_bits[P.n_const] = (uint32_t)b;
+          P.const_hi[P.n_const] = (uint32_t)(b >> 32);
+          P.const_f64[P.n_const] = 2;
         } else {
           P.const_bits[P.n_const] = const_bits(v.cval[0], v.dt);
         }

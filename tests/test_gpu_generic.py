@@ -342,6 +342,7 @@ def test_int64_values_run_in_generated_kernels(lib):
     m = b.emit("Maximum", [t, zc], [64, 40], i64)
     gt = b.emit("Greater", [t, zc], [64, 40], "bool")
     sel = b.emit("Select", [gt, b.emit("Sub", [m, zc], [64, 40], i64), b.emit("Neg", [m], [64, 40], i64)], [64, 40], i64)
+    sel = b.emit("Sub", [sel, b.const(1099511627779, i64)], [64, 40], i64)  # a constant beyond 32 bits (2^40 + 3)
     b.output(sel)
     b.output(b.emit("Cast", [m], [64, 40], i32, [_attr("dst_type", "str", i32)]))
     b.output(gt)
