@@ -111,7 +111,30 @@ bool split_at_sharded_reductions(const Graph& g, StagePlan* out) {
     StageGraph sg;
     sg.g = g;
     sg.g.nodes.clear();
-    for (int i : take) sg.g.nodes.push_back(g.nodes[i]);  // std::set iterates in op order
+    // Small elementwise ops that depend only on inputs, completed partials and one another (mean = sum / n, the
+    // reciprocal standard deviation from the completed sum of squares) go first, in op order; then the rest, in op
+    // order.  In the description they sit between the full-size ops that use them, which would cut the stage into
+    // alternating small and large launches; hoisted, the stage is one small launch and one large one.
+    int64_t largest = 1;
+    for (int i : take) largest = std::max(largest, g.v(g.nodes[i].out).numel());
+    std::set<int> hoisted;
+    for (int i : take) {  // std::set iterates in op order, so producers are seen before their users
+      const Node& nd = g.nodes[i];
+      if (!opk_is_elementwise(nd.kind) || g.v(nd.out).numel() * 16 > largest) continue;
+      bool ok = true;
+      for (int vid : nd.in) {
+        const Value& v = g.v(vid);
+        if (v.is_const || v.producer < 0) continue;
+        const int p = v.producer;
+        if (cut[p] && stage[p] < t) continue;  // arrives completed
+        ok = ok && hoisted.count(p) != 0;
+      }
+      if (ok) hoisted.insert(i);
+    }
+    for (int i : take)
+      if (hoisted.count(i)) sg.g.nodes.push_back(g.nodes[i]);
+    for (int i : take)
+      if (!hoisted.count(i)) sg.g.nodes.push_back(g.nodes[i]);
     relink_values(sg.g);
     for (auto& v : sg.g.values) v.input_index = v.output_index = -1;
     sg.g.inputs.clear();
