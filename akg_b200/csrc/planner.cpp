@@ -1033,10 +1033,15 @@ struct Builder {
       int64_t largest = 1;
       for (auto& v : g.values) largest = std::max(largest, v.numel());
       std::vector<size_t> later;
+      std::set<int> early_nodes;  // chains of such ops too: an operand may be the result of an earlier early op
       for (size_t i = 0; i < g.nodes.size(); ++i) {
         const Node& n = g.nodes[i];
         bool early = opk_is_elementwise(n.kind) && n.kind != OpK::AddN && g.v(n.out).numel() * 4 <= largest;
-        for (int vid : n.in) early = early && (g.v(vid).is_const || g.v(root(vid)).input_index >= 0);  // also through views
+        for (int vid : n.in) {
+          const Value& rv = g.v(root(vid));  // also through views
+          early = early && (g.v(vid).is_const || rv.input_index >= 0 || (rv.producer >= 0 && early_nodes.count(rv.producer)));
+        }
+        if (early) early_nodes.insert((int)i);
         (early ? order : later).push_back(i);
       }
       order.insert(order.end(), later.begin(), later.end());
