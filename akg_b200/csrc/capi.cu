@@ -219,10 +219,11 @@ akgb_status run_plan(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws,
   }
   r.err = g_dev[k->device].err_word;
   if (plan.arg_bytes.size() > 31) return fail(AKGB_UNSUPPORTED, "checked launches take at most 31 tensors");
-  jit_set_checked_ranges(&r);
-  const akgb_status st = run_plan_steps(k, plan, tensors, ws, ws_bytes, s, fx, fx_step);
-  jit_set_checked_ranges(nullptr);
-  return st;
+  struct Scope {  // the table is gone from the thread again however the launches end
+    explicit Scope(const CheckedRanges* t) { jit_set_checked_ranges(t); }
+    ~Scope() { jit_set_checked_ranges(nullptr); }
+  } scope(&r);
+  return run_plan_steps(k, plan, tensors, ws, ws_bytes, s, fx, fx_step);
 }
 
 akgb_status run_plan_steps(akgb_kernel* k, Plan& plan, void* const* tensors, void* ws, size_t ws_bytes, cudaStream_t s,
