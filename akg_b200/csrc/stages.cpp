@@ -29,6 +29,33 @@ void relink_values(Graph& g) {
   }
 }
 
+// Drops the values the stage does not touch (the rest of the region, still at its unsplit shape: the planners look at
+// every value of a graph) and renumbers the others.
+void drop_unused_values(Graph& g) {
+  std::vector<int> remap(g.values.size(), -1);
+  std::vector<Value> kept;
+  auto keep = [&](int vid) {
+    if (remap[vid] < 0) {
+      remap[vid] = (int)kept.size();
+      kept.push_back(g.values[vid]);
+    }
+  };
+  for (int vid : g.inputs) keep(vid);
+  for (auto& nd : g.nodes) {
+    for (int vid : nd.in) keep(vid);
+    keep(nd.out);
+  }
+  for (int vid : g.outputs) keep(vid);
+  for (auto& nd : g.nodes) {
+    for (int& vid : nd.in) vid = remap[vid];
+    nd.out = remap[nd.out];
+  }
+  for (int& vid : g.inputs) vid = remap[vid];
+  for (int& vid : g.outputs) vid = remap[vid];
+  g.values = std::move(kept);
+  relink_values(g);
+}
+
 }  // namespace
 
 bool split_at_sharded_reductions(const Graph& g, StagePlan* out) {
@@ -175,6 +202,7 @@ bool split_at_sharded_reductions(const Graph& g, StagePlan* out) {
       sg.out_carried.push_back(ci);
     }
     sg.g.kernel_name = g.kernel_name + "_stage" + std::to_string(out->stages.size());
+    drop_unused_values(sg.g);
     classify(sg.g);
     out->stages.push_back(std::move(sg));
   }

@@ -397,6 +397,12 @@ def test_reductions_over_the_split_axis_that_feed_later_ops_run_as_stages(lib):
         assert sum(1 for s_ in ks.meta()["steps"] if s_.startswith("| ")) == stages - 1
         assert ks.outputs[0].shard_kind == _capi.SHARD_SPLIT_AXIS0
     assert FusedKernel(descs.scale_by_global_max(4096, 512), shard_rank=0, shard_world=4).outputs[1].shard_kind == _capi.SHARD_REPLICATED
+    # a stage is planned like a region of its own: the centred squares and their column sum are ONE generated kernel
+    # (no full-size value crosses memory), and the small per-channel ops of a stage come before its full-size ops
+    kn = FusedKernel(descs.normalise_over_axis0(8192, 512), shard_rank=0, shard_world=2)
+    assert "| akgb_col_jit" in kn.meta()["steps"] and kn.workspace_size < (1 << 20)
+    kt = FusedKernel(descs.batch_norm_training([64, 256, 56, 56]), shard_rank=0, shard_world=2)
+    assert kt.meta()["steps"][-2:] == ["| ew_generic", "ew_generic"] and kt.launch_count == 7
 
 
 def test_symbolic_shapes_bind_consistently(lib):
