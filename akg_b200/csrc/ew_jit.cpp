@@ -696,7 +696,7 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
     const bool fl = is_float_dt(o.dt);
     std::string src;
     if (v.is_const) {
-      const std::string cexpr = !fl ? "(int)" + v.literal
+      const std::string cexpr = !fl ? (!v.int64_literal.empty() ? v.int64_literal : "(int)" + v.literal)
                                 : f64 && !v.literal64.empty() ? v.literal64
                                                                : (f64 ? "(double)" : "") + ("__uint_as_float(" + v.literal + ")");
       t << "      " << (fl ? fty : ity) << " oc" << i << "[E];\n      #pragma unroll\n      for (int j = 0; j < E; ++j) oc"
