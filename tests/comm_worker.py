@@ -157,8 +157,48 @@ def main():
             ok = False
         except Exception:
             pass
+    # the staged regions at the benchmark's reduction size, [65536 / world, 4096] float32 per rank, timed like the
+    # reductions above (CUDA graph of 10 steps); checked through identities: the normalised columns have zero mean and
+    # unit variance over ALL ranks' rows, the softmax columns sum to one
+    staged_timings = {}
+    if peer:
+        for name, build in (("normalise_over_axis0", descs.normalise_over_axis0), ("softmax_over_axis0", descs.softmax_over_axis0)):
+            kst = FusedKernel(build(65536, 4096), device=local, shard_rank=rank, shard_world=world)
+            ok = ok and kst.op_class == "sharded_stages"
+            ost = [torch.empty(t.shape, dtype=torch.float32, device="cuda") for t in kst.outputs]
+            s = torch.cuda.Stream()
+            with torch.cuda.stream(s):
+                for _ in range(3):
+                    comm.launch_sharded(kst, [big] + ost, s)
+                s.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=s):
+                    for _ in range(10):
+                        comm.launch_sharded(kst, [big] + ost, torch.cuda.current_stream())
+                graph.replay()
+                torch.cuda.synchronize()
+                dist.barrier()
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record(s)
+                graph.replay()
+                t1.record(s)
+                torch.cuda.synchronize()
+            ok = ok and kst.check_device_error() == 0
+            staged_timings[name] = (t0.elapsed_time(t1) / 10 * 1e3, kst.launch_count)
+            y = ost[0].double()
+            col_sum = y.sum(0)
+            dist.all_reduce(col_sum)
+            if name == "softmax_over_axis0":
+                ok = ok and bool(torch.allclose(col_sum, torch.ones_like(col_sum), rtol=1e-4, atol=1e-4))
+            else:
+                col_sq = (y * y).sum(0)
+                dist.all_reduce(col_sq)
+                ok = ok and bool(col_sum.abs().max() < 1e-1) and bool(torch.allclose(col_sq / 65536, torch.ones_like(col_sq), rtol=1e-3))
     if rank == 0:
         print("PEER_EXCHANGE", "on" if peer else "off", flush=True)
+        for name, (us, launches) in sorted(staged_timings.items()):
+            print(f"TIMING staged {name} [65536/{world},4096] per rank, {launches} launches and the exchanges between the "
+                  f"stages: {us:.1f} us per step", flush=True)
         for (name, label), us in sorted(timings.items()):
             print(f"TIMING {name} [65536/{world},4096] per rank, exchange by {label}: {us:.1f} us per step", flush=True)
     flag = torch.tensor([1 if ok else 0], device="cuda")
