@@ -197,8 +197,8 @@ cudaError_t launch_vec_shape(const GeluChainParams& p, const void* x, const void
 }
 
 // CTA shapes measured at 4 / 8 / 16 / 32 / 64 x [512,4096] (0.07 - 1.07 GB, 20 launches in a graph): 512 threads x 2
-// vectors x 2 rounds 13.9 / 23.3 / 42.7 / 81.2 / 158.1 us; one vector per thread and round 12.9 / 22.8 / 42.4 / 81.0 /
-// 158.8 us; one round per CTA, or 256 threads, 7 - 25 % slower at every size (every CTA stages the table).  Small
+// vectors x 2 iterations 13.9 / 23.3 / 42.7 / 81.2 / 158.1 us; one vector per thread and iteration 12.9 / 22.8 / 42.4 /
+// 81.0 / 158.8 us; one iteration per CTA, or 256 threads, 7 - 25 % slower at every size (every CTA stages the table).  Small
 // launches, as a shard of a split tensor is, take the finer shape.
 template <bool BIAS, bool MUL, bool OUTF32>
 cudaError_t launch_vec(const GeluChainParams& p, const void* x, const void* bias, const void* y, void* out,
