@@ -320,6 +320,11 @@ const char* round_fn_d(int dt) {
 }
 const char* wrap_fn(int dt) { return (DT)dt == DT::I8 ? "wr_i8" : (DT)dt == DT::I16 ? "wr_i16" : (DT)dt == DT::I64 ? "wr_i64" : "wr_i32"; }
 
+// results of a 16-bit floating-point type over a whole granule: computed unrounded, then rounded two per instruction
+bool pair_rounded(bool vec, int op, int dt, int cls) {
+  return vec && cls == EWC_FLOAT && ((DT)dt == DT::F16 || (DT)dt == DT::BF16) && op != EW_COPY && op != EW_SELECT;
+}
+
 struct Var {
   std::string name;
   bool is_float = true;
@@ -658,8 +663,7 @@ bool generate(const EwProgram& P, bool vec, std::string* out) {
     const bool fl = ins.cls == EWC_FLOAT;
     std::string name = "t" + std::to_string(tcount++);
     // results of a 16-bit type: the granule is computed unrounded, then rounded two values per instruction
-    const bool pair_round = vec && !f64 && fl && ((DT)ins.dt == DT::F16 || (DT)ins.dt == DT::BF16) && ins.op != EW_COPY &&
-                            ins.op != EW_SELECT;
+    const bool pair_round = !f64 && pair_rounded(vec, ins.op, ins.dt, ins.cls);
     const std::string expr =
         instr_expr(ins.op, pair_round ? (int)DT::F32 : ins.dt, ins.cls, ins.src_cls, ins.a, ins.b, ins.c, ref, f64);
     s << "      " << (fl ? fty : ity) << " " << name << "[E];\n";
@@ -1055,9 +1059,11 @@ template <int OP> __device__ __forceinline__ float row_reduce_cl(float v, float*
     for (int k = 0; k < ni; ++k) {
       if (!need_instr[k]) continue;
       const RowInstr& x = P.instr[k];
-      const std::string expr = instr_expr(x.op, x.dt, x.cls, x.src_cls, x.a, x.b, x.c, ref);
+      const bool pr = pair_rounded(vec, x.op, x.dt, x.cls);
+      const std::string expr = instr_expr(x.op, pr ? (int)DT::F32 : x.dt, x.cls, x.src_cls, x.a, x.b, x.c, ref);
       s << "    " << (x.cls == EWC_FLOAT ? "float " : "int ") << name[x.dst] << "[VW];\n#pragma unroll\n    for (int j = 0; j < VW; ++j) "
         << name[x.dst] << "[j] = " << expr << ";\n";
+      if (pr) s << "    rn8_" << dt_tag(x.dt) << "(" << name[x.dst] << ");\n";
     }
     s << tail << "  }\n";
     // (every pass gives a thread the same columns, so a thread reads back only what it staged itself: no barrier)
@@ -1223,11 +1229,14 @@ template <int OP> __device__ __forceinline__ float row_reduce(float v, float* sm
       s << "    " << v << " = " << round_fn(x.dt) << "(row_reduce<" << x.red_op << ">(acc, sm));\n  }\n";
       continue;
     }
-    const std::string expr = instr_expr(x.op, x.dt, x.cls, x.src_cls, x.a, x.b, x.c, ref_full);
+    const bool pr = x.full && pair_rounded(vec, x.op, x.dt, x.cls);
+    const std::string expr = instr_expr(x.op, pr ? (int)DT::F32 : x.dt, x.cls, x.src_cls, x.a, x.b, x.c, ref_full);
     if (x.full) {
       s << "  " << (fl ? "float " : "int ") << v << "[NV][VW];\n";
       s << "#pragma unroll\n  for (int k = 0; k < NV; ++k) {\n#pragma unroll\n    for (int j = 0; j < VW; ++j) " << v
-        << "[k][j] = " << expr << ";\n  }\n";
+        << "[k][j] = " << expr << ";\n";
+      if (pr) s << "    rn8_" << dt_tag(x.dt) << "(" << v << "[k]);\n";
+      s << "  }\n";
     } else {
       s << "  const " << (fl ? "float " : "int ") << v << " = " << expr << ";\n";
     }
@@ -1357,10 +1366,12 @@ template <int OP> __device__ __forceinline__ float comb(float a, float b) {
     const bool fl = x.cls == EWC_FLOAT;
     const std::string v = "t" + std::to_string(k);
     name[x.dst] = v;
-    const std::string expr = instr_expr(x.op, x.dt, x.cls, x.src_cls, x.a, x.b, x.c, ref);
+    const bool pr = x.full && pair_rounded(vec, x.op, x.dt, x.cls);
+    const std::string expr = instr_expr(x.op, pr ? (int)DT::F32 : x.dt, x.cls, x.src_cls, x.a, x.b, x.c, ref);
     if (x.full) {
       s << "      " << (fl ? "float " : "int ") << v << "[VW];\n#pragma unroll\n      for (int j = 0; j < VW; ++j) " << v
         << "[j] = " << expr << ";\n";
+      if (pr) s << "      rn8_" << dt_tag(x.dt) << "(" << v << ");\n";
     } else {
       s << "      const " << (fl ? "float " : "int ") << v << " = " << expr << ";\n";
     }
