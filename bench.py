@@ -15,7 +15,10 @@ JSON line:
   cpu_baseline  the C restatement of the reference CPU pipeline on a bounded slice of the workload
   classes    one row per fused-op class of the benchmark definition (same timing rules); every row carries
              "checked": a sample of its outputs compared with the CPU oracle after (outside) the timed region
-  ceilings   plain copies of LayerNorm's 67 MB with the same buffer rotation and graph timing
+             (tensor rows also "sustained": the same graph replayed for about a second with the SM clock sampled,
+             step time x clock as "sm_mcycles_per_step")
+  ceilings   plain copies of LayerNorm's 67 MB with the same buffer rotation and graph timing, and cuBLAS on the
+             matmul class's own operands (measuring sticks: no class row runs them)
 
 With N > 1 (under torchrun) the FIXED benchmark shapes are split along their leading axis over the N ranks
 (strong scaling: per-GPU work shrinks with N); `value` is the full configuration's bytes over the slowest rank's
