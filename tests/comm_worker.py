@@ -13,6 +13,42 @@ from akg_b200 import FusedKernel, descs  # noqa: E402
 from akg_b200.sharding import Communicator  # noqa: E402
 
 
+def random_staged_region(seed, rows):
+    """A random region whose reductions over axis 0 (or over all elements) feed later ops: planned as stages when axis 0
+    is split over ranks.  Bounded ops only, so that the values stay finite."""
+    import numpy as np
+    from akg_b200.descs import _Builder, _reduce_attr
+    rng = np.random.default_rng(seed)
+    cols = int(rng.choice([40, 256, 1000]))
+    f = "float32"
+    b = _Builder("Fused_fuzz_stage_%d_1" % seed)
+    x = b.input("x", [rows, cols], f)
+    w = b.input("w", [cols], f) if rng.random() < 0.5 else None
+    cur, results = x, []
+    for _ in range(int(rng.integers(1, 4))):
+        for _ in range(int(rng.integers(0, 3))):
+            op = str(rng.choice(["Abs", "Neg", "Tanh", "Mul", "Add"]))
+            if op in ("Mul", "Add"):
+                other = w if (w is not None and rng.random() < 0.5) else b.const(float(rng.uniform(-1.5, 1.5)), f)
+                cur = b.emit(op, [cur, other], [rows, cols], f)
+            else:
+                cur = b.emit(op, [cur], [rows, cols], f)
+        keep = bool(rng.random() < 0.7)
+        axes = [0] if rng.random() < 0.8 else [0, 1]
+        shp = ([1, cols] if keep else [cols]) if axes == [0] else ([1, 1] if keep else [1])
+        red = b.emit(str(rng.choice(["ReduceSum", "ReduceMax", "ReduceMin"])), [cur], shp, f, _reduce_attr(axes, keep))
+        if rng.random() < 0.3:
+            results.append(red)
+        small = red
+        for _ in range(int(rng.integers(0, 3))):
+            small = b.emit("Mul", [small, b.const(float(rng.uniform(0.05, 0.5)), f)], shp, f)
+        cur = b.emit(str(rng.choice(["Sub", "Mul", "Add"])), [cur if rng.random() < 0.7 else x, small], [rows, cols], f)
+    results.append(cur)
+    for r in results:
+        b.output(r)
+    return b.build()
+
+
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -157,6 +193,28 @@ def main():
             ok = False
         except Exception:
             pass
+    # random regions of the same kind: chains over [rows, cols] with one to three reductions over the split axis (or
+    # over all elements) whose results, after small ops, flow back into the chain; against the oracle on the whole tensor
+    for seed in range(10):
+        d = random_staged_region(seed, 8 * world)
+        frng = np.random.default_rng(100 + seed)
+        full = [frng.standard_normal(t[0]["shape"], dtype=np.float32) for t in d["input_desc"]]
+        want = O.evaluate(d, full)
+        ks = FusedKernel(d, device=local, shard_rank=rank, shard_world=world)
+        ok = ok and ks.op_class == "sharded_stages"
+        lo, hi = 8 * rank, 8 * rank + 8
+        ins = [torch.from_numpy(np.ascontiguousarray(a[lo:hi] if t.shard_kind == 1 else a)).cuda()
+               for a, t in zip(full, ks.inputs)]
+        outs = [torch.empty(t.shape, dtype=torch.float32, device="cuda") for t in ks.outputs]
+        comm.launch_sharded(ks, ins + outs)
+        torch.cuda.synchronize()
+        ok = ok and ks.check_device_error() == 0
+        for o, w, t in zip(outs, want, ks.outputs):
+            w = w[lo:hi] if t.shard_kind == 1 else w
+            good = bool(np.allclose(o.cpu().numpy().reshape(w.shape), w, rtol=2e-4, atol=2e-4 * float(np.abs(w).max() + 1e-6)))
+            if not good and rank == 0:
+                print("FUZZ_STAGE_MISMATCH seed", seed, t.name, flush=True)
+            ok = ok and good
     # the staged regions at the benchmark's reduction size, [65536 / world, 4096] float32 per rank, timed like the
     # reductions above (CUDA graph of 10 steps); checked through identities: the normalised columns have zero mean and
     # unit variance over ALL ranks' rows, the softmax columns sum to one

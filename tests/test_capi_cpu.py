@@ -486,3 +486,26 @@ def test_float64_regions_plan_as_generated_kernels_only(lib):
     b.output(b.emit("ReduceSum", [x], [64, 1], f, _reduce_attr([1], True)))
     with pytest.raises(UnsupportedError):
         FusedKernel(b.build())
+
+
+def test_random_regions_with_reductions_over_the_split_axis_plan_as_stages(lib):
+    """Random chains with one to three reductions over axis 0 (or over all elements) that flow back into the chain:
+    unsplit they are ordinary kernels, split over 2 / 4 / 8 ranks they plan as stages with at least one exchange, and
+    the kernel the caller sees keeps the region's arguments.  (The same regions run against the oracle on 2+ GPUs in
+    tests/comm_worker.py.)"""
+    import importlib.util
+    import os
+    from akg_b200 import FusedKernel, _capi
+    spec = importlib.util.spec_from_file_location("comm_worker", os.path.join(os.path.dirname(__file__), "comm_worker.py"))
+    cw = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(cw)
+    for seed in range(60):
+        d = cw.random_staged_region(seed, 64)
+        assert FusedKernel(d).op_class != "sharded_stages"
+        for world in (2, 4, 8):
+            k = FusedKernel(d, shard_rank=world - 1, shard_world=world)
+            assert k.op_class == "sharded_stages", seed
+            assert sum(1 for s in k.meta()["steps"] if s.startswith("| ")) >= 1
+            assert k.inputs[0].shape[0] == 64 // world and k.inputs[0].shard_kind == _capi.SHARD_SPLIT_AXIS0
+            assert len(k.outputs) == len(d["output_desc"])
+            assert k.outputs[-1].shape[0] == 64 // world and k.outputs[-1].shard_kind == _capi.SHARD_SPLIT_AXIS0
