@@ -88,8 +88,14 @@ std::vector<int64_t> shape_of(const Json& d) {
   if (!d.contains("shape")) return {1};
   std::vector<int64_t> s = d.at("shape").as_int_list();
   if (s.empty()) s.push_back(1);
-  for (auto x : s)
+  // element counts are 64-bit throughout: a tensor of more than 2^46 elements (0.5 PB of float64) is refused here, so
+  // that no product of extents overflows further down
+  long double n = 1;
+  for (auto x : s) {
     if (x < -1) throw JsonError("negative extent");
+    if (x > 0) n *= (long double)x;
+  }
+  if (n > 70368744177664.0L) throw Unsupported("tensor of more than 2^46 elements");
   return s;
 }
 

@@ -509,3 +509,17 @@ def test_random_regions_with_reductions_over_the_split_axis_plan_as_stages(lib):
             assert k.inputs[0].shape[0] == 64 // world and k.inputs[0].shard_kind == _capi.SHARD_SPLIT_AXIS0
             assert len(k.outputs) == len(d["output_desc"])
             assert k.outputs[-1].shape[0] == 64 // world and k.outputs[-1].shard_kind == _capi.SHARD_SPLIT_AXIS0
+
+
+def test_descriptions_that_cannot_be_real_are_refused_not_planned(lib):
+    """Extents whose product would overflow the 64-bit element counts used throughout, and malformed texts: a status
+    and a message, never a crash (the reference exits the process on such input, code_template.py:47-56)."""
+    import copy
+    from akg_b200 import AkgbError, FusedKernel, UnsupportedError, descs
+    d = copy.deepcopy(descs.layernorm(64, 256))
+    d["input_desc"][0][0]["shape"] = [2 ** 40, 2 ** 30]
+    with pytest.raises(UnsupportedError):
+        FusedKernel(d)
+    for text in (b"", b"{", b"[]", b"null", b'{"op":1}', b"\xff\xfe\x00", b'{"a":' * 5000):
+        with pytest.raises(AkgbError):
+            FusedKernel(text)
