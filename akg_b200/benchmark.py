@@ -33,6 +33,8 @@ CASES = {
     "transpose_tile": (lambda s, dtype="float16": descs.transpose(s, list(range(len(s) - 2)) + [len(s) - 1, len(s) - 2],
                                                                   dtype), {}),
     "rmsnorm": (lambda s: descs.rmsnorm(s[0], s[1]), {"g": "gamma"}),
+    # softmax with every op in the tensor's 16-bit type (--dtype float16 / bfloat16): a generated row kernel
+    "softmax_typed": (lambda s, dtype="bfloat16": descs.softmax_rows_typed(s[0], s[1], dtype), {}),
     "mulsum_rows": (lambda s: descs.mul_reduce_sum(s[0], s[1], [0]), {}),
     "mulsum_all": (lambda s: descs.mul_reduce_sum(s[0], s[1], [0, 1]), {}),
     "layernorm_backward": (lambda s: descs.layer_norm_backward(s[0], s[1]), {"gamma": "gamma"}),
@@ -100,7 +102,7 @@ def main(argv=None):
     else:
         shape = [int(x) for x in args.shape.split(",") if x]
         build, kinds = CASES[args.case]
-        desc = build(shape, args.dtype) if args.dtype and args.case in ("matmul", "transpose_tile") else build(shape)
+        desc = build(shape, args.dtype) if args.dtype and args.case in ("matmul", "transpose_tile", "softmax_typed") else build(shape)
     torch.cuda.set_device(args.device)
     device = torch.device("cuda", args.device)
     k = FusedKernel(desc, device=args.device)

@@ -243,6 +243,18 @@ def rmsnorm(rows: int, cols: int, dtype: str = "float32", eps: float = 1e-6) -> 
     return b.build()
 
 
+def softmax_rows_typed(rows: int, cols: int, dtype: str = "bfloat16") -> dict:
+    """Softmax over the last axis with EVERY op in the tensor's own type (no widening casts): max, subtract, exp, sum,
+    divide each round to `dtype` -- a region of the reduce-X class that runs as a generated row kernel."""
+    b = _Builder(f"Fused_SoftmaxTyped_{dtype}_{rows}x{cols}_6")
+    x = b.input("x", [rows, cols], dtype)
+    m = b.emit("ReduceMax", [x], [rows, 1], dtype, _reduce_attr([1], True))
+    e = b.emit("Exp", [b.emit("Sub", [x, m], [rows, cols], dtype)], [rows, cols], dtype)
+    s_ = b.emit("ReduceSum", [e], [rows, 1], dtype, _reduce_attr([1], True))
+    b.output(b.emit("RealDiv", [e, s_], [rows, cols], dtype))
+    return b.build()
+
+
 def mul_reduce_sum(rows: int, cols: int, axes: Sequence[int]) -> dict:
     """sum over `axes` of x * y, both float32[rows, cols] (the shape of bias / scale gradients)."""
     f = "float32"
